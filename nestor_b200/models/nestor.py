@@ -1,0 +1,300 @@
+"""The Nestor decoder: blocks of column-routed attention + expert MLPs joined by depth reads.
+
+Forward semantics follow the reference's registered-experiment path
+(``nestor/backbones/nestor.py``: block ``:9295-9642``, column layer ``:7327-7533`` and
+``:7804-7909``, Kimi layer ``:6952-7034``, backbone ``:10244-10440``):
+
+* A block runs its group router once; slot ``j`` of a token owns column ``idx[j]`` for
+  the whole block. Each token carries ``k`` residual streams plus their running mean.
+* A column layer reads ``h = DepthRead([x0, agg_1.., running])``, normalises, runs
+  column attention into the ``k`` slots, reads again with ``running + mean(attn)``,
+  normalises, runs the hybrid expert pool (private experts per slot, public experts
+  broadcast), and adds both updates to the streams with no residual multiplier.
+* A block exports its ``k`` deviations ``s_j - agg`` and the aggregate ``agg``; sublayer
+  reads see only the aggregates, the final head read sees every export.
+* Baseline (Kimi) blocks are the single-column special case with a plain running sum.
+
+All tensors are flattened to ``[T, ...]`` with ``T = B * S``; residual streams are fp32
+and matrix products run in the compute dtype ``cd``.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Any
+
+import torch
+from torch import Tensor, nn
+
+from nestor_b200 import ops
+from nestor_b200.configs.model import BlockSpec, NestorConfig, ReferenceMupConfig
+from nestor_b200.models.modules import (
+    ColumnProjections, DenseExpert, DepthRead, ExpertBank, Matrix, Norm, RouterParams,
+)
+from nestor_b200.models.tags import ADAMW_DECAY
+
+
+class InitScales:
+    """Initialisation constants of one model (reference muP: ``reference_mup.py:126-127``)."""
+
+    def __init__(self, mup: ReferenceMupConfig | None, dim: int, total_layers: int) -> None:
+        if mup is not None:
+            self.matrix = mup.initializer_range / math.sqrt(mup.width_multiplier)
+            self.output = self.matrix / math.sqrt(2 * mup.num_layers)
+            self.router = self.matrix
+            self.table = mup.initializer_range
+            self.norm_eps = mup.norm_eps
+        else:
+            self.matrix = 1.0 / math.sqrt(dim)
+            self.output = self.matrix / math.sqrt(2 * total_layers)
+            self.router = self.matrix
+            self.table = 1.0
+            self.norm_eps = 1e-6
+
+
+class ExpertPool(nn.Module):
+    """Hybrid pool: ``P`` public experts + ``Q`` private experts per column + 2-logit path gate."""
+
+    def __init__(self, s: BlockSpec, init: InitScales) -> None:
+        super().__init__()
+        self.spec = s
+        mk = lambda c, k, mode: RouterParams(  # noqa: E731
+            s.dim, c, k, std=init.router, gate_mode=mode, loss_free=s.loss_free, bias_rate=s.bias_rate)
+        self.public_router = mk(s.P, s.k_p, "renorm")
+        self.private_routers = nn.ModuleList([mk(s.Q, s.k_q, s.private_gate) for _ in range(s.G)])
+        self.path_gate = Matrix(s.dim, 2, ADAMW_DECAY, init.matrix)
+        self.stacked_public = ExpertBank(s.P, s.dim, s.h_pub, init.matrix, init.output)
+        self.stacked_private = ExpertBank(s.G * s.Q, s.dim, s.h_priv, init.matrix, init.output)
+
+    def private_router_weight(self) -> Tensor:
+        """``[G*Q, d]``: the ``G`` single-matrix private routers stacked (one batched GEMM)."""
+
+        return torch.cat([r.score_mlp.layers[0].weight for r in self.private_routers], dim=0)
+
+    def private_bias(self) -> Tensor:
+        return torch.stack([r.choice_bias for r in self.private_routers], dim=0)
+
+    def forward(self, n: Tensor, idx: Tensor, gates: Tensor, cd: torch.dtype) -> tuple[Tensor, Tensor, dict]:
+        """``n [T, d]`` -> ``(public [T, d], private [T, k, d], aux)``, both already path-weighted."""
+
+        s = self.spec
+        T = n.shape[0]
+        pub_scores = ops.router_scores(n, None, self.public_router.score_mlp.layers[0].weight, cd)
+        pub_idx, pub_gate = ops.route_topk(pub_scores, self.public_router.choice_bias, s.k_p, "renorm")
+        priv_scores = ops.router_scores(n, None, self.private_router_weight(), cd).view(T, s.G, s.Q)
+        col = idx.long()                                                     # [T, k] selected columns
+        sel_scores = priv_scores.gather(1, col.unsqueeze(-1).expand(-1, -1, s.Q))       # [T, k, Q]
+        sel_bias = self.private_bias()[col]                                  # [T, k, Q]
+        priv_idx, priv_gate = ops.route_topk(sel_scores, sel_bias, s.k_q, s.private_gate)  # [T, k, k_q]
+        priv_ids = (col.unsqueeze(-1) * s.Q + priv_idx).reshape(T, s.k * s.k_q)
+        priv_w = (priv_gate.to(cd) * gates.to(cd).unsqueeze(-1)).reshape(T, s.k * s.k_q)
+        path = torch.softmax(ops.router_scores(n, None, self.path_gate.weight, cd).float(), dim=-1).to(cd)
+
+        pub_plan = ops.build_expert_plan(pub_idx, s.P)
+        public = ops.expert_bank(n, pub_plan, pub_gate.to(cd), self.stacked_public.w_up,
+                                 self.stacked_public.w_gate, self.stacked_public.w_down, cd, group=s.k_p)
+        priv_plan = ops.build_expert_plan(priv_ids, s.G * s.Q)
+        private = ops.expert_bank(n, priv_plan, priv_w, self.stacked_private.w_up,
+                                  self.stacked_private.w_gate, self.stacked_private.w_down, cd, group=s.k_q)
+        public = (path[:, 0:1].float() * public[:, 0]).to(cd).float()
+        private = (path[:, 1:2].float().unsqueeze(-1) * private).to(cd).float()
+        aux = {"public_idx": pub_idx, "private_idx": priv_idx, "columns": idx}
+        return public, private, aux
+
+
+class Layer(nn.Module):
+    """One transformer layer (attention half + expert half) of a block."""
+
+    def __init__(self, s: BlockSpec, init: InitScales, max_sources: int, dense_no_router: bool) -> None:
+        super().__init__()
+        self.spec = s
+        self.attn_norm = Norm(s.dim, init.norm_eps)
+        self.mlp_norm = Norm(s.dim, init.norm_eps)
+        self.kimi_attn_read = DepthRead(s.dim, max_sources)
+        self.kimi_mlp_read = DepthRead(s.dim, max_sources)
+        self.attention_groups = nn.ModuleList(
+            [ColumnProjections(s.dim, s.inner, init.matrix, init.output) for _ in range(s.G)])
+        self.expert_pool: ExpertPool | None = None
+        self.expert_router: RouterParams | None = None
+        self.stacked_moe_bank: ExpertBank | None = None
+        self.shared_experts: nn.ModuleList | None = None
+        if s.pool:
+            self.expert_pool = ExpertPool(s, init)
+        else:
+            self.expert_router = RouterParams(
+                s.dim, s.bank_experts, s.bank_top_k, std=init.router,
+                loss_free=s.loss_free, bias_rate=s.bias_rate)
+            if s.bank_experts == 1:
+                # A one-choice gate is the constant 1.0: the router can never receive a
+                # gradient, so it is frozen (and, with dense_no_router, skipped entirely).
+                self.expert_router.requires_grad_(False)
+                self.shared_experts = nn.ModuleList([DenseExpert(s.dim, s.bank_width, init.matrix, init.output)])
+            else:
+                self.stacked_moe_bank = ExpertBank(s.bank_experts, s.dim, s.bank_width, init.matrix, init.output)
+        self.dense_no_router = dense_no_router
+
+    # -- weight views ---------------------------------------------------------------
+    def stacked(self, name: str) -> Tensor:
+        """``[G, ...]`` stack of one projection across columns."""
+
+        return torch.stack([getattr(g, name).weight for g in self.attention_groups], dim=0)
+
+    # -- halves -----------------------------------------------------------------------
+    def attention(self, n: Tensor, ctx: "BlockContext", cd: torch.dtype) -> Tensor:
+        s = self.spec
+        if s.G == 1:
+            g = self.attention_groups[0]
+            out = ops.dense_attention(n, ctx.B, ctx.S, g.q_proj.weight, g.k_proj.weight, g.v_proj.weight,
+                                      g.out_proj.weight, s.heads, s.head_dim, s.rope_base, cd, pos=ctx.pos)
+            return out.unsqueeze(1)
+        return ops.column_attention(
+            n, ctx.plan, ctx.gates, self.stacked("q_proj"), self.stacked("k_proj"), self.stacked("v_proj"),
+            self.stacked("out_proj"), s.heads, s.head_dim, s.rope_base, cd)
+
+    def experts(self, n: Tensor, ctx: "BlockContext", cd: torch.dtype) -> tuple[Tensor, dict]:
+        """Returns the expert update broadcastable against ``[T, k, d]`` and routing aux."""
+
+        s = self.spec
+        if self.expert_pool is not None:
+            public, private, aux = self.expert_pool(n, ctx.idx, ctx.gates, cd)
+            return private + public.unsqueeze(1), aux
+        if self.shared_experts is not None:
+            e = self.shared_experts[0]
+            out = ops.dense_swiglu(n, e.layers[0].weight, e.gate.weight, e.layers[1].weight, cd)
+            return out.unsqueeze(1), {}
+        scores = ops.router_scores(n, None, self.expert_router.score_mlp.layers[0].weight, cd)
+        idx, gate = ops.route_topk(scores, self.expert_router.choice_bias, s.bank_top_k, "renorm")
+        plan = ops.build_expert_plan(idx, s.bank_experts)
+        bank = self.stacked_moe_bank
+        ones = torch.ones_like(gate, dtype=cd)
+        rows = ops.expert_bank(n, plan, ones, bank.w_up, bank.w_gate, bank.w_down, cd, group=1)
+        out = (rows * gate.to(cd).float().unsqueeze(-1)).sum(dim=1).to(cd).float()
+        return out.unsqueeze(1), {"expert_idx": idx}
+
+
+class BlockContext:
+    """Per-block routing state shared by the block's layers."""
+
+    def __init__(self, B: int, S: int, idx: Tensor, gates: Tensor, plan: Any, pos: Tensor | None) -> None:
+        self.B, self.S, self.idx, self.gates, self.plan, self.pos = B, S, idx, gates, plan, pos
+
+
+class Block(nn.Module):
+    def __init__(self, s: BlockSpec, init: InitScales, max_sources: int, dense_no_router: bool) -> None:
+        super().__init__()
+        self.spec = s
+        self.group_router = RouterParams(
+            s.dim, s.G, s.k, hidden=s.router_hidden, score_lr_mul=s.layers ** -0.5,
+            loss_free=s.loss_free, bias_rate=s.bias_rate, noisy=True)
+        if s.G == 1:
+            self.group_router.requires_grad_(False)
+        self.layers = nn.ModuleList([Layer(s, init, max_sources, dense_no_router) for _ in range(s.layers)])
+
+    def route(self, x: Tensor, noise: Tensor | None, cd: torch.dtype) -> tuple[Tensor, Tensor]:
+        """Group router on the block input ``[T, d]`` -> ``(idx [T, k], gates [T, k] fp32)``."""
+
+        s = self.spec
+        T = x.shape[0]
+        if s.G == 1:
+            return (torch.zeros(T, 1, dtype=torch.int64, device=x.device),
+                    torch.ones(T, 1, dtype=torch.float32, device=x.device))
+        r = self.group_router
+        scores = ops.router_scores(x, *r.weights("score"), cd)
+        if self.training and r.noise_mlp is not None:
+            eps = torch.randn_like(scores) if noise is None else noise.to(scores.dtype)
+            scores = scores + eps * torch.nn.functional.softplus(ops.router_scores(x, *r.weights("noise"), cd))
+        return ops.route_topk(scores, r.choice_bias, s.k, "renorm")
+
+    def forward(self, x: Tensor, sources: list[Tensor], B: int, S: int, cd: torch.dtype,
+                pos: Tensor | None, column_mode: bool, noise: Tensor | None = None) -> tuple[list[Tensor], Tensor, dict]:
+        """Run the block. ``x [T, d]`` feeds the router; ``sources`` are the completed aggregates.
+
+        Returns ``(exports, aggregate, aux)``: the depth sources this block contributes (``k``
+        deviations then the aggregate in column mode with ``k > 1``; the aggregate alone
+        otherwise), the aggregate (next block's router input), and routing indices.
+        """
+
+        s = self.spec
+        idx, gates = self.route(x, noise, cd)
+        plan = ops.build_column_plan(idx.view(B, S, s.k), s.G, pos) if s.G > 1 else None
+        ctx = BlockContext(B, S, idx, gates, plan, pos)
+        streams: Tensor | None = None      # [T, k, d] fp32
+        running: Tensor | None = None      # [T, d] fp32 = mean_j streams
+        layer_aux = []
+        for layer in self.layers:
+            read = sources if running is None else [*sources, running]
+            h = ops.depth_read(read, layer.kimi_attn_read.query, layer.kimi_attn_read.value_gains,
+                               layer.kimi_attn_read.eps)
+            n = ops.rmsnorm(h, layer.attn_norm.weight, layer.attn_norm.eps, cd)
+            attn = layer.attention(n, ctx, cd)                                  # [T, k, d]
+            attn_mean = attn.mean(dim=1)
+            mid = attn_mean if running is None else running + attn_mean
+            h = ops.depth_read([*sources, mid], layer.kimi_mlp_read.query, layer.kimi_mlp_read.value_gains,
+                               layer.kimi_mlp_read.eps)
+            n = ops.rmsnorm(h, layer.mlp_norm.weight, layer.mlp_norm.eps, cd)
+            exp, aux = layer.experts(n, ctx, cd)
+            update = attn + exp
+            streams = update if streams is None else streams + update
+            step = update.mean(dim=1)
+            running = step if running is None else running + step
+            layer_aux.append(aux)
+        agg = streams.mean(dim=1)
+        if column_mode and s.k > 1:
+            exports = [*(streams - agg.unsqueeze(1)).unbind(dim=1), agg]
+        else:
+            exports = [agg]
+        return exports, agg, {"group_idx": idx, "layers": layer_aux}
+
+
+class Nestor(nn.Module):
+    """The backbone: blocks, the final head read over every export, the final RMSNorm."""
+
+    def __init__(self, config: NestorConfig, mup: ReferenceMupConfig | None = None,
+                 dense_no_router: bool = True) -> None:
+        super().__init__()
+        self.config = config
+        self.specs = config.resolve()
+        self.column_mode = config.column_mode
+        self.max_depth_sources = config.max_depth_sources()
+        init = InitScales(mup, config.input_dim, sum(s.layers for s in self.specs))
+        self.blocks = nn.ModuleList(
+            [Block(s, init, self.max_depth_sources, dense_no_router) for s in self.specs])
+        self.final_depth_read = DepthRead(config.output_dim, self.max_depth_sources)
+        self.final_norm = Norm(config.output_dim, init.norm_eps)
+        if self.column_mode and config.block_column_gain_init != 1.0:
+            # Head-read gains: deviation slots of every multi-column block start at the
+            # configured value (0 for the registered cells); embedding and aggregates stay 1.
+            g = torch.ones(self.max_depth_sources)
+            slot = 1
+            for s in self.specs:
+                if s.k > 1:
+                    g[slot : slot + s.k] = config.block_column_gain_init
+                slot += s.exports
+            with torch.no_grad():
+                self.final_depth_read.value_gains.copy_(g)
+
+    @property
+    def output_dim(self) -> int:
+        return self.config.output_dim
+
+    def forward(self, x0: Tensor, B: int, S: int, cd: torch.dtype, pos: Tensor | None = None,
+                noises: list[Tensor | None] | None = None) -> tuple[Tensor, dict]:
+        """``x0 [T, d]`` fp32 embeddings -> normalised head input ``[T, d]`` in ``cd`` + aux."""
+
+        narrow = [x0]            # what sublayer reads see: embedding + completed aggregates
+        wide = [x0]              # what the head read sees: every export
+        x = x0
+        aux = []
+        for i, block in enumerate(self.blocks):
+            exports, x, a = block(x, narrow, B, S, cd, pos, self.column_mode,
+                                  None if noises is None else noises[i])
+            wide.extend(exports)
+            narrow = [*narrow, x]
+            aux.append(a)
+        read_sources = wide if self.column_mode else narrow
+        h = ops.depth_read(read_sources, self.final_depth_read.query, self.final_depth_read.value_gains,
+                           self.final_depth_read.eps)
+        return ops.rmsnorm(h, self.final_norm.weight, self.final_norm.eps, cd), {"blocks": aux}
+
+    def routers(self) -> list[tuple[str, RouterParams]]:
+        return [(n, m) for n, m in self.named_modules() if isinstance(m, RouterParams)]

@@ -1,0 +1,129 @@
+"""``SequenceModel(adapter, backbone, head)`` and the ``Model.from_config`` factory.
+
+Parity targets: ``nestor/models/sequence.py:40-179`` (composition, fused head hand-off),
+``nestor/adapters/text.py:120-180`` (embedding x ``embedding_multiplier``, trivial-mask
+contract: pre-tokenised tensors carry no attention mask), ``nestor/heads/language_modeling.py:85-98``
+(``logits = projection(h) * logit_multiplier``).
+"""
+
+from __future__ import annotations
+
+import dataclasses as dc
+import os
+from typing import Any
+
+import torch
+from torch import Tensor, nn
+
+from nestor_b200 import ops
+from nestor_b200.configs.model import (
+    LanguageModelingHeadConfig, NestorConfig, ReferenceMupConfig, SequenceModelConfig, TextAdapterConfig,
+)
+from nestor_b200.models.modules import LayerStack, Matrix
+from nestor_b200.models.nestor import Nestor
+from nestor_b200.models.tags import ADAMW_DECAY, tag
+
+
+@dc.dataclass
+class ModelOutput:
+    """``pred``: logits ``[B, S, V]`` — or the head input ``[B, S, d]`` when the head is fused
+    into the loss — and ``aux``: routing indices per block plus the fused-head handle."""
+
+    pred: Tensor
+    aux: dict[str, Any]
+
+
+class TextAdapter(nn.Module):
+    """Token embedding table; output ``E[ids] * embedding_multiplier`` in fp32."""
+
+    def __init__(self, config: TextAdapterConfig, mup: ReferenceMupConfig | None) -> None:
+        super().__init__()
+        if config.vocab_size is None:
+            raise ValueError("TextAdapterConfig.vocab_size is required (token ids are the only input form).")
+        self.config = config
+        self.embed = nn.Embedding(config.vocab_size, config.embed_dim)
+        tag(self.embed.weight, ADAMW_DECAY)
+        std = mup.initializer_range if mup is not None else 1.0
+        nn.init.normal_(self.embed.weight, 0.0, std)
+        self.embedding_multiplier = mup.embedding_multiplier if mup is not None else 1.0
+
+    def forward(self, ids: Tensor) -> Tensor:
+        return self.embed(ids).float() * self.embedding_multiplier
+
+
+class LanguageModelingHead(nn.Module):
+    """Single-matrix unembedding ``[V, d]``; ``logit_multiplier = 1 / width_multiplier`` under muP."""
+
+    def __init__(self, config: LanguageModelingHeadConfig, dim: int, mup: ReferenceMupConfig | None) -> None:
+        super().__init__()
+        if config.hidden_dims:
+            raise ValueError("Only the single-matrix LM head is supported (hidden_dims must be empty).")
+        std = mup.initializer_range if mup is not None else 1.0 / dim
+        self.projection = LayerStack([Matrix(dim, config.vocab_size, ADAMW_DECAY, std)])
+        self.logit_multiplier = 1.0 / mup.width_multiplier if mup is not None else 1.0
+        self.vocab_size = config.vocab_size
+
+    @property
+    def weight(self) -> Tensor:
+        return self.projection.layers[0].weight
+
+    def forward(self, h: Tensor, cd: torch.dtype) -> Tensor:
+        return (h.to(cd) @ self.weight.to(cd).t()) * self.logit_multiplier
+
+
+class SequenceModel(nn.Module):
+    """adapter -> backbone -> head.
+
+    ``fused_head=True`` (the training default) returns the normalised head input as ``pred``
+    and exposes the head through ``aux["fused_head_module"]`` so the loss can run the
+    chunked head+cross-entropy without materialising ``[T, V]`` logits.
+    """
+
+    def __init__(self, config: SequenceModelConfig) -> None:
+        super().__init__()
+        self.config = config
+        mup = config.reference_mup
+        if not isinstance(config.adapter_config, TextAdapterConfig):
+            raise TypeError("SequenceModel needs a TextAdapterConfig.")
+        if not isinstance(config.backbone_config, NestorConfig):
+            raise TypeError("SequenceModel needs a NestorConfig backbone.")
+        if not isinstance(config.head_config, LanguageModelingHeadConfig):
+            raise TypeError("SequenceModel needs a LanguageModelingHeadConfig.")
+        if config.adapter_config.embed_dim != config.backbone_config.input_dim:
+            raise ValueError("adapter embed_dim must equal backbone input_dim.")
+        dense_no_router = os.environ.get("NESTOR_DENSE_NO_ROUTER", "1") == "1"
+        self.adapter = TextAdapter(config.adapter_config, mup)
+        self.backbone = Nestor(config.backbone_config, mup, dense_no_router=dense_no_router)
+        self.head = LanguageModelingHead(config.head_config, config.backbone_config.output_dim, mup)
+        self.fused_head = False
+        self.compute_dtype: torch.dtype | None = None
+
+    def resolve_compute_dtype(self, device: torch.device) -> torch.dtype:
+        if self.compute_dtype is not None:
+            return self.compute_dtype
+        return torch.bfloat16 if device.type == "cuda" else torch.float32
+
+    def forward(self, ids: Tensor, pos: Tensor | None = None, noises: list | None = None) -> ModelOutput:
+        B, S = ids.shape
+        cd = self.resolve_compute_dtype(ids.device)
+        x0 = self.adapter(ids).reshape(B * S, -1)
+        h, aux = self.backbone(x0, B, S, cd, pos=pos, noises=noises)
+        if self.fused_head:
+            aux["fused_head_module"] = self.head
+            return ModelOutput(pred=h.view(B, S, -1), aux=aux)
+        return ModelOutput(pred=self.head(h, cd).view(B, S, -1), aux=aux)
+
+    def fsdp2_wrap_order(self) -> list[nn.Module]:
+        """Sharding units, in gather order: adapter, each block, backbone tail, head, root."""
+
+        return [self.adapter, *self.backbone.blocks, self.backbone, self.head, self]
+
+
+class Model:
+    """Factory namespace: ``Model.from_config(SequenceModelConfig) -> SequenceModel``."""
+
+    @staticmethod
+    def from_config(config: Any) -> SequenceModel:
+        if isinstance(config, SequenceModelConfig):
+            return SequenceModel(config)
+        raise TypeError(f"Unknown model config {type(config).__name__}.")
