@@ -34,6 +34,22 @@ from nestor_b200.models.modules import (
 from nestor_b200.models.tags import ADAMW_DECAY
 
 
+def W(owner: nn.Module, p: Tensor) -> Tensor:
+    """Weight operand of ``p``: the arena's compute-dtype view when the model is arena-backed."""
+
+    arena = owner.__dict__.get("_nestor_arena")
+    return p if arena is None or not p.requires_grad else arena.compute_view(p)
+
+
+def Wstack(owner: nn.Module, params: list[Tensor]) -> Tensor:
+    """``[n, ...]`` operand over same-shape parameters (a strided arena view when possible)."""
+
+    arena = owner.__dict__.get("_nestor_arena")
+    if arena is None or not params[0].requires_grad:
+        return torch.stack(list(params), dim=0)
+    return arena.stack_view(params)
+
+
 class InitScales:
     """Initialisation constants of one model (reference muP: ``reference_mup.py:126-127``)."""
 
@@ -69,7 +85,8 @@ class ExpertPool(nn.Module):
     def private_router_weight(self) -> Tensor:
         """``[G*Q, d]``: the ``G`` single-matrix private routers stacked (one batched GEMM)."""
 
-        return torch.cat([r.score_mlp.layers[0].weight for r in self.private_routers], dim=0)
+        w = Wstack(self, [r.score_mlp.layers[0].weight for r in self.private_routers])
+        return w.reshape(-1, w.shape[-1])
 
     def private_bias(self) -> Tensor:
         return torch.stack([r.choice_bias for r in self.private_routers], dim=0)
@@ -79,7 +96,7 @@ class ExpertPool(nn.Module):
 
         s = self.spec
         T = n.shape[0]
-        pub_scores = ops.router_scores(n, None, self.public_router.score_mlp.layers[0].weight, cd)
+        pub_scores = ops.router_scores(n, None, W(self, self.public_router.score_mlp.layers[0].weight), cd)
         pub_idx, pub_gate = ops.route_topk(pub_scores, self.public_router.choice_bias, s.k_p, "renorm")
         priv_scores = ops.router_scores(n, None, self.private_router_weight(), cd).view(T, s.G, s.Q)
         col = idx.long()                                                     # [T, k] selected columns
@@ -88,14 +105,14 @@ class ExpertPool(nn.Module):
         priv_idx, priv_gate = ops.route_topk(sel_scores, sel_bias, s.k_q, s.private_gate)  # [T, k, k_q]
         priv_ids = (col.unsqueeze(-1) * s.Q + priv_idx).reshape(T, s.k * s.k_q)
         priv_w = (priv_gate.to(cd) * gates.to(cd).unsqueeze(-1)).reshape(T, s.k * s.k_q)
-        path = torch.softmax(ops.router_scores(n, None, self.path_gate.weight, cd).float(), dim=-1).to(cd)
+        path = torch.softmax(ops.router_scores(n, None, W(self, self.path_gate.weight), cd).float(), dim=-1).to(cd)
 
         pub_plan = ops.build_expert_plan(pub_idx, s.P)
-        public = ops.expert_bank(n, pub_plan, pub_gate.to(cd), self.stacked_public.w_up,
-                                 self.stacked_public.w_gate, self.stacked_public.w_down, cd, group=s.k_p)
+        public = ops.expert_bank(n, pub_plan, pub_gate.to(cd), W(self, self.stacked_public.w_up),
+                                 W(self, self.stacked_public.w_gate), W(self, self.stacked_public.w_down), cd, group=s.k_p)
         priv_plan = ops.build_expert_plan(priv_ids, s.G * s.Q)
-        private = ops.expert_bank(n, priv_plan, priv_w, self.stacked_private.w_up,
-                                  self.stacked_private.w_gate, self.stacked_private.w_down, cd, group=s.k_q)
+        private = ops.expert_bank(n, priv_plan, priv_w, W(self, self.stacked_private.w_up),
+                                  W(self, self.stacked_private.w_gate), W(self, self.stacked_private.w_down), cd, group=s.k_q)
         public = (path[:, 0:1].float() * public[:, 0]).to(cd).float()
         private = (path[:, 1:2].float().unsqueeze(-1) * private).to(cd).float()
         aux = {"public_idx": pub_idx, "private_idx": priv_idx, "columns": idx}
@@ -137,15 +154,15 @@ class Layer(nn.Module):
     def stacked(self, name: str) -> Tensor:
         """``[G, ...]`` stack of one projection across columns."""
 
-        return torch.stack([getattr(g, name).weight for g in self.attention_groups], dim=0)
+        return Wstack(self, [getattr(g, name).weight for g in self.attention_groups])
 
     # -- halves -----------------------------------------------------------------------
     def attention(self, n: Tensor, ctx: "BlockContext", cd: torch.dtype) -> Tensor:
         s = self.spec
         if s.G == 1:
             g = self.attention_groups[0]
-            out = ops.dense_attention(n, ctx.B, ctx.S, g.q_proj.weight, g.k_proj.weight, g.v_proj.weight,
-                                      g.out_proj.weight, s.heads, s.head_dim, s.rope_base, cd, pos=ctx.pos)
+            out = ops.dense_attention(n, ctx.B, ctx.S, W(self, g.q_proj.weight), W(self, g.k_proj.weight),
+                                      W(self, g.v_proj.weight), W(self, g.out_proj.weight), s.heads, s.head_dim, s.rope_base, cd, pos=ctx.pos)
             return out.unsqueeze(1)
         return ops.column_attention(
             n, ctx.plan, ctx.gates, self.stacked("q_proj"), self.stacked("k_proj"), self.stacked("v_proj"),
@@ -160,14 +177,14 @@ class Layer(nn.Module):
             return private + public.unsqueeze(1), aux
         if self.shared_experts is not None:
             e = self.shared_experts[0]
-            out = ops.dense_swiglu(n, e.layers[0].weight, e.gate.weight, e.layers[1].weight, cd)
+            out = ops.dense_swiglu(n, W(self, e.layers[0].weight), W(self, e.gate.weight), W(self, e.layers[1].weight), cd)
             return out.unsqueeze(1), {}
-        scores = ops.router_scores(n, None, self.expert_router.score_mlp.layers[0].weight, cd)
+        scores = ops.router_scores(n, None, W(self, self.expert_router.score_mlp.layers[0].weight), cd)
         idx, gate = ops.route_topk(scores, self.expert_router.choice_bias, s.bank_top_k, "renorm")
         plan = ops.build_expert_plan(idx, s.bank_experts)
         bank = self.stacked_moe_bank
         ones = torch.ones_like(gate, dtype=cd)
-        rows = ops.expert_bank(n, plan, ones, bank.w_up, bank.w_gate, bank.w_down, cd, group=1)
+        rows = ops.expert_bank(n, plan, ones, W(self, bank.w_up), W(self, bank.w_gate), W(self, bank.w_down), cd, group=1)
         out = (rows * gate.to(cd).float().unsqueeze(-1)).sum(dim=1).to(cd).float()
         return out.unsqueeze(1), {"expert_idx": idx}
 
@@ -199,10 +216,12 @@ class Block(nn.Module):
             return (torch.zeros(T, 1, dtype=torch.int64, device=x.device),
                     torch.ones(T, 1, dtype=torch.float32, device=x.device))
         r = self.group_router
-        scores = ops.router_scores(x, *r.weights("score"), cd)
+        w1, w2 = r.weights("score")
+        scores = ops.router_scores(x, W(self, w1), W(self, w2), cd)
         if self.training and r.noise_mlp is not None:
             eps = torch.randn_like(scores) if noise is None else noise.to(scores.dtype)
-            scores = scores + eps * torch.nn.functional.softplus(ops.router_scores(x, *r.weights("noise"), cd))
+            n1, n2 = r.weights("noise")
+            scores = scores + eps * torch.nn.functional.softplus(ops.router_scores(x, W(self, n1), W(self, n2), cd))
         return ops.route_topk(scores, r.choice_bias, s.k, "renorm")
 
     def forward(self, x: Tensor, sources: list[Tensor], B: int, S: int, cd: torch.dtype,
@@ -298,3 +317,70 @@ class Nestor(nn.Module):
 
     def routers(self) -> list[tuple[str, RouterParams]]:
         return [(n, m) for n, m in self.named_modules() if isinstance(m, RouterParams)]
+
+
+# ------------------------------------------------------------------ loss-free balancing
+
+
+def _count(idx: Tensor, n: int) -> Tensor:
+    """Histogram of ``idx`` over ``n`` bins without a host sync."""
+
+    flat = idx.reshape(-1).long()
+    return torch.zeros(n, dtype=torch.float32, device=idx.device).scatter_add_(
+        0, flat, torch.ones_like(flat, dtype=torch.float32))
+
+
+@torch.no_grad()
+def router_counts(backbone: Nestor, aux: dict) -> dict[str, Tensor]:
+    """Per-router selection counts of one forward, keyed by the router's module path.
+
+    Private routers count only tokens routed into their column (the reference passes each
+    private router the mask ``valid & member``, ``expert_pools.py:533-586``).
+    """
+
+    out: dict[str, Tensor] = {}
+    for b, (block, baux) in enumerate(zip(backbone.blocks, aux["blocks"])):
+        s = block.spec
+        if s.G > 1:
+            out[f"blocks.{b}.group_router"] = _count(baux["group_idx"], s.G)
+        for l, (layer, laux) in enumerate(zip(block.layers, baux["layers"])):
+            base = f"blocks.{b}.layers.{l}"
+            if layer.expert_pool is not None:
+                out[f"{base}.expert_pool.public_router"] = _count(laux["public_idx"], s.P)
+                flat = laux["columns"].long().unsqueeze(-1) * s.Q + laux["private_idx"].long()
+                per = _count(flat, s.G * s.Q).view(s.G, s.Q)
+                for g in range(s.G):
+                    out[f"{base}.expert_pool.private_routers.{g}"] = per[g]
+            elif "expert_idx" in laux:
+                out[f"{base}.expert_router"] = _count(laux["expert_idx"], s.bank_experts)
+    return out
+
+
+@torch.no_grad()
+def apply_bias_updates(backbone: Nestor, counts: dict[str, Tensor], *, global_counts: bool = False) -> None:
+    """Loss-free balancing nudge after an optimizer step: ``bias += rate * sign(mean(c) - c)``.
+
+    ``counts`` holds the window's summed selection counts per router (reference
+    ``nestor.py:596-634``). ``global_counts`` sums them over ranks first, which makes every
+    rank compute the same update (the ``NESTOR_LOSSFREE_GLOBAL_COUNTS`` behaviour) — all
+    routers travel in one packed all-reduce.
+    """
+
+    if not counts:
+        return
+    names = sorted(counts)
+    if global_counts and torch.distributed.is_available() and torch.distributed.is_initialized() \
+            and torch.distributed.get_world_size() > 1:
+        flat = torch.cat([counts[n].reshape(-1) for n in names])
+        torch.distributed.all_reduce(flat)
+        off = 0
+        for n in names:
+            k = counts[n].numel()
+            counts[n] = flat[off : off + k]
+            off += k
+    modules = dict(backbone.named_modules())
+    for n in names:
+        r = modules[n]
+        if r.loss_free and r.bias_rate:
+            c = counts[n]
+            r.choice_bias.add_(r.bias_rate * torch.sign(c.mean() - c))

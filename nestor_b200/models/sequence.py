@@ -20,7 +20,7 @@ from nestor_b200.configs.model import (
     LanguageModelingHeadConfig, NestorConfig, ReferenceMupConfig, SequenceModelConfig, TextAdapterConfig,
 )
 from nestor_b200.models.modules import LayerStack, Matrix
-from nestor_b200.models.nestor import Nestor
+from nestor_b200.models.nestor import Nestor, W
 from nestor_b200.models.tags import ADAMW_DECAY, tag
 
 
@@ -68,7 +68,7 @@ class LanguageModelingHead(nn.Module):
         return self.projection.layers[0].weight
 
     def forward(self, h: Tensor, cd: torch.dtype) -> Tensor:
-        return (h.to(cd) @ self.weight.to(cd).t()) * self.logit_multiplier
+        return (h.to(cd) @ W(self, self.weight).to(cd).t()) * self.logit_multiplier
 
 
 class SequenceModel(nn.Module):

@@ -357,12 +357,17 @@ def lm_head_ce(hidden: Tensor, weight: Tensor, targets: Tensor, multiplier: floa
     ``(loss_sum, num_valid)`` as fp32 / int64 scalars (tensors, no host sync).
     """
 
-    w = weight.to(cd)
+    from torch.utils.checkpoint import checkpoint
+
+    def chunk(h: Tensor, t: Tensor, w32: Tensor) -> Tensor:
+        logits = (h.to(cd) @ w32.to(cd).t()) * multiplier
+        return F.cross_entropy(logits.float(), t, ignore_index=ignore_index, reduction="sum")
+
     total = hidden.new_zeros((), dtype=torch.float32)
+    recompute = torch.is_grad_enabled() and (hidden.requires_grad or weight.requires_grad)
     for a in range(0, hidden.shape[0], chunk_rows):
-        logits = (hidden[a : a + chunk_rows].to(cd) @ w.t()) * multiplier
-        total = total + F.cross_entropy(logits.float(), targets[a : a + chunk_rows],
-                                        ignore_index=ignore_index, reduction="sum")
+        h, t = hidden[a : a + chunk_rows], targets[a : a + chunk_rows]
+        total = total + (checkpoint(chunk, h, t, weight, use_reentrant=False) if recompute else chunk(h, t, weight))
     return total, (targets != ignore_index).sum()
 
 

@@ -1,0 +1,354 @@
+"""The training loop.
+
+One optimizer step = ``grad_accum_steps`` micro-batches of forward+backward into the
+gradient arena, one data-parallel reduction, gradient clipping on the flat buffer, the
+Muon/AdamW step, a refresh of the compute copy, the scheduler step and the loss-free
+router-bias nudge. Behaviour parity with the reference's ``Trainer``
+(``nestor/train/trainer.py``): loss is scaled by ``1/accum`` per micro-batch (``:835-866``);
+clipping precedes the step (``:906-911``); bias nudges use the whole window's selections
+(``:1026-1128``); resume fast-forwards the loader by ``(step * accum) % batches_per_epoch``
+micro-batches (``:362-395``); ``NESTOR_RUNAHEAD`` bounds host run-ahead (``:467-479``);
+EMA shadow (``:960-1000``); MFU/throughput metrics (``:761-816``); per-phase wall timers
+under ``NESTOR_TRAIN_PROFILE`` and a ``torch.profiler`` window under ``NESTOR_TORCH_PROFILE``.
+
+What differs by design: gradients are never synchronised per micro-batch (there is no
+``no_sync`` context to manage), host<->device traffic is one pinned async copy in and one
+scalar out per logged step, and step timing is taken with CUDA events.
+"""
+
+from __future__ import annotations
+
+import collections
+import contextlib
+import logging
+import math
+import os
+import subprocess
+import time
+from pathlib import Path
+from typing import Any, Iterable
+
+import torch
+from torch import Tensor, nn
+
+from nestor_b200.configs import TrainJobConfig
+from nestor_b200.models.nestor import apply_bias_updates, router_counts
+from nestor_b200.parallel.arena import ParamArena
+from nestor_b200.parallel.grad_sync import GradReducer
+from nestor_b200.train import checkpoint as ckpt
+from nestor_b200.train.flops import train_flops_per_token
+from nestor_b200.train.losses import LossOutput, build_loss
+from nestor_b200.train.optim import build_optimizer, build_scheduler
+from nestor_b200.utils.distributed import get_rank, get_world_size, is_main_process
+from nestor_b200.utils.logging import get_logger, log_metrics
+from nestor_b200.utils.timing import PROCESS_START
+
+
+def _env_flag(name: str, default: str = "0") -> bool:
+    return os.environ.get(name, default) == "1"
+
+
+class Trainer:
+    def __init__(self, config: TrainJobConfig, model: nn.Module, train_loader: Iterable, *,
+                 device: torch.device, run_dir: Path | None = None, eval_suite: Any = None,
+                 logger: logging.Logger | None = None) -> None:
+        self.config, self.model, self.train_loader = config, model, train_loader
+        self.device, self.run_dir, self.eval_suite = device, run_dir, eval_suite
+        self.logger = logger or get_logger("nestor_b200.train")
+        self.world, self.rank = get_world_size(), get_rank()
+        bf16 = config.use_amp and device.type == "cuda" and os.environ.get("NESTOR_BF16", "1") == "1"
+        self.compute_dtype = torch.bfloat16 if bf16 else torch.float32
+        model.to(device)
+        model.compute_dtype = self.compute_dtype
+        model.fused_head = os.environ.get("NESTOR_FUSED_HEAD_CE", "1") == "1"
+        if _env_flag("NESTOR_FREEZE_ROUTERS"):
+            from nestor_b200.train.frozen_routers import freeze_routers
+            freeze_routers(model)
+        self.arena = ParamArena(model, compute_dtype=self.compute_dtype, device=device)
+        self.reducer = GradReducer(self.arena)
+        self.reducer.sync_buffers(model)
+        self.loss_fn = build_loss(config.loss)
+        self.optimizer = build_optimizer(config.optimizer, model)
+        self.scheduler = build_scheduler(config.scheduler, self.optimizer)
+        self.global_step, self.epoch = 0, 0
+        self.ema: dict[str, Tensor] | None = None
+        decay = os.environ.get("NESTOR_EMA_DECAY")
+        self.ema_decay = float(decay) if decay else config.ema_decay
+        if self.ema_decay:
+            self.ema = {"flat": self.arena.master.clone()}
+        self.runahead = int(os.environ.get("NESTOR_RUNAHEAD", "0"))
+        self._step_events: collections.deque = collections.deque()
+        self.global_counts = _env_flag("NESTOR_LOSSFREE_GLOBAL_COUNTS")
+        self.offload = _env_flag("NESTOR_ACTIVATION_OFFLOAD")
+        self.tokens_per_micro: int | None = None
+        self._oom_dumper = None
+        if _env_flag("NESTOR_DIAG_OOM_SNAPSHOT") and run_dir is not None:
+            from nestor_b200.train.oom_snapshot import install_oom_snapshot
+            self._oom_dumper = install_oom_snapshot(run_dir, rank=self.rank)
+
+    # ------------------------------------------------------------------ one micro-batch
+    def _to_device(self, batch: Any) -> tuple[Tensor, Tensor]:
+        inputs, targets = batch
+        inputs = inputs.to(self.device, non_blocking=True)
+        targets = inputs if targets is batch[0] else targets.to(self.device, non_blocking=True)
+        return inputs, targets
+
+    def _activation_ctx(self):
+        if self.offload and self.device.type == "cuda":
+            from nestor_b200.train.activation_offload import activation_offload
+            return activation_offload()
+        return contextlib.nullcontext()
+
+    def train_step(self, batch: Any) -> tuple[LossOutput, dict[str, Tensor]]:
+        """Forward + backward of one micro-batch; gradients accumulate into the arena."""
+
+        inputs, targets = self._to_device(batch)
+        self.tokens_per_micro = inputs.numel()
+        with self._activation_ctx():
+            out = self.model(inputs)
+            loss = self.loss_fn(out.pred, targets, out.aux)
+        (loss.total / self.config.grad_accum_steps).backward()
+        counts = router_counts(self.model.backbone, out.aux) if self.model.training else {}
+        return loss, counts
+
+    # ----------------------------------------------------------------- optimizer step
+    @torch.no_grad()
+    def clip_grad_norm(self, max_norm: float) -> Tensor:
+        """Global L2 clip on the flat gradient buffer (one reduction, one scale)."""
+
+        norm = torch.linalg.vector_norm(self.arena.grad)
+        scale = (max_norm / (norm + 1e-6)).clamp(max=1.0)
+        self.arena.grad.mul_(scale)
+        return norm
+
+    def update_weights(self, window_counts: dict[str, Tensor]) -> Tensor | None:
+        self.reducer.reduce()
+        norm = None
+        if self.config.max_grad_norm is not None:
+            norm = self.clip_grad_norm(self.config.max_grad_norm)
+        if _env_flag("NESTOR_DEBUG_GRAD") and self.global_step < 5 and is_main_process():
+            g = self.arena.grad
+            self.logger.info("[grad] step %d norm=%s finite=%s absmax=%.3e", self.global_step,
+                             None if norm is None else f"{norm.item():.4e}",
+                             bool(torch.isfinite(g).all().item()), g.abs().max().item())
+        self.optimizer.step()
+        self.arena.refresh_compute()
+        self.arena.zero_grad()
+        if self.ema is not None:
+            self.ema["flat"].lerp_(self.arena.master, 1.0 - self.ema_decay)
+        if self.scheduler is not None:
+            self.scheduler.step()
+        apply_bias_updates(self.model.backbone, window_counts, global_counts=self.global_counts)
+        if self.world > 1 and not self.global_counts and _env_flag("NESTOR_DDP_BROADCAST_BUFFERS", "1"):
+            self.reducer.sync_buffers(self.model)  # rank-0 statistics win, as with DDP buffer broadcast
+        return norm
+
+    # --------------------------------------------------------------------------- loop
+    def train(self) -> None:
+        cfg = self.config
+        self.model.train()
+        log_every = int(os.environ.get("NESTOR_LOG_FREQ") or cfg.log_frequency)
+        peak = float(os.environ.get("NESTOR_MFU_PEAK_TFLOPS", "2250")) * 1e12
+        flops_tok = float(os.environ.get("NESTOR_MFU_FLOPS_PER_TOKEN", "0")) or train_flops_per_token(
+            self.model.config, self._seq_len())
+        profile = _env_flag("NESTOR_TRAIN_PROFILE")
+        tprof, tp_start, tp_n = None, int(os.environ.get("NESTOR_TORCH_PROFILE_START", "12")), \
+            int(os.environ.get("NESTOR_TORCH_PROFILE_STEPS", "10"))
+        if _env_flag("NESTOR_TORCH_PROFILE"):
+            from torch.profiler import ProfilerActivity, profile as torch_profile
+            tprof = torch_profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA])
+        tp_active = False
+        try:
+            batches_per_epoch = len(self.train_loader)
+        except TypeError:
+            batches_per_epoch = 0
+        skip = 0
+        if self.global_step > 0 and batches_per_epoch > 0 and not _env_flag("NESTOR_RESUME_NO_FASTFORWARD"):
+            skip = (self.global_step * cfg.grad_accum_steps) % batches_per_epoch
+            if skip:
+                self.logger.info("[resume] fast-forwarding %d micro-batches (step %d x accum %d, %d per epoch)",
+                                 skip, self.global_step, cfg.grad_accum_steps, batches_per_epoch)
+        self.logger.info("Starting training for %d steps", cfg.max_steps)
+        loss_acc: Tensor | None = None
+        comp_acc: dict[str, Tensor] = {}
+        counts_acc: dict[str, Tensor] = {}
+        micro = 0
+        steps_done, t_steady, t_win, win_steps = 0, None, time.monotonic(), 0
+        t_prev = time.perf_counter()
+        while self.global_step < cfg.max_steps:
+            if hasattr(self.train_loader, "set_epoch"):
+                self.train_loader.set_epoch(self.epoch)
+            for batch in self.train_loader:
+                if skip > 0:
+                    skip -= 1
+                    continue
+                if self.global_step >= cfg.max_steps:
+                    break
+                if tprof is not None:
+                    if steps_done == tp_start and not tp_active:
+                        tprof.__enter__()
+                        tp_active = True
+                    elif tp_active and steps_done >= tp_start + tp_n:
+                        tprof.__exit__(None, None, None)
+                        tp_active, done = False, tprof
+                        tprof = None
+                        if is_main_process():
+                            self.logger.info("[TORCHPROF] top ops:\n%s",
+                                             done.key_averages().table(sort_by="cuda_time_total", row_limit=25))
+                t_data = time.perf_counter() - t_prev
+                t0 = time.perf_counter()
+                loss, counts = self.train_step(batch)
+                if profile and self.device.type == "cuda":
+                    torch.cuda.synchronize()
+                t_fb = time.perf_counter() - t0
+                if (self.global_step + 1) % log_every == 0:
+                    d = loss.total.detach()
+                    loss_acc = d if loss_acc is None else loss_acc + d
+                    for k, v in loss.components.items():
+                        comp_acc[k] = v.detach() if k not in comp_acc else comp_acc[k] + v.detach()
+                for k, v in counts.items():
+                    counts_acc[k] = v if k not in counts_acc else counts_acc[k] + v
+                micro += 1
+                if micro < cfg.grad_accum_steps:
+                    t_prev = time.perf_counter()
+                    continue
+                t1 = time.perf_counter()
+                self.update_weights(counts_acc)
+                if profile:
+                    if self.device.type == "cuda":
+                        torch.cuda.synchronize()
+                    if is_main_process() and steps_done >= 5:
+                        self.logger.info("[TPROF] data=%.3f fwd_bwd=%.3f update=%.3f", t_data, t_fb,
+                                         time.perf_counter() - t1)
+                self.global_step += 1
+                self._bound_runahead()
+                steps_done += 1
+                if steps_done == 1:
+                    if self.device.type == "cuda":
+                        torch.cuda.synchronize()
+                    t_steady = t_win = time.monotonic()
+                    win_steps = steps_done
+                if self.global_step % log_every == 0:
+                    now = time.monotonic()
+                    metrics = {"loss": (loss_acc.item() / micro) if loss_acc is not None else 0.0}
+                    for k, v in comp_acc.items():
+                        metrics[k] = v.item() / micro
+                    if self.scheduler is not None:
+                        lrs = self.scheduler.get_last_lr()
+                        metrics["lr"], metrics["lr_max"] = lrs[0], max(lrs)
+                    dt = (now - t_win) / max(steps_done - win_steps, 1)
+                    t_win, win_steps = now, steps_done
+                    self._add_mfu(metrics, flops_tok, peak, dt, now, steps_done, t_steady)
+                    log_metrics(self.logger, metrics, self.global_step, prefix="train/")
+                loss_acc, comp_acc, counts_acc, micro = None, {}, {}, 0
+                eval_every = int(os.environ.get("NESTOR_EVAL_FREQ") or cfg.eval_frequency)
+                if self.eval_suite is not None and self.global_step % eval_every == 0:
+                    self.run_eval()
+                if self.global_step % cfg.checkpoint_frequency == 0:
+                    self.save_checkpoint()
+                    self.submit_eval_jobs()
+                t_prev = time.perf_counter()
+            self.epoch += 1
+        self.save_checkpoint(final=True)
+        self.logger.info("Training complete!")
+
+    def _bound_runahead(self) -> None:
+        if self.runahead < 0 or self.device.type != "cuda":
+            return
+        if self.runahead == 0:
+            torch.cuda.synchronize()
+            return
+        ev = torch.cuda.Event()
+        ev.record()
+        self._step_events.append(ev)
+        if len(self._step_events) > self.runahead:
+            self._step_events.popleft().synchronize()
+
+    def _add_mfu(self, metrics: dict, flops_tok: float, peak: float, dt: float, now: float,
+                 steps: int, t_steady: float | None) -> None:
+        if not self.tokens_per_micro:
+            return
+        tokens_step = self.tokens_per_micro * self.config.grad_accum_steps * self.world
+        flops_step_gpu = flops_tok * tokens_step / self.world
+        metrics["sec_per_step"] = dt
+        metrics["tokens_per_sec"] = tokens_step / dt if dt > 0 else 0.0
+        metrics["samples_per_sec"] = metrics["tokens_per_sec"] / max(1, self.tokens_per_micro // max(1, self._seq_len()))
+        metrics["tflops_per_gpu"] = flops_step_gpu / dt / 1e12 if dt > 0 else 0.0
+        metrics["mfu_instant"] = flops_step_gpu / dt / peak if dt > 0 else 0.0
+        if t_steady is not None and steps > 1:
+            metrics["mfu_runavg_excl_init"] = flops_step_gpu * (steps - 1) / max(now - t_steady, 1e-9) / peak
+        metrics["mfu_runavg_incl_init"] = flops_step_gpu * steps / max(now - PROCESS_START, 1e-9) / peak
+        if self.device.type == "cuda":
+            metrics["mem_peak_alloc_gib"] = torch.cuda.max_memory_allocated() / 2**30
+            metrics["mem_peak_reserved_gib"] = torch.cuda.max_memory_reserved() / 2**30
+
+    def _seq_len(self) -> int:
+        return int(getattr(self.config.train_dataset, "block_size", 0) or 1)
+
+    # ------------------------------------------------------------------ eval / ckpt
+    def run_eval(self) -> None:
+        results = self.eval_suite.run(self.model)
+        if is_main_process() and self.run_dir is not None:
+            import json
+            out = self.run_dir / "evals"
+            out.mkdir(parents=True, exist_ok=True)
+            (out / f"eval_step_{self.global_step:08d}.json").write_text(json.dumps(results, indent=2))
+        log_metrics(self.logger, {f"{k}": v for k, v in _flatten(results).items()}, self.global_step, prefix="eval/")
+        self.model.train()
+
+    def checkpoint_path(self, final: bool = False) -> Path | None:
+        if self.run_dir is None or self.config.checkpoint_dir is None:
+            return None
+        d = self.run_dir / self.config.checkpoint_dir
+        return d / ("model_final.pt" if final else f"model_{self.global_step:08d}.pt")
+
+    def save_checkpoint(self, final: bool = False) -> None:
+        path = self.checkpoint_path(final)
+        if path is None:
+            return
+        ema = None
+        if self.ema is not None:
+            ema = {s.name: self.ema["flat"][s.offset : s.offset + s.numel].view(s.shape).cpu().clone()
+                   for s in self.arena.slots.values()}
+        ckpt.save_checkpoint(path, self.model, self.optimizer, self.scheduler, step=self.global_step,
+                             epoch=self.epoch, ema=ema)
+        if is_main_process():
+            self.logger.info("saved %s", path)
+
+    def resume(self, path: Path, *, strict: bool = True, allow_partial: bool = False) -> None:
+        state = ckpt.load_checkpoint(path, self.model, self.optimizer if strict else None,
+                                     self.scheduler if strict else None, strict=strict, allow_partial=allow_partial)
+        self.arena.refresh_compute()
+        if strict:
+            self.global_step, self.epoch = int(state.get("step", 0)), int(state.get("epoch", 0))
+            if self.ema is not None and state.get("ema"):
+                for s in self.arena.slots.values():
+                    if s.name in state["ema"]:
+                        self.ema["flat"][s.offset : s.offset + s.numel].copy_(state["ema"][s.name].reshape(-1))
+        self.logger.info("%s from %s at step %d", "resumed" if strict else "initialised", path, self.global_step)
+
+    def submit_eval_jobs(self) -> None:
+        """``sbatch`` the configured evaluation scripts against the checkpoint just written (rank 0)."""
+
+        scripts = self.config.eval_submit_scripts
+        path = self.checkpoint_path()
+        if not scripts or not is_main_process() or path is None:
+            return
+        for script, every in scripts:
+            if every and self.global_step % every:
+                continue
+            try:
+                subprocess.run(["sbatch", str(script), str(path)], check=False, capture_output=True, timeout=60)
+            except (FileNotFoundError, subprocess.TimeoutExpired) as exc:
+                self.logger.warning("eval submission failed for %s: %s", script, exc)
+
+
+def _flatten(d: dict, prefix: str = "") -> dict[str, Any]:
+    out = {}
+    for k, v in d.items():
+        key = f"{prefix}{k}"
+        if isinstance(v, dict):
+            out.update(_flatten(v, key + "/"))
+        elif isinstance(v, (int, float)):
+            out[key] = v
+    return out
