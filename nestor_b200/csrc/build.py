@@ -1,0 +1,71 @@
+"""Build the sm_100a kernel library in-tree: ``nestor_b200/_C/libnestor_b200.so``.
+
+``python -m nestor_b200.csrc.build`` compiles every ``.cu`` file of this directory with
+``nvcc -gencode arch=compute_100a,code=sm_100a`` into one shared library with a C ABI
+(no PyTorch headers; the Python side passes raw device pointers and the current stream
+through ``ctypes``). Objects are cached by source hash, so a rebuild only recompiles
+what changed. The library never links ``libcuda``: the one driver entry point it needs
+(tensor-map encoding) is resolved at run time through the CUDA runtime.
+"""
+
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+SRC = Path(__file__).resolve().parent
+OUT = SRC.parent / "_C"
+LIB = OUT / "libnestor_b200.so"
+FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--use_fast_math", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
+]
+
+
+def nvcc() -> str | None:
+    return shutil.which("nvcc") or (str(p) if (p := Path("/usr/local/cuda/bin/nvcc")).is_file() else None)
+
+
+def _digest(path: Path) -> str:
+    h = hashlib.sha256()
+    for f in [path, *sorted(SRC.glob("*.cuh"))]:
+        h.update(f.read_bytes())
+    h.update(" ".join(FLAGS).encode())
+    return h.hexdigest()[:16]
+
+
+def build(verbose: bool = False, force: bool = False) -> Path:
+    cc = nvcc()
+    if cc is None:
+        raise RuntimeError("nvcc not found: cannot build the sm_100a kernel library")
+    OUT.mkdir(exist_ok=True)
+    objs, rebuilt = [], False
+    for cu in sorted(SRC.glob("*.cu")):
+        obj = OUT / f"{cu.stem}.{_digest(cu)}.o"
+        if force or not obj.is_file():
+            for old in OUT.glob(f"{cu.stem}.*.o"):
+                old.unlink()
+            cmd = [cc, *FLAGS, "-c", str(cu), "-o", str(obj)]
+            res = subprocess.run(cmd, capture_output=True, text=True)
+            if verbose or res.returncode:
+                sys.stderr.write(res.stdout + res.stderr)
+            if res.returncode:
+                raise RuntimeError(f"nvcc failed on {cu.name}")
+            (OUT / f"{cu.stem}.ptxas.txt").write_text(res.stderr)
+            rebuilt = True
+        objs.append(obj)
+    if rebuilt or not LIB.is_file():
+        cmd = [cc, "-shared", "-o", str(LIB), *map(str, objs), "-lcudart"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode:
+            sys.stderr.write(res.stdout + res.stderr)
+            raise RuntimeError("link failed")
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(verbose="-v" in sys.argv, force="-f" in sys.argv))

@@ -32,6 +32,13 @@ def cuda_ops():
     return _cuda_mod
 
 
+def launch_count() -> int:
+    """Kernels of the in-tree library launched so far in this process."""
+
+    from nestor_b200.ops import _lib
+    return _lib.LAUNCHES
+
+
 def use_kernels(t: torch.Tensor) -> bool:
     return t.is_cuda and not _FORCE_REF
 

@@ -1,0 +1,77 @@
+"""ctypes binding of the in-tree sm_100a kernel library.
+
+The library is looked up at ``nestor_b200/_C/libnestor_b200.so``; when it is missing and
+``nvcc`` is present it is built on first use. On a machine with a CUDA device, a missing
+library is an error (there is no silent PyTorch fallback for CUDA tensors).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import torch
+
+_LIB = None
+LAUNCHES = 0   # kernels of this library launched so far (bench.py reports the delta)
+
+
+class Operand(C.Structure):
+    _fields_ = [("ptr", C.c_void_p), ("rows", C.c_long), ("cols", C.c_long), ("ld", C.c_long),
+                ("groups", C.c_long), ("group_stride", C.c_long)]
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("mode", C.c_int), ("groups", C.c_int), ("BN", C.c_int), ("epilogue", C.c_int),
+        ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("K2", C.c_int),
+        ("offsets", C.c_void_p), ("rows_per_group", C.c_int),
+        ("a_mn", C.c_int), ("b_mn", C.c_int), ("b_grouped", C.c_int),
+        ("A", Operand), ("B", Operand), ("A2", Operand), ("B2", Operand),
+        ("C", C.c_void_p), ("ldc", C.c_long), ("c_group_stride", C.c_long),
+        ("C2", C.c_void_p), ("C3", C.c_void_p), ("E1", C.c_void_p), ("E2", C.c_void_p), ("lde", C.c_long),
+        ("alpha", C.c_float), ("status", C.c_void_p), ("max_m_tiles", C.c_int), ("sms", C.c_int),
+    ]
+
+
+def lib() -> C.CDLL:
+    global _LIB
+    if _LIB is None:
+        path = Path(__file__).resolve().parent.parent / "_C" / "libnestor_b200.so"
+        if not path.is_file():
+            from nestor_b200.csrc.build import build
+            build()
+        _LIB = C.CDLL(str(path))
+        _LIB.nb_gemm.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
+        _LIB.nb_gemm.restype = C.c_int
+    return _LIB
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def count_launch(n: int = 1) -> None:
+    global LAUNCHES
+    LAUNCHES += n
+
+
+_status: dict[int, torch.Tensor] = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 the kernels write a nonzero code into when a bounded wait gives up."""
+
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status:
+        _status[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[idx]
+
+
+def check_status(device: torch.device) -> None:
+    """Raise if any kernel on ``device`` reported a timed-out wait (synchronises)."""
+
+    code = int(status_word(device).item())
+    if code:
+        status_word(device).zero_()
+        raise RuntimeError(f"nestor_b200 kernel reported status {code} (a bounded device-side wait gave up)")

@@ -1,0 +1,133 @@
+"""Python front end of the persistent tcgen05 grouped GEMM (``csrc/gemm.cu``).
+
+``gemm_rows``: ``C[r] = A[r] . B[group(r)]`` for rows packed by group (forward and data
+gradients). ``gemm_reduce``: ``C[g] (+)= A[rows of g]^T . B[rows of g]`` (weight
+gradients). Operands are bf16; "MN-major" means the operand is stored with its M (or N)
+index contiguous, i.e. as the transpose of the usual row-of-K layout — both are read by
+TMA without any copy.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+from torch import Tensor
+
+from nestor_b200.ops import _lib
+
+STORE_BF16, STORE_F32, ACCUM_F32, SWIGLU, SWIGLU_BWD, STORE_BF16_STATS = range(6)
+
+
+def pick_bn(n: int, *, mult: int = 16, cap: int = 256) -> int:
+    """Tile width: least padded-N, ties to the wider tile; multiples of ``mult`` up to ``cap``."""
+
+    best, best_cost = mult, None
+    for bn in range(mult, cap + 1, mult):
+        tiles = -(-n // bn)
+        cost = tiles * bn * (1.0 + 24.0 / bn)
+        if best_cost is None or cost <= best_cost:
+            best, best_cost = bn, cost
+    return best
+
+
+def _operand(t: Tensor | None, *, grouped: bool) -> _lib.Operand:
+    if t is None:
+        return _lib.Operand(None, 0, 0, 0, 0, 0)
+    assert t.dtype == torch.bfloat16 and t.stride(-1) == 1, "operands are bf16 with a contiguous last dim"
+    assert t.data_ptr() % 16 == 0 and (t.stride(-2) * 2) % 16 == 0, "TMA needs 16-byte aligned base and row pitch"
+    if t.ndim == 3:
+        assert (t.stride(0) * 2) % 16 == 0
+        return _lib.Operand(t.data_ptr(), t.shape[1], t.shape[2], t.stride(1), t.shape[0], t.stride(0))
+    return _lib.Operand(t.data_ptr(), t.shape[0], t.shape[1], t.stride(0), 1, t.shape[0] * t.stride(0))
+
+
+def _launch(args: _lib.GemmArgs) -> None:
+    rc = _lib.lib().nb_gemm(C.byref(args), C.c_void_p(_lib.stream_ptr()))
+    if rc != 0:
+        raise RuntimeError(f"nb_gemm failed with code {rc}")
+    _lib.count_launch()
+
+
+def gemm_rows(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: int = 1, b_mn: bool = False,
+              out: Tensor | None = None, epilogue: int = STORE_BF16, alpha: float = 1.0, bn: int | None = None,
+              A2: Tensor | None = None, B2: Tensor | None = None, extra_out: tuple = (), extra_in: tuple = (),
+              n: int | None = None, sms: int = 0) -> Tensor:
+    """Row-grouped GEMM.
+
+    ``A [rows, K]``; ``B`` is ``[G, N, K]`` (K-major) or ``[G, K, N]`` (``b_mn``) — 2-D for a
+    single shared matrix. ``offsets [G+1]`` (int32, device) bound the groups; ``None`` with
+    ``groups == 1`` means one group over all rows. ``A2/B2`` extend the reduction. With
+    ``epilogue == SWIGLU``, ``B`` is the gate bank and ``B2`` the up bank (both ``[G, K, h]``);
+    ``out`` receives ``silu(gate) * up`` and ``extra_out = (gate, up)``.
+    """
+
+    rows, K = A.shape
+    if b_mn:
+        N = B.shape[-1] if n is None else n
+    else:
+        N = B.shape[-2] if n is None else n
+    swiglu = epilogue == SWIGLU
+    if swiglu:
+        N = 2 * B.shape[-1]
+    if bn is None:
+        bn = 128 if swiglu else pick_bn(N, mult=64 if b_mn else 16)
+    dev = A.device
+    if out is None:
+        dt = torch.float32 if epilogue in (STORE_F32, ACCUM_F32) else torch.bfloat16
+        out = torch.empty(rows, N // 2 if swiglu else N, dtype=dt, device=dev)
+    a = _lib.GemmArgs()
+    a.mode, a.groups, a.BN, a.epilogue = 0, groups, bn, epilogue
+    a.M, a.N, a.K, a.K2 = rows, N, K, (A2.shape[1] if A2 is not None else 0)
+    a.offsets = offsets.data_ptr() if offsets is not None else None
+    a.rows_per_group = rows if offsets is None else 0
+    if offsets is None and groups != 1:
+        assert rows % groups == 0
+        a.rows_per_group = rows // groups
+    a.a_mn, a.b_mn, a.b_grouped = 0, int(b_mn), int(B.ndim == 3)
+    a.A, a.B = _operand(A, grouped=False), _operand(B, grouped=True)
+    a.A2, a.B2 = _operand(A2, grouped=False), _operand(B2, grouped=True)
+    a.C, a.ldc, a.c_group_stride = out.data_ptr(), out.stride(0), 0
+    a.C2 = extra_out[0].data_ptr() if len(extra_out) > 0 else None
+    a.C3 = extra_out[1].data_ptr() if len(extra_out) > 1 else None
+    a.E1 = extra_in[0].data_ptr() if len(extra_in) > 0 else None
+    a.E2 = extra_in[1].data_ptr() if len(extra_in) > 1 else None
+    a.lde = extra_in[0].stride(0) if len(extra_in) > 0 else 0
+    a.alpha = alpha
+    a.status = _lib.status_word(dev).data_ptr()
+    a.max_m_tiles = -(-rows // 128) + groups
+    a.sms = sms
+    _launch(a)
+    return out
+
+
+def gemm_reduce(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: int = 1, out: Tensor,
+                epilogue: int = ACCUM_F32, alpha: float = 1.0, bn: int | None = None, sms: int = 0) -> Tensor:
+    """Reduction-grouped GEMM: ``out[g] (+)= A[rows_g]^T @ B[rows_g]`` with ``A [rows, M]``, ``B [rows, N]``.
+
+    ``out`` is ``[G, M, N]`` (or ``[M, N]`` for one group) with a contiguous last dim; fp32 for the
+    store/accumulate epilogues.
+    """
+
+    rows, M = A.shape
+    N = B.shape[1]
+    assert B.shape[0] == rows
+    if bn is None:
+        bn = pick_bn(N, mult=64)
+    a = _lib.GemmArgs()
+    a.mode, a.groups, a.BN, a.epilogue = 1, groups, bn, epilogue
+    a.M, a.N, a.K, a.K2 = M, N, rows, 0
+    a.offsets = offsets.data_ptr() if offsets is not None else None
+    a.rows_per_group = 0 if offsets is not None else rows // groups
+    a.a_mn, a.b_mn, a.b_grouped = 1, 1, 0
+    a.A, a.B = _operand(A, grouped=False), _operand(B, grouped=False)
+    a.A2, a.B2 = _operand(None, grouped=False), _operand(None, grouped=False)
+    o3 = out if out.ndim == 3 else out.unsqueeze(0)
+    assert o3.stride(-1) == 1
+    a.C, a.ldc, a.c_group_stride = o3.data_ptr(), o3.stride(1), o3.stride(0)
+    a.alpha = alpha
+    a.status = _lib.status_word(A.device).data_ptr()
+    a.max_m_tiles = 0
+    a.sms = sms
+    _launch(a)
+    return out
