@@ -260,6 +260,18 @@ def run_reference(a: argparse.Namespace) -> dict:
         NESTOR_DDP_NO_SYNC="1", NESTOR_MUON_SHARD="1", NESTOR_STACKED_EXPERT_BANKS="1",
         NESTOR_BATCHED_ROUTERS="1", NESTOR_TRITON_PACKED_ATTN="1", NESTOR_TRITON_INDEX_BUILD="1",
         NESTOR_TRITON_EXPERT_DISPATCH="1")
+    adjusted = None
+    try:   # the reference's packed varlen path calls varlen_attn(..., is_causal=True)
+        import inspect
+        from torch.nn.attention.varlen import varlen_attn
+        if "is_causal" not in inspect.signature(varlen_attn).parameters:
+            for k in ("NESTOR_ATTN_PACKED_VARLEN", "NESTOR_TRITON_PACKED_ATTN", "NESTOR_GATHERED_VARLEN"):
+                stack[k] = "0"
+            adjusted = ("this torch's varlen_attn has no is_causal keyword, which the reference's packed-varlen "
+                        "attention passes; NESTOR_ATTN_PACKED_VARLEN / NESTOR_TRITON_PACKED_ATTN / "
+                        "NESTOR_GATHERED_VARLEN are off, the rest of the speed stack is on")
+    except ImportError:
+        pass
     for k, v in stack.items():
         os.environ.setdefault(k, v)
     os.environ.update(
@@ -267,7 +279,9 @@ def run_reference(a: argparse.Namespace) -> dict:
         DCLM_MAX_STEPS=str(warm + a.steps + 1), DCLM_WARMUP_STEPS="2", DCLM_CKPT_FREQ="1000000",
         DCLM_LOG_FREQ="1000000", DCLM_NUM_WORKERS="2",
         NESTOR_OUTPUT_ROOT=str(Path(tempfile.gettempdir()) / "nestor_ref_out"))
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    for k, v in (("MASTER_ADDR", "127.0.0.1"), ("MASTER_PORT", "29533"), ("RANK", "0"), ("WORLD_SIZE", "1"),
+                 ("LOCAL_RANK", "0")):
+        os.environ.setdefault(k, v)   # a bare `python bench.py` run still gets an env:// rendezvous
     path = _data_path(world, rank, a.steps + warm + 2)
     os.environ["DCLM_DATA_PATH"] = str(path)
     sys.path.insert(0, str(ref))
@@ -324,7 +338,7 @@ def run_reference(a: argparse.Namespace) -> dict:
             "data": "synthetic uniform token ids in log-uniform-length documents; random-init weights",
             "config": {"model": a.experiment, "global_batch": SEQS_PER_GPU * world, "grad_accum": accum,
                        "tokens_per_step": TOKENS_PER_STEP, "seq_len": SEQ_LEN, "parallelism": f"dp{world}",
-                       "speed_stack": {k: os.environ[k] for k in stack}},
+                       "speed_stack": {k: os.environ[k] for k in stack}, "speed_stack_adjusted": adjusted},
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": accum * SEQS_PER_GPU * SEQ_LEN * 16,
                     "d2h_bytes_per_step": 8 * accum,
                     "note": "the reference's stock loop already copies every batch from its pinned DataLoader "

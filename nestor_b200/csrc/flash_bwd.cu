@@ -1,0 +1,332 @@
+// Varlen causal flash attention backward for sm_100a (tcgen05 + TMEM + TMA).
+//
+// Two launches of one templated kernel, both recomputing the probabilities from the saved
+// log-sum-exp (log2 domain):
+//   MODE 0 (dK, dV): a CTA owns a kv tile of 128 rows and walks the q tiles at or below it.
+//       S^T = K Q^T,  dP^T = V dO^T              (tcgen05, K-major operands, fp32 in TMEM)
+//       P^T = exp2(S^T c - lse[q]),  dS^T = P^T (dP^T - delta[q])   (one thread per kv row)
+//       dV += P^T dO,  dK += dS^T Q               (A from swizzled smem, B = dO / Q read MN-major)
+//   MODE 1 (dQ): a CTA owns a q tile and walks the kv tiles up to the diagonal.
+//       S = Q K^T,  dP = dO V^T,  dS = P (dP - delta[q]),  dQ += dS K
+// delta[q] = sum_c dO[q, c] O[q, c] comes from `attn_delta_kernel`. Gradients of the scaled
+// scores are folded back with the softmax scale when dQ / dK are stored.
+// The same shared-memory tile serves as a K-major operand of the score products and as an
+// MN-major operand of the accumulate products, so every tile is fetched once.
+#include "sm100.cuh"
+
+namespace nb {
+
+constexpr int BT = 128;
+
+struct FlashBwdParams {
+  int nseg, H, hd, rows, stages;
+  const int* seg_start;
+  float scale_log2, scale;
+  const float* lse;      // [rows, H]
+  const float* delta;    // [rows, H]
+  __nv_bfloat16* out1; __nv_bfloat16* out2; long ldo;   // MODE 0: dK, dV; MODE 1: dQ
+  int* status;
+};
+
+__device__ __forceinline__ void st_tile_chunk(uint8_t* base, int row, int col0, const uint32_t* w) {
+  int blk = col0 >> 6, ch = (col0 & 63) >> 3;
+  *reinterpret_cast<uint4*>(base + blk * 16384 + row * 128 + ((ch ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+template <int MODE, int HDN>
+__global__ void __launch_bounds__(192, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ CUtensorMap tmR2,
+                 const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ CUtensorMap tmX2,
+                 const FlashBwdParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ uint64_t r_full, x_full[2], x_empty[2], sc_full, ds_ready, acc_done;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+  __shared__ int s_tile[4];
+  __shared__ float s_lse[4][BT], s_delta[4][BT];   // one private copy per softmax warp (no cross-warp barrier)
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y;
+  const int nkb = (p.hd + 63) / 64;
+  const int hd16 = (p.hd + 15) & ~15;
+  const uint32_t tile_bytes = uint32_t(nkb) * 16384;
+  const int stages = p.stages;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sR1 = smem;
+  uint8_t* sR2 = sR1 + tile_bytes;
+  uint8_t* sX = sR2 + tile_bytes;                       // stages x (X1, X2)
+  uint8_t* sDS = sX + stages * 2 * tile_bytes;          // 32 KB: dS (or dS^T)
+  uint8_t* sPT = sDS + 32768;                           // 32 KB: P^T (MODE 0 only)
+
+  if (threadIdx.x == 0) {
+    int t = blockIdx.x, found = 0, b = 0, e = 0, r0 = 0;
+    for (int s = 0; s < p.nseg; ++s) {
+      b = p.seg_start[s]; e = p.seg_start[s + 1];
+      int nt = (e - b + BT - 1) / BT;
+      if (t < nt) {
+        // heaviest first: MODE 0 the earliest kv tile, MODE 1 the last q tile
+        r0 = (MODE == 0) ? b + t * BT : b + (nt - 1 - t) * BT;
+        found = 1; break;
+      }
+      t -= nt;
+    }
+    s_tile[0] = b; s_tile[1] = e; s_tile[2] = r0; s_tile[3] = found;
+    s_abort = 0;
+    mbar_init(&r_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 1); }
+    mbar_init(&sc_full, 1); mbar_init(&ds_ready, 4); mbar_init(&acc_done, 1);
+    fence_barrier_init();
+    prefetch_tmap(&tmR1); prefetch_tmap(&tmR2); prefetch_tmap(&tmX1); prefetch_tmap(&tmX2);
+  }
+  __syncthreads();
+  if (!s_tile[3]) return;
+  if (warp == 1) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t tS = tmem, tDP = tmem + 128, tA1 = tmem + 256, tA2 = tmem + 256 + HDN;
+  const int seg_b = s_tile[0], seg_e = s_tile[1], r0 = s_tile[2];
+  // streamed tiles: MODE 0 -> q tiles r0, r0+128, ... below seg_e; MODE 1 -> kv tiles seg_b .. r0
+  const int x_first = (MODE == 0) ? r0 : seg_b;
+  const int niter = (MODE == 0) ? (seg_e - r0 + BT - 1) / BT : (r0 - seg_b) / BT + 1;
+  volatile int* abort_flag = &s_abort;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      mbar_expect_tx(&r_full, 2 * tile_bytes);
+      for (int b = 0; b < nkb; ++b) {
+        tma_load_3d(sR1 + b * 16384, &tmR1, &r_full, b * 64, head, r0);
+        tma_load_3d(sR2 + b * 16384, &tmR2, &r_full, b * 64, head, r0);
+      }
+      for (int it = 0; it < niter; ++it) {
+        int s = it % stages;
+        if (!mbar_wait(&x_empty[s], ((it / stages) & 1) ^ 1, abort_flag, p.status, kTimeoutEmpty)) break;
+        mbar_expect_tx(&x_full[s], 2 * tile_bytes);
+        int x0 = x_first + it * BT;
+        uint8_t* d = sX + s * 2 * tile_bytes;
+        for (int b = 0; b < nkb; ++b) {
+          tma_load_3d(d + b * 16384, &tmX1, &x_full[s], b * 64, head, x0);
+          tma_load_3d(d + tile_bytes + b * 16384, &tmX2, &x_full[s], b * 64, head, x0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    const uint32_t idesc_sc = make_idesc(BT, BT, 0, 0);
+    const uint32_t idesc_acc = make_idesc(BT, HDN, 0, 1);
+    bool ok = true;
+    if (lane == 0) ok = mbar_wait(&r_full, 0, abort_flag, p.status, kTimeoutFull);
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    for (int it = 0; it < niter && ok; ++it) {
+      int s = it % stages;
+      if (lane == 0) {
+        // (the score accumulators are free: the previous iteration's ds_ready was awaited below)
+        ok = mbar_wait(&x_full[s], (it / stages) & 1, abort_flag, p.status, kTimeoutFull);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      tc_fence_after();
+      uint8_t* x1 = sX + s * 2 * tile_bytes;
+      uint8_t* x2 = x1 + tile_bytes;
+      if (lane == 0) {
+        uint32_t a1 = smem_u32(sR1), a2 = smem_u32(sR2), b1 = smem_u32(x1), b2 = smem_u32(x2);
+        for (int k = 0; k < hd16 / 16; ++k) {
+          uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          umma_bf16(tS, sdesc_kmajor(a1 + off), sdesc_kmajor(b1 + off), idesc_sc, k != 0);
+        }
+        for (int k = 0; k < hd16 / 16; ++k) {
+          uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          umma_bf16(tDP, sdesc_kmajor(a2 + off), sdesc_kmajor(b2 + off), idesc_sc, k != 0);
+        }
+        umma_commit(&sc_full);
+        ok = mbar_wait(&ds_ready, it & 1, abort_flag, p.status, kTimeoutTmemEmpty);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      tc_fence_after();
+      if (lane == 0) {
+        uint32_t ds = smem_u32(sDS), pt = smem_u32(sPT), b1 = smem_u32(x1), b2 = smem_u32(x2);
+        for (int k = 0; k < BT / 16; ++k) {
+          uint32_t aoff = (k >> 2) * 16384 + (k & 3) * 32;
+          if (MODE == 0) {
+            umma_bf16(tA1, sdesc_kmajor(pt + aoff), sdesc_mnmajor(b2 + k * 2048, 16384), idesc_acc, (it | k) != 0);  // dV += P^T dO
+            umma_bf16(tA2, sdesc_kmajor(ds + aoff), sdesc_mnmajor(b1 + k * 2048, 16384), idesc_acc, (it | k) != 0);  // dK += dS^T Q
+          } else {
+            umma_bf16(tA1, sdesc_kmajor(ds + aoff), sdesc_mnmajor(b1 + k * 2048, 16384), idesc_acc, (it | k) != 0);  // dQ += dS K
+          }
+        }
+        umma_commit(&x_empty[s]);
+        umma_commit(&acc_done);
+      }
+      __syncwarp();
+    }
+  } else {
+    const int q4 = warp & 3;
+    const int r = q4 * 32 + lane;
+    const int grow = r0 + r;                        // global row owned by this thread
+    const uint32_t lane_off = uint32_t(q4 * 32) << 16;
+    float my_lse = 0.f, my_delta = 0.f;
+    if (MODE == 1 && grow < p.rows) { my_lse = p.lse[long(grow) * p.H + head]; my_delta = p.delta[long(grow) * p.H + head]; }
+    bool ok = true;
+    for (int it = 0; it < niter; ++it) {
+      const int x0 = x_first + it * BT;
+      if (MODE == 0) {
+        __syncwarp();
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          int cc = lane + 32 * u, xr = x0 + cc;
+          bool in = xr < seg_e;
+          s_lse[q4][cc] = in ? p.lse[long(xr) * p.H + head] : INFINITY;   // exp2(-inf) = 0 for rows past the segment
+          s_delta[q4][cc] = in ? p.delta[long(xr) * p.H + head] : 0.f;
+        }
+        __syncwarp();
+      }
+      if (!mbar_wait(&sc_full, it & 1, abort_flag, p.status, kTimeoutTmemFull)) { ok = false; break; }
+      tc_fence_after();
+      // the smem tiles are free once the previous iteration's accumulate products retired
+      if (it > 0 && !mbar_wait(&acc_done, (it - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) { ok = false; break; }
+      const float* lse_c = s_lse[q4];
+      const float* del_c = s_delta[q4];
+      for (int c = 0; c < BT; c += 16) {
+        float sv[16], dv[16];
+        tmem_ld16(tS + lane_off + c, sv); tmem_ld16(tDP + lane_off + c, dv);
+        tmem_ld_wait();
+        uint32_t wp[8], wd[8];
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+          float pv[2], dsv[2];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            int cc = c + i + h;
+            bool vis; float lz, dl;
+            if (MODE == 0) { vis = (x0 + cc) >= grow; lz = lse_c[cc]; dl = del_c[cc]; }
+            else { vis = (x0 + cc) <= grow; lz = my_lse; dl = my_delta; }
+            float pr = vis ? exp2f(sv[i + h] * p.scale_log2 - lz) : 0.f;
+            pv[h] = pr; dsv[h] = vis ? pr * (dv[i + h] - dl) : 0.f;
+          }
+          wp[i >> 1] = pack_bf16(pv[0], pv[1]); wd[i >> 1] = pack_bf16(dsv[0], dsv[1]);
+        }
+        st_tile_chunk(sDS, r, c, wd); st_tile_chunk(sDS, r, c + 8, wd + 4);
+        if (MODE == 0) { st_tile_chunk(sPT, r, c, wp); st_tile_chunk(sPT, r, c + 8, wp + 4); }
+      }
+      fence_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ds_ready);
+    }
+    if (ok && mbar_wait(&acc_done, (niter - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) {
+      tc_fence_after();
+      const bool row_ok = grow < seg_e;
+      const long o = long(grow) * p.ldo + head * p.hd;
+#pragma unroll
+      for (int c = 0; c < HDN; c += 16) {
+        float a1[16], a2[16];
+        tmem_ld16(tA1 + lane_off + c, a1);
+        if (MODE == 0) tmem_ld16(tA2 + lane_off + c, a2);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 16; i += 8) {
+            if (c + i < p.hd) {
+              uint32_t w[4];
+              if (MODE == 0) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) w[e] = pack_bf16(a2[i + 2 * e] * p.scale, a2[i + 2 * e + 1] * p.scale);
+                *reinterpret_cast<uint4*>(p.out1 + o + c + i) = make_uint4(w[0], w[1], w[2], w[3]);     // dK
+#pragma unroll
+                for (int e = 0; e < 4; ++e) w[e] = pack_bf16(a1[i + 2 * e], a1[i + 2 * e + 1]);
+                *reinterpret_cast<uint4*>(p.out2 + o + c + i) = make_uint4(w[0], w[1], w[2], w[3]);     // dV
+              } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) w[e] = pack_bf16(a1[i + 2 * e] * p.scale, a1[i + 2 * e + 1] * p.scale);
+                *reinterpret_cast<uint4*>(p.out1 + o + c + i) = make_uint4(w[0], w[1], w[2], w[3]);     // dQ
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+// delta[row, h] = sum_c dO[row, h, c] * O[row, h, c]; one warp per (row, head).
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O, long ld_do,
+                                  long ld_o, float* __restrict__ delta, int rows, int H, int hd) {
+  int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (w >= rows * H) return;
+  int row = w / H, h = w - row * H;
+  const __nv_bfloat16* a = dO + long(row) * ld_do + h * hd;
+  const __nv_bfloat16* b = O + long(row) * ld_o + h * hd;
+  float acc = 0.f;
+  for (int c = lane; c < hd; c += 32) acc += __bfloat162float(a[c]) * __bfloat162float(b[c]);
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (lane == 0) delta[w] = acc;
+}
+
+}  // namespace nb
+
+extern "C" int nb_head_map(CUtensorMap* m, const void* base, long rows, int H, int hd, long row_pitch_elems);
+
+extern "C" {
+
+struct NbFlashBwdArgs {
+  const void* Q; const void* K; const void* V; long ld_qkv;    // saved forward operands (shared row pitch)
+  const void* O; long ld_o;
+  const void* dO; long ld_do;
+  const float* lse; float* delta;                              // [rows, H] each (delta is scratch output)
+  void* dQ; void* dK; void* dV; long ld_dqkv;
+  const int* seg_start; int nseg;
+  int rows, H, hd;
+  float scale;
+  int* status;
+  int max_tiles;
+};
+
+int nb_flash_bwd(const NbFlashBwdArgs* a, cudaStream_t stream) {
+  using namespace nb;
+  if (a->hd % 8 || a->hd < 8 || a->hd > 128) return -1;
+  CUtensorMap tq, tk, tv, tdo;
+  if (nb_head_map(&tq, a->Q, a->rows, a->H, a->hd, a->ld_qkv)) return -10;
+  if (nb_head_map(&tk, a->K, a->rows, a->H, a->hd, a->ld_qkv)) return -11;
+  if (nb_head_map(&tv, a->V, a->rows, a->H, a->hd, a->ld_qkv)) return -12;
+  if (nb_head_map(&tdo, a->dO, a->rows, a->H, a->hd, a->ld_do)) return -13;
+  {
+    long warps = long(a->rows) * a->H;
+    int threads = 256;
+    long blocks = (warps * 32 + threads - 1) / threads;
+    attn_delta_kernel<<<unsigned(blocks), threads, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(a->dO), reinterpret_cast<const __nv_bfloat16*>(a->O), a->ld_do, a->ld_o,
+        a->delta, a->rows, a->H, a->hd);
+  }
+  FlashBwdParams p;
+  p.nseg = a->nseg; p.H = a->H; p.hd = a->hd; p.rows = a->rows; p.seg_start = a->seg_start;
+  p.scale = a->scale; p.scale_log2 = a->scale * 1.4426950408889634f;
+  p.lse = a->lse; p.delta = a->delta; p.ldo = a->ld_dqkv; p.status = a->status;
+  const int nkb = (a->hd + 63) / 64;
+  p.stages = nkb == 1 ? 2 : 1;
+  const size_t smem = size_t(nkb) * 16384 * (2 + 2 * p.stages) + 65536 + 1024;
+  dim3 grid(a->max_tiles, a->H);
+#define NB_LAUNCH(MODE, HDN, R1, R2, X1, X2)                                                                        \
+  do {                                                                                                               \
+    static bool set = false;                                                                                         \
+    if (!set) {                                                                                                      \
+      cudaError_t e = cudaFuncSetAttribute(flash_bwd_kernel<MODE, HDN>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                           int(smem));                                                               \
+      if (e != cudaSuccess) return int(e);                                                                           \
+      set = true;                                                                                                    \
+    }                                                                                                                \
+    flash_bwd_kernel<MODE, HDN><<<grid, 192, smem, stream>>>(R1, R2, X1, X2, p);                                     \
+  } while (0)
+  p.out1 = reinterpret_cast<__nv_bfloat16*>(a->dK); p.out2 = reinterpret_cast<__nv_bfloat16*>(a->dV);
+  if (a->hd <= 64) NB_LAUNCH(0, 64, tk, tv, tq, tdo); else NB_LAUNCH(0, 128, tk, tv, tq, tdo);
+  p.out1 = reinterpret_cast<__nv_bfloat16*>(a->dQ); p.out2 = nullptr;
+  if (a->hd <= 64) NB_LAUNCH(1, 64, tq, tdo, tk, tv); else NB_LAUNCH(1, 128, tq, tdo, tk, tv);
+#undef NB_LAUNCH
+  return int(cudaGetLastError());
+}
+
+}  // extern "C"

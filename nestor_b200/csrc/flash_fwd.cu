@@ -1,0 +1,331 @@
+// Varlen causal flash attention forward for sm_100a (tcgen05 + TMEM + TMA).
+//
+// Rows of Q/K/V are packed by segment (the members of one attention column in one
+// sequence, in token order); attention is causal inside a segment and segments never
+// mix. One CTA owns one (q tile of 128 rows, head) pair and walks the kv tiles of its
+// segment up to the diagonal:
+//     S  = Q K^T            tcgen05.mma, K-major operands, fp32 in TMEM (double-buffered)
+//     P  = exp2(S*c - m)    softmax warps: one thread per q row, online max / sum
+//     Oj = P V              tcgen05.mma, A = P (bf16, written to swizzled smem), B = V (MN-major)
+//     O  = O*alpha + Oj     in registers
+// Heads are `hd` wide (any multiple of 8 up to 128); tiles are zero-extended to a multiple
+// of 16 by TMA out-of-bounds fill (the tensor map's innermost extent is `hd`).
+// Tiles start at the segment's first row, so a q or kv tile may run past the segment end;
+// the causal mask hides such kv rows from valid q rows and the store masks such q rows.
+//
+// Replaces torch's varlen_attn / SDPA calls of the reference (nestor/backbones/nestor.py:6357,
+// :6213, :5802) including its 1/head_dim logit scale (:3201).
+#include "sm100.cuh"
+
+namespace nb {
+
+constexpr int FQ = 128;      // q rows per CTA
+constexpr int FK = 128;      // kv rows per tile
+constexpr int kMaxSeg = 1024;
+
+struct FlashParams {
+  int nseg, H, hd, rows;
+  const int* seg_start;        // [nseg + 1]
+  float scale_log2;            // softmax scale * log2(e)
+  __nv_bfloat16* O; long ldo;  // [rows, H*hd]
+  float* lse;                  // [rows, H] log2-domain logsumexp of scaled scores
+  int* status;
+};
+
+__device__ __forceinline__ void st_p_chunk(uint8_t* pbase, int row, int col0, const uint32_t* w) {
+  // 8 bf16 (16 B) of row `row`, columns col0..col0+7, into the 128B-swizzled K-major P tile
+  int blk = col0 >> 6, ch = (col0 & 63) >> 3;
+  uint8_t* dst = pbase + blk * 16384 + row * 128 + ((ch ^ (row & 7)) << 4);
+  *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+template <int HDN>   // N of the P.V product and width of the register accumulator: 64 (hd <= 64) or 128
+__global__ void __launch_bounds__(192, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], p_ready, o_full;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+  __shared__ int s_tile[4];   // seg begin, seg end, q0, valid
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y;
+  const int nkb = (p.hd + 63) / 64;                 // 64-column blocks per operand tile
+  const int hd16 = (p.hd + 15) & ~15;   // reduction width of Q K^T
+  const uint32_t tile_bytes = uint32_t(nkb) * 16384;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + tile_bytes;          // 2 stages
+  uint8_t* sV = sK + 2 * tile_bytes;      // 2 stages
+  uint8_t* sP = sV + 2 * tile_bytes;      // 2 blocks of 16 KB
+
+  if (threadIdx.x == 0) {
+    // locate this CTA's q tile: tiles are numbered segment by segment, heaviest (last) q tile first
+    int t = blockIdx.x, found = 0, b = 0, e = 0, q0 = 0;
+    for (int s = 0; s < p.nseg; ++s) {
+      b = p.seg_start[s]; e = p.seg_start[s + 1];
+      int nt = (e - b + FQ - 1) / FQ;
+      if (t < nt) { q0 = b + (nt - 1 - t) * FQ; found = 1; break; }
+      t -= nt;
+    }
+    s_tile[0] = b; s_tile[1] = e; s_tile[2] = q0; s_tile[3] = found;
+    s_abort = 0;
+    mbar_init(&q_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); mbar_init(&s_full[i], 1); }
+    mbar_init(&p_ready, 4); mbar_init(&o_full, 1);
+    fence_barrier_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+  }
+  __syncthreads();
+  if (!s_tile[3]) return;                          // grid is an upper bound on the tile count
+  if (warp == 1) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t tS0 = tmem, tO = tmem + 256;
+  const int seg_b = s_tile[0], seg_e = s_tile[1], q0 = s_tile[2];
+  const int ntiles = (q0 - seg_b) / FK + 1;        // kv tiles up to and including the diagonal
+  volatile int* abort_flag = &s_abort;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      mbar_expect_tx(&q_full, tile_bytes);
+      for (int b = 0; b < nkb; ++b) tma_load_3d(sQ + b * 16384, &tmQ, &q_full, b * 64, head, q0);
+      for (int j = 0; j < ntiles; ++j) {
+        int s = j & 1;
+        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kTimeoutEmpty)) break;
+        mbar_expect_tx(&kv_full[s], 2 * tile_bytes);
+        int r0 = seg_b + j * FK;
+        for (int b = 0; b < nkb; ++b) {
+          tma_load_3d(sK + s * tile_bytes + b * 16384, &tmK, &kv_full[s], b * 64, head, r0);
+          tma_load_3d(sV + s * tile_bytes + b * 16384, &tmV, &kv_full[s], b * 64, head, r0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    const uint32_t idesc_s = make_idesc(FQ, FK, 0, 0);
+    const uint32_t idesc_o = make_idesc(FQ, HDN, 0, 1);
+    bool ok = true;
+    auto issue_s = [&](int j) {
+      // S_j = Q K_j^T into buffer j&1
+      int s = j & 1;
+      if (lane == 0) ok = mbar_wait(&kv_full[s], (j >> 1) & 1, abort_flag, p.status, kTimeoutFull);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) return;
+      tc_fence_after();
+      if (lane == 0) {
+        uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + s * tile_bytes);
+        for (int k = 0; k < hd16 / 16; ++k) {
+          uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          umma_bf16(tS0 + s * FK, sdesc_kmajor(qa + off), sdesc_kmajor(ka + off), idesc_s, k != 0);
+        }
+        umma_commit(&s_full[s]);
+      }
+      __syncwarp();
+    };
+    if (lane == 0) ok = mbar_wait(&q_full, 0, abort_flag, p.status, kTimeoutFull);
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (ok) issue_s(0);
+    for (int j = 0; j < ntiles && ok; ++j) {
+      if (j + 1 < ntiles) { issue_s(j + 1); if (!ok) break; }
+      if (lane == 0) ok = mbar_wait(&p_ready, j & 1, abort_flag, p.status, kTimeoutTmemEmpty);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      tc_fence_after();
+      if (lane == 0) {
+        int s = j & 1;
+        uint32_t pa = smem_u32(sP), va = smem_u32(sV + s * tile_bytes);
+        for (int k = 0; k < FK / 16; ++k) {
+          uint64_t ad = sdesc_kmajor(pa + (k >> 2) * 16384 + (k & 3) * 32);
+          uint64_t bd = sdesc_mnmajor(va + k * 2048, 16384);
+          umma_bf16(tO, ad, bd, idesc_o, k != 0);
+        }
+        umma_commit(&kv_empty[s]);
+        umma_commit(&o_full);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax + output
+    const int q = warp & 3;
+    const int r = q * 32 + lane;               // row inside the q tile
+    const int qrow = q0 + r;
+    const uint32_t lane_off = uint32_t(q * 32) << 16;
+    float m = -INFINITY, l = 0.f;
+    float o[HDN];
+#pragma unroll
+    for (int i = 0; i < HDN; ++i) o[i] = 0.f;
+    bool ok = true;
+    for (int j = 0; j < ntiles; ++j) {
+      int s = j & 1;
+      if (!mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t ts = tS0 + s * FK + lane_off;
+      const int kv0 = seg_b + j * FK;
+      const int lim = (j == ntiles - 1) ? (qrow - kv0 + 1) : FK;   // columns < lim are visible (causal)
+      // pass 1: row max
+      float mx = m;
+      for (int c = 0; c < FK; c += 32) {
+        float v[32];
+        tmem_ld32(ts + c, v); tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) if (c + i < lim) mx = fmaxf(mx, v[i] * p.scale_log2);
+      }
+      const float m_new = mx;
+      const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      // fold the previous tile's P.V into the running output before P is overwritten
+      if (j > 0) {
+        if (!mbar_wait(&o_full, (j - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < HDN; c += 16) {
+          float v[16];
+          tmem_ld16(tO + lane_off + c, v); tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) o[c + i] = (o[c + i] + v[i]) * alpha;
+        }
+      }
+      // pass 2: probabilities -> bf16 -> swizzled smem
+      float rs = 0.f;
+      for (int c = 0; c < FK; c += 32) {
+        float v[32];
+        tmem_ld32(ts + c, v); tmem_ld_wait();
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = (c + i < lim) ? exp2f(v[i] * p.scale_log2 - m_use) : 0.f;
+          float p1 = (c + i + 1 < lim) ? exp2f(v[i + 1] * p.scale_log2 - m_use) : 0.f;
+          __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+          rs += __bfloat162float(pk.x) + __bfloat162float(pk.y);
+          w[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) st_p_chunk(sP, r, c + g * 8, w + g * 4);
+      }
+      l = l * alpha + rs;
+      m = m_new;
+      fence_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready);
+    }
+    if (ok && mbar_wait(&o_full, (ntiles - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const bool row_ok = qrow < seg_e;
+      __nv_bfloat16* dst = p.O + long(qrow) * p.ldo + head * p.hd;
+#pragma unroll
+      for (int c = 0; c < HDN; c += 16) {
+        {
+          float v[16];
+          tmem_ld16(tO + lane_off + c, v); tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int i = 0; i < 16; i += 8) {
+              if (c + i < p.hd) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  w[e] = pack_bf16((o[c + i + 2 * e] + v[i + 2 * e]) * inv, (o[c + i + 2 * e + 1] + v[i + 2 * e + 1]) * inv);
+                *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            }
+          }
+        }
+      }
+      if (row_ok) p.lse[long(qrow) * p.H + head] = (l > 0.f) ? m + log2f(l) : -INFINITY;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+}  // namespace nb
+
+#include <string.h>
+
+namespace {
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                             const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                             CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn flash_encode_fn() {
+  static EncodeFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess || !ptr) return nullptr;
+    fn = reinterpret_cast<EncodeFn>(ptr);
+  }
+  return fn;
+}
+}  // namespace
+
+// [rows, H, hd] view of a bf16 buffer: element (r, h, c) at base + r*row_pitch + h*hd + c.
+// Box = 64 columns x 1 head x 128 rows; columns past `hd` read as zero.
+extern "C" int nb_head_map(CUtensorMap* m, const void* base, long rows, int H, int hd, long row_pitch_elems) {
+  EncodeFn fn = flash_encode_fn();
+  if (!fn) return 1;
+  cuuint64_t gd[3] = {cuuint64_t(hd), cuuint64_t(H), cuuint64_t(rows)};
+  cuuint64_t gs[2] = {cuuint64_t(hd) * 2, cuuint64_t(row_pitch_elems) * 2};
+  cuuint32_t bx[3] = {64, 1, 128};
+  cuuint32_t es[3] = {1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), gd, gs, bx, es,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 2;
+}
+
+extern "C" {
+
+struct NbFlashArgs {
+  const void* Q; const void* K; const void* V;   // bf16, row pitch `ld_qkv` elements, head h at column h*hd
+  long ld_qkv;
+  void* O; long ldo;
+  float* lse;
+  const int* seg_start; int nseg;
+  int rows, H, hd;
+  float scale;
+  int* status;
+  int max_tiles;       // upper bound on q tiles: ceil(rows/128) + nseg
+};
+
+int nb_flash_fwd(const NbFlashArgs* a, cudaStream_t stream) {
+  using namespace nb;
+  if (a->hd % 8 || a->hd < 8 || a->hd > 128) return -1;
+  if (a->nseg < 1 || a->nseg > kMaxSeg) return -2;
+  CUtensorMap tq, tk, tv;
+  if (nb_head_map(&tq, a->Q, a->rows, a->H, a->hd, a->ld_qkv)) return -10;
+  if (nb_head_map(&tk, a->K, a->rows, a->H, a->hd, a->ld_qkv)) return -11;
+  if (nb_head_map(&tv, a->V, a->rows, a->H, a->hd, a->ld_qkv)) return -12;
+  FlashParams p;
+  p.nseg = a->nseg; p.H = a->H; p.hd = a->hd; p.rows = a->rows; p.seg_start = a->seg_start;
+  p.scale_log2 = a->scale * 1.4426950408889634f;
+  p.O = reinterpret_cast<__nv_bfloat16*>(a->O); p.ldo = a->ldo; p.lse = a->lse; p.status = a->status;
+  const int nkb = (a->hd + 63) / 64;
+  size_t smem = size_t(nkb) * 16384 * 5 + 32768 + 1024;
+  dim3 grid(a->max_tiles, a->H);
+  if (a->hd <= 64) {
+    static bool set64 = false;
+    if (!set64) {
+      cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+      if (e != cudaSuccess) return int(e);
+      set64 = true;
+    }
+    flash_fwd_kernel<64><<<grid, 192, smem, stream>>>(tq, tk, tv, p);
+  } else {
+    static bool set128 = false;
+    if (!set128) {
+      cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+      if (e != cudaSuccess) return int(e);
+      set128 = true;
+    }
+    flash_fwd_kernel<128><<<grid, 192, smem, stream>>>(tq, tk, tv, p);
+  }
+  return int(cudaGetLastError());
+}
+
+}  // extern "C"

@@ -48,6 +48,7 @@ struct GemmParams {
   const void* E1; const void* E2;  // extra inputs (SwiGLU bwd: gate, up)
   long lde;
   float alpha;
+  int n_valid;              // stats epilogue: columns >= n_valid are padding (stored as -inf)
   int* status;
   int max_tiles;
 };
@@ -306,6 +307,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if (!row_ok) continue;
           const long o = c_base + tl.n0 + c;
           if (p.epilogue == kStoreBf16 || p.epilogue == kStoreBf16Stats) {
+            if (p.epilogue == kStoreBf16Stats) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) if (tl.n0 + c + j >= p.n_valid) v[j] = -INFINITY;
+            }
             uint32_t w[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) w[j] = pack_bf16(v[2 * j] * p.alpha, v[2 * j + 1] * p.alpha);
@@ -446,6 +451,7 @@ struct NbGemmArgs {
   void* C; long ldc; long c_group_stride;
   void* C2; void* C3; const void* E1; const void* E2; long lde;
   float alpha;
+  int n_valid;
   int* status;
   int max_m_tiles;          // upper bound on m tiles over all groups (mode 0)
   int sms;                  // 0 = all
@@ -495,7 +501,7 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
   p.M = a->M; p.N = a->N; p.K = a->K; p.K2 = a->K2; p.offsets = a->offsets; p.rows_per_group = a->rows_per_group;
   p.a_mn = a->a_mn; p.b_mn = a->b_mn; p.b_grouped = a->b_grouped;
   p.C = a->C; p.ldc = a->ldc; p.c_group_stride = a->c_group_stride; p.C2 = a->C2; p.C3 = a->C3;
-  p.E1 = a->E1; p.E2 = a->E2; p.lde = a->lde; p.alpha = a->alpha; p.status = a->status;
+  p.E1 = a->E1; p.E2 = a->E2; p.lde = a->lde; p.alpha = a->alpha; p.n_valid = a->n_valid > 0 ? a->n_valid : a->N; p.status = a->status;
 
   const int n_tiles = (a->N + a->BN - 1) / a->BN;
   long tiles = a->mode == 0 ? long(a->max_m_tiles) * n_tiles : long(a->groups) * ((a->M + BM - 1) / BM) * n_tiles;

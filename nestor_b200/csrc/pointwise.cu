@@ -1,0 +1,321 @@
+// Bandwidth-bound companions of the GEMM and attention kernels: row gathers for token
+// dispatch, weighted slot combines, in-place RoPE on packed q/k, the cross-entropy
+// gradient over a logits chunk, and the fused depth-read + RMSNorm.
+//
+// Every kernel is a pure gather (no atomics): each output element has exactly one writer,
+// which is what makes the backward passes deterministic. Counterparts in the reference:
+// Triton pack / dispatch / combine kernels (nestor/backbones/triton_packed.py:112-169,
+// triton_expert.py:270-344), RoPE epilogue (triton_packed.py:171-322), chunked CE
+// (nestor/train/losses.py:177-209), depth read (nestor/backbones/attention_residual.py:488-718).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace nb {
+
+__device__ __forceinline__ float bf(const __nv_bfloat16 x) { return __bfloat162float(x); }
+
+// out[r, :] = bf16(src[idx[r] / div, :])   (src fp32 or bf16, row pitch lds)
+template <typename TIn>
+__global__ void gather_rows_kernel(const TIn* __restrict__ src, long lds, const int* __restrict__ idx, int div,
+                                   __nv_bfloat16* __restrict__ out, long ldo, int rows, int d) {
+  int r = blockIdx.x * blockDim.y + threadIdx.y;
+  if (r >= rows) return;
+  const TIn* s = src + long(idx[r] / div) * lds;
+  __nv_bfloat16* o = out + long(r) * ldo;
+  for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
+    uint32_t w[4];
+    if constexpr (sizeof(TIn) == 4) {
+      float4 a = *reinterpret_cast<const float4*>(s + c), b = *reinterpret_cast<const float4*>(s + c + 4);
+      __nv_bfloat162 t0 = __floats2bfloat162_rn(a.x, a.y), t1 = __floats2bfloat162_rn(a.z, a.w);
+      __nv_bfloat162 t2 = __floats2bfloat162_rn(b.x, b.y), t3 = __floats2bfloat162_rn(b.z, b.w);
+      w[0] = *reinterpret_cast<uint32_t*>(&t0); w[1] = *reinterpret_cast<uint32_t*>(&t1);
+      w[2] = *reinterpret_cast<uint32_t*>(&t2); w[3] = *reinterpret_cast<uint32_t*>(&t3);
+      *reinterpret_cast<uint4*>(o + c) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+      *reinterpret_cast<uint4*>(o + c) = *reinterpret_cast<const uint4*>(s + c);
+    }
+  }
+}
+
+// out[t, g, :] = sum_{e < group} round_bf16(y[idx[(t*G + g)*group + e], :] * w[(t*G + g)*group + e])   (fp32 out)
+// With w == nullptr the weight is 1. `accumulate` adds into out instead of overwriting.
+__global__ void combine_rows_kernel(const __nv_bfloat16* __restrict__ y, long ldy, const int* __restrict__ idx,
+                                    const float* __restrict__ w, int group, float* __restrict__ out, long ldo,
+                                    int n_out, int d, int accumulate) {
+  int o = blockIdx.x * blockDim.y + threadIdx.y;
+  if (o >= n_out) return;
+  float* dst = out + long(o) * ldo;
+  for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int e = 0; e < group; ++e) {
+      int s = o * group + e;
+      float ww = w ? w[s] : 1.f;
+      uint4 q = *reinterpret_cast<const uint4*>(y + long(idx[s]) * ldy + c);
+      const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&q);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += w ? bf(__float2bfloat16(bf(v[i]) * ww)) : bf(v[i]);
+    }
+    float4* d4 = reinterpret_cast<float4*>(dst + c);
+    if (accumulate) {
+      float4 a = d4[0], b = d4[1];
+      d4[0] = make_float4(a.x + acc[0], a.y + acc[1], a.z + acc[2], a.w + acc[3]);
+      d4[1] = make_float4(b.x + acc[4], b.y + acc[5], b.z + acc[6], b.w + acc[7]);
+    } else {
+      d4[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      d4[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+  }
+}
+
+// Backward of the weighted combine, one warp per sorted row r (slot s = slot_of_row[r]):
+//   dy[r, :] = bf16(g[s / group, :] * w[s]);   dw[s] = <g[s / group, :], y[r, :]>
+__global__ void combine_bwd_kernel(const float* __restrict__ g, long ldg, const __nv_bfloat16* __restrict__ y, long ldy,
+                                   const int* __restrict__ slot_of_row, const float* __restrict__ w, int group,
+                                   __nv_bfloat16* __restrict__ dy, long lddy, float* __restrict__ dw, int rows, int d) {
+  int r = blockIdx.x * blockDim.y + threadIdx.y;
+  if (r >= rows) return;
+  int s = slot_of_row[r];
+  float ww = w ? w[s] : 1.f;
+  const float* gr = g + long(s / group) * ldg;
+  const __nv_bfloat16* yr = y + long(r) * ldy;
+  __nv_bfloat16* dr = dy + long(r) * lddy;
+  float dot = 0.f;
+  for (int c = threadIdx.x * 8; c < d; c += 32 * 8) {
+    float4 a = *reinterpret_cast<const float4*>(gr + c), b = *reinterpret_cast<const float4*>(gr + c + 4);
+    float gv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    uint32_t o[4];
+    if (dw) {
+      uint4 q = *reinterpret_cast<const uint4*>(yr + c);
+      const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&q);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dot += gv[i] * bf(v[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 t = __floats2bfloat162_rn(gv[2 * i] * ww, gv[2 * i + 1] * ww);
+      o[i] = *reinterpret_cast<uint32_t*>(&t);
+    }
+    *reinterpret_cast<uint4*>(dr + c) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  if (dw) {
+#pragma unroll
+    for (int sft = 16; sft > 0; sft >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, sft);
+    if (threadIdx.x == 0) dw[s] = dot;
+  }
+}
+
+// In-place rotate-half RoPE on the q and k column ranges of a packed [rows, ld] bf16 buffer.
+// One warp per row; `sign` = +1 forward, -1 for the gradient (inverse rotation).
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ buf, long ld, const int* __restrict__ pos, int rows, int H,
+                            int hd, int k_offset, float log2_base, float sign) {
+  int r = blockIdx.x * blockDim.y + threadIdx.y;
+  if (r >= rows) return;
+  const int half = hd / 2;
+  const float p = float(pos[r]);
+  __nv_bfloat16* row = buf + long(r) * ld;
+  for (int i = threadIdx.x; i < 2 * H * half; i += 32) {
+    int part = i / (H * half), rem = i - part * H * half;
+    int h = rem / half, j = rem - h * half;
+    float inv_freq = exp2f(-log2_base * (2.f * j) / hd);
+    float sn, cs;
+    sincosf(p * inv_freq, &sn, &cs);
+    sn *= sign;
+    __nv_bfloat16* x = row + part * k_offset + h * hd;
+    float x1 = bf(x[j]), x2 = bf(x[j + half]);
+    x[j] = __float2bfloat16(x1 * cs - x2 * sn);
+    x[j + half] = __float2bfloat16(x2 * cs + x1 * sn);
+  }
+}
+
+// Cross-entropy over a chunk of bf16 logits [n, ld] with per-(row, tile) (max, sumexp) partials:
+// loss[row] = lse - logit[target]; logits are overwritten by (softmax - onehot) (zero for ignored rows).
+__global__ void ce_grad_kernel(__nv_bfloat16* __restrict__ logits, long ld, int V, const float2* __restrict__ part,
+                               int n_tiles, const long* __restrict__ targets, long ignore_index,
+                               float* __restrict__ loss, int n) {
+  int r = blockIdx.x;
+  if (r >= n) return;
+  __shared__ float s_lse;
+  if (threadIdx.x < 32) {
+    float m = -INFINITY;
+    for (int t = threadIdx.x; t < n_tiles; t += 32) m = fmaxf(m, part[long(r) * n_tiles + t].x);
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, s));
+    float sum = 0.f;
+    for (int t = threadIdx.x; t < n_tiles; t += 32) {
+      float2 q = part[long(r) * n_tiles + t];
+      sum += q.y * __expf(q.x - m);
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
+    if (threadIdx.x == 0) s_lse = m + __logf(sum);
+  }
+  __syncthreads();
+  const float lse = s_lse;
+  const long tgt = targets[r];
+  const bool valid = tgt != ignore_index;
+  __nv_bfloat16* row = logits + long(r) * ld;
+  if (threadIdx.x == 0) loss[r] = valid ? lse - bf(row[tgt]) : 0.f;
+  __syncthreads();
+  for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+    uint4 q = *reinterpret_cast<uint4*>(row + c);
+    __nv_bfloat16* v = reinterpret_cast<__nv_bfloat16*>(&q);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float g = valid ? __expf(bf(v[i]) - lse) - ((c + i) == tgt ? 1.f : 0.f) : 0.f;
+      v[i] = __float2bfloat16((c + i) < V ? g : 0.f);
+    }
+    *reinterpret_cast<uint4*>(row + c) = q;
+  }
+}
+
+// Fused depth read + RMSNorm, one warp per token (d <= 32 * 8 * DEPTH_VEC ... handled by a strided loop):
+//   r_i = rsqrt(mean(s_i^2) + eps_read);  z_i = r_i <s_i, q> / sqrt(d);  w = softmax_i(z) * gain_i
+//   h = sum_i (w_i r_i) s_i;   out = bf16(h * rsqrt(mean(h^2) + eps_norm) * gamma)
+// Online over sources: one pass, running (max, denominator, accumulator). Saves per-(token, source)
+// (r_i, u_i = <s_i, q>) and per-token rstd for the backward.
+constexpr int kMaxSources = 48;
+struct SourceList { const float* ptr[kMaxSources]; };
+
+template <int NV>   // d == NV * 32 * 4 is not required; each lane owns NV float4 chunks at stride 32
+__global__ void depth_read_norm_fwd_kernel(SourceList src, int n, const float* __restrict__ query,
+                                           const float* __restrict__ gains, const float* __restrict__ gamma,
+                                           float eps_read, float eps_norm, __nv_bfloat16* __restrict__ out,
+                                           float* __restrict__ h_out, float* __restrict__ stats, float* __restrict__ rstd_out,
+                                           int T, int d) {
+  int t = blockIdx.x * blockDim.y + threadIdx.y;
+  if (t >= T) return;
+  const int lane = threadIdx.x;
+  const int nchunk = d / 4;
+  float4 qv[NV], acc[NV];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    int c = lane + 32 * v;
+    qv[v] = c < nchunk ? reinterpret_cast<const float4*>(query)[c] : make_float4(0, 0, 0, 0);
+    acc[v] = make_float4(0, 0, 0, 0);
+  }
+  const float inv_sqrt_d = rsqrtf(float(d));
+  float m = -INFINITY, den = 0.f;
+  for (int i = 0; i < n; ++i) {
+    const float4* s = reinterpret_cast<const float4*>(src.ptr[i] + long(t) * d);
+    float4 sv[NV];
+    float ss = 0.f, dot = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      int c = lane + 32 * v;
+      sv[v] = c < nchunk ? s[c] : make_float4(0, 0, 0, 0);
+      ss += sv[v].x * sv[v].x + sv[v].y * sv[v].y + sv[v].z * sv[v].z + sv[v].w * sv[v].w;
+      dot += sv[v].x * qv[v].x + sv[v].y * qv[v].y + sv[v].z * qv[v].z + sv[v].w * qv[v].w;
+    }
+#pragma unroll
+    for (int sft = 16; sft > 0; sft >>= 1) {
+      ss += __shfl_xor_sync(0xffffffffu, ss, sft);
+      dot += __shfl_xor_sync(0xffffffffu, dot, sft);
+    }
+    float r = rsqrtf(ss / d + eps_read);
+    float z = r * dot * inv_sqrt_d;
+    float m_new = fmaxf(m, z);
+    float a = __expf(m - m_new), e = __expf(z - m_new);
+    float coef = e * gains[i] * r;
+    den = den * a + e;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      acc[v].x = acc[v].x * a + coef * sv[v].x; acc[v].y = acc[v].y * a + coef * sv[v].y;
+      acc[v].z = acc[v].z * a + coef * sv[v].z; acc[v].w = acc[v].w * a + coef * sv[v].w;
+    }
+    m = m_new;
+    if (lane == 0 && stats) { stats[(long(t) * n + i) * 2] = r; stats[(long(t) * n + i) * 2 + 1] = dot; }
+  }
+  float inv_den = 1.f / den, hs = 0.f;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    acc[v].x *= inv_den; acc[v].y *= inv_den; acc[v].z *= inv_den; acc[v].w *= inv_den;
+    hs += acc[v].x * acc[v].x + acc[v].y * acc[v].y + acc[v].z * acc[v].z + acc[v].w * acc[v].w;
+  }
+#pragma unroll
+  for (int sft = 16; sft > 0; sft >>= 1) hs += __shfl_xor_sync(0xffffffffu, hs, sft);
+  float rstd = rsqrtf(hs / d + eps_norm);
+  if (lane == 0 && rstd_out) rstd_out[t] = rstd;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    int c = lane + 32 * v;
+    if (c < nchunk) {
+      if (h_out) reinterpret_cast<float4*>(h_out + long(t) * d)[c] = acc[v];
+      if (out) {
+        float4 g = reinterpret_cast<const float4*>(gamma)[c];
+        __nv_bfloat162 a = __floats2bfloat162_rn(acc[v].x * rstd * g.x, acc[v].y * rstd * g.y);
+        __nv_bfloat162 b = __floats2bfloat162_rn(acc[v].z * rstd * g.z, acc[v].w * rstd * g.w);
+        uint2 w = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+        reinterpret_cast<uint2*>(out + long(t) * d)[c] = w;
+      }
+    }
+  }
+}
+
+}  // namespace nb
+
+extern "C" {
+
+int nb_gather_rows(const void* src, int src_is_f32, long lds, const int* idx, int div, void* out, long ldo, int rows,
+                   int d, cudaStream_t st) {
+  if (d % 8) return -1;
+  dim3 block(32, 8), grid((rows + 7) / 8);
+  if (src_is_f32)
+    nb::gather_rows_kernel<float><<<grid, block, 0, st>>>((const float*)src, lds, idx, div, (__nv_bfloat16*)out, ldo, rows, d);
+  else
+    nb::gather_rows_kernel<__nv_bfloat16><<<grid, block, 0, st>>>((const __nv_bfloat16*)src, lds, idx, div,
+                                                                  (__nv_bfloat16*)out, ldo, rows, d);
+  return int(cudaGetLastError());
+}
+
+int nb_combine_rows(const void* y, long ldy, const int* idx, const float* w, int group, float* out, long ldo, int n_out,
+                    int d, int accumulate, cudaStream_t st) {
+  if (d % 8) return -1;
+  dim3 block(32, 8), grid((n_out + 7) / 8);
+  nb::combine_rows_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)y, ldy, idx, w, group, out, ldo, n_out, d, accumulate);
+  return int(cudaGetLastError());
+}
+
+int nb_combine_bwd(const float* g, long ldg, const void* y, long ldy, const int* slot_of_row, const float* w, int group,
+                   void* dy, long lddy, float* dw, int rows, int d, cudaStream_t st) {
+  if (d % 8) return -1;
+  dim3 block(32, 8), grid((rows + 7) / 8);
+  nb::combine_bwd_kernel<<<grid, block, 0, st>>>(g, ldg, (const __nv_bfloat16*)y, ldy, slot_of_row, w, group,
+                                                (__nv_bfloat16*)dy, lddy, dw, rows, d);
+  return int(cudaGetLastError());
+}
+
+int nb_rope(void* buf, long ld, const int* pos, int rows, int H, int hd, int k_offset, float base, float sign,
+            cudaStream_t st) {
+  dim3 block(32, 8), grid((rows + 7) / 8);
+  nb::rope_kernel<<<grid, block, 0, st>>>((__nv_bfloat16*)buf, ld, pos, rows, H, hd, k_offset, log2f(base), sign);
+  return int(cudaGetLastError());
+}
+
+int nb_ce_grad(void* logits, long ld, int V, const void* part, int n_tiles, const long* targets, long ignore_index,
+               float* loss, int n, cudaStream_t st) {
+  if (ld % 8) return -1;
+  nb::ce_grad_kernel<<<n, 256, 0, st>>>((__nv_bfloat16*)logits, ld, V, (const float2*)part, n_tiles, targets,
+                                        ignore_index, loss, n);
+  return int(cudaGetLastError());
+}
+
+int nb_depth_read_norm(const float* const* sources, int n, const float* query, const float* gains, const float* gamma,
+                       float eps_read, float eps_norm, void* out, float* h_out, float* stats, float* rstd, int T, int d,
+                       cudaStream_t st) {
+  if (n < 1 || n > nb::kMaxSources || d % 4) return -1;
+  nb::SourceList sl;
+  for (int i = 0; i < n; ++i) sl.ptr[i] = sources[i];
+  dim3 block(32, 4), grid((T + 3) / 4);
+  int nv = (d / 4 + 31) / 32;
+#define NB_DR(NV) nb::depth_read_norm_fwd_kernel<NV><<<grid, block, 0, st>>>(sl, n, query, gains, gamma, eps_read, \
+      eps_norm, (__nv_bfloat16*)out, h_out, stats, rstd, T, d)
+  if (nv <= 1) NB_DR(1); else if (nv <= 2) NB_DR(2); else if (nv <= 4) NB_DR(4); else if (nv <= 5) NB_DR(5);
+  else if (nv <= 8) NB_DR(8); else if (nv <= 10) NB_DR(10); else return -2;
+#undef NB_DR
+  return int(cudaGetLastError());
+}
+
+}  // extern "C"

@@ -17,7 +17,7 @@
 
 namespace nb {
 
-constexpr uint32_t kSpinLimit = 1u << 26;   // try_wait polls before a wait gives up
+constexpr uint32_t kSpinLimit = 1u << 24;   // try_wait polls before a wait gives up
 
 enum Status : int {
   kOk = 0,

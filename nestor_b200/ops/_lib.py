@@ -30,7 +30,8 @@ class GemmArgs(C.Structure):
         ("A", Operand), ("B", Operand), ("A2", Operand), ("B2", Operand),
         ("C", C.c_void_p), ("ldc", C.c_long), ("c_group_stride", C.c_long),
         ("C2", C.c_void_p), ("C3", C.c_void_p), ("E1", C.c_void_p), ("E2", C.c_void_p), ("lde", C.c_long),
-        ("alpha", C.c_float), ("status", C.c_void_p), ("max_m_tiles", C.c_int), ("sms", C.c_int),
+        ("alpha", C.c_float), ("n_valid", C.c_int), ("status", C.c_void_p), ("max_m_tiles", C.c_int),
+        ("sms", C.c_int),
     ]
 
 
@@ -75,3 +76,25 @@ def check_status(device: torch.device) -> None:
     if code:
         status_word(device).zero_()
         raise RuntimeError(f"nestor_b200 kernel reported status {code} (a bounded device-side wait gave up)")
+
+
+class FlashArgs(C.Structure):
+    _fields_ = [
+        ("Q", C.c_void_p), ("K", C.c_void_p), ("V", C.c_void_p), ("ld_qkv", C.c_long),
+        ("O", C.c_void_p), ("ldo", C.c_long), ("lse", C.c_void_p),
+        ("seg_start", C.c_void_p), ("nseg", C.c_int),
+        ("rows", C.c_int), ("H", C.c_int), ("hd", C.c_int), ("scale", C.c_float),
+        ("status", C.c_void_p), ("max_tiles", C.c_int),
+    ]
+
+
+class FlashBwdArgs(C.Structure):
+    _fields_ = [
+        ("Q", C.c_void_p), ("K", C.c_void_p), ("V", C.c_void_p), ("ld_qkv", C.c_long),
+        ("O", C.c_void_p), ("ld_o", C.c_long), ("dO", C.c_void_p), ("ld_do", C.c_long),
+        ("lse", C.c_void_p), ("delta", C.c_void_p),
+        ("dQ", C.c_void_p), ("dK", C.c_void_p), ("dV", C.c_void_p), ("ld_dqkv", C.c_long),
+        ("seg_start", C.c_void_p), ("nseg", C.c_int),
+        ("rows", C.c_int), ("H", C.c_int), ("hd", C.c_int), ("scale", C.c_float),
+        ("status", C.c_void_p), ("max_tiles", C.c_int),
+    ]

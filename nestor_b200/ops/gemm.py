@@ -52,7 +52,7 @@ def _launch(args: _lib.GemmArgs) -> None:
 def gemm_rows(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: int = 1, b_mn: bool = False,
               out: Tensor | None = None, epilogue: int = STORE_BF16, alpha: float = 1.0, bn: int | None = None,
               A2: Tensor | None = None, B2: Tensor | None = None, extra_out: tuple = (), extra_in: tuple = (),
-              n: int | None = None, sms: int = 0) -> Tensor:
+              n: int | None = None, n_valid: int = 0, sms: int = 0) -> Tensor:
     """Row-grouped GEMM.
 
     ``A [rows, K]``; ``B`` is ``[G, N, K]`` (K-major) or ``[G, K, N]`` (``b_mn``) — 2-D for a
@@ -94,6 +94,7 @@ def gemm_rows(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: in
     a.E2 = extra_in[1].data_ptr() if len(extra_in) > 1 else None
     a.lde = extra_in[0].stride(0) if len(extra_in) > 0 else 0
     a.alpha = alpha
+    a.n_valid = n_valid
     a.status = _lib.status_word(dev).data_ptr()
     a.max_m_tiles = -(-rows // 128) + groups
     a.sms = sms

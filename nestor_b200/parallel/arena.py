@@ -54,7 +54,16 @@ class _ComputeView(torch.autograd.Function):
     def backward(ctx, grad: Tensor):
         if len(ctx.shapes) == 1:
             return None, grad.reshape(ctx.shapes[0]).to(ctx.dtypes[0])
-        return (None, *[g.reshape(s).to(dt) for g, s, dt in zip(grad.unbind(0), ctx.shapes, ctx.dtypes)])
+        if grad.shape[0] == len(ctx.shapes):          # stack of same-shape parameters
+            return (None, *[g.reshape(s).to(dt) for g, s, dt in zip(grad.unbind(0), ctx.shapes, ctx.dtypes)])
+        per = len(ctx.shapes) // grad.shape[0]        # fused groups: split each group's rows
+        outs = []
+        for gi, g in enumerate(grad.unbind(0)):
+            r = 0
+            for s, dt in zip(ctx.shapes[gi * per : (gi + 1) * per], ctx.dtypes[gi * per : (gi + 1) * per]):
+                outs.append(g[r : r + s[0]].reshape(s).to(dt))
+                r += s[0]
+        return (None, *outs)
 
 
 class ParamArena:
@@ -105,13 +114,27 @@ class ParamArena:
         self.grad.zero_()
 
     def compute_view(self, p: Tensor) -> Tensor:
-        """Compute-dtype weight of ``p`` wired into autograd (gradient lands in ``p.grad``)."""
+        """Compute-dtype weight of ``p`` wired into autograd (gradient lands in ``p.grad``).
 
-        s = self.slot(p)
-        view = self.compute[s.offset : s.offset + s.numel].view(s.shape)
+        The returned tensor carries ``_nb_grad``: the fp32 gradient view a kernel may accumulate
+        into directly (returning no gradient through autograd for that operand).
+        """
+
         if self.compute is self.master:
             return p
-        return _ComputeView.apply(view, p) if torch.is_grad_enabled() and p.requires_grad else view
+        s = self.slot(p)
+        return self._wire(self.compute[s.offset : s.offset + s.numel].view(s.shape),
+                          self.grad[s.offset : s.offset + s.numel].view(s.shape), [p])
+
+    def _wire(self, view: Tensor, grad_view: Tensor, params: list[Tensor]) -> Tensor:
+        out = _ComputeView.apply(view, *params) if torch.is_grad_enabled() and params[0].requires_grad else view
+        out._nb_grad = grad_view
+        return out
+
+    def _strided(self, slots: list[Slot]) -> tuple[int, bool]:
+        stride = slots[1].offset - slots[0].offset if len(slots) > 1 else slots[0].numel
+        ok = all(b.offset - a.offset == stride for a, b in zip(slots[:-1], slots[1:]))
+        return stride, ok
 
     def stack_view(self, params: Iterable[Tensor]) -> Tensor:
         """``[n, *shape]`` operand over ``n`` same-shape parameters at a constant stride (no copy)."""
@@ -119,16 +142,37 @@ class ParamArena:
         params = list(params)
         slots = [self.slot(p) for p in params]
         shape = slots[0].shape
-        stride = slots[1].offset - slots[0].offset if len(slots) > 1 else slots[0].numel
-        ok = all(s.shape == shape for s in slots) and all(
-            b.offset - a.offset == stride for a, b in zip(slots[:-1], slots[1:]))
+        stride, ok = self._strided(slots)
+        ok = ok and all(s.shape == shape for s in slots)
         if not ok or self.compute is self.master:
             return torch.stack([self.compute_view(p) for p in params], dim=0)
         inner = list(torch.empty(shape, device="meta").stride())
-        view = torch.as_strided(self.compute, (len(params), *shape), (stride, *inner), slots[0].offset)
-        if torch.is_grad_enabled() and params[0].requires_grad:
-            return _ComputeView.apply(view, *params)
-        return view
+        geom = ((len(params), *shape), (stride, *inner), slots[0].offset)
+        return self._wire(torch.as_strided(self.compute, *geom), torch.as_strided(self.grad, *geom), params)
+
+    def fused_view(self, groups: list[list[Tensor]]) -> Tensor:
+        """``[G, sum(rows), cols]`` operand where group ``g`` is the row-concatenation of ``groups[g]``.
+
+        Requires the members of a group to be adjacent in the arena (each ``[rows_i, cols]`` with
+        ``rows_i * cols`` a multiple of the arena alignment) and the groups to sit at a constant
+        stride — true for the per-column ``q_proj, k_proj, v_proj`` triples. Falls back to a copy.
+        """
+
+        flat = [p for g in groups for p in g]
+        cols = flat[0].shape[-1]
+        rows = sum(p.shape[0] for p in groups[0])
+        firsts = [self.slot(g[0]) for g in groups]
+        stride, ok = self._strided(firsts)
+        for g in groups:
+            off = self.slot(g[0]).offset
+            for p in g:
+                ok = ok and self.slot(p).offset == off and p.shape[-1] == cols
+                off += p.numel()
+        if not ok or self.compute is self.master:
+            return torch.stack([torch.cat([self.compute_view(p) for p in g], dim=0) for g in groups], dim=0)
+        geom = ((len(groups), rows, cols), (stride, cols, 1), firsts[0].offset)
+        out = self._wire(torch.as_strided(self.compute, *geom), torch.as_strided(self.grad, *geom), flat)
+        return out
 
     def buckets(self, bucket_elems: int) -> list[tuple[int, int]]:
         """``[(offset, numel)]`` covering the arena in order, each at most ``bucket_elems`` long."""
