@@ -39,10 +39,11 @@ __global__ void gather_rows_kernel(const TIn* __restrict__ src, long lds, const 
 }
 
 // out[t, g, :] = sum_{e < group} round_bf16(y[idx[(t*G + g)*group + e], :] * w[(t*G + g)*group + e])   (fp32 out)
-// With w == nullptr the weight is 1. `accumulate` adds into out instead of overwriting.
+// With w == nullptr the weight is 1. `accumulate` adds into out instead of overwriting; `round_products`
+// rounds each weighted row to bf16 before the fp32 sum (the expert-combine contract).
 __global__ void combine_rows_kernel(const __nv_bfloat16* __restrict__ y, long ldy, const int* __restrict__ idx,
                                     const float* __restrict__ w, int group, float* __restrict__ out, long ldo,
-                                    int n_out, int d, int accumulate) {
+                                    int n_out, int d, int accumulate, int round_products) {
   int o = blockIdx.x * blockDim.y + threadIdx.y;
   if (o >= n_out) return;
   float* dst = out + long(o) * ldo;
@@ -56,7 +57,7 @@ __global__ void combine_rows_kernel(const __nv_bfloat16* __restrict__ y, long ld
       uint4 q = *reinterpret_cast<const uint4*>(y + long(idx[s]) * ldy + c);
       const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&q);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] += w ? bf(__float2bfloat16(bf(v[i]) * ww)) : bf(v[i]);
+      for (int i = 0; i < 8; ++i) acc[i] += round_products ? bf(__float2bfloat16(bf(v[i]) * ww)) : bf(v[i]) * ww;
     }
     float4* d4 = reinterpret_cast<float4*>(dst + c);
     if (accumulate) {
@@ -271,10 +272,11 @@ int nb_gather_rows(const void* src, int src_is_f32, long lds, const int* idx, in
 }
 
 int nb_combine_rows(const void* y, long ldy, const int* idx, const float* w, int group, float* out, long ldo, int n_out,
-                    int d, int accumulate, cudaStream_t st) {
+                    int d, int accumulate, int round_products, cudaStream_t st) {
   if (d % 8) return -1;
   dim3 block(32, 8), grid((n_out + 7) / 8);
-  nb::combine_rows_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)y, ldy, idx, w, group, out, ldo, n_out, d, accumulate);
+  nb::combine_rows_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)y, ldy, idx, w, group, out, ldo, n_out, d, accumulate,
+                                                 round_products && w != nullptr);
   return int(cudaGetLastError());
 }
 

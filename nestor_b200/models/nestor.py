@@ -151,22 +151,27 @@ class Layer(nn.Module):
         self.dense_no_router = dense_no_router
 
     # -- weight views ---------------------------------------------------------------
-    def stacked(self, name: str) -> Tensor:
-        """``[G, ...]`` stack of one projection across columns."""
+    def qkv_weight(self) -> Tensor:
+        """``[G, 3*inner, d]``: every column's ``q_proj, k_proj, v_proj`` rows, one operand."""
 
-        return Wstack(self, [getattr(g, name).weight for g in self.attention_groups])
+        groups = [[g.q_proj.weight, g.k_proj.weight, g.v_proj.weight] for g in self.attention_groups]
+        arena = self.__dict__.get("_nestor_arena")
+        if arena is not None and groups[0][0].requires_grad:
+            return arena.fused_view(groups)
+        return torch.stack([torch.cat(g, dim=0) for g in groups], dim=0)
+
+    def out_weight(self) -> Tensor:
+        return Wstack(self, [g.out_proj.weight for g in self.attention_groups])
 
     # -- halves -----------------------------------------------------------------------
     def attention(self, n: Tensor, ctx: "BlockContext", cd: torch.dtype) -> Tensor:
         s = self.spec
         if s.G == 1:
-            g = self.attention_groups[0]
-            out = ops.dense_attention(n, ctx.B, ctx.S, W(self, g.q_proj.weight), W(self, g.k_proj.weight),
-                                      W(self, g.v_proj.weight), W(self, g.out_proj.weight), s.heads, s.head_dim, s.rope_base, cd, pos=ctx.pos)
+            out = ops.dense_attention(n, ctx.B, ctx.S, self.qkv_weight(), self.out_weight(),
+                                      s.heads, s.head_dim, s.rope_base, cd, pos=ctx.pos)
             return out.unsqueeze(1)
-        return ops.column_attention(
-            n, ctx.plan, ctx.gates, self.stacked("q_proj"), self.stacked("k_proj"), self.stacked("v_proj"),
-            self.stacked("out_proj"), s.heads, s.head_dim, s.rope_base, cd)
+        return ops.column_attention(n, ctx.plan, ctx.gates, self.qkv_weight(), self.out_weight(),
+                                    s.heads, s.head_dim, s.rope_base, cd)
 
     def experts(self, n: Tensor, ctx: "BlockContext", cd: torch.dtype) -> tuple[Tensor, dict]:
         """Returns the expert update broadcastable against ``[T, k, d]`` and routing aux."""

@@ -1,1 +1,368 @@
-"""Kernel-backed op bodies (filled in by the modules under ``nestor_b200/ops/kernels``)."""
+"""Kernel-backed bodies of the hot ops (CUDA tensors only).
+
+Each op is a ``torch.autograd.Function`` whose forward and backward are sequences of
+launches from the in-tree sm_100a library: the persistent tcgen05 grouped GEMM
+(:mod:`nestor_b200.ops.gemm`), the varlen flash-attention kernels
+(:mod:`nestor_b200.ops.flash`) and the gather / combine / RoPE / cross-entropy / depth-read
+kernels of ``csrc/pointwise.cu``. Signatures match :mod:`nestor_b200.ops.reference`.
+
+Weight gradients: when a weight operand comes from the parameter arena it carries
+``_nb_grad`` (its fp32 gradient view) and the reduction-grouped GEMM accumulates into that
+view directly; autograd then sees ``None`` for the operand. Otherwise an fp32 gradient
+tensor is returned through autograd as usual.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+from torch import Tensor
+
+from nestor_b200.ops import _lib, flash, gemm as G
+from nestor_b200.ops import reference as ref
+from nestor_b200.ops.reference import ColumnPlan, ExpertPlan
+
+BF16 = torch.bfloat16
+_protos_done = False
+
+
+def _L():
+    global _protos_done
+    L = _lib.lib()
+    if not _protos_done:
+        vp, i, l, f = C.c_void_p, C.c_int, C.c_long, C.c_float
+        L.nb_gather_rows.argtypes = [vp, i, l, vp, i, vp, l, i, i, vp]
+        L.nb_combine_rows.argtypes = [vp, l, vp, vp, i, vp, l, i, i, i, i, vp]
+        L.nb_combine_bwd.argtypes = [vp, l, vp, l, vp, vp, i, vp, l, vp, i, i, vp]
+        L.nb_rope.argtypes = [vp, l, vp, i, i, i, i, f, f, vp]
+        L.nb_ce_grad.argtypes = [vp, l, i, vp, i, vp, l, vp, i, vp]
+        L.nb_depth_read_norm.argtypes = [vp, i, vp, vp, vp, f, f, vp, vp, vp, vp, i, i, vp]
+        for fn in (L.nb_gather_rows, L.nb_combine_rows, L.nb_combine_bwd, L.nb_rope, L.nb_ce_grad,
+                   L.nb_depth_read_norm):
+            fn.restype = C.c_int
+        _protos_done = True
+    return L
+
+
+def _ck(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with code {rc}")
+    _lib.count_launch()
+
+
+def _ptr(t: Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+def _st():
+    return C.c_void_p(_lib.stream_ptr())
+
+
+# ------------------------------------------------------------------- pointwise launchers
+def gather_rows(src: Tensor, idx: Tensor, div: int = 1) -> Tensor:
+    """``out[r] = bf16(src[idx[r] // div])`` for a 2-D fp32/bf16 ``src`` with contiguous rows."""
+
+    rows, d = idx.numel(), src.shape[-1]
+    out = torch.empty(rows, d, dtype=BF16, device=src.device)
+    _ck(_L().nb_gather_rows(src.data_ptr(), int(src.dtype == torch.float32), src.stride(0), idx.data_ptr(), div,
+                            out.data_ptr(), d, rows, d, _st()), "gather_rows")
+    return out
+
+
+def combine_rows(y: Tensor, idx: Tensor, w: Tensor | None, group: int, n_out: int, out: Tensor | None = None,
+                 accumulate: bool = False, round_products: bool = True) -> Tensor:
+    """``out[o] = sum_{e<group} y[idx[o*group+e]] * w[o*group+e]`` in fp32 (each product first rounded to
+    bf16 when ``round_products``)."""
+
+    d = y.shape[-1]
+    if out is None:
+        out = torch.empty(n_out, d, dtype=torch.float32, device=y.device)
+    _ck(_L().nb_combine_rows(y.data_ptr(), y.stride(0), idx.data_ptr(), _ptr(w), group, out.data_ptr(), out.stride(0),
+                             n_out, d, int(accumulate), int(round_products), _st()), "combine_rows")
+    return out
+
+
+def combine_bwd(g: Tensor, y: Tensor, slot_of_row: Tensor, w: Tensor | None, group: int,
+                need_dw: bool) -> tuple[Tensor, Tensor | None]:
+    rows, d = y.shape
+    dy = torch.empty(rows, d, dtype=BF16, device=y.device)
+    dw = torch.empty(rows, dtype=torch.float32, device=y.device) if need_dw else None
+    _ck(_L().nb_combine_bwd(g.data_ptr(), g.stride(0), y.data_ptr(), y.stride(0), slot_of_row.data_ptr(), _ptr(w), group,
+                            dy.data_ptr(), d, _ptr(dw), rows, d, _st()), "combine_bwd")
+    return dy, dw
+
+
+def rope_(buf: Tensor, pos: Tensor, heads: int, head_dim: int, k_offset: int, base: float, sign: float) -> None:
+    """In-place RoPE on the q (columns 0..) and k (columns ``k_offset``..) ranges of ``buf``."""
+
+    _ck(_L().nb_rope(buf.data_ptr(), buf.stride(0), pos.data_ptr(), buf.shape[0], heads, head_dim, k_offset,
+                     float(base), float(sign), _st()), "rope")
+
+
+def _wgrad(a: Tensor, b: Tensor, w: Tensor, *, offsets: Tensor | None, groups: int, transpose_out: bool = False):
+    """Weight gradient ``a^T @ b`` per group. Accumulates into ``w._nb_grad`` when present (returns None)."""
+
+    target = getattr(w, "_nb_grad", None)
+    if target is not None:
+        G.gemm_reduce(a, b, offsets=offsets, groups=groups, out=target, epilogue=G.ACCUM_F32)
+        return None
+    shape = (groups, a.shape[1], b.shape[1]) if w.ndim == 3 else (a.shape[1], b.shape[1])
+    out = torch.empty(shape, dtype=torch.float32, device=a.device)
+    G.gemm_reduce(a, b, offsets=offsets, groups=groups, out=out, epilogue=G.STORE_F32)
+    return out.to(w.dtype)
+
+
+# ---------------------------------------------------------------------------- linear
+class _Linear(torch.autograd.Function):
+    """``y = x @ w^T`` with ``w [N, K]`` (bf16). ``x`` may be fp32 (rounded to bf16 on the way in)."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, w: Tensor) -> Tensor:
+        xb = x if x.dtype == BF16 else x.to(BF16)
+        n = w.shape[0]
+        npad = max(8, -(-n // 8) * 8)
+        y = G.gemm_rows(xb.contiguous(), w, n=npad)
+        ctx.save_for_backward(xb, w)
+        ctx.n, ctx.x_dtype = n, x.dtype
+        ctx.w_ref = w
+        return y if npad == n else y[:, :n]
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):
+        xb, w = ctx.saved_tensors
+        n = ctx.n
+        npad = max(8, -(-n // 8) * 8)
+        dyb = dy.to(BF16)
+        if npad != n:
+            dyb = torch.nn.functional.pad(dyb, (0, npad - n))
+        dyb = dyb.contiguous()
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = G.gemm_rows(dyb, w, b_mn=True, n=w.shape[1]).to(ctx.x_dtype)   # w as [K=N, N=d] MN-major
+        dw = None
+        if ctx.needs_input_grad[1]:
+            wv = ctx.w_ref
+            target = getattr(wv, "_nb_grad", None)
+            if target is not None and npad == n:
+                G.gemm_reduce(dyb, xb, out=target, epilogue=G.ACCUM_F32)
+            else:
+                full = torch.empty(npad, xb.shape[1], dtype=torch.float32, device=xb.device)
+                G.gemm_reduce(dyb, xb, out=full, epilogue=G.STORE_F32)
+                if target is not None:
+                    target.add_(full[:n])
+                else:
+                    dw = full[:n].to(w.dtype)
+        return dx, dw
+
+
+def linear(x: Tensor, w: Tensor) -> Tensor:
+    return _Linear.apply(x, w)
+
+
+def router_scores(x: Tensor, w1: Tensor | None, w2: Tensor, cd: torch.dtype) -> Tensor:
+    h = x
+    if w1 is not None:
+        h = torch.nn.functional.gelu(linear(h, w1.to(BF16) if w1.dtype != BF16 else w1))
+    return linear(h, w2.to(BF16) if w2.dtype != BF16 else w2)
+
+
+# ----------------------------------------------------------------------- expert bank
+class _ExpertBank(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weights, w_up, w_gate, w_down, plan: ExpertPlan, group: int):
+        T, d = x.shape
+        E, _, h = w_up.shape
+        xs = gather_rows(x, plan.order, div=plan.slots)                       # dispatch gather [n, d]
+        hh = torch.empty(plan.n, h, dtype=BF16, device=x.device)
+        gt, ut = torch.empty_like(hh), torch.empty_like(hh)
+        G.gemm_rows(xs, w_gate, B2=w_up, offsets=plan.offsets, groups=E, b_mn=True, out=hh, epilogue=G.SWIGLU,
+                    extra_out=(gt, ut))
+        y = G.gemm_rows(hh, w_down, offsets=plan.offsets, groups=E, b_mn=True)  # [n, d]
+        wf = weights.float().contiguous().view(-1)
+        out = combine_rows(y, plan.inv, wf, group, T * (plan.slots // group))
+        ctx.save_for_backward(xs, hh, gt, ut, y, wf, w_up, w_gate, w_down)
+        ctx.plan, ctx.group, ctx.T, ctx.x_dtype, ctx.w_dtype = plan, group, T, x.dtype, weights.dtype
+        ctx.w_refs = (w_up, w_gate, w_down)
+        return out.view(T, plan.slots // group, d)
+
+    @staticmethod
+    def backward(ctx, dout):
+        xs, hh, gt, ut, y, wf, w_up, w_gate, w_down = ctx.saved_tensors
+        plan, group, T = ctx.plan, ctx.group, ctx.T
+        E, d, h = w_up.shape
+        g2 = dout.contiguous().view(-1, d).float()
+        dy, dw_sorted = combine_bwd(g2, y, plan.order, wf, group, need_dw=ctx.needs_input_grad[1])
+        dgt = torch.empty(plan.n, h, dtype=BF16, device=dy.device)
+        dut = torch.empty_like(dgt)
+        # dH = dY . Wd^T fused with the SwiGLU derivative; Wd [E, h, d] is the K-major B of this product
+        G.gemm_rows(dy, w_down, offsets=plan.offsets, groups=E, out=dgt, epilogue=G.SWIGLU_BWD, extra_out=(dut,),
+                    extra_in=(gt, ut))
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dxs = G.gemm_rows(dgt, w_gate, A2=dut, B2=w_up, offsets=plan.offsets, groups=E)   # [n, d]
+            dx = combine_rows(dxs, plan.inv, None, plan.slots, T).to(ctx.x_dtype)
+        dweights = None
+        if dw_sorted is not None:      # the kernel indexes dw by flat slot already
+            dweights = dw_sorted.view(T, plan.slots).to(ctx.w_dtype)
+        wu, wg, wd = ctx.w_refs
+        d_down = _wgrad(hh, dy, wd, offsets=plan.offsets, groups=E) if ctx.needs_input_grad[4] else None
+        d_gate = _wgrad(xs, dgt, wg, offsets=plan.offsets, groups=E) if ctx.needs_input_grad[3] else None
+        d_up = _wgrad(xs, dut, wu, offsets=plan.offsets, groups=E) if ctx.needs_input_grad[2] else None
+        return dx, dweights, d_up, d_gate, d_down, None, None
+
+
+def expert_bank(x, plan, weights, w_up, w_gate, w_down, cd, group):
+    return _ExpertBank.apply(x, weights, w_up, w_gate, w_down, plan, group)
+
+
+def dense_swiglu(x, w_up, w_gate, w_down, cd):
+    g = linear(x, w_gate)
+    u = linear(x, w_up)
+    return linear(torch.nn.functional.silu(g) * u, w_down).float()
+
+
+# ------------------------------------------------------------------------- attention
+class _Attention(torch.autograd.Function):
+    """Packed varlen attention between the normed stream ``n [T, d]`` and gated slot updates."""
+
+    @staticmethod
+    def forward(ctx, n, gates, wqkv, wo, tok_of_row, row_of_slot, slot_of_row_flat, pos_of_row, seg_start, col_start,
+                groups, k, heads, head_dim, rope_base):
+        T, d = n.shape
+        inner = heads * head_dim
+        x = gather_rows(n, tok_of_row) if tok_of_row is not None else (n if n.dtype == BF16 else n.to(BF16))
+        rows = x.shape[0]
+        qkv = G.gemm_rows(x, wqkv, offsets=col_start, groups=groups)
+        rope_(qkv, pos_of_row, heads, head_dim, inner, rope_base, 1.0)
+        q, kk, v = qkv[:, :inner], qkv[:, inner : 2 * inner], qkv[:, 2 * inner :]
+        o, lse = flash.flash_fwd(q, kk, v, seg_start, heads, head_dim, 1.0 / head_dim)
+        y = G.gemm_rows(o, wo, offsets=col_start, groups=groups)
+        gf = gates.float().contiguous().view(-1)
+        out = combine_rows(y, row_of_slot.view(-1), gf, 1, T * k, round_products=False)
+        ctx.save_for_backward(x, qkv, o, lse, y, gf, wqkv, wo, tok_of_row, row_of_slot, slot_of_row_flat, pos_of_row,
+                              seg_start, col_start)
+        ctx.meta = (groups, k, heads, head_dim, rope_base, T, n.dtype, gates.dtype)
+        ctx.w_refs = (wqkv, wo)
+        return out.view(T, k, d)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (x, qkv, o, lse, y, gf, wqkv, wo, tok_of_row, row_of_slot, slot_of_row_flat, pos_of_row, seg_start,
+         col_start) = ctx.saved_tensors
+        groups, k, heads, head_dim, rope_base, T, n_dtype, g_dtype = ctx.meta
+        inner = heads * head_dim
+        d = y.shape[1]
+        g2 = dout.contiguous().view(-1, d).float()
+        dy, dg_sorted = combine_bwd(g2, y, slot_of_row_flat, gf, 1, need_dw=ctx.needs_input_grad[1])
+        wq_ref, wo_ref = ctx.w_refs
+        do = G.gemm_rows(dy, wo, offsets=col_start, groups=groups, b_mn=True, n=inner)     # wo [G, K=d, N=inner]
+        d_wo = _wgrad(dy, o, wo_ref, offsets=col_start, groups=groups) if ctx.needs_input_grad[3] else None
+        q, kk, v = qkv[:, :inner], qkv[:, inner : 2 * inner], qkv[:, 2 * inner :]
+        dqkv = flash.flash_bwd(q, kk, v, o, do, lse, seg_start, heads, head_dim, 1.0 / head_dim)
+        rope_(dqkv, pos_of_row, heads, head_dim, inner, rope_base, -1.0)
+        d_wqkv = _wgrad(dqkv, x, wq_ref, offsets=col_start, groups=groups) if ctx.needs_input_grad[2] else None
+        dn = None
+        if ctx.needs_input_grad[0]:
+            dx = G.gemm_rows(dqkv, wqkv, offsets=col_start, groups=groups, b_mn=True, n=d)  # wqkv [G, K=3inner, N=d]
+            dn = (combine_rows(dx, row_of_slot.view(-1), None, k, T) if tok_of_row is not None else dx.float()).to(n_dtype)
+        dgates = None
+        if dg_sorted is not None:
+            dgates = dg_sorted.view(T, k).to(g_dtype)
+        return (dn, dgates, d_wqkv, d_wo) + (None,) * 11
+
+
+def column_attention(n, plan: ColumnPlan, gates, wqkv, wo, heads, head_dim, rope_base, cd):
+    slot_flat = plan.extra.get("slot_flat")
+    if slot_flat is None:   # flat (token*k + slot) index of every packed row
+        slot_flat = (plan.tok_of_row * plan.k + plan.slot_of_row).contiguous()
+        plan.extra["slot_flat"] = slot_flat
+    return _Attention.apply(n, gates, wqkv, wo, plan.tok_of_row, plan.row_of_slot, slot_flat, plan.pos_of_row,
+                            plan.seg_start, plan.col_start, plan.G, plan.k, heads, head_dim, rope_base)
+
+
+_dense_plans: dict = {}
+
+
+def dense_attention(n, B, S, wqkv, wo, heads, head_dim, rope_base, cd, pos=None):
+    T = n.shape[0]
+    key = (B, S, n.device)
+    if key not in _dense_plans:
+        ar = torch.arange(T, dtype=torch.int32, device=n.device)
+        _dense_plans[key] = (ar, torch.arange(S, dtype=torch.int32, device=n.device).repeat(B),
+                             torch.arange(0, T + 1, S, dtype=torch.int32, device=n.device),
+                             torch.tensor([0, T], dtype=torch.int32, device=n.device))
+    ar, p0, seg, col = _dense_plans[key]
+    p = p0 if pos is None else pos.reshape(-1).clamp_min(0).to(torch.int32)
+    ones = torch.ones(T, 1, dtype=torch.float32, device=n.device)
+    out = _Attention.apply(n, ones, wqkv, wo, None, ar.view(T, 1), ar, p, seg, col, 1, 1, heads, head_dim, rope_base)
+    return out.view(T, -1)
+
+
+# ------------------------------------------------------------------------ LM head + CE
+class _HeadCE(torch.autograd.Function):
+    """Chunked head GEMM + cross-entropy; gradients are produced in the forward pass and scaled in backward."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, targets, multiplier: float, chunk_rows: int, ignore_index: int):
+        T, d = hidden.shape
+        V = weight.shape[0]
+        ld = -(-V // 8) * 8
+        bn = 256
+        nt = -(-ld // bn)
+        hb = hidden if hidden.dtype == BF16 else hidden.to(BF16)
+        hb = hb.contiguous()
+        dev = hidden.device
+        need_grad = hidden.requires_grad or weight.requires_grad
+        losses = torch.empty(T, dtype=torch.float32, device=dev)
+        dh = torch.empty(T, d, dtype=BF16, device=dev) if need_grad else None
+        dw = torch.empty(V, d, dtype=torch.float32, device=dev) if need_grad else None
+        chunk = min(chunk_rows, T)
+        logits = torch.empty(chunk, ld, dtype=BF16, device=dev)
+        part = torch.empty(chunk, nt, 2, dtype=torch.float32, device=dev)
+        L = _L()
+        for i, a in enumerate(range(0, T, chunk)):
+            n = min(chunk, T - a)
+            G.gemm_rows(hb[a : a + n], weight, out=logits[:n], epilogue=G.STORE_BF16_STATS, alpha=multiplier, bn=bn,
+                        extra_out=(part,), n=ld, n_valid=V)
+            _ck(L.nb_ce_grad(logits.data_ptr(), ld, V, part.data_ptr(), nt, targets[a : a + n].data_ptr(), ignore_index,
+                             losses[a : a + n].data_ptr(), n, _st()), "ce_grad")
+            if need_grad:
+                dl = logits[:n, :V] if ld == V else torch.as_strided(logits, (n, V), (ld, 1))
+                G.gemm_rows(dl, weight, b_mn=True, out=dh[a : a + n], alpha=multiplier, n=d)   # dH = dL . W
+                G.gemm_reduce(dl, hb[a : a + n], out=dw, epilogue=G.STORE_F32 if i == 0 else G.ACCUM_F32,
+                              alpha=multiplier)
+        ctx.save_for_backward(dh, dw)
+        ctx.h_dtype = hidden.dtype
+        ctx.w_ref = weight
+        count = (targets != ignore_index).sum()
+        ctx.mark_non_differentiable(count)
+        return losses.sum(), count
+
+    @staticmethod
+    def backward(ctx, g_loss, _g_count):
+        dh, dw = ctx.saved_tensors
+        d_hidden = (dh.float() * g_loss).to(ctx.h_dtype) if ctx.needs_input_grad[0] else None
+        d_weight = None
+        if ctx.needs_input_grad[1]:
+            target = getattr(ctx.w_ref, "_nb_grad", None)
+            if target is not None:
+                target.addcmul_(dw, g_loss.to(dw.dtype).expand_as(dw))
+            else:
+                d_weight = (dw * g_loss).to(ctx.w_ref.dtype)
+        return d_hidden, d_weight, None, None, None, None
+
+
+def lm_head_ce(hidden, weight, targets, multiplier, cd, chunk_rows=4096, ignore_index=-100):
+    w = weight if weight.dtype == BF16 else weight.to(BF16)
+    return _HeadCE.apply(hidden, w, targets.contiguous(), float(multiplier), int(chunk_rows), int(ignore_index))
+
+
+# ------------------------------------------------------------------------------ plans
+def build_column_plan(idx, G_, pos=None):
+    return ref.build_column_plan(idx, G_, pos)
+
+
+def build_expert_plan(expert_ids, E):
+    return ref.build_expert_plan(expert_ids, E)

@@ -200,6 +200,35 @@ def router_scores(x: Tensor, w1: Tensor | None, w2: Tensor, cd: torch.dtype) -> 
     return h @ w2.to(cd).t()
 
 
+class RoutingTape:
+    """Record the top-k selections of a forward pass, or replay recorded ones.
+
+    Discrete routing makes two numerically different executions of the same model (kernels
+    vs. oracle, recompute vs. first pass) incomparable as soon as one near-tie flips.
+    Replaying a tape pins the selections so only the continuous math differs.
+    """
+
+    def __init__(self) -> None:
+        self.selections: list[Tensor] = []
+        self.cursor = 0
+        self.mode: str | None = None
+
+
+_TAPE: RoutingTape | None = None
+
+
+def set_routing_tape(tape: RoutingTape | None, mode: str | None = None) -> None:
+    """``mode``: ``"record"``, ``"replay"`` or ``None`` (tape off)."""
+
+    global _TAPE
+    _TAPE = tape if mode else None
+    if tape is not None:
+        tape.mode = mode
+        tape.cursor = 0
+        if mode == "record":
+            tape.selections = []
+
+
 def route_topk(scores: Tensor, bias: Tensor, k: int, gate_mode: str) -> tuple[Tensor, Tensor]:
     """Top-k on ``scores + bias``; gates from the raw scores.
 
@@ -207,7 +236,13 @@ def route_topk(scores: Tensor, bias: Tensor, k: int, gate_mode: str) -> tuple[Te
     entries of the full softmax. Gates are fp32. Returns ``(idx [.., k], gates [.., k])``.
     """
 
-    idx = torch.topk(scores.float() + bias.float(), k=k, dim=-1).indices
+    if _TAPE is not None and _TAPE.mode == "replay":
+        idx = _TAPE.selections[_TAPE.cursor]
+        _TAPE.cursor += 1
+    else:
+        idx = torch.topk(scores.float() + bias.float(), k=k, dim=-1).indices
+        if _TAPE is not None and _TAPE.mode == "record":
+            _TAPE.selections.append(idx)
     if gate_mode == "switch":
         gates = torch.softmax(scores.float(), dim=-1).gather(-1, idx)
     else:
@@ -249,35 +284,31 @@ def segment_attention(q: Tensor, k: Tensor, v: Tensor, seg_start: Tensor, scale:
 
 
 def column_attention(
-    n: Tensor, plan: ColumnPlan, gates: Tensor, wq: Tensor, wk: Tensor, wv: Tensor, wo: Tensor,
+    n: Tensor, plan: ColumnPlan, gates: Tensor, wqkv: Tensor, wo: Tensor,
     heads: int, head_dim: int, rope_base: float, cd: torch.dtype,
 ) -> Tensor:
     """Column-routed causal attention: ``[T, d] -> [T, k, d]`` gated slot updates (fp32).
 
-    For every column ``c``: project its member rows with ``wq/wk/wv[c]`` (``[inner, d]``),
-    RoPE at the rows' original positions, causal attention among the members of each
-    sequence with logits scaled by ``1 / head_dim``, project with ``wo[c]`` (``[d, inner]``),
-    multiply by the token's gate for ``c`` and place the result in the slot that owns ``c``.
-    ``gates`` is ``[T, k]`` in slot order.
+    ``wqkv [G, 3*inner, d]`` stacks each column's ``q_proj, k_proj, v_proj`` rows; ``wo [G, d, inner]``.
+    For every column ``c``: project its member rows, RoPE at the rows' original positions,
+    causal attention among the members of each sequence with logits scaled by
+    ``1 / head_dim``, project with ``wo[c]``, multiply by the token's gate for ``c`` and place
+    the result in the slot that owns ``c``. ``gates`` is ``[T, k]`` in slot order.
     """
 
     T, d = n.shape
+    inner = heads * head_dim
     x = n.to(cd)[plan.tok_of_row.long()]                       # pack: [rows, d]
     cos, sin = rope_tables(plan.pos_of_row, head_dim, rope_base)
-    inner = heads * head_dim
-    q = x.new_empty(plan.rows, inner)
-    kk = x.new_empty(plan.rows, inner)
-    v = x.new_empty(plan.rows, inner)
+    qkv = x.new_empty(plan.rows, 3 * inner)
     cs = plan.col_start.tolist()
     for c in range(plan.G):
         a, b = cs[c], cs[c + 1]
-        q[a:b] = x[a:b] @ wq[c].to(cd).t()
-        kk[a:b] = x[a:b] @ wk[c].to(cd).t()
-        v[a:b] = x[a:b] @ wv[c].to(cd).t()
-    q = apply_rope(q.view(-1, heads, head_dim), cos, sin)
-    kk = apply_rope(kk.view(-1, heads, head_dim), cos, sin)
-    o = segment_attention(q, kk, v.view(-1, heads, head_dim), plan.seg_start, 1.0 / head_dim)
-    o = o.reshape(plan.rows, inner)
+        qkv[a:b] = x[a:b] @ wqkv[c].to(cd).t()
+    q = apply_rope(qkv[:, :inner].reshape(-1, heads, head_dim), cos, sin)
+    kk = apply_rope(qkv[:, inner : 2 * inner].reshape(-1, heads, head_dim), cos, sin)
+    v = qkv[:, 2 * inner :].reshape(-1, heads, head_dim)
+    o = segment_attention(q, kk, v, plan.seg_start, 1.0 / head_dim).reshape(plan.rows, inner)
     y = x.new_empty(plan.rows, d)
     for c in range(plan.G):
         a, b = cs[c], cs[c + 1]
@@ -287,20 +318,26 @@ def column_attention(
 
 
 def dense_attention(
-    n: Tensor, B: int, S: int, wq: Tensor, wk: Tensor, wv: Tensor, wo: Tensor,
+    n: Tensor, B: int, S: int, wqkv: Tensor, wo: Tensor,
     heads: int, head_dim: int, rope_base: float, cd: torch.dtype, pos: Tensor | None = None,
 ) -> Tensor:
-    """Single-column causal MHA over whole sequences: ``[T, d] -> [T, d]`` (baseline arms)."""
+    """Single-column causal MHA over whole sequences: ``[T, d] -> [T, d]`` (baseline arms).
 
+    ``wqkv [1, 3*inner, d]`` (``q_proj, k_proj, v_proj`` rows), ``wo [1, d, inner]``.
+    """
+
+    wqkv, wo = wqkv[0], wo[0]
     T, d = n.shape
+    inner = heads * head_dim
     x = n.to(cd)
     p = torch.arange(S, device=n.device).repeat(B) if pos is None else pos.reshape(-1).clamp_min(0)
     cos, sin = rope_tables(p, head_dim, rope_base)
-    q = apply_rope((x @ wq.to(cd).t()).view(T, heads, head_dim), cos, sin)
-    k = apply_rope((x @ wk.to(cd).t()).view(T, heads, head_dim), cos, sin)
-    v = (x @ wv.to(cd).t()).view(T, heads, head_dim)
+    qkv = x @ wqkv.to(cd).t()
+    q = apply_rope(qkv[:, :inner].reshape(T, heads, head_dim), cos, sin)
+    k = apply_rope(qkv[:, inner : 2 * inner].reshape(T, heads, head_dim), cos, sin)
+    v = qkv[:, 2 * inner :].reshape(T, heads, head_dim)
     seg = torch.arange(0, T + 1, S, device=n.device, dtype=torch.int32)
-    o = segment_attention(q, k, v, seg, 1.0 / head_dim).reshape(T, heads * head_dim)
+    o = segment_attention(q, k, v, seg, 1.0 / head_dim).reshape(T, inner)
     return (o @ wo.to(cd).t()).float()
 
 
