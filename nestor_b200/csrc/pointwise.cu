@@ -321,3 +321,182 @@ int nb_depth_read_norm(const float* const* sources, int n, const float* query, c
 }
 
 }  // extern "C"
+
+// ----------------------------------------------------------------------------------------------
+// Backward of the fused depth read + RMSNorm. One warp per token (grid-stride), three sweeps
+// over the token's sources (they stay L1/L2-resident between sweeps):
+//   1. rebuild h = sum_i a_i s_i from the saved (r_i, u_i); turn dn into dh through the norm
+//   2. t_i = <dh, s_i> for every source
+//   3. ds_i = a_i dh + du_i q - dr_i r_i^3 s_i / d   written to its own [T, d] slab
+// Parameter gradients (query, gains, gamma) are reduced per block and added atomically.
+namespace nb {
+
+struct GradList { float* ptr[kMaxSources]; };
+
+template <int NV>
+__global__ void depth_read_norm_bwd_kernel(SourceList src, GradList dsrc, int n, const float* __restrict__ query,
+                                           const float* __restrict__ gains, const float* __restrict__ gamma,
+                                           const float* __restrict__ stats, const float* __restrict__ rstd_in,
+                                           const __nv_bfloat16* __restrict__ dn, const float* __restrict__ dh_in,
+                                           float* __restrict__ dquery, float* __restrict__ dgains,
+                                           float* __restrict__ dgamma, int T, int d) {
+  __shared__ float s_w[4][kMaxSources], s_t[4][kMaxSources];
+  const int lane = threadIdx.x, wy = threadIdx.y;
+  const int nchunk = d / 4;
+  const float inv_sqrt_d = rsqrtf(float(d));
+  float4 qv[NV], gq[NV], gg[NV];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    int c = lane + 32 * v;
+    qv[v] = c < nchunk ? reinterpret_cast<const float4*>(query)[c] : make_float4(0, 0, 0, 0);
+    gq[v] = make_float4(0, 0, 0, 0); gg[v] = make_float4(0, 0, 0, 0);
+  }
+  float dgain_acc[2] = {0.f, 0.f};   // lane owns sources lane and lane + 32
+  for (int t = blockIdx.x * blockDim.y + wy; t < T; t += gridDim.x * blockDim.y) {
+    // softmax weights from the saved statistics
+    float zmax = -INFINITY;
+    for (int i = lane; i < n; i += 32) {
+      float r = stats[(long(t) * n + i) * 2], u = stats[(long(t) * n + i) * 2 + 1];
+      zmax = fmaxf(zmax, r * u * inv_sqrt_d);
+    }
+#pragma unroll
+    for (int sft = 16; sft > 0; sft >>= 1) zmax = fmaxf(zmax, __shfl_xor_sync(0xffffffffu, zmax, sft));
+    float zsum = 0.f;
+    for (int i = lane; i < n; i += 32) {
+      float r = stats[(long(t) * n + i) * 2], u = stats[(long(t) * n + i) * 2 + 1];
+      float e = __expf(r * u * inv_sqrt_d - zmax);
+      s_w[wy][i] = e; zsum += e;
+    }
+#pragma unroll
+    for (int sft = 16; sft > 0; sft >>= 1) zsum += __shfl_xor_sync(0xffffffffu, zsum, sft);
+    __syncwarp();
+    const float inv_z = 1.f / zsum;
+    // sweep 1: h
+    float4 h[NV];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) h[v] = make_float4(0, 0, 0, 0);
+    for (int i = 0; i < n; ++i) {
+      float a = s_w[wy][i] * inv_z * gains[i] * stats[(long(t) * n + i) * 2];
+      const float4* s = reinterpret_cast<const float4*>(src.ptr[i] + long(t) * d);
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        int c = lane + 32 * v;
+        if (c < nchunk) { float4 x = s[c]; h[v].x += a * x.x; h[v].y += a * x.y; h[v].z += a * x.z; h[v].w += a * x.w; }
+      }
+    }
+    // dn -> dh through y = h * rstd * gamma
+    float4 dh[NV];
+    if (dn) {
+      const float rstd = rstd_in[t];
+      float dot = 0.f;
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        int c = lane + 32 * v;
+        dh[v] = make_float4(0, 0, 0, 0);
+        if (c < nchunk) {
+          uint2 raw = reinterpret_cast<const uint2*>(dn + long(t) * d)[c];
+          __nv_bfloat162 p0 = *reinterpret_cast<__nv_bfloat162*>(&raw.x), p1 = *reinterpret_cast<__nv_bfloat162*>(&raw.y);
+          float4 g = reinterpret_cast<const float4*>(gamma)[c];
+          float4 dy = make_float4(bf(p0.x), bf(p0.y), bf(p1.x), bf(p1.y));
+          gg[v].x += dy.x * h[v].x * rstd; gg[v].y += dy.y * h[v].y * rstd;
+          gg[v].z += dy.z * h[v].z * rstd; gg[v].w += dy.w * h[v].w * rstd;
+          dh[v] = make_float4(dy.x * g.x, dy.y * g.y, dy.z * g.z, dy.w * g.w);
+          dot += dh[v].x * h[v].x + dh[v].y * h[v].y + dh[v].z * h[v].z + dh[v].w * h[v].w;
+        }
+      }
+#pragma unroll
+      for (int sft = 16; sft > 0; sft >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, sft);
+      const float k2 = dot * rstd * rstd * rstd / d;
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        dh[v].x = dh[v].x * rstd - h[v].x * k2; dh[v].y = dh[v].y * rstd - h[v].y * k2;
+        dh[v].z = dh[v].z * rstd - h[v].z * k2; dh[v].w = dh[v].w * rstd - h[v].w * k2;
+      }
+    } else {
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        int c = lane + 32 * v;
+        dh[v] = c < nchunk ? reinterpret_cast<const float4*>(dh_in + long(t) * d)[c] : make_float4(0, 0, 0, 0);
+      }
+    }
+    // sweep 2: t_i = <dh, s_i>
+    for (int i = 0; i < n; ++i) {
+      const float4* s = reinterpret_cast<const float4*>(src.ptr[i] + long(t) * d);
+      float acc = 0.f;
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        int c = lane + 32 * v;
+        if (c < nchunk) { float4 x = s[c]; acc += dh[v].x * x.x + dh[v].y * x.y + dh[v].z * x.z + dh[v].w * x.w; }
+      }
+#pragma unroll
+      for (int sft = 16; sft > 0; sft >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, sft);
+      if (lane == 0) s_t[wy][i] = acc;
+    }
+    __syncwarp();
+    float mix = 0.f;   // sum_j w_j dw_j
+    for (int i = lane; i < n; i += 32)
+      mix += s_w[wy][i] * inv_z * s_t[wy][i] * gains[i] * stats[(long(t) * n + i) * 2];
+#pragma unroll
+    for (int sft = 16; sft > 0; sft >>= 1) mix += __shfl_xor_sync(0xffffffffu, mix, sft);
+    for (int i = lane, slot = 0; i < n; i += 32, ++slot)
+      dgain_acc[slot] += s_t[wy][i] * s_w[wy][i] * inv_z * stats[(long(t) * n + i) * 2];
+    // sweep 3: ds_i
+    for (int i = 0; i < n; ++i) {
+      const float r = stats[(long(t) * n + i) * 2], u = stats[(long(t) * n + i) * 2 + 1];
+      const float w = s_w[wy][i] * inv_z, ti = s_t[wy][i], g = gains[i];
+      const float dz = w * (ti * g * r - mix);
+      const float dr = ti * w * g + dz * u * inv_sqrt_d;
+      const float du = dz * r * inv_sqrt_d;
+      const float a = w * g * r, cs = -dr * r * r * r / d;
+      const float4* s = reinterpret_cast<const float4*>(src.ptr[i] + long(t) * d);
+      float4* o = reinterpret_cast<float4*>(dsrc.ptr[i] + long(t) * d);
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        int c = lane + 32 * v;
+        if (c < nchunk) {
+          float4 x = s[c];
+          o[c] = make_float4(a * dh[v].x + du * qv[v].x + cs * x.x, a * dh[v].y + du * qv[v].y + cs * x.y,
+                             a * dh[v].z + du * qv[v].z + cs * x.z, a * dh[v].w + du * qv[v].w + cs * x.w);
+          gq[v].x += du * x.x; gq[v].y += du * x.y; gq[v].z += du * x.z; gq[v].w += du * x.w;
+        }
+      }
+    }
+    __syncwarp();
+  }
+  // parameter gradients: one atomic per (warp, element)
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    int c = lane + 32 * v;
+    if (c < nchunk) {
+      atomicAdd(dquery + 4 * c, gq[v].x); atomicAdd(dquery + 4 * c + 1, gq[v].y);
+      atomicAdd(dquery + 4 * c + 2, gq[v].z); atomicAdd(dquery + 4 * c + 3, gq[v].w);
+      if (dgamma) {
+        atomicAdd(dgamma + 4 * c, gg[v].x); atomicAdd(dgamma + 4 * c + 1, gg[v].y);
+        atomicAdd(dgamma + 4 * c + 2, gg[v].z); atomicAdd(dgamma + 4 * c + 3, gg[v].w);
+      }
+    }
+  }
+  if (lane < n) atomicAdd(dgains + lane, dgain_acc[0]);
+  if (lane + 32 < n) atomicAdd(dgains + lane + 32, dgain_acc[1]);
+}
+
+}  // namespace nb
+
+extern "C" int nb_depth_read_norm_bwd(const float* const* sources, float* const* dsources, int n, const float* query,
+                                      const float* gains, const float* gamma, const float* stats, const float* rstd,
+                                      const void* dn, const float* dh, float* dquery, float* dgains, float* dgamma, int T,
+                                      int d, cudaStream_t st) {
+  if (n < 1 || n > nb::kMaxSources || d % 4) return -1;
+  nb::SourceList sl; nb::GradList gl;
+  for (int i = 0; i < n; ++i) { sl.ptr[i] = sources[i]; gl.ptr[i] = dsources[i]; }
+  dim3 block(32, 4);
+  int blocks = (T + 3) / 4;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  int nv = (d / 4 + 31) / 32;
+#define NB_DRB(NV) nb::depth_read_norm_bwd_kernel<NV><<<blocks, block, 0, st>>>(sl, gl, n, query, gains, gamma, stats, rstd, \
+      (const __nv_bfloat16*)dn, dh, dquery, dgains, dgamma, T, d)
+  if (nv <= 1) NB_DRB(1); else if (nv <= 2) NB_DRB(2); else if (nv <= 4) NB_DRB(4); else if (nv <= 5) NB_DRB(5);
+  else if (nv <= 8) NB_DRB(8); else if (nv <= 10) NB_DRB(10); else return -2;
+#undef NB_DRB
+  return int(cudaGetLastError());
+}

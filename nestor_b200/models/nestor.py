@@ -247,15 +247,13 @@ class Block(nn.Module):
         layer_aux = []
         for layer in self.layers:
             read = sources if running is None else [*sources, running]
-            h = ops.depth_read(read, layer.kimi_attn_read.query, layer.kimi_attn_read.value_gains,
-                               layer.kimi_attn_read.eps)
-            n = ops.rmsnorm(h, layer.attn_norm.weight, layer.attn_norm.eps, cd)
+            n = ops.depth_read_norm(read, layer.kimi_attn_read.query, layer.kimi_attn_read.value_gains,
+                                    layer.attn_norm.weight, layer.kimi_attn_read.eps, layer.attn_norm.eps, cd)
             attn = layer.attention(n, ctx, cd)                                  # [T, k, d]
             attn_mean = attn.mean(dim=1)
             mid = attn_mean if running is None else running + attn_mean
-            h = ops.depth_read([*sources, mid], layer.kimi_mlp_read.query, layer.kimi_mlp_read.value_gains,
-                               layer.kimi_mlp_read.eps)
-            n = ops.rmsnorm(h, layer.mlp_norm.weight, layer.mlp_norm.eps, cd)
+            n = ops.depth_read_norm([*sources, mid], layer.kimi_mlp_read.query, layer.kimi_mlp_read.value_gains,
+                                    layer.mlp_norm.weight, layer.kimi_mlp_read.eps, layer.mlp_norm.eps, cd)
             exp, aux = layer.experts(n, ctx, cd)
             update = attn + exp
             streams = update if streams is None else streams + update
@@ -316,9 +314,9 @@ class Nestor(nn.Module):
             narrow = [*narrow, x]
             aux.append(a)
         read_sources = wide if self.column_mode else narrow
-        h = ops.depth_read(read_sources, self.final_depth_read.query, self.final_depth_read.value_gains,
-                           self.final_depth_read.eps)
-        return ops.rmsnorm(h, self.final_norm.weight, self.final_norm.eps, cd), {"blocks": aux}
+        h = ops.depth_read_norm(read_sources, self.final_depth_read.query, self.final_depth_read.value_gains,
+                                self.final_norm.weight, self.final_depth_read.eps, self.final_norm.eps, cd)
+        return h, {"blocks": aux}
 
     def routers(self) -> list[tuple[str, RouterParams]]:
         return [(n, m) for n, m in self.named_modules() if isinstance(m, RouterParams)]

@@ -63,6 +63,7 @@ def _dispatch(name: str):
 
 rmsnorm = _dispatch("rmsnorm")
 depth_read = _dispatch("depth_read")
+depth_read_norm = _dispatch("depth_read_norm")
 router_scores = _dispatch("router_scores")
 route_topk = _dispatch("route_topk")
 build_column_plan = _dispatch("build_column_plan")

@@ -39,6 +39,8 @@ def _L():
         L.nb_rope.argtypes = [vp, l, vp, i, i, i, i, f, f, vp]
         L.nb_ce_grad.argtypes = [vp, l, i, vp, i, vp, l, vp, i, vp]
         L.nb_depth_read_norm.argtypes = [vp, i, vp, vp, vp, f, f, vp, vp, vp, vp, i, i, vp]
+        L.nb_depth_read_norm_bwd.argtypes = [vp, vp, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, vp]
+        L.nb_depth_read_norm_bwd.restype = C.c_int
         for fn in (L.nb_gather_rows, L.nb_combine_rows, L.nb_combine_bwd, L.nb_rope, L.nb_ce_grad,
                    L.nb_depth_read_norm):
             fn.restype = C.c_int
@@ -357,6 +359,58 @@ class _HeadCE(torch.autograd.Function):
 def lm_head_ce(hidden, weight, targets, multiplier, cd, chunk_rows=4096, ignore_index=-100):
     w = weight if weight.dtype == BF16 else weight.to(BF16)
     return _HeadCE.apply(hidden, w, targets.contiguous(), float(multiplier), int(chunk_rows), int(ignore_index))
+
+
+# ------------------------------------------------------------------- depth read + norm
+def _ptr_array(tensors):
+    arr = (C.c_void_p * len(tensors))()
+    for i, t in enumerate(tensors):
+        arr[i] = t.data_ptr()
+    return arr
+
+
+class _DepthReadNorm(torch.autograd.Function):
+    """One pass over the sources forward (online softmax over depth), three sweeps backward."""
+
+    @staticmethod
+    def forward(ctx, query, gains, gamma, eps_read, eps_norm, *sources):
+        T, d = sources[0].shape
+        n = len(sources)
+        srcs = [s if (s.dtype == torch.float32 and s.is_contiguous()) else s.float().contiguous() for s in sources]
+        out = torch.empty(T, d, dtype=BF16, device=srcs[0].device)
+        stats = torch.empty(T, n, 2, dtype=torch.float32, device=out.device)
+        rstd = torch.empty(T, dtype=torch.float32, device=out.device)
+        q32, g32, w32 = query.float().contiguous(), gains.float().contiguous(), gamma.float().contiguous()
+        _ck(_L().nb_depth_read_norm(_ptr_array(srcs), n, q32.data_ptr(), g32.data_ptr(), w32.data_ptr(), eps_read,
+                                    eps_norm, out.data_ptr(), None, stats.data_ptr(), rstd.data_ptr(), T, d, _st()),
+            "depth_read_norm")
+        ctx.save_for_backward(q32, g32, w32, stats, rstd, *srcs)
+        ctx.dtypes = (query.dtype, gains.dtype, gamma.dtype, [s.dtype for s in sources])
+        ctx.n_gains = gains.numel()
+        return out
+
+    @staticmethod
+    def backward(ctx, dn):
+        q32, g32, w32, stats, rstd, *srcs = ctx.saved_tensors
+        n = len(srcs)
+        T, d = srcs[0].shape
+        ds = torch.empty(n, T, d, dtype=torch.float32, device=dn.device)
+        dq = torch.zeros(d, dtype=torch.float32, device=dn.device)
+        dg = torch.zeros(ctx.n_gains, dtype=torch.float32, device=dn.device)
+        dw = torch.zeros(d, dtype=torch.float32, device=dn.device)
+        dnb = dn if (dn.dtype == BF16 and dn.is_contiguous()) else dn.to(BF16).contiguous()
+        _ck(_L().nb_depth_read_norm_bwd(_ptr_array(srcs), _ptr_array(list(ds.unbind(0))), n, q32.data_ptr(),
+                                        g32.data_ptr(), w32.data_ptr(), stats.data_ptr(), rstd.data_ptr(), dnb.data_ptr(),
+                                        None, dq.data_ptr(), dg.data_ptr(), dw.data_ptr(), T, d, _st()),
+            "depth_read_norm_bwd")
+        qd, gd, wd, sd = ctx.dtypes
+        return (dq.to(qd), dg.to(gd), dw.to(wd), None, None, *[g.to(t) for g, t in zip(ds.unbind(0), sd)])
+
+
+def depth_read_norm(sources, query, gains, gamma, eps_read, eps_norm, out_dtype):
+    if out_dtype != BF16:
+        return ref.depth_read_norm(sources, query, gains, gamma, eps_read, eps_norm, out_dtype)
+    return _DepthReadNorm.apply(query, gains, gamma, float(eps_read), float(eps_norm), *sources)
 
 
 # ------------------------------------------------------------------------------ plans

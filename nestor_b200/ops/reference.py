@@ -170,6 +170,13 @@ def depth_read(sources: list[Tensor], query: Tensor, gains: Tensor, eps: float =
     return out
 
 
+def depth_read_norm(sources: list[Tensor], query: Tensor, gains: Tensor, gamma: Tensor, eps_read: float,
+                    eps_norm: float, out_dtype: torch.dtype) -> Tensor:
+    """``rmsnorm(depth_read(sources))``: the input of every attention / expert half and of the head."""
+
+    return rmsnorm(depth_read(sources, query, gains, eps_read), gamma, eps_norm, out_dtype)
+
+
 def rope_tables(pos: Tensor, head_dim: int, base: float) -> tuple[Tensor, Tensor]:
     """cos/sin ``[n, head_dim/2]`` in fp32 for integer positions."""
 
