@@ -49,11 +49,12 @@ struct GemmParams {
   long lde;
   float alpha;
   int n_valid;              // stats epilogue: columns >= n_valid are padding (stored as -inf)
+  int splits;               // mode 1: each output tile is reduced by `splits` CTAs (atomic fp32 adds)
   int* status;
   int max_tiles;
 };
 
-struct Tile { int g, m0, n0, row_end, kb, kb2, valid; };
+struct Tile { int g, m0, n0, row_end, kb, kb2, kb0, valid; };
 
 struct Sched {
   // tile t -> (group, m tile, n tile); identical arithmetic in every warp role.
@@ -66,6 +67,7 @@ __device__ __forceinline__ Tile decode_tile(const GemmParams& p, const int* s_of
                                             int n_tiles) {
   Tile r;
   r.valid = 1;
+  r.kb0 = 0;
   if (p.mode == 0) {
     int mt = t / n_tiles, nt = t - mt * n_tiles;
     int lo = 0, hi = p.groups;          // find g with tstart[g] <= mt < tstart[g+1]
@@ -81,14 +83,18 @@ __device__ __forceinline__ Tile decode_tile(const GemmParams& p, const int* s_of
     r.kb2 = (p.K2 + BK - 1) / BK;
   } else {
     int m_tiles = (p.M + BM - 1) / BM;
-    int per_g = m_tiles * n_tiles;
+    int per_g = m_tiles * n_tiles * p.splits;
     r.g = t / per_g;
     int rem = t - r.g * per_g;
+    int sp = rem % p.splits; rem /= p.splits;
     int mt = rem / n_tiles, nt = rem - mt * n_tiles;
     r.m0 = mt * BM;
     r.n0 = nt * p.BN;
     r.row_end = s_off[r.g + 1];
-    r.kb = (s_off[r.g + 1] - s_off[r.g] + BK - 1) / BK;
+    int nkb = (s_off[r.g + 1] - s_off[r.g] + BK - 1) / BK;
+    int per = (nkb + p.splits - 1) / p.splits;
+    r.kb0 = sp * per;
+    r.kb = max(0, min(nkb, r.kb0 + per) - r.kb0);
     r.kb2 = 0;
   }
   return r;
@@ -138,7 +144,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   int total_tiles;
   if (p.mode == 0) total_tiles = s_tstart[p.groups] * n_tiles;
-  else total_tiles = p.groups * ((p.M + BM - 1) / BM) * n_tiles;
+  else total_tiles = p.groups * ((p.M + BM - 1) / BM) * n_tiles * p.splits;
 
   volatile int* abort_flag = &s_abort;
 
@@ -174,7 +180,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               for (int a = 0; a < p.BN / 64; ++a) tma_load_3d(sb + a * 8192, mB, &full_bar[s], tl.n0 + a * 64, kk, bg);
             }
           } else {
-            int row = s_off[tl.g] + kb * BK;     // reduction over the group's rows; operands are MN-major
+            int row = s_off[tl.g] + (tl.kb0 + kb) * BK;     // reduction over the group's rows; operands are MN-major
             tma_load_2d(sa, mA, &full_bar[s], tl.m0, row);
             tma_load_2d(sa + 8192, mA, &full_bar[s], tl.m0 + 64, row);
             for (int a = 0; a < p.BN / 64; ++a) tma_load_2d(sb + a * 8192, mB, &full_bar[s], tl.n0 + a * 64, row);
@@ -207,7 +213,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         uint8_t* sb = sa + a_bytes;
         if (p.mode == 1) {
           // zero k-rows past the end of the group (they belong to the next group)
-          int row0 = s_off[tl.g] + kb * BK;
+          int row0 = s_off[tl.g] + (tl.kb0 + kb) * BK;
           int valid = tl.row_end - row0;
           if (valid < BK) {
             int natoms = 2 + p.BN / 64;
@@ -338,9 +344,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               float* Cp = reinterpret_cast<float*>(p.C) + o;
               const int lim = rem >= 16 ? 16 : 8;
               for (int j = 0; j < lim; j += 4) {
-                float4 old = reinterpret_cast<float4*>(Cp + j)[0];
-                reinterpret_cast<float4*>(Cp + j)[0] = make_float4(old.x + v[j] * p.alpha, old.y + v[j + 1] * p.alpha,
-                                                                    old.z + v[j + 2] * p.alpha, old.w + v[j + 3] * p.alpha);
+                float4 add = make_float4(v[j] * p.alpha, v[j + 1] * p.alpha, v[j + 2] * p.alpha, v[j + 3] * p.alpha);
+                if (p.splits > 1) {
+                  atomicAdd(reinterpret_cast<float4*>(Cp + j), add);
+                } else {
+                  float4 old = reinterpret_cast<float4*>(Cp + j)[0];
+                  reinterpret_cast<float4*>(Cp + j)[0] = make_float4(old.x + add.x, old.y + add.y, old.z + add.z, old.w + add.w);
+                }
               }
             }
           } else if (p.epilogue == kSwiGLUBwd) {
@@ -452,6 +462,7 @@ struct NbGemmArgs {
   void* C2; void* C3; const void* E1; const void* E2; long lde;
   float alpha;
   int n_valid;
+  int splits;
   int* status;
   int max_m_tiles;          // upper bound on m tiles over all groups (mode 0)
   int sms;                  // 0 = all
@@ -502,9 +513,11 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
   p.a_mn = a->a_mn; p.b_mn = a->b_mn; p.b_grouped = a->b_grouped;
   p.C = a->C; p.ldc = a->ldc; p.c_group_stride = a->c_group_stride; p.C2 = a->C2; p.C3 = a->C3;
   p.E1 = a->E1; p.E2 = a->E2; p.lde = a->lde; p.alpha = a->alpha; p.n_valid = a->n_valid > 0 ? a->n_valid : a->N; p.status = a->status;
+  p.splits = (a->mode == 1 && a->epilogue == kAccumF32 && a->splits > 1) ? a->splits : 1;
 
   const int n_tiles = (a->N + a->BN - 1) / a->BN;
-  long tiles = a->mode == 0 ? long(a->max_m_tiles) * n_tiles : long(a->groups) * ((a->M + BM - 1) / BM) * n_tiles;
+  long tiles = a->mode == 0 ? long(a->max_m_tiles) * n_tiles
+                            : long(a->groups) * ((a->M + BM - 1) / BM) * n_tiles * p.splits;
   if (tiles <= 0) return 0;
   const uint32_t stage_bytes = BM * BK * 2 + a->BN * BK * 2;
   int stages = int((200 * 1024) / stage_bytes);

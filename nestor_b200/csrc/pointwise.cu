@@ -500,3 +500,154 @@ extern "C" int nb_depth_read_norm_bwd(const float* const* sources, float* const*
 #undef NB_DRB
   return int(cudaGetLastError());
 }
+
+// ----------------------------------------------------------------------------------------------
+// Residual-stream bookkeeping of a column layer, one pass each (float4 per thread over [T, d]).
+namespace nb {
+
+__device__ __forceinline__ float rbf(float x) { return __bfloat162float(__float2bfloat16(x)); }
+__device__ __forceinline__ float4 f4add(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+__device__ __forceinline__ float4 f4scale(float4 a, float s) { return make_float4(a.x * s, a.y * s, a.z * s, a.w * s); }
+
+// mid[t] = running[t] + mean_j attn[t, j]
+__global__ void mid_source_kernel(const float4* __restrict__ running, const float4* __restrict__ attn,
+                                  float4* __restrict__ mid, long n4, int d4, int k) {
+  long i = blockIdx.x * long(blockDim.x) + threadIdx.x;
+  if (i >= n4) return;
+  long t = i / d4; int c = int(i - t * d4);
+  float4 acc = make_float4(0, 0, 0, 0);
+  for (int j = 0; j < k; ++j) acc = f4add(acc, attn[(t * k + j) * d4 + c]);
+  acc = f4scale(acc, 1.f / k);
+  if (running) acc = f4add(acc, running[i]);
+  mid[i] = acc;
+}
+
+// streams'[t,j] = streams[t,j] + attn[t,j] + rbf(p1[t]*priv[t,j]) + rbf(p0[t]*pub[t]);  running' = running + mean_j(update)
+__global__ void layer_combine_kernel(const float4* __restrict__ attn, const float4* __restrict__ priv,
+                                     const float4* __restrict__ pub, const float* __restrict__ path,
+                                     const float4* __restrict__ streams, const float4* __restrict__ running,
+                                     float4* __restrict__ streams_out, float4* __restrict__ running_out, long n4, int d4,
+                                     int k) {
+  long i = blockIdx.x * long(blockDim.x) + threadIdx.x;
+  if (i >= n4) return;
+  long t = i / d4; int c = int(i - t * d4);
+  float p0 = path ? path[2 * t] : 1.f, p1 = path ? path[2 * t + 1] : 1.f;
+  float4 pb = pub[i];
+  if (path) pb = make_float4(rbf(p0 * pb.x), rbf(p0 * pb.y), rbf(p0 * pb.z), rbf(p0 * pb.w));
+  float4 mean = make_float4(0, 0, 0, 0);
+  for (int j = 0; j < k; ++j) {
+    long o = (t * k + j) * d4 + c;
+    float4 u = f4add(attn[o], pb);
+    if (priv) {
+      float4 pv = priv[o];
+      u = f4add(u, make_float4(rbf(p1 * pv.x), rbf(p1 * pv.y), rbf(p1 * pv.z), rbf(p1 * pv.w)));
+    }
+    mean = f4add(mean, u);
+    streams_out[o] = streams ? f4add(streams[o], u) : u;
+  }
+  mean = f4scale(mean, 1.f / k);
+  running_out[i] = running ? f4add(running[i], mean) : mean;
+}
+
+// Backward: du[t,j] = ds[t,j] + dr[t]/k;  d_attn = du;  d_priv = p1*du;  d_pub = p0*sum_j du;
+// d_path (per token, warp-reduced over d): dp1 = sum_{j,c} du*priv, dp0 = sum_c (sum_j du)*pub. One warp per token.
+__global__ void layer_combine_bwd_kernel(const float* __restrict__ ds, const float* __restrict__ dr,
+                                         const float* __restrict__ priv, const float* __restrict__ pub,
+                                         const float* __restrict__ path, float* __restrict__ d_attn,
+                                         float* __restrict__ d_priv, float* __restrict__ d_pub, float* __restrict__ d_path,
+                                         int T, int d, int k) {
+  int t = blockIdx.x * blockDim.y + threadIdx.y;
+  if (t >= T) return;
+  const int lane = threadIdx.x;
+  float p0 = path ? path[2 * t] : 1.f, p1 = path ? path[2 * t + 1] : 1.f;
+  float a0 = 0.f, a1 = 0.f;
+  const float inv_k = 1.f / k;
+  for (int c = lane * 4; c < d; c += 128) {
+    float4 r = dr ? *reinterpret_cast<const float4*>(dr + long(t) * d + c) : make_float4(0, 0, 0, 0);
+    r = f4scale(r, inv_k);
+    float4 sum = make_float4(0, 0, 0, 0);
+    for (int j = 0; j < k; ++j) {
+      long o = (long(t) * k + j) * d + c;
+      float4 u = ds ? f4add(*reinterpret_cast<const float4*>(ds + o), r) : r;
+      *reinterpret_cast<float4*>(d_attn + o) = u;
+      sum = f4add(sum, u);
+      if (priv) {
+        float4 pv = *reinterpret_cast<const float4*>(priv + o);
+        a1 += u.x * pv.x + u.y * pv.y + u.z * pv.z + u.w * pv.w;
+        *reinterpret_cast<float4*>(d_priv + o) = f4scale(u, p1);
+      }
+    }
+    float4 pb = *reinterpret_cast<const float4*>(pub + long(t) * d + c);
+    a0 += sum.x * pb.x + sum.y * pb.y + sum.z * pb.z + sum.w * pb.w;
+    *reinterpret_cast<float4*>(d_pub + long(t) * d + c) = f4scale(sum, p0);
+  }
+  if (d_path) {
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) { a0 += __shfl_xor_sync(0xffffffffu, a0, s); a1 += __shfl_xor_sync(0xffffffffu, a1, s); }
+    if (lane == 0) { d_path[2 * t] = a0; d_path[2 * t + 1] = a1; }
+  }
+}
+
+// Block exit: agg[t] = mean_j s[t,j]; dev[j][t] = s[t,j] - agg[t]   (dev is source-major so every export is contiguous)
+__global__ void block_exit_kernel(const float4* __restrict__ s, float4* __restrict__ dev, float4* __restrict__ agg,
+                                  long n4, int d4, int k) {
+  long i = blockIdx.x * long(blockDim.x) + threadIdx.x;
+  if (i >= n4) return;
+  long t = i / d4; int c = int(i - t * d4);
+  float4 m = make_float4(0, 0, 0, 0);
+  for (int j = 0; j < k; ++j) m = f4add(m, s[(t * k + j) * d4 + c]);
+  m = f4scale(m, 1.f / k);
+  agg[i] = m;
+  for (int j = 0; j < k; ++j) {
+    float4 v = s[(t * k + j) * d4 + c];
+    dev[long(j) * n4 + i] = make_float4(v.x - m.x, v.y - m.y, v.z - m.z, v.w - m.w);
+  }
+}
+// d_s[t,j] = d_dev[j][t] - mean_j' d_dev[j'][t] + d_agg[t]/k
+__global__ void block_exit_bwd_kernel(const float4* __restrict__ d_dev, const float4* __restrict__ d_agg,
+                                      float4* __restrict__ d_s, long n4, int d4, int k) {
+  long i = blockIdx.x * long(blockDim.x) + threadIdx.x;
+  if (i >= n4) return;
+  long t = i / d4; int c = int(i - t * d4);
+  float4 m = make_float4(0, 0, 0, 0);
+  if (d_dev) for (int j = 0; j < k; ++j) m = f4add(m, d_dev[long(j) * n4 + i]);
+  float4 corr = d_agg ? f4add(f4scale(m, -1.f / k), f4scale(d_agg[i], 1.f / k)) : f4scale(m, -1.f / k);
+  for (int j = 0; j < k; ++j) {
+    float4 v = d_dev ? d_dev[long(j) * n4 + i] : make_float4(0, 0, 0, 0);
+    d_s[(t * k + j) * d4 + c] = f4add(v, corr);
+  }
+}
+
+}  // namespace nb
+
+extern "C" {
+int nb_mid_source(const float* running, const float* attn, float* mid, int T, int d, int k, cudaStream_t st) {
+  long n4 = long(T) * d / 4;
+  nb::mid_source_kernel<<<unsigned((n4 + 255) / 256), 256, 0, st>>>((const float4*)running, (const float4*)attn, (float4*)mid, n4, d / 4, k);
+  return int(cudaGetLastError());
+}
+int nb_layer_combine(const float* attn, const float* priv, const float* pub, const float* path, const float* streams,
+                     const float* running, float* streams_out, float* running_out, int T, int d, int k, cudaStream_t st) {
+  long n4 = long(T) * d / 4;
+  nb::layer_combine_kernel<<<unsigned((n4 + 255) / 256), 256, 0, st>>>(
+      (const float4*)attn, (const float4*)priv, (const float4*)pub, path, (const float4*)streams, (const float4*)running,
+      (float4*)streams_out, (float4*)running_out, n4, d / 4, k);
+  return int(cudaGetLastError());
+}
+int nb_layer_combine_bwd(const float* ds, const float* dr, const float* priv, const float* pub, const float* path,
+                         float* d_attn, float* d_priv, float* d_pub, float* d_path, int T, int d, int k, cudaStream_t st) {
+  dim3 block(32, 8), grid((T + 7) / 8);
+  nb::layer_combine_bwd_kernel<<<grid, block, 0, st>>>(ds, dr, priv, pub, path, d_attn, d_priv, d_pub, d_path, T, d, k);
+  return int(cudaGetLastError());
+}
+int nb_block_exit(const float* s, float* dev, float* agg, int T, int d, int k, cudaStream_t st) {
+  long n4 = long(T) * d / 4;
+  nb::block_exit_kernel<<<unsigned((n4 + 255) / 256), 256, 0, st>>>((const float4*)s, (float4*)dev, (float4*)agg, n4, d / 4, k);
+  return int(cudaGetLastError());
+}
+int nb_block_exit_bwd(const float* d_dev, const float* d_agg, float* d_s, int T, int d, int k, cudaStream_t st) {
+  long n4 = long(T) * d / 4;
+  nb::block_exit_bwd_kernel<<<unsigned((n4 + 255) / 256), 256, 0, st>>>((const float4*)d_dev, (const float4*)d_agg, (float4*)d_s, n4, d / 4, k);
+  return int(cudaGetLastError());
+}
+}

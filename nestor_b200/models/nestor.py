@@ -91,21 +91,29 @@ class ExpertPool(nn.Module):
     def private_bias(self) -> Tensor:
         return torch.stack([r.choice_bias for r in self.private_routers], dim=0)
 
-    def forward(self, n: Tensor, idx: Tensor, gates: Tensor, cd: torch.dtype) -> tuple[Tensor, Tensor, dict]:
-        """``n [T, d]`` -> ``(public [T, d], private [T, k, d], aux)``, both already path-weighted."""
+    def forward(self, n: Tensor, idx: Tensor, gates: Tensor, cd: torch.dtype) -> tuple[Tensor, Tensor, Tensor, dict]:
+        """``n [T, d]`` -> ``(public [T, d], private [T, k, d], path [T, 2], aux)``; the path weights are
+        applied when the layer's updates are combined into the streams."""
 
         s = self.spec
         T = n.shape[0]
-        pub_scores = ops.router_scores(n, None, W(self, self.public_router.score_mlp.layers[0].weight), cd)
+        # one GEMM for the public router, the G private routers and the path gate (adjacent parameters)
+        heads = [self.public_router.score_mlp.layers[0].weight,
+                 *[r.score_mlp.layers[0].weight for r in self.private_routers], self.path_gate.weight]
+        arena = self.__dict__.get("_nestor_arena")
+        wcat = arena.concat_view(heads) if arena is not None and heads[0].requires_grad else torch.cat(heads, dim=0)
+        scores = ops.router_scores(n, None, wcat, cd)
+        pub_scores = scores[:, : s.P]
+        priv_scores = scores[:, s.P : s.P + s.G * s.Q].reshape(T, s.G, s.Q)
+        path_logits = scores[:, s.P + s.G * s.Q :]
         pub_idx, pub_gate = ops.route_topk(pub_scores, self.public_router.choice_bias, s.k_p, "renorm")
-        priv_scores = ops.router_scores(n, None, self.private_router_weight(), cd).view(T, s.G, s.Q)
         col = idx.long()                                                     # [T, k] selected columns
         sel_scores = priv_scores.gather(1, col.unsqueeze(-1).expand(-1, -1, s.Q))       # [T, k, Q]
         sel_bias = self.private_bias()[col]                                  # [T, k, Q]
         priv_idx, priv_gate = ops.route_topk(sel_scores, sel_bias, s.k_q, s.private_gate)  # [T, k, k_q]
         priv_ids = (col.unsqueeze(-1) * s.Q + priv_idx).reshape(T, s.k * s.k_q)
         priv_w = (priv_gate.to(cd) * gates.to(cd).unsqueeze(-1)).reshape(T, s.k * s.k_q)
-        path = torch.softmax(ops.router_scores(n, None, W(self, self.path_gate.weight), cd).float(), dim=-1).to(cd)
+        path = torch.softmax(path_logits.float(), dim=-1)
 
         pub_plan = ops.build_expert_plan(pub_idx, s.P)
         public = ops.expert_bank(n, pub_plan, pub_gate.to(cd), W(self, self.stacked_public.w_up),
@@ -113,10 +121,8 @@ class ExpertPool(nn.Module):
         priv_plan = ops.build_expert_plan(priv_ids, s.G * s.Q)
         private = ops.expert_bank(n, priv_plan, priv_w, W(self, self.stacked_private.w_up),
                                   W(self, self.stacked_private.w_gate), W(self, self.stacked_private.w_down), cd, group=s.k_q)
-        public = (path[:, 0:1].float() * public[:, 0]).to(cd).float()
-        private = (path[:, 1:2].float().unsqueeze(-1) * private).to(cd).float()
         aux = {"public_idx": pub_idx, "private_idx": priv_idx, "columns": idx}
-        return public, private, aux
+        return public[:, 0], private, path, aux
 
 
 class Layer(nn.Module):
@@ -173,17 +179,17 @@ class Layer(nn.Module):
         return ops.column_attention(n, ctx.plan, ctx.gates, self.qkv_weight(), self.out_weight(),
                                     s.heads, s.head_dim, s.rope_base, cd)
 
-    def experts(self, n: Tensor, ctx: "BlockContext", cd: torch.dtype) -> tuple[Tensor, dict]:
-        """Returns the expert update broadcastable against ``[T, k, d]`` and routing aux."""
+    def experts(self, n: Tensor, ctx: "BlockContext", cd: torch.dtype) -> tuple[Tensor | None, Tensor, Tensor | None, dict]:
+        """Expert half: ``(private [T, k, d] | None, shared [T, d], path [T, 2] | None, routing aux)``."""
 
         s = self.spec
         if self.expert_pool is not None:
-            public, private, aux = self.expert_pool(n, ctx.idx, ctx.gates, cd)
-            return private + public.unsqueeze(1), aux
+            public, private, path, aux = self.expert_pool(n, ctx.idx, ctx.gates, cd)
+            return private, public, path, aux
         if self.shared_experts is not None:
             e = self.shared_experts[0]
             out = ops.dense_swiglu(n, W(self, e.layers[0].weight), W(self, e.gate.weight), W(self, e.layers[1].weight), cd)
-            return out.unsqueeze(1), {}
+            return None, out, None, {}
         scores = ops.router_scores(n, None, W(self, self.expert_router.score_mlp.layers[0].weight), cd)
         idx, gate = ops.route_topk(scores, self.expert_router.choice_bias, s.bank_top_k, "renorm")
         plan = ops.build_expert_plan(idx, s.bank_experts)
@@ -191,7 +197,7 @@ class Layer(nn.Module):
         ones = torch.ones_like(gate, dtype=cd)
         rows = ops.expert_bank(n, plan, ones, W(self, bank.w_up), W(self, bank.w_gate), W(self, bank.w_down), cd, group=1)
         out = (rows * gate.to(cd).float().unsqueeze(-1)).sum(dim=1).to(cd).float()
-        return out.unsqueeze(1), {"expert_idx": idx}
+        return None, out, None, {"expert_idx": idx}
 
 
 class BlockContext:
@@ -250,20 +256,17 @@ class Block(nn.Module):
             n = ops.depth_read_norm(read, layer.kimi_attn_read.query, layer.kimi_attn_read.value_gains,
                                     layer.attn_norm.weight, layer.kimi_attn_read.eps, layer.attn_norm.eps, cd)
             attn = layer.attention(n, ctx, cd)                                  # [T, k, d]
-            attn_mean = attn.mean(dim=1)
-            mid = attn_mean if running is None else running + attn_mean
+            mid = ops.mid_source(running, attn)
             n = ops.depth_read_norm([*sources, mid], layer.kimi_mlp_read.query, layer.kimi_mlp_read.value_gains,
                                     layer.mlp_norm.weight, layer.kimi_mlp_read.eps, layer.mlp_norm.eps, cd)
-            exp, aux = layer.experts(n, ctx, cd)
-            update = attn + exp
-            streams = update if streams is None else streams + update
-            step = update.mean(dim=1)
-            running = step if running is None else running + step
+            priv, shared, path, aux = layer.experts(n, ctx, cd)
+            streams, running = ops.layer_combine(attn, priv, shared, path, streams, running, cd)
             layer_aux.append(aux)
-        agg = streams.mean(dim=1)
         if column_mode and s.k > 1:
-            exports = [*(streams - agg.unsqueeze(1)).unbind(dim=1), agg]
+            dev, agg = ops.block_exit(streams)
+            exports = [*dev.unbind(dim=0), agg]
         else:
+            agg = streams.mean(dim=1) if s.k > 1 else streams[:, 0]
             exports = [agg]
         return exports, agg, {"group_idx": idx, "layers": layer_aux}
 

@@ -48,7 +48,7 @@ def _dispatch(name: str):
 
     def op(*args, **kwargs):
         first = next(a for a in list(args) + list(kwargs.values()) if isinstance(a, torch.Tensor)
-                     or (isinstance(a, (list, tuple)) and a and isinstance(a[0], torch.Tensor)))
+                     or (isinstance(a, (list, tuple)) and len(a) > 0 and isinstance(a[0], torch.Tensor)))
         probe = first[0] if isinstance(first, (list, tuple)) else first
         if use_kernels(probe):
             fn = getattr(cuda_ops(), name, None)
@@ -64,6 +64,9 @@ def _dispatch(name: str):
 rmsnorm = _dispatch("rmsnorm")
 depth_read = _dispatch("depth_read")
 depth_read_norm = _dispatch("depth_read_norm")
+mid_source = _dispatch("mid_source")
+layer_combine = _dispatch("layer_combine")
+block_exit = _dispatch("block_exit")
 router_scores = _dispatch("router_scores")
 route_topk = _dispatch("route_topk")
 build_column_plan = _dispatch("build_column_plan")

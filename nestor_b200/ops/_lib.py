@@ -30,7 +30,8 @@ class GemmArgs(C.Structure):
         ("A", Operand), ("B", Operand), ("A2", Operand), ("B2", Operand),
         ("C", C.c_void_p), ("ldc", C.c_long), ("c_group_stride", C.c_long),
         ("C2", C.c_void_p), ("C3", C.c_void_p), ("E1", C.c_void_p), ("E2", C.c_void_p), ("lde", C.c_long),
-        ("alpha", C.c_float), ("n_valid", C.c_int), ("status", C.c_void_p), ("max_m_tiles", C.c_int),
+        ("alpha", C.c_float), ("n_valid", C.c_int), ("splits", C.c_int), ("status", C.c_void_p),
+        ("max_m_tiles", C.c_int),
         ("sms", C.c_int),
     ]
 

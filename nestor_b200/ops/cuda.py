@@ -41,6 +41,13 @@ def _L():
         L.nb_depth_read_norm.argtypes = [vp, i, vp, vp, vp, f, f, vp, vp, vp, vp, i, i, vp]
         L.nb_depth_read_norm_bwd.argtypes = [vp, vp, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, vp]
         L.nb_depth_read_norm_bwd.restype = C.c_int
+        L.nb_mid_source.argtypes = [vp, vp, vp, i, i, i, vp]
+        L.nb_layer_combine.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, vp]
+        L.nb_layer_combine_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, vp]
+        L.nb_block_exit.argtypes = [vp, vp, vp, i, i, i, vp]
+        L.nb_block_exit_bwd.argtypes = [vp, vp, vp, i, i, i, vp]
+        for fn in (L.nb_mid_source, L.nb_layer_combine, L.nb_layer_combine_bwd, L.nb_block_exit, L.nb_block_exit_bwd):
+            fn.restype = C.c_int
         for fn in (L.nb_gather_rows, L.nb_combine_rows, L.nb_combine_bwd, L.nb_rope, L.nb_ce_grad,
                    L.nb_depth_read_norm):
             fn.restype = C.c_int
@@ -411,6 +418,97 @@ def depth_read_norm(sources, query, gains, gamma, eps_read, eps_norm, out_dtype)
     if out_dtype != BF16:
         return ref.depth_read_norm(sources, query, gains, gamma, eps_read, eps_norm, out_dtype)
     return _DepthReadNorm.apply(query, gains, gamma, float(eps_read), float(eps_norm), *sources)
+
+
+# --------------------------------------------------------------------- stream updates
+def _f32c(t):
+    return t if (t.dtype == torch.float32 and t.is_contiguous()) else t.float().contiguous()
+
+
+class _MidSource(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, running, attn):
+        T, k, d = attn.shape
+        a = _f32c(attn)
+        r = None if running is None else _f32c(running)
+        out = torch.empty(T, d, dtype=torch.float32, device=attn.device)
+        _ck(_L().nb_mid_source(_ptr(r), a.data_ptr(), out.data_ptr(), T, d, k, _st()), "mid_source")
+        ctx.k = k
+        ctx.has_running = running is not None
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        k = ctx.k
+        d_run = g if ctx.has_running and ctx.needs_input_grad[0] else None
+        return d_run, (g * (1.0 / k)).unsqueeze(1).expand(-1, k, -1)
+
+
+def mid_source(running, attn):
+    return _MidSource.apply(running, attn)
+
+
+class _LayerCombine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, attn, priv, pub, path, streams, running):
+        T, k, d = attn.shape
+        a, pb = _f32c(attn), _f32c(pub)
+        pv = None if priv is None else _f32c(priv)
+        ph = None if path is None else _f32c(path)
+        st = None if streams is None else _f32c(streams)
+        rn = None if running is None else _f32c(running)
+        s_out = torch.empty(T, k, d, dtype=torch.float32, device=attn.device)
+        r_out = torch.empty(T, d, dtype=torch.float32, device=attn.device)
+        _ck(_L().nb_layer_combine(a.data_ptr(), _ptr(pv), pb.data_ptr(), _ptr(ph), _ptr(st), _ptr(rn), s_out.data_ptr(),
+                                  r_out.data_ptr(), T, d, k, _st()), "layer_combine")
+        ctx.save_for_backward(pv, pb, ph)
+        ctx.shape = (T, k, d)
+        ctx.has_state = (streams is not None, running is not None)
+        return s_out, r_out
+
+    @staticmethod
+    def backward(ctx, ds, dr):
+        pv, pb, ph = ctx.saved_tensors
+        T, k, d = ctx.shape
+        dev = pb.device
+        ds_c = None if ds is None else _f32c(ds)
+        dr_c = None if dr is None else _f32c(dr)
+        d_attn = torch.empty(T, k, d, dtype=torch.float32, device=dev)
+        d_priv = torch.empty(T, k, d, dtype=torch.float32, device=dev) if pv is not None else None
+        d_pub = torch.empty(T, d, dtype=torch.float32, device=dev)
+        d_path = torch.empty(T, 2, dtype=torch.float32, device=dev) if ph is not None else None
+        _ck(_L().nb_layer_combine_bwd(_ptr(ds_c), _ptr(dr_c), _ptr(pv), pb.data_ptr(), _ptr(ph), d_attn.data_ptr(),
+                                      _ptr(d_priv), d_pub.data_ptr(), _ptr(d_path), T, d, k, _st()), "layer_combine_bwd")
+        return (d_attn, d_priv, d_pub, d_path, ds if ctx.has_state[0] else None, dr if ctx.has_state[1] else None)
+
+
+def layer_combine(attn, priv, pub, path, streams, running, cd):
+    return _LayerCombine.apply(attn, priv, pub, path, streams, running)
+
+
+class _BlockExit(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, streams):
+        T, k, d = streams.shape
+        s = _f32c(streams)
+        dev_ = torch.empty(k, T, d, dtype=torch.float32, device=s.device)
+        agg = torch.empty(T, d, dtype=torch.float32, device=s.device)
+        _ck(_L().nb_block_exit(s.data_ptr(), dev_.data_ptr(), agg.data_ptr(), T, d, k, _st()), "block_exit")
+        ctx.shape = (T, k, d)
+        return dev_, agg
+
+    @staticmethod
+    def backward(ctx, d_dev, d_agg):
+        T, k, d = ctx.shape
+        dd = None if d_dev is None else _f32c(d_dev)
+        da = None if d_agg is None else _f32c(d_agg)
+        out = torch.empty(T, k, d, dtype=torch.float32, device=(dd if dd is not None else da).device)
+        _ck(_L().nb_block_exit_bwd(_ptr(dd), _ptr(da), out.data_ptr(), T, d, k, _st()), "block_exit_bwd")
+        return out
+
+
+def block_exit(streams):
+    return _BlockExit.apply(streams)
 
 
 # ------------------------------------------------------------------------------ plans

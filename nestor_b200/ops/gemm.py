@@ -127,6 +127,12 @@ def gemm_reduce(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: 
     assert o3.stride(-1) == 1
     a.C, a.ldc, a.c_group_stride = o3.data_ptr(), o3.stride(1), o3.stride(0)
     a.alpha = alpha
+    # few output tiles and a long reduction: let several CTAs share a tile (fp32 atomic adds)
+    tiles = groups * -(-M // 128) * -(-N // bn)
+    kblocks = max(1, rows // (64 * groups))
+    a.splits = 1
+    if epilogue == ACCUM_F32 and tiles < 120:
+        a.splits = max(1, min(148 // tiles, kblocks // 4))
     a.status = _lib.status_word(A.device).data_ptr()
     a.max_m_tiles = 0
     a.sms = sms

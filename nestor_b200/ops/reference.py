@@ -69,10 +69,11 @@ def build_column_plan(idx: Tensor, G: int, pos: Tensor | None = None) -> ColumnP
     B, S, k = idx.shape
     dev = idx.device
     idx = idx.to(torch.int64)
-    member = torch.zeros(B, S, G, dtype=torch.int64, device=dev)
+    member = torch.zeros(B, S, G, dtype=torch.int32, device=dev)
     member.scatter_(2, idx, 1)
-    rank = member.cumsum(dim=1) - 1                                   # [B,S,G] rank inside (b, c)
-    seg_len = member.sum(dim=1).transpose(0, 1).reshape(-1)           # [G*B], column-major
+    # scan along the sequence with the scanned axis innermost (fast path of the scan kernels)
+    rank = (member.transpose(1, 2).contiguous().cumsum(dim=-1, dtype=torch.int64) - 1).transpose(1, 2)  # [B,S,G]
+    seg_len = member.sum(dim=1, dtype=torch.int64).transpose(0, 1).reshape(-1)   # [G*B], column-major
     seg_start = torch.zeros(G * B + 1, dtype=torch.int64, device=dev)
     seg_start[1:] = seg_len.cumsum(0)
     start_bc = seg_start[:-1].view(G, B).transpose(0, 1)              # [B,G]
@@ -175,6 +176,42 @@ def depth_read_norm(sources: list[Tensor], query: Tensor, gains: Tensor, gamma: 
     """``rmsnorm(depth_read(sources))``: the input of every attention / expert half and of the head."""
 
     return rmsnorm(depth_read(sources, query, gains, eps_read), gamma, eps_norm, out_dtype)
+
+
+def mid_source(running: Tensor | None, attn: Tensor) -> Tensor:
+    """Source of the expert-half read: ``running + mean_j attn[:, j]`` (``[T, d]`` fp32)."""
+
+    m = attn.float().mean(dim=1)
+    return m if running is None else running + m
+
+
+def layer_combine(attn: Tensor, priv: Tensor | None, pub: Tensor, path: Tensor | None, streams: Tensor | None,
+                  running: Tensor | None, cd: torch.dtype) -> tuple[Tensor, Tensor]:
+    """Add one layer's updates to the column streams and their running mean.
+
+    ``update[t, j] = attn[t, j] + round_cd(path[t, 1] * priv[t, j]) + round_cd(path[t, 0] * pub[t])`` (the path
+    weights and ``priv`` are absent for bank / dense layers); ``streams += update``;
+    ``running += mean_j update``. Everything is fp32 except the two rounded products.
+    """
+
+    if path is not None:
+        pubv = (path[:, 0:1].float() * pub.float()).to(cd).float()
+        privv = None if priv is None else (path[:, 1:2].float().unsqueeze(-1) * priv.float()).to(cd).float()
+    else:
+        pubv, privv = pub.float(), None if priv is None else priv.float()
+    update = attn.float() + pubv.unsqueeze(1)
+    if privv is not None:
+        update = update + privv
+    streams = update if streams is None else streams + update
+    step = update.mean(dim=1)
+    return streams, (step if running is None else running + step)
+
+
+def block_exit(streams: Tensor) -> tuple[Tensor, Tensor]:
+    """``(deviations [k, T, d], aggregate [T, d])`` of a block's column streams ``[T, k, d]``."""
+
+    agg = streams.mean(dim=1)
+    return (streams - agg.unsqueeze(1)).permute(1, 0, 2), agg
 
 
 def rope_tables(pos: Tensor, head_dim: int, base: float) -> tuple[Tensor, Tensor]:

@@ -174,6 +174,17 @@ class ParamArena:
         out = self._wire(torch.as_strided(self.compute, *geom), torch.as_strided(self.grad, *geom), flat)
         return out
 
+    def concat_view(self, params: Iterable[Tensor]) -> Tensor:
+        """``[sum(rows), cols]`` operand over row-adjacent 2-D parameters (one GEMM for several heads)."""
+
+        params = list(params)
+        v = self.fused_view([params])
+        out = v[0]
+        g = getattr(v, "_nb_grad", None)
+        if g is not None:
+            out._nb_grad = g[0]
+        return out
+
     def buckets(self, bucket_elems: int) -> list[tuple[int, int]]:
         """``[(offset, numel)]`` covering the arena in order, each at most ``bucket_elems`` long."""
 

@@ -1,0 +1,114 @@
+"""Registry, geometry, parameter counts and checkpoint key schema of the registered cells.
+
+Mirrors the pins of the reference's ``tests/test_pretrain_arms.py`` (parameter counts ``:69-73``,
+private top-k ``:74-79``, FLOP ratios ``:80``) and checks the ``state_dict`` key / shape / tag schema
+against fixtures captured from the reference implementation on the meta device.
+"""
+
+import json
+from pathlib import Path
+
+import pytest
+import torch
+
+from nestor_b200.configs import NestorConfig
+from nestor_b200.continual.flops import flop_ratio
+from nestor_b200.experiments import discover_experiments, get_experiment, list_experiments, register_experiment
+from nestor_b200.experiments import pretrain as P
+from nestor_b200.models import Model
+from nestor_b200.models.tags import get_tag
+
+FIX = Path(__file__).parent / "fixtures"
+PARAMS = {
+    "nestor": {"100m": 377_505_845, "200m": 761_788_781, "500m": 2_442_638_813, "1b": 5_532_512_845},
+    "moe": {"100m": 373_387_389, "200m": 786_607_269, "500m": 2_405_976_309, "1b": 5_494_150_469},
+    "dense": {"100m": 141_011_709, "200m": 233_903_269, "500m": 547_500_789, "1b": 1_097_053_509},
+}
+
+
+def _build(name):
+    discover_experiments()
+    with torch.device("meta"):
+        return Model.from_config(get_experiment(name)().jobs[0].model)
+
+
+def test_twelve_cells_registered():
+    discover_experiments()
+    names = list_experiments()
+    for fam in ("dense", "moe", "nestor"):
+        for scale in ("100m", "200m", "500m", "1b"):
+            assert f"{fam}_{scale}" in names
+    with pytest.raises(KeyError):
+        get_experiment("nope")
+    with pytest.raises(ValueError):
+        register_experiment(get_experiment("nestor_200m"))
+
+
+@pytest.mark.parametrize("family", ["nestor", "moe", "dense"])
+@pytest.mark.parametrize("scale", ["100m", "200m", "500m", "1b"])
+def test_parameter_counts(family, scale):
+    model = _build(f"{family}_{scale}")
+    assert sum(p.numel() for p in model.parameters()) == PARAMS[family][scale]
+
+
+def test_private_top_k_and_widths():
+    assert P.nestor_private_top_k(P.SCALES["200m"]) == (2, 2, 1, 1, 1, 1, 1)
+    assert P.nestor_private_top_k(P.SCALES["1b"]) == (2,) * 7
+    specs = P.nestor_backbone(P.SCALES["200m"]).resolve()
+    assert [s.h_priv for s in specs] == [216, 160, 256, 216, 216, 184, 160]
+    assert all(s.h_pub == 640 for s in specs)
+    assert P.moe_expert_width(P.SCALES["200m"]) == 856
+    assert P.nestor_backbone(P.SCALES["200m"]).max_depth_sources() == 47
+    assert P.baseline_backbone(P.SCALES["200m"], experts=1).max_depth_sources() == 5
+
+
+def test_flop_ratios():
+    got = [round(flop_ratio(f"nestor_{s}", f"dense_{s}", seq_len=4096), 3) for s in ("100m", "200m", "500m", "1b")]
+    assert got == [0.986, 0.981, 0.979, 0.989]
+    assert abs(flop_ratio("nestor_200m", "dense_200m", seq_len=65536) - 0.8) < 0.02
+
+
+@pytest.mark.parametrize("family", ["nestor", "moe", "dense"])
+def test_state_dict_schema_matches_reference(family):
+    schema = json.loads((FIX / f"state_schema_{family}_200m.json").read_text())
+    model = _build(f"{family}_200m")
+    params = dict(model.named_parameters())
+    state = model.state_dict()
+    assert [k for k, *_ in schema] == list(state)
+    for key, shape, is_buffer, requires_grad, tag in schema:
+        assert list(state[key].shape) == shape, key
+        if is_buffer:
+            assert key not in params
+            continue
+        p = params[key]
+        assert bool(requires_grad) == p.requires_grad, key
+        if not p.requires_grad:
+            continue
+        t = get_tag(p)
+        assert t is not None, key
+        assert t.optimizer == tag[0], key
+        assert t.lr_mul == pytest.approx(tag[1], rel=1e-9), key
+        assert t.muon_scale == pytest.approx(tag[2], rel=1e-9), key
+        assert t.weight_decay == tag[3], key
+
+
+def test_tokens_per_step_is_pinned(monkeypatch):
+    monkeypatch.setenv("DCLM_GLOBAL_BATCH", "5")
+    with pytest.raises(AssertionError):
+        P.build_experiment("nestor", "200m")
+    monkeypatch.setenv("DCLM_GLOBAL_BATCH", "32")
+    monkeypatch.setenv("DCLM_GRAD_ACCUM", "4")
+    job = P.build_experiment("nestor", "200m").jobs[0]
+    assert job.train_dataloader.batch_size == 32 and job.grad_accum_steps == 4
+
+
+def test_config_validation():
+    base = dict(input_dim=64, num_blocks=1, feature_dims=[64], causal=True, block_mlp_activations="swiglu",
+                block_mlp_hidden_dims=[256], block_residual_mode="attn_res_kimi")
+    NestorConfig(**base).resolve()
+    with pytest.raises(ValueError):
+        NestorConfig(**{**base, "causal": False}).resolve()
+    with pytest.raises(ValueError):
+        NestorConfig(**{**base, "block_residual_mode": "projection"}).resolve()
+    with pytest.raises(ValueError):
+        NestorConfig(**{**base, "num_groups": 2, "num_groups_per_token": 3}).resolve()
