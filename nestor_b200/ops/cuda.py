@@ -339,7 +339,8 @@ class _HeadCE(torch.autograd.Function):
                              losses[a : a + n].data_ptr(), n, _st()), "ce_grad")
             if need_grad:
                 dl = logits[:n, :V] if ld == V else torch.as_strided(logits, (n, V), (ld, 1))
-                G.gemm_rows(dl, weight, b_mn=True, out=dh[a : a + n], alpha=multiplier, n=d)   # dH = dL . W
+                G.gemm_rows(dl, weight, b_mn=True, out=dh[a : a + n], alpha=multiplier, n=d,
+                            bn=_one_wave_bn(n, d))                                        # dH = dL . W
                 G.gemm_reduce(dl, hb[a : a + n], out=dw, epilogue=G.STORE_F32 if i == 0 else G.ACCUM_F32,
                               alpha=multiplier)
         ctx.save_for_backward(dh, dw)
@@ -361,6 +362,17 @@ class _HeadCE(torch.autograd.Function):
             else:
                 d_weight = (dw * g_loss).to(ctx.w_ref.dtype)
         return d_hidden, d_weight, None, None, None, None
+
+
+def _one_wave_bn(rows: int, n: int, sms: int = 148) -> int | None:
+    """Widest 64-multiple tile width whose tile count still fits one wave of CTAs (long-K products)."""
+
+    m_tiles = -(-rows // 128)
+    best = None
+    for bn in (64, 128, 192, 256):
+        if m_tiles * -(-n // bn) <= sms:
+            return bn if best is None else best
+    return best
 
 
 def lm_head_ce(hidden, weight, targets, multiplier, cd, chunk_rows=4096, ignore_index=-100):

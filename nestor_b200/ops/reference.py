@@ -128,7 +128,7 @@ def build_expert_plan(expert_ids: Tensor, E: int) -> ExpertPlan:
     order = torch.sort(flat, stable=True).indices
     inv = torch.empty_like(order)
     inv[order] = torch.arange(order.numel(), device=order.device)
-    counts = torch.bincount(flat, minlength=E)
+    counts = torch.zeros(E, dtype=torch.int64, device=flat.device).scatter_add_(0, flat, torch.ones_like(flat))
     offsets = torch.zeros(E + 1, dtype=torch.int64, device=flat.device)
     offsets[1:] = counts.cumsum(0)
     return ExpertPlan(E=E, n=flat.numel(), slots=slots, order=order.to(torch.int32),

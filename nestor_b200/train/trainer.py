@@ -81,6 +81,10 @@ class Trainer:
         self.global_counts = _env_flag("NESTOR_LOSSFREE_GLOBAL_COUNTS")
         self.offload = _env_flag("NESTOR_ACTIVATION_OFFLOAD")
         self.tokens_per_micro: int | None = None
+        self._graph: dict | None = None
+        self._graph_warmup = 0
+        self._graph_enabled = (device.type == "cuda" and _env_flag("NESTOR_B200_CUDA_GRAPH", "1") and not self.offload
+                               and not _env_flag("NESTOR_TORCH_PROFILE") and not _env_flag("NESTOR_TRAIN_PROFILE"))
         self._oom_dumper = None
         if _env_flag("NESTOR_DIAG_OOM_SNAPSHOT") and run_dir is not None:
             from nestor_b200.train.oom_snapshot import install_oom_snapshot
@@ -100,15 +104,56 @@ class Trainer:
         return contextlib.nullcontext()
 
     def train_step(self, batch: Any) -> tuple[LossOutput, dict[str, Tensor]]:
-        """Forward + backward of one micro-batch; gradients accumulate into the arena."""
+        """Forward + backward of one micro-batch; gradients accumulate into the arena.
 
-        inputs, targets = self._to_device(batch)
+        On CUDA the whole micro-batch (forward, loss, backward, router counts) is captured once
+        into a CUDA graph and replayed afterwards: every shape is static (packed layouts have
+        exactly ``T*k`` rows, plans are built on the device) and nothing in the step reads
+        device memory from the host, so a replay is one launch. ``NESTOR_B200_CUDA_GRAPH=0``
+        keeps eager launches; activation offload and the eager profiler also disable capture.
+        """
+
+        if self._graph_enabled and self.model.training:
+            return self._graphed_step(batch)
+        return self._eager_step(batch)
+
+    def _graphed_step(self, batch: Any) -> tuple[LossOutput, dict[str, Tensor]]:
+        inputs, _ = batch
+        g = self._graph
+        if g is None or g["ids"].shape != inputs.shape:
+            if self._graph_warmup < 2:
+                # First calls run eagerly (lazy kernel attributes, caches) on a side stream, so that no
+                # autograd node created here is tied to the default stream when capture starts.
+                self._graph_warmup += 1
+                side = self._side_stream = getattr(self, "_side_stream", None) or torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    out = self._eager_step(batch)
+                torch.cuda.current_stream().wait_stream(side)
+                return out
+            ids = torch.empty(inputs.shape, dtype=inputs.dtype, device=self.device)
+            ids.copy_(inputs, non_blocking=True)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                loss, counts = self._eager_step((ids, ids), on_device=True)
+            g = self._graph = {"graph": graph, "ids": ids, "loss": loss, "counts": counts}
+            graph.replay()            # capture records without executing: run this micro-batch now
+            return loss, counts
+        g["ids"].copy_(inputs, non_blocking=True)
+        g["graph"].replay()
+        return g["loss"], g["counts"]
+
+    def _eager_step(self, batch: Any, on_device: bool = False) -> tuple[LossOutput, dict[str, Tensor]]:
+        inputs, targets = batch if on_device else self._to_device(batch)
         self.tokens_per_micro = inputs.numel()
         with self._activation_ctx():
             out = self.model(inputs)
             loss = self.loss_fn(out.pred, targets, out.aux)
         (loss.total / self.config.grad_accum_steps).backward()
         counts = router_counts(self.model.backbone, out.aux) if self.model.training else {}
+        # hand back values only: a live grad_fn would keep this step's autograd nodes alive
+        loss = LossOutput(total=loss.total.detach(), components={k: v.detach() for k, v in loss.components.items()})
         return loss, counts
 
     # ----------------------------------------------------------------- optimizer step
