@@ -1,0 +1,173 @@
+// In-kernel collectives over NVLink peer memory (symmetric buffers mapped into every rank).
+//
+//   allreduce_push : every rank owns 1/W of the range; the owner loads its slice from all
+//                    peers (plain peer loads over NVLink), sums in fp32, scales, and stores
+//                    the result into every rank's buffer (plus an optional bf16 mirror).
+//                    Traffic per rank: (W-1)/W in, (W-1)/W out — the all-reduce minimum.
+//   param_push     : after a sharded optimizer step each rank stores its updated master
+//                    range into every peer's fp32 master buffer and bf16 compute buffer
+//                    (all-gather fused with the compute-dtype cast).
+//
+// Synchronisation: block b of every rank meets block b of its peers at a start barrier
+// (the peers' kernels are running, hence everything stream-ordered before them is done)
+// and at an end barrier (all stores into this rank's buffers have landed before its
+// kernel completes). Flags live in the symmetric signal pad, carry a monotonically
+// increasing epoch (never reset), and are written with release / read with acquire
+// semantics at system scope. Every wait is bounded: when the budget runs out the kernel
+// records kTimeoutPeer in the status word and returns; the host turns that into an error.
+//
+// Replaces DDP's bucketed NCCL all-reduce (nestor/utils/distributed.py:436-443), the per-owner
+// reduce / broadcast of the bf16-master path (nestor/scaling/bf16_master.py:142-172) and
+// `_broadcast_muon_params` (nestor/scaling/muon.py:410-433) of the reference.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace nbc {
+
+constexpr int kMaxWorld = 8;
+constexpr int kTimeoutPeer = 5;
+
+struct Peers {
+  void* buf[kMaxWorld];        // fp32 buffer of every rank (index = rank)
+  void* aux[kMaxWorld];        // optional second buffer of every rank (bf16 mirror / compute copy)
+  uint32_t* sig[kMaxWorld];    // signal pad of every rank
+  int world, rank;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Block `blockIdx.x` of every rank meets here. Slot layout: sig[dst][(phase*gridDim.x + block)*kMaxWorld + src].
+// Returns false (and sets *status) when a peer does not show up within `budget` polls.
+__device__ bool block_barrier(const Peers& P, int phase, uint32_t epoch, long budget, int* status) {
+  __shared__ int s_ok;
+  __syncthreads();
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < P.world) {
+    const int peer = threadIdx.x;
+    const long slot = (long(phase) * gridDim.x + blockIdx.x) * kMaxWorld;
+    __threadfence_system();
+    st_release_sys(P.sig[peer] + slot + P.rank, epoch);
+    const uint32_t* mine = P.sig[P.rank] + slot + peer;
+    bool ok = false;
+    for (long i = 0; i < budget; ++i) {
+      if (int32_t(ld_acquire_sys(mine) - epoch) >= 0) { ok = true; break; }
+      __nanosleep(100);
+    }
+    if (!ok) { s_ok = 0; atomicCAS(status, 0, kTimeoutPeer); }
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+__global__ void __launch_bounds__(512, 1)
+allreduce_push_kernel(Peers P, long offset, long numel, float scale, int write_mirror, uint32_t epoch, long budget,
+                      int* status) {
+  if (!block_barrier(P, 0, epoch, budget, status)) return;
+  // this rank's slice of [0, numel), in float4 units
+  const long n4 = numel / 4;
+  const long per = (n4 + P.world - 1) / P.world;
+  const long lo = per * P.rank, hi = min(n4, lo + per);
+  const long stride = long(gridDim.x) * blockDim.x;
+  for (long i = lo + long(blockIdx.x) * blockDim.x + threadIdx.x; i < hi; i += stride) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int p = 0; p < kMaxWorld; ++p) {
+      if (p < P.world) {
+        const float4 v = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(P.buf[p]) + offset)[i];
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+    }
+    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+    __nv_bfloat162 b0 = __floats2bfloat162_rn(acc.x, acc.y), b1 = __floats2bfloat162_rn(acc.z, acc.w);
+    const uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&b0), *reinterpret_cast<uint32_t*>(&b1));
+#pragma unroll
+    for (int p = 0; p < kMaxWorld; ++p) {
+      if (p < P.world) {
+        reinterpret_cast<float4*>(reinterpret_cast<float*>(P.buf[p]) + offset)[i] = acc;
+        if (write_mirror)
+          reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(P.aux[p]) + offset)[i] = packed;
+      }
+    }
+  }
+  block_barrier(P, 1, epoch, budget, status);
+}
+
+// Store master[lo:hi) (fp32) into every peer's master and its bf16 rounding into every rank's compute buffer.
+__global__ void __launch_bounds__(512, 1)
+param_push_kernel(Peers P, long lo, long hi, uint32_t epoch, long budget, int* status) {
+  if (!block_barrier(P, 2, epoch, budget, status)) return;
+  const long lo4 = lo / 4, hi4 = hi / 4;
+  const long stride = long(gridDim.x) * blockDim.x;
+  const float4* src = reinterpret_cast<const float4*>(P.buf[P.rank]);
+  for (long i = lo4 + long(blockIdx.x) * blockDim.x + threadIdx.x; i < hi4; i += stride) {
+    const float4 v = src[i];
+    __nv_bfloat162 b0 = __floats2bfloat162_rn(v.x, v.y), b1 = __floats2bfloat162_rn(v.z, v.w);
+    const uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&b0), *reinterpret_cast<uint32_t*>(&b1));
+#pragma unroll
+    for (int p = 0; p < kMaxWorld; ++p) {
+      if (p < P.world) {
+        if (p != P.rank) reinterpret_cast<float4*>(P.buf[p])[i] = v;
+        if (P.aux[p]) reinterpret_cast<uint2*>(P.aux[p])[i] = packed;
+      }
+    }
+  }
+  block_barrier(P, 3, epoch, budget, status);
+}
+
+// Single-GPU exercise of the bounded wait: spins on a flag nothing sets and reports the timeout.
+__global__ void wait_timeout_probe_kernel(uint32_t* flag, uint32_t expect, long budget, int* status) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    bool ok = false;
+    for (long i = 0; i < budget; ++i) {
+      if (int32_t(ld_acquire_sys(flag) - expect) >= 0) { ok = true; break; }
+      __nanosleep(100);
+    }
+    if (!ok) atomicCAS(status, 0, kTimeoutPeer);
+  }
+}
+
+}  // namespace nbc
+
+extern "C" {
+
+struct NbPeers {
+  void* buf[8]; void* aux[8]; void* sig[8];
+  int world, rank;
+};
+
+static nbc::Peers to_peers(const NbPeers* a) {
+  nbc::Peers P;
+  for (int i = 0; i < 8; ++i) { P.buf[i] = a->buf[i]; P.aux[i] = a->aux[i]; P.sig[i] = reinterpret_cast<uint32_t*>(a->sig[i]); }
+  P.world = a->world; P.rank = a->rank;
+  return P;
+}
+
+// numel and offset in fp32 elements, both multiples of 4. `blocks` must be equal on every rank and at most the SM count.
+int nb_allreduce_push(const NbPeers* a, long offset, long numel, float scale, int write_mirror, unsigned epoch, long budget,
+                      int blocks, int* status, cudaStream_t st) {
+  if (a->world < 1 || a->world > 8 || (numel % 4) || (offset % 4) || blocks < 1 || blocks > 148) return -1;
+  nbc::allreduce_push_kernel<<<blocks, 512, 0, st>>>(to_peers(a), offset, numel, scale, write_mirror, epoch, budget, status);
+  return int(cudaGetLastError());
+}
+
+int nb_param_push(const NbPeers* a, long lo, long hi, unsigned epoch, long budget, int blocks, int* status, cudaStream_t st) {
+  if (a->world < 1 || a->world > 8 || (lo % 4) || (hi % 4) || blocks < 1 || blocks > 148) return -1;
+  nbc::param_push_kernel<<<blocks, 512, 0, st>>>(to_peers(a), lo, hi, epoch, budget, status);
+  return int(cudaGetLastError());
+}
+
+int nb_wait_timeout_probe(void* flag, unsigned expect, long budget, int* status, cudaStream_t st) {
+  nbc::wait_timeout_probe_kernel<<<1, 32, 0, st>>>(reinterpret_cast<uint32_t*>(flag), expect, budget, status);
+  return int(cudaGetLastError());
+}
+
+}  // extern "C"

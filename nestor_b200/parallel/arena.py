@@ -68,7 +68,7 @@ class _ComputeView(torch.autograd.Function):
 
 class ParamArena:
     def __init__(self, model: nn.Module, *, compute_dtype: torch.dtype = torch.float32,
-                 device: torch.device | None = None) -> None:
+                 device: torch.device | None = None, symmetric: bool = False) -> None:
         named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
         if not named:
             raise ValueError("model has no trainable parameters")
@@ -83,8 +83,16 @@ class ParamArena:
             self._slot_of[id(p)] = s
             off += -(-p.numel() // ALIGN) * ALIGN
         self.numel = off
-        self.master = torch.zeros(off, dtype=torch.float32, device=device)
-        self.grad = torch.zeros(off, dtype=torch.float32, device=device)
+        self.symmetric = symmetric
+
+        def alloc(dtype: torch.dtype) -> Tensor:
+            if symmetric:   # peer-mappable memory for the in-kernel collectives
+                from nestor_b200.parallel.symm import symmetric_empty
+                return symmetric_empty(off, dtype, device).zero_()
+            return torch.zeros(off, dtype=dtype, device=device)
+
+        self.master = alloc(torch.float32)
+        self.grad = alloc(torch.float32)
         with torch.no_grad():
             for n, p in named:
                 s = self.slots[n]
@@ -92,8 +100,7 @@ class ParamArena:
                 view.copy_(p.detach().to(device=device, dtype=torch.float32))
                 p.data = view
                 p.grad = self.grad[s.offset : s.offset + s.numel].view(s.shape)
-        self.compute = self.master if compute_dtype == torch.float32 else torch.empty(
-            off, dtype=compute_dtype, device=device)
+        self.compute = self.master if compute_dtype == torch.float32 else alloc(compute_dtype)
         self.params = [p for _, p in named]
         self.refresh_compute()
         for m in model.modules():  # discoverable from every module that owns parameters

@@ -68,7 +68,7 @@ class MuonAdamW(Optimizer):
     def __init__(self, params: Any, *, lr: float = 1e-3, betas: tuple[float, float] = (0.9, 0.95),
                  eps: float = 1e-8, weight_decay: float = 0.0, momentum: float = 0.95,
                  nesterov: bool = True, ns_steps: int = 5, shard: bool | None = None,
-                 param_sync: Callable[["MuonAdamW"], None] | None = None) -> None:
+                 param_sync: Callable[["MuonAdamW"], None] | None = None, arena: Any = None) -> None:
         defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, momentum=momentum,
                         nesterov=nesterov, ns_steps=ns_steps, method="adamw")
         super().__init__(params, defaults)
@@ -80,15 +80,40 @@ class MuonAdamW(Optimizer):
         self.owner: dict[Tensor, int] = {}
         self.owned: list[list[Tensor]] = [[] for _ in range(self.world)]
         self.param_sync = param_sync
+        self.arena = arena
+        self.owner_cuts: list[int] | None = None   # arena offsets where ownership changes (contiguous mode)
         self._assign_owners()
 
     # ------------------------------------------------------------------ ownership
     def _assign_owners(self) -> None:
+        """Give every Muon parameter one owner rank.
+
+        With a parameter arena the owners hold contiguous arena ranges balanced by element count
+        (so the updated parameters of a rank are one range to distribute); without one, owners are
+        dealt round-robin over (shape, dtype) buckets in first-seen order, the reference's rule
+        (``nestor/scaling/muon.py:319-342``). Which rank updates a matrix does not change the result.
+        """
+
+        muon = [p for g in self.param_groups if g.get("method") == "muon" for p in g["params"]]
+        if self.arena is not None and muon:
+            muon.sort(key=lambda p: self.arena.slot(p).offset)
+            total = sum(p.numel() for p in muon)
+            cuts, seen = [0], 0
+            for p in muon:
+                o = min(self.world - 1, seen * self.world // max(total, 1))
+                while len(cuts) <= o:
+                    cuts.append(self.arena.slot(p).offset)
+                self.owner[p] = o
+                self.owned[o].append(p)
+                seen += p.numel()
+            while len(cuts) < self.world:
+                cuts.append(self.arena.numel)
+            cuts.append(self.arena.numel)
+            self.owner_cuts = cuts
+            return
         buckets: dict[tuple, list[Tensor]] = defaultdict(list)
-        for group in self.param_groups:
-            if group.get("method") == "muon":
-                for p in group["params"]:
-                    buckets[(tuple(p.shape), p.dtype, p.device)].append(p)
+        for p in muon:
+            buckets[(tuple(p.shape), p.dtype, p.device)].append(p)
         cursor = 0
         for params in buckets.values():
             for p in params:
@@ -96,6 +121,13 @@ class MuonAdamW(Optimizer):
                 self.owner[p] = o
                 self.owned[o].append(p)
                 cursor += 1
+
+    def owned_range(self, rank: int | None = None) -> tuple[int, int]:
+        """Arena range ``[lo, hi)`` whose parameters ``rank`` is responsible for distributing."""
+
+        assert self.owner_cuts is not None
+        r = self.rank if rank is None else rank
+        return self.owner_cuts[r], self.owner_cuts[r + 1]
 
     def owns(self, p: Tensor) -> bool:
         return (not self.sharded) or self.owner.get(p, self.rank) == self.rank
@@ -267,6 +299,7 @@ def build_param_groups(config: MuonAdamWConfig, model: nn.Module) -> list[dict[s
 
 def build_optimizer(config: OptimizerConfig, model: nn.Module, **kwargs: Any) -> Optimizer:
     if isinstance(config, MuonAdamWConfig):
+        kwargs.setdefault("arena", model.__dict__.get("_nestor_arena"))
         return MuonAdamW(build_param_groups(config, model), lr=config.lr_adamw, betas=config.betas,
                          eps=config.eps, weight_decay=config.weight_decay, momentum=config.muon_momentum,
                          nesterov=config.muon_nesterov, ns_steps=config.muon_ns_steps, **kwargs)

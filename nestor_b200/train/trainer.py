@@ -64,12 +64,19 @@ class Trainer:
         if _env_flag("NESTOR_FREEZE_ROUTERS"):
             from nestor_b200.train.frozen_routers import freeze_routers
             freeze_routers(model)
-        self.arena = ParamArena(model, compute_dtype=self.compute_dtype, device=device)
-        self.reducer = GradReducer(self.arena)
+        transport = os.environ.get("NESTOR_B200_GRAD_TRANSPORT", "fused" if device.type == "cuda" else "gloo")
+        fused = self.world > 1 and device.type == "cuda" and transport == "fused"
+        self.arena = ParamArena(model, compute_dtype=self.compute_dtype, device=device, symmetric=fused)
+        self.reducer = GradReducer(self.arena, transport=transport)
         self.reducer.sync_buffers(model)
         self.loss_fn = build_loss(config.loss)
         self.optimizer = build_optimizer(config.optimizer, model)
         self.scheduler = build_scheduler(config.scheduler, self.optimizer)
+        self.param_push = None
+        if fused and getattr(self.optimizer, "sharded", False) and getattr(self.optimizer, "owner_cuts", None):
+            from nestor_b200.parallel.symm import ParamPush
+            self.param_push = ParamPush(self.arena.master, self.arena.compute)
+            self.optimizer.param_sync = lambda opt: None      # distribution happens after the compute-copy refresh
         self.global_step, self.epoch = 0, 0
         self.ema: dict[str, Tensor] | None = None
         decay = os.environ.get("NESTOR_EMA_DECAY")
@@ -178,6 +185,9 @@ class Trainer:
                              bool(torch.isfinite(g).all().item()), g.abs().max().item())
         self.optimizer.step()
         self.arena.refresh_compute()
+        if self.param_push is not None:
+            # each rank stores the range it owns into every replica (fp32 master + bf16 compute copy)
+            self.param_push.run(*self.optimizer.owned_range())
         self.arena.zero_grad()
         if self.ema is not None:
             self.ema["flat"].lerp_(self.arena.master, 1.0 - self.ema_decay)
