@@ -229,7 +229,7 @@ class Block(nn.Module):
         r = self.group_router
         w1, w2 = r.weights("score")
         scores = ops.router_scores(x, W(self, w1), W(self, w2), cd)
-        if self.training and r.noise_mlp is not None:
+        if self.training and r.noise_mlp is not None and not getattr(self, "freeze_routing_noise", False):
             eps = torch.randn_like(scores) if noise is None else noise.to(scores.dtype)
             n1, n2 = r.weights("noise")
             scores = scores + eps * torch.nn.functional.softplus(ops.router_scores(x, W(self, n1), W(self, n2), cd))

@@ -141,14 +141,19 @@ class Trainer:
             ids = torch.empty(inputs.shape, dtype=inputs.dtype, device=self.device)
             ids.copy_(inputs, non_blocking=True)
             torch.cuda.synchronize()
+            from nestor_b200.ops import _lib
             graph = torch.cuda.CUDAGraph()
+            before = _lib.LAUNCHES
             with torch.cuda.graph(graph):
                 loss, counts = self._eager_step((ids, ids), on_device=True)
-            g = self._graph = {"graph": graph, "ids": ids, "loss": loss, "counts": counts}
+            g = self._graph = {"graph": graph, "ids": ids, "loss": loss, "counts": counts,
+                               "kernels": _lib.LAUNCHES - before}   # in-tree kernels recorded in the graph
             graph.replay()            # capture records without executing: run this micro-batch now
             return loss, counts
+        from nestor_b200.ops import _lib
         g["ids"].copy_(inputs, non_blocking=True)
         g["graph"].replay()
+        _lib.count_launch(g["kernels"])
         return g["loss"], g["counts"]
 
     def _eager_step(self, batch: Any, on_device: bool = False) -> tuple[LossOutput, dict[str, Tensor]]:
