@@ -1,0 +1,15 @@
+#!/usr/bin/env bash
+# Runtime flags every launcher exports before `nestor_cli`. Each can be preset in the environment.
+# The kernel path has one implementation per op, so there are no fast-path switches here; what remains
+# are the flags that change semantics, parameter layout, memory behaviour or the loop.
+export NESTOR_BF16="${NESTOR_BF16:-1}"                                # bf16 compute copy, fp32 masters
+export NESTOR_DENSE_NO_ROUTER="${NESTOR_DENSE_NO_ROUTER:-1}"          # single-choice routers are frozen and skipped
+export NESTOR_STACKED_EXPERT_BANKS="${NESTOR_STACKED_EXPERT_BANKS:-1}" # checkpoint layout of the expert banks
+export NESTOR_MUON_SHARD="${NESTOR_MUON_SHARD:-1}"                    # one owner rank per Muon matrix
+export NESTOR_FUSED_HEAD_CE="${NESTOR_FUSED_HEAD_CE:-1}"              # chunked head + cross-entropy, no [T, V] logits
+export NESTOR_CE_CHUNK_ROWS="${NESTOR_CE_CHUNK_ROWS:-4096}"
+export NESTOR_RUNAHEAD="${NESTOR_RUNAHEAD:-0}"                        # host may run this many steps ahead of the GPU
+export NESTOR_DDP_BROADCAST_BUFFERS="${NESTOR_DDP_BROADCAST_BUFFERS:-1}" # rank 0's balancing biases win each step
+export NESTOR_B200_CUDA_GRAPH="${NESTOR_B200_CUDA_GRAPH:-1}"          # replay the micro-batch as one CUDA graph
+export NESTOR_B200_GRAD_TRANSPORT="${NESTOR_B200_GRAD_TRANSPORT:-fused}" # fused peer-memory all-reduce | nccl
+export NESTOR_MFU_PEAK_TFLOPS="${NESTOR_MFU_PEAK_TFLOPS:-2250}"       # B200 dense bf16
