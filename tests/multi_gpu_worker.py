@@ -1,0 +1,75 @@
+"""Worker for the multi-GPU tests (launched with ``python -m torch.distributed.run``): checks the fused
+peer-memory all-reduce against NCCL, the parameter push, and that replicas stay identical over
+optimizer steps of the tiny model. Uses plain peer loads/stores only."""
+
+import os
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+import torch
+import torch.distributed as dist
+
+from nestor_b200.ops import _lib
+from nestor_b200.parallel import symm
+from nestor_b200.utils.distributed import init_distributed
+
+
+def main() -> None:
+    dev = init_distributed(True)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    torch.manual_seed(100 + rank)
+    N = 8 * 1024 * 1024
+    g = symm.symmetric_empty(N, torch.float32, dev)
+    g.copy_(torch.randn(N, device=dev) * 1e-3)
+    ref = g.clone()
+    dist.all_reduce(ref)
+    ref /= world
+    far = symm.FusedAllReduce(g, [(0, N // 2), (N // 2, N // 2)])
+    dist.barrier()
+    far.run(1.0 / world)
+    torch.cuda.synchronize()
+    far.group.check()
+    assert (g - ref).abs().max().item() < 1e-6, "fused all-reduce mismatch"
+    M = 4 * 1024 * 1024
+    master, comp = symm.symmetric_empty(M, torch.float32, dev), symm.symmetric_empty(M, torch.bfloat16, dev)
+    master.fill_(float(rank + 1))
+    comp.zero_()
+    torch.cuda.synchronize()
+    dist.barrier()
+    per = M // world
+    pp = symm.ParamPush(master, comp)
+    pp.run(rank * per, (rank + 1) * per)
+    torch.cuda.synchronize()
+    pp.group.check()
+    dist.barrier()
+    want = torch.arange(1, world + 1, device=dev, dtype=torch.float32).repeat_interleave(per)
+    assert torch.equal(master, want) and torch.equal(comp.float(), want), "parameter push mismatch"
+    os.environ.setdefault("DCLM_DATA_PATH", "/tmp/unused.bin")
+    from nestor_b200.experiments.tiny import nestor_tiny
+    from nestor_b200.models import Model
+    from nestor_b200.train.trainer import Trainer
+    torch.manual_seed(0)
+    job = nestor_tiny().jobs[0]
+    tr = Trainer(job, Model.from_config(job.model), [], device=dev)
+    assert tr.param_push is not None and tr.reducer.transport == "fused"
+    tr.model.train()
+    for step in range(3):
+        torch.manual_seed(1000 + step * 10 + rank)
+        ids = torch.randint(0, 100277, (2, 256), device=dev)
+        loss, counts = tr.train_step((ids, ids))
+        tr.update_weights(counts)
+    torch.cuda.synchronize()
+    _lib.check_status(dev)
+    chk = torch.tensor([tr.arena.master.double().sum().item(), tr.arena.compute.double().sum().item()], device=dev,
+                       dtype=torch.float64)
+    gathered = [torch.zeros_like(chk) for _ in range(world)]
+    dist.all_gather(gathered, chk)
+    assert all(torch.equal(x, gathered[0]) for x in gathered), "replicas diverged"
+    if rank == 0:
+        print("MULTI_GPU_OK", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,290 @@
+"""sm_100a kernels against plain PyTorch fp32 references (run with ``-m gpu`` on a B200).
+
+Outputs are pre-filled with NaN so any row or column a kernel fails to write shows up; grouped cases
+include empty groups, ragged tiles and widths that are not multiples of the tile sizes.
+"""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+def _offsets(rows, groups, empty=()):
+    w = torch.rand(groups)
+    for e in empty:
+        w[e] = 0
+    c = (w / w.sum() * rows).floor().long()
+    c[-1] += rows - c.sum()
+    off = torch.zeros(groups + 1, dtype=torch.int32)
+    off[1:] = c.cumsum(0)
+    return off.cuda()
+
+
+@pytest.fixture(autouse=True)
+def _status():
+    from nestor_b200.ops import _lib
+    yield
+    torch.cuda.synchronize()
+    _lib.check_status(torch.device("cuda"))
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 128, 64), (1000, 600, 640), (4096, 256, 200), (333, 72, 80)])
+def test_gemm_single_group(M, N, K):
+    from nestor_b200.ops import gemm as G
+    torch.manual_seed(0)
+    A, B = torch.randn(M, K, device="cuda").to(BF), torch.randn(N, K, device="cuda").to(BF)
+    out = torch.full((M, N), float("nan"), device="cuda", dtype=BF)
+    G.gemm_rows(A, B, out=out)
+    assert _rel(out, A.float() @ B.float().t()) < 5e-3 and torch.isfinite(out.float()).all()
+
+
+def test_gemm_grouped_layouts_and_epilogues():
+    from nestor_b200.ops import gemm as G
+    torch.manual_seed(1)
+    rows, E, d, h = 5000, 12, 640, 216
+    off = _offsets(rows, E, empty=(0, 5))
+    o = off.tolist()
+    X = torch.randn(rows, d, device="cuda").to(BF)
+    Wg, Wu = (torch.randn(E, d, h, device="cuda") * 0.05).to(BF), (torch.randn(E, d, h, device="cuda") * 0.05).to(BF)
+    Wd = (torch.randn(E, h, d, device="cuda") * 0.05).to(BF)
+    H = torch.full((rows, h), float("nan"), device="cuda", dtype=BF)
+    Gt, Ut = torch.empty_like(H), torch.empty_like(H)
+    G.gemm_rows(X, Wg, B2=Wu, offsets=off, groups=E, b_mn=True, out=H, epilogue=G.SWIGLU, extra_out=(Gt, Ut))
+    g = torch.cat([X[o[e]:o[e + 1]].float() @ Wg[e].float() for e in range(E)])
+    u = torch.cat([X[o[e]:o[e + 1]].float() @ Wu[e].float() for e in range(E)])
+    assert _rel(Gt, g) < 5e-3 and _rel(Ut, u) < 5e-3
+    assert _rel(H, torch.nn.functional.silu(g.to(BF)).float() * u.to(BF).float()) < 1e-2
+    Y = torch.full((rows, d), float("nan"), device="cuda", dtype=BF)
+    G.gemm_rows(H, Wd, offsets=off, groups=E, b_mn=True, out=Y)                              # MN-major B
+    assert _rel(Y, torch.cat([H[o[e]:o[e + 1]].float() @ Wd[e].float() for e in range(E)])) < 5e-3
+    dG, dU = torch.randn(rows, h, device="cuda").to(BF), torch.randn(rows, h, device="cuda").to(BF)
+    dX = G.gemm_rows(dG, Wg, A2=dU, B2=Wu, offsets=off, groups=E)                            # two reduction segments
+    want = torch.cat([dG[o[e]:o[e + 1]].float() @ Wg[e].float().t() + dU[o[e]:o[e + 1]].float() @ Wu[e].float().t() for e in range(E)])
+    assert _rel(dX, want) < 5e-3
+    acc0 = torch.randn(E, d, h, device="cuda")
+    acc = acc0.clone()
+    G.gemm_reduce(X, dG, offsets=off, groups=E, out=acc)                                     # weight gradient, accumulate
+    want = acc0 + torch.stack([X[o[e]:o[e + 1]].float().t() @ dG[o[e]:o[e + 1]].float() for e in range(E)])
+    assert _rel(acc, want) < 1e-4
+    st = torch.full((E, d, h), float("nan"), device="cuda")
+    G.gemm_reduce(X, dG, offsets=off, groups=E, out=st, epilogue=G.STORE_F32)
+    assert (st[0] == 0).all() and _rel(st, want - acc0) < 1e-4                               # empty group -> zeros
+    small = torch.zeros(8, d, device="cuda")
+    G.gemm_reduce(dG[:, :8].contiguous(), X, out=small)                                      # split reduction path
+    assert _rel(small, dG[:, :8].float().t() @ X.float()) < 1e-4
+
+
+def test_gemm_stats_epilogue_gives_logsumexp():
+    from nestor_b200.ops import gemm as G
+    torch.manual_seed(2)
+    T, V, d = 700, 10023, 640
+    ld = -(-V // 8) * 8
+    h, W = torch.randn(T, d, device="cuda").to(BF), (torch.randn(V, d, device="cuda") * 0.1).to(BF)
+    nt = -(-ld // 256)
+    logits = torch.empty(T, ld, device="cuda", dtype=BF)
+    part = torch.zeros(T, nt, 2, device="cuda")
+    G.gemm_rows(h, W, out=logits, epilogue=G.STORE_BF16_STATS, alpha=0.125, bn=256, extra_out=(part,), n=ld, n_valid=V)
+    m = part[..., 0].max(1).values
+    lse = m + torch.log((part[..., 1] * torch.exp(part[..., 0] - m[:, None])).sum(1))
+    assert _rel(lse, torch.logsumexp(logits[:, :V].float(), 1)) < 1e-4
+    assert torch.isinf(logits[:, V:].float()).all()
+
+
+@pytest.mark.parametrize("H,hd,lens", [(5, 40, [300, 1, 129, 128, 0, 700]), (2, 80, [600, 257]), (3, 64, [512, 64]), (4, 32, [900])])
+def test_flash_forward_backward(H, hd, lens):
+    from nestor_b200.ops import flash as F
+    torch.manual_seed(3)
+    rows, inner = sum(lens), H * hd
+    qkv = torch.randn(rows, 3 * inner, device="cuda").to(BF)
+    seg = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    q, k, v = qkv[:, :inner], qkv[:, inner:2 * inner], qkv[:, 2 * inner:]
+    out = torch.full((rows, inner), float("nan"), device="cuda", dtype=BF)
+    o, lse = F.flash_fwd(q, k, v, seg, H, hd, 1.0 / hd, out=out)
+    qr = qkv.float().clone().requires_grad_(True)
+    ref = torch.zeros(rows, H, hd, device="cuda")
+    ref_lse = torch.zeros(rows, H, device="cuda")
+    s = seg.tolist()
+    for a, b in zip(s[:-1], s[1:]):
+        if b <= a:
+            continue
+        qq, kk, vv = (qr[a:b, i * inner:(i + 1) * inner].reshape(b - a, H, hd).transpose(0, 1) for i in range(3))
+        sc = (qq @ kk.transpose(1, 2)) / hd
+        sc = sc.masked_fill(~torch.ones(b - a, b - a, dtype=torch.bool, device="cuda").tril(), float("-inf"))
+        ref_lse[a:b] = (torch.logsumexp(sc, -1) / math.log(2)).transpose(0, 1).detach()
+        ref = ref.index_put((torch.arange(a, b, device="cuda"),), (torch.softmax(sc, -1) @ vv).transpose(0, 1))
+    assert _rel(o, ref.reshape(rows, inner)) < 1e-2 and (lse - ref_lse).abs().max() < 2e-2
+    do = torch.randn(rows, inner, device="cuda").to(BF)
+    dqkv = torch.full((rows, 3 * inner), float("nan"), device="cuda", dtype=BF)
+    F.flash_bwd(q, k, v, o, do, lse, seg, H, hd, 1.0 / hd, dqkv=dqkv)
+    (ref.reshape(rows, inner) * do.float()).sum().backward()
+    for i in range(3):
+        sl = slice(i * inner, (i + 1) * inner)
+        assert _rel(dqkv[:, sl], qr.grad[:, sl]) < 2e-2
+    assert torch.isfinite(dqkv.float()).all()
+
+
+@pytest.mark.parametrize("nsrc,d", [(3, 640), (9, 640), (47, 640), (5, 256), (4, 1280)])
+def test_depth_read_norm(nsrc, d):
+    from nestor_b200.ops import cuda as K, reference as R
+    torch.manual_seed(4)
+    T = 555
+    srcs = [(torch.randn(T, d, device="cuda") * (0.1 + i)).requires_grad_(True) for i in range(nsrc)]
+    q = (torch.randn(d, device="cuda") * 0.3).requires_grad_(True)
+    gn = (torch.rand(50, device="cuda") + 0.5).requires_grad_(True)
+    gm = (torch.rand(d, device="cuda") + 0.5).requires_grad_(True)
+    out = K.depth_read_norm(srcs, q, gn, gm, 1e-6, 1e-5, BF)
+    gg = torch.randn(T, d, device="cuda").to(BF).float()
+    (out.float() * gg).sum().backward()
+    s2 = [s.detach().clone().requires_grad_(True) for s in srcs]
+    q2, gn2, gm2 = (t.detach().clone().requires_grad_(True) for t in (q, gn, gm))
+    (R.depth_read_norm(s2, q2, gn2, gm2, 1e-6, 1e-5, torch.float32) * gg).sum().backward()
+    assert _rel(q.grad, q2.grad) < 1e-4 and _rel(gn.grad, gn2.grad) < 1e-4 and _rel(gm.grad, gm2.grad) < 1e-4
+    assert _rel(srcs[0].grad, s2[0].grad) < 1e-4 and _rel(srcs[-1].grad, s2[-1].grad) < 1e-4
+
+
+def test_fused_ops_match_oracle_forward_and_backward():
+    from nestor_b200.ops import cuda as K, reference as R
+    torch.manual_seed(5)
+    d = 640
+    # expert bank
+    T, E, h, slots, group = 1500, 16, 216, 4, 2
+    x = torch.randn(T, d, device="cuda", requires_grad=True)
+    ids, wts = torch.randint(0, E, (T, slots), device="cuda"), torch.rand(T, slots, device="cuda", requires_grad=True)
+    ws = [(torch.randn(*s, device="cuda") * 0.04).to(BF).requires_grad_(True) for s in ((E, d, h), (E, d, h), (E, h, d))]
+    plan = R.build_expert_plan(ids, E)
+    out = K.expert_bank(x, plan, wts, *ws, BF, group)
+    gg = torch.randn_like(out)
+    (out * gg).sum().backward()
+    x2, wts2 = x.detach().clone().requires_grad_(True), wts.detach().clone().requires_grad_(True)
+    ws2 = [w.detach().clone().requires_grad_(True) for w in ws]
+    (R.expert_bank(x2, plan, wts2, *ws2, BF, group) * gg).sum().backward()
+    assert _rel(x.grad, x2.grad) < 2e-2 and _rel(wts.grad, wts2.grad) < 2e-2
+    assert all(_rel(a.grad, b.grad) < 2e-2 for a, b in zip(ws, ws2))
+    # column attention
+    B, S, Gc, k, H, hd = 2, 384, 8, 3, 5, 40
+    T, inner = B * S, H * hd
+    n = torch.randn(T, d, device="cuda", requires_grad=True)
+    idx = torch.randn(B, S, Gc, device="cuda").topk(k, -1).indices
+    gates = torch.rand(T, k, device="cuda", requires_grad=True)
+    plan = R.build_column_plan(idx, Gc)
+    wqkv = (torch.randn(Gc, 3 * inner, d, device="cuda") * 0.04).to(BF).requires_grad_(True)
+    wo = (torch.randn(Gc, d, inner, device="cuda") * 0.04).to(BF).requires_grad_(True)
+    out = K.column_attention(n, plan, gates, wqkv, wo, H, hd, 1e4, BF)
+    gg = torch.randn_like(out)
+    (out * gg).sum().backward()
+    n2, g2, wq2, wo2 = (t.detach().clone().requires_grad_(True) for t in (n, gates, wqkv, wo))
+    out2 = R.column_attention(n2, plan, g2, wq2, wo2, H, hd, 1e4, BF)
+    (out2 * gg).sum().backward()
+    assert _rel(out, out2) < 1e-2
+    for a, b in ((n, n2), (gates, g2), (wqkv, wq2), (wo, wo2)):
+        assert _rel(a.grad, b.grad) < 2e-2
+    # head + cross-entropy (vocabulary not a multiple of 8)
+    T, V = 900, 100263
+    hdn = torch.randn(T, d, device="cuda").to(BF).requires_grad_(True)
+    W = (torch.randn(V, d, device="cuda") * 0.1).to(BF).requires_grad_(True)
+    tg = torch.randint(0, V, (T,), device="cuda")
+    tg[::7] = -100
+    ls, cnt = K.lm_head_ce(hdn, W, tg, 0.125, BF, chunk_rows=512)
+    (ls / cnt).backward()
+    h2, W2 = hdn.detach().clone().requires_grad_(True), W.detach().clone().requires_grad_(True)
+    ls2, cnt2 = R.lm_head_ce(h2, W2, tg, 0.125, BF, chunk_rows=512)
+    (ls2 / cnt2).backward()
+    assert int(cnt) == int(cnt2) and abs(float(ls) - float(ls2)) / float(ls2) < 2e-3
+    assert _rel(hdn.grad, h2.grad) < 2e-2 and _rel(W.grad, W2.grad) < 2e-2
+    # stream bookkeeping
+    T, k = 300, 3
+    attn, priv = torch.randn(T, k, d, device="cuda", requires_grad=True), torch.randn(T, k, d, device="cuda", requires_grad=True)
+    pub = torch.randn(T, d, device="cuda", requires_grad=True)
+    path = torch.softmax(torch.randn(T, 2, device="cuda"), -1).requires_grad_(True)
+    st, rn = torch.randn(T, k, d, device="cuda", requires_grad=True), torch.randn(T, d, device="cuda", requires_grad=True)
+    s1, r1 = K.layer_combine(attn, priv, pub, path, st, rn, BF)
+    dev, agg = K.block_exit(s1)
+    mid = K.mid_source(r1, attn)
+    w = [torch.randn_like(t) for t in (dev, agg, mid)]
+    ((dev * w[0]).sum() + (agg * w[1]).sum() + (mid * w[2]).sum()).backward()
+    leaves = (attn, priv, pub, path, st, rn)
+    clones = [t.detach().clone().requires_grad_(True) for t in leaves]
+    s2, r2 = R.layer_combine(*clones[:4], clones[4], clones[5], BF)
+    dev2, agg2 = R.block_exit(s2)
+    mid2 = R.mid_source(r2, clones[0])
+    ((dev2 * w[0]).sum() + (agg2 * w[1]).sum() + (mid2 * w[2]).sum()).backward()
+    assert _rel(s1, s2) < 1e-5 and _rel(dev, dev2) < 1e-5
+    for a, b in zip(leaves, clones):
+        assert _rel(a.grad, b.grad) < 2e-2, a.shape
+
+
+@pytest.mark.parametrize("family", ["nestor", "moe", "dense"])
+def test_whole_model_kernels_vs_oracle_with_pinned_routing(family, tiny_scale, monkeypatch):
+    from nestor_b200 import ops
+    from nestor_b200.models import Model
+    from nestor_b200.parallel.arena import ParamArena
+    from nestor_b200.train.losses import CausalLMLoss
+    monkeypatch.setitem(tiny_scale.SCALES, "tiny", tiny_scale.Scale("tiny", 256, 4, 16, 1024, 10, 2, 1024))
+    monkeypatch.setitem(tiny_scale.NESTOR_LAYERS, "tiny", (1,) * 7)
+    monkeypatch.setenv("DCLM_BLOCK_SIZE", "512")
+    torch.manual_seed(1)
+    m = Model.from_config(tiny_scale.build_experiment(family, "tiny").jobs[0].model).cuda().eval()
+    with torch.no_grad():
+        for name, p in m.named_parameters():
+            if "query" in name:
+                p.normal_(0, 0.3)
+    m.compute_dtype, m.fused_head = BF, True
+    arena = ParamArena(m, compute_dtype=BF, device=torch.device("cuda"))
+    ids = torch.randint(0, 100263, (2, 512), device="cuda")
+    tape, res = ops.RoutingTape(), {}
+    try:
+        for mode in ("kernels", "oracle"):
+            monkeypatch.setattr(ops, "_FORCE_REF", mode == "oracle")
+            ops.set_routing_tape(tape, "record" if mode == "kernels" else "replay")
+            arena.zero_grad()
+            out = m(ids)
+            loss = CausalLMLoss()(out.pred, ids, out.aux).total
+            loss.backward()
+            res[mode] = (float(loss), arena.grad.clone())
+    finally:
+        ops.set_routing_tape(None)
+    assert abs(res["kernels"][0] - res["oracle"][0]) < 2e-3
+    assert _rel(res["kernels"][1], res["oracle"][1]) < 5e-2
+
+
+def test_bounded_wait_reports_timeout_and_context_survives():
+    from nestor_b200.parallel.symm import wait_timeout_probe
+    code = wait_timeout_probe(torch.device("cuda"), budget=2000)
+    assert code == 5                                   # kTimeoutPeer
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0
+
+
+def test_graphed_step_matches_eager_and_smoke(monkeypatch):
+    import __graft_entry__ as entry
+    entry.smoke()
+    from nestor_b200.experiments.tiny import nestor_tiny
+    from nestor_b200.models import Model
+    from nestor_b200.train.trainer import Trainer
+    losses = {}
+    for flag in ("0", "1"):
+        monkeypatch.setenv("NESTOR_B200_CUDA_GRAPH", flag)
+        torch.manual_seed(0)
+        job = nestor_tiny().jobs[0]
+        tr = Trainer(job, Model.from_config(job.model), [], device=torch.device("cuda"))
+        tr.model.eval()                                 # deterministic routing (no exploration noise)
+        tr.model.training = True
+        for blk in tr.model.backbone.blocks:
+            blk.freeze_routing_noise = True
+        vals = []
+        for step in range(5):
+            g = torch.Generator().manual_seed(step)
+            ids = torch.randint(0, 100277, (2, 256), generator=g)
+            loss, counts = tr.train_step((ids, ids))
+            tr.update_weights(counts)
+            vals.append(float(loss.total))
+        losses[flag] = vals
+        assert (tr._graph is not None) == (flag == "1")
+    assert all(abs(a - b) < 5e-3 for a, b in zip(losses["0"], losses["1"])), losses

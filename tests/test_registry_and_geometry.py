@@ -104,7 +104,7 @@ def test_tokens_per_step_is_pinned(monkeypatch):
 
 def test_config_validation():
     base = dict(input_dim=64, num_blocks=1, feature_dims=[64], causal=True, block_mlp_activations="swiglu",
-                block_mlp_hidden_dims=[256], block_residual_mode="attn_res_kimi")
+                block_mlp_hidden_dims=[256], block_residual_mode="attn_res_kimi", router_num_shared_experts=1)
     NestorConfig(**base).resolve()
     with pytest.raises(ValueError):
         NestorConfig(**{**base, "causal": False}).resolve()
