@@ -330,3 +330,53 @@ int nb_flash_bwd(const NbFlashBwdArgs* a, cudaStream_t stream) {
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant (see flash_noalloc.h): the `delta` scratch lives in a fixed device array.
+#include "flash_noalloc.h"
+#include <stdio.h>
+
+static __device__ __align__(256) float g_noalloc_delta[NB_FLASH_NOALLOC_MAX_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};      // device address of g_noalloc_delta, per device
+thread_local char g_noalloc_msg[256] = "";
+}  // namespace
+
+extern "C" const char* nb_flash_bwd_noalloc_error(void) { return g_noalloc_msg; }
+
+extern "C" int nb_flash_bwd_noalloc(const NbFlashBwdArgs* args, cudaStream_t stream) {
+  g_noalloc_msg[0] = 0;
+  const long need = long(args->rows) * args->H;
+  if (need > NB_FLASH_NOALLOC_MAX_FLOATS) {
+    snprintf(g_noalloc_msg, sizeof(g_noalloc_msg),
+             "nb_flash_bwd_noalloc: rows * heads = %ld exceeds the built-in scratch of %d floats; "
+             "use nb_flash_bwd with a caller-provided delta buffer", need, NB_FLASH_NOALLOC_MAX_FLOATS);
+    return NB_FLASH_NOALLOC_TOO_LARGE;
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "nb_flash_bwd_noalloc: cannot identify the current device (%s)",
+             cudaGetErrorString(e));
+    return NB_FLASH_NOALLOC_SETUP_FAILED;
+  }
+  if (!g_noalloc_ptr[dev]) {
+    // Set-up, once per device, with that device current: the array's name is only a host-side handle;
+    // kernels need its device address.
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_delta);
+    if (e != cudaSuccess || !p) {
+      snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "nb_flash_bwd_noalloc: cudaGetSymbolAddress failed (%s)",
+               cudaGetErrorString(e));
+      return NB_FLASH_NOALLOC_SETUP_FAILED;
+    }
+    g_noalloc_ptr[dev] = p;
+  }
+  NbFlashBwdArgs local = *args;
+  local.delta = g_noalloc_ptr[dev];   // fully rewritten (rows * heads entries) before it is read
+  int rc = nb_flash_bwd(&local, stream);
+  if (rc != 0) snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "nb_flash_bwd_noalloc: nb_flash_bwd returned %d", rc);
+  return rc;
+}
