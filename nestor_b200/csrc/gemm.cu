@@ -52,7 +52,17 @@ struct GemmParams {
   int splits;               // mode 1: each output tile is reduced by `splits` CTAs (atomic fp32 adds)
   int* status;
   int max_tiles;
+  unsigned long long* trace;   // optional: per-CTA phase timestamps (ns), 64 slots per CTA (diagnostics)
+  int prefetch_dist;           // producer pulls k-block (i + dist) into L2 while loading k-block i (0 = off)
+  int prefetch_ops;            // operands to prefetch: 1 = A, 2 = B, 3 = both
 };
+
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define NB_TRACE(slot) do { if (p.trace && (slot) < 64) p.trace[blockIdx.x * 64 + (slot)] = gtime(); } while (0)
 
 struct Tile { int g, m0, n0, row_end, kb, kb2, kb0, valid; };
 
@@ -151,39 +161,65 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
     if (elect_one()) {
-      uint32_t it = 0;
-      for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
-        Tile tl = decode_tile(p, s_off, s_tstart, t, n_tiles);
-        int nkb = tl.kb + tl.kb2;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
-          int s = it % stages; uint32_t ph = (it / stages) & 1;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, kTimeoutEmpty)) break;
-          uint8_t* sa = smem + s * stage_bytes;
-          uint8_t* sb = sa + a_bytes;
-          mbar_expect_tx(&full_bar[s], stage_bytes);
-          bool second = kb >= tl.kb;
-          const CUtensorMap* mA = second ? &tmA2 : &tmA;
-          const CUtensorMap* mB = second ? &tmB2 : &tmB;
-          int kk = (second ? kb - tl.kb : kb) * BK;
-          if (p.mode == 0) {
-            if (!p.a_mn) tma_load_2d(sa, mA, &full_bar[s], kk, tl.m0);
-            else { tma_load_2d(sa, mA, &full_bar[s], tl.m0, kk); tma_load_2d(sa + 8192, mA, &full_bar[s], tl.m0 + 64, kk); }
+      // One routine computes the coordinates of a k-block's boxes; `pf` = 0 issues the loads into the stage,
+      // otherwise it only pulls the boxes of the operands in the mask (1 = A, 2 = B) into L2.
+      auto ld2 = [&](void* dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int pf) {
+        if (pf) tma_prefetch_2d(m, x, y); else tma_load_2d(dst, m, bar, x, y);
+      };
+      auto ld3 = [&](void* dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int z, int pf) {
+        if (pf) tma_prefetch_3d(m, x, y, z); else tma_load_3d(dst, m, bar, x, y, z);
+      };
+      auto issue = [&](const Tile& tl, int kb, uint8_t* sa, uint8_t* sb, uint64_t* bar, int pf) {
+        const bool doA = !pf || (pf & 1), doB = !pf || (pf & 2);
+        bool second = kb >= tl.kb;
+        const CUtensorMap* mA = second ? &tmA2 : &tmA;
+        const CUtensorMap* mB = second ? &tmB2 : &tmB;
+        int kk = (second ? kb - tl.kb : kb) * BK;
+        if (p.mode == 0) {
+          if (doA) {
+            if (!p.a_mn) ld2(sa, mA, bar, kk, tl.m0, pf);
+            else { ld2(sa, mA, bar, tl.m0, kk, pf); ld2(sa + 8192, mA, bar, tl.m0 + 64, kk, pf); }
+          }
+          if (doB) {
             int bg = p.b_grouped ? tl.g : 0;
-            if (!p.b_mn) tma_load_3d(sb, mB, &full_bar[s], kk, tl.n0, bg);
+            if (!p.b_mn) ld3(sb, mB, bar, kk, tl.n0, bg, pf);
             else if (p.epilogue == kSwiGLU) {
               // B tile = [gate columns | up columns], each half from its own tensor (tmB = gate, tmB2 = up)
               int half = p.BN / 2, c0 = tl.n0 / 2;
-              for (int a = 0; a < half / 64; ++a) tma_load_3d(sb + a * 8192, &tmB, &full_bar[s], c0 + a * 64, kk, bg);
-              for (int a = 0; a < half / 64; ++a)
-                tma_load_3d(sb + (half / 64 + a) * 8192, &tmB2, &full_bar[s], c0 + a * 64, kk, bg);
+              for (int a = 0; a < half / 64; ++a) ld3(sb + a * 8192, &tmB, bar, c0 + a * 64, kk, bg, pf);
+              for (int a = 0; a < half / 64; ++a) ld3(sb + (half / 64 + a) * 8192, &tmB2, bar, c0 + a * 64, kk, bg, pf);
             } else {
-              for (int a = 0; a < p.BN / 64; ++a) tma_load_3d(sb + a * 8192, mB, &full_bar[s], tl.n0 + a * 64, kk, bg);
+              for (int a = 0; a < p.BN / 64; ++a) ld3(sb + a * 8192, mB, bar, tl.n0 + a * 64, kk, bg, pf);
             }
-          } else {
-            int row = s_off[tl.g] + (tl.kb0 + kb) * BK;     // reduction over the group's rows; operands are MN-major
-            tma_load_2d(sa, mA, &full_bar[s], tl.m0, row);
-            tma_load_2d(sa + 8192, mA, &full_bar[s], tl.m0 + 64, row);
-            for (int a = 0; a < p.BN / 64; ++a) tma_load_2d(sb + a * 8192, mB, &full_bar[s], tl.n0 + a * 64, row);
+          }
+        } else {
+          int row = s_off[tl.g] + (tl.kb0 + kb) * BK;     // reduction over the group's rows; operands are MN-major
+          if (doA) { ld2(sa, mA, bar, tl.m0, row, pf); ld2(sa + 8192, mA, bar, tl.m0 + 64, row, pf); }
+          if (doB) for (int a = 0; a < p.BN / 64; ++a) ld2(sb + a * 8192, mB, bar, tl.n0 + a * 64, row, pf);
+        }
+      };
+      const int D = p.prefetch_dist, pf_mask = p.prefetch_ops;
+      uint32_t it = 0;
+      NB_TRACE(0);
+      for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
+        Tile tl = decode_tile(p, s_off, s_tstart, t, n_tiles);
+        int nkb = tl.kb + tl.kb2;
+        Tile nx = tl; int nx_nkb = 0;
+        if (D > 0 && t + int(gridDim.x) < total_tiles) {
+          nx = decode_tile(p, s_off, s_tstart, t + gridDim.x, n_tiles);
+          nx_nkb = nx.kb + nx.kb2;
+        }
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          int s = it % stages; uint32_t ph = (it / stages) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, kTimeoutEmpty)) break;
+          if (it < 12) NB_TRACE(1 + it);
+          uint8_t* sa = smem + s * stage_bytes;
+          mbar_expect_tx(&full_bar[s], stage_bytes);
+          issue(tl, kb, sa, sa + a_bytes, &full_bar[s], 0);
+          if (D > 0) {
+            int pk = kb + D;
+            if (pk < nkb) issue(tl, pk, nullptr, nullptr, nullptr, pf_mask);
+            else if (pk - nkb < nx_nkb) issue(nx, pk - nkb, nullptr, nullptr, nullptr, pf_mask);
           }
         }
       }
@@ -203,12 +239,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       tc_fence_after();
+      if (lane == 0 && tile_i <= 6) NB_TRACE(16 + 4 * (tile_i - 1));
       uint32_t d_addr = tmem_base + buf * p.BN;
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         int s = it % stages; uint32_t ph = (it / stages) & 1;
         if (lane == 0) ok = mbar_wait(&full_bar[s], ph, abort_flag, p.status, kTimeoutFull);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
+        if (lane == 0 && kb == 0 && tile_i <= 6) NB_TRACE(16 + 4 * (tile_i - 1) + 1);
         uint8_t* sa = smem + s * stage_bytes;
         uint8_t* sb = sa + a_bytes;
         if (p.mode == 1) {
@@ -236,7 +274,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             umma_bf16(d_addr, ad, bd, idesc, (kb | k) != 0);
           }
           umma_commit(&empty_bar[s]);              // stage is free once these MMAs retire
-          if (kb == nkb - 1) umma_commit(&tfull_bar[buf]);
+          if (kb == nkb - 1) { umma_commit(&tfull_bar[buf]); if (tile_i <= 6) NB_TRACE(16 + 4 * (tile_i - 1) + 2); }
         }
         __syncwarp();
       }
@@ -260,6 +298,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         ++tile_i;
         if (!mbar_wait(&tfull_bar[buf], bph, abort_flag, p.status, kTimeoutTmemFull)) break;
         tc_fence_after();
+        if (q == 0 && lane == 0 && tile_i <= 6) NB_TRACE(40 + 3 * (tile_i - 1));
       }
       const uint32_t taddr = tmem_base + buf * p.BN + (uint32_t(q * 32) << 16);
       const int ncols = min(p.BN, p.N - tl.n0);
@@ -302,15 +341,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
       } else {
         float run_max = -INFINITY, run_sum = 0.f;
-        for (int c = 0; c < ncols; c += 16) {
-          float v[16];
-          if (nkb > 0) { tmem_ld16(taddr + c, v); tmem_ld_wait(); }
-          else {
+        for (int c0 = 0; c0 < ncols; c0 += 32) {
+          // 32 accumulator columns per TMEM round trip (16 when that is all that is left of the tile)
+          float v32[32];
+          if (nkb > 0) {
+            if (ncols - c0 > 16) tmem_ld32(taddr + c0, v32); else tmem_ld16(taddr + c0, v32);
+            tmem_ld_wait();
+          } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = 0.f;
+            for (int j = 0; j < 32; ++j) v32[j] = 0.f;
           }
-          const int rem = ncols - c;           // 8 or >= 16
-          if (!row_ok) continue;
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+          const int c = c0 + 16 * hh;
+          float* v = v32 + 16 * hh;
+          const int rem = ncols - c;           // <= 0 (past the tile), 8 or >= 16
+          if (!row_ok || rem <= 0) continue;
           const long o = c_base + tl.n0 + c;
           if (p.epilogue == kStoreBf16 || p.epilogue == kStoreBf16Stats) {
             if (p.epilogue == kStoreBf16Stats) {
@@ -326,24 +372,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if (p.epilogue == kStoreBf16Stats) {
               const int lim = rem >= 16 ? 16 : 8;
               float m = run_max;
-              for (int j = 0; j < lim; ++j) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
                 float x = __bfloat162float(__float2bfloat16(v[j] * p.alpha));
-                v[j] = x; m = fmaxf(m, x);
+                v[j] = j < lim ? x : -INFINITY; m = fmaxf(m, v[j]);
               }
               float ssum = run_sum * __expf(run_max - m);
-              for (int j = 0; j < lim; ++j) ssum += __expf(v[j] - m);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) ssum += __expf(v[j] - m);
               run_max = m; run_sum = ssum;
             }
           } else if (p.epilogue == kStoreF32) {
             float* Cp = reinterpret_cast<float*>(p.C) + o;
             const int lim = rem >= 16 ? 16 : 8;
-            for (int j = 0; j < lim; j += 4)
-              reinterpret_cast<float4*>(Cp + j)[0] = make_float4(v[j] * p.alpha, v[j + 1] * p.alpha, v[j + 2] * p.alpha, v[j + 3] * p.alpha);
+#pragma unroll
+            for (int j = 0; j < 16; j += 4)
+              if (j < lim) reinterpret_cast<float4*>(Cp + j)[0] = make_float4(v[j] * p.alpha, v[j + 1] * p.alpha, v[j + 2] * p.alpha, v[j + 3] * p.alpha);
           } else if (p.epilogue == kAccumF32) {
             if (nkb > 0) {
               float* Cp = reinterpret_cast<float*>(p.C) + o;
               const int lim = rem >= 16 ? 16 : 8;
-              for (int j = 0; j < lim; j += 4) {
+#pragma unroll
+              for (int j = 0; j < 16; j += 4) {
+                if (j >= lim) break;
                 float4 add = make_float4(v[j] * p.alpha, v[j + 1] * p.alpha, v[j + 2] * p.alpha, v[j + 3] * p.alpha);
                 if (p.splits > 1) {
                   atomicAdd(reinterpret_cast<float4*>(Cp + j), add);
@@ -361,7 +412,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             __nv_bfloat16* dG = reinterpret_cast<__nv_bfloat16*>(p.C) + o;
             __nv_bfloat16* dU = reinterpret_cast<__nv_bfloat16*>(p.C2) + o;
             const int lim = rem >= 16 ? 16 : 8;
-            for (int j = 0; j < lim; j += 8) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 8) {
+              if (j >= lim) break;
               uint4 gq = reinterpret_cast<const uint4*>(Gp + j)[0], uq = reinterpret_cast<const uint4*>(Up + j)[0];
               const __nv_bfloat16* gb = reinterpret_cast<const __nv_bfloat16*>(&gq);
               const __nv_bfloat16* ub = reinterpret_cast<const __nv_bfloat16*>(&uq);
@@ -384,6 +437,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
           }
         }
+          }
         if (p.epilogue == kStoreBf16Stats && row_ok) {
           float2* part = reinterpret_cast<float2*>(p.C2) + long(row) * n_tiles + (tl.n0 / p.BN);
           *part = make_float2(run_max, run_sum);
@@ -392,6 +446,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if (nkb > 0) {
         tc_fence_before();
         __syncwarp();
+        if (q == 0 && lane == 0 && tile_i <= 6) NB_TRACE(40 + 3 * (tile_i - 1) + 1);
         if (lane == 0) mbar_arrive(&tempty_bar[buf]);
       }
     }
@@ -466,6 +521,10 @@ struct NbGemmArgs {
   int* status;
   int max_m_tiles;          // upper bound on m tiles over all groups (mode 0)
   int sms;                  // 0 = all
+  unsigned long long* trace;
+  int prefetch_dist;        // L2 look-ahead of the producer in k-blocks (0 = off)
+  int prefetch_ops;         // 1 = A, 2 = B, 3 = both
+  int max_stages;           // 0 = as many as fit
 };
 
 // Returns 0 on success, a negative code for bad arguments / map failures, or a CUDA error code.
@@ -513,6 +572,9 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
   p.a_mn = a->a_mn; p.b_mn = a->b_mn; p.b_grouped = a->b_grouped;
   p.C = a->C; p.ldc = a->ldc; p.c_group_stride = a->c_group_stride; p.C2 = a->C2; p.C3 = a->C3;
   p.E1 = a->E1; p.E2 = a->E2; p.lde = a->lde; p.alpha = a->alpha; p.n_valid = a->n_valid > 0 ? a->n_valid : a->N; p.status = a->status;
+  p.trace = a->trace;
+  p.prefetch_dist = a->prefetch_dist > 0 ? a->prefetch_dist : 0;
+  p.prefetch_ops = a->prefetch_ops & 3;
   p.splits = (a->mode == 1 && a->epilogue == kAccumF32 && a->splits > 1) ? a->splits : 1;
 
   const int n_tiles = (a->N + a->BN - 1) / a->BN;
@@ -520,8 +582,9 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
                             : long(a->groups) * ((a->M + BM - 1) / BM) * n_tiles * p.splits;
   if (tiles <= 0) return 0;
   const uint32_t stage_bytes = BM * BK * 2 + a->BN * BK * 2;
-  int stages = int((200 * 1024) / stage_bytes);
+  int stages = int((220 * 1024) / stage_bytes);   // 227 KB per CTA minus barriers, offsets and alignment slack
   if (stages > 8) stages = 8;
+  if (a->max_stages > 0 && stages > a->max_stages) stages = a->max_stages;
   if (stages < 2) return -7;
   size_t smem = size_t(stages) * stage_bytes + 1024;
   static size_t configured = 0;

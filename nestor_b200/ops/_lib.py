@@ -32,7 +32,8 @@ class GemmArgs(C.Structure):
         ("C2", C.c_void_p), ("C3", C.c_void_p), ("E1", C.c_void_p), ("E2", C.c_void_p), ("lde", C.c_long),
         ("alpha", C.c_float), ("n_valid", C.c_int), ("splits", C.c_int), ("status", C.c_void_p),
         ("max_m_tiles", C.c_int),
-        ("sms", C.c_int),
+        ("sms", C.c_int), ("trace", C.c_void_p),
+        ("prefetch_dist", C.c_int), ("prefetch_ops", C.c_int), ("max_stages", C.c_int),
     ]
 
 

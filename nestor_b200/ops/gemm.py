@@ -10,6 +10,7 @@ TMA without any copy.
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 from torch import Tensor
@@ -17,6 +18,12 @@ from torch import Tensor
 from nestor_b200.ops import _lib
 
 STORE_BF16, STORE_F32, ACCUM_F32, SWIGLU, SWIGLU_BWD, STORE_BF16_STATS = range(6)
+
+# Producer tuning (see csrc/gemm.cu): L2 look-ahead in k-blocks (off: measured slower, the TMA issue rate is the
+# limit, not DRAM latency), and a cap on pipeline stages (0 = all that fit).
+PREFETCH_DIST = int(os.environ.get("NESTOR_B200_GEMM_PREFETCH", "0"))
+MAX_STAGES = int(os.environ.get("NESTOR_B200_GEMM_STAGES", "0"))
+_L2_RESIDENT_BYTES = 48 << 20    # a shared B operand smaller than this stays in L2 without help
 
 
 def pick_bn(n: int, *, mult: int = 16, cap: int = 256) -> int:
@@ -52,7 +59,7 @@ def _launch(args: _lib.GemmArgs) -> None:
 def gemm_rows(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: int = 1, b_mn: bool = False,
               out: Tensor | None = None, epilogue: int = STORE_BF16, alpha: float = 1.0, bn: int | None = None,
               A2: Tensor | None = None, B2: Tensor | None = None, extra_out: tuple = (), extra_in: tuple = (),
-              n: int | None = None, n_valid: int = 0, sms: int = 0) -> Tensor:
+              n: int | None = None, n_valid: int = 0, sms: int = 0, trace: Tensor | None = None) -> Tensor:
     """Row-grouped GEMM.
 
     ``A [rows, K]``; ``B`` is ``[G, N, K]`` (K-major) or ``[G, K, N]`` (``b_mn``) — 2-D for a
@@ -98,6 +105,10 @@ def gemm_rows(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: in
     a.status = _lib.status_word(dev).data_ptr()
     a.max_m_tiles = -(-rows // 128) + groups
     a.sms = sms
+    a.trace = trace.data_ptr() if trace is not None else None
+    # A is streamed once per n-tile pass; B (weights) is re-read by every m-tile and only needs help when it is large
+    a.prefetch_dist, a.max_stages = PREFETCH_DIST, MAX_STAGES
+    a.prefetch_ops = 1 | (2 if B.numel() * 2 > _L2_RESIDENT_BYTES else 0)
     _launch(a)
     return out
 
@@ -136,5 +147,6 @@ def gemm_reduce(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: 
     a.status = _lib.status_word(A.device).data_ptr()
     a.max_m_tiles = 0
     a.sms = sms
+    a.prefetch_dist, a.max_stages, a.prefetch_ops = PREFETCH_DIST, MAX_STAGES, 3
     _launch(a)
     return out
