@@ -12,8 +12,8 @@
 // Operands are bf16, K-major (rows of K) or MN-major (rows of M/N); see sm100.cuh.
 // A second (A2, B2) operand pair extends the reduction (dX = dG.Wg^T + dU.Wu^T in one pass).
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer (+TMEM owner),
-// warps 2..5 = epilogue (warp w reads TMEM lanes 32*(w%4)..+31). Two accumulator buffers
+// Warp roles (352 threads): warp 0 = TMA producer of A tiles, warp 10 = TMA producer of B tiles, warp 1 = MMA issuer
+// (+TMEM owner), warps 2..9 = epilogue (warp w reads TMEM lanes 32*(w%4)..+31; two warps per lane quarter split the columns). Two accumulator buffers
 // let the epilogue of tile i overlap the main loop of tile i+1.
 //
 // Replaces the reference's torch._grouped_mm call sites (nestor/backbones/grouped_mm.py:83,
@@ -55,6 +55,8 @@ struct GemmParams {
   unsigned long long* trace;   // optional: per-CTA phase timestamps (ns), 64 slots per CTA (diagnostics)
   int prefetch_dist;           // producer pulls k-block (i + dist) into L2 while loading k-block i (0 = off)
   int prefetch_ops;            // operands to prefetch: 1 = A, 2 = B, 3 = both
+  int pair;                    // mode 0: CTA pairs (cluster of 2) run 256-row tiles with cta_group::2 MMAs
+  int debug;                   // timing experiments only (results are garbage): 1 = issue no MMAs, 2 = issue no loads, 4 = store nothing
 };
 
 __device__ __forceinline__ unsigned long long gtime() {
@@ -73,20 +75,20 @@ struct Sched {
   const int* off;     // smem offsets
 };
 
+// `g_hint` carries the group of the caller's previous tile: a CTA visits tiles in increasing order, so the
+// group is found by stepping forward instead of searching.
 __device__ __forceinline__ Tile decode_tile(const GemmParams& p, const int* s_off, const int* s_tstart, int t,
-                                            int n_tiles) {
+                                            int n_tiles, int rank, int& g_hint) {
   Tile r;
   r.valid = 1;
   r.kb0 = 0;
   if (p.mode == 0) {
     int mt = t / n_tiles, nt = t - mt * n_tiles;
-    int lo = 0, hi = p.groups;          // find g with tstart[g] <= mt < tstart[g+1]
-    while (hi - lo > 1) {
-      int mid = (lo + hi) >> 1;
-      if (s_tstart[mid] <= mt) lo = mid; else hi = mid;
-    }
+    int lo = g_hint;                    // find g with tstart[g] <= mt < tstart[g+1]
+    while (lo + 1 < p.groups && s_tstart[lo + 1] <= mt) ++lo;
+    g_hint = lo;
     r.g = lo;
-    r.m0 = s_off[lo] + (mt - s_tstart[lo]) * BM;
+    r.m0 = s_off[lo] + (mt - s_tstart[lo]) * (p.pair ? 2 * BM : BM) + rank * BM;   // rank 1 owns the lower half
     r.row_end = s_off[lo + 1];
     r.n0 = nt * p.BN;
     r.kb = (p.K + BK - 1) / BK;
@@ -110,7 +112,64 @@ __device__ __forceinline__ Tile decode_tile(const GemmParams& p, const int* s_of
   return r;
 }
 
-__global__ void __launch_bounds__(192, 1)
+// Epilogue staging: a warp holds its accumulator chunk one row per lane, but a store instruction in that shape
+// touches 32 different 128-byte lines (16 B each) and the load/store unit serialises them. Each warp therefore
+// transposes 32 rows x 32 bf16 columns through a private shared-memory slab (row pitch 80 B keeps both the
+// row-per-lane writes and the read-back free of bank conflicts) and stores 8 rows x 64 B per instruction.
+constexpr int kSlabPitch = 80;
+constexpr int kSlabBytes = 32 * kSlabPitch;      // per epilogue warp
+
+// w[16] = this lane's row, 32 bf16 columns (packed pairs). Rows >= rows_ok and 8-column groups >= cols_ok (a
+// multiple of 8) are not stored. `dst` points at (row 0 of the slab's 32 rows, first column of the chunk).
+__device__ __forceinline__ void store_chunk_bf16(uint8_t* slab, int lane, const uint32_t* w, __nv_bfloat16* dst, long ld,
+                                                 int rows_ok, int cols_ok) {
+  uint4* mine = reinterpret_cast<uint4*>(slab + lane * kSlabPitch);
+  mine[0] = make_uint4(w[0], w[1], w[2], w[3]);
+  mine[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  mine[2] = make_uint4(w[8], w[9], w[10], w[11]);
+  mine[3] = make_uint4(w[12], w[13], w[14], w[15]);
+  __syncwarp();
+  const int c = lane & 3;                                  // 16-byte column group
+  const int r0 = (lane >> 3) + 4 * ((lane >> 2) & 1);      // rows r0, r0 + 8, r0 + 16, r0 + 24
+  if (c * 8 < cols_ok) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = r0 + 8 * i;
+      if (r < rows_ok)
+        *reinterpret_cast<uint4*>(dst + long(r) * ld + c * 8) = *reinterpret_cast<const uint4*>(slab + r * kSlabPitch + c * 16);
+    }
+  }
+  __syncwarp();
+}
+
+// The reverse: 32 rows x 32 bf16 columns from global memory (coalesced) into w[16] = this lane's row.
+__device__ __forceinline__ void load_chunk_bf16(uint8_t* slab, int lane, uint32_t* w, const __nv_bfloat16* src, long ld,
+                                                int rows_ok, int cols_ok) {
+  const int c = lane & 3;
+  const int r0 = (lane >> 3) + 4 * ((lane >> 2) & 1);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = r0 + 8 * i;
+    uint4 x = make_uint4(0u, 0u, 0u, 0u);
+    if (r < rows_ok && c * 8 < cols_ok) x = *reinterpret_cast<const uint4*>(src + long(r) * ld + c * 8);
+    *reinterpret_cast<uint4*>(slab + r * kSlabPitch + c * 16) = x;
+  }
+  __syncwarp();
+  const uint4* mine = reinterpret_cast<const uint4*>(slab + lane * kSlabPitch);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint4 x = mine[i];
+    w[4 * i] = x.x; w[4 * i + 1] = x.y; w[4 * i + 2] = x.z; w[4 * i + 3] = x.w;
+  }
+  __syncwarp();
+}
+
+// PAIR = 1 is compiled separately: a kernel that contains cta_group::2 instructions can only be launched as
+// clusters of two, so the single-CTA variant must not contain them. The epilogue is a template parameter too:
+// with every variant in one kernel the eleven warps of a CTA (each in a different code region) thrash the
+// instruction cache, which showed as "no instruction" stalls on every role.
+template <int PAIR, int EPI>
+__global__ void __launch_bounds__(352, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
             const GemmParams p, int stages) {
@@ -123,8 +182,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int pair = PAIR;
+  const uint32_t rank = pair ? cluster_ctarank() : 0u;   // rank 0 of a pair issues the MMAs
+  const int b_cols = pair ? p.BN / 2 : p.BN;             // B columns staged by this CTA
   const uint32_t a_bytes = BM * BK * 2;               // 16 KB
-  const uint32_t b_bytes = uint32_t(p.BN) * BK * 2;
+  const uint32_t b_bytes = uint32_t(b_cols) * BK * 2;
   const uint32_t stage_bytes = a_bytes + b_bytes;
   const uint32_t tmem_cols = (2 * p.BN <= 32) ? 32 : (2 * p.BN <= 64) ? 64 : (2 * p.BN <= 128) ? 128
                            : (2 * p.BN <= 256) ? 256 : 512;
@@ -137,18 +199,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     int acc = 0;
     for (int g = 0; g < p.groups; ++g) {
       s_tstart[g] = acc;
-      acc += (s_off[g + 1] - s_off[g] + BM - 1) / BM;
+      acc += pair ? (s_off[g + 1] - s_off[g] + 2 * BM - 1) / (2 * BM) : (s_off[g + 1] - s_off[g] + BM - 1) / BM;
     }
     s_tstart[p.groups] = acc;
-    for (int s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4); }
+    for (int s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 2); mbar_init(&empty_bar[s], 1); }   // full: A and B producers
+    // an accumulator is drained by the eight epilogue warps of every CTA that holds a part of it
+    for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], pair ? 16 : 8); }
     fence_barrier_init();
     prefetch_tmap(&tmA); prefetch_tmap(&tmB);
     if (p.K2) { prefetch_tmap(&tmA2); prefetch_tmap(&tmB2); }
   }
-  if (warp == 1) { tmem_alloc(&tmem_base_slot, tmem_cols); tmem_relinquish(); }
+  if (warp == 1) {
+    if (pair) { tmem_alloc_pair(&tmem_base_slot, tmem_cols); tmem_relinquish_pair(); }
+    else { tmem_alloc(&tmem_base_slot, tmem_cols); tmem_relinquish(); }
+  }
   tc_fence_before();
   __syncthreads();
+  if (pair) cluster_sync_all();     // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
 
@@ -157,20 +224,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   else total_tiles = p.groups * ((p.M + BM - 1) / BM) * n_tiles * p.splits;
 
   volatile int* abort_flag = &s_abort;
+  const int cta = pair ? int(blockIdx.x >> 1) : int(blockIdx.x);       // persistent worker index
+  const int n_cta = pair ? int(gridDim.x >> 1) : int(gridDim.x);
 
-  if (warp == 0) {
-    // ------------------------------------------------------------- TMA producer
-    if (elect_one()) {
+  if (warp == 0 || warp == 10) {
+    // ------------------------------------------- TMA producers (warp 0: A tiles, warp 10: B tiles)
+    const int which = warp == 0 ? 1 : 2;
+    {
+      // The whole warp runs the loop (coordinates stay warp-uniform); one elected lane issues the instructions.
+      const bool el = elect_one();
       // One routine computes the coordinates of a k-block's boxes; `pf` = 0 issues the loads into the stage,
       // otherwise it only pulls the boxes of the operands in the mask (1 = A, 2 = B) into L2.
+      // In a pair both CTAs' loads complete on the barrier of rank 0, whose MMA thread consumes both halves.
       auto ld2 = [&](void* dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int pf) {
-        if (pf) tma_prefetch_2d(m, x, y); else tma_load_2d(dst, m, bar, x, y);
+        if (!el) return;
+        if (pf) tma_prefetch_2d(m, x, y);
+        else if (pair) tma_load_2d_pair(dst, m, mapa_shared(smem_u32(bar), 0), x, y);
+        else tma_load_2d(dst, m, bar, x, y);
       };
       auto ld3 = [&](void* dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int z, int pf) {
-        if (pf) tma_prefetch_3d(m, x, y, z); else tma_load_3d(dst, m, bar, x, y, z);
+        if (!el) return;
+        if (pf) tma_prefetch_3d(m, x, y, z);
+        else if (pair) tma_load_3d_pair(dst, m, mapa_shared(smem_u32(bar), 0), x, y, z);
+        else tma_load_3d(dst, m, bar, x, y, z);
       };
       auto issue = [&](const Tile& tl, int kb, uint8_t* sa, uint8_t* sb, uint64_t* bar, int pf) {
-        const bool doA = !pf || (pf & 1), doB = !pf || (pf & 2);
+        const bool doA = (which & 1) && (!pf || (pf & 1)), doB = (which & 2) && (!pf || (pf & 2));
         bool second = kb >= tl.kb;
         const CUtensorMap* mA = second ? &tmA2 : &tmA;
         const CUtensorMap* mB = second ? &tmB2 : &tmB;
@@ -182,14 +261,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
           if (doB) {
             int bg = p.b_grouped ? tl.g : 0;
-            if (!p.b_mn) ld3(sb, mB, bar, kk, tl.n0, bg, pf);
-            else if (p.epilogue == kSwiGLU) {
-              // B tile = [gate columns | up columns], each half from its own tensor (tmB = gate, tmB2 = up)
+            const int nb0 = tl.n0 + int(rank) * b_cols;    // first B column staged by this CTA
+            if (!p.b_mn) ld3(sb, mB, bar, kk, nb0, bg, pf);
+            else if (EPI == kSwiGLU) {
+              // B tile = [gate columns | up columns], each half from its own tensor (tmB = gate, tmB2 = up);
+              // in a pair rank 0 stages the gate half and rank 1 the up half
               int half = p.BN / 2, c0 = tl.n0 / 2;
-              for (int a = 0; a < half / 64; ++a) ld3(sb + a * 8192, &tmB, bar, c0 + a * 64, kk, bg, pf);
-              for (int a = 0; a < half / 64; ++a) ld3(sb + (half / 64 + a) * 8192, &tmB2, bar, c0 + a * 64, kk, bg, pf);
+              if (!pair) {
+                for (int a = 0; a < half / 64; ++a) ld3(sb + a * 8192, &tmB, bar, c0 + a * 64, kk, bg, pf);
+                for (int a = 0; a < half / 64; ++a) ld3(sb + (half / 64 + a) * 8192, &tmB2, bar, c0 + a * 64, kk, bg, pf);
+              } else {
+                const CUtensorMap* mh = rank ? &tmB2 : &tmB;
+                for (int a = 0; a < half / 64; ++a) ld3(sb + a * 8192, mh, bar, c0 + a * 64, kk, bg, pf);
+              }
             } else {
-              for (int a = 0; a < p.BN / 64; ++a) ld3(sb + a * 8192, mB, bar, tl.n0 + a * 64, kk, bg, pf);
+              for (int a = 0; a < b_cols / 64; ++a) ld3(sb + a * 8192, mB, bar, nb0 + a * 64, kk, bg, pf);
             }
           }
         } else {
@@ -199,61 +285,82 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
       };
       const int D = p.prefetch_dist, pf_mask = p.prefetch_ops;
-      uint32_t it = 0;
-      NB_TRACE(0);
-      for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
-        Tile tl = decode_tile(p, s_off, s_tstart, t, n_tiles);
+      uint32_t it = 0, s = 0, ph = 0;
+      int g_hint = 0;
+      const bool trace_on = p.trace != nullptr;
+      long long acc_wait = 0, acc_issue = 0;
+      if (el && which == 1) NB_TRACE(0);
+      for (int t = cta; t < total_tiles && !*abort_flag; t += n_cta) {
+        Tile tl = decode_tile(p, s_off, s_tstart, t, n_tiles, rank, g_hint);
         int nkb = tl.kb + tl.kb2;
         Tile nx = tl; int nx_nkb = 0;
-        if (D > 0 && t + int(gridDim.x) < total_tiles) {
-          nx = decode_tile(p, s_off, s_tstart, t + gridDim.x, n_tiles);
+        if (D > 0 && t + n_cta < total_tiles) {
+          { int gh = g_hint; nx = decode_tile(p, s_off, s_tstart, t + n_cta, n_tiles, rank, gh); }
           nx_nkb = nx.kb + nx.kb2;
         }
         for (int kb = 0; kb < nkb; ++kb, ++it) {
-          int s = it % stages; uint32_t ph = (it / stages) & 1;
+          long long c0 = trace_on ? clock64() : 0;
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, kTimeoutEmpty)) break;
-          if (it < 12) NB_TRACE(1 + it);
+          long long c1 = trace_on ? clock64() : 0;
+          if (trace_on && el && which == 1 && it >= 16 && it < 28) NB_TRACE(1 + it - 16);
           uint8_t* sa = smem + s * stage_bytes;
-          mbar_expect_tx(&full_bar[s], stage_bytes);
-          issue(tl, kb, sa, sa + a_bytes, &full_bar[s], 0);
-          if (D > 0) {
-            int pk = kb + D;
-            if (pk < nkb) issue(tl, pk, nullptr, nullptr, nullptr, pf_mask);
-            else if (pk - nkb < nx_nkb) issue(nx, pk - nkb, nullptr, nullptr, nullptr, pf_mask);
+          if (p.debug & 2) { if (rank == 0 && el) mbar_arrive(&full_bar[s]); }
+          else {
+            if (el && rank == 0) mbar_expect_tx(&full_bar[s], (which == 1 ? a_bytes : b_bytes) * (pair ? 2u : 1u));
+            issue(tl, kb, sa, sa + a_bytes, &full_bar[s], 0);
+            if (D > 0) {
+              int pk = kb + D;
+              if (pk < nkb) issue(tl, pk, nullptr, nullptr, nullptr, pf_mask);
+              else if (pk - nkb < nx_nkb) issue(nx, pk - nkb, nullptr, nullptr, nullptr, pf_mask);
+            }
           }
+          if (trace_on) { acc_wait += c1 - c0; acc_issue += clock64() - c1; }
+          if (++s == uint32_t(stages)) { s = 0; ph ^= 1; }
         }
       }
+      if (trace_on && el) { p.trace[blockIdx.x * 64 + 11 + 2 * which] = acc_wait; p.trace[blockIdx.x * 64 + 12 + 2 * which] = acc_issue; }
     }
   } else if (warp == 1) {
     // --------------------------------------------------------------- MMA issuer
-    const uint32_t idesc = make_idesc(BM, p.BN, p.a_mn, p.b_mn);
-    uint32_t it = 0, tile_i = 0;
-    for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
-      Tile tl = decode_tile(p, s_off, s_tstart, t, n_tiles);
-      int nkb = tl.kb + tl.kb2;
+    // One thread feeds the tensor core, so the per-k-block instruction count of this loop is what bounds the
+    // kernel: stage index, phase and the operand descriptors advance by additions only (the descriptor's
+    // address field is its low 14 bits, in 16-byte units), and all lanes poll the barrier together so that no
+    // shuffle or re-convergence sits between the wait and the issue.
+    const uint32_t idesc = make_idesc(pair ? 2 * BM : BM, p.BN, p.a_mn, p.b_mn);
+    const uint64_t a_desc0 = p.a_mn ? sdesc_mnmajor(0, 8192) : sdesc_kmajor(0);
+    const uint64_t b_desc0 = p.b_mn ? sdesc_mnmajor(0, 8192) : sdesc_kmajor(0);
+    const uint32_t a_step = p.a_mn ? (2048u >> 4) : (32u >> 4);   // descriptor increment per K = 16 step
+    const uint32_t b_step = p.b_mn ? (2048u >> 4) : (32u >> 4);
+    const uint32_t smem_enc = smem_u32(smem) >> 4, stage_enc = stage_bytes >> 4, a_enc = a_bytes >> 4;
+    const bool trace_on = p.trace != nullptr;
+    uint32_t s = 0, ph = 0, it = 0, tile_i = 0;
+    int g_hint = 0;
+    long long acc_wait = 0, acc_issue = 0, acc_commit = 0, acc_tempty = 0;
+    for (int t = cta; t < total_tiles && !*abort_flag && rank == 0; t += n_cta) {
+      Tile tl = decode_tile(p, s_off, s_tstart, t, n_tiles, 0, g_hint);
+      const int nkb = tl.kb + tl.kb2;
       if (nkb == 0) continue;            // empty reduction: epilogue writes zeros without an accumulator
-      uint32_t buf = tile_i & 1, bph = (tile_i >> 1) & 1;
+      const uint32_t buf = tile_i & 1, bph = (tile_i >> 1) & 1;
       ++tile_i;
+      long long cte = trace_on ? clock64() : 0;
+      if (!mbar_wait(&tempty_bar[buf], bph ^ 1, abort_flag, p.status, kTimeoutTmemEmpty)) break;
+      if (trace_on) acc_tempty += clock64() - cte;
+      tc_fence_after();                  // orders the epilogue's TMEM reads of this buffer before the new MMAs
+      const uint32_t d_addr = tmem_base + buf * p.BN;
       bool ok = true;
-      if (lane == 0) ok = mbar_wait(&tempty_bar[buf], bph ^ 1, abort_flag, p.status, kTimeoutTmemEmpty);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
-      tc_fence_after();
-      if (lane == 0 && tile_i <= 6) NB_TRACE(16 + 4 * (tile_i - 1));
-      uint32_t d_addr = tmem_base + buf * p.BN;
       for (int kb = 0; kb < nkb; ++kb, ++it) {
-        int s = it % stages; uint32_t ph = (it / stages) & 1;
-        if (lane == 0) ok = mbar_wait(&full_bar[s], ph, abort_flag, p.status, kTimeoutFull);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
+        long long c0 = trace_on ? clock64() : 0;
+        ok = mbar_wait(&full_bar[s], ph, abort_flag, p.status, kTimeoutFull);
         if (!ok) break;
-        if (lane == 0 && kb == 0 && tile_i <= 6) NB_TRACE(16 + 4 * (tile_i - 1) + 1);
-        uint8_t* sa = smem + s * stage_bytes;
-        uint8_t* sb = sa + a_bytes;
+        long long c1 = trace_on ? clock64() : 0;
+        if (trace_on && lane == 0 && it >= 16 && it < 28) NB_TRACE(16 + it - 16);
         if (p.mode == 1) {
           // zero k-rows past the end of the group (they belong to the next group)
           int row0 = s_off[tl.g] + (tl.kb0 + kb) * BK;
           int valid = tl.row_end - row0;
           if (valid < BK) {
+            uint8_t* sa = smem + s * stage_bytes;
+            uint8_t* sb = sa + a_bytes;
             int natoms = 2 + p.BN / 64;
             for (int a = 0; a < natoms; ++a) {
               uint8_t* base = (a < 2) ? sa + a * 8192 : sb + (a - 2) * 8192;
@@ -264,137 +371,182 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             __syncwarp();
           }
         }
-        tc_fence_after();
-        if (lane == 0) {
-          uint32_t a0 = smem_u32(sa), b0 = smem_u32(sb);
+        // operands are computed by the whole warp (warp-uniform values stay in uniform registers, which is where
+        // the MMA instruction wants them); only the instructions themselves are issued by one elected lane
+        const uint64_t ad = a_desc0 + (smem_enc + s * stage_enc);
+        const uint64_t bd = b_desc0 + (smem_enc + s * stage_enc + a_enc);
+        const uint32_t empty_addr = smem_u32(&empty_bar[s]), tfull_addr = smem_u32(&tfull_bar[buf]);
+        const uint32_t empty_peer = pair ? mapa_shared(empty_addr, 1) : 0u, tfull_peer = pair ? mapa_shared(tfull_addr, 1) : 0u;
+        if (elect_one()) {
+          if (!(p.debug & 1)) {
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            uint64_t ad = p.a_mn ? sdesc_mnmajor(a0 + k * 2048, 8192) : sdesc_kmajor(a0 + k * 32);
-            uint64_t bd = p.b_mn ? sdesc_mnmajor(b0 + k * 2048, 8192) : sdesc_kmajor(b0 + k * 32);
-            umma_bf16(d_addr, ad, bd, idesc, (kb | k) != 0);
+            for (int k = 0; k < BK / 16; ++k) {
+              if (pair) umma_bf16_pair(d_addr, ad + k * a_step, bd + k * b_step, idesc, (kb | k) != 0);
+              else umma_bf16(d_addr, ad + k * a_step, bd + k * b_step, idesc, (kb | k) != 0);
+            }
           }
-          umma_commit(&empty_bar[s]);              // stage is free once these MMAs retire
-          if (kb == nkb - 1) { umma_commit(&tfull_bar[buf]); if (tile_i <= 6) NB_TRACE(16 + 4 * (tile_i - 1) + 2); }
+          long long c2 = trace_on ? clock64() : 0;
+          // the stage is free once these MMAs retire; in a pair both CTAs' barriers are told
+          if (pair) { umma_commit_pair(empty_addr); umma_commit_pair(empty_peer); }
+          else umma_commit(&empty_bar[s]);
+          if (kb == nkb - 1) {
+            if (pair) { umma_commit_pair(tfull_addr); umma_commit_pair(tfull_peer); }
+            else umma_commit(&tfull_bar[buf]);
+          }
+          if (trace_on) {
+            acc_wait += c1 - c0; acc_issue += c2 - c1; acc_commit += clock64() - c2;
+            if (it >= 16 && it < 28) NB_TRACE(32 + it - 16);
+          }
         }
         __syncwarp();
+        if (++s == uint32_t(stages)) { s = 0; ph ^= 1; }
       }
       if (!ok) break;
     }
+    if (trace_on && acc_issue != 0) {      // only the elected lane accumulated
+      unsigned long long* tr = p.trace + blockIdx.x * 64;
+      tr[56] = acc_wait; tr[57] = acc_issue; tr[58] = acc_commit; tr[60] = it; tr[61] = acc_tempty;
+    }
   } else {
     // ----------------------------------------------------------------- epilogue
-    const int q = warp & 3;                      // TMEM lane quarter this warp may read
+    // Eight warps: warp w reads TMEM lane quarter w % 4 (its 32 rows); the two warps of a quarter split the
+    // tile's columns in alternating chunks. TMEM loads are double-buffered in registers: the load of the next
+    // chunk is in flight while the current one is converted and stored.
+    const int q = warp & 3;
+    const int grp = (warp - 2) >> 2;             // column group 0 / 1
+    uint8_t* slab = smem + uint32_t(stages) * stage_bytes + (warp - 2) * kSlabBytes;
     uint32_t tile_i = 0;
-    for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
-      Tile tl = decode_tile(p, s_off, s_tstart, t, n_tiles);
-      int nkb = tl.kb + tl.kb2;
+    int g_hint = 0;
+    const bool trace_on = p.trace != nullptr;
+    long long e_wait = 0, e_work = 0, e_decode = 0, e_t0 = 0;
+    for (int t = cta; t < total_tiles && !*abort_flag; t += n_cta) {
+      if (trace_on) e_t0 = clock64();
+      Tile tl = decode_tile(p, s_off, s_tstart, t, n_tiles, rank, g_hint);
+      const int nkb = tl.kb + tl.kb2;
       const int row = tl.m0 + q * 32 + lane;
       bool row_ok;
       long c_base;
       if (p.mode == 0) { row_ok = row < tl.row_end; c_base = long(row) * p.ldc; }
       else { row_ok = row < p.M; c_base = long(tl.g) * p.c_group_stride + long(row) * p.ldc; }
+      if (p.debug & 4) row_ok = false;           // timing experiment: no global stores
+      // the warp's 32 rows start at row_w; the first rows_w of them exist
+      const int row_w = tl.m0 + q * 32;
+      const int rows_w = (p.debug & 4) ? 0 : max(0, min(32, (p.mode == 0 ? tl.row_end : p.M) - row_w));
+      const long cw_base = (p.mode == 0 ? 0 : long(tl.g) * p.c_group_stride) + long(row_w) * p.ldc;
       uint32_t buf = 0;
       if (nkb > 0) {
         buf = tile_i & 1; uint32_t bph = (tile_i >> 1) & 1;
         ++tile_i;
-        if (!mbar_wait(&tfull_bar[buf], bph, abort_flag, p.status, kTimeoutTmemFull)) break;
+        // one lane polls (with back-off): a warp spinning on the barrier takes issue slots and shared-memory
+        // cycles from the MMA issuer that shares its scheduler
+        bool ok = true;
+        long long e_t1 = trace_on ? clock64() : 0;
+        if (lane == 0) ok = mbar_wait(&tfull_bar[buf], bph, abort_flag, p.status, kTimeoutTmemFull, 32);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
         tc_fence_after();
-        if (q == 0 && lane == 0 && tile_i <= 6) NB_TRACE(40 + 3 * (tile_i - 1));
+        if (trace_on) { long long e_t2 = clock64(); e_decode += e_t1 - e_t0; e_wait += e_t2 - e_t1; e_t0 = e_t2; }
+        if (warp == 4 && lane == 0 && tile_i <= 4) NB_TRACE(48 + 2 * (tile_i - 1));
       }
       const uint32_t taddr = tmem_base + buf * p.BN + (uint32_t(q * 32) << 16);
       const int ncols = min(p.BN, p.N - tl.n0);
-      if (p.epilogue == kSwiGLU) {
+      if (EPI == kSwiGLU) {
         const int half = p.BN / 2, h0 = tl.n0 / 2;
         const int hcols = min(half, p.N / 2 - h0);
-        for (int c = 0; c < hcols; c += 16) {
-          float g[16], u[16];
-          tmem_ld16(taddr + c, g); tmem_ld16(taddr + half + c, u);
-          tmem_ld_wait();
-          if (row_ok) {
-            uint32_t og[8], ou[8], oh[8];
+        const int nch = (hcols + 31) >> 5;       // chunks of 32 gate + 32 up columns, alternating between the groups
+        for (int j = grp; j < nch; j += 2) {
+          float g[32], u[32];
+          const int c = 32 * j;
+          if (hcols - c > 16) { tmem_ld32(taddr + c, g); tmem_ld32(taddr + half + c, u); }
+          else {
+            tmem_ld16(taddr + c, g); tmem_ld16(taddr + half + c, u);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              // round gate/up to bf16 first: the product must match silu evaluated on the stored values
-              float g0 = __bfloat162float(__float2bfloat16(g[2 * j])), g1 = __bfloat162float(__float2bfloat16(g[2 * j + 1]));
-              float u0 = __bfloat162float(__float2bfloat16(u[2 * j])), u1 = __bfloat162float(__float2bfloat16(u[2 * j + 1]));
-              float s0 = __bfloat162float(__float2bfloat16(g0 / (1.f + __expf(-g0))));
-              float s1 = __bfloat162float(__float2bfloat16(g1 / (1.f + __expf(-g1))));
-              og[j] = pack_bf16(g0, g1); ou[j] = pack_bf16(u0, u1); oh[j] = pack_bf16(s0 * u0, s1 * u1);
-            }
-            long o = long(row) * p.ldc + h0 + c;
-            int rem = hcols - c;
-            __nv_bfloat16* H = reinterpret_cast<__nv_bfloat16*>(p.C) + o;
-            __nv_bfloat16* Gp = reinterpret_cast<__nv_bfloat16*>(p.C2) + o;
-            __nv_bfloat16* Up = reinterpret_cast<__nv_bfloat16*>(p.C3) + o;
-            if (rem >= 16) {
-              reinterpret_cast<uint4*>(H)[0] = make_uint4(oh[0], oh[1], oh[2], oh[3]);
-              reinterpret_cast<uint4*>(H)[1] = make_uint4(oh[4], oh[5], oh[6], oh[7]);
-              reinterpret_cast<uint4*>(Gp)[0] = make_uint4(og[0], og[1], og[2], og[3]);
-              reinterpret_cast<uint4*>(Gp)[1] = make_uint4(og[4], og[5], og[6], og[7]);
-              reinterpret_cast<uint4*>(Up)[0] = make_uint4(ou[0], ou[1], ou[2], ou[3]);
-              reinterpret_cast<uint4*>(Up)[1] = make_uint4(ou[4], ou[5], ou[6], ou[7]);
-            } else {  // rem == 8 (all widths are multiples of 8)
-              reinterpret_cast<uint4*>(H)[0] = make_uint4(oh[0], oh[1], oh[2], oh[3]);
-              reinterpret_cast<uint4*>(Gp)[0] = make_uint4(og[0], og[1], og[2], og[3]);
-              reinterpret_cast<uint4*>(Up)[0] = make_uint4(ou[0], ou[1], ou[2], ou[3]);
-            }
+            for (int i = 16; i < 32; ++i) { g[i] = 0.f; u[i] = 0.f; }
           }
+          tmem_ld_wait();
+          uint32_t og[16], ou[16], oh[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            // round gate/up to bf16 first: the product must match silu evaluated on the stored values
+            float g0 = __bfloat162float(__float2bfloat16(g[2 * i])), g1 = __bfloat162float(__float2bfloat16(g[2 * i + 1]));
+            float u0 = __bfloat162float(__float2bfloat16(u[2 * i])), u1 = __bfloat162float(__float2bfloat16(u[2 * i + 1]));
+            float s0 = __bfloat162float(__float2bfloat16(g0 / (1.f + __expf(-g0))));
+            float s1 = __bfloat162float(__float2bfloat16(g1 / (1.f + __expf(-g1))));
+            og[i] = pack_bf16(g0, g1); ou[i] = pack_bf16(u0, u1); oh[i] = pack_bf16(s0 * u0, s1 * u1);
+          }
+          const long o = cw_base + h0 + c;
+          const int cols_ok = hcols - c;
+          store_chunk_bf16(slab, lane, oh, reinterpret_cast<__nv_bfloat16*>(p.C) + o, p.ldc, rows_w, cols_ok);
+          store_chunk_bf16(slab, lane, og, reinterpret_cast<__nv_bfloat16*>(p.C2) + o, p.ldc, rows_w, cols_ok);
+          store_chunk_bf16(slab, lane, ou, reinterpret_cast<__nv_bfloat16*>(p.C3) + o, p.ldc, rows_w, cols_ok);
         }
       } else {
         float run_max = -INFINITY, run_sum = 0.f;
-        for (int c0 = 0; c0 < ncols; c0 += 32) {
-          // 32 accumulator columns per TMEM round trip (16 when that is all that is left of the tile)
-          float v32[32];
-          if (nkb > 0) {
-            if (ncols - c0 > 16) tmem_ld32(taddr + c0, v32); else tmem_ld16(taddr + c0, v32);
-            tmem_ld_wait();
-          } else {
+        const int nch = (ncols + 31) >> 5;       // chunks of 32 columns (the last one may hold 8, 16 or 24)
+        auto load = [&](int jj, float* v) {
+          if (nkb == 0) return;
+          if (ncols - 32 * jj > 16) tmem_ld32(taddr + 32 * jj, v); else tmem_ld16(taddr + 32 * jj, v);
+        };
+        auto process = [&](float* v, int c0) {
+          const int rem = ncols - c0;            // columns of this chunk that exist: 8, 16, 24 or >= 32
+          if (EPI == kStoreBf16 || EPI == kStoreBf16Stats) {
+            if (EPI == kStoreBf16Stats) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v32[j] = 0.f;
-          }
-#pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {
-          const int c = c0 + 16 * hh;
-          float* v = v32 + 16 * hh;
-          const int rem = ncols - c;           // <= 0 (past the tile), 8 or >= 16
-          if (!row_ok || rem <= 0) continue;
-          const long o = c_base + tl.n0 + c;
-          if (p.epilogue == kStoreBf16 || p.epilogue == kStoreBf16Stats) {
-            if (p.epilogue == kStoreBf16Stats) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) if (tl.n0 + c + j >= p.n_valid) v[j] = -INFINITY;
+              for (int j = 0; j < 32; ++j) if (tl.n0 + c0 + j >= p.n_valid || j >= rem) v[j] = -INFINITY;
             }
-            uint32_t w[8];
+            uint32_t w[16];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) w[j] = pack_bf16(v[2 * j] * p.alpha, v[2 * j + 1] * p.alpha);
-            __nv_bfloat16* Cp = reinterpret_cast<__nv_bfloat16*>(p.C) + o;
-            reinterpret_cast<uint4*>(Cp)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-            if (rem >= 16) reinterpret_cast<uint4*>(Cp)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-            if (p.epilogue == kStoreBf16Stats) {
-              const int lim = rem >= 16 ? 16 : 8;
+            for (int j = 0; j < 16; ++j) w[j] = pack_bf16(v[2 * j] * p.alpha, v[2 * j + 1] * p.alpha);
+            store_chunk_bf16(slab, lane, w, reinterpret_cast<__nv_bfloat16*>(p.C) + cw_base + tl.n0 + c0, p.ldc, rows_w, rem);
+            if (EPI == kStoreBf16Stats) {
               float m = run_max;
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                float x = __bfloat162float(__float2bfloat16(v[j] * p.alpha));
-                v[j] = j < lim ? x : -INFINITY; m = fmaxf(m, v[j]);
+              for (int j = 0; j < 32; ++j) {
+                v[j] = __bfloat162float(__float2bfloat16(v[j] * p.alpha));    // statistics of the stored values
+                m = fmaxf(m, v[j]);
               }
-              float ssum = run_sum * __expf(run_max - m);
+              if (m != -INFINITY) {
+                float ssum = run_sum * __expf(run_max - m);
 #pragma unroll
-              for (int j = 0; j < 16; ++j) ssum += __expf(v[j] - m);
-              run_max = m; run_sum = ssum;
+                for (int j = 0; j < 32; ++j) ssum += __expf(v[j] - m);
+                run_max = m; run_sum = ssum;
+              }
             }
-          } else if (p.epilogue == kStoreF32) {
-            float* Cp = reinterpret_cast<float*>(p.C) + o;
-            const int lim = rem >= 16 ? 16 : 8;
+          } else if (EPI == kSwiGLUBwd) {
+            // v = dH. dGate = dH * up * s * (1 + g * (1 - s)); dUp = dH * silu(g)   (s = sigmoid(g))
+            const long oe = long(row_w) * p.lde + tl.n0 + c0;
+            uint32_t gw[16], uw[16], wg[16], wu[16];
+            load_chunk_bf16(slab, lane, gw, reinterpret_cast<const __nv_bfloat16*>(p.E1) + oe, p.lde, rows_w, rem);
+            load_chunk_bf16(slab, lane, uw, reinterpret_cast<const __nv_bfloat16*>(p.E2) + oe, p.lde, rows_w, rem);
 #pragma unroll
-            for (int j = 0; j < 16; j += 4)
-              if (j < lim) reinterpret_cast<float4*>(Cp + j)[0] = make_float4(v[j] * p.alpha, v[j + 1] * p.alpha, v[j + 2] * p.alpha, v[j + 3] * p.alpha);
-          } else if (p.epilogue == kAccumF32) {
-            if (nkb > 0) {
-              float* Cp = reinterpret_cast<float*>(p.C) + o;
-              const int lim = rem >= 16 ? 16 : 8;
+            for (int e = 0; e < 16; ++e) {
+              float r[2][2];
 #pragma unroll
-              for (int j = 0; j < 16; j += 4) {
-                if (j >= lim) break;
+              for (int h = 0; h < 2; ++h) {
+                const uint32_t gbits = h ? (gw[e] & 0xFFFF0000u) : (gw[e] << 16);
+                const uint32_t ubits = h ? (uw[e] & 0xFFFF0000u) : (uw[e] << 16);
+                float gg = __uint_as_float(gbits), uu = __uint_as_float(ubits);
+                float dh = __bfloat162float(__float2bfloat16(v[2 * e + h]));
+                float sg = 1.f / (1.f + __expf(-gg));
+                r[h][0] = dh * uu * sg * (1.f + gg * (1.f - sg));
+                r[h][1] = dh * gg * sg;
+              }
+              wg[e] = pack_bf16(r[0][0], r[1][0]); wu[e] = pack_bf16(r[0][1], r[1][1]);
+            }
+            const long o = cw_base + tl.n0 + c0;
+            store_chunk_bf16(slab, lane, wg, reinterpret_cast<__nv_bfloat16*>(p.C) + o, p.ldc, rows_w, rem);
+            store_chunk_bf16(slab, lane, wu, reinterpret_cast<__nv_bfloat16*>(p.C2) + o, p.ldc, rows_w, rem);
+          } else if (row_ok) {
+            // fp32 outputs (weight gradients): one row per lane
+            float* Cp = reinterpret_cast<float*>(p.C) + c_base + tl.n0 + c0;
+            if (EPI == kStoreF32) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                if (j < rem) reinterpret_cast<float4*>(Cp + j)[0] = make_float4(v[j] * p.alpha, v[j + 1] * p.alpha, v[j + 2] * p.alpha, v[j + 3] * p.alpha);
+            } else if (nkb > 0) {                // kAccumF32
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                if (j >= rem) break;
                 float4 add = make_float4(v[j] * p.alpha, v[j + 1] * p.alpha, v[j + 2] * p.alpha, v[j + 3] * p.alpha);
                 if (p.splits > 1) {
                   atomicAdd(reinterpret_cast<float4*>(Cp + j), add);
@@ -404,58 +556,57 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 }
               }
             }
-          } else if (p.epilogue == kSwiGLUBwd) {
-            // v = dH. dGate = dH * up * s * (1 + g * (1 - s)); dUp = dH * silu(g)   (s = sigmoid(g))
-            const long oe = long(row) * p.lde + tl.n0 + c;
-            const __nv_bfloat16* Gp = reinterpret_cast<const __nv_bfloat16*>(p.E1) + oe;
-            const __nv_bfloat16* Up = reinterpret_cast<const __nv_bfloat16*>(p.E2) + oe;
-            __nv_bfloat16* dG = reinterpret_cast<__nv_bfloat16*>(p.C) + o;
-            __nv_bfloat16* dU = reinterpret_cast<__nv_bfloat16*>(p.C2) + o;
-            const int lim = rem >= 16 ? 16 : 8;
-#pragma unroll
-            for (int j = 0; j < 16; j += 8) {
-              if (j >= lim) break;
-              uint4 gq = reinterpret_cast<const uint4*>(Gp + j)[0], uq = reinterpret_cast<const uint4*>(Up + j)[0];
-              const __nv_bfloat16* gb = reinterpret_cast<const __nv_bfloat16*>(&gq);
-              const __nv_bfloat16* ub = reinterpret_cast<const __nv_bfloat16*>(&uq);
-              uint32_t wg[4], wu[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                float r[2][2];
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                  float gg = __bfloat162float(gb[2 * e + h]), uu = __bfloat162float(ub[2 * e + h]);
-                  float dh = __bfloat162float(__float2bfloat16(v[j + 2 * e + h]));
-                  float sg = 1.f / (1.f + __expf(-gg));
-                  r[h][0] = dh * uu * sg * (1.f + gg * (1.f - sg));
-                  r[h][1] = dh * gg * sg;
-                }
-                wg[e] = pack_bf16(r[0][0], r[1][0]); wu[e] = pack_bf16(r[0][1], r[1][1]);
-              }
-              reinterpret_cast<uint4*>(dG + j)[0] = make_uint4(wg[0], wg[1], wg[2], wg[3]);
-              reinterpret_cast<uint4*>(dU + j)[0] = make_uint4(wu[0], wu[1], wu[2], wu[3]);
-            }
           }
+        };
+        float va[32], vb[32];
+        if (nkb == 0) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) { va[j] = 0.f; vb[j] = 0.f; }
         }
-          }
-        if (p.epilogue == kStoreBf16Stats && row_ok) {
-          float2* part = reinterpret_cast<float2*>(p.C2) + long(row) * n_tiles + (tl.n0 / p.BN);
+        int j = grp;
+        if (j < nch) load(j, va);
+        while (j < nch) {
+          if (nkb > 0) tmem_ld_wait32(va);
+          if (j + 2 < nch) load(j + 2, vb);
+          process(va, 32 * j);
+          j += 2;
+          if (j >= nch) break;
+          if (nkb > 0) tmem_ld_wait32(vb);
+          if (j + 2 < nch) load(j + 2, va);
+          process(vb, 32 * j);
+          j += 2;
+        }
+        if (EPI == kStoreBf16Stats && row_ok) {
+          // one (max, sum-exp) partial per row, n-tile and column group
+          float2* part = reinterpret_cast<float2*>(p.C2) + (long(row) * n_tiles + (tl.n0 / p.BN)) * 2 + grp;
           *part = make_float2(run_max, run_sum);
         }
       }
       if (nkb > 0) {
         tc_fence_before();
         __syncwarp();
-        if (q == 0 && lane == 0 && tile_i <= 6) NB_TRACE(40 + 3 * (tile_i - 1) + 1);
-        if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+        if (warp == 4 && lane == 0 && tile_i <= 4) NB_TRACE(48 + 2 * (tile_i - 1) + 1);
+        if (lane == 0) {
+          if (pair) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[buf]), 0));
+          else mbar_arrive(&tempty_bar[buf]);
+        }
+        if (trace_on) e_work += clock64() - e_t0;
       }
+    }
+    if (trace_on && warp == 4 && lane == 0) {
+      unsigned long long* tr = p.trace + blockIdx.x * 64;
+      tr[44] = e_decode; tr[45] = e_wait; tr[46] = e_work; tr[47] = tile_i;
     }
   }
 
   // ----------------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, tmem_cols); }
+  if (pair) cluster_sync_all();     // neither CTA leaves (or frees TMEM) while its peer may still signal or read it
+  if (warp == 1) {
+    tc_fence_after();
+    if (pair) tmem_dealloc_pair(tmem_base, tmem_cols); else tmem_dealloc(tmem_base, tmem_cols);
+  }
 }
 
 }  // namespace nb
@@ -525,6 +676,8 @@ struct NbGemmArgs {
   int prefetch_dist;        // L2 look-ahead of the producer in k-blocks (0 = off)
   int prefetch_ops;         // 1 = A, 2 = B, 3 = both
   int max_stages;           // 0 = as many as fit
+  int pair;                 // mode 0 only: 256-row tiles on CTA pairs (cta_group::2), each CTA stages half of B
+  int debug;                // timing experiments: 1 = no MMAs, 2 = no loads (outputs are garbage)
 };
 
 // Returns 0 on success, a negative code for bad arguments / map failures, or a CUDA error code.
@@ -536,6 +689,8 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
   if (a->b_mn && a->BN % 64) return -4;
   if (a->mode == 1 && !(a->a_mn && a->b_mn)) return -5;
   if (a->epilogue == kSwiGLU && (a->BN % 128 || !a->b_mn)) return -6;
+  const int pair = a->pair ? 1 : 0;
+  if (pair && (a->mode != 0 || a->a_mn || a->BN % 16 || (a->b_mn && a->BN % 128))) return -8;
   if (!g_num_sms) {
     int dev; cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
@@ -556,7 +711,7 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
     }
     long dims[3] = {o.cols, o.rows, o.groups > 0 ? o.groups : 1};
     long st[2] = {o.ld, o.group_stride > 0 ? o.group_stride : o.rows * o.ld};
-    int box_k[3] = {BK, a->BN, 1};      // K-major B [N, K]: 64 k x BN rows
+    int box_k[3] = {BK, pair ? a->BN / 2 : a->BN, 1};   // K-major B [N, K]: 64 k x (this CTA's) rows
     int box_mn[3] = {64, BK, 1};        // MN-major B [K, N]: 64 n x 64 k-rows
     return make_map(m, o.ptr, 3, dims, st, a->b_mn ? box_mn : box_k);
   };
@@ -575,28 +730,49 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
   p.trace = a->trace;
   p.prefetch_dist = a->prefetch_dist > 0 ? a->prefetch_dist : 0;
   p.prefetch_ops = a->prefetch_ops & 3;
+  p.pair = pair;
+  p.debug = a->debug;
   p.splits = (a->mode == 1 && a->epilogue == kAccumF32 && a->splits > 1) ? a->splits : 1;
 
   const int n_tiles = (a->N + a->BN - 1) / a->BN;
+  // mode 0: max_m_tiles bounds the row tiles over all groups (tiles of 256 rows for pairs)
   long tiles = a->mode == 0 ? long(a->max_m_tiles) * n_tiles
                             : long(a->groups) * ((a->M + BM - 1) / BM) * n_tiles * p.splits;
   if (tiles <= 0) return 0;
-  const uint32_t stage_bytes = BM * BK * 2 + a->BN * BK * 2;
-  int stages = int((220 * 1024) / stage_bytes);   // 227 KB per CTA minus barriers, offsets and alignment slack
+  const uint32_t stage_bytes = BM * BK * 2 + (pair ? a->BN / 2 : a->BN) * BK * 2;
+  int stages = int((200 * 1024) / stage_bytes);   // 227 KB per CTA minus epilogue slabs, barriers, offsets, alignment slack
   if (stages > 8) stages = 8;
   if (a->max_stages > 0 && stages > a->max_stages) stages = a->max_stages;
   if (stages < 2) return -7;
-  size_t smem = size_t(stages) * stage_bytes + 1024;
-  static size_t configured = 0;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+  size_t smem = size_t(stages) * stage_bytes + 1024 + 8 * kSlabBytes;
+  typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams, int);
+  static const KernelFn kernels[2][6] = {
+      {gemm_kernel<0, 0>, gemm_kernel<0, 1>, gemm_kernel<0, 2>, gemm_kernel<0, 3>, gemm_kernel<0, 4>, gemm_kernel<0, 5>},
+      {gemm_kernel<1, 0>, gemm_kernel<1, 1>, gemm_kernel<1, 2>, gemm_kernel<1, 3>, gemm_kernel<1, 4>, gemm_kernel<1, 5>}};
+  if (a->epilogue < 0 || a->epilogue > 5) return -9;
+  const KernelFn kernel = kernels[pair][a->epilogue];
+  static size_t configured[2][6] = {{0, 0, 0, 0, 0, 0}, {0, 0, 0, 0, 0, 0}};
+  if (smem > configured[pair][a->epilogue]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return int(e);
-    configured = smem;
+    configured[pair][a->epilogue] = smem;
   }
   int sms = a->sms > 0 ? a->sms : g_num_sms;
-  int grid = int(tiles < sms ? tiles : sms);
-  gemm_kernel<<<grid, 192, smem, stream>>>(tmA, tmB, tmA2, tmB2, p, stages);
-  return int(cudaGetLastError());
+  if (!pair) {
+    int grid = int(tiles < sms ? tiles : sms);
+    kernel<<<grid, 352, smem, stream>>>(tmA, tmB, tmA2, tmB2, p, stages);
+    return int(cudaGetLastError());
+  }
+  int pairs = sms / 2;
+  if (tiles < pairs) pairs = int(tiles);
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(352); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return int(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmA2, tmB2, p, stages));
 }
 
 }  // extern "C"

@@ -33,7 +33,7 @@ class GemmArgs(C.Structure):
         ("alpha", C.c_float), ("n_valid", C.c_int), ("splits", C.c_int), ("status", C.c_void_p),
         ("max_m_tiles", C.c_int),
         ("sms", C.c_int), ("trace", C.c_void_p),
-        ("prefetch_dist", C.c_int), ("prefetch_ops", C.c_int), ("max_stages", C.c_int),
+        ("prefetch_dist", C.c_int), ("prefetch_ops", C.c_int), ("max_stages", C.c_int), ("pair", C.c_int), ("debug", C.c_int),
     ]
 
 

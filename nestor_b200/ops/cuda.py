@@ -329,13 +329,13 @@ class _HeadCE(torch.autograd.Function):
         dw = torch.empty(V, d, dtype=torch.float32, device=dev) if need_grad else None
         chunk = min(chunk_rows, T)
         logits = torch.empty(chunk, ld, dtype=BF16, device=dev)
-        part = torch.empty(chunk, nt, 2, dtype=torch.float32, device=dev)
+        part = torch.empty(chunk, nt * G.STATS_PARTS, 2, dtype=torch.float32, device=dev)
         L = _L()
         for i, a in enumerate(range(0, T, chunk)):
             n = min(chunk, T - a)
             G.gemm_rows(hb[a : a + n], weight, out=logits[:n], epilogue=G.STORE_BF16_STATS, alpha=multiplier, bn=bn,
                         extra_out=(part,), n=ld, n_valid=V)
-            _ck(L.nb_ce_grad(logits.data_ptr(), ld, V, part.data_ptr(), nt, targets[a : a + n].data_ptr(), ignore_index,
+            _ck(L.nb_ce_grad(logits.data_ptr(), ld, V, part.data_ptr(), nt * G.STATS_PARTS, targets[a : a + n].data_ptr(), ignore_index,
                              losses[a : a + n].data_ptr(), n, _st()), "ce_grad")
             if need_grad:
                 dl = logits[:n, :V] if ld == V else torch.as_strided(logits, (n, V), (ld, 1))

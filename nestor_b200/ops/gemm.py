@@ -18,11 +18,18 @@ from torch import Tensor
 from nestor_b200.ops import _lib
 
 STORE_BF16, STORE_F32, ACCUM_F32, SWIGLU, SWIGLU_BWD, STORE_BF16_STATS = range(6)
+# STORE_BF16_STATS writes this many (max, sum-exp) partials per row and n-tile: extra_out[0] is [rows, n_tiles * STATS_PARTS, 2]
+STATS_PARTS = 2
 
 # Producer tuning (see csrc/gemm.cu): L2 look-ahead in k-blocks (off: measured slower, the TMA issue rate is the
 # limit, not DRAM latency), and a cap on pipeline stages (0 = all that fit).
 PREFETCH_DIST = int(os.environ.get("NESTOR_B200_GEMM_PREFETCH", "0"))
 MAX_STAGES = int(os.environ.get("NESTOR_B200_GEMM_STAGES", "0"))
+# CTA pairs: 256-row tiles where each CTA of a 2-CTA cluster stages half of B (cta_group::2 MMAs). The L2 -> SM
+# traffic per FLOP drops by the B half, which is what bounds these shapes. "auto" uses pairs for big row counts.
+PAIR = os.environ.get("NESTOR_B200_GEMM_PAIR", "auto")
+_PAIR_MIN_ROWS = 4096
+DEBUG = 0   # kernel timing experiments (see csrc/gemm.cu); never set outside of them
 _L2_RESIDENT_BYTES = 48 << 20    # a shared B operand smaller than this stays in L2 without help
 
 
@@ -59,7 +66,8 @@ def _launch(args: _lib.GemmArgs) -> None:
 def gemm_rows(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: int = 1, b_mn: bool = False,
               out: Tensor | None = None, epilogue: int = STORE_BF16, alpha: float = 1.0, bn: int | None = None,
               A2: Tensor | None = None, B2: Tensor | None = None, extra_out: tuple = (), extra_in: tuple = (),
-              n: int | None = None, n_valid: int = 0, sms: int = 0, trace: Tensor | None = None) -> Tensor:
+              n: int | None = None, n_valid: int = 0, sms: int = 0, trace: Tensor | None = None,
+              pair: bool | None = None) -> Tensor:
     """Row-grouped GEMM.
 
     ``A [rows, K]``; ``B`` is ``[G, N, K]`` (K-major) or ``[G, K, N]`` (``b_mn``) — 2-D for a
@@ -77,8 +85,20 @@ def gemm_rows(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: in
     swiglu = epilogue == SWIGLU
     if swiglu:
         N = 2 * B.shape[-1]
+    if pair is None:
+        # pairs pay off when the main loop dominates (long K) and the tile is wide; short-K products are bound by
+        # the epilogue, where 256-row tiles only add masked rows at group ends
+        wide = swiglu or (bn or (N if b_mn else pick_bn(N))) >= 192
+        pair = PAIR == "1" or (PAIR == "auto" and rows >= _PAIR_MIN_ROWS and K >= 512 and wide and (not b_mn or swiglu or N >= 256))
     if bn is None:
-        bn = 128 if swiglu else pick_bn(N, mult=64 if b_mn else 16)
+        if pair:
+            bn = 256 if swiglu else pick_bn(N, mult=128 if b_mn else 16)
+        else:
+            bn = 128 if swiglu else pick_bn(N, mult=64 if b_mn else 16)
+    if pair and (bn % 16 or (b_mn and bn % 128)):
+        pair = False
+        if swiglu:
+            bn = 128
     dev = A.device
     if out is None:
         dt = torch.float32 if epilogue in (STORE_F32, ACCUM_F32) else torch.bfloat16
@@ -103,7 +123,9 @@ def gemm_rows(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: in
     a.alpha = alpha
     a.n_valid = n_valid
     a.status = _lib.status_word(dev).data_ptr()
-    a.max_m_tiles = -(-rows // 128) + groups
+    a.pair = int(pair)
+    a.debug = DEBUG
+    a.max_m_tiles = -(-rows // (256 if pair else 128)) + groups
     a.sms = sms
     a.trace = trace.data_ptr() if trace is not None else None
     # A is streamed once per n-tile pass; B (weights) is re-read by every m-tile and only needs help when it is large

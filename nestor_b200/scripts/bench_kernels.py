@@ -27,13 +27,14 @@ def peaks() -> tuple[float, float, str]:
 
 
 _flush = None
+WARMUP = 3
 
 
 def timed(fn, reps: int, flush: bool = True) -> float:
     global _flush
     if flush and _flush is None:
         _flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device="cuda")
-    for _ in range(3):
+    for _ in range(WARMUP):
         fn()
     torch.cuda.synchronize()
     total = 0.0
@@ -100,7 +101,7 @@ def case_gemm(reps: int, small: bool = False) -> None:
         return
     V, ld, ch = 100263, 100264, 4096
     Hd, W = torch.randn(ch, d, device="cuda").to(BF), torch.randn(V, d, device="cuda").to(BF)
-    lg, part = torch.empty(ch, ld, device="cuda", dtype=BF), torch.empty(ch, 392, 2, device="cuda")
+    lg, part = torch.empty(ch, ld, device="cuda", dtype=BF), torch.empty(ch, 392 * G.STATS_PARTS, 2, device="cuda")
     report("head logits + softmax statistics [4096x640]x[100263,640]", timed(lambda: G.gemm_rows(
         Hd, W, out=lg, epilogue=G.STORE_BF16_STATS, alpha=0.125, bn=256, extra_out=(part,), n=ld, n_valid=V), reps), 2.0 * ch * d * V)
     A, B = torch.randn(8192, 8192, device="cuda").to(BF), torch.randn(8192, 8192, device="cuda").to(BF)
@@ -142,7 +143,10 @@ def main(argv: list[str] | None = None) -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("cases", nargs="*", default=["gemm", "flash", "depth"])
     ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3, help="untimed launches per shape (0 under a profiler: one launch per shape)")
     a = ap.parse_args(argv)
+    global WARMUP
+    WARMUP = a.warmup
     torch.manual_seed(0)
     for c in a.cases:
         if c == "small":

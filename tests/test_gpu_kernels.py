@@ -90,7 +90,7 @@ def test_gemm_stats_epilogue_gives_logsumexp():
     h, W = torch.randn(T, d, device="cuda").to(BF), (torch.randn(V, d, device="cuda") * 0.1).to(BF)
     nt = -(-ld // 256)
     logits = torch.empty(T, ld, device="cuda", dtype=BF)
-    part = torch.zeros(T, nt, 2, device="cuda")
+    part = torch.zeros(T, nt * G.STATS_PARTS, 2, device="cuda")
     G.gemm_rows(h, W, out=logits, epilogue=G.STORE_BF16_STATS, alpha=0.125, bn=256, extra_out=(part,), n=ld, n_valid=V)
     m = part[..., 0].max(1).values
     lse = m + torch.log((part[..., 1] * torch.exp(part[..., 0] - m[:, None])).sum(1))
