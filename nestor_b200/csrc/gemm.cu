@@ -56,6 +56,7 @@ struct GemmParams {
   int prefetch_dist;           // producer pulls k-block (i + dist) into L2 while loading k-block i (0 = off)
   int prefetch_ops;            // operands to prefetch: 1 = A, 2 = B, 3 = both
   int pair;                    // mode 0: CTA pairs (cluster of 2) run 256-row tiles with cta_group::2 MMAs
+  int a_atoms, b_atoms;        // MN-major operand read through an "atom" map: one TMA instruction per k-block
   int debug;                   // timing experiments only (results are garbage): 1 = issue no MMAs, 2 = issue no loads, 4 = store nothing
 };
 
@@ -248,6 +249,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         else if (pair) tma_load_3d_pair(dst, m, mapa_shared(smem_u32(bar), 0), x, y, z);
         else tma_load_3d(dst, m, bar, x, y, z);
       };
+      auto ld4 = [&](void* dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int z, int w, int pf) {
+        if (!el || pf) return;
+        if (pair) tma_load_4d_pair(dst, m, mapa_shared(smem_u32(bar), 0), x, y, z, w);
+        else tma_load_4d(dst, m, bar, x, y, z, w);
+      };
       auto issue = [&](const Tile& tl, int kb, uint8_t* sa, uint8_t* sb, uint64_t* bar, int pf) {
         const bool doA = (which & 1) && (!pf || (pf & 1)), doB = (which & 2) && (!pf || (pf & 2));
         bool second = kb >= tl.kb;
@@ -263,7 +269,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             int bg = p.b_grouped ? tl.g : 0;
             const int nb0 = tl.n0 + int(rank) * b_cols;    // first B column staged by this CTA
             if (!p.b_mn) ld3(sb, mB, bar, kk, nb0, bg, pf);
-            else if (EPI == kSwiGLU) {
+            else if (p.b_atoms) {
+              // atom map [64, K rows, column atoms, groups]: the whole B stage is one box
+              if (EPI == kSwiGLU) {
+                int half = p.BN / 2, c0 = tl.n0 / 2;
+                if (!pair) {
+                  ld4(sb, &tmB, bar, 0, kk, c0 / 64, bg, pf);
+                  ld4(sb + (half / 64) * 8192, &tmB2, bar, 0, kk, c0 / 64, bg, pf);
+                } else ld4(sb, rank ? &tmB2 : &tmB, bar, 0, kk, c0 / 64, bg, pf);
+              } else ld4(sb, mB, bar, 0, kk, nb0 / 64, bg, pf);
+            } else if (EPI == kSwiGLU) {
               // B tile = [gate columns | up columns], each half from its own tensor (tmB = gate, tmB2 = up);
               // in a pair rank 0 stages the gate half and rank 1 the up half
               int half = p.BN / 2, c0 = tl.n0 / 2;
@@ -280,8 +295,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
         } else {
           int row = s_off[tl.g] + (tl.kb0 + kb) * BK;     // reduction over the group's rows; operands are MN-major
-          if (doA) { ld2(sa, mA, bar, tl.m0, row, pf); ld2(sa + 8192, mA, bar, tl.m0 + 64, row, pf); }
-          if (doB) for (int a = 0; a < p.BN / 64; ++a) ld2(sb + a * 8192, mB, bar, tl.n0 + a * 64, row, pf);
+          if (doA) {
+            if (p.a_atoms) { if (!pf) ld3(sa, mA, bar, 0, row, tl.m0 / 64, 0); }
+            else { ld2(sa, mA, bar, tl.m0, row, pf); ld2(sa + 8192, mA, bar, tl.m0 + 64, row, pf); }
+          }
+          if (doB) {
+            if (p.b_atoms) { if (!pf) ld3(sb, mB, bar, 0, row, tl.n0 / 64, 0); }
+            else for (int a = 0; a < p.BN / 64; ++a) ld2(sb + a * 8192, mB, bar, tl.n0 + a * 64, row, pf);
+          }
         }
       };
       const int D = p.prefetch_dist, pf_mask = p.prefetch_ops;
@@ -318,7 +339,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if (++s == uint32_t(stages)) { s = 0; ph ^= 1; }
         }
       }
-      if (trace_on && el) { p.trace[blockIdx.x * 64 + 11 + 2 * which] = acc_wait; p.trace[blockIdx.x * 64 + 12 + 2 * which] = acc_issue; }
+      if (trace_on && el) { const int o = which == 1 ? 13 : 62; p.trace[blockIdx.x * 64 + o] = acc_wait; p.trace[blockIdx.x * 64 + o + 1] = acc_issue; }
     }
   } else if (warp == 1) {
     // --------------------------------------------------------------- MMA issuer
@@ -632,12 +653,12 @@ EncodeFn encode_fn() {
   return fn;
 }
 
-// bf16 tensor of rank 2 or 3 (dims innermost-first), strides in elements for dims 1.. (innermost is contiguous).
+// bf16 tensor of rank 2 to 4 (dims innermost-first), strides in elements for dims 1.. (innermost is contiguous).
 int make_map(CUtensorMap* m, const void* base, int rank, const long* dims, const long* strides_elems,
              const int* box) {
   EncodeFn fn = encode_fn();
   if (!fn) return 1;
-  cuuint64_t gd[3]; cuuint64_t gs[2]; cuuint32_t bx[3]; cuuint32_t es[3] = {1, 1, 1};
+  cuuint64_t gd[4]; cuuint64_t gs[3]; cuuint32_t bx[4]; cuuint32_t es[4] = {1, 1, 1, 1};
   for (int i = 0; i < rank; ++i) { gd[i] = cuuint64_t(dims[i]); bx[i] = cuuint32_t(box[i]); }
   for (int i = 0; i + 1 < rank; ++i) gs[i] = cuuint64_t(strides_elems[i]) * 2;
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, cuuint32_t(rank), const_cast<void*>(base), gd, gs, bx, es,
@@ -697,7 +718,19 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
   }
   CUtensorMap tmA, tmB, tmA2, tmB2;
   memset(&tmA2, 0, sizeof(tmA2)); memset(&tmB2, 0, sizeof(tmB2));
+  // An MN-major operand [k rows, cols] whose row pitch covers whole 64-column atoms can be viewed as
+  // [64, k rows, atoms]: one box then fills every atom of a stage (atom-major in shared memory, as the MMA
+  // descriptors expect). Columns past `cols` inside the last atom are whatever the pitch padding holds; they only
+  // reach output rows / columns that the epilogue masks. Atoms past the last one are zero-filled.
+  auto atoms_ok = [&](const NbOperand& o) { return o.ptr != nullptr && o.ld >= ((o.cols + 63) / 64) * 64; };
+  const int a_atoms = a->mode == 1 && atoms_ok(a->A);
+  const int b_atoms = (a->mode == 1 || a->b_mn) && atoms_ok(a->B) && (a->epilogue != kSwiGLU || atoms_ok(a->B2));
   auto map_a = [&](CUtensorMap* m, const NbOperand& o) -> int {
+    if (a_atoms) {
+      long dims[3] = {64, o.rows, (o.cols + 63) / 64}; long st[2] = {o.ld, 64};
+      int box[3] = {64, BK, 2};
+      return make_map(m, o.ptr, 3, dims, st, box);
+    }
     long dims[2] = {o.cols, o.rows}; long st[1] = {o.ld};
     int box_k[2] = {BK, BM};            // K-major: 64 k x 128 rows
     int box_mn[2] = {64, BK};           // MN-major: 64 m x 64 k-rows
@@ -705,9 +738,21 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
   };
   auto map_b = [&](CUtensorMap* m, const NbOperand& o) -> int {
     if (a->mode == 1) {
+      if (b_atoms) {
+        long dims[3] = {64, o.rows, (o.cols + 63) / 64}; long st[2] = {o.ld, 64};
+        int box[3] = {64, BK, a->BN / 64};
+        return make_map(m, o.ptr, 3, dims, st, box);
+      }
       long dims[2] = {o.cols, o.rows}; long st[1] = {o.ld};
       int box[2] = {64, BK};
       return make_map(m, o.ptr, 2, dims, st, box);
+    }
+    if (b_atoms) {
+      const int cols_cta = pair ? a->BN / 2 : a->BN;
+      long dims[4] = {64, o.rows, (o.cols + 63) / 64, o.groups > 0 ? o.groups : 1};
+      long st[3] = {o.ld, 64, o.group_stride > 0 ? o.group_stride : o.rows * o.ld};
+      int box[4] = {64, BK, (a->epilogue == kSwiGLU ? (pair ? a->BN / 2 : a->BN / 2) : cols_cta) / 64, 1};
+      return make_map(m, o.ptr, 4, dims, st, box);
     }
     long dims[3] = {o.cols, o.rows, o.groups > 0 ? o.groups : 1};
     long st[2] = {o.ld, o.group_stride > 0 ? o.group_stride : o.rows * o.ld};
@@ -731,6 +776,7 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
   p.prefetch_dist = a->prefetch_dist > 0 ? a->prefetch_dist : 0;
   p.prefetch_ops = a->prefetch_ops & 3;
   p.pair = pair;
+  p.a_atoms = a_atoms; p.b_atoms = b_atoms;
   p.debug = a->debug;
   p.splits = (a->mode == 1 && a->epilogue == kAccumF32 && a->splits > 1) ? a->splits : 1;
 

@@ -339,7 +339,9 @@ __global__ void depth_read_norm_bwd_kernel(SourceList src, GradList dsrc, int n,
                                            const float* __restrict__ stats, const float* __restrict__ rstd_in,
                                            const __nv_bfloat16* __restrict__ dn, const float* __restrict__ dh_in,
                                            float* __restrict__ dquery, float* __restrict__ dgains,
-                                           float* __restrict__ dgamma, int T, int d) {
+                                           float* __restrict__ dgamma, int T, int d, unsigned long long acc_mask) {
+  // bit i of acc_mask: the gradient of source i is added to what dsrc[i] already holds (a buffer shared by every
+  // reader of that source) instead of overwriting it
   __shared__ float s_w[4][kMaxSources], s_t[4][kMaxSources];
   const int lane = threadIdx.x, wy = threadIdx.y;
   const int nchunk = d / 4;
@@ -455,8 +457,10 @@ __global__ void depth_read_norm_bwd_kernel(SourceList src, GradList dsrc, int n,
         int c = lane + 32 * v;
         if (c < nchunk) {
           float4 x = s[c];
-          o[c] = make_float4(a * dh[v].x + du * qv[v].x + cs * x.x, a * dh[v].y + du * qv[v].y + cs * x.y,
-                             a * dh[v].z + du * qv[v].z + cs * x.z, a * dh[v].w + du * qv[v].w + cs * x.w);
+          float4 r4 = make_float4(a * dh[v].x + du * qv[v].x + cs * x.x, a * dh[v].y + du * qv[v].y + cs * x.y,
+                                  a * dh[v].z + du * qv[v].z + cs * x.z, a * dh[v].w + du * qv[v].w + cs * x.w);
+          if ((acc_mask >> i) & 1ull) { float4 old = o[c]; r4.x += old.x; r4.y += old.y; r4.z += old.z; r4.w += old.w; }
+          o[c] = r4;
           gq[v].x += du * x.x; gq[v].y += du * x.y; gq[v].z += du * x.z; gq[v].w += du * x.w;
         }
       }
@@ -485,7 +489,7 @@ __global__ void depth_read_norm_bwd_kernel(SourceList src, GradList dsrc, int n,
 extern "C" int nb_depth_read_norm_bwd(const float* const* sources, float* const* dsources, int n, const float* query,
                                       const float* gains, const float* gamma, const float* stats, const float* rstd,
                                       const void* dn, const float* dh, float* dquery, float* dgains, float* dgamma, int T,
-                                      int d, cudaStream_t st) {
+                                      int d, unsigned long long acc_mask, cudaStream_t st) {
   if (n < 1 || n > nb::kMaxSources || d % 4) return -1;
   nb::SourceList sl; nb::GradList gl;
   for (int i = 0; i < n; ++i) { sl.ptr[i] = sources[i]; gl.ptr[i] = dsources[i]; }
@@ -494,7 +498,7 @@ extern "C" int nb_depth_read_norm_bwd(const float* const* sources, float* const*
   if (blocks > 148 * 8) blocks = 148 * 8;
   int nv = (d / 4 + 31) / 32;
 #define NB_DRB(NV) nb::depth_read_norm_bwd_kernel<NV><<<blocks, block, 0, st>>>(sl, gl, n, query, gains, gamma, stats, rstd, \
-      (const __nv_bfloat16*)dn, dh, dquery, dgains, dgamma, T, d)
+      (const __nv_bfloat16*)dn, dh, dquery, dgains, dgamma, T, d, acc_mask)
   if (nv <= 1) NB_DRB(1); else if (nv <= 2) NB_DRB(2); else if (nv <= 4) NB_DRB(4); else if (nv <= 5) NB_DRB(5);
   else if (nv <= 8) NB_DRB(8); else if (nv <= 10) NB_DRB(10); else return -2;
 #undef NB_DRB

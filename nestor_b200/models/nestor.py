@@ -107,12 +107,9 @@ class ExpertPool(nn.Module):
         priv_scores = scores[:, s.P : s.P + s.G * s.Q].reshape(T, s.G, s.Q)
         path_logits = scores[:, s.P + s.G * s.Q :]
         pub_idx, pub_gate = ops.route_topk(pub_scores, self.public_router.choice_bias, s.k_p, "renorm")
-        col = idx.long()                                                     # [T, k] selected columns
-        sel_scores = priv_scores.gather(1, col.unsqueeze(-1).expand(-1, -1, s.Q))       # [T, k, Q]
-        sel_bias = self.private_bias()[col]                                  # [T, k, Q]
-        priv_idx, priv_gate = ops.route_topk(sel_scores, sel_bias, s.k_q, s.private_gate)  # [T, k, k_q]
-        priv_ids = (col.unsqueeze(-1) * s.Q + priv_idx).reshape(T, s.k * s.k_q)
-        priv_w = (priv_gate.to(cd) * gates.to(cd).unsqueeze(-1)).reshape(T, s.k * s.k_q)
+        # every (token, selected column) pair picks k_q of that column's Q private experts
+        priv_ids, priv_w, priv_idx = ops.route_selected(priv_scores, self.private_bias(), idx, gates, s.k_q,
+                                                        s.private_gate, cd)
         path = torch.softmax(path_logits.float(), dim=-1)
 
         pub_plan = ops.build_expert_plan(pub_idx, s.P)
@@ -121,7 +118,8 @@ class ExpertPool(nn.Module):
         priv_plan = ops.build_expert_plan(priv_ids, s.G * s.Q)
         private = ops.expert_bank(n, priv_plan, priv_w, W(self, self.stacked_private.w_up),
                                   W(self, self.stacked_private.w_gate), W(self, self.stacked_private.w_down), cd, group=s.k_q)
-        aux = {"public_idx": pub_idx, "private_idx": priv_idx, "columns": idx}
+        aux = {"public_idx": pub_idx, "private_idx": priv_idx, "columns": idx,
+               "public_offsets": pub_plan.offsets, "private_offsets": priv_plan.offsets}
         return public[:, 0], private, path, aux
 
 
@@ -306,6 +304,7 @@ class Nestor(nn.Module):
                 noises: list[Tensor | None] | None = None) -> tuple[Tensor, dict]:
         """``x0 [T, d]`` fp32 embeddings -> normalised head input ``[T, d]`` in ``cd`` + aux."""
 
+        x0 = ops.grad_sink(x0)   # depth sources are read by every later sublayer: their gradients share a buffer
         narrow = [x0]            # what sublayer reads see: embedding + completed aggregates
         wide = [x0]              # what the head read sees: every export
         x = x0
@@ -313,6 +312,8 @@ class Nestor(nn.Module):
         for i, block in enumerate(self.blocks):
             exports, x, a = block(x, narrow, B, S, cd, pos, self.column_mode,
                                   None if noises is None else noises[i])
+            exports = [ops.grad_sink(e) for e in exports]
+            x = exports[-1]      # the aggregate is the block's last export
             wide.extend(exports)
             narrow = [*narrow, x]
             aux.append(a)
@@ -352,9 +353,13 @@ def router_counts(backbone: Nestor, aux: dict) -> dict[str, Tensor]:
         for l, (layer, laux) in enumerate(zip(block.layers, baux["layers"])):
             base = f"blocks.{b}.layers.{l}"
             if layer.expert_pool is not None:
-                out[f"{base}.expert_pool.public_router"] = _count(laux["public_idx"], s.P)
-                flat = laux["columns"].long().unsqueeze(-1) * s.Q + laux["private_idx"].long()
-                per = _count(flat, s.G * s.Q).view(s.G, s.Q)
+                if "public_offsets" in laux:      # the dispatch plans already hold the per-expert histograms
+                    out[f"{base}.expert_pool.public_router"] = laux["public_offsets"].diff().float()
+                    per = laux["private_offsets"].diff().float().view(s.G, s.Q)
+                else:
+                    out[f"{base}.expert_pool.public_router"] = _count(laux["public_idx"], s.P)
+                    flat = laux["columns"].long().unsqueeze(-1) * s.Q + laux["private_idx"].long()
+                    per = _count(flat, s.G * s.Q).view(s.G, s.Q)
                 for g in range(s.G):
                     out[f"{base}.expert_pool.private_routers.{g}"] = per[g]
             elif "expert_idx" in laux:

@@ -64,11 +64,13 @@ def _dispatch(name: str):
 rmsnorm = _dispatch("rmsnorm")
 depth_read = _dispatch("depth_read")
 depth_read_norm = _dispatch("depth_read_norm")
+grad_sink = _dispatch("grad_sink")
 mid_source = _dispatch("mid_source")
 layer_combine = _dispatch("layer_combine")
 block_exit = _dispatch("block_exit")
 router_scores = _dispatch("router_scores")
 route_topk = _dispatch("route_topk")
+route_selected = _dispatch("route_selected")
 build_column_plan = _dispatch("build_column_plan")
 build_expert_plan = _dispatch("build_expert_plan")
 column_attention = _dispatch("column_attention")

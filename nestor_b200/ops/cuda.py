@@ -39,7 +39,7 @@ def _L():
         L.nb_rope.argtypes = [vp, l, vp, i, i, i, i, f, f, vp]
         L.nb_ce_grad.argtypes = [vp, l, i, vp, i, vp, l, vp, i, vp]
         L.nb_depth_read_norm.argtypes = [vp, i, vp, vp, vp, f, f, vp, vp, vp, vp, i, i, vp]
-        L.nb_depth_read_norm_bwd.argtypes = [vp, vp, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, vp]
+        L.nb_depth_read_norm_bwd.argtypes = [vp, vp, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, C.c_ulonglong, vp]
         L.nb_depth_read_norm_bwd.restype = C.c_int
         L.nb_mid_source.argtypes = [vp, vp, vp, i, i, i, vp]
         L.nb_layer_combine.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, vp]
@@ -47,6 +47,11 @@ def _L():
         L.nb_block_exit.argtypes = [vp, vp, vp, i, i, i, vp]
         L.nb_block_exit_bwd.argtypes = [vp, vp, vp, i, i, i, vp]
         for fn in (L.nb_mid_source, L.nb_layer_combine, L.nb_layer_combine_bwd, L.nb_block_exit, L.nb_block_exit_bwd):
+            fn.restype = C.c_int
+        L.nb_expert_plan.argtypes = [vp, i, i, vp, vp, vp, vp, vp]
+        L.nb_route_fwd.argtypes = [vp, vp]
+        L.nb_route_bwd.argtypes = [vp, vp, vp, vp, l, i, vp, vp]
+        for fn in (L.nb_expert_plan, L.nb_route_fwd, L.nb_route_bwd):
             fn.restype = C.c_int
         for fn in (L.nb_gather_rows, L.nb_combine_rows, L.nb_combine_bwd, L.nb_rope, L.nb_ce_grad,
                    L.nb_depth_read_norm):
@@ -388,6 +393,47 @@ def _ptr_array(tensors):
     return arr
 
 
+class _SinkState:
+    """Gradient buffer shared by every depth read of one source (see ``grad_sink``)."""
+
+    __slots__ = ("buf",)
+
+    def __init__(self) -> None:
+        self.buf = None
+
+
+class _GradSink(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, state):
+        ctx.state = state
+        ctx.set_materialize_grads(False)
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        st = ctx.state
+        buf, st.buf = st.buf, None
+        if buf is None:
+            return g, None
+        if g is not None:
+            buf.add_(g)
+        return buf, None
+
+
+def grad_sink(x: Tensor) -> Tensor:
+    """Mark ``x`` as a depth source read many times: the depth reads' backward passes add their
+    gradients for it into one shared buffer (inside their kernel) instead of handing autograd one
+    ``[T, d]`` tensor per read to sum. Autograd runs this node after every reader, where the
+    buffer joins the gradient from ``x``'s other consumers."""
+
+    if not (x.requires_grad and torch.is_grad_enabled() and x.dtype == torch.float32 and x.is_contiguous()):
+        return x
+    state = _SinkState()
+    out = _GradSink.apply(x, state)
+    out._nb_sink = state
+    return out
+
+
 class _DepthReadNorm(torch.autograd.Function):
     """One pass over the sources forward (online softmax over depth), three sweeps backward."""
 
@@ -404,6 +450,7 @@ class _DepthReadNorm(torch.autograd.Function):
                                     eps_norm, out.data_ptr(), None, stats.data_ptr(), rstd.data_ptr(), T, d, _st()),
             "depth_read_norm")
         ctx.save_for_backward(q32, g32, w32, stats, rstd, *srcs)
+        ctx.sinks = [getattr(s, "_nb_sink", None) if c is s else None for s, c in zip(sources, srcs)]
         ctx.dtypes = (query.dtype, gains.dtype, gamma.dtype, [s.dtype for s in sources])
         ctx.n_gains = gains.numel()
         return out
@@ -413,17 +460,29 @@ class _DepthReadNorm(torch.autograd.Function):
         q32, g32, w32, stats, rstd, *srcs = ctx.saved_tensors
         n = len(srcs)
         T, d = srcs[0].shape
-        ds = torch.empty(n, T, d, dtype=torch.float32, device=dn.device)
+        # sources with a shared gradient buffer: the first reader to run backward creates it, later ones add
+        outs, mask = [], 0
+        for i, sink in enumerate(ctx.sinks):
+            if sink is not None and ctx.needs_input_grad[5 + i]:
+                if sink.buf is None:
+                    sink.buf = torch.empty(T, d, dtype=torch.float32, device=dn.device)
+                else:
+                    mask |= 1 << i
+                outs.append(sink.buf)
+            else:
+                outs.append(torch.empty(T, d, dtype=torch.float32, device=dn.device))
         dq = torch.zeros(d, dtype=torch.float32, device=dn.device)
         dg = torch.zeros(ctx.n_gains, dtype=torch.float32, device=dn.device)
         dw = torch.zeros(d, dtype=torch.float32, device=dn.device)
         dnb = dn if (dn.dtype == BF16 and dn.is_contiguous()) else dn.to(BF16).contiguous()
-        _ck(_L().nb_depth_read_norm_bwd(_ptr_array(srcs), _ptr_array(list(ds.unbind(0))), n, q32.data_ptr(),
+        _ck(_L().nb_depth_read_norm_bwd(_ptr_array(srcs), _ptr_array(outs), n, q32.data_ptr(),
                                         g32.data_ptr(), w32.data_ptr(), stats.data_ptr(), rstd.data_ptr(), dnb.data_ptr(),
-                                        None, dq.data_ptr(), dg.data_ptr(), dw.data_ptr(), T, d, _st()),
+                                        None, dq.data_ptr(), dg.data_ptr(), dw.data_ptr(), T, d, C.c_ulonglong(mask), _st()),
             "depth_read_norm_bwd")
         qd, gd, wd, sd = ctx.dtypes
-        return (dq.to(qd), dg.to(gd), dw.to(wd), None, None, *[g.to(t) for g, t in zip(ds.unbind(0), sd)])
+        grads = [None if (sink is not None and ctx.needs_input_grad[5 + i]) else g.to(t)
+                 for i, (g, t, sink) in enumerate(zip(outs, sd, ctx.sinks))]
+        return (dq.to(qd), dg.to(gd), dw.to(wd), None, None, *grads)
 
 
 def depth_read_norm(sources, query, gains, gamma, eps_read, eps_norm, out_dtype):
@@ -529,4 +588,126 @@ def build_column_plan(idx, G_, pos=None):
 
 
 def build_expert_plan(expert_ids, E):
-    return ref.build_expert_plan(expert_ids, E)
+    """Counting sort by expert (three small kernels; the oracle sorts)."""
+
+    if E > 64:
+        return ref.build_expert_plan(expert_ids, E)
+    T, slots = expert_ids.shape
+    ids = expert_ids.reshape(-1)
+    if ids.dtype != torch.int32:
+        ids = ids.to(torch.int32)
+    ids = ids.contiguous()
+    n = ids.numel()
+    dev = ids.device
+    order = torch.empty(n, dtype=torch.int32, device=dev)
+    inv = torch.empty(n, dtype=torch.int32, device=dev)
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    scratch = torch.empty(max(1, -(-n // 1024)) * E, dtype=torch.int32, device=dev)
+    L = _L()
+    _ck(L.nb_expert_plan(ids.data_ptr(), n, E, scratch.data_ptr(), order.data_ptr(), inv.data_ptr(), offsets.data_ptr(),
+                         _st()), "expert_plan")
+    _lib.count_launch(2)
+    return ExpertPlan(E=E, n=n, slots=slots, order=order, inv=inv, offsets=offsets)
+
+
+# ---------------------------------------------------------------------------- routing
+class RouteArgs(C.Structure):
+    _fields_ = [("scores", C.c_void_p), ("ld", C.c_long), ("is_f32", C.c_int), ("col_off", C.c_int),
+                ("cols", C.c_void_p), ("k_cols", C.c_int), ("bias", C.c_void_p),
+                ("E", C.c_int), ("k", C.c_int), ("mode", C.c_int), ("T", C.c_int),
+                ("idx_in", C.c_void_p), ("idx_out", C.c_void_p), ("id_out", C.c_void_p), ("gates", C.c_void_p),
+                ("colgate", C.c_void_p), ("w_out", C.c_void_p)]
+
+
+_MODES = {"renorm": 0, "switch": 1, "all": 2}
+
+
+def _route_args(scores, E, k, mode, cols, bias, idx_in, idx, ids, gates, colgate, w) -> RouteArgs:
+    a = RouteArgs()
+    a.scores, a.ld, a.is_f32, a.col_off = scores.data_ptr(), scores.stride(0), int(scores.dtype == torch.float32), 0
+    a.cols, a.k_cols = _ptr(cols), (cols.shape[1] if cols is not None else 1)
+    a.bias = _ptr(bias)
+    a.E, a.k, a.mode, a.T = E, k, mode, scores.shape[0]
+    a.idx_in, a.idx_out, a.id_out, a.gates = _ptr(idx_in), idx.data_ptr(), _ptr(ids), gates.data_ptr()
+    a.colgate, a.w_out = _ptr(colgate), _ptr(w)
+    return a
+
+
+class _Route(torch.autograd.Function):
+    """Top-k selection + gates of one router family in one kernel (and one for the backward)."""
+
+    @staticmethod
+    def forward(ctx, scores, bias, cols, colgate, k: int, mode: int, idx_in, want_w: bool):
+        # scores: [T, E] (stride(1) == 1, any row pitch) or, with a column selection, [T, G, E] (E contiguous, G*E per row)
+        sel = cols is not None
+        E = scores.shape[-1]
+        T = scores.shape[0]
+        assert scores.stride(-1) == 1 and scores.dtype in (BF16, torch.float32)
+        if sel:
+            assert scores.ndim == 3 and scores.stride(1) == E
+            cols = cols.to(torch.int32).contiguous()
+            colgate = colgate.float().contiguous()
+        nprob = T * (cols.shape[1] if sel else 1)
+        dev = scores.device
+        idx = torch.empty(nprob, k, dtype=torch.int32, device=dev)
+        gates = torch.empty(nprob, k, dtype=torch.float32, device=dev)
+        ids = torch.empty(nprob, k, dtype=torch.int32, device=dev) if sel else None
+        w = torch.empty(nprob, k, dtype=BF16, device=dev) if want_w else None
+        b = bias.float().contiguous() if bias is not None else None
+        ii = idx_in.to(torch.int32).contiguous() if idx_in is not None else None
+        a = _route_args(scores, E, k, mode, cols if sel else None, b, ii, idx, ids, gates, colgate if sel else None, w)
+        _ck(_L().nb_route_fwd(C.byref(a), _st()), "route_fwd")
+        ctx.save_for_backward(scores, idx, gates, cols if sel else None, colgate if sel else None, b)
+        ctx.meta = (E, k, mode, sel, want_w)
+        ctx.mark_non_differentiable(idx)
+        if ids is not None:
+            ctx.mark_non_differentiable(ids)
+        return idx, gates, ids, w
+
+    @staticmethod
+    def backward(ctx, _d_idx, d_gates, _d_ids, d_w):
+        scores, idx, gates, cols, colgate, b = ctx.saved_tensors
+        E, k, mode, sel, want_w = ctx.meta
+        dscores = torch.zeros(scores.shape, dtype=scores.dtype, device=scores.device)
+        dcolgate = torch.empty(colgate.shape, dtype=torch.float32, device=scores.device) if sel else None
+        a = _route_args(scores, E, k, mode, cols, b, None, idx, None, gates, colgate, None)
+        dg = d_gates.float().contiguous() if d_gates is not None else None
+        dw = d_w.contiguous() if d_w is not None else None
+        # the gradient buffer is dense over this family's columns: its own row pitch, same block layout
+        ld_d = dscores.stride(0)
+        a_d = RouteArgs.from_buffer_copy(a)
+        _ck(_L().nb_route_bwd(C.byref(a_d), _ptr(dg), _ptr(dw), dscores.data_ptr(), ld_d,
+                              int(dscores.dtype == torch.float32), _ptr(dcolgate), _st()), "route_bwd")
+        return dscores, None, None, dcolgate, None, None, None, None
+
+
+def route_topk(scores: Tensor, bias: Tensor, k: int, gate_mode: str):
+    """Kernel body of ``reference.route_topk`` for 2-D score matrices (others take the oracle path)."""
+
+    if scores.ndim != 2 or scores.shape[-1] > 64 or k > 8 or scores.stride(-1) != 1:
+        return ref.route_topk(scores, bias, k, gate_mode)
+    tape = ref._TAPE
+    idx_in = None
+    if tape is not None and tape.mode == "replay":
+        idx_in = tape.selections[tape.cursor]
+        tape.cursor += 1
+    idx, gates, _, _ = _Route.apply(scores, bias, None, None, k, _MODES[gate_mode], idx_in, False)
+    if tape is not None and tape.mode == "record":
+        tape.selections.append(idx.long())
+    return idx, gates
+
+
+def route_selected(scores: Tensor, bias: Tensor, cols: Tensor, col_gates: Tensor, k: int, gate_mode: str, cd):
+    T, Gn, Q = scores.shape
+    if Q > 64 or k > 8 or scores.stride(-1) != 1 or scores.stride(1) != Q or cd != BF16:
+        return ref.route_selected(scores, bias, cols, col_gates, k, gate_mode, cd)
+    kc = cols.shape[1]
+    tape = ref._TAPE
+    idx_in = None
+    if tape is not None and tape.mode == "replay":
+        idx_in = tape.selections[tape.cursor].reshape(T * kc, k)
+        tape.cursor += 1
+    idx, _gates, ids, w = _Route.apply(scores, bias, cols, col_gates, k, _MODES[gate_mode], idx_in, True)
+    if tape is not None and tape.mode == "record":
+        tape.selections.append(idx.long().view(T, kc, k))
+    return ids.view(T, kc * k), w.view(T, kc * k), idx.view(T, kc, k)

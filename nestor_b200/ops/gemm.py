@@ -136,7 +136,8 @@ def gemm_rows(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: in
 
 
 def gemm_reduce(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: int = 1, out: Tensor,
-                epilogue: int = ACCUM_F32, alpha: float = 1.0, bn: int | None = None, sms: int = 0) -> Tensor:
+                epilogue: int = ACCUM_F32, alpha: float = 1.0, bn: int | None = None, sms: int = 0,
+                trace: Tensor | None = None) -> Tensor:
     """Reduction-grouped GEMM: ``out[g] (+)= A[rows_g]^T @ B[rows_g]`` with ``A [rows, M]``, ``B [rows, N]``.
 
     ``out`` is ``[G, M, N]`` (or ``[M, N]`` for one group) with a contiguous last dim; fp32 for the
@@ -170,5 +171,7 @@ def gemm_reduce(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: 
     a.max_m_tiles = 0
     a.sms = sms
     a.prefetch_dist, a.max_stages, a.prefetch_ops = PREFETCH_DIST, MAX_STAGES, 3
+    a.trace = trace.data_ptr() if trace is not None else None
+    a.debug = DEBUG
     _launch(a)
     return out

@@ -146,6 +146,13 @@ def rmsnorm(x: Tensor, weight: Tensor, eps: float, out_dtype: torch.dtype) -> Te
     return (y * weight.float()).to(out_dtype)
 
 
+def grad_sink(x: Tensor) -> Tensor:
+    """Identity. The kernel path uses this point to collect the gradients of a depth source that is
+    read by many depth reads in one buffer; plain autograd needs no help."""
+
+    return x
+
+
 def depth_read(sources: list[Tensor], query: Tensor, gains: Tensor, eps: float = 1e-6) -> Tensor:
     """Softmax-over-depth mixture of unit-RMS sources (fp32).
 
@@ -292,6 +299,26 @@ def route_topk(scores: Tensor, bias: Tensor, k: int, gate_mode: str) -> tuple[Te
     else:
         gates = torch.softmax(scores.float().gather(-1, idx), dim=-1)
     return idx, gates
+
+
+def route_selected(scores: Tensor, bias: Tensor, cols: Tensor, col_gates: Tensor, k: int, gate_mode: str,
+                   cd: torch.dtype) -> tuple[Tensor, Tensor, Tensor]:
+    """Private-expert routing inside the selected columns.
+
+    ``scores [T, G, Q]`` holds every column's private-router scores, ``bias [G, Q]`` their selection
+    biases, ``cols [T, kc]`` the columns a token was routed to and ``col_gates [T, kc]`` their gates.
+    Each (token, selected column) pair picks ``k`` of that column's ``Q`` experts (``route_topk``).
+    Returns ``(expert ids [T, kc*k]`` (``column * Q + choice``), ``weights [T, kc*k]`` in ``cd``
+    (``gate.to(cd) * col_gate.to(cd)``), ``choices [T, kc, k])``.
+    """
+
+    T, G, Q = scores.shape
+    col = cols.long()
+    sel_scores = scores.gather(1, col.unsqueeze(-1).expand(-1, -1, Q))          # [T, kc, Q]
+    idx, gate = route_topk(sel_scores, bias[col], k, gate_mode)                 # [T, kc, k]
+    ids = (col.unsqueeze(-1) * Q + idx).reshape(T, -1)
+    w = (gate.to(cd) * col_gates.to(cd).unsqueeze(-1)).reshape(T, -1)
+    return ids, w, idx
 
 
 # ---------------------------------------------------------------------------- attention

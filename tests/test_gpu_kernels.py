@@ -288,3 +288,46 @@ def test_graphed_step_matches_eager_and_smoke(monkeypatch):
         losses[flag] = vals
         assert (tr._graph is not None) == (flag == "1")
     assert all(abs(a - b) < 5e-3 for a, b in zip(losses["0"], losses["1"])), losses
+
+
+def test_route_and_plan_kernels_match_oracle():
+    from nestor_b200 import ops
+    from nestor_b200.ops import cuda as K, reference as R
+    torch.manual_seed(5)
+    T, P, Gc, Q, kc, kq = 3000, 12, 8, 8, 3, 2
+    width = P + Gc * Q + 2
+    base = torch.randn(T, width, device="cuda").to(BF)
+    bias_p, bias_q = torch.randn(P, device="cuda") * 0.1, torch.randn(Gc, Q, device="cuda") * 0.1
+    cols = torch.rand(T, Gc, device="cuda").topk(kc, dim=-1).indices
+    cg = torch.rand(T, kc, device="cuda") + 0.1
+    tape = ops.RoutingTape()
+
+    def run(mod, mode):
+        s = base.clone().requires_grad_()
+        g = cg.clone().requires_grad_()
+        ops.set_routing_tape(tape, mode)
+        pub_idx, pub_gate = mod.route_topk(s[:, :P], bias_p, 4, "renorm")
+        out = {}
+        for gm in ("renorm", "switch"):
+            out[gm] = mod.route_selected(s[:, P:P + Gc * Q].reshape(T, Gc, Q), bias_q, cols, g, kq, gm, BF)
+        ops.set_routing_tape(None)
+        loss = (pub_gate * torch.arange(1, 5, device="cuda")).sum()
+        for gm, (ids, w, _) in out.items():
+            loss = loss + (w.float() * torch.linspace(0.5, 1.5, kc * kq, device="cuda")).sum()
+        loss.backward()
+        return pub_idx, pub_gate, out, s.grad, g.grad
+
+    a = run(K, "record")
+    b = run(R, "replay")
+    assert torch.equal(a[0].long(), b[0].long()) and _rel(a[1], b[1]) < 1e-5
+    for gm in ("renorm", "switch"):
+        assert torch.equal(a[2][gm][0].long(), b[2][gm][0].long())
+        assert _rel(a[2][gm][1], b[2][gm][1]) < 1e-2
+    assert _rel(a[3], b[3]) < 2e-2 and _rel(a[4], b[4]) < 2e-2
+    # free selection: the chosen entries carry the k largest biased scores
+    idx, _ = K.route_topk(base[:, :P], bias_p, 4, "renorm")
+    biased = base[:, :P].float() + bias_p
+    assert torch.allclose(biased.gather(1, idx.long()).sort(1).values, biased.topk(4, dim=1).values.sort(1).values)
+    ids = torch.randint(0, 24, (5000, 3), device="cuda")
+    pa, pb = K.build_expert_plan(ids, 24), R.build_expert_plan(ids, 24)
+    assert torch.equal(pa.order, pb.order) and torch.equal(pa.inv, pb.inv) and torch.equal(pa.offsets, pb.offsets)
