@@ -568,13 +568,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
               for (int j = 0; j < 32; j += 4) {
                 if (j >= rem) break;
+                // a vector reduction (no return value): fire-and-forget, so the epilogue never waits on a load of the
+                // old value. Without a split reduction every address is touched once per launch, so the sum is
+                // still deterministic.
                 float4 add = make_float4(v[j] * p.alpha, v[j + 1] * p.alpha, v[j + 2] * p.alpha, v[j + 3] * p.alpha);
-                if (p.splits > 1) {
-                  atomicAdd(reinterpret_cast<float4*>(Cp + j), add);
-                } else {
-                  float4 old = reinterpret_cast<float4*>(Cp + j)[0];
-                  reinterpret_cast<float4*>(Cp + j)[0] = make_float4(old.x + add.x, old.y + add.y, old.z + add.z, old.w + add.w);
-                }
+                atomicAdd(reinterpret_cast<float4*>(Cp + j), add);
               }
             }
           }

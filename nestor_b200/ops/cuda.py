@@ -189,8 +189,7 @@ class _ExpertBank(torch.autograd.Function):
         T, d = x.shape
         E, _, h = w_up.shape
         xs = gather_rows(x, plan.order, div=plan.slots)                       # dispatch gather [n, d]
-        hh = torch.empty(plan.n, h, dtype=BF16, device=x.device)
-        gt, ut = torch.empty_like(hh), torch.empty_like(hh)
+        hh, gt, ut = (G.rows_buffer(plan.n, h, BF16, x.device) for _ in range(3))
         G.gemm_rows(xs, w_gate, B2=w_up, offsets=plan.offsets, groups=E, b_mn=True, out=hh, epilogue=G.SWIGLU,
                     extra_out=(gt, ut))
         y = G.gemm_rows(hh, w_down, offsets=plan.offsets, groups=E, b_mn=True)  # [n, d]
@@ -208,8 +207,7 @@ class _ExpertBank(torch.autograd.Function):
         E, d, h = w_up.shape
         g2 = dout.contiguous().view(-1, d).float()
         dy, dw_sorted = combine_bwd(g2, y, plan.order, wf, group, need_dw=ctx.needs_input_grad[1])
-        dgt = torch.empty(plan.n, h, dtype=BF16, device=dy.device)
-        dut = torch.empty_like(dgt)
+        dgt, dut = G.rows_buffer(plan.n, h, BF16, dy.device), G.rows_buffer(plan.n, h, BF16, dy.device)
         # dH = dY . Wd^T fused with the SwiGLU derivative; Wd [E, h, d] is the K-major B of this product
         G.gemm_rows(dy, w_down, offsets=plan.offsets, groups=E, out=dgt, epilogue=G.SWIGLU_BWD, extra_out=(dut,),
                     extra_in=(gt, ut))
@@ -248,10 +246,11 @@ class _Attention(torch.autograd.Function):
         inner = heads * head_dim
         x = gather_rows(n, tok_of_row) if tok_of_row is not None else (n if n.dtype == BF16 else n.to(BF16))
         rows = x.shape[0]
-        qkv = G.gemm_rows(x, wqkv, offsets=col_start, groups=groups)
+        qkv = G.gemm_rows(x, wqkv, offsets=col_start, groups=groups, out=G.rows_buffer(rows, 3 * inner, BF16, x.device))
         rope_(qkv, pos_of_row, heads, head_dim, inner, rope_base, 1.0)
         q, kk, v = qkv[:, :inner], qkv[:, inner : 2 * inner], qkv[:, 2 * inner :]
-        o, lse = flash.flash_fwd(q, kk, v, seg_start, heads, head_dim, 1.0 / head_dim)
+        o, lse = flash.flash_fwd(q, kk, v, seg_start, heads, head_dim, 1.0 / head_dim,
+                                 out=G.rows_buffer(rows, inner, BF16, x.device))
         y = G.gemm_rows(o, wo, offsets=col_start, groups=groups)
         gf = gates.float().contiguous().view(-1)
         out = combine_rows(y, row_of_slot.view(-1), gf, 1, T * k, round_products=False)
@@ -271,10 +270,12 @@ class _Attention(torch.autograd.Function):
         g2 = dout.contiguous().view(-1, d).float()
         dy, dg_sorted = combine_bwd(g2, y, slot_of_row_flat, gf, 1, need_dw=ctx.needs_input_grad[1])
         wq_ref, wo_ref = ctx.w_refs
-        do = G.gemm_rows(dy, wo, offsets=col_start, groups=groups, b_mn=True, n=inner)     # wo [G, K=d, N=inner]
+        do = G.gemm_rows(dy, wo, offsets=col_start, groups=groups, b_mn=True, n=inner,
+                         out=G.rows_buffer(dy.shape[0], inner, BF16, dy.device))               # wo [G, K=d, N=inner]
         d_wo = _wgrad(dy, o, wo_ref, offsets=col_start, groups=groups) if ctx.needs_input_grad[3] else None
         q, kk, v = qkv[:, :inner], qkv[:, inner : 2 * inner], qkv[:, 2 * inner :]
-        dqkv = flash.flash_bwd(q, kk, v, o, do, lse, seg_start, heads, head_dim, 1.0 / head_dim)
+        dqkv = flash.flash_bwd(q, kk, v, o, do, lse, seg_start, heads, head_dim, 1.0 / head_dim,
+                               dqkv=G.rows_buffer(q.shape[0], 3 * inner, BF16, q.device))
         rope_(dqkv, pos_of_row, heads, head_dim, inner, rope_base, -1.0)
         d_wqkv = _wgrad(dqkv, x, wq_ref, offsets=col_start, groups=groups) if ctx.needs_input_grad[2] else None
         dn = None

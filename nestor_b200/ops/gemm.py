@@ -45,6 +45,19 @@ def pick_bn(n: int, *, mult: int = 16, cap: int = 256) -> int:
     return best
 
 
+def rows_buffer(rows: int, cols: int, dtype: torch.dtype = torch.bfloat16, device=None) -> Tensor:
+    """``[rows, cols]`` activation buffer whose row pitch is a multiple of 64 elements.
+
+    The weight-gradient product reads activations "MN-major" (as ``[k rows, M or N columns]``); with a pitch
+    that covers whole 64-column atoms the kernel fetches every atom of a pipeline stage with one TMA
+    instruction. The padding columns are never written and only ever reach masked outputs.
+    """
+
+    pitch = -(-cols // 64) * 64
+    buf = torch.empty(rows, pitch, dtype=dtype, device=device)
+    return buf if pitch == cols else buf[:, :cols]
+
+
 def _operand(t: Tensor | None, *, grouped: bool) -> _lib.Operand:
     if t is None:
         return _lib.Operand(None, 0, 0, 0, 0, 0)
