@@ -48,10 +48,15 @@ class _ComputeView(torch.autograd.Function):
     def forward(ctx, view: Tensor, *params: Tensor) -> Tensor:
         ctx.shapes = [p.shape for p in params]
         ctx.dtypes = [p.dtype for p in params]
+        # kernels that add a weight gradient straight into the arena return no gradient for the view: without this
+        # autograd would materialise a zero tensor and add it to every parameter behind the view
+        ctx.set_materialize_grads(False)
         return view.detach()
 
     @staticmethod
     def backward(ctx, grad: Tensor):
+        if grad is None:
+            return (None,) * (1 + len(ctx.shapes))
         if len(ctx.shapes) == 1:
             return None, grad.reshape(ctx.shapes[0]).to(ctx.dtypes[0])
         if grad.shape[0] == len(ctx.shapes):          # stack of same-shape parameters
