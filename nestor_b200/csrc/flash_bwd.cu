@@ -112,53 +112,53 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
       }
     }
   } else if (warp == 1) {
+    // Warp-uniform descriptor arithmetic, one elected lane issues (see flash_fwd.cu).
     const uint32_t idesc_sc = make_idesc(BT, BT, 0, 0);
     const uint32_t idesc_acc = make_idesc(BT, HDN, 0, 1);
-    bool ok = true;
-    if (lane == 0) ok = mbar_wait(&r_full, 0, abort_flag, p.status, kTimeoutFull);
-    ok = __shfl_sync(0xffffffffu, ok, 0);
+    const uint64_t r1_desc = sdesc_kmajor(smem_u32(sR1)), r2_desc = sdesc_kmajor(smem_u32(sR2));
+    const uint64_t ds_desc = sdesc_kmajor(smem_u32(sDS)), pt_desc = sdesc_kmajor(smem_u32(sPT));
+    const int ks = hd16 / 16;
+    bool ok = mbar_wait(&r_full, 0, abort_flag, p.status, kTimeoutFull);
+    int s = 0; uint32_t ph = 0;
     for (int it = 0; it < niter && ok; ++it) {
-      int s = it % stages;
-      if (lane == 0) {
-        // (the score accumulators are free: the previous iteration's ds_ready was awaited below)
-        ok = mbar_wait(&x_full[s], (it / stages) & 1, abort_flag, p.status, kTimeoutFull);
-      }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
+      // (the score accumulators are free: the previous iteration's ds_ready was awaited below)
+      ok = mbar_wait(&x_full[s], ph, abort_flag, p.status, kTimeoutFull);
       if (!ok) break;
-      tc_fence_after();
       uint8_t* x1 = sX + s * 2 * tile_bytes;
       uint8_t* x2 = x1 + tile_bytes;
-      if (lane == 0) {
-        uint32_t a1 = smem_u32(sR1), a2 = smem_u32(sR2), b1 = smem_u32(x1), b2 = smem_u32(x2);
-        for (int k = 0; k < hd16 / 16; ++k) {
-          uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
-          umma_bf16(tS, sdesc_kmajor(a1 + off), sdesc_kmajor(b1 + off), idesc_sc, k != 0);
+      const uint64_t x1_k = sdesc_kmajor(smem_u32(x1)), x2_k = sdesc_kmajor(smem_u32(x2));
+      const uint64_t x1_mn = sdesc_mnmajor(smem_u32(x1), 16384), x2_mn = sdesc_mnmajor(smem_u32(x2), 16384);
+      if (elect_one()) {
+        for (int k = 0; k < ks; ++k) {
+          const uint32_t off = (k >> 2) * 1024 + (k & 3) * 2;
+          umma_bf16(tS, r1_desc + off, x1_k + off, idesc_sc, k != 0);
         }
-        for (int k = 0; k < hd16 / 16; ++k) {
-          uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
-          umma_bf16(tDP, sdesc_kmajor(a2 + off), sdesc_kmajor(b2 + off), idesc_sc, k != 0);
+        for (int k = 0; k < ks; ++k) {
+          const uint32_t off = (k >> 2) * 1024 + (k & 3) * 2;
+          umma_bf16(tDP, r2_desc + off, x2_k + off, idesc_sc, k != 0);
         }
         umma_commit(&sc_full);
-        ok = mbar_wait(&ds_ready, it & 1, abort_flag, p.status, kTimeoutTmemEmpty);
       }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
+      __syncwarp();
+      ok = mbar_wait(&ds_ready, it & 1, abort_flag, p.status, kTimeoutTmemEmpty);
       if (!ok) break;
       tc_fence_after();
-      if (lane == 0) {
-        uint32_t ds = smem_u32(sDS), pt = smem_u32(sPT), b1 = smem_u32(x1), b2 = smem_u32(x2);
+      if (elect_one()) {
+#pragma unroll
         for (int k = 0; k < BT / 16; ++k) {
-          uint32_t aoff = (k >> 2) * 16384 + (k & 3) * 32;
+          const uint32_t aoff = (k >> 2) * 1024 + (k & 3) * 2;
           if (MODE == 0) {
-            umma_bf16(tA1, sdesc_kmajor(pt + aoff), sdesc_mnmajor(b2 + k * 2048, 16384), idesc_acc, (it | k) != 0);  // dV += P^T dO
-            umma_bf16(tA2, sdesc_kmajor(ds + aoff), sdesc_mnmajor(b1 + k * 2048, 16384), idesc_acc, (it | k) != 0);  // dK += dS^T Q
+            umma_bf16(tA1, pt_desc + aoff, x2_mn + k * 128, idesc_acc, (it | k) != 0);  // dV += P^T dO
+            umma_bf16(tA2, ds_desc + aoff, x1_mn + k * 128, idesc_acc, (it | k) != 0);  // dK += dS^T Q
           } else {
-            umma_bf16(tA1, sdesc_kmajor(ds + aoff), sdesc_mnmajor(b1 + k * 2048, 16384), idesc_acc, (it | k) != 0);  // dQ += dS K
+            umma_bf16(tA1, ds_desc + aoff, x1_mn + k * 128, idesc_acc, (it | k) != 0);  // dQ += dS K
           }
         }
         umma_commit(&x_empty[s]);
         umma_commit(&acc_done);
       }
       __syncwarp();
+      if (++s == stages) { s = 0; ph ^= 1; }
     }
   } else {
     const int q4 = warp & 3;

@@ -105,43 +105,44 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
   } else if (warp == 1) {
+    // Descriptors are computed by the whole warp (warp-uniform values stay in uniform registers, where the MMA
+    // instruction reads them) and advance by additions on the 16-byte-unit address field; one elected lane
+    // issues. All lanes poll the barriers together, so no shuffle sits between a wait and the issue.
     const uint32_t idesc_s = make_idesc(FQ, FK, 0, 0);
     const uint32_t idesc_o = make_idesc(FQ, HDN, 0, 1);
+    const uint64_t q_desc = sdesc_kmajor(smem_u32(sQ));
+    const uint64_t p_desc = sdesc_kmajor(smem_u32(sP));
+    const int ks = hd16 / 16;
     bool ok = true;
     auto issue_s = [&](int j) {
       // S_j = Q K_j^T into buffer j&1
-      int s = j & 1;
-      if (lane == 0) ok = mbar_wait(&kv_full[s], (j >> 1) & 1, abort_flag, p.status, kTimeoutFull);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
+      const int s = j & 1;
+      ok = mbar_wait(&kv_full[s], (j >> 1) & 1, abort_flag, p.status, kTimeoutFull);
       if (!ok) return;
-      tc_fence_after();
-      if (lane == 0) {
-        uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + s * tile_bytes);
-        for (int k = 0; k < hd16 / 16; ++k) {
-          uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
-          umma_bf16(tS0 + s * FK, sdesc_kmajor(qa + off), sdesc_kmajor(ka + off), idesc_s, k != 0);
+      const uint64_t k_desc = sdesc_kmajor(smem_u32(sK + s * tile_bytes));
+      const uint32_t d_addr = tS0 + s * FK;
+      if (elect_one()) {
+        for (int k = 0; k < ks; ++k) {
+          const uint32_t off = (k >> 2) * 1024 + (k & 3) * 2;     // (64-column block, 32 B per K step) in 16-byte units
+          umma_bf16(d_addr, q_desc + off, k_desc + off, idesc_s, k != 0);
         }
         umma_commit(&s_full[s]);
       }
       __syncwarp();
     };
-    if (lane == 0) ok = mbar_wait(&q_full, 0, abort_flag, p.status, kTimeoutFull);
-    ok = __shfl_sync(0xffffffffu, ok, 0);
+    ok = mbar_wait(&q_full, 0, abort_flag, p.status, kTimeoutFull);
     if (ok) issue_s(0);
     for (int j = 0; j < ntiles && ok; ++j) {
       if (j + 1 < ntiles) { issue_s(j + 1); if (!ok) break; }
-      if (lane == 0) ok = mbar_wait(&p_ready, j & 1, abort_flag, p.status, kTimeoutTmemEmpty);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
+      ok = mbar_wait(&p_ready, j & 1, abort_flag, p.status, kTimeoutTmemEmpty);
       if (!ok) break;
       tc_fence_after();
-      if (lane == 0) {
-        int s = j & 1;
-        uint32_t pa = smem_u32(sP), va = smem_u32(sV + s * tile_bytes);
-        for (int k = 0; k < FK / 16; ++k) {
-          uint64_t ad = sdesc_kmajor(pa + (k >> 2) * 16384 + (k & 3) * 32);
-          uint64_t bd = sdesc_mnmajor(va + k * 2048, 16384);
-          umma_bf16(tO, ad, bd, idesc_o, k != 0);
-        }
+      const int s = j & 1;
+      const uint64_t v_desc = sdesc_mnmajor(smem_u32(sV + s * tile_bytes), 16384);
+      if (elect_one()) {
+#pragma unroll
+        for (int k = 0; k < FK / 16; ++k)
+          umma_bf16(tO, p_desc + ((k >> 2) * 1024 + (k & 3) * 2), v_desc + k * 128, idesc_o, k != 0);
         umma_commit(&kv_empty[s]);
         umma_commit(&o_full);
       }
