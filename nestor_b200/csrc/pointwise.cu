@@ -178,6 +178,7 @@ __global__ void ce_grad_kernel(__nv_bfloat16* __restrict__ logits, long ld, int 
 // Online over sources: one pass, running (max, denominator, accumulator). Saves per-(token, source)
 // (r_i, u_i = <s_i, q>) and per-token rstd for the backward.
 constexpr int kMaxSources = 48;
+constexpr int kMaxDepthDim = 1280;     // widest model dim of the fused depth read (10 float4 per lane)
 struct SourceList { const float* ptr[kMaxSources]; };
 
 template <int NV>   // d == NV * 32 * 4 is not required; each lane owns NV float4 chunks at stride 32
@@ -338,8 +339,11 @@ __global__ void depth_read_norm_bwd_kernel(SourceList src, GradList dsrc, int n,
                                            const float* __restrict__ gains, const float* __restrict__ gamma,
                                            const float* __restrict__ stats, const float* __restrict__ rstd_in,
                                            const __nv_bfloat16* __restrict__ dn, const float* __restrict__ dh_in,
-                                           float* __restrict__ dquery, float* __restrict__ dgains,
-                                           float* __restrict__ dgamma, int T, int d, unsigned long long acc_mask) {
+                                           float* __restrict__ partial, int has_gamma, int T, int d,
+                                           unsigned long long acc_mask) {
+  // Parameter gradients leave the kernel as one partial row per block, [dquery (d) | dgamma (d) | dgains (64)],
+  // summed by depth_param_reduce_kernel: thousands of warps adding atomically into the same 2d + n addresses
+  // serialised in L2 and cost more than the rest of the kernel.
   // bit i of acc_mask: the gradient of source i is added to what dsrc[i] already holds (a buffer shared by every
   // reader of that source) instead of overwriting it
   __shared__ float s_w[4][kMaxSources], s_t[4][kMaxSources];
@@ -467,21 +471,46 @@ __global__ void depth_read_norm_bwd_kernel(SourceList src, GradList dsrc, int n,
     }
     __syncwarp();
   }
-  // parameter gradients: one atomic per (warp, element)
+  // parameter gradients: sum the block's four warps through shared memory, write the block's partial row
+  __shared__ float s_red[4][kMaxDepthDim];
+  const int tid = wy * 32 + lane, stride = 2 * d + 64;
+  float* prow = partial + long(blockIdx.x) * stride;
+  for (int pass = 0; pass < 2; ++pass) {
+    if (pass == 1 && !has_gamma) break;
 #pragma unroll
-  for (int v = 0; v < NV; ++v) {
-    int c = lane + 32 * v;
-    if (c < nchunk) {
-      atomicAdd(dquery + 4 * c, gq[v].x); atomicAdd(dquery + 4 * c + 1, gq[v].y);
-      atomicAdd(dquery + 4 * c + 2, gq[v].z); atomicAdd(dquery + 4 * c + 3, gq[v].w);
-      if (dgamma) {
-        atomicAdd(dgamma + 4 * c, gg[v].x); atomicAdd(dgamma + 4 * c + 1, gg[v].y);
-        atomicAdd(dgamma + 4 * c + 2, gg[v].z); atomicAdd(dgamma + 4 * c + 3, gg[v].w);
-      }
+    for (int v = 0; v < NV; ++v) {
+      int c = lane + 32 * v;
+      if (c < nchunk) reinterpret_cast<float4*>(&s_red[wy][0])[c] = pass == 0 ? gq[v] : gg[v];
     }
+    __syncthreads();
+    for (int j = tid; j < d; j += 128) prow[pass * d + j] = s_red[0][j] + s_red[1][j] + s_red[2][j] + s_red[3][j];
+    __syncthreads();
   }
-  if (lane < n) atomicAdd(dgains + lane, dgain_acc[0]);
-  if (lane + 32 < n) atomicAdd(dgains + lane + 32, dgain_acc[1]);
+  s_red[wy][lane] = dgain_acc[0]; s_red[wy][lane + 32] = dgain_acc[1];
+  __syncthreads();
+  if (tid < 64) prow[2 * d + tid] = s_red[0][tid] + s_red[1][tid] + s_red[2][tid] + s_red[3][tid];
+}
+
+// Column sums of the [nblk, 2d + 64] partial rows -> dquery [d], dgamma [d] (optional), dgains [n].
+__global__ void depth_param_reduce_kernel(const float* __restrict__ partial, int nblk, int d, int n,
+                                          float* __restrict__ dquery, float* __restrict__ dgains,
+                                          float* __restrict__ dgamma) {
+  __shared__ float s_acc[8][32];
+  const int stride = 2 * d + 64;
+  const int col = blockIdx.x * 32 + threadIdx.x;
+  float acc = 0.f;
+  if (col < stride)
+    for (int r = threadIdx.y; r < nblk; r += 8) acc += partial[long(r) * stride + col];
+  s_acc[threadIdx.y][threadIdx.x] = acc;
+  __syncthreads();
+  if (threadIdx.y == 0 && col < stride) {
+    float t = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) t += s_acc[r][threadIdx.x];
+    if (col < d) dquery[col] = t;
+    else if (col < 2 * d) { if (dgamma) dgamma[col - d] = t; }
+    else if (col - 2 * d < n) dgains[col - 2 * d] = t;
+  }
 }
 
 }  // namespace nb
@@ -489,8 +518,9 @@ __global__ void depth_read_norm_bwd_kernel(SourceList src, GradList dsrc, int n,
 extern "C" int nb_depth_read_norm_bwd(const float* const* sources, float* const* dsources, int n, const float* query,
                                       const float* gains, const float* gamma, const float* stats, const float* rstd,
                                       const void* dn, const float* dh, float* dquery, float* dgains, float* dgamma, int T,
-                                      int d, unsigned long long acc_mask, cudaStream_t st) {
-  if (n < 1 || n > nb::kMaxSources || d % 4) return -1;
+                                      int d, unsigned long long acc_mask, float* scratch, cudaStream_t st) {
+  // scratch: fp32 [1184 * (2d + 64)] per-block partial sums of the parameter gradients
+  if (n < 1 || n > nb::kMaxSources || d % 4 || d > nb::kMaxDepthDim || !scratch) return -1;
   nb::SourceList sl; nb::GradList gl;
   for (int i = 0; i < n; ++i) { sl.ptr[i] = sources[i]; gl.ptr[i] = dsources[i]; }
   dim3 block(32, 4);
@@ -498,10 +528,11 @@ extern "C" int nb_depth_read_norm_bwd(const float* const* sources, float* const*
   if (blocks > 148 * 8) blocks = 148 * 8;
   int nv = (d / 4 + 31) / 32;
 #define NB_DRB(NV) nb::depth_read_norm_bwd_kernel<NV><<<blocks, block, 0, st>>>(sl, gl, n, query, gains, gamma, stats, rstd, \
-      (const __nv_bfloat16*)dn, dh, dquery, dgains, dgamma, T, d, acc_mask)
+      (const __nv_bfloat16*)dn, dh, scratch, dgamma != nullptr, T, d, acc_mask)
   if (nv <= 1) NB_DRB(1); else if (nv <= 2) NB_DRB(2); else if (nv <= 4) NB_DRB(4); else if (nv <= 5) NB_DRB(5);
   else if (nv <= 8) NB_DRB(8); else if (nv <= 10) NB_DRB(10); else return -2;
 #undef NB_DRB
+  nb::depth_param_reduce_kernel<<<(2 * d + 64 + 31) / 32, dim3(32, 8), 0, st>>>(scratch, blocks, d, n, dquery, dgains, dgamma);
   return int(cudaGetLastError());
 }
 

@@ -39,7 +39,7 @@ def _L():
         L.nb_rope.argtypes = [vp, l, vp, i, i, i, i, f, f, vp]
         L.nb_ce_grad.argtypes = [vp, l, i, vp, i, vp, l, vp, i, vp]
         L.nb_depth_read_norm.argtypes = [vp, i, vp, vp, vp, f, f, vp, vp, vp, vp, i, i, vp]
-        L.nb_depth_read_norm_bwd.argtypes = [vp, vp, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, C.c_ulonglong, vp]
+        L.nb_depth_read_norm_bwd.argtypes = [vp, vp, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, C.c_ulonglong, vp, vp]
         L.nb_depth_read_norm_bwd.restype = C.c_int
         L.nb_mid_source.argtypes = [vp, vp, vp, i, i, i, vp]
         L.nb_layer_combine.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, vp]
@@ -472,14 +472,17 @@ class _DepthReadNorm(torch.autograd.Function):
                 outs.append(sink.buf)
             else:
                 outs.append(torch.empty(T, d, dtype=torch.float32, device=dn.device))
-        dq = torch.zeros(d, dtype=torch.float32, device=dn.device)
-        dg = torch.zeros(ctx.n_gains, dtype=torch.float32, device=dn.device)
-        dw = torch.zeros(d, dtype=torch.float32, device=dn.device)
+        dq = torch.empty(d, dtype=torch.float32, device=dn.device)
+        dg = torch.zeros(ctx.n_gains, dtype=torch.float32, device=dn.device)     # gains past the n sources read get no gradient
+        dw = torch.empty(d, dtype=torch.float32, device=dn.device)
+        scratch = torch.empty(1184 * (2 * d + 64), dtype=torch.float32, device=dn.device)
         dnb = dn if (dn.dtype == BF16 and dn.is_contiguous()) else dn.to(BF16).contiguous()
         _ck(_L().nb_depth_read_norm_bwd(_ptr_array(srcs), _ptr_array(outs), n, q32.data_ptr(),
                                         g32.data_ptr(), w32.data_ptr(), stats.data_ptr(), rstd.data_ptr(), dnb.data_ptr(),
-                                        None, dq.data_ptr(), dg.data_ptr(), dw.data_ptr(), T, d, C.c_ulonglong(mask), _st()),
+                                        None, dq.data_ptr(), dg.data_ptr(), dw.data_ptr(), T, d, C.c_ulonglong(mask),
+                                        scratch.data_ptr(), _st()),
             "depth_read_norm_bwd")
+        _lib.count_launch()
         qd, gd, wd, sd = ctx.dtypes
         grads = [None if (sink is not None and ctx.needs_input_grad[5 + i]) else g.to(t)
                  for i, (g, t, sink) in enumerate(zip(outs, sd, ctx.sinks))]
