@@ -76,25 +76,43 @@ allreduce_push_kernel(Peers P, long offset, long numel, float scale, int write_m
   const long n4 = numel / 4;
   const long per = (n4 + P.world - 1) / P.world;
   const long lo = per * P.rank, hi = min(n4, lo + per);
+  // kUnroll float4 per thread and iteration: every peer load of the batch is issued before the first add, so
+  // (world - 1) * kUnroll NVLink reads are in flight per thread
+  constexpr int kUnroll = 4;
   const long stride = long(gridDim.x) * blockDim.x;
-  for (long i = lo + long(blockIdx.x) * blockDim.x + threadIdx.x; i < hi; i += stride) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (long i0 = lo + long(blockIdx.x) * blockDim.x + threadIdx.x; i0 < hi; i0 += stride * kUnroll) {
+    float4 acc[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int p = 0; p < kMaxWorld; ++p) {
       if (p < P.world) {
-        const float4 v = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(P.buf[p]) + offset)[i];
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(P.buf[p]) + offset);
+        float4 v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const long i = i0 + u * stride;
+          v[u] = i < hi ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) { acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w; }
       }
     }
-    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
-    __nv_bfloat162 b0 = __floats2bfloat162_rn(acc.x, acc.y), b1 = __floats2bfloat162_rn(acc.z, acc.w);
-    const uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&b0), *reinterpret_cast<uint32_t*>(&b1));
 #pragma unroll
-    for (int p = 0; p < kMaxWorld; ++p) {
-      if (p < P.world) {
-        reinterpret_cast<float4*>(reinterpret_cast<float*>(P.buf[p]) + offset)[i] = acc;
-        if (write_mirror)
-          reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(P.aux[p]) + offset)[i] = packed;
+    for (int u = 0; u < kUnroll; ++u) {
+      const long i = i0 + u * stride;
+      if (i >= hi) break;
+      float4 a = acc[u];
+      a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
+      __nv_bfloat162 b0 = __floats2bfloat162_rn(a.x, a.y), b1 = __floats2bfloat162_rn(a.z, a.w);
+      const uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&b0), *reinterpret_cast<uint32_t*>(&b1));
+#pragma unroll
+      for (int p = 0; p < kMaxWorld; ++p) {
+        if (p < P.world) {
+          reinterpret_cast<float4*>(reinterpret_cast<float*>(P.buf[p]) + offset)[i] = a;
+          if (write_mirror)
+            reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(P.aux[p]) + offset)[i] = packed;
+        }
       }
     }
   }

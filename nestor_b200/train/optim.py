@@ -34,11 +34,18 @@ from torch.optim import Optimizer
 from torch.optim.lr_scheduler import CosineAnnealingLR, LambdaLR, LRScheduler, SequentialLR, StepLR
 
 from nestor_b200 import ops
+from nestor_b200.train import fused_optim
 from nestor_b200.configs import (
     AdamConfig, AdamWConfig, CosineAnnealingConfig, MuonAdamWConfig, OptimizerConfig, PowerLawConfig,
     SchedulerConfig, SGDConfig, StepLRConfig, WSDConfig,
 )
 from nestor_b200.models.tags import get_tag
+
+
+def _fused(*lists: list[Tensor]) -> bool:
+    """The multi-tensor kernels apply: CUDA, fp32, contiguous tensors (arena views and their states are)."""
+
+    return all(t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() for ts in lists for t in ts)
 
 
 def _dist_on() -> bool:
@@ -164,6 +171,20 @@ class MuonAdamW(Optimizer):
             bufs.append(st["momentum_buffer"])
         if not params:
             return
+        if _fused(params, grads, bufs):
+            # one launch for the momentum update of the whole group, one for the parameter update
+            directions = [torch.empty_like(b) for b in bufs]
+            fused_optim.launch(fused_optim.MOMENTUM, [grads, bufs, directions], [mu, 1.0 if group["nesterov"] else 0.0])
+            updates = orthogonalize(directions, group["ns_steps"])
+            updates = [u if u.is_contiguous() else u.contiguous() for u in updates]
+            op = fused_optim.AXPY_BF16 if updates[0].dtype == torch.bfloat16 else fused_optim.AXPY_F32
+            if all(u.dtype == updates[0].dtype and u.dtype in (torch.float32, torch.bfloat16) for u in updates):
+                fused_optim.launch(op, [params, updates], [1.0 - lr * wd, -lr])
+                return
+            if wd != 0.0:
+                torch._foreach_mul_(params, 1.0 - lr * wd)
+            torch._foreach_add_(params, updates, alpha=-lr)
+            return
         torch._foreach_mul_(bufs, mu)
         torch._foreach_add_(bufs, grads)
         directions = torch._foreach_add(grads, bufs, alpha=mu) if group["nesterov"] else bufs
@@ -190,6 +211,12 @@ class MuonAdamW(Optimizer):
             m2.append(st["exp_avg_sq"])
             steps.append(st["step"])
         if not params:
+            return
+        if _fused(params, grads, m1, m2) and len(set(steps)) == 1:
+            s = steps[0]
+            fused_optim.launch(fused_optim.ADAMW, [params, grads, m1, m2],
+                               [1.0 - lr * wd, 1.0 - b1, b2, 1.0 - b2, 1.0 / math.sqrt(1.0 - b2 ** s), eps,
+                                lr / (1.0 - b1 ** s)])
             return
         if wd != 0.0:
             torch._foreach_mul_(params, 1.0 - lr * wd)

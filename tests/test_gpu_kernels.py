@@ -331,3 +331,29 @@ def test_route_and_plan_kernels_match_oracle():
     ids = torch.randint(0, 24, (5000, 3), device="cuda")
     pa, pb = K.build_expert_plan(ids, 24), R.build_expert_plan(ids, 24)
     assert torch.equal(pa.order, pb.order) and torch.equal(pa.inv, pb.inv) and torch.equal(pa.offsets, pb.offsets)
+
+
+def test_multi_tensor_optimizer_matches_foreach(monkeypatch):
+    from nestor_b200.train import optim as O
+    torch.manual_seed(7)
+
+    def make():
+        torch.manual_seed(7)
+        mats = [torch.nn.Parameter(torch.randn(64, 96, device="cuda")), torch.nn.Parameter(torch.randn(3, 48, 32, device="cuda"))]
+        vecs = [torch.nn.Parameter(torch.randn(1000, device="cuda")), torch.nn.Parameter(torch.randn(70000, device="cuda"))]
+        groups = [dict(params=mats, method="muon", lr=0.02, weight_decay=0.1, momentum=0.95, nesterov=True, ns_steps=5),
+                  dict(params=vecs, method="adamw", lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)]
+        return mats + vecs, O.MuonAdamW(groups)
+
+    pa, oa = make()
+    pb, ob = make()
+    for step in range(3):
+        for x, y in zip(pa, pb):
+            g = torch.randn_like(x)
+            x.grad, y.grad = g.clone(), g.clone()
+        oa.step()
+        with monkeypatch.context() as m:
+            m.setattr(O, "_fused", lambda *a: False)
+            ob.step()
+    for x, y in zip(pa, pb):
+        assert _rel(x, y) < 1e-5
