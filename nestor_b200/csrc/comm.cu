@@ -68,14 +68,17 @@ __device__ bool block_barrier(const Peers& P, int phase, uint32_t epoch, long bu
   return s_ok != 0;
 }
 
+// store_all = 1: all-reduce (the owner of a slice writes the sum into every replica). store_all = 0:
+// reduce-scatter (the sum stays with the owner, whose slice [own_lo, own_hi) is given explicitly so that it can
+// follow the optimizer's ownership ranges; the other ranks' copies of that slice are only read).
 __global__ void __launch_bounds__(512, 1)
 allreduce_push_kernel(Peers P, long offset, long numel, float scale, int write_mirror, uint32_t epoch, long budget,
-                      int* status) {
+                      int* status, int store_all, long own_lo, long own_hi) {
   if (!block_barrier(P, 0, epoch, budget, status)) return;
   // this rank's slice of [0, numel), in float4 units
   const long n4 = numel / 4;
   const long per = (n4 + P.world - 1) / P.world;
-  const long lo = per * P.rank, hi = min(n4, lo + per);
+  const long lo = store_all ? per * P.rank : own_lo / 4, hi = store_all ? min(n4, lo + per) : own_hi / 4;
   // kUnroll float4 per thread and iteration: every peer load of the batch is issued before the first add, so
   // (world - 1) * kUnroll NVLink reads are in flight per thread
   constexpr int kUnroll = 4;
@@ -108,7 +111,7 @@ allreduce_push_kernel(Peers P, long offset, long numel, float scale, int write_m
       const uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&b0), *reinterpret_cast<uint32_t*>(&b1));
 #pragma unroll
       for (int p = 0; p < kMaxWorld; ++p) {
-        if (p < P.world) {
+        if (p < P.world && (store_all || p == P.rank)) {
           reinterpret_cast<float4*>(reinterpret_cast<float*>(P.buf[p]) + offset)[i] = a;
           if (write_mirror)
             reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(P.aux[p]) + offset)[i] = packed;
@@ -173,7 +176,17 @@ static nbc::Peers to_peers(const NbPeers* a) {
 int nb_allreduce_push(const NbPeers* a, long offset, long numel, float scale, int write_mirror, unsigned epoch, long budget,
                       int blocks, int* status, cudaStream_t st) {
   if (a->world < 1 || a->world > 8 || (numel % 4) || (offset % 4) || blocks < 1 || blocks > 148) return -1;
-  nbc::allreduce_push_kernel<<<blocks, 512, 0, st>>>(to_peers(a), offset, numel, scale, write_mirror, epoch, budget, status);
+  nbc::allreduce_push_kernel<<<blocks, 512, 0, st>>>(to_peers(a), offset, numel, scale, write_mirror, epoch, budget, status,
+                                                     1, 0, 0);
+  return int(cudaGetLastError());
+}
+
+// Reduce-scatter: this rank sums [lo, hi) (fp32 elements, multiples of 4) of every replica into its own buffer
+// (x scale). Every rank passes its own range; ranges may differ in size and must not overlap.
+int nb_reduce_scatter_push(const NbPeers* a, long lo, long hi, float scale, int write_mirror, unsigned epoch, long budget,
+                           int blocks, int* status, cudaStream_t st) {
+  if (a->world < 1 || a->world > 8 || (lo % 4) || (hi % 4) || hi < lo || blocks < 1 || blocks > 148) return -1;
+  nbc::allreduce_push_kernel<<<blocks, 512, 0, st>>>(to_peers(a), 0, 0, scale, write_mirror, epoch, budget, status, 0, lo, hi);
   return int(cudaGetLastError());
 }
 

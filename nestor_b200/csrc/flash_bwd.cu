@@ -16,7 +16,9 @@
 
 namespace nb {
 
-constexpr int BT = 128;
+constexpr int BT = 128;     // rows of the resident tile (kv tile in MODE 0, q tile in MODE 1)
+constexpr int BX = 64;      // rows of a streamed tile: half a resident tile, so that score + dP accumulators take 128
+                            // TMEM columns, a CTA needs 256 columns and < 100 KB of shared memory, and two CTAs share an SM
 
 struct FlashBwdParams {
   int nseg, H, hd, rows, stages;
@@ -34,7 +36,7 @@ __device__ __forceinline__ void st_tile_chunk(uint8_t* base, int row, int col0, 
 }
 
 template <int MODE, int HDN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, HDN == 64 ? 2 : 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ CUtensorMap tmR2,
                  const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ CUtensorMap tmX2,
                  const FlashBwdParams p) {
@@ -43,20 +45,21 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
   __shared__ int s_tile[4];
-  __shared__ float s_lse[4][BT], s_delta[4][BT];   // one private copy per softmax warp (no cross-warp barrier)
+  __shared__ float s_lse[4][BX], s_delta[4][BX];   // one private copy per softmax warp (no cross-warp barrier)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.y;
   const int nkb = (p.hd + 63) / 64;
   const int hd16 = (p.hd + 15) & ~15;
-  const uint32_t tile_bytes = uint32_t(nkb) * 16384;
+  const uint32_t tile_bytes = uint32_t(nkb) * 16384;   // resident tile: 128 rows, 64-column blocks of 16 KB
+  const uint32_t xtile_bytes = uint32_t(nkb) * 8192;   // streamed tile: 64 rows, 64-column blocks of 8 KB
   const int stages = p.stages;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sR1 = smem;
   uint8_t* sR2 = sR1 + tile_bytes;
   uint8_t* sX = sR2 + tile_bytes;                       // stages x (X1, X2)
-  uint8_t* sDS = sX + stages * 2 * tile_bytes;          // 32 KB: dS (or dS^T)
-  uint8_t* sPT = sDS + 32768;                           // 32 KB: P^T (MODE 0 only)
+  uint8_t* sDS = sX + stages * 2 * xtile_bytes;         // 16 KB: dS (or dS^T), 128 rows x 64 streamed columns
+  uint8_t* sPT = sDS + 16384;                           // 16 KB: P^T (MODE 0 only)
 
   if (threadIdx.x == 0) {
     int t = blockIdx.x, found = 0, b = 0, e = 0, r0 = 0;
@@ -80,16 +83,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
   }
   __syncthreads();
   if (!s_tile[3]) return;
-  if (warp == 1) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
+  constexpr uint32_t kTmemCols = HDN == 64 ? 256 : 512;   // S 64 + dP 64 + accumulators 2 x HDN
+  if (warp == 1) { tmem_alloc(&tmem_slot, kTmemCols); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  const uint32_t tS = tmem, tDP = tmem + 128, tA1 = tmem + 256, tA2 = tmem + 256 + HDN;
+  const uint32_t tS = tmem, tDP = tmem + BX, tA1 = tmem + 2 * BX, tA2 = tmem + 2 * BX + HDN;
   const int seg_b = s_tile[0], seg_e = s_tile[1], r0 = s_tile[2];
   // streamed tiles: MODE 0 -> q tiles r0, r0+128, ... below seg_e; MODE 1 -> kv tiles seg_b .. r0
   const int x_first = (MODE == 0) ? r0 : seg_b;
-  const int niter = (MODE == 0) ? (seg_e - r0 + BT - 1) / BT : (r0 - seg_b) / BT + 1;
+  // MODE 0: q rows r0 .. seg_e; MODE 1: kv rows seg_b .. r0 + 127 (up to and including the diagonal tile)
+  const int niter = (MODE == 0) ? (seg_e - r0 + BX - 1) / BX : (min(r0 + BT, seg_e) - seg_b + BX - 1) / BX;
   volatile int* abort_flag = &s_abort;
 
   if (warp == 0) {
@@ -102,18 +107,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
       for (int it = 0; it < niter; ++it) {
         int s = it % stages;
         if (!mbar_wait(&x_empty[s], ((it / stages) & 1) ^ 1, abort_flag, p.status, kTimeoutEmpty)) break;
-        mbar_expect_tx(&x_full[s], 2 * tile_bytes);
-        int x0 = x_first + it * BT;
-        uint8_t* d = sX + s * 2 * tile_bytes;
+        mbar_expect_tx(&x_full[s], 2 * xtile_bytes);
+        int x0 = x_first + it * BX;
+        uint8_t* d = sX + s * 2 * xtile_bytes;
         for (int b = 0; b < nkb; ++b) {
-          tma_load_3d(d + b * 16384, &tmX1, &x_full[s], b * 64, head, x0);
-          tma_load_3d(d + tile_bytes + b * 16384, &tmX2, &x_full[s], b * 64, head, x0);
+          tma_load_3d(d + b * 8192, &tmX1, &x_full[s], b * 64, head, x0);
+          tma_load_3d(d + xtile_bytes + b * 8192, &tmX2, &x_full[s], b * 64, head, x0);
         }
       }
     }
   } else if (warp == 1) {
     // Warp-uniform descriptor arithmetic, one elected lane issues (see flash_fwd.cu).
-    const uint32_t idesc_sc = make_idesc(BT, BT, 0, 0);
+    const uint32_t idesc_sc = make_idesc(BT, BX, 0, 0);
     const uint32_t idesc_acc = make_idesc(BT, HDN, 0, 1);
     const uint64_t r1_desc = sdesc_kmajor(smem_u32(sR1)), r2_desc = sdesc_kmajor(smem_u32(sR2));
     const uint64_t ds_desc = sdesc_kmajor(smem_u32(sDS)), pt_desc = sdesc_kmajor(smem_u32(sPT));
@@ -124,18 +129,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
       // (the score accumulators are free: the previous iteration's ds_ready was awaited below)
       ok = mbar_wait(&x_full[s], ph, abort_flag, p.status, kTimeoutFull);
       if (!ok) break;
-      uint8_t* x1 = sX + s * 2 * tile_bytes;
-      uint8_t* x2 = x1 + tile_bytes;
+      uint8_t* x1 = sX + s * 2 * xtile_bytes;
+      uint8_t* x2 = x1 + xtile_bytes;
       const uint64_t x1_k = sdesc_kmajor(smem_u32(x1)), x2_k = sdesc_kmajor(smem_u32(x2));
-      const uint64_t x1_mn = sdesc_mnmajor(smem_u32(x1), 16384), x2_mn = sdesc_mnmajor(smem_u32(x2), 16384);
+      const uint64_t x1_mn = sdesc_mnmajor(smem_u32(x1), 8192), x2_mn = sdesc_mnmajor(smem_u32(x2), 8192);
       if (elect_one()) {
-        for (int k = 0; k < ks; ++k) {
-          const uint32_t off = (k >> 2) * 1024 + (k & 3) * 2;
-          umma_bf16(tS, r1_desc + off, x1_k + off, idesc_sc, k != 0);
+        for (int k = 0; k < ks; ++k) {   // 64-column blocks are 16 KB apart in the resident tile, 8 KB in the streamed one
+          const uint32_t roff = (k >> 2) * 1024 + (k & 3) * 2, xoff = (k >> 2) * 512 + (k & 3) * 2;
+          umma_bf16(tS, r1_desc + roff, x1_k + xoff, idesc_sc, k != 0);
         }
         for (int k = 0; k < ks; ++k) {
-          const uint32_t off = (k >> 2) * 1024 + (k & 3) * 2;
-          umma_bf16(tDP, r2_desc + off, x2_k + off, idesc_sc, k != 0);
+          const uint32_t roff = (k >> 2) * 1024 + (k & 3) * 2, xoff = (k >> 2) * 512 + (k & 3) * 2;
+          umma_bf16(tDP, r2_desc + roff, x2_k + xoff, idesc_sc, k != 0);
         }
         umma_commit(&sc_full);
       }
@@ -145,8 +150,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
       tc_fence_after();
       if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < BT / 16; ++k) {
-          const uint32_t aoff = (k >> 2) * 1024 + (k & 3) * 2;
+        for (int k = 0; k < BX / 16; ++k) {
+          const uint32_t aoff = (k & 3) * 2;
           if (MODE == 0) {
             umma_bf16(tA1, pt_desc + aoff, x2_mn + k * 128, idesc_acc, (it | k) != 0);  // dV += P^T dO
             umma_bf16(tA2, ds_desc + aoff, x1_mn + k * 128, idesc_acc, (it | k) != 0);  // dK += dS^T Q
@@ -169,11 +174,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
     if (MODE == 1 && grow < p.rows) { my_lse = p.lse[long(grow) * p.H + head]; my_delta = p.delta[long(grow) * p.H + head]; }
     bool ok = true;
     for (int it = 0; it < niter; ++it) {
-      const int x0 = x_first + it * BT;
+      const int x0 = x_first + it * BX;
       if (MODE == 0) {
         __syncwarp();
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < BX / 32; ++u) {
           int cc = lane + 32 * u, xr = x0 + cc;
           bool in = xr < seg_e;
           s_lse[q4][cc] = in ? p.lse[long(xr) * p.H + head] : INFINITY;   // exp2(-inf) = 0 for rows past the segment
@@ -187,7 +192,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
       if (it > 0 && !mbar_wait(&acc_done, (it - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) { ok = false; break; }
       const float* lse_c = s_lse[q4];
       const float* del_c = s_delta[q4];
-      for (int c = 0; c < BT; c += 16) {
+      for (int c = 0; c < BX; c += 16) {
         float sv[16], dv[16];
         tmem_ld16(tS + lane_off + c, sv); tmem_ld16(tDP + lane_off + c, dv);
         tmem_ld_wait();
@@ -249,7 +254,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, kTmemCols); }
 }
 
 // delta[row, h] = sum_c dO[row, h, c] * O[row, h, c]; one warp per (row, head).
@@ -270,6 +275,7 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __
 }  // namespace nb
 
 extern "C" int nb_head_map(CUtensorMap* m, const void* base, long rows, int H, int hd, long row_pitch_elems);
+extern "C" int nb_head_map_rows(CUtensorMap* m, const void* base, long rows, int H, int hd, long row_pitch_elems, int box_rows);
 
 extern "C" {
 
@@ -289,11 +295,16 @@ struct NbFlashBwdArgs {
 int nb_flash_bwd(const NbFlashBwdArgs* a, cudaStream_t stream) {
   using namespace nb;
   if (a->hd % 8 || a->hd < 8 || a->hd > 128) return -1;
-  CUtensorMap tq, tk, tv, tdo;
+  // resident tiles are fetched in boxes of 128 rows, streamed tiles in boxes of 64 rows
+  CUtensorMap tq, tk, tv, tdo, xq, xk, xv, xdo;
   if (nb_head_map(&tq, a->Q, a->rows, a->H, a->hd, a->ld_qkv)) return -10;
   if (nb_head_map(&tk, a->K, a->rows, a->H, a->hd, a->ld_qkv)) return -11;
   if (nb_head_map(&tv, a->V, a->rows, a->H, a->hd, a->ld_qkv)) return -12;
   if (nb_head_map(&tdo, a->dO, a->rows, a->H, a->hd, a->ld_do)) return -13;
+  if (nb_head_map_rows(&xq, a->Q, a->rows, a->H, a->hd, a->ld_qkv, BX)) return -14;
+  if (nb_head_map_rows(&xk, a->K, a->rows, a->H, a->hd, a->ld_qkv, BX)) return -15;
+  if (nb_head_map_rows(&xv, a->V, a->rows, a->H, a->hd, a->ld_qkv, BX)) return -16;
+  if (nb_head_map_rows(&xdo, a->dO, a->rows, a->H, a->hd, a->ld_do, BX)) return -17;
   {
     long warps = long(a->rows) * a->H;
     int threads = 256;
@@ -308,7 +319,7 @@ int nb_flash_bwd(const NbFlashBwdArgs* a, cudaStream_t stream) {
   p.lse = a->lse; p.delta = a->delta; p.ldo = a->ld_dqkv; p.status = a->status;
   const int nkb = (a->hd + 63) / 64;
   p.stages = nkb == 1 ? 2 : 1;
-  const size_t smem = size_t(nkb) * 16384 * (2 + 2 * p.stages) + 65536 + 1024;
+  const size_t smem = size_t(nkb) * (2 * 16384 + 2 * p.stages * 8192) + 32768 + 1024;
   dim3 grid(a->max_tiles, a->H);
 #define NB_LAUNCH(MODE, HDN, R1, R2, X1, X2)                                                                        \
   do {                                                                                                               \
@@ -322,9 +333,9 @@ int nb_flash_bwd(const NbFlashBwdArgs* a, cudaStream_t stream) {
     flash_bwd_kernel<MODE, HDN><<<grid, 192, smem, stream>>>(R1, R2, X1, X2, p);                                     \
   } while (0)
   p.out1 = reinterpret_cast<__nv_bfloat16*>(a->dK); p.out2 = reinterpret_cast<__nv_bfloat16*>(a->dV);
-  if (a->hd <= 64) NB_LAUNCH(0, 64, tk, tv, tq, tdo); else NB_LAUNCH(0, 128, tk, tv, tq, tdo);
+  if (a->hd <= 64) NB_LAUNCH(0, 64, tk, tv, xq, xdo); else NB_LAUNCH(0, 128, tk, tv, xq, xdo);
   p.out1 = reinterpret_cast<__nv_bfloat16*>(a->dQ); p.out2 = nullptr;
-  if (a->hd <= 64) NB_LAUNCH(1, 64, tq, tdo, tk, tv); else NB_LAUNCH(1, 128, tq, tdo, tk, tv);
+  if (a->hd <= 64) NB_LAUNCH(1, 64, tq, tdo, xk, xv); else NB_LAUNCH(1, 128, tq, tdo, xk, xv);
 #undef NB_LAUNCH
   return int(cudaGetLastError());
 }

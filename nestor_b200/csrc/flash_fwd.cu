@@ -20,7 +20,8 @@
 namespace nb {
 
 constexpr int FQ = 128;      // q rows per CTA
-constexpr int FK = 128;      // kv rows per tile
+constexpr int FK = 64;      // kv rows per tile: with 64 the CTA needs 192 TMEM columns and 64 KB of shared memory,
+                            // so two CTAs share an SM and one's softmax overlaps the other's loads and MMAs
 constexpr int kMaxSeg = 1024;
 
 struct FlashParams {
@@ -40,7 +41,7 @@ __device__ __forceinline__ void st_p_chunk(uint8_t* pbase, int row, int col0, co
 }
 
 template <int HDN>   // N of the P.V product and width of the register accumulator: 64 (hd <= 64) or 128
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, HDN == 64 ? 2 : 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -53,12 +54,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int head = blockIdx.y;
   const int nkb = (p.hd + 63) / 64;                 // 64-column blocks per operand tile
   const int hd16 = (p.hd + 15) & ~15;   // reduction width of Q K^T
-  const uint32_t tile_bytes = uint32_t(nkb) * 16384;
+  const uint32_t tile_bytes = uint32_t(nkb) * 16384;   // Q tile: 128 rows, 64-column blocks of 16 KB
+  const uint32_t ktile_bytes = uint32_t(nkb) * 8192;   // K / V tile: 64 rows, 64-column blocks of 8 KB
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + tile_bytes;          // 2 stages
-  uint8_t* sV = sK + 2 * tile_bytes;      // 2 stages
-  uint8_t* sP = sV + 2 * tile_bytes;      // 2 blocks of 16 KB
+  uint8_t* sV = sK + 2 * ktile_bytes;     // 2 stages
+  uint8_t* sP = sV + 2 * ktile_bytes;     // 128 rows x 64 kv columns: one 16 KB block
 
   if (threadIdx.x == 0) {
     // locate this CTA's q tile: tiles are numbered segment by segment, heaviest (last) q tile first
@@ -79,14 +81,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
   __syncthreads();
   if (!s_tile[3]) return;                          // grid is an upper bound on the tile count
-  if (warp == 1) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
+  if (warp == 1) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  const uint32_t tS0 = tmem, tO = tmem + 256;
+  const uint32_t tS0 = tmem, tO = tmem + 2 * FK;        // S double-buffered in columns [0, 128), O from 128
   const int seg_b = s_tile[0], seg_e = s_tile[1], q0 = s_tile[2];
-  const int ntiles = (q0 - seg_b) / FK + 1;        // kv tiles up to and including the diagonal
+  const int ntiles = (min(q0 + FQ, seg_e) - seg_b + FK - 1) / FK;   // kv tiles up to and including the diagonal
   volatile int* abort_flag = &s_abort;
 
   if (warp == 0) {
@@ -96,11 +98,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int j = 0; j < ntiles; ++j) {
         int s = j & 1;
         if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kTimeoutEmpty)) break;
-        mbar_expect_tx(&kv_full[s], 2 * tile_bytes);
+        mbar_expect_tx(&kv_full[s], 2 * ktile_bytes);
         int r0 = seg_b + j * FK;
         for (int b = 0; b < nkb; ++b) {
-          tma_load_3d(sK + s * tile_bytes + b * 16384, &tmK, &kv_full[s], b * 64, head, r0);
-          tma_load_3d(sV + s * tile_bytes + b * 16384, &tmV, &kv_full[s], b * 64, head, r0);
+          tma_load_3d(sK + s * ktile_bytes + b * 8192, &tmK, &kv_full[s], b * 64, head, r0);
+          tma_load_3d(sV + s * ktile_bytes + b * 8192, &tmV, &kv_full[s], b * 64, head, r0);
         }
       }
     }
@@ -119,12 +121,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int s = j & 1;
       ok = mbar_wait(&kv_full[s], (j >> 1) & 1, abort_flag, p.status, kTimeoutFull);
       if (!ok) return;
-      const uint64_t k_desc = sdesc_kmajor(smem_u32(sK + s * tile_bytes));
+      const uint64_t k_desc = sdesc_kmajor(smem_u32(sK + s * ktile_bytes));
       const uint32_t d_addr = tS0 + s * FK;
       if (elect_one()) {
         for (int k = 0; k < ks; ++k) {
-          const uint32_t off = (k >> 2) * 1024 + (k & 3) * 2;     // (64-column block, 32 B per K step) in 16-byte units
-          umma_bf16(d_addr, q_desc + off, k_desc + off, idesc_s, k != 0);
+          // (64-column block, 32 B per K step) in 16-byte units; blocks are 16 KB apart in Q, 8 KB in K
+          const uint32_t qoff = (k >> 2) * 1024 + (k & 3) * 2, koff = (k >> 2) * 512 + (k & 3) * 2;
+          umma_bf16(d_addr, q_desc + qoff, k_desc + koff, idesc_s, k != 0);
         }
         umma_commit(&s_full[s]);
       }
@@ -138,11 +141,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (!ok) break;
       tc_fence_after();
       const int s = j & 1;
-      const uint64_t v_desc = sdesc_mnmajor(smem_u32(sV + s * tile_bytes), 16384);
+      const uint64_t v_desc = sdesc_mnmajor(smem_u32(sV + s * ktile_bytes), 8192);
       if (elect_one()) {
 #pragma unroll
         for (int k = 0; k < FK / 16; ++k)
-          umma_bf16(tO, p_desc + ((k >> 2) * 1024 + (k & 3) * 2), v_desc + k * 128, idesc_o, k != 0);
+          umma_bf16(tO, p_desc + (k & 3) * 2, v_desc + k * 128, idesc_o, k != 0);
         umma_commit(&kv_empty[s]);
         umma_commit(&o_full);
       }
@@ -165,7 +168,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_after();
       const uint32_t ts = tS0 + s * FK + lane_off;
       const int kv0 = seg_b + j * FK;
-      const int lim = (j == ntiles - 1) ? (qrow - kv0 + 1) : FK;   // columns < lim are visible (causal)
+      const int lim = min(FK, qrow - kv0 + 1);     // columns < lim are visible (causal); the diagonal spans two tiles
       // pass 1: row max
       float mx = m;
       for (int c = 0; c < FK; c += 32) {
@@ -242,7 +245,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 256); }
 }
 
 }  // namespace nb
@@ -267,17 +270,22 @@ EncodeFn flash_encode_fn() {
 
 // [rows, H, hd] view of a bf16 buffer: element (r, h, c) at base + r*row_pitch + h*hd + c.
 // Box = 64 columns x 1 head x 128 rows; columns past `hd` read as zero.
-extern "C" int nb_head_map(CUtensorMap* m, const void* base, long rows, int H, int hd, long row_pitch_elems) {
+extern "C" int nb_head_map_rows(CUtensorMap* m, const void* base, long rows, int H, int hd, long row_pitch_elems,
+                                int box_rows) {
   EncodeFn fn = flash_encode_fn();
   if (!fn) return 1;
   cuuint64_t gd[3] = {cuuint64_t(hd), cuuint64_t(H), cuuint64_t(rows)};
   cuuint64_t gs[2] = {cuuint64_t(hd) * 2, cuuint64_t(row_pitch_elems) * 2};
-  cuuint32_t bx[3] = {64, 1, 128};
+  cuuint32_t bx[3] = {64, 1, cuuint32_t(box_rows)};
   cuuint32_t es[3] = {1, 1, 1};
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), gd, gs, bx, es,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : 2;
+}
+
+extern "C" int nb_head_map(CUtensorMap* m, const void* base, long rows, int H, int hd, long row_pitch_elems) {
+  return nb_head_map_rows(m, base, rows, H, hd, row_pitch_elems, 128);
 }
 
 extern "C" {
@@ -300,14 +308,14 @@ int nb_flash_fwd(const NbFlashArgs* a, cudaStream_t stream) {
   if (a->nseg < 1 || a->nseg > kMaxSeg) return -2;
   CUtensorMap tq, tk, tv;
   if (nb_head_map(&tq, a->Q, a->rows, a->H, a->hd, a->ld_qkv)) return -10;
-  if (nb_head_map(&tk, a->K, a->rows, a->H, a->hd, a->ld_qkv)) return -11;
-  if (nb_head_map(&tv, a->V, a->rows, a->H, a->hd, a->ld_qkv)) return -12;
+  if (nb_head_map_rows(&tk, a->K, a->rows, a->H, a->hd, a->ld_qkv, FK)) return -11;
+  if (nb_head_map_rows(&tv, a->V, a->rows, a->H, a->hd, a->ld_qkv, FK)) return -12;
   FlashParams p;
   p.nseg = a->nseg; p.H = a->H; p.hd = a->hd; p.rows = a->rows; p.seg_start = a->seg_start;
   p.scale_log2 = a->scale * 1.4426950408889634f;
   p.O = reinterpret_cast<__nv_bfloat16*>(a->O); p.ldo = a->ldo; p.lse = a->lse; p.status = a->status;
   const int nkb = (a->hd + 63) / 64;
-  size_t smem = size_t(nkb) * 16384 * 5 + 32768 + 1024;
+  size_t smem = size_t(nkb) * (16384 + 4 * 8192) + 16384 + 1024;
   dim3 grid(a->max_tiles, a->H);
   if (a->hd <= 64) {
     static bool set64 = false;

@@ -149,13 +149,15 @@ __global__ void route_bwd_kernel(RouteBwdArgs a) {
 }
 
 // ------------------------------------------------------------------------------- expert plan
-// n elements (flat token*slots + slot order), ids in [0, E), E <= 64. Blocks of kPlanBlock elements.
+// n elements (flat token*slots + slot order), ids in [0, E), E <= kMaxKeys. Blocks of kPlanBlock elements.
+// The same sort builds the packed-attention plan of a block with key = column * B + sequence.
 constexpr int kPlanBlock = 1024;
+constexpr int kMaxKeys = 256;
 
 // Per-block histogram. hist[blk * E + e].
 __global__ void plan_hist_kernel(const int* __restrict__ ids, int n, int E, int* __restrict__ hist) {
-  __shared__ int s_h[kMaxE];
-  if (threadIdx.x < kMaxE) s_h[threadIdx.x] = 0;
+  __shared__ int s_h[kMaxKeys];
+  if (threadIdx.x < kMaxKeys) s_h[threadIdx.x] = 0;
   __syncthreads();
   const int i = blockIdx.x * kPlanBlock + threadIdx.x;
   if (i < n) atomicAdd(&s_h[ids[i]], 1);
@@ -166,7 +168,7 @@ __global__ void plan_hist_kernel(const int* __restrict__ ids, int n, int E, int*
 // One block: exclusive scan of every expert's counts over the blocks (hist becomes the block's base inside the
 // expert's range) and the expert offsets.
 __global__ void plan_scan_kernel(int* __restrict__ hist, int nblk, int E, int* __restrict__ offsets) {
-  __shared__ int s_tot[kMaxE + 1];
+  __shared__ int s_tot[kMaxKeys + 1];
   const int e = threadIdx.x;
   if (e < E) {
     int run = 0;
@@ -184,9 +186,9 @@ __global__ void plan_scan_kernel(int* __restrict__ hist, int nblk, int E, int* _
 // Stable placement: element i goes to offsets[e] + base[blk][e] + (number of earlier elements of e in the block).
 __global__ void plan_place_kernel(const int* __restrict__ ids, int n, int E, const int* __restrict__ base,
                                   const int* __restrict__ offsets, int* __restrict__ order, int* __restrict__ inv) {
-  __shared__ int s_w[kPlanBlock / 32][kMaxE];     // per-warp counts, then exclusive prefix over the warps
+  __shared__ int s_w[kPlanBlock / 32][kMaxKeys];  // per-warp counts, then exclusive prefix over the warps
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int j = threadIdx.x; j < (kPlanBlock / 32) * kMaxE; j += blockDim.x) (&s_w[0][0])[j] = 0;
+  for (int j = threadIdx.x; j < (kPlanBlock / 32) * kMaxKeys; j += blockDim.x) (&s_w[0][0])[j] = 0;
   __syncthreads();
   const int i = blockIdx.x * kPlanBlock + threadIdx.x;
   const bool live = i < n;
@@ -205,6 +207,26 @@ __global__ void plan_place_kernel(const int* __restrict__ ids, int n, int E, con
     inv[i] = pos;
     order[pos] = i;
   }
+}
+
+// Packed-attention plan from the sort of keys column * B + sequence: per packed row its token, slot and position.
+__global__ void column_plan_finish_kernel(const int* __restrict__ order, int rows, int k, const int* __restrict__ pos,
+                                          int S, int* __restrict__ tok_of_row, int* __restrict__ slot_of_row,
+                                          int* __restrict__ pos_of_row) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  const int flat = order[r];
+  const int t = flat / k;
+  tok_of_row[r] = t;
+  slot_of_row[r] = flat - t * k;
+  pos_of_row[r] = pos ? max(pos[t], 0) : t % S;
+}
+
+// keys[t * k + j] = idx[t, j] * B + t / S
+__global__ void column_plan_keys_kernel(const int* __restrict__ idx, int n, int k, int S, int B, int* __restrict__ keys) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  keys[i] = idx[i] * B + (i / k) / S;
 }
 
 }  // namespace nbr
@@ -261,11 +283,24 @@ int nb_route_bwd(const NbRouteArgs* a, const float* dgates, const void* dw, void
 
 // ids [n] int32 in [0, E). scratch: int32 [ceil(n / 1024) * E]. Outputs: order [n], inv [n], offsets [E + 1].
 int nb_expert_plan(const int* ids, int n, int E, int* scratch, int* order, int* inv, int* offsets, cudaStream_t st) {
-  if (E < 1 || E > nbr::kMaxE || n < 0) return -1;
+  if (E < 1 || E > nbr::kMaxKeys || n < 0) return -1;
   const int nblk = (n + nbr::kPlanBlock - 1) / nbr::kPlanBlock;
   if (nblk > 0) nbr::plan_hist_kernel<<<nblk, nbr::kPlanBlock, 0, st>>>(ids, n, E, scratch);
-  nbr::plan_scan_kernel<<<1, 64, 0, st>>>(scratch, nblk, E, offsets);
+  nbr::plan_scan_kernel<<<1, nbr::kMaxKeys, 0, st>>>(scratch, nblk, E, offsets);
   if (nblk > 0) nbr::plan_place_kernel<<<nblk, nbr::kPlanBlock, 0, st>>>(ids, n, E, scratch, offsets, order, inv);
+  return int(cudaGetLastError());
+}
+
+// Packed-attention plan of one block. idx [T, k] int32 columns (T = B * S tokens), pos [T] int32 or null.
+// keys / order / inv: int32 [T * k]; seg_start: int32 [G * B + 1]; scratch: int32 [ceil(T * k / 1024) * G * B].
+int nb_column_plan(const int* idx, int T, int k, int S, int B, int G, const int* pos, int* keys, int* scratch, int* order,
+                   int* inv, int* seg_start, int* tok_of_row, int* slot_of_row, int* pos_of_row, cudaStream_t st) {
+  const int n = T * k;
+  if (G * B > nbr::kMaxKeys || n <= 0) return -1;
+  nbr::column_plan_keys_kernel<<<(n + 255) / 256, 256, 0, st>>>(idx, n, k, S, B, keys);
+  int rc = nb_expert_plan(keys, n, G * B, scratch, order, inv, seg_start, st);
+  if (rc) return rc;
+  nbr::column_plan_finish_kernel<<<(n + 255) / 256, 256, 0, st>>>(order, n, k, pos, S, tok_of_row, slot_of_row, pos_of_row);
   return int(cudaGetLastError());
 }
 

@@ -49,6 +49,8 @@ def _L():
         for fn in (L.nb_mid_source, L.nb_layer_combine, L.nb_layer_combine_bwd, L.nb_block_exit, L.nb_block_exit_bwd):
             fn.restype = C.c_int
         L.nb_expert_plan.argtypes = [vp, i, i, vp, vp, vp, vp, vp]
+        L.nb_column_plan.argtypes = [vp, i, i, i, i, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+        L.nb_column_plan.restype = C.c_int
         L.nb_route_fwd.argtypes = [vp, vp]
         L.nb_route_bwd.argtypes = [vp, vp, vp, vp, l, i, vp, vp]
         for fn in (L.nb_expert_plan, L.nb_route_fwd, L.nb_route_bwd):
@@ -588,13 +590,33 @@ def block_exit(streams):
 
 # ------------------------------------------------------------------------------ plans
 def build_column_plan(idx, G_, pos=None):
-    return ref.build_column_plan(idx, G_, pos)
+    """Packed-attention plan by a counting sort on (column, sequence) keys: five small kernels."""
+
+    B, S, k = idx.shape
+    if G_ * B > 256:
+        return ref.build_column_plan(idx, G_, pos)
+    dev = idx.device
+    T, n = B * S, B * S * k
+    i32 = torch.int32
+    idx32 = idx.reshape(T, k).to(i32).contiguous()
+    p32 = None if pos is None else pos.reshape(-1).to(i32).contiguous()
+    keys, order, inv = (torch.empty(n, dtype=i32, device=dev) for _ in range(3))
+    tok, slot, prow = (torch.empty(n, dtype=i32, device=dev) for _ in range(3))
+    seg = torch.empty(G_ * B + 1, dtype=i32, device=dev)
+    scratch = torch.empty(max(1, -(-n // 1024)) * G_ * B, dtype=i32, device=dev)
+    _ck(_L().nb_column_plan(idx32.data_ptr(), T, k, S, B, G_, _ptr(p32), keys.data_ptr(), scratch.data_ptr(),
+                            order.data_ptr(), inv.data_ptr(), seg.data_ptr(), tok.data_ptr(), slot.data_ptr(),
+                            prow.data_ptr(), _st()), "column_plan")
+    _lib.count_launch(4)
+    return ColumnPlan(B=B, S=S, G=G_, k=k, idx=idx32, row_of_slot=inv.view(T, k), tok_of_row=tok, slot_of_row=slot,
+                      pos_of_row=prow, seg_start=seg, col_start=seg[::B].contiguous(),
+                      extra={"slot_flat": order})      # the sorted flat (token * k + slot) index of every packed row
 
 
 def build_expert_plan(expert_ids, E):
     """Counting sort by expert (three small kernels; the oracle sorts)."""
 
-    if E > 64:
+    if E > 256:
         return ref.build_expert_plan(expert_ids, E)
     T, slots = expert_ids.shape
     ids = expert_ids.reshape(-1)

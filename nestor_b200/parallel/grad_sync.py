@@ -36,9 +36,11 @@ class GradReducer:
             transport = os.environ.get("NESTOR_B200_GRAD_TRANSPORT", "fused" if arena.grad.is_cuda else "gloo")
         self.transport = transport
         self._fused = None
+        self._fused_rs = None
         if self.world > 1 and transport == "fused":
-            from nestor_b200.parallel.symm import FusedAllReduce
+            from nestor_b200.parallel.symm import FusedAllReduce, FusedReduceScatter
             self._fused = FusedAllReduce(arena.grad, self.buckets)
+            self._fused_rs = FusedReduceScatter(arena.grad)
 
     @torch.no_grad()
     def reduce(self) -> None:
@@ -55,6 +57,19 @@ class GradReducer:
         for w in works:
             w.wait()
         self.arena.grad.mul_(1.0 / self.world)
+
+    @torch.no_grad()
+    def reduce_scatter(self, lo: int, hi: int) -> None:
+        """Average ``arena.grad[lo:hi]`` (this rank's ownership range) over ranks; the rest of the local
+        gradient buffer keeps this rank's partial sums, which nothing reads (sharded optimizer)."""
+
+        if self.world == 1:
+            return
+        if self._fused_rs is not None:
+            self._fused_rs.run(lo, hi, 1.0 / self.world)
+            return
+        # library transports have no ragged reduce-scatter over arena ranges: reduce everything
+        self.reduce()
 
     @torch.no_grad()
     def sync_buffers(self, model: torch.nn.Module, src: int = 0) -> None:

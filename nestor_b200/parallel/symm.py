@@ -44,6 +44,8 @@ def _L():
     if not _protos:
         vp, i, l, f, u = C.c_void_p, C.c_int, C.c_long, C.c_float, C.c_uint
         L.nb_allreduce_push.argtypes = [C.POINTER(Peers), l, l, f, i, u, l, i, vp, vp]
+        L.nb_reduce_scatter_push.argtypes = [C.POINTER(Peers), l, l, f, i, u, l, i, vp, vp]
+        L.nb_reduce_scatter_push.restype = C.c_int
         L.nb_param_push.argtypes = [C.POINTER(Peers), l, l, u, l, i, vp, vp]
         L.nb_wait_timeout_probe.argtypes = [vp, u, l, vp, vp]
         for fn in (L.nb_allreduce_push, L.nb_param_push, L.nb_wait_timeout_probe):
@@ -136,6 +138,24 @@ class FusedAllReduce:
                 tail = g.main[off + n4 : off + n]
                 dist.all_reduce(tail)
                 tail.mul_(scale)
+
+
+class FusedReduceScatter:
+    """Sum a symmetric fp32 buffer over ranks, each rank keeping only the range it owns (one kernel)."""
+
+    def __init__(self, grad: torch.Tensor, mirror: torch.Tensor | None = None) -> None:
+        self.group = PeerGroup(grad, mirror)
+        self.mirror = mirror is not None
+
+    @torch.no_grad()
+    def run(self, lo: int, hi: int, scale: float) -> None:
+        g = self.group
+        assert lo % 4 == 0 and hi % 4 == 0
+        rc = _L().nb_reduce_scatter_push(C.byref(g.peers), lo, hi, scale, int(self.mirror), PeerGroup.next_epoch(),
+                                         wait_budget(), g.blocks, g.status.data_ptr(), C.c_void_p(_lib.stream_ptr()))
+        if rc != 0:
+            raise RuntimeError(f"nb_reduce_scatter_push failed with code {rc}")
+        _lib.count_launch()
 
 
 class ParamPush:

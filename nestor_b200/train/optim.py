@@ -90,6 +90,10 @@ class MuonAdamW(Optimizer):
         self.arena = arena
         self.owner_cuts: list[int] | None = None   # arena offsets where ownership changes (contiguous mode)
         self._assign_owners()
+        # ZeRO-1 for AdamW too (the reference's NESTOR_ZERO1): needs the arena ranges and a parameter distribution step
+        # (off until the owner of a range also distributes its AdamW parameters: the trainer turns it on together
+        # with the parameter push)
+        self.shard_adamw = False
 
     # ------------------------------------------------------------------ ownership
     def _assign_owners(self) -> None:
@@ -138,6 +142,15 @@ class MuonAdamW(Optimizer):
 
     def owns(self, p: Tensor) -> bool:
         return (not self.sharded) or self.owner.get(p, self.rank) == self.rank
+
+    def owns_adamw(self, p: Tensor) -> bool:
+        """AdamW parameters follow the arena ownership ranges when the optimizer state is fully sharded
+        (``shard_adamw``): the owner of a range updates everything in it and distributes the range."""
+
+        if not (self.sharded and self.shard_adamw and self.owner_cuts is not None):
+            return True
+        off = self.arena.slot(p).offset
+        return self.owner_cuts[self.rank] <= off < self.owner_cuts[self.rank + 1]
 
     # ------------------------------------------------------------------------ step
     @torch.no_grad()
@@ -197,7 +210,7 @@ class MuonAdamW(Optimizer):
         lr, (b1, b2), eps, wd = group["lr"], group["betas"], group["eps"], group["weight_decay"]
         params, grads, m1, m2, steps = [], [], [], [], []
         for p in group["params"]:
-            if p.grad is None:
+            if p.grad is None or not self.owns_adamw(p):
                 continue
             st = self.state[p]
             if not st:
@@ -246,6 +259,25 @@ class MuonAdamW(Optimizer):
                 dist.broadcast(buf, src=owner)
                 if self.rank == to and owner != self.rank:
                     self._consolidated[p] = buf
+        self._consolidated_adamw: dict[Tensor, dict[str, Any]] = {}
+        if self.shard_adamw:
+            for g in self.param_groups:
+                if g.get("method") == "muon":
+                    continue
+                for p in g["params"]:
+                    off = self.arena.slot(p).offset
+                    owner = max(r for r in range(self.world) if self.owner_cuts[r] <= off)
+                    st = self.state.get(p, {}) if owner == self.rank else {}
+                    step = torch.tensor([float(st.get("step", 0))], device=p.device)
+                    dist.broadcast(step, src=owner)
+                    bufs = {}
+                    for key in ("exp_avg", "exp_avg_sq"):
+                        b = st.get(key)
+                        b = torch.zeros_like(p, memory_format=torch.contiguous_format) if b is None else b
+                        dist.broadcast(b, src=owner)
+                        bufs[key] = b
+                    if self.rank == to and owner != self.rank and step.item() > 0:
+                        self._consolidated_adamw[p] = {"step": int(step.item()), **bufs}
 
     def state_dict(self) -> dict[str, Any]:
         """Unsharded torch-format state dict (momentum of every Muon parameter present)."""
@@ -256,12 +288,20 @@ class MuonAdamW(Optimizer):
             if "momentum_buffer" not in self.state[p]:
                 self.state[p]["momentum_buffer"] = buf
                 added.append(p)
+        added_adamw = []
+        for p, st in getattr(self, "_consolidated_adamw", {}).items():
+            if not self.state.get(p):
+                self.state[p] = dict(st)
+                added_adamw.append(p)
         try:
             return super().state_dict()
         finally:
             for p in added:
                 del self.state[p]["momentum_buffer"]
+            for p in added_adamw:
+                del self.state[p]
             self._consolidated = {}
+            self._consolidated_adamw = {}
 
     def load_state_dict(self, state_dict: dict[str, Any]) -> None:
         super().load_state_dict(state_dict)
@@ -269,6 +309,12 @@ class MuonAdamW(Optimizer):
             for p, owner in self.owner.items():
                 if owner != self.rank and p in self.state:
                     self.state[p].pop("momentum_buffer", None)
+            if self.shard_adamw:
+                for g in self.param_groups:
+                    if g.get("method") != "muon":
+                        for p in g["params"]:
+                            if not self.owns_adamw(p):
+                                self.state.pop(p, None)
 
 
 @torch.no_grad()

@@ -77,6 +77,10 @@ class Trainer:
             from nestor_b200.parallel.symm import ParamPush
             self.param_push = ParamPush(self.arena.master, self.arena.compute)
             self.optimizer.param_sync = lambda opt: None      # distribution happens after the compute-copy refresh
+            # the pushed range carries every parameter in it, so its owner can be the only one to update them
+            # (ZeRO-1 for AdamW as well) and the only one that needs their reduced gradients (reduce-scatter)
+            self.optimizer.shard_adamw = os.environ.get("NESTOR_ZERO1", "1") == "1"
+        self.zero = bool(self.param_push is not None and self.optimizer.shard_adamw)
         self.global_step, self.epoch = 0, 0
         self.ema: dict[str, Tensor] | None = None
         decay = os.environ.get("NESTOR_EMA_DECAY")
@@ -173,13 +177,25 @@ class Trainer:
     def clip_grad_norm(self, max_norm: float) -> Tensor:
         """Global L2 clip on the flat gradient buffer (one reduction, one scale)."""
 
+        if self.zero:
+            # every rank holds the reduced gradient of its own range only: partial sums of squares, one scalar reduce
+            lo, hi = self.optimizer.owned_range()
+            own = self.arena.grad[lo:hi]
+            sq = torch.linalg.vector_norm(own).square()
+            torch.distributed.all_reduce(sq)
+            norm = sq.sqrt()
+            own.mul_((max_norm / (norm + 1e-6)).clamp(max=1.0))
+            return norm
         norm = torch.linalg.vector_norm(self.arena.grad)
         scale = (max_norm / (norm + 1e-6)).clamp(max=1.0)
         self.arena.grad.mul_(scale)
         return norm
 
     def update_weights(self, window_counts: dict[str, Tensor]) -> Tensor | None:
-        self.reducer.reduce()
+        if self.zero:
+            self.reducer.reduce_scatter(*self.optimizer.owned_range())
+        else:
+            self.reducer.reduce()
         norm = None
         if self.config.max_grad_norm is not None:
             norm = self.clip_grad_norm(self.config.max_grad_norm)

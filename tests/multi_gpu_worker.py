@@ -31,6 +31,22 @@ def main() -> None:
     torch.cuda.synchronize()
     far.group.check()
     assert (g - ref).abs().max().item() < 1e-6, "fused all-reduce mismatch"
+    # reduce-scatter with ragged ownership ranges: every rank ends with the average of its own range only
+    g.copy_(torch.randn(N, device=dev) * 1e-3)
+    ref = g.clone()
+    dist.all_reduce(ref)
+    ref /= world
+    cuts = [0] + [((N * (r + 1) // world) + 4096 * (r % 2)) // 4 * 4 for r in range(world - 1)] + [N]
+    lo, hi = cuts[rank], cuts[rank + 1]
+    mine = g.clone()
+    frs = symm.FusedReduceScatter(g)
+    dist.barrier()
+    frs.run(lo, hi, 1.0 / world)
+    torch.cuda.synchronize()
+    frs.group.check()
+    assert (g[lo:hi] - ref[lo:hi]).abs().max().item() < 1e-6, "fused reduce-scatter mismatch"
+    assert torch.equal(g[:lo], mine[:lo]) and torch.equal(g[hi:], mine[hi:]), "reduce-scatter wrote outside its range"
+    dist.barrier()
     M = 4 * 1024 * 1024
     master, comp = symm.symmetric_empty(M, torch.float32, dev), symm.symmetric_empty(M, torch.bfloat16, dev)
     master.fill_(float(rank + 1))
@@ -49,23 +65,35 @@ def main() -> None:
     from nestor_b200.experiments.tiny import nestor_tiny
     from nestor_b200.models import Model
     from nestor_b200.train.trainer import Trainer
-    torch.manual_seed(0)
-    job = nestor_tiny().jobs[0]
-    tr = Trainer(job, Model.from_config(job.model), [], device=dev)
-    assert tr.param_push is not None and tr.reducer.transport == "fused"
-    tr.model.train()
-    for step in range(3):
-        torch.manual_seed(1000 + step * 10 + rank)
-        ids = torch.randint(0, 100277, (2, 256), device=dev)
-        loss, counts = tr.train_step((ids, ids))
-        tr.update_weights(counts)
-    torch.cuda.synchronize()
-    _lib.check_status(dev)
-    chk = torch.tensor([tr.arena.master.double().sum().item(), tr.arena.compute.double().sum().item()], device=dev,
-                       dtype=torch.float64)
-    gathered = [torch.zeros_like(chk) for _ in range(world)]
-    dist.all_gather(gathered, chk)
-    assert all(torch.equal(x, gathered[0]) for x in gathered), "replicas diverged"
+    results = {}
+    for zero in ("1", "0"):     # sharded optimizer state + reduce-scatter, then replicated AdamW + all-reduce
+        os.environ["NESTOR_ZERO1"] = zero
+        torch.manual_seed(0)
+        job = nestor_tiny().jobs[0]
+        tr = Trainer(job, Model.from_config(job.model), [], device=dev)
+        assert tr.param_push is not None and tr.reducer.transport == "fused" and tr.zero == (zero == "1")
+        tr.model.train()
+        for step in range(3):
+            torch.manual_seed(1000 + step * 10 + rank)
+            ids = torch.randint(0, 100277, (2, 256), device=dev)
+            loss, counts = tr.train_step((ids, ids))
+            tr.update_weights(counts)
+        torch.cuda.synchronize()
+        _lib.check_status(dev)
+        chk = torch.tensor([tr.arena.master.double().sum().item(), tr.arena.compute.double().sum().item()], device=dev,
+                           dtype=torch.float64)
+        gathered = [torch.zeros_like(chk) for _ in range(world)]
+        dist.all_gather(gathered, chk)
+        assert all(torch.equal(x, gathered[0]) for x in gathered), "replicas diverged"
+        results[zero] = tr.arena.master.clone()
+        sd = None
+        tr.optimizer.consolidate_state_dict()
+        if rank == 0:
+            sd = tr.optimizer.state_dict()
+            assert len(sd["state"]) == sum(len(g["params"]) for g in sd["param_groups"]), "optimizer state incomplete"
+        del tr
+    rel = ((results["1"] - results["0"]).norm() / results["0"].norm()).item()
+    assert rel < 1e-5, f"sharded and replicated optimizer paths disagree: {rel}"
     if rank == 0:
         print("MULTI_GPU_OK", flush=True)
     dist.destroy_process_group()

@@ -357,3 +357,14 @@ def test_multi_tensor_optimizer_matches_foreach(monkeypatch):
             ob.step()
     for x, y in zip(pa, pb):
         assert _rel(x, y) < 1e-5
+
+
+def test_column_plan_kernel_matches_oracle():
+    from nestor_b200.ops import cuda as K, reference as R
+    torch.manual_seed(11)
+    for (B, S, Gc, k, with_pos) in [(4, 512, 8, 3, False), (2, 300, 8, 6, True), (16, 64, 8, 8, False)]:
+        idx = torch.rand(B, S, Gc, device="cuda").topk(k, dim=-1).indices
+        pos = torch.randint(0, 4 * S, (B, S), device="cuda") if with_pos else None
+        a, b = K.build_column_plan(idx, Gc, pos), R.build_column_plan(idx, Gc, pos)
+        for f in ("row_of_slot", "tok_of_row", "slot_of_row", "pos_of_row", "seg_start", "col_start", "idx"):
+            assert torch.equal(getattr(a, f).long(), getattr(b, f).long()), f
