@@ -350,12 +350,17 @@ __global__ void depth_read_norm_bwd_kernel(SourceList src, GradList dsrc, int n,
   const int lane = threadIdx.x, wy = threadIdx.y;
   const int nchunk = d / 4;
   const float inv_sqrt_d = rsqrtf(float(d));
-  float4 qv[NV], gq[NV], gg[NV];
+  // The norm-weight gradient accumulates in this warp's row of s_red (one read-modify-write per token) instead of
+  // registers: the kernel is bound by memory latency at low occupancy, and 20 registers fewer is one more block per SM.
+  __shared__ float s_red[4][kMaxDepthDim];
+  float4* gg_acc = reinterpret_cast<float4*>(&s_red[wy][0]);
+  float4 qv[NV], gq[NV];
 #pragma unroll
   for (int v = 0; v < NV; ++v) {
     int c = lane + 32 * v;
     qv[v] = c < nchunk ? reinterpret_cast<const float4*>(query)[c] : make_float4(0, 0, 0, 0);
-    gq[v] = make_float4(0, 0, 0, 0); gg[v] = make_float4(0, 0, 0, 0);
+    gq[v] = make_float4(0, 0, 0, 0);
+    if (c < nchunk) gg_acc[c] = make_float4(0, 0, 0, 0);
   }
   float dgain_acc[2] = {0.f, 0.f};   // lane owns sources lane and lane + 32
   for (int t = blockIdx.x * blockDim.y + wy; t < T; t += gridDim.x * blockDim.y) {
@@ -404,8 +409,10 @@ __global__ void depth_read_norm_bwd_kernel(SourceList src, GradList dsrc, int n,
           __nv_bfloat162 p0 = *reinterpret_cast<__nv_bfloat162*>(&raw.x), p1 = *reinterpret_cast<__nv_bfloat162*>(&raw.y);
           float4 g = reinterpret_cast<const float4*>(gamma)[c];
           float4 dy = make_float4(bf(p0.x), bf(p0.y), bf(p1.x), bf(p1.y));
-          gg[v].x += dy.x * h[v].x * rstd; gg[v].y += dy.y * h[v].y * rstd;
-          gg[v].z += dy.z * h[v].z * rstd; gg[v].w += dy.w * h[v].w * rstd;
+          float4 ga = gg_acc[c];
+          ga.x += dy.x * h[v].x * rstd; ga.y += dy.y * h[v].y * rstd;
+          ga.z += dy.z * h[v].z * rstd; ga.w += dy.w * h[v].w * rstd;
+          gg_acc[c] = ga;
           dh[v] = make_float4(dy.x * g.x, dy.y * g.y, dy.z * g.z, dy.w * g.w);
           dot += dh[v].x * h[v].x + dh[v].y * h[v].y + dh[v].z * h[v].z + dh[v].w * h[v].w;
         }
@@ -472,20 +479,20 @@ __global__ void depth_read_norm_bwd_kernel(SourceList src, GradList dsrc, int n,
     __syncwarp();
   }
   // parameter gradients: sum the block's four warps through shared memory, write the block's partial row
-  __shared__ float s_red[4][kMaxDepthDim];
   const int tid = wy * 32 + lane, stride = 2 * d + 64;
   float* prow = partial + long(blockIdx.x) * stride;
-  for (int pass = 0; pass < 2; ++pass) {
-    if (pass == 1 && !has_gamma) break;
+  __syncthreads();                                   // every warp's gamma row is complete
+  if (has_gamma)
+    for (int j = tid; j < d; j += 128) prow[d + j] = s_red[0][j] + s_red[1][j] + s_red[2][j] + s_red[3][j];
+  __syncthreads();
 #pragma unroll
-    for (int v = 0; v < NV; ++v) {
-      int c = lane + 32 * v;
-      if (c < nchunk) reinterpret_cast<float4*>(&s_red[wy][0])[c] = pass == 0 ? gq[v] : gg[v];
-    }
-    __syncthreads();
-    for (int j = tid; j < d; j += 128) prow[pass * d + j] = s_red[0][j] + s_red[1][j] + s_red[2][j] + s_red[3][j];
-    __syncthreads();
+  for (int v = 0; v < NV; ++v) {
+    int c = lane + 32 * v;
+    if (c < nchunk) gg_acc[c] = gq[v];
   }
+  __syncthreads();
+  for (int j = tid; j < d; j += 128) prow[j] = s_red[0][j] + s_red[1][j] + s_red[2][j] + s_red[3][j];
+  __syncthreads();
   s_red[wy][lane] = dgain_acc[0]; s_red[wy][lane + 32] = dgain_acc[1];
   __syncthreads();
   if (tid < 64) prow[2 * d + tid] = s_red[0][tid] + s_red[1][tid] + s_red[2][tid] + s_red[3][tid];

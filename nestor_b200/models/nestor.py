@@ -20,6 +20,8 @@ and matrix products run in the compute dtype ``cd``.
 
 from __future__ import annotations
 
+import os
+
 import math
 from typing import Any
 
@@ -309,9 +311,17 @@ class Nestor(nn.Module):
         wide = [x0]              # what the head read sees: every export
         x = x0
         aux = []
+        # NESTOR_ACTIVATION_CHECKPOINT=1: keep only each block's inputs and recompute its activations in the
+        # backward pass (the reference's per-block checkpointing, nestor/train/activation_offload.py:13-35). The
+        # recomputation replays the random state, and the kernels are deterministic, so routing repeats exactly.
+        recompute = os.environ.get("NESTOR_ACTIVATION_CHECKPOINT") == "1" and torch.is_grad_enabled() and self.training
         for i, block in enumerate(self.blocks):
-            exports, x, a = block(x, narrow, B, S, cd, pos, self.column_mode,
-                                  None if noises is None else noises[i])
+            noise = None if noises is None else noises[i]
+            if recompute:
+                from torch.utils.checkpoint import checkpoint
+                exports, x, a = checkpoint(block, x, narrow, B, S, cd, pos, self.column_mode, noise, use_reentrant=False)
+            else:
+                exports, x, a = block(x, narrow, B, S, cd, pos, self.column_mode, noise)
             exports = [ops.grad_sink(e) for e in exports]
             x = exports[-1]      # the aggregate is the block's last export
             wide.extend(exports)

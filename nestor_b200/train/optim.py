@@ -91,9 +91,9 @@ class MuonAdamW(Optimizer):
         self.owner_cuts: list[int] | None = None   # arena offsets where ownership changes (contiguous mode)
         self._assign_owners()
         # ZeRO-1 for AdamW too (the reference's NESTOR_ZERO1): needs the arena ranges and a parameter distribution step
-        # (off until the owner of a range also distributes its AdamW parameters: the trainer turns it on together
-        # with the parameter push)
-        self.shard_adamw = False
+        # Parameter distribution in arena mode moves whole ownership ranges, AdamW parameters included.
+        self.shard_adamw = bool(self.sharded and self.owner_cuts is not None
+                                and os.environ.get("NESTOR_ZERO1", "1") == "1")
 
     # ------------------------------------------------------------------ ownership
     def _assign_owners(self) -> None:
@@ -319,8 +319,18 @@ class MuonAdamW(Optimizer):
 
 @torch.no_grad()
 def _broadcast_owned(opt: MuonAdamW) -> None:
-    """Baseline parameter distribution: one flat broadcast per owner (reference ``muon.py:410-433``)."""
+    """Baseline parameter distribution: one flat broadcast per owner (reference ``muon.py:410-433``).
 
+    In arena mode an owner's parameters are one contiguous range of the fp32 master buffer, so the range itself is
+    broadcast (no flattening copy); it carries the AdamW parameters of the range too.
+    """
+
+    if opt.owner_cuts is not None and opt.arena is not None:
+        for owner in range(opt.world):
+            lo, hi = opt.owned_range(owner)
+            if hi > lo:
+                dist.broadcast(opt.arena.master[lo:hi], src=owner)
+        return
     for owner in range(opt.world):
         ps = opt.owned[owner]
         if not ps:

@@ -77,10 +77,9 @@ class Trainer:
             from nestor_b200.parallel.symm import ParamPush
             self.param_push = ParamPush(self.arena.master, self.arena.compute)
             self.optimizer.param_sync = lambda opt: None      # distribution happens after the compute-copy refresh
-            # the pushed range carries every parameter in it, so its owner can be the only one to update them
-            # (ZeRO-1 for AdamW as well) and the only one that needs their reduced gradients (reduce-scatter)
-            self.optimizer.shard_adamw = os.environ.get("NESTOR_ZERO1", "1") == "1"
-        self.zero = bool(self.param_push is not None and self.optimizer.shard_adamw)
+        # the pushed range carries every parameter in it; when its owner is the only one to update them (ZeRO-1 for
+        # AdamW as well) it is also the only one that needs their reduced gradients: reduce-scatter
+        self.zero = bool(self.param_push is not None and getattr(self.optimizer, "shard_adamw", False))
         self.global_step, self.epoch = 0, 0
         self.ema: dict[str, Tensor] | None = None
         decay = os.environ.get("NESTOR_EMA_DECAY")

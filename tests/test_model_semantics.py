@@ -178,3 +178,24 @@ def test_parity_with_installed_reference(family, tiny_scale, monkeypatch):
             continue
         if g1.norm() > 1e-5:
             assert (g1 - g2).norm() / g1.norm() < 2e-3, n
+
+
+def test_activation_checkpointing_changes_nothing(tiny_scale, monkeypatch):
+    """Per-block recomputation (NESTOR_ACTIVATION_CHECKPOINT=1) gives the same loss and the same gradients."""
+
+    ids = torch.randint(0, 100263, (2, 48))
+
+    def run(flag):
+        monkeypatch.setenv("NESTOR_ACTIVATION_CHECKPOINT", flag)
+        m = _model(tiny_scale, "nestor").train()
+        torch.manual_seed(3)                      # router noise
+        out = m(ids)
+        loss = F.cross_entropy(out.pred.reshape(-1, out.pred.shape[-1]).float(), ids.reshape(-1))
+        loss.backward()
+        return loss.detach(), {n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None}
+
+    l0, g0 = run("0")
+    l1, g1 = run("1")
+    assert torch.equal(l0, l1) and g0.keys() == g1.keys()
+    for n in g0:
+        assert torch.allclose(g0[n], g1[n], atol=1e-6, rtol=1e-5), n
