@@ -4,8 +4,8 @@
 over an evaluation and over ranks) into the flat metric names the reference logs
 (``nestor/eval/metrics.py:197-270``): per-choice assignment fractions, the largest fraction, and a
 balance score ``1 - cv / cv_max`` (1 = perfectly even, 0 = everything on one choice), plus
-per-kind means. The reference's ``prob/*`` entries need full softmax probabilities, which the fused
-routers do not materialise; they are reported only when probabilities are supplied.
+per-kind means. The ``prob/*`` entries (mean softmax routing mass per choice) come from the probability
+sums the model attaches to evaluation forwards (``models.nestor.router_prob_sums``).
 """
 
 from __future__ import annotations

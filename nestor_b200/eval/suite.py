@@ -18,7 +18,7 @@ import torch.nn.functional as F
 from nestor_b200.configs import EvalConfig, EvalSuiteConfig, LanguageModelingEvalConfig
 from nestor_b200.data.datasets import build_dataset
 from nestor_b200.eval.metrics import routing_metrics
-from nestor_b200.models.nestor import router_counts
+from nestor_b200.models.nestor import router_counts, router_prob_sums
 from nestor_b200.utils.distributed import get_padded_rank_indices, get_rank, get_world_size, sum_tensor_across_ranks
 
 
@@ -38,6 +38,7 @@ class LanguageModelingEval:
         real = set(range(n)[get_rank()::get_world_size()])
         totals = torch.zeros(2, dtype=torch.float64, device=self.device)
         counts: dict[str, torch.Tensor] = {}
+        probs: dict[str, torch.Tensor] = {}
         for a in range(0, len(idx), self.batch_size):
             rows = idx[a : a + self.batch_size]
             ids = torch.stack([self.dataset[i][0] for i in rows]).to(self.device)
@@ -51,14 +52,18 @@ class LanguageModelingEval:
             if bool(keep.all()):
                 for k, v in router_counts(model.backbone, out.aux).items():
                     counts[k] = v if k not in counts else counts[k] + v
+                for k, v in router_prob_sums(model.backbone, out.aux).items():
+                    probs[k] = v if k not in probs else probs[k] + v
         sum_tensor_across_ranks(totals)
         for k in sorted(counts):
             sum_tensor_across_ranks(counts[k])
+        for k in sorted(probs):
+            sum_tensor_across_ranks(probs[k])
         ce = float(totals[0] / totals[1].clamp_min(1))
         model.fused_head = was_fused
         model.train(was_training)
         result = {"cross_entropy": ce, "perplexity": math.exp(min(ce, 50.0)), "tokens": int(totals[1].item())}
-        result.update(routing_metrics({k: v.cpu() for k, v in counts.items()}))
+        result.update(routing_metrics({k: v.cpu() for k, v in counts.items()}, {k: v.cpu() for k, v in probs.items()}))
         return result
 
 

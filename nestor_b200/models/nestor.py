@@ -122,6 +122,12 @@ class ExpertPool(nn.Module):
                                   W(self, self.stacked_private.w_gate), W(self, self.stacked_private.w_down), cd, group=s.k_q)
         aux = {"public_idx": pub_idx, "private_idx": priv_idx, "columns": idx,
                "public_offsets": pub_plan.offsets, "private_offsets": priv_plan.offsets}
+        if not self.training and not torch.is_grad_enabled():
+            # evaluation only: soft routing mass per choice (the reference's ``prob/*`` metrics). A private router's
+            # mass counts the tokens routed into its column.
+            aux["public_prob"] = torch.softmax(pub_scores.float(), dim=-1).sum(0)
+            member = torch.zeros(T, s.G, device=n.device).scatter_(1, idx.long(), 1.0)
+            aux["private_prob"] = (torch.softmax(priv_scores.float(), dim=-1) * member.unsqueeze(-1)).sum(0)
         return public[:, 0], private, path, aux
 
 
@@ -197,7 +203,10 @@ class Layer(nn.Module):
         ones = torch.ones_like(gate, dtype=cd)
         rows = ops.expert_bank(n, plan, ones, W(self, bank.w_up), W(self, bank.w_gate), W(self, bank.w_down), cd, group=1)
         out = (rows * gate.to(cd).float().unsqueeze(-1)).sum(dim=1).to(cd).float()
-        return None, out, None, {"expert_idx": idx}
+        aux = {"expert_idx": idx}
+        if not self.training and not torch.is_grad_enabled():
+            aux["expert_prob"] = torch.softmax(scores.float(), dim=-1).sum(0)
+        return None, out, None, aux
 
 
 class BlockContext:
@@ -233,6 +242,8 @@ class Block(nn.Module):
             eps = torch.randn_like(scores) if noise is None else noise.to(scores.dtype)
             n1, n2 = r.weights("noise")
             scores = scores + eps * torch.nn.functional.softplus(ops.router_scores(x, W(self, n1), W(self, n2), cd))
+        if not self.training and not torch.is_grad_enabled():
+            self._last_group_prob = torch.softmax(scores.float(), dim=-1).sum(0)
         return ops.route_topk(scores, r.choice_bias, s.k, "renorm")
 
     def forward(self, x: Tensor, sources: list[Tensor], B: int, S: int, cd: torch.dtype,
@@ -268,7 +279,10 @@ class Block(nn.Module):
         else:
             agg = streams.mean(dim=1) if s.k > 1 else streams[:, 0]
             exports = [agg]
-        return exports, agg, {"group_idx": idx, "layers": layer_aux}
+        baux = {"group_idx": idx, "layers": layer_aux}
+        if not self.training and not torch.is_grad_enabled() and s.G > 1:
+            baux["group_prob"] = self.__dict__.pop("_last_group_prob", None)
+        return exports, agg, baux
 
 
 class Nestor(nn.Module):
@@ -374,6 +388,26 @@ def router_counts(backbone: Nestor, aux: dict) -> dict[str, Tensor]:
                     out[f"{base}.expert_pool.private_routers.{g}"] = per[g]
             elif "expert_idx" in laux:
                 out[f"{base}.expert_router"] = _count(laux["expert_idx"], s.bank_experts)
+    return out
+
+
+def router_prob_sums(backbone: Nestor, aux: dict) -> dict[str, Tensor]:
+    """Summed softmax routing probabilities of one evaluation forward, keyed like :func:`router_counts`
+    (present only for forwards run in eval mode without gradients)."""
+
+    out: dict[str, Tensor] = {}
+    for b, (block, baux) in enumerate(zip(backbone.blocks, aux["blocks"])):
+        s = block.spec
+        if baux.get("group_prob") is not None:
+            out[f"blocks.{b}.group_router"] = baux["group_prob"]
+        for l, (layer, laux) in enumerate(zip(block.layers, baux["layers"])):
+            base = f"blocks.{b}.layers.{l}"
+            if "public_prob" in laux:
+                out[f"{base}.expert_pool.public_router"] = laux["public_prob"]
+                for g in range(s.G):
+                    out[f"{base}.expert_pool.private_routers.{g}"] = laux["private_prob"][g]
+            elif "expert_prob" in laux:
+                out[f"{base}.expert_router"] = laux["expert_prob"]
     return out
 
 

@@ -199,3 +199,23 @@ def test_activation_checkpointing_changes_nothing(tiny_scale, monkeypatch):
     assert torch.equal(l0, l1) and g0.keys() == g1.keys()
     for n in g0:
         assert torch.allclose(g0[n], g1[n], atol=1e-6, rtol=1e-5), n
+
+
+def test_eval_forward_reports_routing_probability_sums(tiny_scale):
+    """An evaluation forward carries the soft routing mass per choice of every router (the ``prob/*`` metrics)."""
+
+    from nestor_b200.eval.metrics import routing_metrics
+    from nestor_b200.models.nestor import router_prob_sums
+    m = _model(tiny_scale, "nestor")
+    ids = torch.randint(0, 100263, (2, 32))
+    with torch.no_grad():
+        out = m(ids)
+    probs, counts = router_prob_sums(m.backbone, out.aux), router_counts(m.backbone, out.aux)
+    assert probs.keys() == counts.keys()
+    T = ids.numel()
+    spec = m.backbone.blocks[0].spec
+    assert probs["blocks.0.group_router"].sum().item() == pytest.approx(T, rel=1e-4)
+    priv_total = sum(probs[f"blocks.0.layers.0.expert_pool.private_routers.{g}"].sum().item() for g in range(spec.G))
+    assert priv_total == pytest.approx(T * spec.k, rel=1e-4)        # every (token, selected column) pair contributes 1
+    metrics = routing_metrics({k: v.cpu() for k, v in counts.items()}, {k: v.cpu() for k, v in probs.items()})
+    assert "routing/blocks.0.group_router/prob/c0" in metrics and "routing/group/mean_max_prob" in metrics
