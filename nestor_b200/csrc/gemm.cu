@@ -368,6 +368,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if (trace_on) acc_tempty += clock64() - cte;
       tc_fence_after();                  // orders the epilogue's TMEM reads of this buffer before the new MMAs
       const uint32_t d_addr = tmem_base + buf * p.BN;
+      // mode 1: only the k-block that holds the group's last rows can be partial; find it once per tile so that
+      // the per-k-block path carries no shared-memory reads
+      int tail_kb = -1, tail_valid = 0;
+      if (p.mode == 1) {
+        const int rows_g = tl.row_end - s_off[tl.g];
+        if (rows_g % BK) { tail_kb = rows_g / BK - tl.kb0; tail_valid = rows_g % BK; }
+      }
       bool ok = true;
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         long long c0 = trace_on ? clock64() : 0;
@@ -375,11 +382,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (!ok) break;
         long long c1 = trace_on ? clock64() : 0;
         if (trace_on && lane == 0 && it >= 16 && it < 28) NB_TRACE(16 + it - 16);
-        if (p.mode == 1) {
+        if (kb == tail_kb) {
           // zero k-rows past the end of the group (they belong to the next group)
-          int row0 = s_off[tl.g] + (tl.kb0 + kb) * BK;
-          int valid = tl.row_end - row0;
-          if (valid < BK) {
+          const int valid = tail_valid;
+          {
             uint8_t* sa = smem + s * stage_bytes;
             uint8_t* sb = sa + a_bytes;
             int natoms = 2 + p.BN / 64;
