@@ -12,9 +12,16 @@
 // Operands are bf16, K-major (rows of K) or MN-major (rows of M/N); see sm100.cuh.
 // A second (A2, B2) operand pair extends the reduction (dX = dG.Wg^T + dU.Wu^T in one pass).
 //
-// Warp roles (352 threads): warp 0 = TMA producer of A tiles, warp 10 = TMA producer of B tiles, warp 1 = MMA issuer
-// (+TMEM owner), warps 2..9 = epilogue (warp w reads TMEM lanes 32*(w%4)..+31; two warps per lane quarter split the columns). Two accumulator buffers
-// let the epilogue of tile i overlap the main loop of tile i+1.
+// Warp roles (352 threads): warp 0 = TMA producer of A tiles, warp 10 = TMA producer of B tiles, warp 1 = MMA
+// issuer (+TMEM owner), warps 2..9 = epilogue (warp w reads TMEM lanes 32*(w%4)..+31; the two warps of a lane
+// quarter take alternating 32-column chunks). Two accumulator buffers let the epilogue of tile i overlap the main
+// loop of tile i+1. With PAIR = 1 the kernel runs as clusters of two CTAs on 256-row tiles (cta_group::2): each CTA
+// stages its 128 rows of A and half of B, rank 0 issues the MMAs for both and signals both CTAs' barriers.
+//
+// What bounds it (measured with the trace / debug switches below): shared memory is filled at about 85 bytes per
+// clock per SM whatever the number of producer warps, so a 128 x 256 x 64 k-block (48 KB) takes ~560 cycles to
+// load against 512 cycles of tensor-core time; pairs cut the bytes per CTA to 32 KB. Short-K products are bound
+// by the epilogue and the per-tile hand-shakes instead.
 //
 // Replaces the reference's torch._grouped_mm call sites (nestor/backbones/grouped_mm.py:83,
 // :417-450; nestor/backbones/nestor.py:6337, :6367) and their Triton pointwise companions.
