@@ -40,7 +40,7 @@ class GradReducer:
         if self.world > 1 and transport == "fused":
             from nestor_b200.parallel.symm import FusedAllReduce, FusedReduceScatter
             self._fused = FusedAllReduce(arena.grad, self.buckets)
-            self._fused_rs = FusedReduceScatter(arena.grad)
+            self._fused_rs = FusedReduceScatter(arena.grad, group=self._fused.group)
 
     @torch.no_grad()
     def reduce(self) -> None:

@@ -143,9 +143,9 @@ class FusedAllReduce:
 class FusedReduceScatter:
     """Sum a symmetric fp32 buffer over ranks, each rank keeping only the range it owns (one kernel)."""
 
-    def __init__(self, grad: torch.Tensor, mirror: torch.Tensor | None = None) -> None:
-        self.group = PeerGroup(grad, mirror)
-        self.mirror = mirror is not None
+    def __init__(self, grad: torch.Tensor, mirror: torch.Tensor | None = None, group: PeerGroup | None = None) -> None:
+        self.group = group if group is not None else PeerGroup(grad, mirror)   # may share the all-reduce's peer table
+        self.mirror = self.group.aux is not None
 
     @torch.no_grad()
     def run(self, lo: int, hi: int, scale: float) -> None:
