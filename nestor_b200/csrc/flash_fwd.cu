@@ -145,7 +145,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (elect_one()) {
 #pragma unroll
         for (int k = 0; k < FK / 16; ++k)
-          umma_bf16(tO, p_desc + (k & 3) * 2, v_desc + k * 128, idesc_o, k != 0);
+          umma_bf16(tO, p_desc + (k & 3) * 2, v_desc + k * 128, idesc_o, (j | k) != 0);   // O accumulates in TMEM over the kv tiles
         umma_commit(&kv_empty[s]);
         umma_commit(&o_full);
       }
@@ -157,10 +157,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int r = q * 32 + lane;               // row inside the q tile
     const int qrow = q0 + r;
     const uint32_t lane_off = uint32_t(q * 32) << 16;
+    // O stays in TMEM and is accumulated by the MMAs across kv tiles, relative to a reference maximum m that is
+    // only moved (and O rescaled in TMEM) when some row of the warp finds a score more than 2^8 above it: the
+    // probabilities stay below 256, exact enough in bf16, and most tiles skip the 2 x HDN TMEM round trip.
     float m = -INFINITY, l = 0.f;
-    float o[HDN];
-#pragma unroll
-    for (int i = 0; i < HDN; ++i) o[i] = 0.f;
     bool ok = true;
     for (int j = 0; j < ntiles; ++j) {
       int s = j & 1;
@@ -177,21 +177,29 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int i = 0; i < 32; ++i) if (c + i < lim) mx = fmaxf(mx, v[i] * p.scale_log2);
       }
-      const float m_new = mx;
-      const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      // fold the previous tile's P.V into the running output before P is overwritten
+      // the previous tile's P.V must have retired before P is overwritten (and before O is touched)
       if (j > 0) {
         if (!mbar_wait(&o_full, (j - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) { ok = false; break; }
         tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < HDN; c += 16) {
-          float v[16];
-          tmem_ld16(tO + lane_off + c, v); tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) o[c + i] = (o[c + i] + v[i]) * alpha;
-        }
       }
+      const bool moved = mx > m + 8.f || (m == -INFINITY && mx != -INFINITY);
+      if (__any_sync(0xffffffffu, moved)) {
+        const float f = (m == -INFINITY) ? 0.f : exp2f(m - mx);     // 1 for rows whose maximum did not move
+        if (j > 0) {
+#pragma unroll
+          for (int c = 0; c < HDN; c += 32) {
+            float v[32];
+            tmem_ld32(tO + lane_off + c, v); tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= f;
+            tmem_st32(tO + lane_off + c, v);
+          }
+          tmem_st_wait();
+        }
+        l *= f;
+        m = mx;
+      }
+      const float m_use = (m == -INFINITY) ? 0.f : m;
       // pass 2: probabilities -> bf16 -> swizzled smem
       float rs = 0.f;
       for (int c = 0; c < FK; c += 32) {
@@ -209,8 +217,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int g = 0; g < 4; ++g) st_p_chunk(sP, r, c + g * 8, w + g * 4);
       }
-      l = l * alpha + rs;
-      m = m_new;
+      l += rs;
       fence_async_smem();
       tc_fence_before();
       __syncwarp();
@@ -233,7 +240,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 uint32_t w[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
-                  w[e] = pack_bf16((o[c + i + 2 * e] + v[i + 2 * e]) * inv, (o[c + i + 2 * e + 1] + v[i + 2 * e + 1]) * inv);
+                  w[e] = pack_bf16(v[i + 2 * e] * inv, v[i + 2 * e + 1] * inv);
                 *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(w[0], w[1], w[2], w[3]);
               }
             }
