@@ -45,6 +45,8 @@ from nestor_b200.models.tags import get_tag
 def _fused(*lists: list[Tensor]) -> bool:
     """The multi-tensor kernels apply: CUDA, fp32, contiguous tensors (arena views and their states are)."""
 
+    if os.environ.get("NESTOR_ADAMW_FUSED", "1") != "1":       # the reference's switch between foreach and fused updates
+        return False
     return all(t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() for ts in lists for t in ts)
 
 
