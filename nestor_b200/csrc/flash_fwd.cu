@@ -40,7 +40,9 @@ __device__ __forceinline__ void st_p_chunk(uint8_t* pbase, int row, int col0, co
   *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-template <int HDN>   // N of the P.V product and width of the register accumulator: 64 (hd <= 64) or 128
+// HDN: N of the P.V product, 64 (hd <= 64) or 128. LAZY: O stays in TMEM across kv tiles and is rescaled only when a
+// row maximum moves by more than 2^8 (otherwise O is folded into registers after every tile).
+template <int HDN, bool LAZY>
 __global__ void __launch_bounds__(192, HDN == 64 ? 2 : 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
@@ -145,7 +147,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (elect_one()) {
 #pragma unroll
         for (int k = 0; k < FK / 16; ++k)
-          umma_bf16(tO, p_desc + (k & 3) * 2, v_desc + k * 128, idesc_o, (j | k) != 0);   // O accumulates in TMEM over the kv tiles
+          umma_bf16(tO, p_desc + (k & 3) * 2, v_desc + k * 128, idesc_o, LAZY ? (j | k) != 0 : k != 0);   // lazy mode: O accumulates in TMEM over the kv tiles
         umma_commit(&kv_empty[s]);
         umma_commit(&o_full);
       }
@@ -157,71 +159,131 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int r = q * 32 + lane;               // row inside the q tile
     const int qrow = q0 + r;
     const uint32_t lane_off = uint32_t(q * 32) << 16;
-    // O stays in TMEM and is accumulated by the MMAs across kv tiles, relative to a reference maximum m that is
-    // only moved (and O rescaled in TMEM) when some row of the warp finds a score more than 2^8 above it: the
-    // probabilities stay below 256, exact enough in bf16, and most tiles skip the 2 x HDN TMEM round trip.
     float m = -INFINITY, l = 0.f;
+    float o[LAZY ? 1 : HDN];     // eager mode: running output in registers
     bool ok = true;
-    for (int j = 0; j < ntiles; ++j) {
-      int s = j & 1;
-      if (!mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) { ok = false; break; }
-      tc_fence_after();
-      const uint32_t ts = tS0 + s * FK + lane_off;
-      const int kv0 = seg_b + j * FK;
-      const int lim = min(FK, qrow - kv0 + 1);     // columns < lim are visible (causal); the diagonal spans two tiles
-      // pass 1: row max
-      float mx = m;
-      for (int c = 0; c < FK; c += 32) {
-        float v[32];
-        tmem_ld32(ts + c, v); tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) if (c + i < lim) mx = fmaxf(mx, v[i] * p.scale_log2);
-      }
-      // the previous tile's P.V must have retired before P is overwritten (and before O is touched)
-      if (j > 0) {
-        if (!mbar_wait(&o_full, (j - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) { ok = false; break; }
+    if constexpr (LAZY) {
+      // O stays in TMEM and is accumulated by the MMAs across kv tiles, relative to a reference maximum m that is
+      // only moved (and O rescaled in TMEM) when some row of the warp finds a score more than 2^8 above it: the
+      // probabilities stay below 256, exact enough in bf16, and most tiles skip the 2 x HDN TMEM round trip.
+      for (int j = 0; j < ntiles; ++j) {
+        int s = j & 1;
+        if (!mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) { ok = false; break; }
         tc_fence_after();
-      }
-      const bool moved = mx > m + 8.f || (m == -INFINITY && mx != -INFINITY);
-      if (__any_sync(0xffffffffu, moved)) {
-        const float f = (m == -INFINITY) ? 0.f : exp2f(m - mx);     // 1 for rows whose maximum did not move
+        const uint32_t ts = tS0 + s * FK + lane_off;
+        const int kv0 = seg_b + j * FK;
+        const int lim = min(FK, qrow - kv0 + 1);     // columns < lim are visible (causal); the diagonal spans two tiles
+        // pass 1: row max
+        float mx = m;
+        for (int c = 0; c < FK; c += 32) {
+          float v[32];
+          tmem_ld32(ts + c, v); tmem_ld_wait();
+  #pragma unroll
+          for (int i = 0; i < 32; ++i) if (c + i < lim) mx = fmaxf(mx, v[i] * p.scale_log2);
+        }
+        // the previous tile's P.V must have retired before P is overwritten (and before O is touched)
         if (j > 0) {
-#pragma unroll
-          for (int c = 0; c < HDN; c += 32) {
-            float v[32];
-            tmem_ld32(tO + lane_off + c, v); tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] *= f;
-            tmem_st32(tO + lane_off + c, v);
+          if (!mbar_wait(&o_full, (j - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) { ok = false; break; }
+          tc_fence_after();
+        }
+        const bool moved = mx > m + 8.f || (m == -INFINITY && mx != -INFINITY);
+        if (__any_sync(0xffffffffu, moved)) {
+          const float f = (m == -INFINITY) ? 0.f : exp2f(m - mx);     // 1 for rows whose maximum did not move
+          if (j > 0) {
+  #pragma unroll
+            for (int c = 0; c < HDN; c += 32) {
+              float v[32];
+              tmem_ld32(tO + lane_off + c, v); tmem_ld_wait();
+  #pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] *= f;
+              tmem_st32(tO + lane_off + c, v);
+            }
+            tmem_st_wait();
           }
-          tmem_st_wait();
+          l *= f;
+          m = mx;
         }
-        l *= f;
-        m = mx;
-      }
-      const float m_use = (m == -INFINITY) ? 0.f : m;
-      // pass 2: probabilities -> bf16 -> swizzled smem
-      float rs = 0.f;
-      for (int c = 0; c < FK; c += 32) {
-        float v[32];
-        tmem_ld32(ts + c, v); tmem_ld_wait();
-        uint32_t w[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = (c + i < lim) ? exp2f(v[i] * p.scale_log2 - m_use) : 0.f;
-          float p1 = (c + i + 1 < lim) ? exp2f(v[i + 1] * p.scale_log2 - m_use) : 0.f;
-          __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-          rs += __bfloat162float(pk.x) + __bfloat162float(pk.y);
-          w[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
+        const float m_use = (m == -INFINITY) ? 0.f : m;
+        // pass 2: probabilities -> bf16 -> swizzled smem
+        float rs = 0.f;
+        for (int c = 0; c < FK; c += 32) {
+          float v[32];
+          tmem_ld32(ts + c, v); tmem_ld_wait();
+          uint32_t w[16];
+  #pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = (c + i < lim) ? exp2f(v[i] * p.scale_log2 - m_use) : 0.f;
+            float p1 = (c + i + 1 < lim) ? exp2f(v[i + 1] * p.scale_log2 - m_use) : 0.f;
+            __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+            rs += __bfloat162float(pk.x) + __bfloat162float(pk.y);
+            w[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
+          }
+  #pragma unroll
+          for (int g = 0; g < 4; ++g) st_p_chunk(sP, r, c + g * 8, w + g * 4);
         }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) st_p_chunk(sP, r, c + g * 8, w + g * 4);
+        l += rs;
+        fence_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_ready);
       }
-      l += rs;
-      fence_async_smem();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&p_ready);
+    } else {
+  #pragma unroll
+      for (int i = 0; i < HDN; ++i) o[i] = 0.f;
+      for (int j = 0; j < ntiles; ++j) {
+        int s = j & 1;
+        if (!mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t ts = tS0 + s * FK + lane_off;
+        const int kv0 = seg_b + j * FK;
+        const int lim = min(FK, qrow - kv0 + 1);     // columns < lim are visible (causal); the diagonal spans two tiles
+        // pass 1: row max
+        float mx = m;
+        for (int c = 0; c < FK; c += 32) {
+          float v[32];
+          tmem_ld32(ts + c, v); tmem_ld_wait();
+  #pragma unroll
+          for (int i = 0; i < 32; ++i) if (c + i < lim) mx = fmaxf(mx, v[i] * p.scale_log2);
+        }
+        const float m_new = mx;
+        const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        // fold the previous tile's P.V into the running output before P is overwritten
+        if (j > 0) {
+          if (!mbar_wait(&o_full, (j - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) { ok = false; break; }
+          tc_fence_after();
+  #pragma unroll
+          for (int c = 0; c < HDN; c += 16) {
+            float v[16];
+            tmem_ld16(tO + lane_off + c, v); tmem_ld_wait();
+  #pragma unroll
+            for (int i = 0; i < 16; ++i) o[c + i] = (o[c + i] + v[i]) * alpha;
+          }
+        }
+        // pass 2: probabilities -> bf16 -> swizzled smem
+        float rs = 0.f;
+        for (int c = 0; c < FK; c += 32) {
+          float v[32];
+          tmem_ld32(ts + c, v); tmem_ld_wait();
+          uint32_t w[16];
+  #pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = (c + i < lim) ? exp2f(v[i] * p.scale_log2 - m_use) : 0.f;
+            float p1 = (c + i + 1 < lim) ? exp2f(v[i + 1] * p.scale_log2 - m_use) : 0.f;
+            __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+            rs += __bfloat162float(pk.x) + __bfloat162float(pk.y);
+            w[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
+          }
+  #pragma unroll
+          for (int g = 0; g < 4; ++g) st_p_chunk(sP, r, c + g * 8, w + g * 4);
+        }
+        l = l * alpha + rs;
+        m = m_new;
+        fence_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_ready);
+      }
     }
     if (ok && mbar_wait(&o_full, (ntiles - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) {
       tc_fence_after();
@@ -240,7 +302,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 uint32_t w[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
-                  w[e] = pack_bf16(v[i + 2 * e] * inv, v[i + 2 * e + 1] * inv);
+                  w[e] = LAZY ? pack_bf16(v[i + 2 * e] * inv, v[i + 2 * e + 1] * inv)
+                              : pack_bf16((o[c + i + 2 * e] + v[i + 2 * e]) * inv, (o[c + i + 2 * e + 1] + v[i + 2 * e + 1]) * inv);
                 *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(w[0], w[1], w[2], w[3]);
               }
             }
@@ -307,6 +370,7 @@ struct NbFlashArgs {
   float scale;
   int* status;
   int max_tiles;       // upper bound on q tiles: ceil(rows/128) + nseg
+  int lazy_rescale;    // 1: keep O in TMEM and rescale it only when a row maximum moves by more than 2^8
 };
 
 int nb_flash_fwd(const NbFlashArgs* a, cudaStream_t stream) {
@@ -324,23 +388,20 @@ int nb_flash_fwd(const NbFlashArgs* a, cudaStream_t stream) {
   const int nkb = (a->hd + 63) / 64;
   size_t smem = size_t(nkb) * (16384 + 4 * 8192) + 16384 + 1024;
   dim3 grid(a->max_tiles, a->H);
-  if (a->hd <= 64) {
-    static bool set64 = false;
-    if (!set64) {
-      cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-      if (e != cudaSuccess) return int(e);
-      set64 = true;
-    }
-    flash_fwd_kernel<64><<<grid, 192, smem, stream>>>(tq, tk, tv, p);
-  } else {
-    static bool set128 = false;
-    if (!set128) {
-      cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-      if (e != cudaSuccess) return int(e);
-      set128 = true;
-    }
-    flash_fwd_kernel<128><<<grid, 192, smem, stream>>>(tq, tk, tv, p);
-  }
+#define NB_FWD(HDN, LAZY)                                                                                          \
+  do {                                                                                                             \
+    static bool set = false;                                                                                       \
+    if (!set) {                                                                                                    \
+      cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<HDN, LAZY>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                           int(smem));                                                             \
+      if (e != cudaSuccess) return int(e);                                                                         \
+      set = true;                                                                                                  \
+    }                                                                                                              \
+    flash_fwd_kernel<HDN, LAZY><<<grid, 192, smem, stream>>>(tq, tk, tv, p);                                       \
+  } while (0)
+  if (a->hd <= 64) { if (a->lazy_rescale) NB_FWD(64, true); else NB_FWD(64, false); }
+  else { if (a->lazy_rescale) NB_FWD(128, true); else NB_FWD(128, false); }
+#undef NB_FWD
   return int(cudaGetLastError());
 }
 

@@ -86,7 +86,7 @@ class FlashArgs(C.Structure):
         ("O", C.c_void_p), ("ldo", C.c_long), ("lse", C.c_void_p),
         ("seg_start", C.c_void_p), ("nseg", C.c_int),
         ("rows", C.c_int), ("H", C.c_int), ("hd", C.c_int), ("scale", C.c_float),
-        ("status", C.c_void_p), ("max_tiles", C.c_int),
+        ("status", C.c_void_p), ("max_tiles", C.c_int), ("lazy_rescale", C.c_int),
     ]
 
 

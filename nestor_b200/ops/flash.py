@@ -3,11 +3,16 @@
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 from torch import Tensor
 
 from nestor_b200.ops import _lib
+
+# Forward variant: keep the output accumulator in TMEM across kv tiles and rescale it only when a row maximum moves by
+# more than 2^8 (1), or fold it into registers after every tile (0).
+LAZY_RESCALE = os.environ.get("NESTOR_B200_FLASH_LAZY", "0") == "1"
 
 
 def flash_fwd(q: Tensor, k: Tensor, v: Tensor, seg_start: Tensor, heads: int, head_dim: int, scale: float,
@@ -36,6 +41,7 @@ def flash_fwd(q: Tensor, k: Tensor, v: Tensor, seg_start: Tensor, heads: int, he
     a.rows, a.H, a.hd, a.scale = rows, heads, head_dim, scale
     a.status = _lib.status_word(q.device).data_ptr()
     a.max_tiles = -(-rows // 128) + nseg
+    a.lazy_rescale = int(LAZY_RESCALE)
     L = _lib.lib()
     L.nb_flash_fwd.argtypes = [C.POINTER(_lib.FlashArgs), C.c_void_p]
     L.nb_flash_fwd.restype = C.c_int

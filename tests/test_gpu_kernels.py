@@ -98,9 +98,11 @@ def test_gemm_stats_epilogue_gives_logsumexp():
     assert torch.isinf(logits[:, V:].float()).all()
 
 
+@pytest.mark.parametrize("lazy", [False, True])
 @pytest.mark.parametrize("H,hd,lens", [(5, 40, [300, 1, 129, 128, 0, 700]), (2, 80, [600, 257]), (3, 64, [512, 64]), (4, 32, [900])])
-def test_flash_forward_backward(H, hd, lens):
+def test_flash_forward_backward(H, hd, lens, lazy, monkeypatch):
     from nestor_b200.ops import flash as F
+    monkeypatch.setattr(F, "LAZY_RESCALE", lazy)     # output accumulator in TMEM with rare rescales / in registers
     torch.manual_seed(3)
     rows, inner = sum(lens), H * hd
     qkv = torch.randn(rows, 3 * inner, device="cuda").to(BF)
@@ -368,3 +370,25 @@ def test_column_plan_kernel_matches_oracle():
         a, b = K.build_column_plan(idx, Gc, pos), R.build_column_plan(idx, Gc, pos)
         for f in ("row_of_slot", "tok_of_row", "slot_of_row", "pos_of_row", "seg_start", "col_start", "idx"):
             assert torch.equal(getattr(a, f).long(), getattr(b, f).long()), f
+
+
+def test_flash_lazy_rescale_follows_growing_maxima(monkeypatch):
+    """Scores that keep growing along the sequence force the TMEM-resident accumulator to be rescaled many times."""
+
+    from nestor_b200.ops import flash as F
+    monkeypatch.setattr(F, "LAZY_RESCALE", True)
+    torch.manual_seed(9)
+    H, hd, n = 2, 40, 700
+    inner = H * hd
+    q = (torch.randn(n, inner, device="cuda") * 6).to(BF)
+    k = (torch.randn(n, inner, device="cuda") * (1 + torch.arange(n, device="cuda")[:, None] / 20.0)).to(BF)
+    v = torch.randn(n, inner, device="cuda").to(BF)
+    seg = torch.tensor([0, n], dtype=torch.int32, device="cuda")
+    o, lse = F.flash_fwd(q, k, v, seg, H, hd, 1.0 / hd)
+    qq, kk, vv = (t.float().reshape(n, H, hd).transpose(0, 1) for t in (q, k, v))
+    sc = (qq @ kk.transpose(1, 2)) / hd
+    sc = sc.masked_fill(~torch.ones(n, n, dtype=torch.bool, device="cuda").tril(), float("-inf"))
+    ref = (torch.softmax(sc, -1) @ vv).transpose(0, 1).reshape(n, inner)
+    assert (sc.amax(-1).diff(dim=-1) > 0).float().mean() > 0.2        # the maxima do move
+    assert _rel(o, ref) < 1e-2
+    assert (lse - (torch.logsumexp(sc, -1) / math.log(2)).transpose(0, 1)).abs().max() < 5e-2
