@@ -12,7 +12,7 @@ from nestor_b200.ops import _lib
 
 # Forward variant: keep the output accumulator in TMEM across kv tiles and rescale it only when a row maximum moves by
 # more than 2^8 (1), or fold it into registers after every tile (0).
-LAZY_RESCALE = os.environ.get("NESTOR_B200_FLASH_LAZY", "0") == "1"
+LAZY_RESCALE = os.environ.get("NESTOR_B200_FLASH_LAZY", "1") == "1"
 
 
 def flash_fwd(q: Tensor, k: Tensor, v: Tensor, seg_start: Tensor, heads: int, head_dim: int, scale: float,
