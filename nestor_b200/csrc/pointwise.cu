@@ -131,6 +131,22 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ buf, long ld, const int*
   }
 }
 
+// Re-pitch heads: dst[r, h, 0:min(hs, hd)] = src[r, h, 0:min(hs, hd)], zero where hd > hs, and zero the columns
+// [nheads * hd, dst_cols) of every row. Pads head dims that are not multiples of 8 (30, 60) to the next multiple
+// for the TMA-fed attention kernels and strips the padding again; hs and hd are even, pairs move as 32-bit words.
+__global__ void repack_heads_kernel(const __nv_bfloat16* __restrict__ src, long ld_src, __nv_bfloat16* __restrict__ dst,
+                                    long ld_dst, int rows, int nheads, int hs, int hd, int dst_cols) {
+  const int pairs = dst_cols / 2, hp = hd / 2, sp = hs / 2;
+  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < long(rows) * pairs; i += long(gridDim.x) * blockDim.x) {
+    const long r = i / pairs;
+    const int c = int(i - r * pairs);
+    const int h = c / hp, j = c - h * hp;
+    uint32_t v = 0u;
+    if (h < nheads && j < sp) v = reinterpret_cast<const uint32_t*>(src + r * ld_src + h * hs)[j];
+    reinterpret_cast<uint32_t*>(dst + r * ld_dst)[c] = v;
+  }
+}
+
 // Cross-entropy over a chunk of bf16 logits [n, ld] with per-(row, tile) (max, sumexp) partials:
 // loss[row] = lse - logit[target]; logits are overwritten by (softmax - onehot) (zero for ignored rows).
 __global__ void ce_grad_kernel(__nv_bfloat16* __restrict__ logits, long ld, int V, const float2* __restrict__ part,
@@ -287,6 +303,18 @@ int nb_combine_bwd(const float* g, long ldg, const void* y, long ldy, const int*
   dim3 block(32, 8), grid((rows + 7) / 8);
   nb::combine_bwd_kernel<<<grid, block, 0, st>>>(g, ldg, (const __nv_bfloat16*)y, ldy, slot_of_row, w, group,
                                                 (__nv_bfloat16*)dy, lddy, dw, rows, d);
+  return int(cudaGetLastError());
+}
+
+// src [rows, nheads * hs] (pitch ld_src) -> dst [rows, dst_cols] (pitch ld_dst) with head stride hd; see the kernel.
+int nb_repack_heads(const void* src, long ld_src, void* dst, long ld_dst, int rows, int nheads, int hs, int hd,
+                    int dst_cols, cudaStream_t st) {
+  if ((hs | hd | dst_cols) & 1 || dst_cols < nheads * hd || (ld_src & 1) || (ld_dst & 1) || rows < 0) return -1;
+  if (rows == 0) return 0;
+  long n = long(rows) * (dst_cols / 2);
+  int blocks = int(n / 256 + 1 < 148 * 16 ? n / 256 + 1 : 148 * 16);
+  nb::repack_heads_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)src, ld_src, (__nv_bfloat16*)dst, ld_dst, rows,
+                                                  nheads, hs, hd, dst_cols);
   return int(cudaGetLastError());
 }
 

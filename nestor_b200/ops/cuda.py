@@ -37,6 +37,8 @@ def _L():
         L.nb_combine_rows.argtypes = [vp, l, vp, vp, i, vp, l, i, i, i, i, vp]
         L.nb_combine_bwd.argtypes = [vp, l, vp, l, vp, vp, i, vp, l, vp, i, i, vp]
         L.nb_rope.argtypes = [vp, l, vp, i, i, i, i, f, f, vp]
+        L.nb_repack_heads.argtypes = [vp, l, vp, l, i, i, i, i, i, vp]
+        L.nb_repack_heads.restype = C.c_int
         L.nb_ce_grad.argtypes = [vp, l, i, vp, i, vp, l, vp, i, vp]
         L.nb_depth_read_norm.argtypes = [vp, i, vp, vp, vp, f, f, vp, vp, vp, vp, i, i, vp]
         L.nb_depth_read_norm_bwd.argtypes = [vp, vp, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, C.c_ulonglong, vp, vp]
@@ -115,6 +117,16 @@ def rope_(buf: Tensor, pos: Tensor, heads: int, head_dim: int, k_offset: int, ba
 
     _ck(_L().nb_rope(buf.data_ptr(), buf.stride(0), pos.data_ptr(), buf.shape[0], heads, head_dim, k_offset,
                      float(base), float(sign), _st()), "rope")
+
+
+def repack_heads(src: Tensor, nheads: int, hs: int, hd: int, dst_cols: int) -> Tensor:
+    """``[rows, nheads*hs]`` -> ``[rows, dst_cols]`` with head stride ``hd`` (zero-filled padding, or padding stripped)."""
+
+    rows = src.shape[0]
+    dst = G.rows_buffer(rows, dst_cols, BF16, src.device)
+    _ck(_L().nb_repack_heads(src.data_ptr(), src.stride(0), dst.data_ptr(), dst.stride(0), rows, nheads, hs, hd, dst_cols,
+                             _st()), "repack_heads")
+    return dst
 
 
 def _wgrad(a: Tensor, b: Tensor, w: Tensor, *, offsets: Tensor | None, groups: int, transpose_out: bool = False):
@@ -241,48 +253,80 @@ def dense_swiglu(x, w_up, w_gate, w_down, cd):
 class _Attention(torch.autograd.Function):
     """Packed varlen attention between the normed stream ``n [T, d]`` and gated slot updates."""
 
+    # Head dims that are not multiples of 8 (30 at the 100m scale, 60 at 500m) break the 16-byte alignment TMA needs
+    # for head starts and for the rows of W_o: such heads are re-pitched to the next multiple of 8 (zero-filled)
+    # around the attention kernels, W_o is zero-padded along its inner dim for the GEMMs that read it, and its
+    # gradient goes through a padded fp32 buffer.
+
     @staticmethod
     def forward(ctx, n, gates, wqkv, wo, tok_of_row, row_of_slot, slot_of_row_flat, pos_of_row, seg_start, col_start,
                 groups, k, heads, head_dim, rope_base):
         T, d = n.shape
         inner = heads * head_dim
+        hdp = -(-head_dim // 8) * 8
+        pad = hdp != head_dim
+        inner_p, inner8, n3 = heads * hdp, -(-inner // 8) * 8, -(-3 * inner // 8) * 8
         x = gather_rows(n, tok_of_row) if tok_of_row is not None else (n if n.dtype == BF16 else n.to(BF16))
         rows = x.shape[0]
-        qkv = G.gemm_rows(x, wqkv, offsets=col_start, groups=groups, out=G.rows_buffer(rows, 3 * inner, BF16, x.device))
+        dev = x.device
+        qkv = G.gemm_rows(x, wqkv, offsets=col_start, groups=groups, n=n3, out=G.rows_buffer(rows, n3, BF16, dev))
         rope_(qkv, pos_of_row, heads, head_dim, inner, rope_base, 1.0)
-        q, kk, v = qkv[:, :inner], qkv[:, inner : 2 * inner], qkv[:, 2 * inner :]
-        o, lse = flash.flash_fwd(q, kk, v, seg_start, heads, head_dim, 1.0 / head_dim,
-                                 out=G.rows_buffer(rows, inner, BF16, x.device))
-        y = G.gemm_rows(o, wo, offsets=col_start, groups=groups)
+        att = repack_heads(qkv, 3 * heads, head_dim, hdp, 3 * inner_p) if pad else qkv
+        q, kk, v = att[:, :inner_p], att[:, inner_p : 2 * inner_p], att[:, 2 * inner_p : 3 * inner_p]
+        o_att, lse = flash.flash_fwd(q, kk, v, seg_start, heads, hdp, 1.0 / head_dim,
+                                     out=G.rows_buffer(rows, inner_p, BF16, dev))
+        o = repack_heads(o_att, heads, hdp, head_dim, inner8) if pad else o_att
+        wo_use = torch.nn.functional.pad(wo, (0, inner8 - inner)) if inner8 != inner else wo
+        y = G.gemm_rows(o, wo_use, offsets=col_start, groups=groups)
         gf = gates.float().contiguous().view(-1)
         out = combine_rows(y, row_of_slot.view(-1), gf, 1, T * k, round_products=False)
-        ctx.save_for_backward(x, qkv, o, lse, y, gf, wqkv, wo, tok_of_row, row_of_slot, slot_of_row_flat, pos_of_row,
-                              seg_start, col_start)
+        ctx.save_for_backward(x, att, o_att, o, lse, y, gf, wqkv, wo_use, tok_of_row, row_of_slot, slot_of_row_flat,
+                              pos_of_row, seg_start, col_start)
         ctx.meta = (groups, k, heads, head_dim, rope_base, T, n.dtype, gates.dtype)
         ctx.w_refs = (wqkv, wo)
         return out.view(T, k, d)
 
     @staticmethod
     def backward(ctx, dout):
-        (x, qkv, o, lse, y, gf, wqkv, wo, tok_of_row, row_of_slot, slot_of_row_flat, pos_of_row, seg_start,
+        (x, att, o_att, o, lse, y, gf, wqkv, wo_use, tok_of_row, row_of_slot, slot_of_row_flat, pos_of_row, seg_start,
          col_start) = ctx.saved_tensors
         groups, k, heads, head_dim, rope_base, T, n_dtype, g_dtype = ctx.meta
         inner = heads * head_dim
+        hdp = -(-head_dim // 8) * 8
+        pad = hdp != head_dim
+        inner_p, inner8, n3 = heads * hdp, -(-inner // 8) * 8, -(-3 * inner // 8) * 8
         d = y.shape[1]
+        rows = x.shape[0]
         g2 = dout.contiguous().view(-1, d).float()
         dy, dg_sorted = combine_bwd(g2, y, slot_of_row_flat, gf, 1, need_dw=ctx.needs_input_grad[1])
         wq_ref, wo_ref = ctx.w_refs
-        do = G.gemm_rows(dy, wo, offsets=col_start, groups=groups, b_mn=True, n=inner,
-                         out=G.rows_buffer(dy.shape[0], inner, BF16, dy.device))               # wo [G, K=d, N=inner]
-        d_wo = _wgrad(dy, o, wo_ref, offsets=col_start, groups=groups) if ctx.needs_input_grad[3] else None
-        q, kk, v = qkv[:, :inner], qkv[:, inner : 2 * inner], qkv[:, 2 * inner :]
-        dqkv = flash.flash_bwd(q, kk, v, o, do, lse, seg_start, heads, head_dim, 1.0 / head_dim,
-                               dqkv=G.rows_buffer(q.shape[0], 3 * inner, BF16, q.device))
+        do = G.gemm_rows(dy, wo_use, offsets=col_start, groups=groups, b_mn=True, n=inner8,
+                         out=G.rows_buffer(rows, inner8, BF16, dy.device))                     # wo [G, K=d, N=inner]
+        d_wo = None
+        if ctx.needs_input_grad[3]:
+            if inner8 == inner:
+                d_wo = _wgrad(dy, o, wo_ref, offsets=col_start, groups=groups)
+            else:   # the gradient's rows would be misaligned for vector stores: reduce into a padded buffer first
+                tmp = torch.empty(groups, d, inner8, dtype=torch.float32, device=dy.device)
+                G.gemm_reduce(dy, o, offsets=col_start, groups=groups, out=tmp, epilogue=G.STORE_F32)
+                part = tmp[..., :inner].reshape(wo_ref.shape)
+                target = getattr(wo_ref, "_nb_grad", None)
+                if target is not None:
+                    target.add_(part)
+                else:
+                    d_wo = part.to(wo_ref.dtype)
+        do_att = repack_heads(do, heads, head_dim, hdp, inner_p) if pad else do
+        q, kk, v = att[:, :inner_p], att[:, inner_p : 2 * inner_p], att[:, 2 * inner_p : 3 * inner_p]
+        dqkv = flash.flash_bwd(q, kk, v, o_att, do_att, lse, seg_start, heads, hdp, 1.0 / head_dim,
+                               dqkv=G.rows_buffer(rows, 3 * inner_p, BF16, q.device))
+        if pad:
+            dqkv = repack_heads(dqkv, 3 * heads, hdp, head_dim, n3)
         rope_(dqkv, pos_of_row, heads, head_dim, inner, rope_base, -1.0)
-        d_wqkv = _wgrad(dqkv, x, wq_ref, offsets=col_start, groups=groups) if ctx.needs_input_grad[2] else None
+        dq3 = dqkv[:, : 3 * inner]
+        d_wqkv = _wgrad(dq3, x, wq_ref, offsets=col_start, groups=groups) if ctx.needs_input_grad[2] else None
         dn = None
         if ctx.needs_input_grad[0]:
-            dx = G.gemm_rows(dqkv, wqkv, offsets=col_start, groups=groups, b_mn=True, n=d)  # wqkv [G, K=3inner, N=d]
+            dx = G.gemm_rows(dq3, wqkv, offsets=col_start, groups=groups, b_mn=True, n=d)  # wqkv [G, K=3inner, N=d]
             dn = (combine_rows(dx, row_of_slot.view(-1), None, k, T) if tok_of_row is not None else dx.float()).to(n_dtype)
         dgates = None
         if dg_sorted is not None:

@@ -116,6 +116,10 @@ def gemm_rows(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: in
     if out is None:
         dt = torch.float32 if epilogue in (STORE_F32, ACCUM_F32) else torch.bfloat16
         out = torch.empty(rows, N // 2 if swiglu else N, dtype=dt, device=dev)
+    # vector stores of the epilogue: 16-byte aligned rows, widths in whole 8-column (bf16) / 4-column (fp32) groups
+    per16 = 16 // out.element_size()
+    assert out.stride(-1) == 1 and out.stride(0) % per16 == 0 and out.data_ptr() % 16 == 0, "misaligned GEMM output"
+    assert (N // 2 if swiglu else N) % per16 == 0, f"GEMM output width {N} must be a multiple of {per16}"
     a = _lib.GemmArgs()
     a.mode, a.groups, a.BN, a.epilogue = 0, groups, bn, epilogue
     a.M, a.N, a.K, a.K2 = rows, N, K, (A2.shape[1] if A2 is not None else 0)
@@ -172,6 +176,9 @@ def gemm_reduce(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: 
     a.A2, a.B2 = _operand(None, grouped=False), _operand(None, grouped=False)
     o3 = out if out.ndim == 3 else out.unsqueeze(0)
     assert o3.stride(-1) == 1
+    per16 = 16 // out.element_size()
+    assert o3.stride(1) % per16 == 0 and o3.stride(0) % per16 == 0 and out.data_ptr() % 16 == 0 and N % per16 == 0, \
+        "weight-gradient output rows must be 16-byte aligned (pad the inner dim)"
     a.C, a.ldc, a.c_group_stride = o3.data_ptr(), o3.stride(1), o3.stride(0)
     a.alpha = alpha
     # few output tiles and a long reduction: let several CTAs share a tile (fp32 atomic adds)

@@ -392,3 +392,35 @@ def test_flash_lazy_rescale_follows_growing_maxima(monkeypatch):
     assert (sc.amax(-1).diff(dim=-1) > 0).float().mean() > 0.2        # the maxima do move
     assert _rel(o, ref) < 1e-2
     assert (lse - (torch.logsumexp(sc, -1) / math.log(2)).transpose(0, 1)).abs().max() < 5e-2
+
+
+@pytest.mark.parametrize("d,H,hd,Gc,k", [(480, 5, 30, 8, 3), (960, 3, 60, 8, 5), (480, 16, 30, 1, 1)])
+def test_attention_with_head_dims_that_are_not_multiples_of_eight(d, H, hd, Gc, k):
+    """The 100m (head_dim 30) and 500m (head_dim 60) scales: heads are re-pitched around the attention kernels."""
+
+    from nestor_b200.ops import cuda as K, reference as R
+    torch.manual_seed(6)
+    B, S = 2, 320
+    T, inner = B * S, H * hd
+    n = torch.randn(T, d, device="cuda", requires_grad=True)
+    wqkv = (torch.randn(Gc, 3 * inner, d, device="cuda") * 0.04).to(BF).requires_grad_(True)
+    wo = (torch.randn(Gc, d, inner, device="cuda") * 0.04).to(BF).requires_grad_(True)
+    gg = torch.randn(T, k, d, device="cuda")
+    n2, wq2, wo2 = (t.detach().clone().requires_grad_(True) for t in (n, wqkv, wo))
+    if Gc > 1:
+        idx = torch.randn(B, S, Gc, device="cuda").topk(k, -1).indices
+        gates = torch.rand(T, k, device="cuda", requires_grad=True)
+        g2 = gates.detach().clone().requires_grad_(True)
+        plan = R.build_column_plan(idx, Gc)
+        out = K.column_attention(n, plan, gates, wqkv, wo, H, hd, 1e4, BF)
+        out2 = R.column_attention(n2, plan, g2, wq2, wo2, H, hd, 1e4, BF)
+        pairs = [(n, n2), (gates, g2), (wqkv, wq2), (wo, wo2)]
+    else:
+        out = K.dense_attention(n, B, S, wqkv, wo, H, hd, 1e4, BF).view(T, 1, d)
+        out2 = R.dense_attention(n2, B, S, wq2, wo2, H, hd, 1e4, BF).view(T, 1, d)
+        pairs = [(n, n2), (wqkv, wq2), (wo, wo2)]
+    (out * gg).sum().backward()
+    (out2 * gg).sum().backward()
+    assert _rel(out, out2) < 1e-2
+    for a, b in pairs:
+        assert _rel(a.grad, b.grad) < 2e-2
