@@ -204,10 +204,12 @@ class Trainer:
                              None if norm is None else f"{norm.item():.4e}",
                              bool(torch.isfinite(g).all().item()), g.abs().max().item())
         self.optimizer.step()
-        self.arena.refresh_compute()
         if self.param_push is not None:
-            # each rank stores the range it owns into every replica (fp32 master + bf16 compute copy)
+            # each rank stores the range it owns into every replica, itself included (fp32 master + bf16 compute
+            # copy); the ranges tile the arena, so this is also the refresh of the whole compute copy
             self.param_push.run(*self.optimizer.owned_range())
+        else:
+            self.arena.refresh_compute()
         self.arena.zero_grad()
         if self.ema is not None:
             self.ema["flat"].lerp_(self.arena.master, 1.0 - self.ema_decay)
