@@ -42,6 +42,30 @@ enum Epilogue : int {
   kStoreBf16Stats = 5 // store bf16 (scaled) and per-(row, n-tile) max / sum-exp partials
 };
 
+// All-gather fused into the product (mode 0, grouped B). The groups of B (one or two tensors of the same shape:
+// B and, for SwiGLU / two-segment products, B2) are sharded over ranks: rank r holds the current values of groups
+// [r * groups_per_rank, (r + 1) * groups_per_rank) in its copy of the weight arena, which every rank maps
+// (`src[r]`). The first `ctas` CTAs of the launch do not compute: they pull every group from its owner into the
+// local staging tensor that the B tensor maps describe, in group order, with bulk copies through shared memory,
+// and count finished chunks in `flags[group]`. The B producers of the computing CTAs wait (bounded) for a group's
+// count before their first load of it, so the product of the early groups overlaps the transfer of the later
+// ones. Nothing waits on another GPU: a shard is constant while the products that read it run. The last CTA to
+// leave zeroes the counters for the next launch (launches that share `flags` must be stream-ordered).
+struct GatherParams {
+  const uint8_t* src[8];       // per rank: base address of its weight arena as mapped here
+  uint8_t* dst;                // base address of the local staging tensors
+  long seg_src_off[2];         // byte offset of group 0 of B / B2 inside an arena
+  long seg_dst_off[2];         // byte offset of group 0 of the staged B / B2 from `dst`
+  long group_bytes;            // bytes of one group (contiguous, multiple of 16)
+  long group_stride_src;       // byte distance between groups in the arena (the staging is dense)
+  int nseg;                    // 1 or 2 tensors
+  int groups_per_rank;
+  int ctas;                    // leading CTAs that gather (even for CTA pairs); 0 = no gather
+  int chunk_bytes;             // bulk-copy granularity (multiple of 16)
+  int nbuf;                    // shared-memory ring depth (chunks), 3..8
+  int* flags;                  // [groups] finished chunks per group, then [groups]: CTAs that left
+};
+
 struct GemmParams {
   int mode, groups, BN, epilogue;
   int M, N, K;              // mode 0: M = total rows. mode 1: M x N output per group, K = total rows
@@ -65,6 +89,7 @@ struct GemmParams {
   int pair;                    // mode 0: CTA pairs (cluster of 2) run 256-row tiles with cta_group::2 MMAs
   int a_atoms, b_atoms;        // MN-major operand read through an "atom" map: one TMA instruction per k-block
   int debug;                   // timing experiments only (results are garbage): 1 = issue no MMAs, 2 = issue no loads, 4 = store nothing
+  GatherParams gather;         // fused all-gather of a rank-sharded B operand (gather.ctas == 0: off)
 };
 
 __device__ __forceinline__ unsigned long long gtime() {
@@ -172,6 +197,78 @@ __device__ __forceinline__ void load_chunk_bf16(uint8_t* slab, int lane, uint32_
   __syncwarp();
 }
 
+// The copy role of a fused all-gather launch (see GatherParams). One thread drives a ring of `nbuf` chunk buffers:
+// loads run `nbuf - kGatherLag` chunks ahead; a chunk is published once its store to the staging tensor has
+// completed, which is also when its buffer is reused.
+constexpr int kGatherLag = 2;
+constexpr uint32_t kGatherSpinLimit = 1u << 22;   // polls of >= 100 ns: a consumer gives up after about half a second
+__device__ __noinline__ void gather_role(const GatherParams& g, int groups, uint8_t* smem, uint64_t* bars, int* status) {
+  if (threadIdx.x != 0) return;
+  for (int b = 0; b < g.nbuf; ++b) mbar_init(&bars[b], 1);
+  fence_barrier_init();
+  const long chunk = g.chunk_bytes;
+  const long per_seg = (g.group_bytes + chunk - 1) / chunk;
+  const long per_group = per_seg * g.nseg;
+  const long total = long(groups) * per_group;
+  const long first = blockIdx.x, step = g.ctas;
+  const long n_mine = first < total ? (total - first + step - 1) / step : 0;
+  int abort_local = 0;
+  volatile int* abort_flag = &abort_local;
+  auto locate = [&](long i, const uint8_t*& src, uint8_t*& dst, uint32_t& bytes) -> int {
+    const long c = first + i * step;
+    const int grp = int(c / per_group);
+    const long rem = c - long(grp) * per_group;
+    const int seg = int(rem / per_seg);
+    const long off = (rem - long(seg) * per_seg) * chunk;
+    bytes = uint32_t(min(chunk, g.group_bytes - off));
+    src = g.src[grp / g.groups_per_rank] + g.seg_src_off[seg] + long(grp) * g.group_stride_src + off;
+    dst = g.dst + g.seg_dst_off[seg] + long(grp) * g.group_bytes + off;
+    return grp;
+  };
+  auto load = [&](long i) {
+    const uint8_t* src; uint8_t* dst; uint32_t bytes;
+    locate(i, src, dst, bytes);
+    const int b = int(i % g.nbuf);
+    mbar_expect_tx(&bars[b], bytes);
+    bulk_load(smem + long(b) * chunk, src, bytes, &bars[b]);
+  };
+  auto publish = [&](long i) {
+    const uint8_t* src; uint8_t* dst; uint32_t bytes;
+    const int grp = locate(i, src, dst, bytes);
+    fence_async_all();
+    __threadfence();
+    atomicAdd(&g.flags[grp], 1);
+  };
+  for (long i = 0; i < n_mine && i < g.nbuf; ++i) load(i);
+  long done = 0;      // chunks published
+  for (long i = 0; i < n_mine; ++i) {
+    const int b = int(i % g.nbuf);
+    if (!mbar_wait(&bars[b], uint32_t(i / g.nbuf) & 1u, abort_flag, status, kTimeoutPeer, 64)) break;
+    const uint8_t* src; uint8_t* dst; uint32_t bytes;
+    locate(i, src, dst, bytes);
+    fence_async_smem();
+    bulk_store(dst, smem + long(b) * chunk, bytes);
+    bulk_commit();
+    if (i >= kGatherLag) {
+      bulk_wait<kGatherLag>();
+      publish(i - kGatherLag);
+      ++done;
+      if (i - kGatherLag + g.nbuf < n_mine) load(i - kGatherLag + g.nbuf);   // its buffer: the chunk just published
+    }
+  }
+  bulk_wait<0>();        // also on a timeout: no copy of this CTA is in flight when it leaves
+  if (!abort_local) for (; done < n_mine; ++done) publish(done);
+}
+
+// Every CTA of a gathering launch counts itself out; the last one clears the counters for the next launch.
+__device__ __forceinline__ void gather_leave(const GatherParams& g, int groups) {
+  __threadfence();
+  if (atomicAdd(&g.flags[groups], 1) == int(gridDim.x) - 1) {
+    for (int i = 0; i <= groups; ++i) g.flags[i] = 0;
+    __threadfence();
+  }
+}
+
 // PAIR = 1 is compiled separately: a kernel that contains cta_group::2 instructions can only be launched as
 // clusters of two, so the single-CTA variant must not contain them. The epilogue is a template parameter too:
 // with every variant in one kernel the eleven warps of a CTA (each in a different code region) thrash the
@@ -191,6 +288,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int pair = PAIR;
+  const int n_gather = p.gather.ctas;
+  if (int(blockIdx.x) < n_gather) {       // copy role (whole pairs when PAIR): no TMEM, no cluster barrier
+    gather_role(p.gather, p.groups, smem, full_bar, p.status);
+    if (threadIdx.x == 0) gather_leave(p.gather, p.groups);
+    return;
+  }
   const uint32_t rank = pair ? cluster_ctarank() : 0u;   // rank 0 of a pair issues the MMAs
   const int b_cols = pair ? p.BN / 2 : p.BN;             // B columns staged by this CTA
   const uint32_t a_bytes = BM * BK * 2;               // 16 KB
@@ -232,8 +335,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   else total_tiles = p.groups * ((p.M + BM - 1) / BM) * n_tiles * p.splits;
 
   volatile int* abort_flag = &s_abort;
-  const int cta = pair ? int(blockIdx.x >> 1) : int(blockIdx.x);       // persistent worker index
-  const int n_cta = pair ? int(gridDim.x >> 1) : int(gridDim.x);
+  const int cta = pair ? int((blockIdx.x - n_gather) >> 1) : int(blockIdx.x) - n_gather;   // persistent worker index
+  const int n_cta = pair ? int((gridDim.x - n_gather) >> 1) : int(gridDim.x) - n_gather;
 
   if (warp == 0 || warp == 10) {
     // ------------------------------------------- TMA producers (warp 0: A tiles, warp 10: B tiles)
@@ -314,13 +417,30 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       };
       const int D = p.prefetch_dist, pf_mask = p.prefetch_ops;
       uint32_t it = 0, s = 0, ph = 0;
-      int g_hint = 0;
+      int g_hint = 0, g_ready = -1;
       const bool trace_on = p.trace != nullptr;
       long long acc_wait = 0, acc_issue = 0;
       if (el && which == 1) NB_TRACE(0);
       for (int t = cta; t < total_tiles && !*abort_flag; t += n_cta) {
         Tile tl = decode_tile(p, s_off, s_tstart, t, n_tiles, rank, g_hint);
         int nkb = tl.kb + tl.kb2;
+        if (n_gather && which == 2 && tl.g != g_ready) {
+          // first load of a gathered group: wait until the copy CTAs have staged all of its chunks
+          const int need = int((p.gather.group_bytes + p.gather.chunk_bytes - 1) / p.gather.chunk_bytes) * p.gather.nseg;
+          const volatile int* fl = p.gather.flags + tl.g;
+          uint32_t spins = 0;
+          while (*fl < need) {
+            __nanosleep(100);
+            if (++spins > kGatherSpinLimit || *abort_flag) {
+              if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, int(kTimeoutPeer)); }
+              break;
+            }
+          }
+          if (*abort_flag) break;
+          __threadfence();
+          fence_async_all();
+          g_ready = tl.g;
+        }
         Tile nx = tl; int nx_nkb = 0;
         if (D > 0 && t + n_cta < total_tiles) {
           { int gh = g_hint; nx = decode_tile(p, s_off, s_tstart, t + n_cta, n_tiles, rank, gh); }
@@ -639,6 +759,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     tc_fence_after();
     if (pair) tmem_dealloc_pair(tmem_base, tmem_cols); else tmem_dealloc(tmem_base, tmem_cols);
   }
+  if (n_gather && threadIdx.x == 0) gather_leave(p.gather, p.groups);
 }
 
 }  // namespace nb
@@ -710,6 +831,13 @@ struct NbGemmArgs {
   int max_stages;           // 0 = as many as fit
   int pair;                 // mode 0 only: 256-row tiles on CTA pairs (cta_group::2), each CTA stages half of B
   int debug;                // timing experiments: 1 = no MMAs, 2 = no loads (outputs are garbage)
+  // fused all-gather of B (and B2) from rank-sharded weight arenas; see nb::GatherParams. gather_ctas == 0: off.
+  const void* gather_src[8];
+  void* gather_dst;
+  long gather_seg_src_off[2], gather_seg_dst_off[2];
+  long gather_group_bytes, gather_group_stride_src;
+  int gather_nseg, gather_groups_per_rank, gather_ctas, gather_chunk;
+  int* gather_flags;        // [groups + 1] ints, zero before the first launch
 };
 
 // Returns 0 on success, a negative code for bad arguments / map failures, or a CUDA error code.
@@ -815,8 +943,37 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
     configured[pair][a->epilogue] = smem;
   }
   int sms = a->sms > 0 ? a->sms : g_num_sms;
+  int gather = 0;
+  if (a->gather_ctas > 0) {
+    // the copy CTAs take SMs away from the product: all CTAs of the launch must be resident together
+    if (a->mode != 0 || !a->b_grouped || !a->gather_flags || !a->gather_dst) return -20;
+    if (a->gather_nseg < 1 || a->gather_nseg > 2 || a->gather_groups_per_rank < 1) return -21;
+    if (a->gather_group_bytes <= 0 || a->gather_group_bytes % 16 || a->gather_group_stride_src % 16) return -22;
+    if (a->gather_chunk < 1024 || a->gather_chunk % 16) return -23;
+    gather = a->gather_ctas;
+    if (pair) gather += gather & 1;
+    if (gather >= sms - 2) return -24;
+    p.gather.ctas = gather;
+    p.gather.chunk_bytes = a->gather_chunk;
+    p.gather.nbuf = int((size_t(stages) * stage_bytes) / size_t(a->gather_chunk));
+    if (p.gather.nbuf > 8) p.gather.nbuf = 8;
+    if (p.gather.nbuf < kGatherLag + 1) return -25;
+    for (int r = 0; r < 8; ++r) p.gather.src[r] = static_cast<const uint8_t*>(a->gather_src[r]);
+    p.gather.dst = static_cast<uint8_t*>(a->gather_dst);
+    for (int i = 0; i < 2; ++i) {
+      if (a->gather_seg_src_off[i] % 16 || a->gather_seg_dst_off[i] % 16) return -22;
+      p.gather.seg_src_off[i] = a->gather_seg_src_off[i]; p.gather.seg_dst_off[i] = a->gather_seg_dst_off[i];
+    }
+    const int owners = (a->groups + a->gather_groups_per_rank - 1) / a->gather_groups_per_rank;
+    if (owners > 8) return -26;
+    for (int r = 0; r < owners; ++r) if (!a->gather_src[r]) return -26;
+    p.gather.group_bytes = a->gather_group_bytes; p.gather.group_stride_src = a->gather_group_stride_src;
+    p.gather.nseg = a->gather_nseg; p.gather.groups_per_rank = a->gather_groups_per_rank;
+    p.gather.flags = a->gather_flags;
+    sms -= gather;
+  }
   if (!pair) {
-    int grid = int(tiles < sms ? tiles : sms);
+    int grid = gather + int(tiles < sms ? tiles : sms);
     kernel<<<grid, 352, smem, stream>>>(tmA, tmB, tmA2, tmB2, p, stages);
     return int(cudaGetLastError());
   }
@@ -824,7 +981,7 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
   if (tiles < pairs) pairs = int(tiles);
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(352); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cfg.gridDim = dim3(gather + 2 * pairs); cfg.blockDim = dim3(352); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;

@@ -34,6 +34,12 @@ class GemmArgs(C.Structure):
         ("max_m_tiles", C.c_int),
         ("sms", C.c_int), ("trace", C.c_void_p),
         ("prefetch_dist", C.c_int), ("prefetch_ops", C.c_int), ("max_stages", C.c_int), ("pair", C.c_int), ("debug", C.c_int),
+        # fused all-gather of B / B2 (csrc/gemm.cu: GatherParams)
+        ("gather_src", C.c_void_p * 8), ("gather_dst", C.c_void_p),
+        ("gather_seg_src_off", C.c_long * 2), ("gather_seg_dst_off", C.c_long * 2),
+        ("gather_group_bytes", C.c_long), ("gather_group_stride_src", C.c_long),
+        ("gather_nseg", C.c_int), ("gather_groups_per_rank", C.c_int), ("gather_ctas", C.c_int), ("gather_chunk", C.c_int),
+        ("gather_flags", C.c_void_p),
     ]
 
 

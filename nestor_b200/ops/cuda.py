@@ -197,6 +197,15 @@ def router_scores(x: Tensor, w1: Tensor | None, w2: Tensor, cd: torch.dtype) -> 
 
 
 # ----------------------------------------------------------------------- expert bank
+# Set by the trainer when expert banks are rank-sharded (parallel/shard.py: ShardedBanks): the bank products then
+# stage their weights from the owners' arenas inside the GEMM launch instead of reading the local copy.
+BANK_SHARDS = None
+
+
+def _bank_gather(w, w2=None):
+    return BANK_SHARDS.spec(w, w2) if BANK_SHARDS is not None else None
+
+
 class _ExpertBank(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weights, w_up, w_gate, w_down, plan: ExpertPlan, group: int):
@@ -205,8 +214,8 @@ class _ExpertBank(torch.autograd.Function):
         xs = gather_rows(x, plan.order, div=plan.slots)                       # dispatch gather [n, d]
         hh, gt, ut = (G.rows_buffer(plan.n, h, BF16, x.device) for _ in range(3))
         G.gemm_rows(xs, w_gate, B2=w_up, offsets=plan.offsets, groups=E, b_mn=True, out=hh, epilogue=G.SWIGLU,
-                    extra_out=(gt, ut))
-        y = G.gemm_rows(hh, w_down, offsets=plan.offsets, groups=E, b_mn=True)  # [n, d]
+                    extra_out=(gt, ut), gather=_bank_gather(w_gate, w_up))
+        y = G.gemm_rows(hh, w_down, offsets=plan.offsets, groups=E, b_mn=True, gather=_bank_gather(w_down))  # [n, d]
         wf = weights.float().contiguous().view(-1)
         out = combine_rows(y, plan.inv, wf, group, T * (plan.slots // group))
         ctx.save_for_backward(xs, hh, gt, ut, y, wf, w_up, w_gate, w_down)
@@ -224,10 +233,11 @@ class _ExpertBank(torch.autograd.Function):
         dgt, dut = G.rows_buffer(plan.n, h, BF16, dy.device), G.rows_buffer(plan.n, h, BF16, dy.device)
         # dH = dY . Wd^T fused with the SwiGLU derivative; Wd [E, h, d] is the K-major B of this product
         G.gemm_rows(dy, w_down, offsets=plan.offsets, groups=E, out=dgt, epilogue=G.SWIGLU_BWD, extra_out=(dut,),
-                    extra_in=(gt, ut))
+                    extra_in=(gt, ut), gather=_bank_gather(w_down))
         dx = None
         if ctx.needs_input_grad[0]:
-            dxs = G.gemm_rows(dgt, w_gate, A2=dut, B2=w_up, offsets=plan.offsets, groups=E)   # [n, d]
+            dxs = G.gemm_rows(dgt, w_gate, A2=dut, B2=w_up, offsets=plan.offsets, groups=E,
+                              gather=_bank_gather(w_gate, w_up))                                # [n, d]
             dx = combine_rows(dxs, plan.inv, None, plan.slots, T).to(ctx.x_dtype)
         dweights = None
         if dw_sorted is not None:      # the kernel indexes dw by flat slot already

@@ -10,6 +10,7 @@ TMA without any copy.
 from __future__ import annotations
 
 import ctypes as C
+import dataclasses
 import os
 
 import torch
@@ -31,6 +32,26 @@ PAIR = os.environ.get("NESTOR_B200_GEMM_PAIR", "auto")
 _PAIR_MIN_ROWS = 4096
 DEBUG = 0   # kernel timing experiments (see csrc/gemm.cu); never set outside of them
 _L2_RESIDENT_BYTES = 48 << 20    # a shared B operand smaller than this stays in L2 without help
+
+
+@dataclasses.dataclass
+class Gather:
+    """Where a rank-sharded weight operand lives, for the all-gather fused into ``gemm_rows``.
+
+    ``src[r]`` is the address of rank ``r``'s weight arena as mapped into this process and ``arena_ptr`` the
+    address of the local one: the operand handed to ``gemm_rows`` is a view of the local arena and only tells
+    *where* in an arena the groups sit; their values are read from each group's owner (``group // groups_per_rank``)
+    into ``stage`` by copy CTAs of the same launch, and the tensor maps of the product point at ``stage``.
+    ``flags`` is an ``int32`` tensor of at least ``groups + 1`` zeros shared by stream-ordered launches.
+    """
+
+    src: list[int]
+    arena_ptr: int
+    stage: Tensor
+    flags: Tensor
+    groups_per_rank: int
+    ctas: int = 8
+    chunk: int = 32768
 
 
 def pick_bn(n: int, *, mult: int = 16, cap: int = 256) -> int:
@@ -69,6 +90,31 @@ def _operand(t: Tensor | None, *, grouped: bool) -> _lib.Operand:
     return _lib.Operand(t.data_ptr(), t.shape[0], t.shape[1], t.stride(0), 1, t.shape[0] * t.stride(0))
 
 
+def _stage_for_gather(a: _lib.GemmArgs, g: Gather, B: Tensor, B2: Tensor | None) -> tuple[Tensor, Tensor | None]:
+    """Fill the gather fields of ``a`` and return the staged stand-ins of ``B`` / ``B2`` (dense, same shapes)."""
+
+    assert B.ndim == 3 and B[0].is_contiguous() and (B2 is None or (B2.shape == B.shape and B2.stride() == B.stride()))
+    groups, group_elems = B.shape[0], B.shape[1] * B.shape[2]
+    assert groups % g.groups_per_rank == 0 and groups // g.groups_per_rank <= len(g.src)
+    assert (group_elems * 2) % 16 == 0 and (B.stride(0) * 2) % 16 == 0 and g.stage.data_ptr() % 256 == 0
+    segs = [B] if B2 is None else [B, B2]
+    assert g.stage.numel() * g.stage.element_size() >= len(segs) * groups * group_elems * 2, "staging buffer too small"
+    assert g.flags.numel() >= groups + 1 and g.flags.dtype == torch.int32
+    flat = g.stage.view(torch.bfloat16).view(-1)
+    staged = []
+    for i, t in enumerate(segs):
+        a.gather_seg_src_off[i] = t.data_ptr() - g.arena_ptr
+        a.gather_seg_dst_off[i] = i * groups * group_elems * 2
+        staged.append(flat[i * groups * group_elems : (i + 1) * groups * group_elems].view(B.shape))
+    for r, ptr in enumerate(g.src):
+        a.gather_src[r] = ptr
+    a.gather_dst = g.stage.data_ptr()
+    a.gather_group_bytes, a.gather_group_stride_src = group_elems * 2, B.stride(0) * 2
+    a.gather_nseg, a.gather_groups_per_rank, a.gather_ctas, a.gather_chunk = len(segs), g.groups_per_rank, g.ctas, g.chunk
+    a.gather_flags = g.flags.data_ptr()
+    return staged[0], (staged[1] if B2 is not None else None)
+
+
 def _launch(args: _lib.GemmArgs) -> None:
     rc = _lib.lib().nb_gemm(C.byref(args), C.c_void_p(_lib.stream_ptr()))
     if rc != 0:
@@ -80,14 +126,16 @@ def gemm_rows(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: in
               out: Tensor | None = None, epilogue: int = STORE_BF16, alpha: float = 1.0, bn: int | None = None,
               A2: Tensor | None = None, B2: Tensor | None = None, extra_out: tuple = (), extra_in: tuple = (),
               n: int | None = None, n_valid: int = 0, sms: int = 0, trace: Tensor | None = None,
-              pair: bool | None = None) -> Tensor:
+              pair: bool | None = None, gather: Gather | None = None) -> Tensor:
     """Row-grouped GEMM.
 
     ``A [rows, K]``; ``B`` is ``[G, N, K]`` (K-major) or ``[G, K, N]`` (``b_mn``) — 2-D for a
     single shared matrix. ``offsets [G+1]`` (int32, device) bound the groups; ``None`` with
     ``groups == 1`` means one group over all rows. ``A2/B2`` extend the reduction. With
     ``epilogue == SWIGLU``, ``B`` is the gate bank and ``B2`` the up bank (both ``[G, K, h]``);
-    ``out`` receives ``silu(gate) * up`` and ``extra_out = (gate, up)``.
+    ``out`` receives ``silu(gate) * up`` and ``extra_out = (gate, up)``. With ``gather``, ``B`` (and ``B2``)
+    are 3-D views of the local weight arena whose groups are owned by different ranks: the launch stages them
+    from their owners while it computes (see ``Gather``).
     """
 
     rows, K = A.shape
@@ -129,6 +177,8 @@ def gemm_rows(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: in
         assert rows % groups == 0
         a.rows_per_group = rows // groups
     a.a_mn, a.b_mn, a.b_grouped = 0, int(b_mn), int(B.ndim == 3)
+    if gather is not None:
+        B, B2 = _stage_for_gather(a, gather, B, B2)
     a.A, a.B = _operand(A, grouped=False), _operand(B, grouped=True)
     a.A2, a.B2 = _operand(A2, grouped=False), _operand(B2, grouped=True)
     a.C, a.ldc, a.c_group_stride = out.data_ptr(), out.stride(0), 0

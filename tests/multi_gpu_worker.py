@@ -15,6 +15,45 @@ from nestor_b200.parallel import symm
 from nestor_b200.utils.distributed import init_distributed
 
 
+def check_gathered_gemm(dev, rank: int, world: int) -> None:
+    """Grouped products whose weights are staged from their owner ranks inside the GEMM launch."""
+
+    from nestor_b200.ops import gemm as G
+    E, d, h, rows = 8, 640, 216, 6000
+    torch.manual_seed(7)                       # the same values on every rank
+    Wg, Wu = (torch.randn(E, d, h, device=dev) * 0.05).bfloat16(), (torch.randn(E, d, h, device=dev) * 0.05).bfloat16()
+    X = torch.randn(rows, d, device=dev).bfloat16()
+    off = torch.tensor([0, 700, 700, 1500, 2600, 3000, 4100, 5000, rows], dtype=torch.int32, device=dev)
+    n = E * d * h
+    arena = symm.symmetric_empty(2 * n + 64, torch.bfloat16, dev)
+    arena.fill_(float("nan"))                  # a rank holds valid values for its own experts only
+    per = E // world
+    vg, vu = arena[64 : 64 + n].view(E, d, h), arena[64 + n : 64 + 2 * n].view(E, d, h)
+    vg[rank * per : (rank + 1) * per] = Wg[rank * per : (rank + 1) * per]
+    vu[rank * per : (rank + 1) * per] = Wu[rank * per : (rank + 1) * per]
+    handle = symm.rendezvous(arena)
+    torch.cuda.synchronize()
+    dist.barrier()
+    spec = G.Gather(src=[int(handle.buffer_ptrs[r]) for r in range(world)], arena_ptr=arena.data_ptr(),
+                    stage=torch.full((2 * n,), float("nan"), device=dev, dtype=torch.bfloat16),
+                    flags=torch.zeros(257, dtype=torch.int32, device=dev), groups_per_rank=per, ctas=8)
+
+    def run(gather, wg, wu):
+        H = torch.full((rows, h), float("nan"), device=dev, dtype=torch.bfloat16)
+        Gt, Ut = torch.empty_like(H), torch.empty_like(H)
+        G.gemm_rows(X, wg, B2=wu, offsets=off, groups=E, b_mn=True, out=H, epilogue=G.SWIGLU, extra_out=(Gt, Ut),
+                    gather=gather)
+        return H, G.gemm_rows(H, wg, offsets=off, groups=E, gather=gather)
+
+    want = run(None, Wg, Wu)
+    for _ in range(2):
+        got = run(spec, vg, vu)
+        torch.cuda.synchronize()
+        _lib.check_status(dev)
+        assert all(torch.equal(a, b) for a, b in zip(want, got)), "fused all-gather GEMM mismatch"
+    dist.barrier()
+
+
 def main() -> None:
     dev = init_distributed(True)
     rank, world = dist.get_rank(), dist.get_world_size()
@@ -61,6 +100,7 @@ def main() -> None:
     dist.barrier()
     want = torch.arange(1, world + 1, device=dev, dtype=torch.float32).repeat_interleave(per)
     assert torch.equal(master, want) and torch.equal(comp.float(), want), "parameter push mismatch"
+    check_gathered_gemm(dev, rank, world)
     os.environ.setdefault("DCLM_DATA_PATH", "/tmp/unused.bin")
     from nestor_b200.experiments.tiny import nestor_tiny
     from nestor_b200.models import Model
@@ -94,6 +134,27 @@ def main() -> None:
         del tr
     rel = ((results["1"] - results["0"]).norm() / results["0"].norm()).item()
     assert rel < 1e-5, f"sharded and replicated optimizer paths disagree: {rel}"
+    # expert banks read from their owner ranks through the all-gather fused into the bank GEMMs
+    from nestor_b200.ops import cuda as cuda_ops
+    os.environ["NESTOR_ZERO1"], os.environ["NESTOR_FSDP_BANKS"] = "1", "1"
+    torch.manual_seed(0)
+    job = nestor_tiny().jobs[0]
+    tr = Trainer(job, Model.from_config(job.model), [], device=dev)
+    assert cuda_ops.BANK_SHARDS is not None
+    tr.model.train()
+    for step in range(3):
+        torch.manual_seed(1000 + step * 10 + rank)
+        ids = torch.randint(0, 100277, (2, 256), device=dev)
+        loss, counts = tr.train_step((ids, ids))
+        tr.update_weights(counts)
+    torch.cuda.synchronize()
+    _lib.check_status(dev)
+    assert cuda_ops.BANK_SHARDS.gathered_bytes > 0, "no bank product used the fused all-gather"
+    rel = ((tr.arena.master - results["1"]).norm() / results["1"].norm()).item()
+    assert rel < 1e-5, f"rank-sharded banks disagree with replicated banks: {rel}"
+    cuda_ops.BANK_SHARDS = None
+    os.environ["NESTOR_FSDP_BANKS"] = "0"
+    dist.barrier()
     if rank == 0:
         print("MULTI_GPU_OK", flush=True)
     dist.destroy_process_group()

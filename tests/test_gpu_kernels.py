@@ -424,3 +424,60 @@ def test_attention_with_head_dims_that_are_not_multiples_of_eight(d, H, hd, Gc, 
     assert _rel(out, out2) < 1e-2
     for a, b in pairs:
         assert _rel(a.grad, b.grad) < 2e-2
+
+
+@pytest.mark.parametrize("rows,world", [(9000, 4), (1500, 2)])
+def test_gemm_with_fused_all_gather_of_rank_sharded_banks(rows, world):
+    """Weights staged from their owners' arenas by copy CTAs of the same launch (ranks emulated as local buffers).
+
+    Every emulated arena holds valid values only for the groups its rank owns (NaN elsewhere, the local arena
+    included), so a finite result equal to the ungathered product proves that each group came from its owner.
+    """
+
+    from nestor_b200.ops import gemm as G
+    torch.manual_seed(5)
+    E, d, h = 8, 640, 216
+    per = E // world
+    off = _offsets(rows, E, empty=(3,))
+    X = torch.randn(rows, d, device="cuda").to(BF)
+    Hh = torch.randn(rows, h, device="cuda").to(BF)
+    Wg, Wu = (torch.randn(E, d, h, device="cuda") * 0.05).to(BF), (torch.randn(E, d, h, device="cuda") * 0.05).to(BF)
+    Wd = (torch.randn(E, h, d, device="cuda") * 0.05).to(BF)
+    # arena layout: [pad | gate | up | down(strided groups)]; the down bank sits at a group stride wider than a group
+    n_gu, n_d, gap = E * d * h, h * d, 64
+    o_g, o_u, o_d = 128, 128 + n_gu, 128 + 2 * n_gu
+    total = o_d + E * (n_d + gap)
+    arenas = []
+    for r in range(world):
+        a = torch.full((total,), float("nan"), device="cuda", dtype=BF)
+        lo, hi = r * per, (r + 1) * per
+        a[o_g : o_g + n_gu].view(E, d, h)[lo:hi] = Wg[lo:hi]
+        a[o_u : o_u + n_gu].view(E, d, h)[lo:hi] = Wu[lo:hi]
+        torch.as_strided(a, (E, h, d), (n_d + gap, d, 1), o_d)[lo:hi] = Wd[lo:hi]
+        arenas.append(a)
+    local = arenas[0]
+    vg, vu = local[o_g : o_g + n_gu].view(E, d, h), local[o_u : o_u + n_gu].view(E, d, h)
+    vd = torch.as_strided(local, (E, h, d), (n_d + gap, d, 1), o_d)
+    stage = torch.full((2 * n_gu,), float("nan"), device="cuda", dtype=BF)
+    flags = torch.zeros(257, dtype=torch.int32, device="cuda")
+    spec = G.Gather(src=[a.data_ptr() for a in arenas], arena_ptr=local.data_ptr(), stage=stage, flags=flags,
+                    groups_per_rank=per, ctas=6)
+
+    def run(gather, wg, wu, wd):
+        H = torch.full((rows, h), float("nan"), device="cuda", dtype=BF)
+        Gt, Ut = torch.empty_like(H), torch.empty_like(H)
+        G.gemm_rows(X, wg, B2=wu, offsets=off, groups=E, b_mn=True, out=H, epilogue=G.SWIGLU, extra_out=(Gt, Ut),
+                    gather=gather)
+        Y = G.gemm_rows(Hh, wd, offsets=off, groups=E, b_mn=True, gather=gather)          # down: MN-major B
+        dH = G.gemm_rows(X, wd, offsets=off, groups=E, gather=gather)                     # K-major B [E, h, d]
+        dX = G.gemm_rows(Hh, wg, A2=Hh, B2=wu, offsets=off, groups=E, gather=gather)      # two segments
+        return H, Gt, Ut, Y, dH, dX
+
+    want = run(None, Wg, Wu, Wd)
+    for _ in range(2):       # twice: the counters must come back to zero between launches
+        got = run(spec, vg, vu, vd)
+        torch.cuda.synchronize()
+        assert int(flags.abs().sum().item()) == 0
+        for w, g in zip(want, got):
+            assert torch.isfinite(g.float()).all()
+            assert torch.equal(w, g)
