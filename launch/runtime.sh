@@ -7,6 +7,7 @@ export NESTOR_DENSE_NO_ROUTER="${NESTOR_DENSE_NO_ROUTER:-1}"          # single-c
 export NESTOR_STACKED_EXPERT_BANKS="${NESTOR_STACKED_EXPERT_BANKS:-1}" # checkpoint layout of the expert banks
 export NESTOR_MUON_SHARD="${NESTOR_MUON_SHARD:-1}"                    # one owner rank per Muon matrix
 export NESTOR_ZERO1="${NESTOR_ZERO1:-1}"                              # AdamW state sharded like Muon (owner of an arena range updates it)
+export NESTOR_FSDP_BANKS="${NESTOR_FSDP_BANKS:-0}"                      # expert banks read from their owner ranks inside the bank GEMMs (slower than replicated banks on 2 GPUs; saves no memory yet)
 export NESTOR_ACTIVATION_CHECKPOINT="${NESTOR_ACTIVATION_CHECKPOINT:-0}" # recompute each block in the backward pass
 export NESTOR_FUSED_HEAD_CE="${NESTOR_FUSED_HEAD_CE:-1}"              # chunked head + cross-entropy, no [T, V] logits
 export NESTOR_CE_CHUNK_ROWS="${NESTOR_CE_CHUNK_ROWS:-4096}"

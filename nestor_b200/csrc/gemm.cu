@@ -12,7 +12,7 @@
 // Operands are bf16, K-major (rows of K) or MN-major (rows of M/N); see sm100.cuh.
 // A second (A2, B2) operand pair extends the reduction (dX = dG.Wg^T + dU.Wu^T in one pass).
 //
-// Warp roles (352 threads): warp 0 = TMA producer of A tiles, warp 10 = TMA producer of B tiles, warp 1 = MMA
+// Warp roles (352 threads; a gathering launch adds warp 11, see GatherParams): warp 0 = TMA producer of A tiles, warp 10 = TMA producer of B tiles, warp 1 = MMA
 // issuer (+TMEM owner), warps 2..9 = epilogue (warp w reads TMEM lanes 32*(w%4)..+31; the two warps of a lane
 // quarter take alternating 32-column chunks). Two accumulator buffers let the epilogue of tile i overlap the main
 // loop of tile i+1. With PAIR = 1 the kernel runs as clusters of two CTAs on 256-row tiles (cta_group::2): each CTA
@@ -45,12 +45,14 @@ enum Epilogue : int {
 // All-gather fused into the product (mode 0, grouped B). The groups of B (one or two tensors of the same shape:
 // B and, for SwiGLU / two-segment products, B2) are sharded over ranks: rank r holds the current values of groups
 // [r * groups_per_rank, (r + 1) * groups_per_rank) in its copy of the weight arena, which every rank maps
-// (`src[r]`). The first `ctas` CTAs of the launch do not compute: they pull every group from its owner into the
-// local staging tensor that the B tensor maps describe, in group order, with bulk copies through shared memory,
-// and count finished chunks in `flags[group]`. The B producers of the computing CTAs wait (bounded) for a group's
-// count before their first load of it, so the product of the early groups overlaps the transfer of the later
-// ones. Nothing waits on another GPU: a shard is constant while the products that read it run. The last CTA to
-// leave zeroes the counters for the next launch (launches that share `flags` must be stream-ordered).
+// (`src[r]`). A twelfth warp of every CTA of the launch pulls its share of the chunks of every group from the
+// group's owner into the local staging tensor that the B tensor maps describe, in group order, with bulk copies
+// through a small shared-memory ring, and counts finished chunks in `flags[group]`. (The bytes one SM can keep in
+// flight over NVLink bound its copy rate to about 13 GB/s, so the copy is spread over all SMs instead of being
+// given to a few dedicated CTAs.) The B producers wait (bounded) for a group's count before their first load of
+// it, so the product of the early groups overlaps the transfer of the later ones. Nothing waits on another GPU:
+// a shard is constant while the products that read it run. The last CTA to leave zeroes the counters for the next
+// launch (launches that share `flags` must be stream-ordered).
 struct GatherParams {
   const uint8_t* src[8];       // per rank: base address of its weight arena as mapped here
   uint8_t* dst;                // base address of the local staging tensors
@@ -60,9 +62,10 @@ struct GatherParams {
   long group_stride_src;       // byte distance between groups in the arena (the staging is dense)
   int nseg;                    // 1 or 2 tensors
   int groups_per_rank;
-  int ctas;                    // leading CTAs that gather (even for CTA pairs); 0 = no gather
+  int on;                      // 0 = no gather
   int chunk_bytes;             // bulk-copy granularity (multiple of 16)
-  int nbuf;                    // shared-memory ring depth (chunks), 3..8
+  int nbuf;                    // shared-memory ring depth per copying lane (chunks), >= 2
+  int lanes;                   // lanes of the copy warp that copy (1..4); lanes * nbuf <= 8
   int* flags;                  // [groups] finished chunks per group, then [groups]: CTAs that left
 };
 
@@ -89,7 +92,7 @@ struct GemmParams {
   int pair;                    // mode 0: CTA pairs (cluster of 2) run 256-row tiles with cta_group::2 MMAs
   int a_atoms, b_atoms;        // MN-major operand read through an "atom" map: one TMA instruction per k-block
   int debug;                   // timing experiments only (results are garbage): 1 = issue no MMAs, 2 = issue no loads, 4 = store nothing
-  GatherParams gather;         // fused all-gather of a rank-sharded B operand (gather.ctas == 0: off)
+  GatherParams gather;         // fused all-gather of a rank-sharded B operand (gather.on == 0: off)
 };
 
 __device__ __forceinline__ unsigned long long gtime() {
@@ -197,67 +200,81 @@ __device__ __forceinline__ void load_chunk_bf16(uint8_t* slab, int lane, uint32_
   __syncwarp();
 }
 
-// The copy role of a fused all-gather launch (see GatherParams). One thread drives a ring of `nbuf` chunk buffers:
-// loads run `nbuf - kGatherLag` chunks ahead; a chunk is published once its store to the staging tensor has
-// completed, which is also when its buffer is reused.
-constexpr int kGatherLag = 2;
+// The copy warp of a fused all-gather launch (see GatherParams). One thread drives a ring of `nbuf` chunk buffers.
+// A buffer is refilled as soon as the store that drains it has read it (`wait_group.read`), so `nbuf - 1` loads
+// stay in flight; a chunk is published `kGatherLag` stores later, when its store has completed. No proxy fence
+// sits in the loop: the mbarrier orders load -> store inside the async proxy, and the completion of a bulk group
+// is what makes the stored bytes visible to this thread before it releases them with a fence and the counter
+// (the consumer's own proxy fence then orders its TMA loads after its flag read).
+constexpr int kGatherLag = 4;
 constexpr uint32_t kGatherSpinLimit = 1u << 22;   // polls of >= 100 ns: a consumer gives up after about half a second
-__device__ __noinline__ void gather_role(const GatherParams& g, int groups, uint8_t* smem, uint64_t* bars, int* status) {
-  if (threadIdx.x != 0) return;
-  for (int b = 0; b < g.nbuf; ++b) mbar_init(&bars[b], 1);
+__device__ __noinline__ void gather_role(const GatherParams& g, int groups, uint8_t* smem, uint64_t* bars, int* status,
+                                         volatile int* abort_flag) {
+  // per-buffer destination and size, and the group of each recent chunk, are computed once when the chunk's load
+  // is issued: one thread runs this loop, so its index arithmetic (32-bit, one division per chunk) is on the
+  // critical path of the copy
+  __shared__ uint8_t* s_dst_all[4][8];
+  __shared__ uint32_t s_bytes_all[4][8];
+  __shared__ int s_grp_all[4][16];
+  // up to four lanes of the warp run the loop independently, each on its own slice of the ring, its own barriers
+  // and its own bulk groups: the loop is a chain of waits, so several chains per SM raise the copy rate
+  const uint32_t lane = threadIdx.x & 31u, lanes = uint32_t(g.lanes);
+  if (lane >= lanes) return;
+  const uint32_t nbuf = uint32_t(g.nbuf);
+  uint8_t** s_dst = s_dst_all[lane];
+  uint32_t* s_bytes = s_bytes_all[lane];
+  int* s_grp = s_grp_all[lane];
+  bars += lane * nbuf;
+  smem += size_t(lane) * nbuf * uint32_t(g.chunk_bytes);
+  for (uint32_t b = 0; b < nbuf; ++b) mbar_init(&bars[b], 1);
   fence_barrier_init();
-  const long chunk = g.chunk_bytes;
-  const long per_seg = (g.group_bytes + chunk - 1) / chunk;
-  const long per_group = per_seg * g.nseg;
-  const long total = long(groups) * per_group;
-  const long first = blockIdx.x, step = g.ctas;
-  const long n_mine = first < total ? (total - first + step - 1) / step : 0;
-  int abort_local = 0;
-  volatile int* abort_flag = &abort_local;
-  auto locate = [&](long i, const uint8_t*& src, uint8_t*& dst, uint32_t& bytes) -> int {
-    const long c = first + i * step;
-    const int grp = int(c / per_group);
-    const long rem = c - long(grp) * per_group;
-    const int seg = int(rem / per_seg);
-    const long off = (rem - long(seg) * per_seg) * chunk;
-    bytes = uint32_t(min(chunk, g.group_bytes - off));
-    src = g.src[grp / g.groups_per_rank] + g.seg_src_off[seg] + long(grp) * g.group_stride_src + off;
-    dst = g.dst + g.seg_dst_off[seg] + long(grp) * g.group_bytes + off;
-    return grp;
+  const uint32_t chunk = uint32_t(g.chunk_bytes);
+  const uint32_t per_seg = uint32_t((g.group_bytes + chunk - 1) / chunk);
+  const uint32_t per_group = per_seg * uint32_t(g.nseg);
+  const uint32_t total = uint32_t(groups) * per_group;
+  const uint32_t first = blockIdx.x * lanes + lane, step = gridDim.x * lanes;
+  const uint32_t n_mine = first < total ? (total - first + step - 1) / step : 0;
+  uint32_t li = 0, lb = 0, lc = first;       // next load: index, buffer, global chunk number
+  auto load = [&]() {
+    const uint32_t grp = lc / per_group;
+    uint32_t rem = lc - grp * per_group;
+    const uint32_t seg = rem >= per_seg ? 1u : 0u;
+    rem -= seg * per_seg;
+    const long off = long(rem) * chunk;
+    const long left = g.group_bytes - off;
+    const uint32_t bytes = left < long(chunk) ? uint32_t(left) : chunk;
+    const uint8_t* src = g.src[grp / uint32_t(g.groups_per_rank)] + g.seg_src_off[seg] + long(grp) * g.group_stride_src + off;
+    s_dst[lb] = g.dst + g.seg_dst_off[seg] + long(grp) * g.group_bytes + off;
+    s_bytes[lb] = bytes;
+    s_grp[li & 15u] = int(grp);
+    mbar_expect_tx(&bars[lb], bytes);
+    bulk_load(smem + size_t(lb) * chunk, src, bytes, &bars[lb]);
+    ++li; lc += step;
+    if (++lb == nbuf) lb = 0;
   };
-  auto load = [&](long i) {
-    const uint8_t* src; uint8_t* dst; uint32_t bytes;
-    locate(i, src, dst, bytes);
-    const int b = int(i % g.nbuf);
-    mbar_expect_tx(&bars[b], bytes);
-    bulk_load(smem + long(b) * chunk, src, bytes, &bars[b]);
-  };
-  auto publish = [&](long i) {
-    const uint8_t* src; uint8_t* dst; uint32_t bytes;
-    const int grp = locate(i, src, dst, bytes);
-    fence_async_all();
+  auto publish = [&](uint32_t i) {
     __threadfence();
-    atomicAdd(&g.flags[grp], 1);
+    atomicAdd(&g.flags[s_grp[i & 15u]], 1);
   };
-  for (long i = 0; i < n_mine && i < g.nbuf; ++i) load(i);
-  long done = 0;      // chunks published
-  for (long i = 0; i < n_mine; ++i) {
-    const int b = int(i % g.nbuf);
-    if (!mbar_wait(&bars[b], uint32_t(i / g.nbuf) & 1u, abort_flag, status, kTimeoutPeer, 64)) break;
-    const uint8_t* src; uint8_t* dst; uint32_t bytes;
-    locate(i, src, dst, bytes);
-    fence_async_smem();
-    bulk_store(dst, smem + long(b) * chunk, bytes);
+  while (li < n_mine && li < nbuf) load();
+  uint32_t done = 0, b = 0, ph = 0;      // chunks published; buffer and barrier phase of chunk i
+  for (uint32_t i = 0; i < n_mine; ++i) {
+    if (!mbar_wait(&bars[b], ph, abort_flag, status, kTimeoutPeer, 32)) break;
+    bulk_store(s_dst[b], smem + size_t(b) * chunk, s_bytes[b]);
     bulk_commit();
-    if (i >= kGatherLag) {
+    if (i >= 1 && li < n_mine) {
+      bulk_wait_read<1>();                      // the store of chunk i - 1 has read its buffer: refill it
+      load();
+    }
+    if (i >= uint32_t(kGatherLag)) {
       bulk_wait<kGatherLag>();
       publish(i - kGatherLag);
       ++done;
-      if (i - kGatherLag + g.nbuf < n_mine) load(i - kGatherLag + g.nbuf);   // its buffer: the chunk just published
     }
+    if (++b == nbuf) { b = 0; ph ^= 1u; }
   }
-  bulk_wait<0>();        // also on a timeout: no copy of this CTA is in flight when it leaves
-  if (!abort_local) for (; done < n_mine; ++done) publish(done);
+  bulk_wait<0>();        // also on a timeout: no store of this CTA is in flight when it leaves
+  if (!*abort_flag) for (; done < n_mine; ++done) publish(done);
 }
 
 // Every CTA of a gathering launch counts itself out; the last one clears the counters for the next launch.
@@ -274,12 +291,12 @@ __device__ __forceinline__ void gather_leave(const GatherParams& g, int groups) 
 // with every variant in one kernel the eleven warps of a CTA (each in a different code region) thrash the
 // instruction cache, which showed as "no instruction" stalls on every role.
 template <int PAIR, int EPI>
-__global__ void __launch_bounds__(352, 1)
+__global__ void __launch_bounds__(384, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
             const GemmParams p, int stages) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ uint64_t full_bar[8], empty_bar[8], tfull_bar[2], tempty_bar[2];
+  __shared__ uint64_t full_bar[8], empty_bar[8], tfull_bar[2], tempty_bar[2], gather_bar[8];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int s_abort;
   __shared__ int s_off[kMaxGroups + 1];
@@ -288,12 +305,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int pair = PAIR;
-  const int n_gather = p.gather.ctas;
-  if (int(blockIdx.x) < n_gather) {       // copy role (whole pairs when PAIR): no TMEM, no cluster barrier
-    gather_role(p.gather, p.groups, smem, full_bar, p.status);
-    if (threadIdx.x == 0) gather_leave(p.gather, p.groups);
-    return;
-  }
+  const int n_gather = p.gather.on;
   const uint32_t rank = pair ? cluster_ctarank() : 0u;   // rank 0 of a pair issues the MMAs
   const int b_cols = pair ? p.BN / 2 : p.BN;             // B columns staged by this CTA
   const uint32_t a_bytes = BM * BK * 2;               // 16 KB
@@ -335,8 +347,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   else total_tiles = p.groups * ((p.M + BM - 1) / BM) * n_tiles * p.splits;
 
   volatile int* abort_flag = &s_abort;
-  const int cta = pair ? int((blockIdx.x - n_gather) >> 1) : int(blockIdx.x) - n_gather;   // persistent worker index
-  const int n_cta = pair ? int((gridDim.x - n_gather) >> 1) : int(gridDim.x) - n_gather;
+  const int cta = pair ? int(blockIdx.x >> 1) : int(blockIdx.x);       // persistent worker index
+  const int n_cta = pair ? int(gridDim.x >> 1) : int(gridDim.x);
 
   if (warp == 0 || warp == 10) {
     // ------------------------------------------- TMA producers (warp 0: A tiles, warp 10: B tiles)
@@ -561,6 +573,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       unsigned long long* tr = p.trace + blockIdx.x * 64;
       tr[56] = acc_wait; tr[57] = acc_issue; tr[58] = acc_commit; tr[60] = it; tr[61] = acc_tempty;
     }
+  } else if (warp == 11) {
+    // ----------------------------------------------------------------- copy warp of a gathering launch
+    if (n_gather)
+      gather_role(p.gather, p.groups, smem + uint32_t(stages) * stage_bytes + 8 * kSlabBytes, gather_bar, p.status, abort_flag);
   } else {
     // ----------------------------------------------------------------- epilogue
     // Eight warps: warp w reads TMEM lane quarter w % 4 (its 32 rows); the two warps of a quarter split the
@@ -831,13 +847,15 @@ struct NbGemmArgs {
   int max_stages;           // 0 = as many as fit
   int pair;                 // mode 0 only: 256-row tiles on CTA pairs (cta_group::2), each CTA stages half of B
   int debug;                // timing experiments: 1 = no MMAs, 2 = no loads (outputs are garbage)
-  // fused all-gather of B (and B2) from rank-sharded weight arenas; see nb::GatherParams. gather_ctas == 0: off.
+  // fused all-gather of B (and B2) from rank-sharded weight arenas; see nb::GatherParams. gather_on == 0: off.
   const void* gather_src[8];
   void* gather_dst;
   long gather_seg_src_off[2], gather_seg_dst_off[2];
   long gather_group_bytes, gather_group_stride_src;
-  int gather_nseg, gather_groups_per_rank, gather_ctas, gather_chunk;
+  int gather_nseg, gather_groups_per_rank, gather_on, gather_chunk;
   int* gather_flags;        // [groups + 1] ints, zero before the first launch
+  int gather_nbuf;          // ring depth per copying lane (chunks)
+  int gather_lanes;         // copying lanes of the copy warp (0 = 1)
 };
 
 // Returns 0 on success, a negative code for bad arguments / map failures, or a CUDA error code.
@@ -925,11 +943,37 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
                             : long(a->groups) * ((a->M + BM - 1) / BM) * n_tiles * p.splits;
   if (tiles <= 0) return 0;
   const uint32_t stage_bytes = BM * BK * 2 + (pair ? a->BN / 2 : a->BN) * BK * 2;
-  int stages = int((200 * 1024) / stage_bytes);   // 227 KB per CTA minus epilogue slabs, barriers, offsets, alignment slack
+  size_t ring_bytes = 0;
+  if (a->gather_on) {
+    if (a->mode != 0 || !a->b_grouped || !a->gather_flags || !a->gather_dst) return -20;
+    if (a->gather_nseg < 1 || a->gather_nseg > 2 || a->gather_groups_per_rank < 1) return -21;
+    if (a->gather_group_bytes <= 0 || a->gather_group_bytes % 16 || a->gather_group_stride_src % 16) return -22;
+    if (a->gather_chunk < 1024 || a->gather_chunk % 1024 || a->gather_chunk > 32768) return -23;
+    p.gather.on = 1;
+    p.gather.chunk_bytes = a->gather_chunk;
+    p.gather.nbuf = a->gather_nbuf;
+    p.gather.lanes = a->gather_lanes > 0 ? a->gather_lanes : 1;
+    if (p.gather.lanes > 4 || p.gather.nbuf < 2 || p.gather.nbuf * p.gather.lanes > 8 ||
+        size_t(p.gather.nbuf) * p.gather.lanes * a->gather_chunk > 64 * 1024) return -25;
+    for (int r = 0; r < 8; ++r) p.gather.src[r] = static_cast<const uint8_t*>(a->gather_src[r]);
+    p.gather.dst = static_cast<uint8_t*>(a->gather_dst);
+    for (int i = 0; i < 2; ++i) {
+      if (a->gather_seg_src_off[i] % 16 || a->gather_seg_dst_off[i] % 16) return -22;
+      p.gather.seg_src_off[i] = a->gather_seg_src_off[i]; p.gather.seg_dst_off[i] = a->gather_seg_dst_off[i];
+    }
+    const int owners = (a->groups + a->gather_groups_per_rank - 1) / a->gather_groups_per_rank;
+    if (owners > 8) return -26;
+    for (int r = 0; r < owners; ++r) if (!a->gather_src[r]) return -26;
+    p.gather.group_bytes = a->gather_group_bytes; p.gather.group_stride_src = a->gather_group_stride_src;
+    p.gather.nseg = a->gather_nseg; p.gather.groups_per_rank = a->gather_groups_per_rank;
+    p.gather.flags = a->gather_flags;
+    ring_bytes = size_t(p.gather.nbuf) * p.gather.lanes * a->gather_chunk;
+  }
+  int stages = int((200 * 1024 - ring_bytes) / stage_bytes);   // 227 KB per CTA minus epilogue slabs, barriers, offsets, alignment slack
   if (stages > 8) stages = 8;
   if (a->max_stages > 0 && stages > a->max_stages) stages = a->max_stages;
   if (stages < 2) return -7;
-  size_t smem = size_t(stages) * stage_bytes + 1024 + 8 * kSlabBytes;
+  size_t smem = size_t(stages) * stage_bytes + 1024 + 8 * kSlabBytes + ring_bytes;
   typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams, int);
   static const KernelFn kernels[2][6] = {
       {gemm_kernel<0, 0>, gemm_kernel<0, 1>, gemm_kernel<0, 2>, gemm_kernel<0, 3>, gemm_kernel<0, 4>, gemm_kernel<0, 5>},
@@ -943,45 +987,17 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
     configured[pair][a->epilogue] = smem;
   }
   int sms = a->sms > 0 ? a->sms : g_num_sms;
-  int gather = 0;
-  if (a->gather_ctas > 0) {
-    // the copy CTAs take SMs away from the product: all CTAs of the launch must be resident together
-    if (a->mode != 0 || !a->b_grouped || !a->gather_flags || !a->gather_dst) return -20;
-    if (a->gather_nseg < 1 || a->gather_nseg > 2 || a->gather_groups_per_rank < 1) return -21;
-    if (a->gather_group_bytes <= 0 || a->gather_group_bytes % 16 || a->gather_group_stride_src % 16) return -22;
-    if (a->gather_chunk < 1024 || a->gather_chunk % 16) return -23;
-    gather = a->gather_ctas;
-    if (pair) gather += gather & 1;
-    if (gather >= sms - 2) return -24;
-    p.gather.ctas = gather;
-    p.gather.chunk_bytes = a->gather_chunk;
-    p.gather.nbuf = int((size_t(stages) * stage_bytes) / size_t(a->gather_chunk));
-    if (p.gather.nbuf > 8) p.gather.nbuf = 8;
-    if (p.gather.nbuf < kGatherLag + 1) return -25;
-    for (int r = 0; r < 8; ++r) p.gather.src[r] = static_cast<const uint8_t*>(a->gather_src[r]);
-    p.gather.dst = static_cast<uint8_t*>(a->gather_dst);
-    for (int i = 0; i < 2; ++i) {
-      if (a->gather_seg_src_off[i] % 16 || a->gather_seg_dst_off[i] % 16) return -22;
-      p.gather.seg_src_off[i] = a->gather_seg_src_off[i]; p.gather.seg_dst_off[i] = a->gather_seg_dst_off[i];
-    }
-    const int owners = (a->groups + a->gather_groups_per_rank - 1) / a->gather_groups_per_rank;
-    if (owners > 8) return -26;
-    for (int r = 0; r < owners; ++r) if (!a->gather_src[r]) return -26;
-    p.gather.group_bytes = a->gather_group_bytes; p.gather.group_stride_src = a->gather_group_stride_src;
-    p.gather.nseg = a->gather_nseg; p.gather.groups_per_rank = a->gather_groups_per_rank;
-    p.gather.flags = a->gather_flags;
-    sms -= gather;
-  }
+  const int threads = p.gather.on ? 384 : 352;
   if (!pair) {
-    int grid = gather + int(tiles < sms ? tiles : sms);
-    kernel<<<grid, 352, smem, stream>>>(tmA, tmB, tmA2, tmB2, p, stages);
+    int grid = int(tiles < sms ? tiles : sms);
+    kernel<<<grid, threads, smem, stream>>>(tmA, tmB, tmA2, tmB2, p, stages);
     return int(cudaGetLastError());
   }
   int pairs = sms / 2;
   if (tiles < pairs) pairs = int(tiles);
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(gather + 2 * pairs); cfg.blockDim = dim3(352); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(threads); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;

@@ -38,8 +38,8 @@ class GemmArgs(C.Structure):
         ("gather_src", C.c_void_p * 8), ("gather_dst", C.c_void_p),
         ("gather_seg_src_off", C.c_long * 2), ("gather_seg_dst_off", C.c_long * 2),
         ("gather_group_bytes", C.c_long), ("gather_group_stride_src", C.c_long),
-        ("gather_nseg", C.c_int), ("gather_groups_per_rank", C.c_int), ("gather_ctas", C.c_int), ("gather_chunk", C.c_int),
-        ("gather_flags", C.c_void_p),
+        ("gather_nseg", C.c_int), ("gather_groups_per_rank", C.c_int), ("gather_on", C.c_int), ("gather_chunk", C.c_int),
+        ("gather_flags", C.c_void_p), ("gather_nbuf", C.c_int), ("gather_lanes", C.c_int),
     ]
 
 

@@ -41,7 +41,9 @@ class Gather:
     ``src[r]`` is the address of rank ``r``'s weight arena as mapped into this process and ``arena_ptr`` the
     address of the local one: the operand handed to ``gemm_rows`` is a view of the local arena and only tells
     *where* in an arena the groups sit; their values are read from each group's owner (``group // groups_per_rank``)
-    into ``stage`` by copy CTAs of the same launch, and the tensor maps of the product point at ``stage``.
+    into ``stage`` by a copy warp in every CTA of the same launch, and the tensor maps of the product point at
+    ``stage``. ``lanes`` lanes of that warp copy independently; ``chunk`` x ``nbuf`` x ``lanes`` bytes of shared
+    memory per CTA go to the copy rings (``nbuf * lanes <= 8``).
     ``flags`` is an ``int32`` tensor of at least ``groups + 1`` zeros shared by stream-ordered launches.
     """
 
@@ -50,8 +52,9 @@ class Gather:
     stage: Tensor
     flags: Tensor
     groups_per_rank: int
-    ctas: int = 8
-    chunk: int = 32768
+    chunk: int = 8192
+    nbuf: int = 4
+    lanes: int = 1
 
 
 def pick_bn(n: int, *, mult: int = 16, cap: int = 256) -> int:
@@ -110,7 +113,8 @@ def _stage_for_gather(a: _lib.GemmArgs, g: Gather, B: Tensor, B2: Tensor | None)
         a.gather_src[r] = ptr
     a.gather_dst = g.stage.data_ptr()
     a.gather_group_bytes, a.gather_group_stride_src = group_elems * 2, B.stride(0) * 2
-    a.gather_nseg, a.gather_groups_per_rank, a.gather_ctas, a.gather_chunk = len(segs), g.groups_per_rank, g.ctas, g.chunk
+    a.gather_nseg, a.gather_groups_per_rank, a.gather_on, a.gather_chunk = len(segs), g.groups_per_rank, 1, g.chunk
+    a.gather_nbuf, a.gather_lanes = g.nbuf, g.lanes
     a.gather_flags = g.flags.data_ptr()
     return staged[0], (staged[1] if B2 is not None else None)
 

@@ -3,8 +3,8 @@
 With ``NESTOR_FSDP_BANKS=1`` the expert-bank products of a data-parallel run stop reading the local bf16
 copy of the banks: rank ``r`` is the owner of experts ``[r * E / W, (r + 1) * E / W)`` of every bank, and each
 product that consumes a bank stages the experts from their owners' weight arenas (which every rank maps through
-symmetric memory) inside the GEMM launch itself — copy CTAs pull the shards over NVLink with bulk copies while
-the remaining CTAs already multiply the experts that have arrived (``csrc/gemm.cu``: ``GatherParams``). The
+symmetric memory) inside the GEMM launch itself — a copy warp in every CTA pulls the shards over NVLink with bulk
+copies while the other warps already multiply the experts that have arrived (``csrc/gemm.cu``: ``GatherParams``). The
 staging buffer holds one product's banks only and is reused by the next product, forward and backward alike
 (the "reshard after forward" policy of the reference's FSDP2 wrapping, ``nestor/utils/distributed.py:445-489``).
 
@@ -28,11 +28,12 @@ MAX_GROUPS = 256
 class ShardedBanks:
     """Hands ``ops.gemm.Gather`` descriptions to the expert-bank products of one device."""
 
-    def __init__(self, compute: Tensor, peer_ptrs: list[int], rank: int, *, ctas: int | None = None) -> None:
+    def __init__(self, compute: Tensor, peer_ptrs: list[int], rank: int) -> None:
         self.compute, self.peer_ptrs, self.rank, self.world = compute, list(peer_ptrs), rank, len(peer_ptrs)
         self.lo = compute.data_ptr()
         self.hi = self.lo + compute.numel() * compute.element_size()
-        self.ctas = int(os.environ.get("NESTOR_FSDP_GATHER_CTAS", "8")) if ctas is None else ctas
+        self.chunk = int(os.environ.get("NESTOR_FSDP_GATHER_CHUNK", "8192"))
+        self.nbuf = int(os.environ.get("NESTOR_FSDP_GATHER_NBUF", "4"))
         self.flags = torch.zeros(MAX_GROUPS + 1, dtype=torch.int32, device=compute.device)
         self.stage: Tensor | None = None
         self.gathered_bytes = 0       # bytes staged since construction (host-side count, for reports)
@@ -54,4 +55,4 @@ class ShardedBanks:
             self.stage = torch.empty(need // 2, dtype=torch.bfloat16, device=w.device)
         self.gathered_bytes += need
         return G.Gather(src=self.peer_ptrs, arena_ptr=self.lo, stage=self.stage, flags=self.flags,
-                        groups_per_rank=w.shape[0] // self.world, ctas=self.ctas)
+                        groups_per_rank=w.shape[0] // self.world, chunk=self.chunk, nbuf=self.nbuf)

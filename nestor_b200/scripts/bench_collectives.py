@@ -40,6 +40,9 @@ def main(argv: list[str] | None = None) -> None:
     ap.add_argument("--sizes-mb", type=int, nargs="*", default=[1, 4, 16, 64, 256, 1024])
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--mirror", action="store_true", help="also write the bf16 mirror in the all-reduce kernel")
+    ap.add_argument("--ag-gemm", action="store_true", help="also time the all-gather fused into the expert-bank GEMMs")
+    ap.add_argument("--gather-rings", type=str, nargs="*", default=["8192x4x1", "8192x2x4", "4096x2x4"],
+                    help="copy-ring shapes to time: chunk bytes x buffers per lane x copying lanes")
     a = ap.parse_args(argv)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     from nestor_b200.parallel import symm
@@ -88,7 +91,76 @@ def main(argv: list[str] | None = None) -> None:
             print(f"param push {mb:5d} MB: fused {ms:8.3f} ms {bus / ms * 1e3:6.0f} GB/s "
                   f"({bus / ms * 1e3 / PEER_COPY_GBS:5.1%} of the peer-copy rate) | NCCL all-gather + cast {ms_nccl:8.3f} ms", flush=True)
         pp.group.check()
+    if a.ag_gemm:
+        bench_ag_gemm(dev, rank, world, a.reps, a.gather_rings)
     dist.destroy_process_group()
+
+
+def bench_ag_gemm(dev, rank: int, world: int, reps: int, rings: list[str]) -> None:
+    """All-gather fused into the expert-bank GEMMs of nestor_200m against NCCL all-gather followed by the GEMM.
+
+    Shapes: 98,304 dispatched rows over 64 experts, up||gate + SwiGLU ``[640 -> 2 x 216]`` and down
+    ``[216 -> 640]``. Each rank owns 64 / W experts of every bank. The roofline is the slower of the product
+    alone (timed here) and the remote bytes over the measured peer-copy rate.
+    """
+
+    from nestor_b200.ops import gemm as G
+    from nestor_b200.parallel import symm
+    E, d, h, rows = 64, 640, 216, 98304
+    n = E * d * h
+    per = E // world
+    arena = symm.symmetric_empty(3 * n, torch.bfloat16, dev)
+    arena.copy_(torch.randn(3 * n, device=dev) * 0.03)
+    handle = symm.rendezvous(arena)
+    vg, vu, vd = arena[:n].view(E, d, h), arena[n : 2 * n].view(E, d, h), arena[2 * n :].view(E, h, d)
+    X = torch.randn(rows, d, device=dev).bfloat16()
+    Hh = torch.randn(rows, h, device=dev).bfloat16()
+    off = (torch.arange(E + 1, device=dev, dtype=torch.int32) * (rows // E)).contiguous()
+    H, Gt, Ut = (G.rows_buffer(rows, h, torch.bfloat16, dev) for _ in range(3))
+    Y = torch.empty(rows, d, dtype=torch.bfloat16, device=dev)
+    stage = torch.empty(2 * n, dtype=torch.bfloat16, device=dev)
+    flags = torch.zeros(257, dtype=torch.int32, device=dev)
+    full = torch.empty(2 * n, dtype=torch.bfloat16, device=dev)
+    shard_gu = torch.cat([vg[rank * per : (rank + 1) * per].reshape(-1), vu[rank * per : (rank + 1) * per].reshape(-1)]).clone()
+    shard_d = vd[rank * per : (rank + 1) * per].reshape(-1).clone()
+    torch.cuda.synchronize()
+    dist.barrier()
+
+    def up(gather, wg=vg, wu=vu):
+        G.gemm_rows(X, wg, B2=wu, offsets=off, groups=E, b_mn=True, out=H, epilogue=G.SWIGLU, extra_out=(Gt, Ut), gather=gather)
+
+    def down(gather, wd=vd):
+        G.gemm_rows(Hh, wd, offsets=off, groups=E, b_mn=True, out=Y, gather=gather)
+
+    def nccl_up():
+        dist.all_gather_into_tensor(full, shard_gu)
+        up(None)
+
+    def nccl_down():
+        dist.all_gather_into_tensor(full[:n], shard_d)
+        down(None)
+
+    base_up, base_down = timed(lambda: up(None), reps, dev), timed(lambda: down(None), reps, dev)
+    t_nccl_up, t_nccl_down = timed(nccl_up, reps, dev), timed(nccl_down, reps, dev)
+    remote_up, remote_down = 2 * n * 2 * (world - 1) / world, n * 2 * (world - 1) / world
+    if rank == 0:
+        print(f"all-gather + GEMM, world {world}: product alone up||gate {base_up * 1e3:.0f} us, down {base_down * 1e3:.0f} us; "
+              f"NCCL all-gather then product {t_nccl_up * 1e3:.0f} / {t_nccl_down * 1e3:.0f} us; remote bytes "
+              f"{remote_up / 1e6:.1f} / {remote_down / 1e6:.1f} MB = {remote_up / PEER_COPY_GBS / 1e3:.0f} / "
+              f"{remote_down / PEER_COPY_GBS / 1e3:.0f} us at the peer-copy rate", flush=True)
+    for ring in rings:
+        chunk, nbuf, lanes = (int(v) for v in ring.split("x"))
+        spec = G.Gather(src=[int(handle.buffer_ptrs[r]) for r in range(world)], arena_ptr=arena.data_ptr(), stage=stage,
+                        flags=flags, groups_per_rank=per, chunk=chunk, nbuf=nbuf, lanes=lanes)
+        t_up, t_down = timed(lambda: up(spec), reps, dev), timed(lambda: down(spec), reps, dev)
+        roof_up = max(base_up, remote_up / PEER_COPY_GBS / 1e6)
+        roof_down = max(base_down, remote_down / PEER_COPY_GBS / 1e6)
+        if rank == 0:
+            print(f"  fused, copy ring {ring:>9s}: up||gate {t_up * 1e3:.0f} us ({roof_up / t_up:5.1%} of roofline), "
+                  f"down {t_down * 1e3:.0f} us ({roof_down / t_down:5.1%})", flush=True)
+    from nestor_b200.ops import _lib
+    torch.cuda.synchronize()
+    _lib.check_status(dev)
 
 
 if __name__ == "__main__":

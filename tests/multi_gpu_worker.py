@@ -36,7 +36,7 @@ def check_gathered_gemm(dev, rank: int, world: int) -> None:
     dist.barrier()
     spec = G.Gather(src=[int(handle.buffer_ptrs[r]) for r in range(world)], arena_ptr=arena.data_ptr(),
                     stage=torch.full((2 * n,), float("nan"), device=dev, dtype=torch.bfloat16),
-                    flags=torch.zeros(257, dtype=torch.int32, device=dev), groups_per_rank=per, ctas=8)
+                    flags=torch.zeros(257, dtype=torch.int32, device=dev), groups_per_rank=per)
 
     def run(gather, wg, wu):
         H = torch.full((rows, h), float("nan"), device=dev, dtype=torch.bfloat16)

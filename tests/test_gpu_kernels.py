@@ -428,7 +428,7 @@ def test_attention_with_head_dims_that_are_not_multiples_of_eight(d, H, hd, Gc, 
 
 @pytest.mark.parametrize("rows,world", [(9000, 4), (1500, 2)])
 def test_gemm_with_fused_all_gather_of_rank_sharded_banks(rows, world):
-    """Weights staged from their owners' arenas by copy CTAs of the same launch (ranks emulated as local buffers).
+    """Weights staged from their owners' arenas by the copy warps of the same launch (ranks emulated as local buffers).
 
     Every emulated arena holds valid values only for the groups its rank owns (NaN elsewhere, the local arena
     included), so a finite result equal to the ungathered product proves that each group came from its owner.
@@ -461,7 +461,7 @@ def test_gemm_with_fused_all_gather_of_rank_sharded_banks(rows, world):
     stage = torch.full((2 * n_gu,), float("nan"), device="cuda", dtype=BF)
     flags = torch.zeros(257, dtype=torch.int32, device="cuda")
     spec = G.Gather(src=[a.data_ptr() for a in arenas], arena_ptr=local.data_ptr(), stage=stage, flags=flags,
-                    groups_per_rank=per, ctas=6)
+                    groups_per_rank=per)
 
     def run(gather, wg, wu, wd):
         H = torch.full((rows, h), float("nan"), device="cuda", dtype=BF)
@@ -473,9 +473,13 @@ def test_gemm_with_fused_all_gather_of_rank_sharded_banks(rows, world):
         dX = G.gemm_rows(Hh, wg, A2=Hh, B2=wu, offsets=off, groups=E, gather=gather)      # two segments
         return H, Gt, Ut, Y, dH, dX
 
+    import dataclasses
     want = run(None, Wg, Wu, Wd)
-    for _ in range(2):       # twice: the counters must come back to zero between launches
-        got = run(spec, vg, vu, vd)
+    # twice per ring shape (the counters must come back to zero between launches); the second shape has four
+    # lanes of the copy warp copying independently
+    for sp in (spec, spec, dataclasses.replace(spec, chunk=4096, nbuf=2, lanes=4), dataclasses.replace(spec, nbuf=2, lanes=4)):
+        stage.fill_(float("nan"))
+        got = run(sp, vg, vu, vd)
         torch.cuda.synchronize()
         assert int(flags.abs().sum().item()) == 0
         for w, g in zip(want, got):
