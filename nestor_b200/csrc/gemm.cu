@@ -290,13 +290,18 @@ __device__ __forceinline__ void gather_leave(const GatherParams& g, int groups) 
 // clusters of two, so the single-CTA variant must not contain them. The epilogue is a template parameter too:
 // with every variant in one kernel the eleven warps of a CTA (each in a different code region) thrash the
 // instruction cache, which showed as "no instruction" stalls on every role.
-template <int PAIR, int EPI>
-__global__ void __launch_bounds__(384, 1)
+// GATHER = 1 adds the copy warp and the per-group waits of the fused all-gather (GatherParams). It is a template
+// parameter so that the kernels of ordinary launches contain none of it: with the gather code compiled into every
+// variant the weight-gradient product ran 60 % slower (130 vs 81 us on its nestor_200m shape) although it never
+// executes that code, and the one-GPU training step lost 5 %.
+template <int PAIR, int EPI, int GATHER>
+__global__ void __launch_bounds__(GATHER ? 384 : 352, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
-            const GemmParams p, int stages) {
+            const __grid_constant__ GemmParams p, int stages) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ uint64_t full_bar[8], empty_bar[8], tfull_bar[2], tempty_bar[2], gather_bar[8];
+  __shared__ uint64_t full_bar[8], empty_bar[8], tfull_bar[2], tempty_bar[2];
+  __shared__ uint64_t gather_bar[GATHER ? 8 : 1];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int s_abort;
   __shared__ int s_off[kMaxGroups + 1];
@@ -305,7 +310,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int pair = PAIR;
-  const int n_gather = p.gather.on;
+  constexpr int n_gather = GATHER;
   const uint32_t rank = pair ? cluster_ctarank() : 0u;   // rank 0 of a pair issues the MMAs
   const int b_cols = pair ? p.BN / 2 : p.BN;             // B columns staged by this CTA
   const uint32_t a_bytes = BM * BK * 2;               // 16 KB
@@ -436,7 +441,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       for (int t = cta; t < total_tiles && !*abort_flag; t += n_cta) {
         Tile tl = decode_tile(p, s_off, s_tstart, t, n_tiles, rank, g_hint);
         int nkb = tl.kb + tl.kb2;
-        if (n_gather && which == 2 && tl.g != g_ready) {
+        if constexpr (GATHER) if (which == 2 && tl.g != g_ready) {
           // first load of a gathered group: wait until the copy CTAs have staged all of its chunks
           const int need = int((p.gather.group_bytes + p.gather.chunk_bytes - 1) / p.gather.chunk_bytes) * p.gather.nseg;
           const volatile int* fl = p.gather.flags + tl.g;
@@ -575,7 +580,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
   } else if (warp == 11) {
     // ----------------------------------------------------------------- copy warp of a gathering launch
-    if (n_gather)
+    // (`p` is a __grid_constant__ parameter so that handing `p.gather` to the out-of-line copy loop by reference does
+    // not make every instantiation keep a local-memory copy of the parameter block and read its fields from there)
+    if constexpr (GATHER)
       gather_role(p.gather, p.groups, smem + uint32_t(stages) * stage_bytes + 8 * kSlabBytes, gather_bar, p.status, abort_flag);
   } else {
     // ----------------------------------------------------------------- epilogue
@@ -775,7 +782,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     tc_fence_after();
     if (pair) tmem_dealloc_pair(tmem_base, tmem_cols); else tmem_dealloc(tmem_base, tmem_cols);
   }
-  if (n_gather && threadIdx.x == 0) gather_leave(p.gather, p.groups);
+  if constexpr (GATHER) { if (threadIdx.x == 0) gather_leave(p.gather, p.groups); }
 }
 
 }  // namespace nb
@@ -976,15 +983,21 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
   size_t smem = size_t(stages) * stage_bytes + 1024 + 8 * kSlabBytes + ring_bytes;
   typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams, int);
   static const KernelFn kernels[2][6] = {
-      {gemm_kernel<0, 0>, gemm_kernel<0, 1>, gemm_kernel<0, 2>, gemm_kernel<0, 3>, gemm_kernel<0, 4>, gemm_kernel<0, 5>},
-      {gemm_kernel<1, 0>, gemm_kernel<1, 1>, gemm_kernel<1, 2>, gemm_kernel<1, 3>, gemm_kernel<1, 4>, gemm_kernel<1, 5>}};
+      {gemm_kernel<0, 0, 0>, gemm_kernel<0, 1, 0>, gemm_kernel<0, 2, 0>, gemm_kernel<0, 3, 0>, gemm_kernel<0, 4, 0>, gemm_kernel<0, 5, 0>},
+      {gemm_kernel<1, 0, 0>, gemm_kernel<1, 1, 0>, gemm_kernel<1, 2, 0>, gemm_kernel<1, 3, 0>, gemm_kernel<1, 4, 0>, gemm_kernel<1, 5, 0>}};
+  // gathering launches: the expert-bank products only (plain store, SwiGLU forward, SwiGLU backward)
+  static const KernelFn gather_kernels[2][6] = {
+      {gemm_kernel<0, 0, 1>, nullptr, nullptr, gemm_kernel<0, 3, 1>, gemm_kernel<0, 4, 1>, nullptr},
+      {gemm_kernel<1, 0, 1>, nullptr, nullptr, gemm_kernel<1, 3, 1>, gemm_kernel<1, 4, 1>, nullptr}};
   if (a->epilogue < 0 || a->epilogue > 5) return -9;
-  const KernelFn kernel = kernels[pair][a->epilogue];
-  static size_t configured[2][6] = {{0, 0, 0, 0, 0, 0}, {0, 0, 0, 0, 0, 0}};
-  if (smem > configured[pair][a->epilogue]) {
+  const int gat = p.gather.on ? 1 : 0;
+  const KernelFn kernel = gat ? gather_kernels[pair][a->epilogue] : kernels[pair][a->epilogue];
+  if (!kernel) return -27;      // no gathering variant of this epilogue
+  static size_t configured[2][2][6] = {};
+  if (smem > configured[gat][pair][a->epilogue]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return int(e);
-    configured[pair][a->epilogue] = smem;
+    configured[gat][pair][a->epilogue] = smem;
   }
   int sms = a->sms > 0 ? a->sms : g_num_sms;
   const int threads = p.gather.on ? 384 : 352;
