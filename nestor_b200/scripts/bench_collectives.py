@@ -19,7 +19,7 @@ import torch.distributed as dist
 PEER_COPY_GBS = 770.0
 
 
-def timed(fn, reps: int, dev) -> float:
+def timed(fn, reps: int, dev, per_rank: list | None = None) -> float:
     for _ in range(3):
         fn()
     dist.barrier()
@@ -31,6 +31,10 @@ def timed(fn, reps: int, dev) -> float:
     e1.record()
     torch.cuda.synchronize()
     t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+    if per_rank is not None:          # every rank's own time, for launches whose cost depends on the rank
+        every = [torch.zeros_like(t) for _ in range(dist.get_world_size())]
+        dist.all_gather(every, t)
+        per_rank.extend(float(x.item()) for x in every)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
 
@@ -152,12 +156,14 @@ def bench_ag_gemm(dev, rank: int, world: int, reps: int, rings: list[str]) -> No
         chunk, nbuf, lanes = (int(v) for v in ring.split("x"))
         spec = G.Gather(src=[int(handle.buffer_ptrs[r]) for r in range(world)], arena_ptr=arena.data_ptr(), stage=stage,
                         flags=flags, groups_per_rank=per, chunk=chunk, nbuf=nbuf, lanes=lanes)
-        t_up, t_down = timed(lambda: up(spec), reps, dev), timed(lambda: down(spec), reps, dev)
+        r_up, r_down = [], []
+        t_up, t_down = timed(lambda: up(spec), reps, dev, r_up), timed(lambda: down(spec), reps, dev, r_down)
         roof_up = max(base_up, remote_up / PEER_COPY_GBS / 1e6)
         roof_down = max(base_down, remote_down / PEER_COPY_GBS / 1e6)
         if rank == 0:
             print(f"  fused, copy ring {ring:>9s}: up||gate {t_up * 1e3:.0f} us ({roof_up / t_up:5.1%} of roofline), "
-                  f"down {t_down * 1e3:.0f} us ({roof_down / t_down:5.1%})", flush=True)
+                  f"down {t_down * 1e3:.0f} us ({roof_down / t_down:5.1%}); per rank "
+                  f"{'/'.join(f'{x * 1e3:.0f}' for x in r_up)} and {'/'.join(f'{x * 1e3:.0f}' for x in r_down)} us", flush=True)
     from nestor_b200.ops import _lib
     torch.cuda.synchronize()
     _lib.check_status(dev)
