@@ -47,8 +47,8 @@ enum Epilogue : int {
 // [r * groups_per_rank, (r + 1) * groups_per_rank) in its copy of the weight arena, which every rank maps
 // (`src[r]`). A twelfth warp of every CTA of the launch pulls its share of the chunks of every group from the
 // group's owner into the local staging tensor that the B tensor maps describe, in group order, with bulk copies
-// through a small shared-memory ring, and counts finished chunks in `flags[group]`. (The bytes one SM can keep in
-// flight over NVLink bound its copy rate to about 13 GB/s, so the copy is spread over all SMs instead of being
+// through a small shared-memory ring, and counts finished chunks in `flags[group]`. (Measured on two GPUs: a CTA that only
+// copies moves 11-14 GB/s whatever its ring depth or chunk size, so the copy is spread over all SMs instead of being
 // given to a few dedicated CTAs.) The B producers wait (bounded) for a group's count before their first load of
 // it, so the product of the early groups overlaps the transfer of the later ones. Nothing waits on another GPU:
 // a shard is constant while the products that read it run. The last CTA to leave zeroes the counters for the next
@@ -202,10 +202,10 @@ __device__ __forceinline__ void load_chunk_bf16(uint8_t* slab, int lane, uint32_
 
 // The copy warp of a fused all-gather launch (see GatherParams). One thread drives a ring of `nbuf` chunk buffers.
 // A buffer is refilled as soon as the store that drains it has read it (`wait_group.read`), so `nbuf - 1` loads
-// stay in flight; a chunk is published `kGatherLag` stores later, when its store has completed. No proxy fence
-// sits in the loop: the mbarrier orders load -> store inside the async proxy, and the completion of a bulk group
-// is what makes the stored bytes visible to this thread before it releases them with a fence and the counter
-// (the consumer's own proxy fence then orders its TMA loads after its flag read).
+// stay in flight; a chunk is published `kGatherLag` stores later, when its store has completed. Hand-offs between
+// the generic and the async proxy are fenced on both sides although the mbarrier (load -> store) and the bulk-group
+// completion (store -> this thread) arguably order them already: taking the fences out did not raise the copy rate
+// when that was tried, so the loop keeps them and does not depend on that reading of the proxy rules.
 constexpr int kGatherLag = 4;
 constexpr uint32_t kGatherSpinLimit = 1u << 22;   // polls of >= 100 ns: a consumer gives up after about half a second
 __device__ __noinline__ void gather_role(const GatherParams& g, int groups, uint8_t* smem, uint64_t* bars, int* status,
@@ -253,6 +253,7 @@ __device__ __noinline__ void gather_role(const GatherParams& g, int groups, uint
     if (++lb == nbuf) lb = 0;
   };
   auto publish = [&](uint32_t i) {
+    fence_async_all();
     __threadfence();
     atomicAdd(&g.flags[s_grp[i & 15u]], 1);
   };
@@ -260,6 +261,7 @@ __device__ __noinline__ void gather_role(const GatherParams& g, int groups, uint
   uint32_t done = 0, b = 0, ph = 0;      // chunks published; buffer and barrier phase of chunk i
   for (uint32_t i = 0; i < n_mine; ++i) {
     if (!mbar_wait(&bars[b], ph, abort_flag, status, kTimeoutPeer, 32)) break;
+    fence_async_smem();
     bulk_store(s_dst[b], smem + size_t(b) * chunk, s_bytes[b]);
     bulk_commit();
     if (i >= 1 && li < n_mine) {
