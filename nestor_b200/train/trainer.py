@@ -77,12 +77,15 @@ class Trainer:
             from nestor_b200.parallel.symm import ParamPush
             self.param_push = ParamPush(self.arena.master, self.arena.compute)
             self.optimizer.param_sync = lambda opt: None      # distribution happens after the compute-copy refresh
-        if fused and self.param_push is not None and self.compute_dtype == torch.bfloat16 and _env_flag("NESTOR_FSDP_BANKS"):
-            # expert banks are read from their owner ranks by the all-gather fused into the bank GEMMs
+        if device.type == "cuda":
+            # expert banks read from their owner ranks by the all-gather fused into the bank GEMMs (off unless asked
+            # for); always reassigned, so that a trainer never inherits the peer table of an earlier one's arena
             from nestor_b200.ops import cuda as cuda_ops
-            from nestor_b200.parallel.shard import ShardedBanks
-            g = self.param_push.group
-            cuda_ops.BANK_SHARDS = ShardedBanks(self.arena.compute, [int(g.peers.aux[r]) for r in range(g.world)], g.rank)
+            cuda_ops.BANK_SHARDS = None
+            if fused and self.param_push is not None and self.compute_dtype == torch.bfloat16 and _env_flag("NESTOR_FSDP_BANKS"):
+                from nestor_b200.parallel.shard import ShardedBanks
+                g = self.param_push.group
+                cuda_ops.BANK_SHARDS = ShardedBanks(self.arena.compute, [int(g.peers.aux[r]) for r in range(g.world)], g.rank)
         # the pushed range carries every parameter in it; when its owner is the only one to update them (ZeRO-1 for
         # AdamW as well) it is also the only one that needs their reduced gradients: reduce-scatter
         self.zero = bool(self.param_push is not None and getattr(self.optimizer, "shard_adamw", False))
