@@ -139,6 +139,42 @@ def case_depth(reps: int, small: bool = False) -> None:
                nbytes=(n * 8 + 2) * T * d)
 
 
+def case_gather(reps: int, small: bool = False) -> None:
+    """Cost of the staging mechanism of the fused all-gather GEMM by itself: every "rank" is this GPU.
+
+    The expert-bank products of nestor_200m, once reading their weights in place and once with the weights staged
+    through the copy warps of the same launch (``ops.gemm.Gather`` whose eight sources all point at the local
+    arena), so that no byte crosses NVLink and the difference is the price of the in-kernel copy and hand-off.
+    """
+
+    from nestor_b200.ops import gemm as G
+    E, d, h, rows = 64, 640, 216, (24576 if small else 98304)
+    n = E * d * h
+    arena = (torch.randn(3 * n, device="cuda") * 0.03).to(BF)
+    vg, vu, vd = arena[:n].view(E, d, h), arena[n : 2 * n].view(E, d, h), arena[2 * n :].view(E, h, d)
+    X, Hh = torch.randn(rows, d, device="cuda").to(BF), torch.randn(rows, h, device="cuda").to(BF)
+    off = (torch.arange(E + 1, dtype=torch.int32) * (rows // E)).cuda()
+    H, Gt, Ut = (G.rows_buffer(rows, h, BF, "cuda") for _ in range(3))
+    Y = torch.empty(rows, d, dtype=BF, device="cuda")
+    stage = torch.empty(2 * n, dtype=BF, device="cuda")
+    flags = torch.zeros(257, dtype=torch.int32, device="cuda")
+
+    def up(g):
+        G.gemm_rows(X, vg, B2=vu, offsets=off, groups=E, b_mn=True, out=H, epilogue=G.SWIGLU, extra_out=(Gt, Ut), gather=g)
+
+    def down(g):
+        G.gemm_rows(Hh, vd, offsets=off, groups=E, b_mn=True, out=Y, gather=g)
+
+    report("up|gate+SwiGLU, weights in place", timed(lambda: up(None), reps), 2.0 * rows * d * 2 * h)
+    report("down, weights in place", timed(lambda: down(None), reps), 2.0 * rows * d * h)
+    for chunk, nbuf, lanes in ((8192, 4, 1), (32768, 2, 1), (8192, 2, 4)):
+        spec = G.Gather(src=[arena.data_ptr()] * 8, arena_ptr=arena.data_ptr(), stage=stage, flags=flags,
+                        groups_per_rank=E // 8, chunk=chunk, nbuf=nbuf, lanes=lanes)
+        ring = f"{chunk} B x {nbuf} x {lanes} lane(s)"
+        report(f"up|gate+SwiGLU, weights staged (ring {ring})", timed(lambda: up(spec), reps), 2.0 * rows * d * 2 * h)
+        report(f"down, weights staged (ring {ring})", timed(lambda: down(spec), reps), 2.0 * rows * d * h)
+
+
 def main(argv: list[str] | None = None) -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("cases", nargs="*", default=["gemm", "flash", "depth"])
@@ -152,7 +188,7 @@ def main(argv: list[str] | None = None) -> None:
         if c == "small":
             case_gemm(a.reps, small=True); case_flash(a.reps, small=True); case_depth(a.reps, small=True)
         else:
-            {"gemm": case_gemm, "flash": case_flash, "depth": case_depth}[c](a.reps)
+            {"gemm": case_gemm, "flash": case_flash, "depth": case_depth, "gather": case_gather}[c](a.reps)
     from nestor_b200.ops import _lib
     _lib.check_status(torch.device("cuda"))
 
