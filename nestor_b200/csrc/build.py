@@ -32,7 +32,7 @@ def nvcc() -> str | None:
 
 def _digest(path: Path) -> str:
     h = hashlib.sha256()
-    for f in [path, *sorted(SRC.glob("*.cuh"))]:
+    for f in [path, *sorted(SRC.glob("*.cuh")), *sorted(SRC.glob("*.h"))]:
         h.update(f.read_bytes())
     h.update(" ".join(FLAGS).encode())
     return h.hexdigest()[:16]
@@ -64,6 +64,28 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         if res.returncode:
             sys.stderr.write(res.stdout + res.stderr)
             raise RuntimeError("link failed")
+    return LIB
+
+
+def stale_sources() -> list[str]:
+    """Sources whose cached object (named by source digest) is missing: the built library predates them."""
+
+    return [cu.name for cu in sorted(SRC.glob("*.cu")) if not (OUT / f"{cu.stem}.{_digest(cu)}.o").is_file()]
+
+
+def ensure() -> Path:
+    """The up-to-date library: rebuild what changed when a compiler is present, else refuse a stale binary.
+
+    A library older than its sources would be called with argument structures it does not know (the Python
+    side mirrors the C structs), so loading it is never safe.
+    """
+
+    if nvcc() is not None:
+        return build()
+    stale = stale_sources()
+    if stale or not LIB.is_file():
+        raise RuntimeError(
+            f"{LIB} is missing or older than {', '.join(stale) or 'its sources'} and there is no nvcc to rebuild it")
     return LIB
 
 

@@ -13,6 +13,7 @@
 // The same shared-memory tile serves as a K-major operand of the score products and as an
 // MN-major operand of the accumulate products, so every tile is fetched once.
 #include "sm100.cuh"
+#include "flash.h"
 
 namespace nb {
 
@@ -279,18 +280,7 @@ extern "C" int nb_head_map_rows(CUtensorMap* m, const void* base, long rows, int
 
 extern "C" {
 
-struct NbFlashBwdArgs {
-  const void* Q; const void* K; const void* V; long ld_qkv;    // saved forward operands (shared row pitch)
-  const void* O; long ld_o;
-  const void* dO; long ld_do;
-  const float* lse; float* delta;                              // [rows, H] each (delta is scratch output)
-  void* dQ; void* dK; void* dV; long ld_dqkv;
-  const int* seg_start; int nseg;
-  int rows, H, hd;
-  float scale;
-  int* status;
-  int max_tiles;
-};
+int nb_flash_bwd_args_size(void) { return int(sizeof(NbFlashBwdArgs)); }
 
 int nb_flash_bwd(const NbFlashBwdArgs* a, cudaStream_t stream) {
   using namespace nb;
@@ -323,13 +313,8 @@ int nb_flash_bwd(const NbFlashBwdArgs* a, cudaStream_t stream) {
   dim3 grid(a->max_tiles, a->H);
 #define NB_LAUNCH(MODE, HDN, R1, R2, X1, X2)                                                                        \
   do {                                                                                                               \
-    static bool set = false;                                                                                         \
-    if (!set) {                                                                                                      \
-      cudaError_t e = cudaFuncSetAttribute(flash_bwd_kernel<MODE, HDN>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                           int(smem));                                                               \
-      if (e != cudaSuccess) return int(e);                                                                           \
-      set = true;                                                                                                    \
-    }                                                                                                                \
+    static SmemAttr attr;                                                                                            \
+    if (int e = attr.ensure(flash_bwd_kernel<MODE, HDN>, smem)) return e;                                            \
     flash_bwd_kernel<MODE, HDN><<<grid, 192, smem, stream>>>(R1, R2, X1, X2, p);                                     \
   } while (0)
   p.out1 = reinterpret_cast<__nv_bfloat16*>(a->dK); p.out2 = reinterpret_cast<__nv_bfloat16*>(a->dV);

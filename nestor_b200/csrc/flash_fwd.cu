@@ -16,6 +16,7 @@
 // Replaces torch's varlen_attn / SDPA calls of the reference (nestor/backbones/nestor.py:6357,
 // :6213, :5802) including its 1/head_dim logit scale (:3201).
 #include "sm100.cuh"
+#include "flash.h"
 
 namespace nb {
 
@@ -360,18 +361,7 @@ extern "C" int nb_head_map(CUtensorMap* m, const void* base, long rows, int H, i
 
 extern "C" {
 
-struct NbFlashArgs {
-  const void* Q; const void* K; const void* V;   // bf16, row pitch `ld_qkv` elements, head h at column h*hd
-  long ld_qkv;
-  void* O; long ldo;
-  float* lse;
-  const int* seg_start; int nseg;
-  int rows, H, hd;
-  float scale;
-  int* status;
-  int max_tiles;       // upper bound on q tiles: ceil(rows/128) + nseg
-  int lazy_rescale;    // 1: keep O in TMEM and rescale it only when a row maximum moves by more than 2^8
-};
+int nb_flash_args_size(void) { return int(sizeof(NbFlashArgs)); }
 
 int nb_flash_fwd(const NbFlashArgs* a, cudaStream_t stream) {
   using namespace nb;
@@ -390,13 +380,8 @@ int nb_flash_fwd(const NbFlashArgs* a, cudaStream_t stream) {
   dim3 grid(a->max_tiles, a->H);
 #define NB_FWD(HDN, LAZY)                                                                                          \
   do {                                                                                                             \
-    static bool set = false;                                                                                       \
-    if (!set) {                                                                                                    \
-      cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<HDN, LAZY>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                           int(smem));                                                             \
-      if (e != cudaSuccess) return int(e);                                                                         \
-      set = true;                                                                                                  \
-    }                                                                                                              \
+    static SmemAttr attr;                                                                                          \
+    if (int e = attr.ensure(flash_fwd_kernel<HDN, LAZY>, smem)) return e;                                          \
     flash_fwd_kernel<HDN, LAZY><<<grid, 192, smem, stream>>>(tq, tk, tv, p);                                       \
   } while (0)
   if (a->hd <= 64) { if (a->lazy_rescale) NB_FWD(64, true); else NB_FWD(64, false); }

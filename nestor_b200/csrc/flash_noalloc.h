@@ -13,14 +13,15 @@
 // per call; this variant keeps that scratch in a fixed array inside the library instead.
 //
 // Contract
-//   * Same arguments as `nb_flash_bwd`; the `delta` field is ignored. Inputs and outputs
-//     still belong to the caller.
+//   * Same argument block as `nb_flash_bwd` (`struct NbFlashBwdArgs`, flash.h); the `delta`
+//     field is ignored. Inputs and outputs still belong to the caller.
 //   * The scratch is one file-scope device array of NB_FLASH_NOALLOC_MAX_FLOATS floats
 //     (4 MiB). Every GPU that loads the library holds it until the process exits.
 //     A call with rows * heads above that limit is refused with
 //     NB_FLASH_NOALLOC_TOO_LARGE and does nothing.
 //   * The first call on each device looks up the array's device address (with that device
-//     current). Make that first call outside of any stream capture.
+//     current). Make that first call outside of any stream capture. Threads that make a
+//     device's first call at the same time all store the same address, which is harmless.
 //   * The call itself performs no cudaMalloc / cudaFree and calls no allocating library
 //     routine.
 //   * All calls on a device share the one array and it keeps whatever the last call left
@@ -29,6 +30,7 @@
 //     streams, no ordering between them) race on it. Serialise them.
 #pragma once
 #include <cuda_runtime.h>
+#include "flash.h"   // struct NbFlashBwdArgs, nb_flash_bwd
 
 #ifdef __cplusplus
 extern "C" {
@@ -37,8 +39,6 @@ extern "C" {
 #define NB_FLASH_NOALLOC_MAX_FLOATS (1 << 20)
 #define NB_FLASH_NOALLOC_TOO_LARGE (-100)
 #define NB_FLASH_NOALLOC_SETUP_FAILED (-101)
-
-struct NbFlashBwdArgs;
 
 // Returns 0 on success, NB_FLASH_NOALLOC_TOO_LARGE / NB_FLASH_NOALLOC_SETUP_FAILED, or the
 // code `nb_flash_bwd` would return.

@@ -39,7 +39,8 @@ enum Epilogue : int {
   kAccumF32 = 2,      // C fp32 += acc * alpha
   kSwiGLU = 3,        // tile columns [0,BN/2) = gate, [BN/2,BN) = up: write gate, up and silu(gate)*up (bf16)
   kSwiGLUBwd = 4,     // acc = dH: read gate/up, write dGate, dUp (bf16)
-  kStoreBf16Stats = 5 // store bf16 (scaled) and per-(row, n-tile) max / sum-exp partials
+  kStoreBf16Stats = 5,// store bf16 (scaled) and per-(row, n-tile) max / sum-exp partials
+  kAxpbyBf16 = 6      // C = alpha * acc + beta * E1 (bf16 in, bf16 out): the Newton-Schulz polynomial steps
 };
 
 // All-gather fused into the product (mode 0, grouped B). The groups of B (one or two tensors of the same shape:
@@ -81,7 +82,7 @@ struct GemmParams {
   void* C2; void* C3;       // extra outputs (SwiGLU: gate/up; stats: partials)
   const void* E1; const void* E2;  // extra inputs (SwiGLU bwd: gate, up)
   long lde;
-  float alpha;
+  float alpha, beta;
   int n_valid;              // stats epilogue: columns >= n_valid are padding (stored as -inf)
   int splits;               // mode 1: each output tile is reduced by `splits` CTAs (atomic fp32 adds)
   int* status;
@@ -95,12 +96,20 @@ struct GemmParams {
   GatherParams gather;         // fused all-gather of a rank-sharded B operand (gather.on == 0: off)
 };
 
+// Timing diagnostics (per-CTA phase timestamps, "issue no MMAs / loads / stores" experiments) are compiled in only
+// with -DNB_GEMM_DIAG; the library build leaves them out, so the production kernels carry none of that code.
+#ifdef NB_GEMM_DIAG
+constexpr bool kDiag = true;
+#else
+constexpr bool kDiag = false;
+#endif
+
 __device__ __forceinline__ unsigned long long gtime() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-#define NB_TRACE(slot) do { if (p.trace && (slot) < 64) p.trace[blockIdx.x * 64 + (slot)] = gtime(); } while (0)
+#define NB_TRACE(slot) do { if (kDiag && p.trace && (slot) < 64) p.trace[blockIdx.x * 64 + (slot)] = gtime(); } while (0)
 
 struct Tile { int g, m0, n0, row_end, kb, kb2, kb0, valid; };
 
@@ -437,7 +446,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int D = p.prefetch_dist, pf_mask = p.prefetch_ops;
       uint32_t it = 0, s = 0, ph = 0;
       int g_hint = 0, g_ready = -1;
-      const bool trace_on = p.trace != nullptr;
+      const bool trace_on = kDiag && p.trace != nullptr;
       long long acc_wait = 0, acc_issue = 0;
       if (el && which == 1) NB_TRACE(0);
       for (int t = cta; t < total_tiles && !*abort_flag; t += n_cta) {
@@ -471,7 +480,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           long long c1 = trace_on ? clock64() : 0;
           if (trace_on && el && which == 1 && it >= 16 && it < 28) NB_TRACE(1 + it - 16);
           uint8_t* sa = smem + s * stage_bytes;
-          if (p.debug & 2) { if (rank == 0 && el) mbar_arrive(&full_bar[s]); }
+          if (kDiag && (p.debug & 2)) { if (rank == 0 && el) mbar_arrive(&full_bar[s]); }
           else {
             if (el && rank == 0) mbar_expect_tx(&full_bar[s], (which == 1 ? a_bytes : b_bytes) * (pair ? 2u : 1u));
             issue(tl, kb, sa, sa + a_bytes, &full_bar[s], 0);
@@ -499,7 +508,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const uint32_t a_step = p.a_mn ? (2048u >> 4) : (32u >> 4);   // descriptor increment per K = 16 step
     const uint32_t b_step = p.b_mn ? (2048u >> 4) : (32u >> 4);
     const uint32_t smem_enc = smem_u32(smem) >> 4, stage_enc = stage_bytes >> 4, a_enc = a_bytes >> 4;
-    const bool trace_on = p.trace != nullptr;
+    const bool trace_on = kDiag && p.trace != nullptr;
     uint32_t s = 0, ph = 0, it = 0, tile_i = 0;
     int g_hint = 0;
     long long acc_wait = 0, acc_issue = 0, acc_commit = 0, acc_tempty = 0;
@@ -551,7 +560,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const uint32_t empty_addr = smem_u32(&empty_bar[s]), tfull_addr = smem_u32(&tfull_bar[buf]);
         const uint32_t empty_peer = pair ? mapa_shared(empty_addr, 1) : 0u, tfull_peer = pair ? mapa_shared(tfull_addr, 1) : 0u;
         if (elect_one()) {
-          if (!(p.debug & 1)) {
+          if (!(kDiag && (p.debug & 1))) {
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k) {
               if (pair) umma_bf16_pair(d_addr, ad + k * a_step, bd + k * b_step, idesc, (kb | k) != 0);
@@ -596,7 +605,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     uint8_t* slab = smem + uint32_t(stages) * stage_bytes + (warp - 2) * kSlabBytes;
     uint32_t tile_i = 0;
     int g_hint = 0;
-    const bool trace_on = p.trace != nullptr;
+    const bool trace_on = kDiag && p.trace != nullptr;
     long long e_wait = 0, e_work = 0, e_decode = 0, e_t0 = 0;
     for (int t = cta; t < total_tiles && !*abort_flag; t += n_cta) {
       if (trace_on) e_t0 = clock64();
@@ -607,10 +616,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       long c_base;
       if (p.mode == 0) { row_ok = row < tl.row_end; c_base = long(row) * p.ldc; }
       else { row_ok = row < p.M; c_base = long(tl.g) * p.c_group_stride + long(row) * p.ldc; }
-      if (p.debug & 4) row_ok = false;           // timing experiment: no global stores
+      if (kDiag && (p.debug & 4)) row_ok = false;           // timing experiment: no global stores
       // the warp's 32 rows start at row_w; the first rows_w of them exist
       const int row_w = tl.m0 + q * 32;
-      const int rows_w = (p.debug & 4) ? 0 : max(0, min(32, (p.mode == 0 ? tl.row_end : p.M) - row_w));
+      const int rows_w = (kDiag && (p.debug & 4)) ? 0 : max(0, min(32, (p.mode == 0 ? tl.row_end : p.M) - row_w));
       const long cw_base = (p.mode == 0 ? 0 : long(tl.g) * p.c_group_stride) + long(row_w) * p.ldc;
       uint32_t buf = 0;
       if (nkb > 0) {
@@ -715,6 +724,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             const long o = cw_base + tl.n0 + c0;
             store_chunk_bf16(slab, lane, wg, reinterpret_cast<__nv_bfloat16*>(p.C) + o, p.ldc, rows_w, rem);
             store_chunk_bf16(slab, lane, wu, reinterpret_cast<__nv_bfloat16*>(p.C2) + o, p.ldc, rows_w, rem);
+          } else if (EPI == kAxpbyBf16) {
+            // C = alpha * acc + beta * E1 in fp32, one rounding to bf16
+            const long oe = long(row_w) * p.lde + tl.n0 + c0;
+            uint32_t ew[16], w[16];
+            load_chunk_bf16(slab, lane, ew, reinterpret_cast<const __nv_bfloat16*>(p.E1) + oe, p.lde, rows_w, rem);
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const float lo = __uint_as_float(ew[e] << 16), hi = __uint_as_float(ew[e] & 0xFFFF0000u);
+              w[e] = pack_bf16(p.alpha * v[2 * e] + p.beta * lo, p.alpha * v[2 * e + 1] + p.beta * hi);
+            }
+            store_chunk_bf16(slab, lane, w, reinterpret_cast<__nv_bfloat16*>(p.C) + cw_base + tl.n0 + c0, p.ldc, rows_w, rem);
           } else if (row_ok) {
             // fp32 outputs (weight gradients): one row per lane
             float* Cp = reinterpret_cast<float*>(p.C) + c_base + tl.n0 + c0;
@@ -845,6 +865,7 @@ struct NbGemmArgs {
   void* C; long ldc; long c_group_stride;
   void* C2; void* C3; const void* E1; const void* E2; long lde;
   float alpha;
+  float beta;               // kAxpbyBf16: weight of E1
   int n_valid;
   int splits;
   int* status;
@@ -855,7 +876,7 @@ struct NbGemmArgs {
   int prefetch_ops;         // 1 = A, 2 = B, 3 = both
   int max_stages;           // 0 = as many as fit
   int pair;                 // mode 0 only: 256-row tiles on CTA pairs (cta_group::2), each CTA stages half of B
-  int debug;                // timing experiments: 1 = no MMAs, 2 = no loads (outputs are garbage)
+  int debug;                // builds with -DNB_GEMM_DIAG only: 1 = no MMAs, 2 = no loads, 4 = no stores (outputs are garbage)
   // fused all-gather of B (and B2) from rank-sharded weight arenas; see nb::GatherParams. gather_on == 0: off.
   const void* gather_src[8];
   void* gather_dst;
@@ -878,7 +899,7 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
   if (a->epilogue == kSwiGLU && (a->BN % 128 || !a->b_mn)) return -6;
   const int pair = a->pair ? 1 : 0;
   if (pair && (a->mode != 0 || a->a_mn || a->BN % 16 || (a->b_mn && a->BN % 128))) return -8;
-  if (!g_num_sms) {
+  if (!g_num_sms) {   // the GPUs of one machine are identical: the first device asked answers for all
     int dev; cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
@@ -937,7 +958,7 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
   p.M = a->M; p.N = a->N; p.K = a->K; p.K2 = a->K2; p.offsets = a->offsets; p.rows_per_group = a->rows_per_group;
   p.a_mn = a->a_mn; p.b_mn = a->b_mn; p.b_grouped = a->b_grouped;
   p.C = a->C; p.ldc = a->ldc; p.c_group_stride = a->c_group_stride; p.C2 = a->C2; p.C3 = a->C3;
-  p.E1 = a->E1; p.E2 = a->E2; p.lde = a->lde; p.alpha = a->alpha; p.n_valid = a->n_valid > 0 ? a->n_valid : a->N; p.status = a->status;
+  p.E1 = a->E1; p.E2 = a->E2; p.lde = a->lde; p.alpha = a->alpha; p.beta = a->beta; p.n_valid = a->n_valid > 0 ? a->n_valid : a->N; p.status = a->status;
   p.trace = a->trace;
   p.prefetch_dist = a->prefetch_dist > 0 ? a->prefetch_dist : 0;
   p.prefetch_ops = a->prefetch_ops & 3;
@@ -984,23 +1005,22 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
   if (stages < 2) return -7;
   size_t smem = size_t(stages) * stage_bytes + 1024 + 8 * kSlabBytes + ring_bytes;
   typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams, int);
-  static const KernelFn kernels[2][6] = {
-      {gemm_kernel<0, 0, 0>, gemm_kernel<0, 1, 0>, gemm_kernel<0, 2, 0>, gemm_kernel<0, 3, 0>, gemm_kernel<0, 4, 0>, gemm_kernel<0, 5, 0>},
-      {gemm_kernel<1, 0, 0>, gemm_kernel<1, 1, 0>, gemm_kernel<1, 2, 0>, gemm_kernel<1, 3, 0>, gemm_kernel<1, 4, 0>, gemm_kernel<1, 5, 0>}};
+  static const KernelFn kernels[2][7] = {
+      {gemm_kernel<0, 0, 0>, gemm_kernel<0, 1, 0>, gemm_kernel<0, 2, 0>, gemm_kernel<0, 3, 0>, gemm_kernel<0, 4, 0>, gemm_kernel<0, 5, 0>,
+       gemm_kernel<0, 6, 0>},
+      {gemm_kernel<1, 0, 0>, gemm_kernel<1, 1, 0>, gemm_kernel<1, 2, 0>, gemm_kernel<1, 3, 0>, gemm_kernel<1, 4, 0>, gemm_kernel<1, 5, 0>,
+       gemm_kernel<1, 6, 0>}};
   // gathering launches: the expert-bank products only (plain store, SwiGLU forward, SwiGLU backward)
-  static const KernelFn gather_kernels[2][6] = {
-      {gemm_kernel<0, 0, 1>, nullptr, nullptr, gemm_kernel<0, 3, 1>, gemm_kernel<0, 4, 1>, nullptr},
-      {gemm_kernel<1, 0, 1>, nullptr, nullptr, gemm_kernel<1, 3, 1>, gemm_kernel<1, 4, 1>, nullptr}};
-  if (a->epilogue < 0 || a->epilogue > 5) return -9;
+  static const KernelFn gather_kernels[2][7] = {
+      {gemm_kernel<0, 0, 1>, nullptr, nullptr, gemm_kernel<0, 3, 1>, gemm_kernel<0, 4, 1>, nullptr, nullptr},
+      {gemm_kernel<1, 0, 1>, nullptr, nullptr, gemm_kernel<1, 3, 1>, gemm_kernel<1, 4, 1>, nullptr, nullptr}};
+  if (a->epilogue < 0 || a->epilogue > 6) return -9;
+  if (a->epilogue == kAxpbyBf16 && !a->E1) return -9;
   const int gat = p.gather.on ? 1 : 0;
   const KernelFn kernel = gat ? gather_kernels[pair][a->epilogue] : kernels[pair][a->epilogue];
   if (!kernel) return -27;      // no gathering variant of this epilogue
-  static size_t configured[2][2][6] = {};
-  if (smem > configured[gat][pair][a->epilogue]) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    if (e != cudaSuccess) return int(e);
-    configured[gat][pair][a->epilogue] = smem;
-  }
+  static SmemAttr configured[2][2][7];
+  if (int e = configured[gat][pair][a->epilogue].ensure(kernel, smem)) return e;
   int sms = a->sms > 0 ? a->sms : g_num_sms;
   const int threads = p.gather.on ? 384 : 352;
   if (!pair) {

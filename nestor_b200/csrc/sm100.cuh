@@ -296,6 +296,26 @@ __device__ __forceinline__ uint64_t sdesc_mnmajor(uint32_t saddr, uint32_t atom_
   return make_sdesc(saddr, atom_bytes, 1024);
 }
 
+// Host side: the dynamic shared-memory limit of a kernel is a per-device attribute. One instance per kernel
+// instantiation remembers, for every device, the largest size already granted, and raises it when a launch
+// needs more (racing threads set the same value twice, which is harmless).
+struct SmemAttr {
+  static constexpr int kMaxDevices = 64;
+  int granted[kMaxDevices] = {0};
+  template <typename Kernel>
+  int ensure(Kernel kernel, size_t bytes) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return int(e);
+    if (dev < 0 || dev >= kMaxDevices) return int(cudaErrorInvalidDevice);
+    if (int(bytes) <= granted[dev]) return 0;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes));
+    if (e != cudaSuccess) return int(e);
+    granted[dev] = int(bytes);
+    return 0;
+  }
+};
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&t);

@@ -39,8 +39,30 @@ def launch_count() -> int:
     return _lib.LAUNCHES
 
 
+_oracle_depth = 0
+
+
+class oracle_ops:
+    """``with ops.oracle_ops():`` run the PyTorch statement of every op on any device.
+
+    The kernels compute in bf16 with fp32 accumulation. Code that wants full-precision arithmetic on a GPU (fp32
+    evaluation, numerics comparisons) asks for the oracle explicitly with this context; nothing selects it behind
+    the caller's back.
+    """
+
+    def __enter__(self):
+        global _oracle_depth
+        _oracle_depth += 1
+        return self
+
+    def __exit__(self, *exc):
+        global _oracle_depth
+        _oracle_depth -= 1
+        return False
+
+
 def use_kernels(t: torch.Tensor) -> bool:
-    return t.is_cuda and not _FORCE_REF
+    return t.is_cuda and not _FORCE_REF and _oracle_depth == 0
 
 
 def _dispatch(name: str):
@@ -52,8 +74,10 @@ def _dispatch(name: str):
         probe = first[0] if isinstance(first, (list, tuple)) else first
         if use_kernels(probe):
             fn = getattr(cuda_ops(), name, None)
-            if fn is not None:
-                return fn(*args, **kwargs)
+            if fn is None:
+                raise RuntimeError(f"ops.{name} has no sm_100a kernel body; CUDA tensors never take the PyTorch "
+                                   "statement silently (set NESTOR_B200_REFERENCE_OPS=1 to run the oracle on a GPU)")
+            return fn(*args, **kwargs)
         return ref_fn(*args, **kwargs)
 
     op.__name__ = name
@@ -61,8 +85,9 @@ def _dispatch(name: str):
     return op
 
 
-rmsnorm = _dispatch("rmsnorm")
-depth_read = _dispatch("depth_read")
+# The two halves of ``depth_read_norm`` as separate equations: test oracles only (the model calls the fused op).
+rmsnorm = _ref.rmsnorm
+depth_read = _ref.depth_read
 depth_read_norm = _dispatch("depth_read_norm")
 grad_sink = _dispatch("grad_sink")
 mid_source = _dispatch("mid_source")

@@ -1,8 +1,9 @@
 """ctypes binding of the in-tree sm_100a kernel library.
 
-The library is looked up at ``nestor_b200/_C/libnestor_b200.so``; when it is missing and
-``nvcc`` is present it is built on first use. On a machine with a CUDA device, a missing
-library is an error (there is no silent PyTorch fallback for CUDA tensors).
+The library lives at ``nestor_b200/_C/libnestor_b200.so`` and is brought up to date on first use
+(objects are cached by source digest, so nothing is recompiled when nothing changed). Without a
+compiler a stale or missing library is an error: there is no silent PyTorch fallback for CUDA
+tensors, and a binary older than the ctypes structures of this package is never loaded.
 """
 
 from __future__ import annotations
@@ -30,7 +31,7 @@ class GemmArgs(C.Structure):
         ("A", Operand), ("B", Operand), ("A2", Operand), ("B2", Operand),
         ("C", C.c_void_p), ("ldc", C.c_long), ("c_group_stride", C.c_long),
         ("C2", C.c_void_p), ("C3", C.c_void_p), ("E1", C.c_void_p), ("E2", C.c_void_p), ("lde", C.c_long),
-        ("alpha", C.c_float), ("n_valid", C.c_int), ("splits", C.c_int), ("status", C.c_void_p),
+        ("alpha", C.c_float), ("beta", C.c_float), ("n_valid", C.c_int), ("splits", C.c_int), ("status", C.c_void_p),
         ("max_m_tiles", C.c_int),
         ("sms", C.c_int), ("trace", C.c_void_p),
         ("prefetch_dist", C.c_int), ("prefetch_ops", C.c_int), ("max_stages", C.c_int), ("pair", C.c_int), ("debug", C.c_int),
@@ -46,11 +47,10 @@ class GemmArgs(C.Structure):
 def lib() -> C.CDLL:
     global _LIB
     if _LIB is None:
-        path = Path(__file__).resolve().parent.parent / "_C" / "libnestor_b200.so"
-        if not path.is_file():
-            from nestor_b200.csrc.build import build
-            build()
-        _LIB = C.CDLL(str(path))
+        # always go through the build front end: unchanged sources cost a hash, changed ones are recompiled, and a
+        # machine without a compiler refuses a binary that is older than its sources
+        from nestor_b200.csrc.build import ensure
+        _LIB = C.CDLL(str(ensure()))
         _LIB.nb_gemm.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
         _LIB.nb_gemm.restype = C.c_int
     return _LIB

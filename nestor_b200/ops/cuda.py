@@ -57,6 +57,9 @@ def _L():
         L.nb_route_bwd.argtypes = [vp, vp, vp, vp, l, i, vp, vp]
         for fn in (L.nb_expert_plan, L.nb_route_fwd, L.nb_route_bwd):
             fn.restype = C.c_int
+        L.nb_ns_prepare.argtypes = [vp, vp, i, i, i, i, i, vp]
+        L.nb_ns_finish.argtypes = [vp, vp, i, i, i, i, i, vp]
+        L.nb_ns_prepare.restype = L.nb_ns_finish.restype = C.c_int
         for fn in (L.nb_gather_rows, L.nb_combine_rows, L.nb_combine_bwd, L.nb_rope, L.nb_ce_grad,
                    L.nb_depth_read_norm):
             fn.restype = C.c_int
@@ -791,3 +794,51 @@ def route_selected(scores: Tensor, bias: Tensor, cols: Tensor, col_gates: Tensor
     if tape is not None and tape.mode == "record":
         tape.selections.append(idx.long().view(T, kc, k))
     return ids.view(T, kc * k), w.view(T, kc * k), idx.view(T, kc, k)
+
+
+# ---------------------------------------------------------------------- Newton-Schulz
+_NS_MAX_BATCH = 256      # groups per grouped-GEMM launch
+
+
+@torch.no_grad()
+def newton_schulz(g: Tensor, steps: int = 5, out_dtype: torch.dtype | None = None) -> Tensor:
+    """Quintic Newton-Schulz on ``[..., m, n]`` matrices, every product on the tcgen05 grouped GEMM.
+
+    One batch (up to 256 same-shape matrices) costs ``2 + 3 * steps`` launches: normalise + cast + orient
+    (``nb_ns_prepare``), then per iteration ``A = X X^T`` (K-major B = X), ``B = b A + c A A`` and
+    ``X <- a X + B X`` (B operand X read MN-major), the last two through the ``alpha * acc + beta * E1``
+    epilogue, then ``nb_ns_finish`` when the result has to be turned back or un-padded. Matrices are the
+    groups of the launches; rows of a matrix shorter than a 128-row tile are masked, not padded.
+    """
+
+    a, b, c = ref.NS_COEFFS
+    squeeze = g.ndim == 2
+    x = g.unsqueeze(0) if squeeze else g
+    if x.ndim != 3:
+        x = x.reshape(-1, *x.shape[-2:])
+    x = x.float().contiguous()
+    Bt, m, n = x.shape
+    rows, cols = min(m, n), max(m, n)
+    mp, npad = -(-rows // 8) * 8, -(-cols // 8) * 8
+    direct = m <= n and mp == m and npad == n      # the iterate already has the parameter's layout
+    dev = x.device
+    out = torch.empty(Bt, m, n, dtype=BF16, device=dev)
+    L = _L()
+    for lo in range(0, Bt, _NS_MAX_BATCH):
+        nb = min(_NS_MAX_BATCH, Bt - lo)
+        X = out[lo : lo + nb].view(nb * mp, npad) if direct and steps % 2 == 0 else torch.empty(nb * mp, npad, dtype=BF16, device=dev)
+        X2 = out[lo : lo + nb].view(nb * mp, npad) if direct and steps % 2 == 1 else torch.empty(nb * mp, npad, dtype=BF16, device=dev)
+        A = torch.empty(nb * mp, mp, dtype=BF16, device=dev)
+        Bm = torch.empty(nb * mp, mp, dtype=BF16, device=dev)
+        _ck(L.nb_ns_prepare(x[lo : lo + nb].data_ptr(), X.data_ptr(), nb, m, n, mp, npad, _st()), "ns_prepare")
+        for _ in range(steps):
+            G.gemm_rows(X, X.view(nb, mp, npad), groups=nb, out=A)
+            G.gemm_rows(A, A.view(nb, mp, mp), groups=nb, out=Bm, epilogue=G.AXPBY_BF16, alpha=c, beta=b, extra_in=(A,))
+            G.gemm_rows(Bm, X.view(nb, mp, npad), groups=nb, b_mn=True, n=npad, out=X2, epilogue=G.AXPBY_BF16,
+                        alpha=1.0, beta=a, extra_in=(X,))
+            X, X2 = X2, X
+        if not direct:
+            _ck(L.nb_ns_finish(X.data_ptr(), out[lo : lo + nb].data_ptr(), nb, m, n, mp, npad, _st()), "ns_finish")
+    out = out.view(g.shape)
+    want = g.dtype if out_dtype is None else out_dtype
+    return out if want == BF16 else out.to(want)

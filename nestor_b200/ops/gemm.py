@@ -18,7 +18,7 @@ from torch import Tensor
 
 from nestor_b200.ops import _lib
 
-STORE_BF16, STORE_F32, ACCUM_F32, SWIGLU, SWIGLU_BWD, STORE_BF16_STATS = range(6)
+STORE_BF16, STORE_F32, ACCUM_F32, SWIGLU, SWIGLU_BWD, STORE_BF16_STATS, AXPBY_BF16 = range(7)
 # STORE_BF16_STATS writes this many (max, sum-exp) partials per row and n-tile: extra_out[0] is [rows, n_tiles * STATS_PARTS, 2]
 STATS_PARTS = 2
 
@@ -127,7 +127,8 @@ def _launch(args: _lib.GemmArgs) -> None:
 
 
 def gemm_rows(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: int = 1, b_mn: bool = False,
-              out: Tensor | None = None, epilogue: int = STORE_BF16, alpha: float = 1.0, bn: int | None = None,
+              out: Tensor | None = None, epilogue: int = STORE_BF16, alpha: float = 1.0, beta: float = 0.0,
+              bn: int | None = None,
               A2: Tensor | None = None, B2: Tensor | None = None, extra_out: tuple = (), extra_in: tuple = (),
               n: int | None = None, n_valid: int = 0, sms: int = 0, trace: Tensor | None = None,
               pair: bool | None = None, gather: Gather | None = None) -> Tensor:
@@ -137,7 +138,8 @@ def gemm_rows(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: in
     single shared matrix. ``offsets [G+1]`` (int32, device) bound the groups; ``None`` with
     ``groups == 1`` means one group over all rows. ``A2/B2`` extend the reduction. With
     ``epilogue == SWIGLU``, ``B`` is the gate bank and ``B2`` the up bank (both ``[G, K, h]``);
-    ``out`` receives ``silu(gate) * up`` and ``extra_out = (gate, up)``. With ``gather``, ``B`` (and ``B2``)
+    ``out`` receives ``silu(gate) * up`` and ``extra_out = (gate, up)``. With ``epilogue == AXPBY_BF16`` the
+    result is ``alpha * (A . B) + beta * extra_in[0]`` (bf16, same shape and pitch rules as ``out``). With ``gather``, ``B`` (and ``B2``)
     are 3-D views of the local weight arena whose groups are owned by different ranks: the launch stages them
     from their owners while it computes (see ``Gather``).
     """
@@ -191,7 +193,7 @@ def gemm_rows(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: in
     a.E1 = extra_in[0].data_ptr() if len(extra_in) > 0 else None
     a.E2 = extra_in[1].data_ptr() if len(extra_in) > 1 else None
     a.lde = extra_in[0].stride(0) if len(extra_in) > 0 else 0
-    a.alpha = alpha
+    a.alpha, a.beta = alpha, beta
     a.n_valid = n_valid
     a.status = _lib.status_word(dev).data_ptr()
     a.pair = int(pair)

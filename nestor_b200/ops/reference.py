@@ -484,7 +484,7 @@ def lm_head_ce(hidden: Tensor, weight: Tensor, targets: Tensor, multiplier: floa
 NS_COEFFS = (3.4445, -4.7750, 2.0315)
 
 
-def newton_schulz(g: Tensor, steps: int = 5) -> Tensor:
+def newton_schulz(g: Tensor, steps: int = 5, out_dtype: torch.dtype | None = None) -> Tensor:
     """Quintic Newton–Schulz orthogonalisation of ``[..., m, n]`` matrices in bf16.
 
     Normalise by the Frobenius norm (+1e-7), work on the wide orientation, iterate
@@ -504,5 +504,5 @@ def newton_schulz(g: Tensor, steps: int = 5) -> Tensor:
         x = a * x + bb @ x
     if transposed:
         x = x.mT
-    x = x.to(g.dtype)
+    x = x.to(g.dtype if out_dtype is None else out_dtype)
     return x.squeeze(0) if squeeze else x

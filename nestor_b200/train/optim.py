@@ -64,7 +64,8 @@ def orthogonalize(directions: list[Tensor], steps: int) -> list[Tensor]:
     for idxs in buckets.values():
         stack = torch.cat([directions[i] if directions[i].ndim == 3 else directions[i].unsqueeze(0)
                            for i in idxs], dim=0)
-        ortho = ops.newton_schulz(stack, steps)
+        # the kernel path hands back bf16 (the iterate's own precision); the parameter update reads it directly
+        ortho = ops.newton_schulz(stack, steps, out_dtype=torch.bfloat16 if stack.is_cuda else None)
         counts = [directions[i].shape[0] if directions[i].ndim == 3 else 1 for i in idxs]
         for i, chunk in zip(idxs, ortho.split(counts)):
             out[i] = chunk if directions[i].ndim == 3 else chunk.squeeze(0)

@@ -39,7 +39,7 @@ from nestor_b200.train import checkpoint as ckpt
 from nestor_b200.train.flops import train_flops_per_token
 from nestor_b200.train.losses import LossOutput, build_loss
 from nestor_b200.train.optim import build_optimizer, build_scheduler
-from nestor_b200.utils.distributed import get_rank, get_world_size, is_main_process
+from nestor_b200.utils.distributed import barrier, get_rank, get_world_size, is_main_process
 from nestor_b200.utils.logging import get_logger, log_metrics
 from nestor_b200.utils.timing import PROCESS_START
 
@@ -89,6 +89,14 @@ class Trainer:
         # the pushed range carries every parameter in it; when its owner is the only one to update them (ZeRO-1 for
         # AdamW as well) it is also the only one that needs their reduced gradients: reduce-scatter
         self.zero = bool(self.param_push is not None and getattr(self.optimizer, "shard_adamw", False))
+        # Device status word of the in-kernel collectives: a bounded peer wait that gave up leaves a nonzero code
+        # there and the kernel returns without reducing / pushing. It is read back once per optimizer step.
+        self.peer_status: Tensor | None = None
+        self._status_host: Tensor | None = None
+        self._status_event = None
+        if fused:
+            from nestor_b200.ops import _lib
+            self.peer_status = _lib.status_word(device)
         self.global_step, self.epoch = 0, 0
         self.ema: dict[str, Tensor] | None = None
         decay = os.environ.get("NESTOR_EMA_DECAY")
@@ -199,7 +207,48 @@ class Trainer:
         self.arena.grad.mul_(scale)
         return norm
 
+    def _probe_peer_status(self) -> None:
+        """Queue an asynchronous read-back of the status word behind this step's collectives."""
+
+        st = self.peer_status
+        if st is None:
+            return
+        if st.is_cuda:
+            if self._status_host is None:
+                self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+            self._status_host.copy_(st, non_blocking=True)
+            self._status_event = torch.cuda.Event()
+            self._status_event.record()
+        else:
+            self._status_host = st
+
+    def check_peer_status(self) -> None:
+        """Raise ``PeerTimeout`` if a collective of an earlier optimizer step gave up waiting for a peer.
+
+        Without this the step would carry on with unreduced local gradients and stale parameters, and the replicas
+        would silently diverge. The value inspected is the one queued by the previous ``update_weights`` (already
+        complete by the time the next step's micro-batches have been submitted), so the check costs no extra stall.
+        """
+
+        if self._status_host is None:
+            return
+        if self._status_event is not None:
+            self._status_event.synchronize()
+            self._status_event = None
+        code = int(self._status_host.item())
+        if code:
+            from nestor_b200.parallel.symm import PeerTimeout
+            if self.peer_status is not None:
+                self.peer_status.zero_()
+            self._status_host = None
+            raise PeerTimeout(f"rank {self.rank}: an in-kernel collective reported status {code} at step "
+                              f"{self.global_step} (a bounded wait on a peer gave up); gradients or parameters of "
+                              "that step are not synchronised")
+        if self.peer_status is not None and not self.peer_status.is_cuda:
+            self._status_host = None
+
     def update_weights(self, window_counts: dict[str, Tensor]) -> Tensor | None:
+        self.check_peer_status()
         if self.zero:
             self.reducer.reduce_scatter(*self.optimizer.owned_range())
         else:
@@ -227,6 +276,7 @@ class Trainer:
         apply_bias_updates(self.model.backbone, window_counts, global_counts=self.global_counts)
         if self.world > 1 and not self.global_counts and _env_flag("NESTOR_DDP_BROADCAST_BUFFERS", "1"):
             self.reducer.sync_buffers(self.model)  # rank-0 statistics win, as with DDP buffer broadcast
+        self._probe_peer_status()
         return norm
 
     # --------------------------------------------------------------------------- loop
@@ -343,6 +393,7 @@ class Trainer:
             return
         if self.runahead == 0:
             torch.cuda.synchronize()
+            self.check_peer_status()
             return
         ev = torch.cuda.Event()
         ev.record()
@@ -400,6 +451,9 @@ class Trainer:
                              epoch=self.epoch, ema=ema)
         if is_main_process():
             self.logger.info("saved %s", path)
+        # Only rank 0 writes the file. The others wait here, on the process group's long timeout, instead of inside
+        # the next step's in-kernel barrier, whose wait budget is seconds.
+        barrier()
 
     def resume(self, path: Path, *, strict: bool = True, allow_partial: bool = False) -> None:
         state = ckpt.load_checkpoint(path, self.model, self.optimizer if strict else None,

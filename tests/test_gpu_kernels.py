@@ -485,3 +485,40 @@ def test_gemm_with_fused_all_gather_of_rank_sharded_banks(rows, world):
         for w, g in zip(want, got):
             assert torch.isfinite(g.float()).all()
             assert torch.equal(w, g)
+
+
+@pytest.mark.parametrize("shape", [(3, 200, 640), (2, 640, 200), (5, 216, 640), (4, 640, 216), (1, 128, 640), (2, 640, 640),
+                                   (3, 80, 640), (2, 90, 480), (1, 640, 856), (300, 120, 640)])
+def test_newton_schulz_matches_oracle(shape):
+    """The tcgen05 Newton-Schulz against the fp32-input PyTorch statement, and orthogonality of the result.
+
+    The iteration is run in bf16 on both sides with different rounding points, so the two results are compared
+    loosely (bf16 noise amplified over five iterations); the singular values, which is what the optimizer relies on,
+    must land in the same band as the oracle's.
+    """
+
+    from nestor_b200.ops import cuda as K, reference as R
+    torch.manual_seed(sum(shape))
+    g = torch.randn(*shape, device="cuda")
+    got = K.newton_schulz(g, 5)
+    want = R.newton_schulz(g, 5)
+    assert got.shape == want.shape and got.dtype == g.dtype and torch.isfinite(got).all()
+    assert _rel(got, want) < 0.08, _rel(got, want)
+    sv_got = torch.linalg.svdvals(got[0].float())
+    sv_want = torch.linalg.svdvals(want[0].float())
+    assert sv_got.max() < max(1.3, 1.05 * float(sv_want.max())) and sv_got.min() > min(0.3, 0.9 * float(sv_want.min()))
+    # 2-D input and bf16 output
+    one = K.newton_schulz(g[0], 5, out_dtype=BF)
+    assert one.dtype == BF and one.shape == g[0].shape and _rel(one, got[0]) < 1e-2
+
+
+def test_dispatch_refuses_cuda_tensor_without_kernel_body():
+    from nestor_b200 import ops
+    op = ops._dispatch("rope_tables") if hasattr(ops._ref, "rope_tables") else None
+    x = torch.ones(4, device="cuda")
+    if op is not None:
+        with pytest.raises(RuntimeError, match="no sm_100a kernel body"):
+            op(x)
+    with ops.oracle_ops():
+        assert not ops.use_kernels(x)
+    assert ops.use_kernels(x)

@@ -178,3 +178,32 @@ def test_cli_train_checkpoint_and_auto_resume(tmp_path, monkeypatch):
     trainer.train()
     assert trainer.global_step == 3
     pipe.ctx.close()
+
+
+def test_update_weights_raises_when_a_collective_reported_a_timeout(tiny_scale, tmp_path, monkeypatch):
+    """A nonzero device status word (a bounded peer wait that gave up) must surface as ``PeerTimeout`` out of the
+    optimizer step instead of letting training continue on unreduced gradients."""
+
+    from nestor_b200.models import Model
+    from nestor_b200.parallel.symm import PeerTimeout
+    from nestor_b200.train.trainer import Trainer
+    data = write_synthetic_bin(tmp_path / "train.bin", 64 * 40, 100_277, doc_len_range=(16, 64))
+    monkeypatch.setenv("DCLM_DATA_PATH", str(data))
+    job = tiny_scale.build_experiment("nestor", "tiny").jobs[0]
+    trainer = Trainer(job, Model.from_config(job.model), [], device=torch.device("cpu"))
+    ids = torch.randint(0, 1000, (2, 64))
+    trainer.model.train()
+    trainer.train_step((ids, ids))
+    trainer.update_weights({})                      # no status source on a single CPU process: nothing to check
+    trainer.peer_status = torch.zeros(1, dtype=torch.int32)
+    trainer.train_step((ids, ids))
+    trainer.update_weights({})                      # clean status: the probe is queued and passes
+    trainer.check_peer_status()
+    trainer.train_step((ids, ids))
+    trainer.update_weights({})
+    trainer.peer_status.fill_(5)                    # what a timed-out in-kernel barrier leaves behind
+    trainer._probe_peer_status()
+    trainer.train_step((ids, ids))
+    with pytest.raises(PeerTimeout, match="status 5"):
+        trainer.update_weights({})
+    assert int(trainer.peer_status.item()) == 0     # cleared, so a caller that recovers can carry on
