@@ -144,6 +144,85 @@ param_push_kernel(Peers P, long lo, long hi, uint32_t epoch, long budget, int* s
   block_barrier(P, 3, epoch, budget, status);
 }
 
+// ------------------------------------------------------------------------------------------------
+// NVLS variants: the symmetric buffers are also mapped through one NVLink multicast address each. A
+// `multimem.ld_reduce` on that address returns the sum of every rank's copy, added inside the NVSwitch (each GPU
+// receives one reduced stream instead of world - 1 peer streams), and a `multimem.st` writes every rank's copy at once
+// (the owner sends one stream instead of world - 1). Same barriers, same bounded waits, same status word.
+__device__ __forceinline__ float4 mm_ld_reduce_f32x4(const float* mc) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+__device__ __forceinline__ void mm_st_f32x4(float* mc, float4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+               :: "l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ void mm_st_bf16x4(__nv_bfloat16* mc, uint2 packed) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.bf16x2 [%0], {%1,%2};" :: "l"(mc), "r"(packed.x), "r"(packed.y) : "memory");
+}
+
+// Reduce-scatter (store_all = 0: the sum of [own_lo, own_hi) lands in this rank's buffer only) or all-reduce
+// (store_all = 1: every rank reduces its 1/world slice of [offset, offset + numel) and multicasts the result).
+// `mc_buf` / `mc_aux` are the multicast addresses of the fp32 buffer and of the optional bf16 mirror.
+__global__ void __launch_bounds__(512, 1)
+allreduce_nvls_kernel(Peers P, float* mc_buf, __nv_bfloat16* mc_aux, long offset, long numel, float scale, int write_mirror,
+                      uint32_t epoch, long budget, int* status, int store_all, long own_lo, long own_hi) {
+  if (!block_barrier(P, 0, epoch, budget, status)) return;
+  const long n4 = numel / 4;
+  const long per = (n4 + P.world - 1) / P.world;
+  const long lo = store_all ? per * P.rank : own_lo / 4, hi = store_all ? min(n4, lo + per) : own_hi / 4;
+  constexpr int kUnroll = 4;
+  const long stride = long(gridDim.x) * blockDim.x;
+  float* mine = reinterpret_cast<float*>(P.buf[P.rank]) + offset;
+  __nv_bfloat16* mine_aux = reinterpret_cast<__nv_bfloat16*>(P.aux[P.rank]) + offset;
+  for (long i0 = lo + long(blockIdx.x) * blockDim.x + threadIdx.x; i0 < hi; i0 += stride * kUnroll) {
+    float4 v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long i = i0 + u * stride;
+      v[u] = i < hi ? mm_ld_reduce_f32x4(mc_buf + offset + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long i = i0 + u * stride;
+      if (i >= hi) break;
+      float4 a = v[u];
+      a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
+      __nv_bfloat162 b0 = __floats2bfloat162_rn(a.x, a.y), b1 = __floats2bfloat162_rn(a.z, a.w);
+      const uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&b0), *reinterpret_cast<uint32_t*>(&b1));
+      if (store_all) {
+        mm_st_f32x4(mc_buf + offset + 4 * i, a);
+        if (write_mirror) mm_st_bf16x4(mc_aux + offset + 4 * i, packed);
+      } else {
+        reinterpret_cast<float4*>(mine)[i] = a;
+        if (write_mirror) reinterpret_cast<uint2*>(mine_aux)[i] = packed;
+      }
+    }
+  }
+  block_barrier(P, 1, epoch, budget, status);
+}
+
+// Parameter push through the multicast mapping: one store per element reaches every replica (this rank's included,
+// which rewrites its own master with the value just read).
+__global__ void __launch_bounds__(512, 1)
+param_push_nvls_kernel(Peers P, float* mc_master, __nv_bfloat16* mc_compute, long lo, long hi, uint32_t epoch, long budget,
+                       int* status) {
+  if (!block_barrier(P, 2, epoch, budget, status)) return;
+  const long lo4 = lo / 4, hi4 = hi / 4;
+  const long stride = long(gridDim.x) * blockDim.x;
+  const float4* src = reinterpret_cast<const float4*>(P.buf[P.rank]);
+  for (long i = lo4 + long(blockIdx.x) * blockDim.x + threadIdx.x; i < hi4; i += stride) {
+    const float4 v = src[i];
+    __nv_bfloat162 b0 = __floats2bfloat162_rn(v.x, v.y), b1 = __floats2bfloat162_rn(v.z, v.w);
+    const uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&b0), *reinterpret_cast<uint32_t*>(&b1));
+    mm_st_f32x4(mc_master + 4 * i, v);
+    if (mc_compute) mm_st_bf16x4(mc_compute + 4 * i, packed);
+  }
+  block_barrier(P, 3, epoch, budget, status);
+}
+
 // Single-GPU exercise of the bounded wait: spins on a flag nothing sets and reports the timeout.
 __global__ void wait_timeout_probe_kernel(uint32_t* flag, uint32_t expect, long budget, int* status) {
   if (threadIdx.x == 0 && blockIdx.x == 0) {
@@ -165,6 +244,21 @@ struct NbPeers {
   int world, rank;
 };
 
+static int max_blocks() {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 1;
+  }
+  return sms;
+}
+
+// Launches are one block per SM at most (512 threads, one block resident per SM): every block of every rank must be
+// running for the in-kernel barriers to complete.
+int nb_comm_max_blocks(void) { return max_blocks(); }
+
 static nbc::Peers to_peers(const NbPeers* a) {
   nbc::Peers P;
   for (int i = 0; i < 8; ++i) { P.buf[i] = a->buf[i]; P.aux[i] = a->aux[i]; P.sig[i] = reinterpret_cast<uint32_t*>(a->sig[i]); }
@@ -172,10 +266,11 @@ static nbc::Peers to_peers(const NbPeers* a) {
   return P;
 }
 
-// numel and offset in fp32 elements, both multiples of 4. `blocks` must be equal on every rank and at most the SM count.
+// numel and offset in fp32 elements, both multiples of 4. `blocks` must be equal on every rank and at most the SM count
+// (nb_comm_max_blocks).
 int nb_allreduce_push(const NbPeers* a, long offset, long numel, float scale, int write_mirror, unsigned epoch, long budget,
                       int blocks, int* status, cudaStream_t st) {
-  if (a->world < 1 || a->world > 8 || (numel % 4) || (offset % 4) || blocks < 1 || blocks > 148) return -1;
+  if (a->world < 1 || a->world > 8 || (numel % 4) || (offset % 4) || blocks < 1 || blocks > max_blocks()) return -1;
   nbc::allreduce_push_kernel<<<blocks, 512, 0, st>>>(to_peers(a), offset, numel, scale, write_mirror, epoch, budget, status,
                                                      1, 0, 0);
   return int(cudaGetLastError());
@@ -185,14 +280,41 @@ int nb_allreduce_push(const NbPeers* a, long offset, long numel, float scale, in
 // (x scale). Every rank passes its own range; ranges may differ in size and must not overlap.
 int nb_reduce_scatter_push(const NbPeers* a, long lo, long hi, float scale, int write_mirror, unsigned epoch, long budget,
                            int blocks, int* status, cudaStream_t st) {
-  if (a->world < 1 || a->world > 8 || (lo % 4) || (hi % 4) || hi < lo || blocks < 1 || blocks > 148) return -1;
+  if (a->world < 1 || a->world > 8 || (lo % 4) || (hi % 4) || hi < lo || blocks < 1 || blocks > max_blocks()) return -1;
   nbc::allreduce_push_kernel<<<blocks, 512, 0, st>>>(to_peers(a), 0, 0, scale, write_mirror, epoch, budget, status, 0, lo, hi);
   return int(cudaGetLastError());
 }
 
 int nb_param_push(const NbPeers* a, long lo, long hi, unsigned epoch, long budget, int blocks, int* status, cudaStream_t st) {
-  if (a->world < 1 || a->world > 8 || (lo % 4) || (hi % 4) || blocks < 1 || blocks > 148) return -1;
+  if (a->world < 1 || a->world > 8 || (lo % 4) || (hi % 4) || blocks < 1 || blocks > max_blocks()) return -1;
   nbc::param_push_kernel<<<blocks, 512, 0, st>>>(to_peers(a), lo, hi, epoch, budget, status);
+  return int(cudaGetLastError());
+}
+
+// NVLS forms of the three collectives: `mc_buf` / `mc_aux` are the multicast addresses of the buffers whose per-rank
+// addresses are in `a->buf` / `a->aux` (mc_aux may be null when no mirror / compute copy is written).
+int nb_allreduce_nvls(const NbPeers* a, void* mc_buf, void* mc_aux, long offset, long numel, float scale, int write_mirror,
+                      unsigned epoch, long budget, int blocks, int* status, cudaStream_t st) {
+  if (a->world < 1 || a->world > 8 || !mc_buf || (numel % 4) || (offset % 4) || blocks < 1 || blocks > max_blocks()) return -1;
+  if (write_mirror && !mc_aux) return -1;
+  nbc::allreduce_nvls_kernel<<<blocks, 512, 0, st>>>(to_peers(a), static_cast<float*>(mc_buf), static_cast<__nv_bfloat16*>(mc_aux),
+                                                     offset, numel, scale, write_mirror, epoch, budget, status, 1, 0, 0);
+  return int(cudaGetLastError());
+}
+
+int nb_reduce_scatter_nvls(const NbPeers* a, void* mc_buf, long lo, long hi, float scale, int write_mirror, unsigned epoch,
+                           long budget, int blocks, int* status, cudaStream_t st) {
+  if (a->world < 1 || a->world > 8 || !mc_buf || (lo % 4) || (hi % 4) || hi < lo || blocks < 1 || blocks > max_blocks()) return -1;
+  nbc::allreduce_nvls_kernel<<<blocks, 512, 0, st>>>(to_peers(a), static_cast<float*>(mc_buf), nullptr, 0, 0, scale, write_mirror,
+                                                     epoch, budget, status, 0, lo, hi);
+  return int(cudaGetLastError());
+}
+
+int nb_param_push_nvls(const NbPeers* a, void* mc_master, void* mc_compute, long lo, long hi, unsigned epoch, long budget,
+                       int blocks, int* status, cudaStream_t st) {
+  if (a->world < 1 || a->world > 8 || !mc_master || (lo % 4) || (hi % 4) || blocks < 1 || blocks > max_blocks()) return -1;
+  nbc::param_push_nvls_kernel<<<blocks, 512, 0, st>>>(to_peers(a), static_cast<float*>(mc_master),
+                                                      static_cast<__nv_bfloat16*>(mc_compute), lo, hi, epoch, budget, status);
   return int(cudaGetLastError());
 }
 

@@ -37,16 +37,16 @@ __device__ __forceinline__ void st_tile_chunk(uint8_t* base, int row, int col0, 
 }
 
 template <int MODE, int HDN>
-__global__ void __launch_bounds__(192, HDN == 64 ? 2 : 1)
+__global__ void __launch_bounds__(320, HDN == 64 ? 2 : 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant__ CUtensorMap tmR2,
                  const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ CUtensorMap tmX2,
                  const FlashBwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ uint64_t r_full, x_full[2], x_empty[2], sc_full, ds_ready, acc_done;
+  __shared__ uint64_t r_full, x_full[3], x_empty[3], sc_full, ds_ready, acc_done;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
   __shared__ int s_tile[4];
-  __shared__ float s_lse[4][BX], s_delta[4][BX];   // one private copy per softmax warp (no cross-warp barrier)
+  __shared__ __align__(16) float s_lse[8][32], s_delta[8][32];   // negated; the 32 columns of each softmax warp (no cross-warp barrier)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.y;
@@ -62,25 +62,19 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
   uint8_t* sDS = sX + stages * 2 * xtile_bytes;         // 16 KB: dS (or dS^T), 128 rows x 64 streamed columns
   uint8_t* sPT = sDS + 16384;                           // 16 KB: P^T (MODE 0 only)
 
-  if (threadIdx.x == 0) {
-    int t = blockIdx.x, found = 0, b = 0, e = 0, r0 = 0;
-    for (int s = 0; s < p.nseg; ++s) {
-      b = p.seg_start[s]; e = p.seg_start[s + 1];
-      int nt = (e - b + BT - 1) / BT;
-      if (t < nt) {
-        // heaviest first: MODE 0 the earliest kv tile, MODE 1 the last q tile
-        r0 = (MODE == 0) ? b + t * BT : b + (nt - 1 - t) * BT;
-        found = 1; break;
-      }
-      t -= nt;
+  if (warp == 0) {
+    int b = 0, e = 0, local = 0, nt = 0;
+    const bool found = find_segment_tile(p.seg_start, p.nseg, BT, blockIdx.x, b, e, local, nt);
+    if (lane == 0) {
+      // heaviest first: MODE 0 the earliest kv tile, MODE 1 the last q tile
+      s_tile[0] = b; s_tile[1] = e; s_tile[2] = (MODE == 0) ? b + local * BT : b + (nt - 1 - local) * BT; s_tile[3] = found ? 1 : 0;
+      s_abort = 0;
+      mbar_init(&r_full, 1);
+      for (int i = 0; i < 3; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 1); }
+      mbar_init(&sc_full, 1); mbar_init(&ds_ready, 8); mbar_init(&acc_done, 1);
+      fence_barrier_init();
+      prefetch_tmap(&tmR1); prefetch_tmap(&tmR2); prefetch_tmap(&tmX1); prefetch_tmap(&tmX2);
     }
-    s_tile[0] = b; s_tile[1] = e; s_tile[2] = r0; s_tile[3] = found;
-    s_abort = 0;
-    mbar_init(&r_full, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 1); }
-    mbar_init(&sc_full, 1); mbar_init(&ds_ready, 4); mbar_init(&acc_done, 1);
-    fence_barrier_init();
-    prefetch_tmap(&tmR1); prefetch_tmap(&tmR2); prefetch_tmap(&tmX1); prefetch_tmap(&tmX2);
   }
   __syncthreads();
   if (!s_tile[3]) return;
@@ -167,53 +161,82 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
       if (++s == stages) { s = 0; ph ^= 1; }
     }
   } else {
+    // Eight warps: warp w reads TMEM lane quarter w % 4 (its 32 rows of the resident tile); the two warps of a quarter
+    // split the streamed tile's 64 columns, so every row is worked on by two threads. Nothing here is bound by a
+    // unit's throughput (exponential pipe ~30 %, issue slots ~30 % with one thread per row); what matters is how many
+    // independent instruction streams the schedulers can switch between while TMEM reads, exponentials and
+    // shared-memory stores are in flight.
     const int q4 = warp & 3;
+    const int half = (warp - 2) >> 2;               // which 32 streamed columns
     const int r = q4 * 32 + lane;
     const int grow = r0 + r;                        // global row owned by this thread
     const uint32_t lane_off = uint32_t(q4 * 32) << 16;
-    float my_lse = 0.f, my_delta = 0.f;
-    if (MODE == 1 && grow < p.rows) { my_lse = p.lse[long(grow) * p.H + head]; my_delta = p.delta[long(grow) * p.H + head]; }
+    const int c0 = half * 32;
+    float* nlse_c = s_lse[warp - 2];
+    float* ndel_c = s_delta[warp - 2];
+    float my_nlse = 0.f, my_ndelta = 0.f;
+    if (MODE == 1 && grow < p.rows) { my_nlse = -p.lse[long(grow) * p.H + head]; my_ndelta = -p.delta[long(grow) * p.H + head]; }
+    const uint64_t my_nlse2 = f2_pack(my_nlse, my_nlse), my_ndelta2 = f2_pack(my_ndelta, my_ndelta);
+    const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2);
     bool ok = true;
+    float pre_l = 0.f, pre_d = 0.f;
+    auto fetch_stats = [&](int xbase) {
+      const int xr = xbase + c0 + lane;
+      const bool in = xr < seg_e;
+      pre_l = in ? -p.lse[long(xr) * p.H + head] : -INFINITY;   // exp2(-inf) = 0 for rows past the segment
+      pre_d = in ? -p.delta[long(xr) * p.H + head] : 0.f;
+    };
+    if (MODE == 0) fetch_stats(x_first);
     for (int it = 0; it < niter; ++it) {
       const int x0 = x_first + it * BX;
       if (MODE == 0) {
+        // the streamed q rows' (negated) log-sum-exp and delta: this iteration's values were fetched during the previous
+        // one, the next iteration's are requested now, so their latency never sits between two tiles
         __syncwarp();
-#pragma unroll
-        for (int u = 0; u < BX / 32; ++u) {
-          int cc = lane + 32 * u, xr = x0 + cc;
-          bool in = xr < seg_e;
-          s_lse[q4][cc] = in ? p.lse[long(xr) * p.H + head] : INFINITY;   // exp2(-inf) = 0 for rows past the segment
-          s_delta[q4][cc] = in ? p.delta[long(xr) * p.H + head] : 0.f;
-        }
+        nlse_c[lane] = pre_l; ndel_c[lane] = pre_d;
         __syncwarp();
+        if (it + 1 < niter) fetch_stats(x0 + BX);
       }
       if (!mbar_wait(&sc_full, it & 1, abort_flag, p.status, kTimeoutTmemFull)) { ok = false; break; }
       tc_fence_after();
       // the smem tiles are free once the previous iteration's accumulate products retired
       if (it > 0 && !mbar_wait(&acc_done, (it - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) { ok = false; break; }
-      const float* lse_c = s_lse[q4];
-      const float* del_c = s_delta[q4];
-      for (int c = 0; c < BX; c += 16) {
-        float sv[16], dv[16];
-        tmem_ld16(tS + lane_off + c, sv); tmem_ld16(tDP + lane_off + c, dv);
-        tmem_ld_wait();
-        uint32_t wp[8], wd[8];
+      // does any (row of the resident tile, column of the streamed tile) pair fall on the hidden side of the diagonal?
+      const bool diag = (MODE == 0) ? (x0 < r0 + BT - 1) : (x0 + BX - 1 > r0);
+      float sv[32], dv[32];
+      tmem_ld32(tS + lane_off + c0, sv); tmem_ld32(tDP + lane_off + c0, dv);
+      tmem_ld_wait32x2(sv, dv);
+      // phase 1: scaled, shifted scores and (dP - delta), two columns per instruction
 #pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-          float pv[2], dsv[2];
+      for (int i = 0; i < 32; i += 2) {
+        const uint64_t nl2 = (MODE == 0) ? *reinterpret_cast<const uint64_t*>(nlse_c + i) : my_nlse2;
+        const uint64_t nd2 = (MODE == 0) ? *reinterpret_cast<const uint64_t*>(ndel_c + i) : my_ndelta2;
+        f2_unpack(f2_fma(f2_pack(sv[i], sv[i + 1]), scale2, nl2), sv[i], sv[i + 1]);
+        f2_unpack(f2_add(f2_pack(dv[i], dv[i + 1]), nd2), dv[i], dv[i + 1]);
+      }
+      // phase 2: probabilities (independent exponentials back to back)
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            int cc = c + i + h;
-            bool vis; float lz, dl;
-            if (MODE == 0) { vis = (x0 + cc) >= grow; lz = lse_c[cc]; dl = del_c[cc]; }
-            else { vis = (x0 + cc) <= grow; lz = my_lse; dl = my_delta; }
-            float pr = vis ? exp2f(sv[i + h] * p.scale_log2 - lz) : 0.f;
-            pv[h] = pr; dsv[h] = vis ? pr * (dv[i + h] - dl) : 0.f;
-          }
-          wp[i >> 1] = pack_bf16(pv[0], pv[1]); wd[i >> 1] = pack_bf16(dsv[0], dsv[1]);
+      for (int i = 0; i < 32; ++i) sv[i] = ex2_approx(sv[i]);
+      if (diag) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const bool vis = (MODE == 0) ? (x0 + c0 + i) >= grow : (x0 + c0 + i) <= grow;
+          sv[i] = vis ? sv[i] : 0.f;
         }
-        st_tile_chunk(sDS, r, c, wd); st_tile_chunk(sDS, r, c + 8, wd + 4);
-        if (MODE == 0) { st_tile_chunk(sPT, r, c, wp); st_tile_chunk(sPT, r, c + 8, wp + 4); }
+      }
+      // phase 3: dS = P (dP - delta), both rounded to bf16 into the swizzled operand tiles
+      uint32_t wp[16], wd[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        float d0, d1;
+        f2_unpack(f2_mul(f2_pack(sv[i], sv[i + 1]), f2_pack(dv[i], dv[i + 1])), d0, d1);
+        wd[i >> 1] = pack_bf16(d0, d1);
+        if (MODE == 0) wp[i >> 1] = pack_bf16(sv[i], sv[i + 1]);
+      }
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        st_tile_chunk(sDS, r, c0 + 8 * g, wd + 4 * g);
+        if (MODE == 0) st_tile_chunk(sPT, r, c0 + 8 * g, wp + 4 * g);
       }
       fence_async_smem();
       tc_fence_before();
@@ -224,8 +247,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
       tc_fence_after();
       const bool row_ok = grow < seg_e;
       const long o = long(grow) * p.ldo + head * p.hd;
+      // the two warps of a lane quarter take alternating 16-column groups of the accumulators
 #pragma unroll
-      for (int c = 0; c < HDN; c += 16) {
+      for (int c = 16 * half; c < HDN; c += 32) {
+        if (c >= p.hd) break;
         float a1[16], a2[16];
         tmem_ld16(tA1 + lane_off + c, a1);
         if (MODE == 0) tmem_ld16(tA2 + lane_off + c, a2);
@@ -308,14 +333,17 @@ int nb_flash_bwd(const NbFlashBwdArgs* a, cudaStream_t stream) {
   p.scale = a->scale; p.scale_log2 = a->scale * 1.4426950408889634f;
   p.lse = a->lse; p.delta = a->delta; p.ldo = a->ld_dqkv; p.status = a->status;
   const int nkb = (a->hd + 63) / 64;
-  p.stages = nkb == 1 ? 2 : 1;
-  const size_t smem = size_t(nkb) * (2 * 16384 + 2 * p.stages * 8192) + 32768 + 1024;
+  // Streamed-tile ring: two stages next to the two 16 KB operand tiles of the dK/dV pass, three in the dQ pass, which
+  // has no P^T tile (both sized so that two CTAs of head dims <= 64 share an SM)
   dim3 grid(a->max_tiles, a->H);
+  size_t smem = 0;
 #define NB_LAUNCH(MODE, HDN, R1, R2, X1, X2)                                                                        \
   do {                                                                                                               \
     static SmemAttr attr;                                                                                            \
+    p.stages = nkb == 1 ? (MODE == 0 ? 2 : 3) : 1;                                                                   \
+    smem = size_t(nkb) * (2 * 16384 + 2 * p.stages * 8192) + (MODE == 0 ? 32768 : 16384) + 1024;                     \
     if (int e = attr.ensure(flash_bwd_kernel<MODE, HDN>, smem)) return e;                                            \
-    flash_bwd_kernel<MODE, HDN><<<grid, 192, smem, stream>>>(R1, R2, X1, X2, p);                                     \
+    flash_bwd_kernel<MODE, HDN><<<grid, 320, smem, stream>>>(R1, R2, X1, X2, p);                                     \
   } while (0)
   p.out1 = reinterpret_cast<__nv_bfloat16*>(a->dK); p.out2 = reinterpret_cast<__nv_bfloat16*>(a->dV);
   if (a->hd <= 64) NB_LAUNCH(0, 64, tk, tv, xq, xdo); else NB_LAUNCH(0, 128, tk, tv, xq, xdo);

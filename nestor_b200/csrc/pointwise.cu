@@ -75,18 +75,34 @@ __global__ void combine_rows_kernel(const __nv_bfloat16* __restrict__ y, long ld
 //   dy[r, :] = bf16(g[s / group, :] * w[s]);   dw[s] = <g[s / group, :], y[r, :]>
 __global__ void combine_bwd_kernel(const float* __restrict__ g, long ldg, const __nv_bfloat16* __restrict__ y, long ldy,
                                    const int* __restrict__ slot_of_row, const float* __restrict__ w, int group,
-                                   __nv_bfloat16* __restrict__ dy, long lddy, float* __restrict__ dw, int rows, int d) {
+                                   __nv_bfloat16* __restrict__ dy, long lddy, float* __restrict__ dw, int rows, int d,
+                                   const float* __restrict__ g2, const float* __restrict__ g3, long ldg2, int g2_div,
+                                   float g2_scale) {
   int r = blockIdx.x * blockDim.y + threadIdx.y;
   if (r >= rows) return;
   int s = slot_of_row[r];
   float ww = w ? w[s] : 1.f;
   const float* gr = g + long(s / group) * ldg;
+  // optional second gradient of the same output, shared by `g2_div` consecutive slots (the mean over a token's slots
+  // that feeds the next depth read): added here instead of by a separate pass over the [slots, d] gradient
+  const float* g2r = g2 ? g2 + long(s / g2_div) * ldg2 : nullptr;
+  const float* g3r = g3 ? g3 + long(s / g2_div) * ldg2 : nullptr;
   const __nv_bfloat16* yr = y + long(r) * ldy;
   __nv_bfloat16* dr = dy + long(r) * lddy;
   float dot = 0.f;
   for (int c = threadIdx.x * 8; c < d; c += 32 * 8) {
     float4 a = *reinterpret_cast<const float4*>(gr + c), b = *reinterpret_cast<const float4*>(gr + c + 4);
     float gv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    if (g2r) {
+      float4 e = *reinterpret_cast<const float4*>(g2r + c), f = *reinterpret_cast<const float4*>(g2r + c + 4);
+      gv[0] += e.x * g2_scale; gv[1] += e.y * g2_scale; gv[2] += e.z * g2_scale; gv[3] += e.w * g2_scale;
+      gv[4] += f.x * g2_scale; gv[5] += f.y * g2_scale; gv[6] += f.z * g2_scale; gv[7] += f.w * g2_scale;
+    }
+    if (g3r) {
+      float4 e = *reinterpret_cast<const float4*>(g3r + c), f = *reinterpret_cast<const float4*>(g3r + c + 4);
+      gv[0] += e.x * g2_scale; gv[1] += e.y * g2_scale; gv[2] += e.z * g2_scale; gv[3] += e.w * g2_scale;
+      gv[4] += f.x * g2_scale; gv[5] += f.y * g2_scale; gv[6] += f.z * g2_scale; gv[7] += f.w * g2_scale;
+    }
     uint32_t o[4];
     if (dw) {
       uint4 q = *reinterpret_cast<const uint4*>(yr + c);
@@ -274,6 +290,18 @@ __global__ void depth_read_norm_fwd_kernel(SourceList src, int n, const float* _
 
 }  // namespace nb
 
+// SM count of the current device (grids of the grid-stride kernels are sized from it).
+static int nb_pointwise_sms() {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 1;
+  }
+  return sms;
+}
+
 extern "C" {
 
 int nb_gather_rows(const void* src, int src_is_f32, long lds, const int* idx, int div, void* out, long ldo, int rows,
@@ -298,11 +326,12 @@ int nb_combine_rows(const void* y, long ldy, const int* idx, const float* w, int
 }
 
 int nb_combine_bwd(const float* g, long ldg, const void* y, long ldy, const int* slot_of_row, const float* w, int group,
-                   void* dy, long lddy, float* dw, int rows, int d, cudaStream_t st) {
-  if (d % 8) return -1;
+                   void* dy, long lddy, float* dw, int rows, int d, const float* g2, const float* g3, long ldg2, int g2_div,
+                   float g2_scale, cudaStream_t st) {
+  if (d % 8 || ((g2 || g3) && g2_div < 1)) return -1;
   dim3 block(32, 8), grid((rows + 7) / 8);
   nb::combine_bwd_kernel<<<grid, block, 0, st>>>(g, ldg, (const __nv_bfloat16*)y, ldy, slot_of_row, w, group,
-                                                (__nv_bfloat16*)dy, lddy, dw, rows, d);
+                                                (__nv_bfloat16*)dy, lddy, dw, rows, d, g2, g3, ldg2, g2_div, g2_scale);
   return int(cudaGetLastError());
 }
 
@@ -312,7 +341,8 @@ int nb_repack_heads(const void* src, long ld_src, void* dst, long ld_dst, int ro
   if ((hs | hd | dst_cols) & 1 || dst_cols < nheads * hd || (ld_src & 1) || (ld_dst & 1) || rows < 0) return -1;
   if (rows == 0) return 0;
   long n = long(rows) * (dst_cols / 2);
-  int blocks = int(n / 256 + 1 < 148 * 16 ? n / 256 + 1 : 148 * 16);
+  const long cap = long(nb_pointwise_sms()) * 16;
+  int blocks = int(n / 256 + 1 < cap ? n / 256 + 1 : cap);
   nb::repack_heads_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)src, ld_src, (__nv_bfloat16*)dst, ld_dst, rows,
                                                   nheads, hs, hd, dst_cols);
   return int(cudaGetLastError());
@@ -554,13 +584,13 @@ extern "C" int nb_depth_read_norm_bwd(const float* const* sources, float* const*
                                       const float* gains, const float* gamma, const float* stats, const float* rstd,
                                       const void* dn, const float* dh, float* dquery, float* dgains, float* dgamma, int T,
                                       int d, unsigned long long acc_mask, float* scratch, cudaStream_t st) {
-  // scratch: fp32 [1184 * (2d + 64)] per-block partial sums of the parameter gradients
+  // scratch: fp32 [8 * SMs * (2d + 64)] per-block partial sums of the parameter gradients
   if (n < 1 || n > nb::kMaxSources || d % 4 || d > nb::kMaxDepthDim || !scratch) return -1;
   nb::SourceList sl; nb::GradList gl;
   for (int i = 0; i < n; ++i) { sl.ptr[i] = sources[i]; gl.ptr[i] = dsources[i]; }
   dim3 block(32, 4);
   int blocks = (T + 3) / 4;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > nb_pointwise_sms() * 8) blocks = nb_pointwise_sms() * 8;
   int nv = (d / 4 + 31) / 32;
 #define NB_DRB(NV) nb::depth_read_norm_bwd_kernel<NV><<<blocks, block, 0, st>>>(sl, gl, n, query, gains, gamma, stats, rstd, \
       (const __nv_bfloat16*)dn, dh, scratch, dgamma != nullptr, T, d, acc_mask)
@@ -619,7 +649,8 @@ __global__ void layer_combine_kernel(const float4* __restrict__ attn, const floa
   running_out[i] = running ? f4add(running[i], mean) : mean;
 }
 
-// Backward: du[t,j] = ds[t,j] + dr[t]/k;  d_attn = du;  d_priv = p1*du;  d_pub = p0*sum_j du;
+// Backward: du[t,j] = ds[t,j] + dr[t]/k;  d_attn = du (optional: a consumer that can add dr[t]/k itself reads ds);
+// d_priv = p1*du;  d_pub = p0*sum_j du;
 // d_path (per token, warp-reduced over d): dp1 = sum_{j,c} du*priv, dp0 = sum_c (sum_j du)*pub. One warp per token.
 __global__ void layer_combine_bwd_kernel(const float* __restrict__ ds, const float* __restrict__ dr,
                                          const float* __restrict__ priv, const float* __restrict__ pub,
@@ -639,7 +670,7 @@ __global__ void layer_combine_bwd_kernel(const float* __restrict__ ds, const flo
     for (int j = 0; j < k; ++j) {
       long o = (long(t) * k + j) * d + c;
       float4 u = ds ? f4add(*reinterpret_cast<const float4*>(ds + o), r) : r;
-      *reinterpret_cast<float4*>(d_attn + o) = u;
+      if (d_attn) *reinterpret_cast<float4*>(d_attn + o) = u;
       sum = f4add(sum, u);
       if (priv) {
         float4 pv = *reinterpret_cast<const float4*>(priv + o);

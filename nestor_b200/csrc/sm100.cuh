@@ -296,6 +296,74 @@ __device__ __forceinline__ uint64_t sdesc_mnmajor(uint32_t saddr, uint32_t atom_
   return make_sdesc(saddr, atom_bytes, 1024);
 }
 
+// Packed fp32 pairs (sm_100 runs add / mul / fma on two floats per instruction) and the three-input maximum.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+// Which tile of a packed-segment problem a CTA owns. Tiles of `tile_rows` rows are numbered segment by segment; a
+// whole warp calls this (lanes read 32 segment bounds at a time and scan their tile counts), so the look-up costs
+// one or two coalesced loads instead of a serial walk over the segment table. Returns false when `tile` is past
+// the last tile. `local` is the tile's index inside its segment, `ntiles` that segment's tile count.
+__device__ __forceinline__ bool find_segment_tile(const int* __restrict__ seg_start, int nseg, int tile_rows, int tile,
+                                                  int& seg_b, int& seg_e, int& local, int& ntiles) {
+  const int lane = threadIdx.x & 31;
+  int base = 0;
+  for (int s0 = 0; s0 < nseg; s0 += 32) {
+    const int s = s0 + lane;
+    const int b = s < nseg ? seg_start[s] : 0, e = s < nseg ? seg_start[s + 1] : 0;
+    const int nt = s < nseg ? (e - b + tile_rows - 1) / tile_rows : 0;
+    int incl = nt;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += o;
+    }
+    const int excl = base + incl - nt;
+    const unsigned hit = __ballot_sync(0xffffffffu, nt > 0 && tile >= excl && tile < excl + nt);
+    if (hit) {
+      const int src = __ffs(hit) - 1;
+      seg_b = __shfl_sync(0xffffffffu, b, src);
+      seg_e = __shfl_sync(0xffffffffu, e, src);
+      local = tile - __shfl_sync(0xffffffffu, excl, src);
+      ntiles = __shfl_sync(0xffffffffu, nt, src);
+      return true;
+    }
+    base += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  return false;
+}
+
 // Host side: the dynamic shared-memory limit of a kernel is a per-device attribute. One instance per kernel
 // instantiation remembers, for every device, the largest size already granted, and raises it when a launch
 // needs more (racing threads set the same value twice, which is harmless).

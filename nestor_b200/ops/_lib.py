@@ -56,6 +56,18 @@ def lib() -> C.CDLL:
     return _LIB
 
 
+_sms: dict[int, int] = {}
+
+
+def sm_count(device: torch.device | None = None) -> int:
+    """Streaming multiprocessors of ``device`` (grids and split factors are sized from it)."""
+
+    idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+    if idx not in _sms:
+        _sms[idx] = int(torch.cuda.get_device_properties(idx).multi_processor_count)
+    return _sms[idx]
+
+
 def stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
 

@@ -35,7 +35,7 @@ def _L():
         vp, i, l, f = C.c_void_p, C.c_int, C.c_long, C.c_float
         L.nb_gather_rows.argtypes = [vp, i, l, vp, i, vp, l, i, i, vp]
         L.nb_combine_rows.argtypes = [vp, l, vp, vp, i, vp, l, i, i, i, i, vp]
-        L.nb_combine_bwd.argtypes = [vp, l, vp, l, vp, vp, i, vp, l, vp, i, i, vp]
+        L.nb_combine_bwd.argtypes = [vp, l, vp, l, vp, vp, i, vp, l, vp, i, i, vp, vp, l, i, f, vp]
         L.nb_rope.argtypes = [vp, l, vp, i, i, i, i, f, f, vp]
         L.nb_repack_heads.argtypes = [vp, l, vp, l, i, i, i, i, i, vp]
         L.nb_repack_heads.restype = C.c_int
@@ -106,12 +106,23 @@ def combine_rows(y: Tensor, idx: Tensor, w: Tensor | None, group: int, n_out: in
 
 
 def combine_bwd(g: Tensor, y: Tensor, slot_of_row: Tensor, w: Tensor | None, group: int,
-                need_dw: bool) -> tuple[Tensor, Tensor | None]:
+                need_dw: bool, shared: tuple = (), shared_div: int = 1,
+                shared_scale: float = 1.0) -> tuple[Tensor, Tensor | None]:
+    """Backward of ``combine_rows``. ``shared`` holds up to two ``[n, d]`` fp32 tensors: extra gradients of the
+    combined output that ``shared_div`` consecutive slots have in common, added as
+    ``shared[i][slot // shared_div] * shared_scale``."""
+
+    shared = [t for t in shared if t is not None]
+    sh0 = shared[0] if len(shared) > 0 else None
+    sh1 = shared[1] if len(shared) > 1 else None
+    assert sh1 is None or sh1.stride(0) == sh0.stride(0)
+
     rows, d = y.shape
     dy = torch.empty(rows, d, dtype=BF16, device=y.device)
     dw = torch.empty(rows, dtype=torch.float32, device=y.device) if need_dw else None
     _ck(_L().nb_combine_bwd(g.data_ptr(), g.stride(0), y.data_ptr(), y.stride(0), slot_of_row.data_ptr(), _ptr(w), group,
-                            dy.data_ptr(), d, _ptr(dw), rows, d, _st()), "combine_bwd")
+                            dy.data_ptr(), d, _ptr(dw), rows, d, _ptr(sh0), _ptr(sh1), sh0.stride(0) if sh0 is not None else 0,
+                            shared_div, float(shared_scale), _st()), "combine_bwd")
     return dy, dw
 
 
@@ -263,6 +274,19 @@ def dense_swiglu(x, w_up, w_gate, w_down, cd):
 
 
 # ------------------------------------------------------------------------- attention
+class _MidState:
+    """Where the two consumers of an attention output leave the part of its gradient that is one ``[T, d]`` row per
+    token, spread over the token's ``k`` slots with weight ``1/k``: ``grad`` from ``mid_source`` (the slot mean that
+    feeds the next depth read), ``grad_running`` from ``layer_combine`` (the running mean). The attention backward
+    adds both while it gathers rows, so neither is ever expanded to ``[T, k, d]``."""
+
+    __slots__ = ("grad", "grad_running")
+
+    def __init__(self) -> None:
+        self.grad = None
+        self.grad_running = None
+
+
 class _Attention(torch.autograd.Function):
     """Packed varlen attention between the normed stream ``n [T, d]`` and gated slot updates."""
 
@@ -273,7 +297,8 @@ class _Attention(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, n, gates, wqkv, wo, tok_of_row, row_of_slot, slot_of_row_flat, pos_of_row, seg_start, col_start,
-                groups, k, heads, head_dim, rope_base):
+                groups, k, heads, head_dim, rope_base, mid_state=None):
+        ctx.mid_state = mid_state
         T, d = n.shape
         inner = heads * head_dim
         hdp = -(-head_dim // 8) * 8
@@ -311,7 +336,14 @@ class _Attention(torch.autograd.Function):
         d = y.shape[1]
         rows = x.shape[0]
         g2 = dout.contiguous().view(-1, d).float()
-        dy, dg_sorted = combine_bwd(g2, y, slot_of_row_flat, gf, 1, need_dw=ctx.needs_input_grad[1])
+        # the gradient that reached this output through the slot mean (``mid_source``) was left in the shared state by
+        # that node's backward; it is the same [T, d] row for the k slots of a token
+        g_mid = g_run = None
+        if ctx.mid_state is not None:
+            g_mid, ctx.mid_state.grad = ctx.mid_state.grad, None
+            g_run, ctx.mid_state.grad_running = ctx.mid_state.grad_running, None
+        dy, dg_sorted = combine_bwd(g2, y, slot_of_row_flat, gf, 1, need_dw=ctx.needs_input_grad[1],
+                                    shared=(g_mid, g_run), shared_div=k, shared_scale=1.0 / k)
         wq_ref, wo_ref = ctx.w_refs
         do = G.gemm_rows(dy, wo_use, offsets=col_start, groups=groups, b_mn=True, n=inner8,
                          out=G.rows_buffer(rows, inner8, BF16, dy.device))                     # wo [G, K=d, N=inner]
@@ -344,7 +376,7 @@ class _Attention(torch.autograd.Function):
         dgates = None
         if dg_sorted is not None:
             dgates = dg_sorted.view(T, k).to(g_dtype)
-        return (dn, dgates, d_wqkv, d_wo) + (None,) * 11
+        return (dn, dgates, d_wqkv, d_wo) + (None,) * 12
 
 
 def column_attention(n, plan: ColumnPlan, gates, wqkv, wo, heads, head_dim, rope_base, cd):
@@ -352,8 +384,12 @@ def column_attention(n, plan: ColumnPlan, gates, wqkv, wo, heads, head_dim, rope
     if slot_flat is None:   # flat (token*k + slot) index of every packed row
         slot_flat = (plan.tok_of_row * plan.k + plan.slot_of_row).contiguous()
         plan.extra["slot_flat"] = slot_flat
-    return _Attention.apply(n, gates, wqkv, wo, plan.tok_of_row, plan.row_of_slot, slot_flat, plan.pos_of_row,
-                            plan.seg_start, plan.col_start, plan.G, plan.k, heads, head_dim, rope_base)
+    state = _MidState() if torch.is_grad_enabled() else None
+    out = _Attention.apply(n, gates, wqkv, wo, plan.tok_of_row, plan.row_of_slot, slot_flat, plan.pos_of_row,
+                           plan.seg_start, plan.col_start, plan.G, plan.k, heads, head_dim, rope_base, state)
+    if state is not None:
+        out._nb_mid_state = state     # picked up by mid_source: its gradient for this tensor travels through the state
+    return out
 
 
 _dense_plans: dict = {}
@@ -429,9 +465,10 @@ class _HeadCE(torch.autograd.Function):
         return d_hidden, d_weight, None, None, None, None
 
 
-def _one_wave_bn(rows: int, n: int, sms: int = 148) -> int | None:
+def _one_wave_bn(rows: int, n: int, sms: int | None = None) -> int | None:
     """Widest 64-multiple tile width whose tile count still fits one wave of CTAs (long-K products)."""
 
+    sms = _lib.sm_count() if sms is None else sms
     m_tiles = -(-rows // 128)
     best = None
     for bn in (64, 128, 192, 256):
@@ -534,7 +571,7 @@ class _DepthReadNorm(torch.autograd.Function):
         dq = torch.empty(d, dtype=torch.float32, device=dn.device)
         dg = torch.zeros(ctx.n_gains, dtype=torch.float32, device=dn.device)     # gains past the n sources read get no gradient
         dw = torch.empty(d, dtype=torch.float32, device=dn.device)
-        scratch = torch.empty(1184 * (2 * d + 64), dtype=torch.float32, device=dn.device)
+        scratch = torch.empty(8 * _lib.sm_count(dn.device) * (2 * d + 64), dtype=torch.float32, device=dn.device)
         dnb = dn if (dn.dtype == BF16 and dn.is_contiguous()) else dn.to(BF16).contiguous()
         _ck(_L().nb_depth_read_norm_bwd(_ptr_array(srcs), _ptr_array(outs), n, q32.data_ptr(),
                                         g32.data_ptr(), w32.data_ptr(), stats.data_ptr(), rstd.data_ptr(), dnb.data_ptr(),
@@ -560,8 +597,14 @@ def _f32c(t):
 
 
 class _MidSource(torch.autograd.Function):
+    """``running + mean_j attn_j``. The attention output has a second consumer (``layer_combine``), so autograd would
+    add this node's broadcast gradient ``g / k`` to the other one with a pass over ``[T, k, d]``. When the attention
+    op offers a shared state, the ``[T, d]`` gradient is parked there instead and the attention backward, which
+    autograd runs after both consumers, adds it while it gathers its rows."""
+
     @staticmethod
-    def forward(ctx, running, attn):
+    def forward(ctx, running, attn, state=None):
+        ctx.state = state
         T, k, d = attn.shape
         a = _f32c(attn)
         r = None if running is None else _f32c(running)
@@ -575,16 +618,20 @@ class _MidSource(torch.autograd.Function):
     def backward(ctx, g):
         k = ctx.k
         d_run = g if ctx.has_running and ctx.needs_input_grad[0] else None
-        return d_run, (g * (1.0 / k)).unsqueeze(1).expand(-1, k, -1)
+        if ctx.state is not None:
+            ctx.state.grad = g if g.is_contiguous() else g.contiguous()
+            return d_run, None, None
+        return d_run, (g * (1.0 / k)).unsqueeze(1).expand(-1, k, -1), None
 
 
 def mid_source(running, attn):
-    return _MidSource.apply(running, attn)
+    return _MidSource.apply(running, attn, getattr(attn, "_nb_mid_state", None))
 
 
 class _LayerCombine(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, attn, priv, pub, path, streams, running):
+    def forward(ctx, attn, priv, pub, path, streams, running, attn_state=None):
+        ctx.attn_state = attn_state
         T, k, d = attn.shape
         a, pb = _f32c(attn), _f32c(pub)
         pv = None if priv is None else _f32c(priv)
@@ -607,17 +654,23 @@ class _LayerCombine(torch.autograd.Function):
         dev = pb.device
         ds_c = None if ds is None else _f32c(ds)
         dr_c = None if dr is None else _f32c(dr)
-        d_attn = torch.empty(T, k, d, dtype=torch.float32, device=dev)
+        # d_attn = ds + dr / k. When the attention op offers its shared state, ds itself is handed on as the gradient
+        # and dr is parked for the attention backward to add, which saves writing (and re-reading) a [T, k, d] tensor
+        park = ctx.attn_state is not None and ds_c is not None
+        d_attn = None if park else torch.empty(T, k, d, dtype=torch.float32, device=dev)
         d_priv = torch.empty(T, k, d, dtype=torch.float32, device=dev) if pv is not None else None
         d_pub = torch.empty(T, d, dtype=torch.float32, device=dev)
         d_path = torch.empty(T, 2, dtype=torch.float32, device=dev) if ph is not None else None
-        _ck(_L().nb_layer_combine_bwd(_ptr(ds_c), _ptr(dr_c), _ptr(pv), pb.data_ptr(), _ptr(ph), d_attn.data_ptr(),
+        _ck(_L().nb_layer_combine_bwd(_ptr(ds_c), _ptr(dr_c), _ptr(pv), pb.data_ptr(), _ptr(ph), _ptr(d_attn),
                                       _ptr(d_priv), d_pub.data_ptr(), _ptr(d_path), T, d, k, _st()), "layer_combine_bwd")
-        return (d_attn, d_priv, d_pub, d_path, ds if ctx.has_state[0] else None, dr if ctx.has_state[1] else None)
+        if park:
+            ctx.attn_state.grad_running = dr_c
+            d_attn = ds_c
+        return (d_attn, d_priv, d_pub, d_path, ds if ctx.has_state[0] else None, dr if ctx.has_state[1] else None, None)
 
 
 def layer_combine(attn, priv, pub, path, streams, running, cd):
-    return _LayerCombine.apply(attn, priv, pub, path, streams, running)
+    return _LayerCombine.apply(attn, priv, pub, path, streams, running, getattr(attn, "_nb_mid_state", None))
 
 
 class _BlockExit(torch.autograd.Function):

@@ -241,8 +241,8 @@ def gemm_reduce(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: 
     tiles = groups * -(-M // 128) * -(-N // bn)
     kblocks = max(1, rows // (64 * groups))
     a.splits = 1
-    if epilogue == ACCUM_F32 and tiles < 120:
-        a.splits = max(1, min(148 // tiles, kblocks // 4))
+    if epilogue == ACCUM_F32 and tiles < (_lib.sm_count(A.device) * 13) // 16:
+        a.splits = max(1, min(_lib.sm_count(A.device) // tiles, kblocks // 4))
     a.status = _lib.status_word(A.device).data_ptr()
     a.max_m_tiles = 0
     a.sms = sms

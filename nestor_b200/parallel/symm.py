@@ -22,8 +22,21 @@ import torch.distributed as dist
 from nestor_b200.ops import _lib
 
 MAX_WORLD = 8
-MAX_BLOCKS = 148
 PHASES = 4
+
+
+def max_blocks() -> int:
+    """Upper bound on the blocks of a collective launch: one per SM of this device."""
+
+    return int(_L().nb_comm_max_blocks())
+
+
+def nvls_wanted() -> bool:
+    """``NESTOR_B200_NVLS``: ``auto`` (default) uses the NVLink multicast mapping whenever the symmetric buffers have
+    one, ``0`` keeps every collective on plain peer loads and stores (failure-handling tests run that way: a rank must
+    never die while its memory is bound to a multicast object)."""
+
+    return os.environ.get("NESTOR_B200_NVLS", "auto") != "0"
 
 
 class PeerTimeout(RuntimeError):
@@ -48,7 +61,12 @@ def _L():
         L.nb_reduce_scatter_push.restype = C.c_int
         L.nb_param_push.argtypes = [C.POINTER(Peers), l, l, u, l, i, vp, vp]
         L.nb_wait_timeout_probe.argtypes = [vp, u, l, vp, vp]
-        for fn in (L.nb_allreduce_push, L.nb_param_push, L.nb_wait_timeout_probe):
+        L.nb_allreduce_nvls.argtypes = [C.POINTER(Peers), vp, vp, l, l, f, i, u, l, i, vp, vp]
+        L.nb_reduce_scatter_nvls.argtypes = [C.POINTER(Peers), vp, l, l, f, i, u, l, i, vp, vp]
+        L.nb_param_push_nvls.argtypes = [C.POINTER(Peers), vp, vp, l, l, u, l, i, vp, vp]
+        L.nb_comm_max_blocks.argtypes = []
+        for fn in (L.nb_allreduce_push, L.nb_param_push, L.nb_wait_timeout_probe, L.nb_allreduce_nvls,
+                   L.nb_reduce_scatter_nvls, L.nb_param_push_nvls, L.nb_comm_max_blocks):
             fn.restype = C.c_int
         _protos = True
     return L
@@ -88,7 +106,7 @@ class PeerGroup:
         self.h_main = rendezvous(main)
         self.h_aux = rendezvous(aux) if aux is not None else None
         if PeerGroup._flags is None:
-            flags = symmetric_empty(PHASES * MAX_BLOCKS * MAX_WORLD, torch.int32, main.device)
+            flags = symmetric_empty(PHASES * max_blocks() * MAX_WORLD, torch.int32, main.device)
             flags.zero_()
             torch.cuda.synchronize()
             PeerGroup._flags, PeerGroup._flags_handle = flags, rendezvous(flags)
@@ -99,8 +117,12 @@ class PeerGroup:
             self.peers.aux[r] = int(self.h_aux.buffer_ptrs[r]) if self.h_aux is not None else None
             self.peers.sig[r] = int(PeerGroup._flags_handle.buffer_ptrs[r])
         self.peers.world, self.peers.rank = self.world, self.rank
-        self.blocks = int(os.environ.get("NESTOR_B200_COMM_BLOCKS", "64"))
+        self.blocks = min(int(os.environ.get("NESTOR_B200_COMM_BLOCKS", "64")), max_blocks())
         self.status = _lib.status_word(main.device)
+        # NVLink multicast addresses of the two buffers (0 when the fabric or the allocation has none)
+        self.mc_main = int(getattr(self.h_main, "multicast_ptr", 0) or 0) if nvls_wanted() else 0
+        self.mc_aux = (int(getattr(self.h_aux, "multicast_ptr", 0) or 0) if self.h_aux is not None else 0) if nvls_wanted() else 0
+        self.nvls = bool(self.mc_main) and (self.h_aux is None or bool(self.mc_aux))
 
     @classmethod
     def next_epoch(cls) -> int:
@@ -129,10 +151,14 @@ class FusedAllReduce:
         budget = wait_budget()
         for off, n in self.buckets:
             n4 = (n // 4) * 4
-            rc = _L().nb_allreduce_push(C.byref(g.peers), off, n4, scale, int(self.mirror), PeerGroup.next_epoch(), budget,
-                                        g.blocks, g.status.data_ptr(), st)
+            if g.nvls:
+                rc = _L().nb_allreduce_nvls(C.byref(g.peers), g.mc_main, g.mc_aux or None, off, n4, scale, int(self.mirror),
+                                            PeerGroup.next_epoch(), budget, g.blocks, g.status.data_ptr(), st)
+            else:
+                rc = _L().nb_allreduce_push(C.byref(g.peers), off, n4, scale, int(self.mirror), PeerGroup.next_epoch(), budget,
+                                            g.blocks, g.status.data_ptr(), st)
             if rc != 0:
-                raise RuntimeError(f"nb_allreduce_push failed with code {rc}")
+                raise RuntimeError(f"fused all-reduce launch failed with code {rc}")
             _lib.count_launch()
             if n4 != n:   # ragged tail (arena sizes are multiples of 64, so this is for ad-hoc buffers only)
                 tail = g.main[off + n4 : off + n]
@@ -151,10 +177,14 @@ class FusedReduceScatter:
     def run(self, lo: int, hi: int, scale: float) -> None:
         g = self.group
         assert lo % 4 == 0 and hi % 4 == 0
-        rc = _L().nb_reduce_scatter_push(C.byref(g.peers), lo, hi, scale, int(self.mirror), PeerGroup.next_epoch(),
-                                         wait_budget(), g.blocks, g.status.data_ptr(), C.c_void_p(_lib.stream_ptr()))
+        if g.nvls:
+            rc = _L().nb_reduce_scatter_nvls(C.byref(g.peers), g.mc_main, lo, hi, scale, int(self.mirror), PeerGroup.next_epoch(),
+                                             wait_budget(), g.blocks, g.status.data_ptr(), C.c_void_p(_lib.stream_ptr()))
+        else:
+            rc = _L().nb_reduce_scatter_push(C.byref(g.peers), lo, hi, scale, int(self.mirror), PeerGroup.next_epoch(),
+                                             wait_budget(), g.blocks, g.status.data_ptr(), C.c_void_p(_lib.stream_ptr()))
         if rc != 0:
-            raise RuntimeError(f"nb_reduce_scatter_push failed with code {rc}")
+            raise RuntimeError(f"fused reduce-scatter launch failed with code {rc}")
         _lib.count_launch()
 
 
@@ -167,10 +197,14 @@ class ParamPush:
     @torch.no_grad()
     def run(self, lo: int, hi: int) -> None:
         g = self.group
-        rc = _L().nb_param_push(C.byref(g.peers), lo, hi, PeerGroup.next_epoch(), wait_budget(), g.blocks,
-                                g.status.data_ptr(), C.c_void_p(_lib.stream_ptr()))
+        if g.nvls:
+            rc = _L().nb_param_push_nvls(C.byref(g.peers), g.mc_main, g.mc_aux or None, lo, hi, PeerGroup.next_epoch(),
+                                         wait_budget(), g.blocks, g.status.data_ptr(), C.c_void_p(_lib.stream_ptr()))
+        else:
+            rc = _L().nb_param_push(C.byref(g.peers), lo, hi, PeerGroup.next_epoch(), wait_budget(), g.blocks,
+                                    g.status.data_ptr(), C.c_void_p(_lib.stream_ptr()))
         if rc != 0:
-            raise RuntimeError(f"nb_param_push failed with code {rc}")
+            raise RuntimeError(f"fused parameter push launch failed with code {rc}")
         _lib.count_launch()
 
 

@@ -3,7 +3,7 @@
 ``python -m nestor_b200.scripts.bench_kernels [case ...] [--reps N]`` prints one line per kernel launch
 shape: time, achieved TFLOP/s or GB/s and the fraction of the measured peaks in ``MEASURED_PEAKS.json``
 (fallback 1590 TFLOP/s, 6650 GB/s). Cases: ``gemm`` (expert / attention / head GEMMs of nestor_200m),
-``flash``, ``depth``, ``small`` (one launch of each, sized for a profiler capture). Inputs are larger
+``flash``, ``depth``, ``ns`` (Newton-Schulz), ``small`` (one launch of each, sized for a profiler capture). Inputs are larger
 than the 126 MB L2 or an L2 flush is written between repetitions.
 """
 
@@ -139,6 +139,20 @@ def case_depth(reps: int, small: bool = False) -> None:
                nbytes=(n * 8 + 2) * T * d)
 
 
+def case_ns(reps: int, small: bool = False) -> None:
+    """Newton-Schulz (5 iterations) on the Muon shape buckets of nestor_200m: the tcgen05 grouped-GEMM path against
+    the same iteration on ``torch.bmm`` (the PyTorch statement of the op)."""
+
+    from nestor_b200.ops import cuda as K, reference as R
+    shapes = [(8, 200, 640)] if small else [(96, 200, 640), (96, 640, 200), (408, 640, 640), (512, 640, 216), (512, 216, 640), (7, 128, 640)]
+    for bt, m, n in shapes:
+        g = torch.randn(bt, m, n, device="cuda")
+        r, c = min(m, n), max(m, n)
+        fl = 5.0 * bt * (4.0 * r * r * c + 2.0 * r ** 3)
+        report(f"newton-schulz x5 tcgen05 [{bt},{m},{n}]", timed(lambda: K.newton_schulz(g, 5, out_dtype=BF), reps, flush=False), fl)
+        report(f"newton-schulz x5 torch.bmm [{bt},{m},{n}]", timed(lambda: R.newton_schulz(g, 5, out_dtype=BF), reps, flush=False), fl)
+
+
 def case_gather(reps: int, small: bool = False) -> None:
     """Cost of the staging mechanism of the fused all-gather GEMM by itself: every "rank" is this GPU.
 
@@ -188,7 +202,7 @@ def main(argv: list[str] | None = None) -> None:
         if c == "small":
             case_gemm(a.reps, small=True); case_flash(a.reps, small=True); case_depth(a.reps, small=True)
         else:
-            {"gemm": case_gemm, "flash": case_flash, "depth": case_depth, "gather": case_gather}[c](a.reps)
+            {"gemm": case_gemm, "flash": case_flash, "depth": case_depth, "gather": case_gather, "ns": case_ns}[c](a.reps)
     from nestor_b200.ops import _lib
     _lib.check_status(torch.device("cuda"))
 
