@@ -219,6 +219,23 @@ def run_ours(a: argparse.Namespace) -> dict:
     clocks = sampler.stop() if rank == 0 else {}
     ms_e2e = _max_over_ranks(f0.elapsed_time(f1), device)
 
+    # Where a step's time goes beyond its micro-batches (untimed extra steps): the micro-batch alone, then one step
+    # with an event at every phase boundary of the optimizer step. "exposed" = step - accum x micro-batch.
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    _bracket(device)
+    g0.record()
+    for b in resident:
+        trainer.train_step((b[0], b[0]))
+    g1.record()
+    _bracket(device)
+    ms_micro = _max_over_ranks(g0.elapsed_time(g1), device) / accum
+    trainer.phase_events = []
+    trainer.update_weights({})
+    phases = {k: _max_over_ranks(v, device) for k, v in trainer.phase_times_ms().items()}
+    trainer.phase_events = None
+    comm_ms = phases.get("grad_reduce", 0.0) + phases.get("param_push", 0.0)
+    exposed = ms_dev / a.steps - accum * ms_micro
+
     tokens = TOKENS_PER_STEP * a.steps
     value = tokens / (ms_dev / 1e3)
     h2d = accum * SEQS_PER_GPU * SEQ_LEN * 8
@@ -236,6 +253,8 @@ def run_ours(a: argparse.Namespace) -> dict:
         "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / a.steps,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "last_loss": last_loss},
         "gpu_launches": launches, "clocks": clocks,
+        "step_breakdown_ms": {"micro_batch": ms_micro, "outside_micro_batches": exposed, "exposed_comm_ms": comm_ms if world > 1 else 0.0,
+                              **{f"update_{k}": v for k, v in phases.items()}},
     }
 
 

@@ -81,7 +81,7 @@ allreduce_push_kernel(Peers P, long offset, long numel, float scale, int write_m
   const long lo = store_all ? per * P.rank : own_lo / 4, hi = store_all ? min(n4, lo + per) : own_hi / 4;
   // kUnroll float4 per thread and iteration: every peer load of the batch is issued before the first add, so
   // (world - 1) * kUnroll NVLink reads are in flight per thread
-  constexpr int kUnroll = 4;
+  constexpr int kUnroll = 8;
   const long stride = long(gridDim.x) * blockDim.x;
   for (long i0 = lo + long(blockIdx.x) * blockDim.x + threadIdx.x; i0 < hi; i0 += stride * kUnroll) {
     float4 acc[kUnroll];
@@ -173,7 +173,7 @@ allreduce_nvls_kernel(Peers P, float* mc_buf, __nv_bfloat16* mc_aux, long offset
   const long n4 = numel / 4;
   const long per = (n4 + P.world - 1) / P.world;
   const long lo = store_all ? per * P.rank : own_lo / 4, hi = store_all ? min(n4, lo + per) : own_hi / 4;
-  constexpr int kUnroll = 4;
+  constexpr int kUnroll = 8;
   const long stride = long(gridDim.x) * blockDim.x;
   float* mine = reinterpret_cast<float*>(P.buf[P.rank]) + offset;
   __nv_bfloat16* mine_aux = reinterpret_cast<__nv_bfloat16*>(P.aux[P.rank]) + offset;

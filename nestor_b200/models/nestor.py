@@ -185,6 +185,44 @@ class Layer(nn.Module):
         return ops.column_attention(n, ctx.plan, ctx.gates, self.qkv_weight(), self.out_weight(),
                                     s.heads, s.head_dim, s.rope_base, cd)
 
+    def attention_step(self, n: Tensor, ctx: "BlockContext", cd: torch.dtype, cache: "LayerKVCache") -> Tensor:
+        """Attention half for ONE new token per sequence (``n [B, d]``) against this layer's key/value cache.
+
+        Slot ``j`` of sequence ``b`` projects with the weights of column ``idx[b, j]``, appends its rotated key and its
+        value to that column's cache and attends over everything the column has seen of the sequence so far, which
+        is exactly the causal row the full forward computes for that token (the members of a column are visited in
+        position order). Returns the gated slot updates ``[B, k, d]`` in fp32.
+        """
+
+        s = self.spec
+        B = n.shape[0]
+        heads, hd, inner = s.heads, s.head_dim, s.heads * s.head_dim
+        wqkv, wo = self.qkv_weight().to(cd), self.out_weight().to(cd)            # [G, 3*inner, d], [G, d, inner]
+        cos, sin = ops.rope_tables(ctx.pos.reshape(-1).clamp_min(0), hd, s.rope_base)
+        x = n.to(cd)
+        rows = torch.arange(B, device=n.device)
+        out = []
+        for j in range(ctx.idx.shape[1]):
+            c = ctx.idx[:, j].long()
+            qkv = torch.einsum("bd,bnd->bn", x, wqkv[c])
+            q = ops.apply_rope(qkv[:, :inner].reshape(B, heads, hd), cos, sin)
+            k = ops.apply_rope(qkv[:, inner : 2 * inner].reshape(B, heads, hd), cos, sin)
+            v = qkv[:, 2 * inner :].reshape(B, heads, hd)
+            at = cache.count[rows, c]
+            if int(at.max()) >= cache.keys.shape[2]:
+                raise ValueError(f"key/value cache of {cache.keys.shape[2]} positions per column is full")
+            cache.keys[rows, c, at] = k.to(cache.keys.dtype)
+            cache.values[rows, c, at] = v.to(cache.values.dtype)
+            cache.count[rows, c] = at + 1
+            K, V = cache.keys[rows, c], cache.values[rows, c]                 # [B, L, H, hd]
+            visible = torch.arange(K.shape[1], device=n.device).unsqueeze(0) <= at.unsqueeze(1)
+            sc = torch.einsum("bhd,blhd->bhl", q.float(), K.float()) / hd
+            p = torch.softmax(sc.masked_fill(~visible.unsqueeze(1), float("-inf")), dim=-1)
+            o = torch.einsum("bhl,blhd->bhd", p.to(cd).float(), V.float()).to(cd).reshape(B, inner)
+            y = torch.einsum("bi,bdi->bd", o, wo[c]).float()
+            out.append(y * ctx.gates[:, j].float().unsqueeze(-1))
+        return torch.stack(out, dim=1)
+
     def experts(self, n: Tensor, ctx: "BlockContext", cd: torch.dtype) -> tuple[Tensor | None, Tensor, Tensor | None, dict]:
         """Expert half: ``(private [T, k, d] | None, shared [T, d], path [T, 2] | None, routing aux)``."""
 
@@ -203,10 +241,29 @@ class Layer(nn.Module):
         ones = torch.ones_like(gate, dtype=cd)
         rows = ops.expert_bank(n, plan, ones, W(self, bank.w_up), W(self, bank.w_gate), W(self, bank.w_down), cd, group=1)
         out = (rows * gate.to(cd).float().unsqueeze(-1)).sum(dim=1).to(cd).float()
-        aux = {"expert_idx": idx}
+        aux = {"expert_idx": idx, "expert_router": {"scores": scores, "topk_indices": idx}}
         if not self.training and not torch.is_grad_enabled():
             aux["expert_prob"] = torch.softmax(scores.float(), dim=-1).sum(0)
         return None, out, None, aux
+
+
+class LayerKVCache:
+    """Keys and values one layer has seen, per sequence and column: ``keys / values [B, G, L, H, hd]`` and the number
+    of entries ``count [B, G]`` (a token only enters the columns it was routed to, so the counts differ)."""
+
+    def __init__(self, B: int, G: int, max_len: int, heads: int, head_dim: int, device, dtype) -> None:
+        self.keys = torch.zeros(B, G, max_len, heads, head_dim, device=device, dtype=dtype)
+        self.values = torch.zeros_like(self.keys)
+        self.count = torch.zeros(B, G, dtype=torch.long, device=device)
+
+
+class NestorKVCache:
+    """Decode state of the whole backbone: one ``LayerKVCache`` per (block, layer)."""
+
+    def __init__(self, backbone: "Nestor", B: int, max_len: int, device, dtype=torch.float32) -> None:
+        self.blocks = [[LayerKVCache(B, blk.spec.G, max_len, blk.spec.heads, blk.spec.head_dim, device, dtype)
+                        for _ in blk.layers] for blk in backbone.blocks]
+        self.length = 0
 
 
 class BlockContext:
@@ -244,11 +301,14 @@ class Block(nn.Module):
             scores = scores + eps * torch.nn.functional.softplus(ops.router_scores(x, W(self, n1), W(self, n2), cd))
         if not self.training and not torch.is_grad_enabled():
             self._last_group_prob = torch.softmax(scores.float(), dim=-1).sum(0)
+        self.__dict__["_last_scores"] = scores       # reported in the block's aux for the auxiliary losses
         return ops.route_topk(scores, r.choice_bias, s.k, "renorm")
 
     def forward(self, x: Tensor, sources: list[Tensor], B: int, S: int, cd: torch.dtype,
-                pos: Tensor | None, column_mode: bool, noise: Tensor | None = None) -> tuple[list[Tensor], Tensor, dict]:
-        """Run the block. ``x [T, d]`` feeds the router; ``sources`` are the completed aggregates.
+                pos: Tensor | None, column_mode: bool, noise: Tensor | None = None,
+                cache: list | None = None) -> tuple[list[Tensor], Tensor, dict]:
+        """Run the block. ``x [T, d]`` feeds the router; ``sources`` are the completed aggregates. With ``cache`` (one
+        ``LayerKVCache`` per layer) the rows are one new token per sequence and attention runs against the cache.
 
         Returns ``(exports, aggregate, aux)``: the depth sources this block contributes (``k``
         deviations then the aggregate in column mode with ``k > 1``; the aggregate alone
@@ -257,16 +317,16 @@ class Block(nn.Module):
 
         s = self.spec
         idx, gates = self.route(x, noise, cd)
-        plan = ops.build_column_plan(idx.view(B, S, s.k), s.G, pos) if s.G > 1 else None
+        plan = ops.build_column_plan(idx.view(B, S, s.k), s.G, pos) if s.G > 1 and cache is None else None
         ctx = BlockContext(B, S, idx, gates, plan, pos)
         streams: Tensor | None = None      # [T, k, d] fp32
         running: Tensor | None = None      # [T, d] fp32 = mean_j streams
         layer_aux = []
-        for layer in self.layers:
+        for li, layer in enumerate(self.layers):
             read = sources if running is None else [*sources, running]
             n = ops.depth_read_norm(read, layer.kimi_attn_read.query, layer.kimi_attn_read.value_gains,
                                     layer.attn_norm.weight, layer.kimi_attn_read.eps, layer.attn_norm.eps, cd)
-            attn = layer.attention(n, ctx, cd)                                  # [T, k, d]
+            attn = layer.attention(n, ctx, cd) if cache is None else layer.attention_step(n, ctx, cd, cache[li])   # [T, k, d]
             mid = ops.mid_source(running, attn)
             n = ops.depth_read_norm([*sources, mid], layer.kimi_mlp_read.query, layer.kimi_mlp_read.value_gains,
                                     layer.mlp_norm.weight, layer.kimi_mlp_read.eps, layer.mlp_norm.eps, cd)
@@ -280,6 +340,10 @@ class Block(nn.Module):
             agg = streams.mean(dim=1) if s.k > 1 else streams[:, 0]
             exports = [agg]
         baux = {"group_idx": idx, "layers": layer_aux}
+        scores = self.__dict__.pop("_last_scores", None)
+        if s.G > 1 and scores is not None:
+            # what the auxiliary losses read (reference aux layout, tokens flattened): raw scores incl. training noise
+            baux["group_router"] = {"scores": scores, "topk_indices": idx}
         if not self.training and not torch.is_grad_enabled() and s.G > 1:
             baux["group_prob"] = self.__dict__.pop("_last_group_prob", None)
         return exports, agg, baux
@@ -315,6 +379,40 @@ class Nestor(nn.Module):
     @property
     def output_dim(self) -> int:
         return self.config.output_dim
+
+    def init_kv_cache(self, batch_size: int, max_len: int, device, dtype=torch.float32) -> NestorKVCache:
+        """Empty decode state for ``batch_size`` sequences of up to ``max_len`` tokens."""
+
+        return NestorKVCache(self, batch_size, max_len, device, dtype)
+
+    @torch.no_grad()
+    def forward_step(self, x0: Tensor, pos: Tensor, cache: NestorKVCache, cd: torch.dtype) -> tuple[Tensor, dict]:
+        """One incremental causal step: ``x0 [B, d]`` embeddings of the next token of every sequence at positions
+        ``pos [B]`` -> normalised head input ``[B, d]``, with ``cache`` updated in place.
+
+        Depth reads mix a token's own sources over depth, routers and experts act per token, and a column attends
+        over the members it has already seen, so feeding a sequence token by token reproduces the full forward
+        (in evaluation mode: training noise on the group router is a full-sequence feature). The reference offers
+        stepwise decoding for its projection-residual mode only (``nestor/backbones/nestor.py:10442-10506`` raises
+        for the depth-read modes the registered models use); this covers those modes.
+        """
+
+        if self.training:
+            raise RuntimeError("forward_step is an evaluation path: call model.eval() first")
+        B = x0.shape[0]
+        with ops.oracle_ops():        # per-token work: the PyTorch statement of the ops on any device
+            narrow, wide, x, aux = [x0], [x0], x0, []
+            for block, bcache in zip(self.blocks, cache.blocks):
+                exports, x, a = block(x, narrow, B, 1, cd, pos, self.column_mode, None, cache=bcache)
+                x = exports[-1]
+                wide.extend(exports)
+                narrow = [*narrow, x]
+                aux.append(a)
+            read = wide if self.column_mode else narrow
+            h = ops.depth_read_norm(read, self.final_depth_read.query, self.final_depth_read.value_gains,
+                                    self.final_norm.weight, self.final_depth_read.eps, self.final_norm.eps, cd)
+        cache.length += 1
+        return h, {"blocks": aux}
 
     def forward(self, x0: Tensor, B: int, S: int, cd: torch.dtype, pos: Tensor | None = None,
                 noises: list[Tensor | None] | None = None) -> tuple[Tensor, dict]:

@@ -113,6 +113,48 @@ class SequenceModel(nn.Module):
             return ModelOutput(pred=h.view(B, S, -1), aux=aux)
         return ModelOutput(pred=self.head(h, cd).view(B, S, -1), aux=aux)
 
+    # ------------------------------------------------------------------ incremental decoding
+    def init_kv_cache(self, batch_size: int, max_len: int, device=None, dtype: torch.dtype = torch.float32):
+        device = self.head.weight.device if device is None else device
+        return self.backbone.init_kv_cache(batch_size, max_len, device, dtype)
+
+    @torch.no_grad()
+    def decode_step(self, ids: Tensor, cache, pos: Tensor | None = None) -> Tensor:
+        """Logits ``[B, V]`` of the next position given the new tokens ``ids [B]`` (``cache`` is advanced)."""
+
+        B = ids.shape[0]
+        if pos is None:
+            pos = torch.full((B,), cache.length, dtype=torch.long, device=ids.device)
+        cd = torch.float32 if self.compute_dtype is None else self.compute_dtype
+        if ids.device.type != "cuda":
+            cd = torch.float32
+        x0 = self.adapter(ids.reshape(B, 1)).reshape(B, -1)
+        h, _ = self.backbone.forward_step(x0, pos, cache, cd)
+        return self.head(h, cd).float()
+
+    @torch.no_grad()
+    def generate(self, prompt: Tensor, max_new_tokens: int, temperature: float = 0.0,
+                 generator: torch.Generator | None = None) -> Tensor:
+        """Greedy (``temperature == 0``) or sampled continuation of ``prompt [B, S0]``; returns ``[B, S0 + new]``."""
+
+        was_training = self.training
+        self.eval()
+        B, S0 = prompt.shape
+        cache = self.init_kv_cache(B, S0 + max_new_tokens, prompt.device)
+        logits = None
+        for t in range(S0):
+            logits = self.decode_step(prompt[:, t], cache)
+        out = [prompt]
+        for _ in range(max_new_tokens):
+            if temperature > 0:
+                nxt = torch.multinomial(torch.softmax(logits / temperature, dim=-1), 1, generator=generator).squeeze(1)
+            else:
+                nxt = logits.argmax(dim=-1)
+            out.append(nxt.unsqueeze(1))
+            logits = self.decode_step(nxt, cache)
+        self.train(was_training)
+        return torch.cat(out, dim=1)
+
     def fsdp2_wrap_order(self) -> list[nn.Module]:
         """Sharding units, in gather order: adapter, each block, backbone tail, head, root."""
 

@@ -193,11 +193,14 @@ class ParamPush:
 
     def __init__(self, master: torch.Tensor, compute: torch.Tensor | None) -> None:
         self.group = PeerGroup(master, compute if compute is not None and compute is not master else None)
+        # A multicast store also lands in the sender's own copy, so on few ranks it moves more bytes than the
+        # world - 1 peer stores it replaces (measured on 2 GPUs: 330 vs 609 GB/s); it pays from 4 ranks on.
+        self.use_nvls = self.group.nvls and self.group.world >= int(os.environ.get("NESTOR_B200_NVLS_PUSH_MIN_WORLD", "4"))
 
     @torch.no_grad()
     def run(self, lo: int, hi: int) -> None:
         g = self.group
-        if g.nvls:
+        if self.use_nvls:
             rc = _L().nb_param_push_nvls(C.byref(g.peers), g.mc_main, g.mc_aux or None, lo, hi, PeerGroup.next_epoch(),
                                          wait_budget(), g.blocks, g.status.data_ptr(), C.c_void_p(_lib.stream_ptr()))
         else:

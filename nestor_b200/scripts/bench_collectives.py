@@ -1,9 +1,11 @@
 """Micro-benchmark of the in-kernel collectives against NCCL (gradient all-reduce + cast, parameter push).
 
 ``torchrun --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 -m nestor_b200.scripts.bench_collectives``
-times, for 1 MB ... 1 GB fp32 buffers: the owner-push all-reduce kernel (fp32 sum, 1/W scale, optional bf16
-mirror) and ``torch.distributed.all_reduce`` (NCCL) on the same buffer, and the parameter push (all-gather fused
-with the bf16 cast) against ``all_gather_into_tensor`` + cast. Device-timed with CUDA events, max over ranks.
+times, for 1 MB ... 1 GB fp32 buffers: the all-reduce kernel (fp32 sum, 1/W scale, optional bf16 mirror) and
+``torch.distributed.all_reduce`` (NCCL) on the same buffer, the reduce-scatter onto per-rank ranges against
+``reduce_scatter_tensor``, and the parameter push (all-gather fused with the bf16 cast) against
+``all_gather_into_tensor`` + cast. Each of ours is timed on plain peer loads/stores and, when the symmetric buffers
+have an NVLink multicast mapping, on ``multimem`` instructions. Device-timed with CUDA events, max over ranks.
 Bus bandwidth is ``2 (W-1)/W * bytes / time`` for the all-reduce and ``(W-1)/W * bytes / time`` for the
 gather; the roofline is the measured peer copy of 770 GB/s per direction per GPU (900 nominal).
 """
@@ -61,42 +63,89 @@ def main(argv: list[str] | None = None) -> None:
     ref = g.clone()
     dist.all_reduce(ref)
     ref /= world
-    symm.FusedAllReduce(g, [(0, nmax)], mirror).run(1.0 / world)
+    first = symm.FusedAllReduce(g, [(0, nmax)], mirror)
+    first.run(1.0 / world)
     torch.cuda.synchronize()
     err = (g - ref).abs().max().item()
+    have_nvls = first.group.nvls
     if rank == 0:
-        print(f"world {world}: fused all-reduce max |diff| vs NCCL = {err:.2e}", flush=True)
+        print(f"world {world}: fused all-reduce max |diff| vs NCCL = {err:.2e}; NVLink multicast mapping: "
+              f"{'yes' if have_nvls else 'no'}", flush=True)
+
+    def both(make):
+        """Time one collective on plain peer loads/stores and, when the buffers have a multicast mapping, on multimem."""
+        out = {}
+        for name, env in (("p2p", "0"), ("nvls", "auto")):
+            if name == "nvls" and not have_nvls:
+                continue
+            os.environ["NESTOR_B200_NVLS"] = env
+            obj, fn = make()
+            out[name] = timed(fn, a.reps, dev)
+            obj.group.check()
+        os.environ["NESTOR_B200_NVLS"] = "auto"
+        return out
+
     for mb in a.sizes_mb:
         n = mb * 1024 * 1024 // 4
-        fa = symm.FusedAllReduce(g, [(0, n)], mirror)
         t = g[:n].clone()
-        ms = timed(lambda: fa.run(1.0 / world), a.reps, dev)
+
+        def make_ar():
+            fa = symm.FusedAllReduce(g, [(0, n)], mirror)
+            return fa, lambda: fa.run(1.0 / world)
+
+        res = both(make_ar)
         ms_nccl = timed(lambda: dist.all_reduce(t), a.reps, dev)
         bus = 2 * (world - 1) / world * n * 4 / 1e9
         if rank == 0:
-            print(f"all-reduce {mb:5d} MB: fused {ms:8.3f} ms {bus / ms * 1e3:6.0f} GB/s bus "
-                  f"({bus / ms * 1e3 / PEER_COPY_GBS:5.1%} of the peer-copy rate) | NCCL {ms_nccl:8.3f} ms "
-                  f"{bus / ms_nccl * 1e3:6.0f} GB/s", flush=True)
-        fa.group.check()
+            ours = " | ".join(f"{k} {v:8.3f} ms {bus / v * 1e3:6.0f} GB/s bus ({bus / v * 1e3 / PEER_COPY_GBS:5.1%} of the peer-copy rate)"
+                              for k, v in res.items())
+            print(f"all-reduce {mb:5d} MB: {ours} | NCCL {ms_nccl:8.3f} ms {bus / ms_nccl * 1e3:6.0f} GB/s", flush=True)
+    # reduce-scatter onto ownership ranges (what the sharded optimizer uses) vs NCCL reduce_scatter_tensor
+    for mb in a.sizes_mb:
+        n = (mb * 1024 * 1024 // 4) // (4 * world) * (4 * world)
+        per = n // world
+        t = g[:n].clone()
+        shard = torch.empty(per, dtype=torch.float32, device=dev)
+
+        def make_rs():
+            rs = symm.FusedReduceScatter(g)
+            return rs, lambda: rs.run(rank * per, (rank + 1) * per, 1.0 / world)
+
+        res = both(make_rs)
+        ms_nccl = timed(lambda: dist.reduce_scatter_tensor(shard, t), a.reps, dev)
+        bus = (world - 1) / world * n * 4 / 1e9
+        if rank == 0:
+            ours = " | ".join(f"{k} {v:8.3f} ms {bus / v * 1e3:6.0f} GB/s bus ({bus / v * 1e3 / PEER_COPY_GBS:5.1%})" for k, v in res.items())
+            print(f"reduce-scatter {mb:5d} MB: {ours} | NCCL {ms_nccl:8.3f} ms {bus / ms_nccl * 1e3:6.0f} GB/s", flush=True)
     # parameter push vs all-gather + cast
     master = symm.symmetric_empty(nmax, torch.float32, dev)
     comp = symm.symmetric_empty(nmax, torch.bfloat16, dev)
     master.fill_(float(rank + 1))
-    pp = symm.ParamPush(master, comp)
     for mb in a.sizes_mb:
         n = (mb * 1024 * 1024 // 4) // (4 * world) * (4 * world)
         per = n // world
-        ms = timed(lambda: pp.run(rank * per, (rank + 1) * per), a.reps, dev)
+
+        def make_pp():
+            pp = symm.ParamPush(master, comp)
+            return pp, lambda: pp.run(rank * per, (rank + 1) * per)
+
+        res = both(make_pp)
         shard = master[rank * per : (rank + 1) * per].clone()
         full = torch.empty(n, dtype=torch.float32, device=dev)
         ms_nccl = timed(lambda: (dist.all_gather_into_tensor(full, shard), full.to(torch.bfloat16)), a.reps, dev)
         bus = (world - 1) / world * n * 6 / 1e9          # fp32 master + bf16 compute copy cross the links
         if rank == 0:
-            print(f"param push {mb:5d} MB: fused {ms:8.3f} ms {bus / ms * 1e3:6.0f} GB/s "
-                  f"({bus / ms * 1e3 / PEER_COPY_GBS:5.1%} of the peer-copy rate) | NCCL all-gather + cast {ms_nccl:8.3f} ms", flush=True)
-        pp.group.check()
+            ours = " | ".join(f"{k} {v:8.3f} ms {bus / v * 1e3:6.0f} GB/s ({bus / v * 1e3 / PEER_COPY_GBS:5.1%} of the peer-copy rate)"
+                              for k, v in res.items())
+            print(f"param push {mb:5d} MB: {ours} | NCCL all-gather + cast {ms_nccl:8.3f} ms", flush=True)
     if a.ag_gemm:
         bench_ag_gemm(dev, rank, world, a.reps, a.gather_rings)
+    # leave in step: nothing of a rank is unmapped while a peer may still touch it
+    torch.cuda.synchronize()
+    dist.barrier()
+    del g, mirror, master, comp, first
+    torch.cuda.synchronize()
+    dist.barrier()
     dist.destroy_process_group()
 
 

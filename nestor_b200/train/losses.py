@@ -85,55 +85,101 @@ class CausalLMLoss(nn.Module):
         return LossOutput(total=loss, components={"cross_entropy": loss, "perplexity": loss.detach().exp()})
 
 
-def _router_stats(aux: dict[str, Any]) -> list[tuple[Tensor, int]]:
-    """(indices, num_choices) for every router that reported its selection."""
+def _flat_router(router_aux: dict[str, Any]) -> tuple[Tensor, Tensor, Tensor]:
+    """``(scores [N, C], topk_indices [N, k], valid [N])`` of one router record, tokens flattened."""
 
-    out = []
+    scores = router_aux["scores"]
+    C = scores.shape[-1]
+    scores = scores.reshape(-1, C)
+    idx = router_aux["topk_indices"].reshape(scores.shape[0], -1).long()
+    valid = router_aux.get("valid_token_mask")
+    valid = torch.ones(scores.shape[0], dtype=torch.bool, device=scores.device) if valid is None else valid.reshape(-1)
+    return scores, idx, valid
+
+
+def _assignment_counts(idx: Tensor, valid: Tensor, num_choices: int) -> Tensor:
+    """How many valid tokens selected each choice (``[C]``, fp32, no gradient)."""
+
+    w = valid.to(torch.float32).unsqueeze(-1).expand_as(idx).reshape(-1)
+    return torch.zeros(num_choices, dtype=torch.float32, device=idx.device).scatter_add_(0, idx.reshape(-1), w)
+
+
+def _router_records(aux: dict[str, Any] | None) -> tuple[list[dict], list[dict]]:
+    """Group-router and expert-router records the backbone reported (``aux["blocks"][b]["group_router"]`` and
+    ``aux["blocks"][b]["layers"][l]["expert_router"]``, each with ``scores`` and ``topk_indices``)."""
+
+    groups, experts = [], []
     for block in (aux or {}).get("blocks", []):
-        gi = block.get("group_idx")
-        if gi is not None and block.get("num_groups", 0) > 1:
-            out.append((gi, block["num_groups"]))
-    return out
+        rec = block.get("group_router")
+        if isinstance(rec, dict):
+            groups.append(rec)
+        for layer in block.get("layers", []):
+            rec = layer.get("expert_router") if isinstance(layer, dict) else None
+            if isinstance(rec, dict):
+                experts.append(rec)
+    return groups, experts
 
 
 class RouterBalanceLoss(nn.Module):
-    """Switch-style load-balance penalty on the group routers' hard assignment fractions."""
+    """Switch-style load-balance penalty, ``C * sum_c f_c p_c`` per router, with ``f`` the fraction of valid tokens
+    assigned to choice ``c`` and ``p`` the mean softmax probability of ``c``; averaged over the group routers and,
+    separately, over the expert routers (reference ``nestor/train/losses.py:288-400``)."""
 
     def __init__(self, config: RouterBalanceLossConfig) -> None:
         super().__init__()
         self.config = config
 
+    @staticmethod
+    def balance_term(router_aux: dict[str, Any]) -> Tensor:
+        scores, idx, valid = _flat_router(router_aux)
+        C = scores.shape[-1]
+        vf = valid.to(torch.float32)
+        n = vf.sum().clamp_min(1.0)
+        assigned = _assignment_counts(idx, valid, C) / n
+        routed = (torch.softmax(scores.float(), dim=-1) * vf.unsqueeze(-1)).sum(0) / n
+        return C * (assigned * routed).sum()
+
     def forward(self, pred: Tensor, target: Tensor, aux: dict[str, Any] | None = None) -> LossOutput:
-        terms = []
-        for idx, n in _router_stats(aux or {}):
-            frac = torch.bincount(idx.reshape(-1), minlength=n).float()
-            frac = frac / frac.sum().clamp_min(1)
-            terms.append(n * (frac * frac).sum() - 1.0)
+        groups, experts = _router_records(aux)
         total = pred.new_zeros((), dtype=torch.float32)
-        if terms:
-            total = self.config.balance_weight * torch.stack(terms).mean()
-        return LossOutput(total=total, components={"router_balance": total.detach()})
+        comps: dict[str, Tensor] = {}
+        for name, recs in (("router_balance_group", groups), ("router_balance_expert", experts)):
+            if recs:
+                term = torch.stack([self.balance_term(r) for r in recs]).mean() * self.config.balance_weight
+                comps[name] = term.detach()
+                total = total + term
+        comps["router_balance"] = total.detach()
+        return LossOutput(total=total, components=comps)
 
 
 class ReferenceMoEAuxLoss(nn.Module):
-    """``coefficient * E * sum_e f_e p_e`` with ``f`` summed across ranks, plus a router z-loss."""
+    """Per-layer switch loss ``E * <normalize(sum probs), normalize(frequency)>`` with the assignment frequency
+    summed over ranks, plus ``z_loss_weight * mean(logsumexp(scores)^2)``; summed over the layers' expert routers and
+    scaled by ``coefficient`` (reference ``nestor/train/losses.py:403-486``)."""
 
     def __init__(self, config: ReferenceMoEAuxLossConfig) -> None:
         super().__init__()
         self.config = config
 
+    def layer_term(self, router_aux: dict[str, Any]) -> Tensor:
+        scores, idx, valid = _flat_router(router_aux)
+        E = scores.shape[-1]
+        logits = scores.float()
+        vf = valid.to(torch.float32)
+        acc_probs = (torch.softmax(logits, dim=-1) * vf.unsqueeze(-1)).sum(0)
+        freq = _assignment_counts(idx, valid, E).detach()
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(freq)
+        switch = E * (acc_probs / acc_probs.sum().clamp_min(1e-12) * (freq / freq.sum().clamp_min(1e-12))).sum()
+        z = (torch.logsumexp(logits, dim=-1).square() * vf).sum() / vf.sum().clamp_min(1)
+        return switch + self.config.z_loss_weight * z
+
     def forward(self, pred: Tensor, target: Tensor, aux: dict[str, Any] | None = None) -> LossOutput:
+        _, experts = _router_records(aux)
         total = pred.new_zeros((), dtype=torch.float32)
-        for rec in (aux or {}).get("moe_aux", []):
-            probs, idx = rec["probs"], rec["idx"]
-            E = probs.shape[-1]
-            freq = torch.bincount(idx.reshape(-1), minlength=E).float()
-            if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
-                dist.all_reduce(freq)
-            freq = freq / freq.sum().clamp_min(1)
-            total = total + self.config.coefficient * E * (freq * probs.float().mean(dim=0)).sum()
-            total = total + self.config.z_loss_weight * torch.logsumexp(rec["scores"].float(), dim=-1).pow(2).mean()
-        return LossOutput(total=total, components={"moe_aux": total.detach()})
+        if experts:
+            total = torch.stack([self.layer_term(r) for r in experts]).sum() * self.config.coefficient
+        return LossOutput(total=total, components={"reference_moe_aux": total.detach()})
 
 
 class CompositeLoss(nn.Module):

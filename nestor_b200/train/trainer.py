@@ -91,6 +91,7 @@ class Trainer:
         self.zero = bool(self.param_push is not None and getattr(self.optimizer, "shard_adamw", False))
         # Device status word of the in-kernel collectives: a bounded peer wait that gave up leaves a nonzero code
         # there and the kernel returns without reducing / pushing. It is read back once per optimizer step.
+        self.phase_events: list | None = None     # set to [] to time the phases of the next update_weights
         self.peer_status: Tensor | None = None
         self._status_host: Tensor | None = None
         self._status_event = None
@@ -247,27 +248,48 @@ class Trainer:
         if self.peer_status is not None and not self.peer_status.is_cuda:
             self._status_host = None
 
+    def _mark(self, name: str) -> None:
+        """Phase boundary of ``update_weights`` (CUDA events, only while ``phase_events`` is a list)."""
+
+        if self.phase_events is not None and self.device.type == "cuda":
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.phase_events.append((name, ev))
+
+    def phase_times_ms(self) -> dict[str, float]:
+        """Device time of each phase of the last ``update_weights`` recorded with ``phase_events = []``."""
+
+        ev = self.phase_events or []
+        if ev:
+            ev[-1][1].synchronize()
+        return {ev[i + 1][0]: ev[i][1].elapsed_time(ev[i + 1][1]) for i in range(len(ev) - 1)}
+
     def update_weights(self, window_counts: dict[str, Tensor]) -> Tensor | None:
         self.check_peer_status()
+        self._mark("start")
         if self.zero:
             self.reducer.reduce_scatter(*self.optimizer.owned_range())
         else:
             self.reducer.reduce()
+        self._mark("grad_reduce")
         norm = None
         if self.config.max_grad_norm is not None:
             norm = self.clip_grad_norm(self.config.max_grad_norm)
+        self._mark("clip")
         if _env_flag("NESTOR_DEBUG_GRAD") and self.global_step < 5 and is_main_process():
             g = self.arena.grad
             self.logger.info("[grad] step %d norm=%s finite=%s absmax=%.3e", self.global_step,
                              None if norm is None else f"{norm.item():.4e}",
                              bool(torch.isfinite(g).all().item()), g.abs().max().item())
         self.optimizer.step()
+        self._mark("optimizer")
         if self.param_push is not None:
             # each rank stores the range it owns into every replica, itself included (fp32 master + bf16 compute
             # copy); the ranges tile the arena, so this is also the refresh of the whole compute copy
             self.param_push.run(*self.optimizer.owned_range())
         else:
             self.arena.refresh_compute()
+        self._mark("param_push")
         self.arena.zero_grad()
         if self.ema is not None:
             self.ema["flat"].lerp_(self.arena.master, 1.0 - self.ema_decay)
@@ -276,6 +298,7 @@ class Trainer:
         apply_bias_updates(self.model.backbone, window_counts, global_counts=self.global_counts)
         if self.world > 1 and not self.global_counts and _env_flag("NESTOR_DDP_BROADCAST_BUFFERS", "1"):
             self.reducer.sync_buffers(self.model)  # rank-0 statistics win, as with DDP buffer broadcast
+        self._mark("rest")
         self._probe_peer_status()
         return norm
 

@@ -1,6 +1,7 @@
 """Worker for the multi-GPU tests (launched with ``python -m torch.distributed.run``): checks the fused
-peer-memory all-reduce against NCCL, the parameter push, and that replicas stay identical over
-optimizer steps of the tiny model. Uses plain peer loads/stores only."""
+all-reduce / reduce-scatter against NCCL and the parameter push, on plain peer loads/stores and (when the symmetric
+buffers have an NVLink multicast mapping) on ``multimem`` instructions, then that replicas stay identical over
+optimizer steps of the tiny model. Every rank leaves in step, after the symmetric buffers are released."""
 
 import os
 import sys
@@ -54,10 +55,10 @@ def check_gathered_gemm(dev, rank: int, world: int) -> None:
     dist.barrier()
 
 
-def main() -> None:
-    dev = init_distributed(True)
-    rank, world = dist.get_rank(), dist.get_world_size()
-    torch.manual_seed(100 + rank)
+def check_collectives(dev, rank: int, world: int, nvls: str) -> bool:
+    """All-reduce, ragged reduce-scatter and parameter push against NCCL results; returns whether multimem was used."""
+
+    os.environ["NESTOR_B200_NVLS"] = nvls
     N = 8 * 1024 * 1024
     g = symm.symmetric_empty(N, torch.float32, dev)
     g.copy_(torch.randn(N, device=dev) * 1e-3)
@@ -100,6 +101,21 @@ def main() -> None:
     dist.barrier()
     want = torch.arange(1, world + 1, device=dev, dtype=torch.float32).repeat_interleave(per)
     assert torch.equal(master, want) and torch.equal(comp.float(), want), "parameter push mismatch"
+    used = bool(far.group.nvls and frs.group.nvls and pp.group.nvls)
+    torch.cuda.synchronize()
+    dist.barrier()
+    del g, master, comp, far, frs, pp
+    return used
+
+
+def main() -> None:
+    dev = init_distributed(True)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    torch.manual_seed(100 + rank)
+    used = {mode: check_collectives(dev, rank, world, mode) for mode in ("0", "auto")}
+    assert not used["0"], "NESTOR_B200_NVLS=0 must keep the collectives on plain peer loads and stores"
+    if rank == 0:
+        print(f"collectives ok on peer loads/stores; multimem path {'ok' if used['auto'] else 'not available on this box'}", flush=True)
     check_gathered_gemm(dev, rank, world)
     os.environ.setdefault("DCLM_DATA_PATH", "/tmp/unused.bin")
     from nestor_b200.experiments.tiny import nestor_tiny
@@ -154,6 +170,11 @@ def main() -> None:
     assert rel < 1e-5, f"rank-sharded banks disagree with replicated banks: {rel}"
     cuda_ops.BANK_SHARDS = None
     os.environ["NESTOR_FSDP_BANKS"] = "0"
+    dist.barrier()
+    torch.cuda.synchronize()
+    dist.barrier()
+    del tr, results
+    torch.cuda.synchronize()
     dist.barrier()
     if rank == 0:
         print("MULTI_GPU_OK", flush=True)
