@@ -240,13 +240,17 @@ class NestorConfig(BackboneConfig):
             raise ValueError("Only causal decoders are supported (causal=True).")
         if any(s != 1 for s in _per_block(self.pooling_strides, n, "pooling_strides")):
             raise ValueError("Token pooling between blocks is not supported (pooling_strides must be 1).")
-        if self.pooling_keep_ratios is not None or self.num_global_tokens or self.drop_path_rate:
-            raise ValueError("pooling_keep_ratios / num_global_tokens / drop_path_rate must stay at defaults.")
-        if self.block_residual_mode not in ("attn_res_kimi", "attn_res_column"):
+        if self.pooling_keep_ratios is not None or self.num_global_tokens:
+            raise ValueError("pooling_keep_ratios / num_global_tokens must stay at defaults.")
+        if not 0.0 <= self.drop_path_rate < 1.0:
+            raise ValueError("drop_path_rate must be in [0, 1).")
+        if self.block_residual_mode not in ("attn_res_kimi", "attn_res_column", "projection"):
             raise ValueError(
-                "block_residual_mode must be 'attn_res_kimi' or 'attn_res_column', got "
+                "block_residual_mode must be 'projection', 'attn_res_kimi' or 'attn_res_column', got "
                 f"{self.block_residual_mode!r}."
             )
+        if self.residual_mode != "convex":
+            raise ValueError("residual_mode must be 'convex' (the additive rule comes with the reference-muP config).")
         if self.block_residual_mode == "attn_res_column":
             if not (self.block_column_head_only and self.block_column_include_aggregate
                     and self.block_column_deviation_sources):
@@ -338,6 +342,13 @@ class NestorConfig(BackboneConfig):
     @property
     def column_mode(self) -> bool:
         return self.block_residual_mode == "attn_res_column"
+
+    @property
+    def depth_reads(self) -> bool:
+        """Whether sublayers read a softmax-over-depth mixture (the two ``attn_res_*`` modes) or the plain residual
+        stream (``projection``: ``x + m * update`` under the reference muP, the convex rule otherwise)."""
+
+        return self.block_residual_mode != "projection"
 
     def max_depth_sources(self) -> int:
         """Slots of the widest depth read: the embedding plus every block's exports."""

@@ -134,13 +134,16 @@ class ExpertPool(nn.Module):
 class Layer(nn.Module):
     """One transformer layer (attention half + expert half) of a block."""
 
-    def __init__(self, s: BlockSpec, init: InitScales, max_sources: int, dense_no_router: bool) -> None:
+    def __init__(self, s: BlockSpec, init: InitScales, max_sources: int, dense_no_router: bool,
+                 depth_reads: bool = True, drop_path: float = 0.0) -> None:
         super().__init__()
         self.spec = s
         self.attn_norm = Norm(s.dim, init.norm_eps)
         self.mlp_norm = Norm(s.dim, init.norm_eps)
-        self.kimi_attn_read = DepthRead(s.dim, max_sources)
-        self.kimi_mlp_read = DepthRead(s.dim, max_sources)
+        self.drop_path = float(os.environ.get("NESTOR_DROP_PATH_RATE") or drop_path)
+        if depth_reads:
+            self.kimi_attn_read = DepthRead(s.dim, max_sources)
+            self.kimi_mlp_read = DepthRead(s.dim, max_sources)
         self.attention_groups = nn.ModuleList(
             [ColumnProjections(s.dim, s.inner, init.matrix, init.output) for _ in range(s.G)])
         self.expert_pool: ExpertPool | None = None
@@ -174,6 +177,18 @@ class Layer(nn.Module):
 
     def out_weight(self) -> Tensor:
         return Wstack(self, [g.out_proj.weight for g in self.attention_groups])
+
+    def drop(self, update: Tensor, B: int) -> Tensor:
+        """Stochastic depth on a sublayer update (per sequence, survivors rescaled by ``1 / keep``): training only
+        (reference ``nestor/backbones/nestor.py:4891-4910``)."""
+
+        p = self.drop_path
+        if p <= 0.0 or not self.training:
+            return update
+        keep = 1.0 - p
+        mask = (torch.rand(B, device=update.device) < keep).to(update.dtype) / keep
+        rows = update.shape[0] // B
+        return update * mask.repeat_interleave(rows).view(-1, *([1] * (update.dim() - 1)))
 
     # -- halves -----------------------------------------------------------------------
     def attention(self, n: Tensor, ctx: "BlockContext", cd: torch.dtype) -> Tensor:
@@ -274,15 +289,21 @@ class BlockContext:
 
 
 class Block(nn.Module):
-    def __init__(self, s: BlockSpec, init: InitScales, max_sources: int, dense_no_router: bool) -> None:
+    def __init__(self, s: BlockSpec, init: InitScales, max_sources: int, dense_no_router: bool,
+                 depth_reads: bool = True, residual: tuple[str, float] = ("add", 1.0),
+                 drop_rates: list[float] | None = None) -> None:
         super().__init__()
         self.spec = s
+        self.depth_reads = depth_reads
+        self.residual = residual       # projection mode: ("add", m) -> x + m*u, ("convex", 1/D) -> (1 - 1/D) x + u/D
         self.group_router = RouterParams(
             s.dim, s.G, s.k, hidden=s.router_hidden, score_lr_mul=s.layers ** -0.5,
             loss_free=s.loss_free, bias_rate=s.bias_rate, noisy=True)
         if s.G == 1:
             self.group_router.requires_grad_(False)
-        self.layers = nn.ModuleList([Layer(s, init, max_sources, dense_no_router) for _ in range(s.layers)])
+        rates = drop_rates or [0.0] * s.layers
+        self.layers = nn.ModuleList([Layer(s, init, max_sources, dense_no_router, depth_reads, rates[i])
+                                     for i in range(s.layers)])
 
     def route(self, x: Tensor, noise: Tensor | None, cd: torch.dtype) -> tuple[Tensor, Tensor]:
         """Group router on the block input ``[T, d]`` -> ``(idx [T, k], gates [T, k] fp32)``."""
@@ -319,6 +340,8 @@ class Block(nn.Module):
         idx, gates = self.route(x, noise, cd)
         plan = ops.build_column_plan(idx.view(B, S, s.k), s.G, pos) if s.G > 1 and cache is None else None
         ctx = BlockContext(B, S, idx, gates, plan, pos)
+        if not self.depth_reads:
+            return self._forward_projection(x, ctx, cd, cache, idx)
         streams: Tensor | None = None      # [T, k, d] fp32
         running: Tensor | None = None      # [T, d] fp32 = mean_j streams
         layer_aux = []
@@ -331,6 +354,10 @@ class Block(nn.Module):
             n = ops.depth_read_norm([*sources, mid], layer.kimi_mlp_read.query, layer.kimi_mlp_read.value_gains,
                                     layer.mlp_norm.weight, layer.kimi_mlp_read.eps, layer.mlp_norm.eps, cd)
             priv, shared, path, aux = layer.experts(n, ctx, cd)
+            if layer.drop_path > 0.0 and self.training:
+                attn = layer.drop(attn, B)
+                shared = layer.drop(shared, B)
+                priv = None if priv is None else layer.drop(priv, B)
             streams, running = ops.layer_combine(attn, priv, shared, path, streams, running, cd)
             layer_aux.append(aux)
         if column_mode and s.k > 1:
@@ -349,6 +376,38 @@ class Block(nn.Module):
         return exports, agg, baux
 
 
+    def _apply_residual(self, x: Tensor, update: Tensor) -> Tensor:
+        rule, c = self.residual
+        return x + c * update if rule == "add" else (1.0 - c) * x + c * update
+
+    def _forward_projection(self, x: Tensor, ctx: "BlockContext", cd: torch.dtype, cache: list | None,
+                            idx: Tensor) -> tuple[list[Tensor], Tensor, dict]:
+        """Plain pre-norm residual block (``block_residual_mode='projection'``): every layer adds its attention and
+        expert updates to one fp32 stream with the model's residual rule, a token's update being the gate-weighted
+        sum over its columns (reference ``nestor/backbones/nestor.py:4746-4763``, ``:4918-4940``)."""
+
+        layer_aux = []
+        for li, layer in enumerate(self.layers):
+            n = ops.rmsnorm(x, layer.attn_norm.weight, layer.attn_norm.eps, cd)
+            attn = layer.attention(n, ctx, cd) if cache is None else layer.attention_step(n, ctx, cd, cache[li])
+            x = self._apply_residual(x, layer.drop(attn.float().sum(dim=1), ctx.B))
+            n = ops.rmsnorm(x, layer.mlp_norm.weight, layer.mlp_norm.eps, cd)
+            priv, shared, path, aux = layer.experts(n, ctx, cd)
+            if path is not None:
+                update = (path[:, 0:1].float() * shared.float()).to(cd).float()
+                if priv is not None:
+                    update = update + (path[:, 1:2].float() * priv.float().sum(dim=1)).to(cd).float()
+            else:
+                update = shared.float()
+            x = self._apply_residual(x, layer.drop(update, ctx.B))
+            layer_aux.append(aux)
+        baux = {"group_idx": idx, "layers": layer_aux}
+        scores = self.__dict__.pop("_last_scores", None)
+        if self.spec.G > 1 and scores is not None:
+            baux["group_router"] = {"scores": scores, "topk_indices": idx}
+        return [x], x, baux
+
+
 class Nestor(nn.Module):
     """The backbone: blocks, the final head read over every export, the final RMSNorm."""
 
@@ -359,12 +418,21 @@ class Nestor(nn.Module):
         self.specs = config.resolve()
         self.column_mode = config.column_mode
         self.max_depth_sources = config.max_depth_sources()
-        init = InitScales(mup, config.input_dim, sum(s.layers for s in self.specs))
+        total_layers = sum(s.layers for s in self.specs)
+        init = InitScales(mup, config.input_dim, total_layers)
+        self.depth_reads = config.depth_reads
+        # projection mode: additive rule with the reference-muP multiplier, else the convex rule with 1/D, D = 2 * layers
+        residual = ("add", mup.residual_multiplier) if mup is not None else ("convex", 1.0 / (2 * total_layers))
+        # stochastic depth rises linearly over the layers of a block (timm rule): 0 for its first layer, the
+        # configured rate for its last (reference ``nestor/backbones/nestor.py:2338-2345``)
+        rates = [[config.drop_path_rate * i / max(s.layers - 1, 1) for i in range(s.layers)] for s in self.specs]
         self.blocks = nn.ModuleList(
-            [Block(s, init, self.max_depth_sources, dense_no_router) for s in self.specs])
-        self.final_depth_read = DepthRead(config.output_dim, self.max_depth_sources)
+            [Block(s, init, self.max_depth_sources, dense_no_router, self.depth_reads, residual, rates[i])
+             for i, s in enumerate(self.specs)])
+        if self.depth_reads:
+            self.final_depth_read = DepthRead(config.output_dim, self.max_depth_sources)
         self.final_norm = Norm(config.output_dim, init.norm_eps)
-        if self.column_mode and config.block_column_gain_init != 1.0:
+        if self.depth_reads and self.column_mode and config.block_column_gain_init != 1.0:
             # Head-read gains: deviation slots of every multi-column block start at the
             # configured value (0 for the registered cells); embedding and aggregates stay 1.
             g = torch.ones(self.max_depth_sources)
@@ -408,9 +476,7 @@ class Nestor(nn.Module):
                 wide.extend(exports)
                 narrow = [*narrow, x]
                 aux.append(a)
-            read = wide if self.column_mode else narrow
-            h = ops.depth_read_norm(read, self.final_depth_read.query, self.final_depth_read.value_gains,
-                                    self.final_norm.weight, self.final_depth_read.eps, self.final_norm.eps, cd)
+            h = self._head_input(wide, narrow, x, cd)
         cache.length += 1
         return h, {"blocks": aux}
 
@@ -439,10 +505,16 @@ class Nestor(nn.Module):
             wide.extend(exports)
             narrow = [*narrow, x]
             aux.append(a)
+        return self._head_input(wide, narrow, x, cd), {"blocks": aux}
+
+    def _head_input(self, wide: list[Tensor], narrow: list[Tensor], x: Tensor, cd: torch.dtype) -> Tensor:
+        """The normalised head input: the final depth read over every export, or (projection mode) the stream itself."""
+
+        if not self.depth_reads:
+            return ops.rmsnorm(x, self.final_norm.weight, self.final_norm.eps, cd)
         read_sources = wide if self.column_mode else narrow
-        h = ops.depth_read_norm(read_sources, self.final_depth_read.query, self.final_depth_read.value_gains,
-                                self.final_norm.weight, self.final_depth_read.eps, self.final_norm.eps, cd)
-        return h, {"blocks": aux}
+        return ops.depth_read_norm(read_sources, self.final_depth_read.query, self.final_depth_read.value_gains,
+                                   self.final_norm.weight, self.final_depth_read.eps, self.final_norm.eps, cd)
 
     def routers(self) -> list[tuple[str, RouterParams]]:
         return [(n, m) for n, m in self.named_modules() if isinstance(m, RouterParams)]
@@ -451,12 +523,15 @@ class Nestor(nn.Module):
 # ------------------------------------------------------------------ loss-free balancing
 
 
-def _count(idx: Tensor, n: int) -> Tensor:
-    """Histogram of ``idx`` over ``n`` bins without a host sync."""
+def _count(idx: Tensor, n: int, valid: Tensor | None = None) -> Tensor:
+    """Histogram of ``idx [T, ...]`` over ``n`` bins without a host sync; ``valid [T]`` drops padding tokens."""
 
     flat = idx.reshape(-1).long()
-    return torch.zeros(n, dtype=torch.float32, device=idx.device).scatter_add_(
-        0, flat, torch.ones_like(flat, dtype=torch.float32))
+    if valid is None:
+        w = torch.ones_like(flat, dtype=torch.float32)
+    else:
+        w = valid.reshape(-1, *([1] * (idx.dim() - 1))).expand_as(idx).reshape(-1).to(torch.float32)
+    return torch.zeros(n, dtype=torch.float32, device=idx.device).scatter_add_(0, flat, w)
 
 
 @torch.no_grad()
@@ -468,24 +543,26 @@ def router_counts(backbone: Nestor, aux: dict) -> dict[str, Tensor]:
     """
 
     out: dict[str, Tensor] = {}
+    valid = aux.get("valid_token_mask")
+    valid = None if valid is None else valid.reshape(-1)
     for b, (block, baux) in enumerate(zip(backbone.blocks, aux["blocks"])):
         s = block.spec
         if s.G > 1:
-            out[f"blocks.{b}.group_router"] = _count(baux["group_idx"], s.G)
+            out[f"blocks.{b}.group_router"] = _count(baux["group_idx"], s.G, valid)
         for l, (layer, laux) in enumerate(zip(block.layers, baux["layers"])):
             base = f"blocks.{b}.layers.{l}"
             if layer.expert_pool is not None:
-                if "public_offsets" in laux:      # the dispatch plans already hold the per-expert histograms
+                if "public_offsets" in laux and valid is None:      # the dispatch plans already hold the per-expert histograms
                     out[f"{base}.expert_pool.public_router"] = laux["public_offsets"].diff().float()
                     per = laux["private_offsets"].diff().float().view(s.G, s.Q)
                 else:
-                    out[f"{base}.expert_pool.public_router"] = _count(laux["public_idx"], s.P)
+                    out[f"{base}.expert_pool.public_router"] = _count(laux["public_idx"], s.P, valid)
                     flat = laux["columns"].long().unsqueeze(-1) * s.Q + laux["private_idx"].long()
-                    per = _count(flat, s.G * s.Q).view(s.G, s.Q)
+                    per = _count(flat, s.G * s.Q, valid).view(s.G, s.Q)
                 for g in range(s.G):
                     out[f"{base}.expert_pool.private_routers.{g}"] = per[g]
             elif "expert_idx" in laux:
-                out[f"{base}.expert_router"] = _count(laux["expert_idx"], s.bank_experts)
+                out[f"{base}.expert_router"] = _count(laux["expert_idx"], s.bank_experts, valid)
     return out
 
 

@@ -33,8 +33,26 @@ class ModelOutput:
     aux: dict[str, Any]
 
 
+class ByteTokenizer:
+    """UTF-8 bytes as token ids (``tokenizer="bytes"``): needs no vocabulary file, for tests and offline use."""
+
+    n_vocab = 256
+
+    def encode_ordinary(self, text: str) -> list[int]:
+        return list(text.encode("utf-8"))
+
+    def decode(self, ids: list[int]) -> str:
+        return bytes(int(i) & 0xFF for i in ids).decode("utf-8", errors="replace")
+
+
 class TextAdapter(nn.Module):
-    """Token embedding table; output ``E[ids] * embedding_multiplier`` in fp32."""
+    """Token embedding table; output ``E[ids] * embedding_multiplier`` in fp32.
+
+    The adapter is also the tokenizer for string inputs (reference ``nestor/adapters/text.py:59-101``): a tiktoken
+    encoding named by ``config.tokenizer`` (loaded lazily; pre-tokenised tensors never need it), or the built-in
+    ``"bytes"`` tokenizer. ``encode_texts`` right-pads a batch to its longest entry (capped at ``max_length``) and
+    returns the validity mask; pre-tokenised tensors carry no mask (every position is a real token).
+    """
 
     def __init__(self, config: TextAdapterConfig, mup: ReferenceMupConfig | None) -> None:
         super().__init__()
@@ -46,6 +64,37 @@ class TextAdapter(nn.Module):
         std = mup.initializer_range if mup is not None else 1.0
         nn.init.normal_(self.embed.weight, 0.0, std)
         self.embedding_multiplier = mup.embedding_multiplier if mup is not None else 1.0
+
+        self._tokenizer: Any = None
+
+    def tokenizer(self) -> Any:
+        if self._tokenizer is None:
+            if self.config.tokenizer == "bytes":
+                self._tokenizer = ByteTokenizer()
+            else:
+                try:
+                    import tiktoken
+                    self._tokenizer = tiktoken.get_encoding(self.config.tokenizer)
+                except Exception as exc:   # no package, or no vocabulary file on a machine without network
+                    raise RuntimeError(f"cannot load the {self.config.tokenizer!r} tokenizer for string inputs: {exc}. "
+                                       "Pass token-id tensors, or use tokenizer='bytes'.") from exc
+        return self._tokenizer
+
+    def encode_texts(self, texts: list[str], device: torch.device | None = None) -> tuple[Tensor, Tensor]:
+        """``(ids [B, L] int64, valid [B, L] bool)`` for a batch of strings, right-padded with id 0."""
+
+        tok = self.tokenizer()
+        rows = [tok.encode_ordinary(t)[: self.config.max_length] for t in texts]
+        if any(max(r, default=0) >= self.embed.num_embeddings for r in rows):
+            raise ValueError("the tokenizer produced an id beyond the embedding table")
+        L = max(1, max(len(r) for r in rows))
+        ids = torch.zeros(len(rows), L, dtype=torch.long)
+        valid = torch.zeros(len(rows), L, dtype=torch.bool)
+        for i, r in enumerate(rows):
+            ids[i, : len(r)] = torch.tensor(r, dtype=torch.long)
+            valid[i, : len(r)] = True
+        device = self.embed.weight.device if device is None else device
+        return ids.to(device), valid.to(device)
 
     def forward(self, ids: Tensor) -> Tensor:
         return self.embed(ids).float() * self.embedding_multiplier
@@ -103,11 +152,36 @@ class SequenceModel(nn.Module):
             return self.compute_dtype
         return torch.bfloat16 if device.type == "cuda" else torch.float32
 
-    def forward(self, ids: Tensor, pos: Tensor | None = None, noises: list | None = None) -> ModelOutput:
+    def forward(self, ids: Tensor | list[str], pos: Tensor | None = None, noises: list | None = None,
+                valid: Tensor | None = None) -> ModelOutput:
+        """``ids``: token ids ``[B, S]`` or a list of strings (tokenised by the adapter, right-padded).
+
+        ``valid [B, S]`` marks real tokens of right-padded batches. The decoder is causal, so padding after a
+        sequence cannot reach any valid position; the mask only has to keep padding out of what is *counted*: it is
+        handed on as ``aux["valid_token_mask"]``, which the loss (targets), the router statistics (loss-free
+        balancing, auxiliary losses) and the evaluation metrics honour. Padding must follow the real tokens.
+        """
+
+        if isinstance(ids, (list, tuple)) and ids and isinstance(ids[0], str):
+            ids, valid = self.adapter.encode_texts(list(ids))
+        if valid is not None and bool((valid[:, 1:] & ~valid[:, :-1]).any()):
+            raise ValueError("valid_token_mask must be a prefix mask (padding only after the real tokens).")
         B, S = ids.shape
         cd = self.resolve_compute_dtype(ids.device)
         x0 = self.adapter(ids).reshape(B * S, -1)
+        if valid is not None:
+            x0 = x0 * valid.reshape(B * S, 1).to(x0.dtype)
         h, aux = self.backbone(x0, B, S, cd, pos=pos, noises=noises)
+        if valid is not None:
+            aux["valid_token_mask"] = valid
+            aux["input_ids"] = ids
+            flat = valid.reshape(-1)
+            for block in aux["blocks"]:          # the routers' own records carry the mask too
+                if "group_router" in block:
+                    block["group_router"]["valid_token_mask"] = flat
+                for layer in block["layers"]:
+                    if "expert_router" in layer:
+                        layer["expert_router"]["valid_token_mask"] = flat
         if self.fused_head:
             aux["fused_head_module"] = self.head
             return ModelOutput(pred=h.view(B, S, -1), aux=aux)

@@ -69,6 +69,9 @@ class CausalLMLoss(nn.Module):
 
     def forward(self, pred: Tensor, target: Tensor, aux: dict[str, Any] | None = None) -> LossOutput:
         head = (aux or {}).get("fused_head_module")
+        valid = (aux or {}).get("valid_token_mask")
+        if valid is not None:        # padded batch: padding positions are not targets
+            target = target.masked_fill(~valid, PADDING_TOKEN_VALUE)
         if head is not None:
             hidden = pred[:, :-1, :].reshape(-1, pred.shape[-1])
             tgt = target[:, 1:].reshape(-1)

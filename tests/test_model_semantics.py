@@ -219,3 +219,69 @@ def test_eval_forward_reports_routing_probability_sums(tiny_scale):
     assert priv_total == pytest.approx(T * spec.k, rel=1e-4)        # every (token, selected column) pair contributes 1
     metrics = routing_metrics({k: v.cpu() for k, v in counts.items()}, {k: v.cpu() for k, v in probs.items()})
     assert "routing/blocks.0.group_router/prob/c0" in metrics and "routing/group/mean_max_prob" in metrics
+
+
+@pytest.mark.parametrize("family", ["moe", "dense"])
+def test_projection_residual_mode_matches_reference(family, tiny_scale, monkeypatch):
+    """``block_residual_mode='projection'`` (plain residual stream, ``x + 0.22 u`` under the reference muP): same
+    state-dict keys as the reference model in that mode, same logits, same gradients."""
+
+    import dataclasses as dc
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "nestor").is_dir():
+        pytest.skip("reference package not installed under baseline/_ref")
+    monkeypatch.setenv("NESTOR_STACKED_EXPERT_BANKS", "1")
+    monkeypatch.setenv("NESTOR_DENSE_NO_ROUTER", "1")
+    monkeypatch.syspath_prepend(str(ref_root))
+    try:
+        from nestor.experiments import pretrain as RP
+        from nestor.models import Model as RefModel
+    except Exception as exc:
+        pytest.skip(f"reference import failed: {exc}")
+    P = tiny_scale
+    monkeypatch.setitem(RP.SCALES, "tiny", RP.Scale("tiny", 128, 4, 8, 512, 10, 2, 1024))
+    monkeypatch.setattr(RP, "BLOCK_SIZE", 64)
+    for fam in ("dense", "moe", "nestor"):
+        monkeypatch.setitem(RP.BATCH_SHAPE, (fam, "tiny"), (2, 1))
+    torch.manual_seed(0)
+    rcfg = {"moe": RP._moe, "dense": RP._dense}[family]("tiny").jobs[0].model
+    rcfg = dc.replace(rcfg, backbone_config=dc.replace(rcfg.backbone_config, block_residual_mode="projection"))
+    rm = RefModel.from_config(rcfg).eval()
+    cfg = P.build_experiment(family, "tiny").jobs[0].model
+    cfg = dc.replace(cfg, backbone_config=dc.replace(cfg.backbone_config, block_residual_mode="projection"))
+    mm = Model.from_config(cfg).eval()
+    assert set(mm.state_dict()) == set(rm.state_dict())
+    mm.load_state_dict(rm.state_dict(), strict=True)
+    ids = torch.randint(0, 100263, (2, 48))
+    lr = F.cross_entropy(rm(ids).pred[:, :-1].reshape(-1, 100263), ids[:, 1:].reshape(-1))
+    lm = F.cross_entropy(mm(ids).pred[:, :-1].reshape(-1, 100263), ids[:, 1:].reshape(-1))
+    assert torch.allclose(lr, lm, atol=1e-5)
+    lr.backward(); lm.backward()
+    ref_grads = dict(rm.named_parameters())
+    for n, p in mm.named_parameters():
+        g1, g2 = ref_grads[n].grad, p.grad
+        if g1 is not None and g2 is not None and g1.norm() > 1e-5:
+            assert (g1 - g2).norm() / g1.norm() < 2e-3, n
+    # stepwise decoding works in this mode too
+    with torch.no_grad():
+        full = mm(ids).pred
+    cache = mm.init_kv_cache(2, 48)
+    for t in range(6):
+        assert torch.allclose(mm.decode_step(ids[:, t], cache), full[:, t], atol=2e-4, rtol=1e-4)
+
+
+def test_drop_path_is_identity_in_eval_and_unbiased_in_training(tiny_scale):
+    import dataclasses as dc
+    cfg = tiny_scale.build_experiment("nestor", "tiny").jobs[0].model
+    cfg = dc.replace(cfg, backbone_config=dc.replace(cfg.backbone_config, drop_path_rate=0.5))
+    torch.manual_seed(0)
+    m = Model.from_config(cfg)
+    rates = [[l.drop_path for l in b.layers] for b in m.backbone.blocks]
+    assert rates[0] == [0.0, 0.5] and rates[1] == [0.0]       # linear inside a block; a one-layer block never drops
+    layer = m.backbone.blocks[0].layers[-1]
+    u = torch.ones(4 * 8, 3)
+    m.eval()
+    assert torch.equal(layer.drop(u, 4), u)
+    m.train()
+    d = layer.drop(u, 4).view(4, 8, 3)
+    assert set(d.unique().tolist()) <= {0.0, 2.0} and all(len(d[b].unique()) == 1 for b in range(4))   # whole sequences
