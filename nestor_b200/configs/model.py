@@ -244,9 +244,9 @@ class NestorConfig(BackboneConfig):
             raise ValueError("pooling_keep_ratios / num_global_tokens must stay at defaults.")
         if not 0.0 <= self.drop_path_rate < 1.0:
             raise ValueError("drop_path_rate must be in [0, 1).")
-        if self.block_residual_mode not in ("attn_res_kimi", "attn_res_column", "projection"):
+        if self.block_residual_mode not in ("attn_res_kimi", "attn_res_column", "projection", "attn_res"):
             raise ValueError(
-                "block_residual_mode must be 'projection', 'attn_res_kimi' or 'attn_res_column', got "
+                "block_residual_mode must be 'projection', 'attn_res', 'attn_res_kimi' or 'attn_res_column', got "
                 f"{self.block_residual_mode!r}."
             )
         if self.residual_mode != "convex":
@@ -348,7 +348,7 @@ class NestorConfig(BackboneConfig):
         """Whether sublayers read a softmax-over-depth mixture (the two ``attn_res_*`` modes) or the plain residual
         stream (``projection``: ``x + m * update`` under the reference muP, the convex rule otherwise)."""
 
-        return self.block_residual_mode != "projection"
+        return self.block_residual_mode not in ("projection", "attn_res")
 
     def max_depth_sources(self) -> int:
         """Slots of the widest depth read: the embedding plus every block's exports."""

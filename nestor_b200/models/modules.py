@@ -148,3 +148,38 @@ class DenseExpert(nn.Module):
             Matrix(hidden, dim, muon_matrix(dim, hidden), out_std),
         ])
         self.gate = Matrix(dim, hidden, muon_matrix(hidden, dim), std)
+
+
+class BlockAttentionResidual(nn.Module):
+    """Softmax-over-depth mixture of earlier block outputs with per-source key and value projections.
+
+    Source ``i`` (width ``source_widths[i]``) owns ``key_projections.{i}`` and ``value_projections.{i}`` into
+    ``target_width``; a zero-initialised query ``[1, target_width]`` scores the projected keys at every position, and
+    the output is the convex mixture of the projected values (fp32 softmax across sources). With the query at zero the
+    mixture is the plain mean. Used between blocks by ``block_residual_mode='attn_res'``
+    (reference ``nestor/backbones/attention_residual.py:259-392``).
+    """
+
+    def __init__(self, source_widths: list[int], target_width: int, std: float) -> None:
+        super().__init__()
+        if not source_widths or min(source_widths) < 1 or target_width < 1:
+            raise ValueError("BlockAttentionResidual needs at least one source and positive widths.")
+        self.source_widths, self.target_width = tuple(int(w) for w in source_widths), int(target_width)
+        mk = lambda w: Matrix(w, target_width, muon_matrix(target_width, w), std)   # noqa: E731
+        self.key_projections = nn.ModuleList([mk(w) for w in self.source_widths])
+        self.value_projections = nn.ModuleList([mk(w) for w in self.source_widths])
+        self.query = Matrix(target_width, 1, ParamTag("adamw", lr_mul=1.0 / target_width), 0.0)
+
+    def forward(self, sources: list[Tensor]) -> Tensor:
+        if len(sources) != len(self.source_widths):
+            raise ValueError(f"Expected {len(self.source_widths)} sources, got {len(sources)}.")
+        lead = sources[0].shape[:-1]
+        values, logits = [], []
+        for i, (src, w, kp, vp) in enumerate(zip(sources, self.source_widths, self.key_projections, self.value_projections)):
+            if src.shape[:-1] != lead or src.shape[-1] != w:
+                raise ValueError(f"Source {i} must have shape {tuple(lead) + (w,)}, got {tuple(src.shape)}.")
+            key = src @ kp.weight.t().to(src.dtype)
+            values.append(src @ vp.weight.t().to(src.dtype))
+            logits.append((key @ self.query.weight.t().to(src.dtype)).squeeze(-1))
+        weights = torch.stack(logits, dim=0).float().softmax(dim=0).to(values[0].dtype)
+        return (torch.stack(values, dim=0) * weights.unsqueeze(-1)).sum(dim=0)

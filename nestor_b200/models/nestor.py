@@ -31,7 +31,7 @@ from torch import Tensor, nn
 from nestor_b200 import ops
 from nestor_b200.configs.model import BlockSpec, NestorConfig, ReferenceMupConfig
 from nestor_b200.models.modules import (
-    ColumnProjections, DenseExpert, DepthRead, ExpertBank, Matrix, Norm, RouterParams,
+    BlockAttentionResidual, ColumnProjections, DenseExpert, DepthRead, ExpertBank, Matrix, Norm, RouterParams,
 )
 from nestor_b200.models.tags import ADAMW_DECAY
 
@@ -327,7 +327,7 @@ class Block(nn.Module):
 
     def forward(self, x: Tensor, sources: list[Tensor], B: int, S: int, cd: torch.dtype,
                 pos: Tensor | None, column_mode: bool, noise: Tensor | None = None,
-                cache: list | None = None) -> tuple[list[Tensor], Tensor, dict]:
+                cache: list | None = None, key_cache: Any = None) -> tuple[list[Tensor], Tensor, dict]:
         """Run the block. ``x [T, d]`` feeds the router; ``sources`` are the completed aggregates. With ``cache`` (one
         ``LayerKVCache`` per layer) the rows are one new token per sequence and attention runs against the cache.
 
@@ -347,12 +347,13 @@ class Block(nn.Module):
         layer_aux = []
         for li, layer in enumerate(self.layers):
             read = sources if running is None else [*sources, running]
+            kc = {} if key_cache is None else {"key_cache": key_cache}     # scales of the completed sources, shared by all reads
             n = ops.depth_read_norm(read, layer.kimi_attn_read.query, layer.kimi_attn_read.value_gains,
-                                    layer.attn_norm.weight, layer.kimi_attn_read.eps, layer.attn_norm.eps, cd)
+                                    layer.attn_norm.weight, layer.kimi_attn_read.eps, layer.attn_norm.eps, cd, **kc)
             attn = layer.attention(n, ctx, cd) if cache is None else layer.attention_step(n, ctx, cd, cache[li])   # [T, k, d]
             mid = ops.mid_source(running, attn)
             n = ops.depth_read_norm([*sources, mid], layer.kimi_mlp_read.query, layer.kimi_mlp_read.value_gains,
-                                    layer.mlp_norm.weight, layer.kimi_mlp_read.eps, layer.mlp_norm.eps, cd)
+                                    layer.mlp_norm.weight, layer.kimi_mlp_read.eps, layer.mlp_norm.eps, cd, **kc)
             priv, shared, path, aux = layer.experts(n, ctx, cd)
             if layer.drop_path > 0.0 and self.training:
                 attn = layer.drop(attn, B)
@@ -431,6 +432,12 @@ class Nestor(nn.Module):
              for i, s in enumerate(self.specs)])
         if self.depth_reads:
             self.final_depth_read = DepthRead(config.output_dim, self.max_depth_sources)
+        # 'attn_res': plain residual blocks joined by a per-source key/value mixture of the block outputs so far
+        self.block_attention_residuals: nn.ModuleList | None = None
+        if config.block_residual_mode == "attn_res":
+            d, emb = config.input_dim, int(config.block_attn_res_include_embedding)
+            self.block_attention_residuals = nn.ModuleList(
+                [BlockAttentionResidual([d] * (b + 1 + emb), d, std=1.0 / math.sqrt(d)) for b in range(len(self.specs))])
         self.final_norm = Norm(config.output_dim, init.norm_eps)
         if self.depth_reads and self.column_mode and config.block_column_gain_init != 1.0:
             # Head-read gains: deviation slots of every multi-column block start at the
@@ -475,6 +482,8 @@ class Nestor(nn.Module):
                 x = exports[-1]
                 wide.extend(exports)
                 narrow = [*narrow, x]
+                if self.block_attention_residuals is not None:
+                    x = self._mix_block_outputs(len(aux), narrow)
                 aux.append(a)
             h = self._head_input(wide, narrow, x, cd)
         cache.length += 1
@@ -493,19 +502,37 @@ class Nestor(nn.Module):
         # backward pass (the reference's per-block checkpointing, nestor/train/activation_offload.py:13-35). The
         # recomputation replays the random state, and the kernels are deterministic, so routing repeats exactly.
         recompute = os.environ.get("NESTOR_ACTIVATION_CHECKPOINT") == "1" and torch.is_grad_enabled() and self.training
+        # Key scales of the completed sources are shared by every sublayer read (NESTOR_NO_DEPTH_KEY_CACHE=1 turns the
+        # sharing off). Off under recomputation, as in the reference (nestor/backbones/nestor.py:10334-10346): a replayed
+        # block must not pick up tensors of the first pass. The fused kernel ignores it (the scale is free there).
+        key_cache = None
+        if (self.depth_reads and not recompute and not ops.use_kernels(x0)
+                and os.environ.get("NESTOR_NO_DEPTH_KEY_CACHE") != "1"):
+            key_cache = ops.DepthKeyCache(narrow, eps=self.final_depth_read.eps)
+        self.last_key_cache = key_cache
         for i, block in enumerate(self.blocks):
             noise = None if noises is None else noises[i]
             if recompute:
                 from torch.utils.checkpoint import checkpoint
                 exports, x, a = checkpoint(block, x, narrow, B, S, cd, pos, self.column_mode, noise, use_reentrant=False)
             else:
-                exports, x, a = block(x, narrow, B, S, cd, pos, self.column_mode, noise)
+                exports, x, a = block(x, narrow, B, S, cd, pos, self.column_mode, noise, key_cache=key_cache)
             exports = [ops.grad_sink(e) for e in exports]
             x = exports[-1]      # the aggregate is the block's last export
             wide.extend(exports)
             narrow = [*narrow, x]
+            if key_cache is not None:
+                key_cache.extend([x])
+            if self.block_attention_residuals is not None:
+                x = self._mix_block_outputs(i, narrow)
             aux.append(a)
         return self._head_input(wide, narrow, x, cd), {"blocks": aux}
+
+    def _mix_block_outputs(self, block_index: int, narrow: list[Tensor]) -> Tensor:
+        """Input of the next block in 'attn_res' mode: the mixture of the embedding (optional) and the block outputs."""
+
+        srcs = narrow if self.config.block_attn_res_include_embedding else narrow[1:]
+        return self.block_attention_residuals[block_index](srcs)
 
     def _head_input(self, wide: list[Tensor], narrow: list[Tensor], x: Tensor, cd: torch.dtype) -> Tensor:
         """The normalised head input: the final depth read over every export, or (projection mode) the stream itself."""

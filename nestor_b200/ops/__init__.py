@@ -15,7 +15,7 @@ import torch
 
 from nestor_b200.ops import reference as _ref
 from nestor_b200.ops.reference import (  # noqa: F401  (plans + pure helpers are shared)
-    ColumnPlan, ExpertPlan, NS_COEFFS, RoutingTape, apply_rope, rope_tables, set_routing_tape,
+    ColumnPlan, DepthKeyCache, ExpertPlan, NS_COEFFS, RoutingTape, apply_rope, rope_tables, set_routing_tape,
 )
 
 _FORCE_REF = os.environ.get("NESTOR_B200_REFERENCE_OPS") == "1"

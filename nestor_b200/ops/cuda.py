@@ -585,9 +585,10 @@ class _DepthReadNorm(torch.autograd.Function):
         return (dq.to(qd), dg.to(gd), dw.to(wd), None, None, *grads)
 
 
-def depth_read_norm(sources, query, gains, gamma, eps_read, eps_norm, out_dtype):
+def depth_read_norm(sources, query, gains, gamma, eps_read, eps_norm, out_dtype, key_cache=None):
+    # (a key cache is accepted and ignored: the kernel derives every source's scale inside its one pass)
     if out_dtype != BF16:
-        return ref.depth_read_norm(sources, query, gains, gamma, eps_read, eps_norm, out_dtype)
+        raise RuntimeError("the fused depth-read kernel writes bf16; run full-precision evaluation under ops.oracle_ops()")
     return _DepthReadNorm.apply(query, gains, gamma, float(eps_read), float(eps_norm), *sources)
 
 

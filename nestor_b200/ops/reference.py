@@ -153,20 +153,61 @@ def grad_sink(x: Tensor) -> Tensor:
     return x
 
 
-def depth_read(sources: list[Tensor], query: Tensor, gains: Tensor, eps: float = 1e-6) -> Tensor:
+class DepthKeyCache:
+    """Key scales ``r_i = rsqrt(mean(s_i^2) + eps)`` of depth sources that many reads share.
+
+    The key map of a depth read has no learnable weight, so a source's scale does not depend on the read: every
+    sublayer read of a forward pass sees the same embedding and completed-block sources and only its own tail
+    changes. The cache holds the leading sources (by object identity) and their scales, computed lazily once and
+    reused by every ``depth_read(..., key_cache=cache)``; the list grows with ``extend`` as blocks complete. Pure
+    common-subexpression elimination: results are bit-identical to uncached reads (reference
+    ``nestor/backbones/attention_residual.py:171-256``). The fused GPU kernel recomputes the scale inside its single
+    pass over the sources (it is free there), so the cache serves the PyTorch statement of the op (CPU / evaluation).
+    """
+
+    def __init__(self, sources: list[Tensor] | tuple = (), *, eps: float = 1e-6) -> None:
+        self.sources = list(sources)
+        self.eps = float(eps)
+        self._scales: list[Tensor] = []
+        self.computed = 0           # how many scale reductions the cache has run (for tests and accounting)
+
+    @property
+    def num_sources(self) -> int:
+        return len(self.sources)
+
+    def extend(self, sources) -> None:
+        self.sources.extend(sources)
+
+    def scales(self) -> list[Tensor]:
+        for s in self.sources[len(self._scales):]:
+            self._scales.append(torch.rsqrt(s.float().pow(2).mean(dim=-1) + self.eps))
+            self.computed += 1
+        return self._scales
+
+
+def depth_read(sources: list[Tensor], query: Tensor, gains: Tensor, eps: float = 1e-6,
+               key_cache: DepthKeyCache | None = None) -> Tensor:
     """Softmax-over-depth mixture of unit-RMS sources (fp32).
 
     ``r_i = rsqrt(mean(s_i^2) + eps)``, ``z_i = r_i (s_i . q) / sqrt(d)``,
-    ``w = softmax_i(z) * gain_i``, ``out = sum_i (w_i r_i) s_i``. Sources are ``[..., d]``.
+    ``w = softmax_i(z) * gain_i``, ``out = sum_i (w_i r_i) s_i``. Sources are ``[..., d]``. ``key_cache`` supplies the
+    scales of the leading sources (which must be the very tensors it holds).
     """
 
     d = sources[0].shape[-1]
     n = len(sources)
     q = query.float()
+    cached: list[Tensor] = []
+    if key_cache is not None:
+        if key_cache.eps != eps:
+            raise ValueError("the key cache was built with a different epsilon than this read")
+        if key_cache.num_sources > n or any(a is not b for a, b in zip(key_cache.sources, sources)):
+            raise ValueError("the leading sources of a cached read must be the cache's own tensors, in order")
+        cached = key_cache.scales()[: key_cache.num_sources]
     r, z = [], []
-    for s in sources:
+    for i, s in enumerate(sources):
         s32 = s.float()
-        ri = torch.rsqrt(s32.pow(2).mean(dim=-1) + eps)
+        ri = cached[i] if i < len(cached) else torch.rsqrt(s32.pow(2).mean(dim=-1) + eps)
         r.append(ri)
         z.append(ri * (s32 @ q))
     r_all = torch.stack(r, dim=-1)
@@ -179,10 +220,10 @@ def depth_read(sources: list[Tensor], query: Tensor, gains: Tensor, eps: float =
 
 
 def depth_read_norm(sources: list[Tensor], query: Tensor, gains: Tensor, gamma: Tensor, eps_read: float,
-                    eps_norm: float, out_dtype: torch.dtype) -> Tensor:
+                    eps_norm: float, out_dtype: torch.dtype, key_cache: DepthKeyCache | None = None) -> Tensor:
     """``rmsnorm(depth_read(sources))``: the input of every attention / expert half and of the head."""
 
-    return rmsnorm(depth_read(sources, query, gains, eps_read), gamma, eps_norm, out_dtype)
+    return rmsnorm(depth_read(sources, query, gains, eps_read, key_cache), gamma, eps_norm, out_dtype)
 
 
 def mid_source(running: Tensor | None, attn: Tensor) -> Tensor:

@@ -221,10 +221,11 @@ def test_eval_forward_reports_routing_probability_sums(tiny_scale):
     assert "routing/blocks.0.group_router/prob/c0" in metrics and "routing/group/mean_max_prob" in metrics
 
 
-@pytest.mark.parametrize("family", ["moe", "dense"])
-def test_projection_residual_mode_matches_reference(family, tiny_scale, monkeypatch):
-    """``block_residual_mode='projection'`` (plain residual stream, ``x + 0.22 u`` under the reference muP): same
-    state-dict keys as the reference model in that mode, same logits, same gradients."""
+@pytest.mark.parametrize("family,mode", [("moe", "projection"), ("dense", "projection"), ("dense", "attn_res")])
+def test_projection_residual_mode_matches_reference(family, mode, tiny_scale, monkeypatch):
+    """``block_residual_mode='projection'`` (plain residual stream, ``x + 0.22 u`` under the reference muP) and
+    ``'attn_res'`` (the same blocks joined by per-source key/value mixtures of the block outputs): same state-dict keys
+    as the reference model in that mode, same logits, same gradients."""
 
     import dataclasses as dc
     ref_root = ROOT / "baseline" / "_ref"
@@ -245,10 +246,14 @@ def test_projection_residual_mode_matches_reference(family, tiny_scale, monkeypa
         monkeypatch.setitem(RP.BATCH_SHAPE, (fam, "tiny"), (2, 1))
     torch.manual_seed(0)
     rcfg = {"moe": RP._moe, "dense": RP._dense}[family]("tiny").jobs[0].model
-    rcfg = dc.replace(rcfg, backbone_config=dc.replace(rcfg.backbone_config, block_residual_mode="projection"))
+    rcfg = dc.replace(rcfg, backbone_config=dc.replace(rcfg.backbone_config, block_residual_mode=mode))
     rm = RefModel.from_config(rcfg).eval()
+    with torch.no_grad():
+        for n, p in rm.named_parameters():
+            if n.endswith("query.weight"):
+                p.normal_(0, 0.5)
     cfg = P.build_experiment(family, "tiny").jobs[0].model
-    cfg = dc.replace(cfg, backbone_config=dc.replace(cfg.backbone_config, block_residual_mode="projection"))
+    cfg = dc.replace(cfg, backbone_config=dc.replace(cfg.backbone_config, block_residual_mode=mode))
     mm = Model.from_config(cfg).eval()
     assert set(mm.state_dict()) == set(rm.state_dict())
     mm.load_state_dict(rm.state_dict(), strict=True)
