@@ -12,6 +12,7 @@ eval "$(python -m nestor_b200.continual.protocols "$kind" --experiment "$experim
 export DCLM_GLOBAL_BATCH="${DCLM_GLOBAL_BATCH:-$gpus}"
 export DCLM_GRAD_ACCUM="${DCLM_GRAD_ACCUM:-$((CONTINUAL_SEQS_PER_STEP / DCLM_GLOBAL_BATCH))}"
 export NESTOR_ACTIVATION_OFFLOAD="${NESTOR_ACTIVATION_OFFLOAD:-0}"
+source "$here/memory_recipe.sh" "$experiment" "${DCLM_BLOCK_SIZE:-4096}"
 export WANDB_MODE="${WANDB_MODE:-disabled}"
 exec python -m torch.distributed.run --standalone --local-addr 127.0.0.1 --nproc-per-node "$gpus" \
   -m nestor_b200.cli --experiment "$experiment"

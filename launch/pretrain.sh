@@ -14,6 +14,7 @@ if [[ -n "$seqs" && -z "${DCLM_GLOBAL_BATCH:-}" ]]; then
   export DCLM_GLOBAL_BATCH=$((per_gpu * gpus))
   export DCLM_GRAD_ACCUM=$((seqs / DCLM_GLOBAL_BATCH))
 fi
+source "$here/memory_recipe.sh" "$experiment" "${DCLM_BLOCK_SIZE:-4096}"
 export WANDB_MODE="${WANDB_MODE:-disabled}"
 exec python -m torch.distributed.run --standalone --local-addr 127.0.0.1 --nproc-per-node "$gpus" \
   -m nestor_b200.cli --experiment "$experiment"

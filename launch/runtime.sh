@@ -8,7 +8,12 @@ export NESTOR_STACKED_EXPERT_BANKS="${NESTOR_STACKED_EXPERT_BANKS:-1}" # checkpo
 export NESTOR_MUON_SHARD="${NESTOR_MUON_SHARD:-1}"                    # one owner rank per Muon matrix
 export NESTOR_ZERO1="${NESTOR_ZERO1:-1}"                              # AdamW state sharded like Muon (owner of an arena range updates it)
 export NESTOR_FSDP_BANKS="${NESTOR_FSDP_BANKS:-0}"                      # expert banks read from their owner ranks inside the bank GEMMs (slower than replicated banks on 2 GPUs; saves no memory yet)
-export NESTOR_ACTIVATION_CHECKPOINT="${NESTOR_ACTIVATION_CHECKPOINT:-0}" # recompute each block in the backward pass
+export NESTOR_ACTIVATION_CHECKPOINT="${NESTOR_ACTIVATION_CHECKPOINT:-0}" # recompute ladder, rung 1: every layer is a recomputed region
+export NESTOR_ACTIVATION_CHECKPOINT_SPLIT="${NESTOR_ACTIVATION_CHECKPOINT_SPLIT:-0}" # attention half and expert half are separate regions
+export NESTOR_ACTIVATION_CHECKPOINT_LEAN="${NESTOR_ACTIVATION_CHECKPOINT_LEAN:-0}"   # alias of the split (a half's inputs are [T, d] tensors only)
+export NESTOR_ACTIVATION_CHECKPOINT_BLOCK="${NESTOR_ACTIVATION_CHECKPOINT_BLOCK:-0}" # the whole block is one outer region
+export NESTOR_EXPERT_HALF_CHUNKS="${NESTOR_EXPERT_HALF_CHUNKS:-0}"     # expert half over n row chunks, one region each
+export NESTOR_ACTIVATION_OFFLOAD="${NESTOR_ACTIVATION_OFFLOAD:-0}"     # saved activations parked in pinned host memory
 export NESTOR_FUSED_HEAD_CE="${NESTOR_FUSED_HEAD_CE:-1}"              # chunked head + cross-entropy, no [T, V] logits
 export NESTOR_CE_CHUNK_ROWS="${NESTOR_CE_CHUNK_ROWS:-4096}"
 export NESTOR_RUNAHEAD="${NESTOR_RUNAHEAD:-0}"                        # host may run this many steps ahead of the GPU

@@ -287,6 +287,83 @@ class BlockContext:
     def __init__(self, B: int, S: int, idx: Tensor, gates: Tensor, plan: Any, pos: Tensor | None) -> None:
         self.B, self.S, self.idx, self.gates, self.plan, self.pos = B, S, idx, gates, plan, pos
 
+    def rows(self, a: int, b: int) -> "BlockContext":
+        """The routing state of token rows ``a:b`` (what a per-token op such as the expert half needs)."""
+
+        return BlockContext(self.B, self.S, self.idx[a:b], self.gates[a:b], None, None)
+
+
+class RecomputeLadder:
+    """Which parts of a block are recomputed in the backward pass instead of kept (all exact: the regions are pure
+    functions of their tensor arguments, the random state is replayed, the kernels are deterministic).
+
+    Flags, read at every forward (reference ``nestor/backbones/nestor.py:1077-1401``, launcher recipes
+    ``scripts/slurm_extend.sh:66-85``):
+
+    * ``NESTOR_ACTIVATION_CHECKPOINT=1``           every layer is a region (keeps ``streams [T, k, d]`` per layer);
+    * ``..._CHECKPOINT_SPLIT=1``                   the attention half and the expert half are separate regions;
+    * ``..._CHECKPOINT_LEAN=1``                    same split; named for what it keeps: a half's inputs here are the
+      ``[T, d]`` sources and running mean only, so split halves are lean by construction;
+    * ``..._CHECKPOINT_BLOCK=1``                   the whole block is one outer region (least memory, most recompute);
+    * ``NESTOR_EXPERT_HALF_CHUNKS=n``              the expert half runs over ``n`` row chunks, one region each;
+    * ``NESTOR_DENSE_TAIL_QUERY_CHUNKS``           accepted for launcher compatibility, no effect: the attention
+      kernels never materialise scores, which is what that rung saved.
+    """
+
+    def __init__(self, on: bool, split: bool, block: bool, chunks: int) -> None:
+        self.on, self.split, self.block, self.chunks = on, split, block, chunks
+
+    @classmethod
+    def current(cls, active: bool) -> "RecomputeLadder":
+        env = os.environ.get
+        on = active and env("NESTOR_ACTIVATION_CHECKPOINT") == "1" and torch.is_grad_enabled()
+        split = env("NESTOR_ACTIVATION_CHECKPOINT_SPLIT") == "1" or env("NESTOR_ACTIVATION_CHECKPOINT_LEAN") == "1"
+        return cls(on, split, env("NESTOR_ACTIVATION_CHECKPOINT_BLOCK") == "1", int(env("NESTOR_EXPERT_HALF_CHUNKS") or 0))
+
+    @property
+    def any(self) -> bool:
+        return self.on
+
+    @property
+    def outer(self) -> bool:
+        """The block itself is the region (the layers inside run plainly)."""
+
+        return self.on and self.block
+
+    def expert_chunks(self, rows: int) -> list[tuple[int, int]] | None:
+        if not self.on or self.block or self.chunks <= 1:
+            return None
+        step = -(-rows // self.chunks)
+        return [(a, min(rows, a + step)) for a in range(0, rows, step)]
+
+    def region(self, level: str, fn, *args):
+        """Run ``fn(*args)``, as a recomputed region when this rung of the ladder asks for it."""
+
+        use = self.on and not self.block and (
+            (level == "layer" and not self.split and self.chunks <= 1)
+            or (level == "half" and (self.split or self.chunks > 1))
+            or level == "chunk")
+        if not use:
+            return fn(*args)
+        from torch.utils.checkpoint import checkpoint
+        return checkpoint(fn, *args, use_reentrant=False)
+
+
+def _merge_chunk_aux(parts: list[dict]) -> dict:
+    """Routing records of an expert half that ran in row chunks: per-token tensors are concatenated; per-chunk
+    dispatch offsets are dropped (the statistics fall back to counting the indices)."""
+
+    out: dict = {}
+    for key in parts[0]:
+        vals = [p[key] for p in parts]
+        if key.endswith("_offsets") or key.endswith("_prob"):
+            continue
+        if isinstance(vals[0], Tensor):
+            out[key] = torch.cat(vals, dim=0)
+        elif isinstance(vals[0], dict):
+            out[key] = _merge_chunk_aux(vals)
+    return out
+
 
 class Block(nn.Module):
     def __init__(self, s: BlockSpec, init: InitScales, max_sources: int, dense_no_router: bool,
@@ -345,22 +422,48 @@ class Block(nn.Module):
         streams: Tensor | None = None      # [T, k, d] fp32
         running: Tensor | None = None      # [T, d] fp32 = mean_j streams
         layer_aux = []
-        for li, layer in enumerate(self.layers):
-            read = sources if running is None else [*sources, running]
-            kc = {} if key_cache is None else {"key_cache": key_cache}     # scales of the completed sources, shared by all reads
-            n = ops.depth_read_norm(read, layer.kimi_attn_read.query, layer.kimi_attn_read.value_gains,
+        rung = RecomputeLadder.current(self.training and cache is None)
+        kc = {} if key_cache is None or rung.any else {"key_cache": key_cache}   # scales of the completed sources, shared by all reads
+        nsrc = len(sources)
+
+        def attn_half(layer, li, *tensors):
+            # tensors = completed sources (+ the running mean from the second layer on): [T, d] each
+            n = ops.depth_read_norm(list(tensors), layer.kimi_attn_read.query, layer.kimi_attn_read.value_gains,
                                     layer.attn_norm.weight, layer.kimi_attn_read.eps, layer.attn_norm.eps, cd, **kc)
-            attn = layer.attention(n, ctx, cd) if cache is None else layer.attention_step(n, ctx, cd, cache[li])   # [T, k, d]
-            mid = ops.mid_source(running, attn)
-            n = ops.depth_read_norm([*sources, mid], layer.kimi_mlp_read.query, layer.kimi_mlp_read.value_gains,
+            return layer.attention(n, ctx, cd) if cache is None else layer.attention_step(n, ctx, cd, cache[li])   # [T, k, d]
+
+        def expert_half(layer, c, *tensors):
+            # tensors = completed sources + the mid-layer source, [T, d] each; c = (row begin, row end) or None
+            n = ops.depth_read_norm(list(tensors), layer.kimi_mlp_read.query, layer.kimi_mlp_read.value_gains,
                                     layer.mlp_norm.weight, layer.kimi_mlp_read.eps, layer.mlp_norm.eps, cd, **kc)
-            priv, shared, path, aux = layer.experts(n, ctx, cd)
+            return layer.experts(n, ctx if c is None else ctx.rows(*c), cd)
+
+        def one_layer(layer, li, streams, running, *srcs):
+            read = list(srcs) if running is None else [*srcs, running]
+            attn = rung.region("half", attn_half, layer, li, *read)
+            mid = ops.mid_source(running, attn)
+            chunks = rung.expert_chunks(mid.shape[0]) if cache is None else None
+            if chunks is None:
+                priv, shared, path, aux = rung.region("half", expert_half, layer, None, *srcs, mid)
+            else:
+                # the expert half over row chunks, each its own region: its activations never exist for all rows at once
+                parts = [rung.region("chunk", expert_half, layer, (a, b), *[t[a:b] for t in srcs], mid[a:b])
+                         for a, b in chunks]
+                priv = None if parts[0][0] is None else torch.cat([p[0] for p in parts], dim=0)
+                shared = torch.cat([p[1] for p in parts], dim=0)
+                path = None if parts[0][2] is None else torch.cat([p[2] for p in parts], dim=0)
+                aux = _merge_chunk_aux([p[3] for p in parts])
             if layer.drop_path > 0.0 and self.training:
                 attn = layer.drop(attn, B)
                 shared = layer.drop(shared, B)
                 priv = None if priv is None else layer.drop(priv, B)
             streams, running = ops.layer_combine(attn, priv, shared, path, streams, running, cd)
+            return streams, running, aux
+
+        for li, layer in enumerate(self.layers):
+            streams, running, aux = rung.region("layer", one_layer, layer, li, streams, running, *sources)
             layer_aux.append(aux)
+        assert len(sources) == nsrc
         if column_mode and s.k > 1:
             dev, agg = ops.block_exit(streams)
             exports = [*dev.unbind(dim=0), agg]
@@ -501,7 +604,12 @@ class Nestor(nn.Module):
         # NESTOR_ACTIVATION_CHECKPOINT=1: keep only each block's inputs and recompute its activations in the
         # backward pass (the reference's per-block checkpointing, nestor/train/activation_offload.py:13-35). The
         # recomputation replays the random state, and the kernels are deterministic, so routing repeats exactly.
-        recompute = os.environ.get("NESTOR_ACTIVATION_CHECKPOINT") == "1" and torch.is_grad_enabled() and self.training
+        rung = RecomputeLadder.current(self.training)
+        recompute = rung.any
+        if recompute and noises is None and self.training:
+            # router noise is drawn here, outside every recomputed region, so a region is a pure function of its inputs
+            noises = [torch.randn(x0.shape[0], b.spec.G, device=x0.device) if b.spec.G > 1 and b.group_router.noise_mlp is not None
+                      else None for b in self.blocks]
         # Key scales of the completed sources are shared by every sublayer read (NESTOR_NO_DEPTH_KEY_CACHE=1 turns the
         # sharing off). Off under recomputation, as in the reference (nestor/backbones/nestor.py:10334-10346): a replayed
         # block must not pick up tensors of the first pass. The fused kernel ignores it (the scale is free there).
@@ -512,7 +620,7 @@ class Nestor(nn.Module):
         self.last_key_cache = key_cache
         for i, block in enumerate(self.blocks):
             noise = None if noises is None else noises[i]
-            if recompute:
+            if rung.outer:
                 from torch.utils.checkpoint import checkpoint
                 exports, x, a = checkpoint(block, x, narrow, B, S, cd, pos, self.column_mode, noise, use_reentrant=False)
             else:
