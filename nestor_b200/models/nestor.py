@@ -33,6 +33,7 @@ from nestor_b200.configs.model import BlockSpec, NestorConfig, ReferenceMupConfi
 from nestor_b200.models.modules import (
     BlockAttentionResidual, ColumnProjections, DenseExpert, DepthRead, ExpertBank, Matrix, Norm, RouterParams,
 )
+from nestor_b200.models.registry import Backbone
 from nestor_b200.models.tags import ADAMW_DECAY
 
 
@@ -512,7 +513,7 @@ class Block(nn.Module):
         return [x], x, baux
 
 
-class Nestor(nn.Module):
+class Nestor(Backbone):
     """The backbone: blocks, the final head read over every export, the final RMSNorm."""
 
     def __init__(self, config: NestorConfig, mup: ReferenceMupConfig | None = None,

@@ -21,6 +21,9 @@ from nestor_b200.configs.model import (
 )
 from nestor_b200.models.modules import LayerStack, Matrix
 from nestor_b200.models.nestor import Nestor, W
+from nestor_b200.models.registry import (
+    ADAPTERS, BACKBONES, HEADS, MODELS, register_adapter, register_backbone, register_head, register_model,
+)
 from nestor_b200.models.tags import ADAMW_DECAY, tag
 
 
@@ -45,6 +48,7 @@ class ByteTokenizer:
         return bytes(int(i) & 0xFF for i in ids).decode("utf-8", errors="replace")
 
 
+@register_adapter(TextAdapterConfig)
 class TextAdapter(nn.Module):
     """Token embedding table; output ``E[ids] * embedding_multiplier`` in fp32.
 
@@ -100,6 +104,7 @@ class TextAdapter(nn.Module):
         return self.embed(ids).float() * self.embedding_multiplier
 
 
+@register_head(LanguageModelingHeadConfig)
 class LanguageModelingHead(nn.Module):
     """Single-matrix unembedding ``[V, d]``; ``logit_multiplier = 1 / width_multiplier`` under muP."""
 
@@ -120,8 +125,12 @@ class LanguageModelingHead(nn.Module):
         return (h.to(cd) @ W(self, self.weight).to(cd).t()) * self.logit_multiplier
 
 
+register_backbone(NestorConfig)(lambda config, mup, **kw: Nestor(config, mup, **kw))
+
+
+@register_model(SequenceModelConfig)
 class SequenceModel(nn.Module):
-    """adapter -> backbone -> head.
+    """adapter -> backbone -> head, each built from its config through the registries.
 
     ``fused_head=True`` (the training default) returns the normalised head input as ``pred``
     and exposes the head through ``aux["fused_head_module"]`` so the loss can run the
@@ -132,18 +141,12 @@ class SequenceModel(nn.Module):
         super().__init__()
         self.config = config
         mup = config.reference_mup
-        if not isinstance(config.adapter_config, TextAdapterConfig):
-            raise TypeError("SequenceModel needs a TextAdapterConfig.")
-        if not isinstance(config.backbone_config, NestorConfig):
-            raise TypeError("SequenceModel needs a NestorConfig backbone.")
-        if not isinstance(config.head_config, LanguageModelingHeadConfig):
-            raise TypeError("SequenceModel needs a LanguageModelingHeadConfig.")
         if config.adapter_config.embed_dim != config.backbone_config.input_dim:
             raise ValueError("adapter embed_dim must equal backbone input_dim.")
         dense_no_router = os.environ.get("NESTOR_DENSE_NO_ROUTER", "1") == "1"
-        self.adapter = TextAdapter(config.adapter_config, mup)
-        self.backbone = Nestor(config.backbone_config, mup, dense_no_router=dense_no_router)
-        self.head = LanguageModelingHead(config.head_config, config.backbone_config.output_dim, mup)
+        self.adapter = ADAPTERS.build(config.adapter_config, mup)
+        self.backbone = BACKBONES.build(config.backbone_config, mup, dense_no_router=dense_no_router)
+        self.head = HEADS.build(config.head_config, self.backbone.output_dim, mup)
         self.fused_head = False
         self.compute_dtype: torch.dtype | None = None
 
@@ -236,10 +239,8 @@ class SequenceModel(nn.Module):
 
 
 class Model:
-    """Factory namespace: ``Model.from_config(SequenceModelConfig) -> SequenceModel``."""
+    """Factory namespace: ``Model.from_config(config)`` builds whatever model is registered for the config's type."""
 
     @staticmethod
-    def from_config(config: Any) -> SequenceModel:
-        if isinstance(config, SequenceModelConfig):
-            return SequenceModel(config)
-        raise TypeError(f"Unknown model config {type(config).__name__}.")
+    def from_config(config: Any) -> nn.Module:
+        return MODELS.build(config)

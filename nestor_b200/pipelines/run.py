@@ -78,6 +78,10 @@ class RunContext:
             sha = get_git_sha()
             if sha:
                 (self.run_dir / "git_sha.txt").write_text(sha + "\n")
+            if getattr(experiment, "save_source_snapshot", False):
+                from nestor_b200.utils.snapshot import snapshot_sources
+                repo = Path(__file__).resolve().parents[2]
+                snapshot_sources(repo, self.run_dir / "source_snapshot.zip")
             self.logger.info("Run directory: %s", self.run_dir)
         barrier()
         self.wandb_run = None

@@ -134,3 +134,19 @@ def test_long_context_nll_and_frozen_routers(tiny_scale):
     m.train()
     a = m(ids).aux["blocks"][0]["group_idx"]; b = m(ids).aux["blocks"][0]["group_idx"]
     assert torch.equal(a, b)                                        # no exploration noise once frozen
+
+
+def test_source_snapshot_keeps_sources_and_prunes_the_rest(tmp_path):
+    import zipfile
+    from nestor_b200.utils.snapshot import snapshot_sources, source_files
+    root = tmp_path / "repo"
+    for rel, text in {"pkg/a.py": "x = 1", "pkg/csrc/k.cu": "__global__ void k(){}", "pkg/_C/lib.so": "bin",
+                      "pkg/__pycache__/a.pyc": "", "outputs/run/model.pt": "w", "data/train.bin": "t", ".git/HEAD": "ref",
+                      "README.md": "# hi", "pkg/notes.ckpt": "c", "big.txt": "y" * 64}.items():
+        f = root / rel
+        f.parent.mkdir(parents=True, exist_ok=True)
+        f.write_text(text)
+    names = {p.as_posix() for p in source_files(root)}
+    assert names == {"pkg/a.py", "pkg/csrc/k.cu", "README.md", "big.txt"}
+    out = snapshot_sources(root, tmp_path / "run" / "source_snapshot", max_file_bytes=32)
+    assert out.suffix == ".zip" and set(zipfile.ZipFile(out).namelist()) == names - {"big.txt"}

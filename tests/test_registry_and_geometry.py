@@ -109,6 +109,32 @@ def test_config_validation():
     with pytest.raises(ValueError):
         NestorConfig(**{**base, "causal": False}).resolve()
     with pytest.raises(ValueError):
-        NestorConfig(**{**base, "block_residual_mode": "projection"}).resolve()
+        NestorConfig(**{**base, "block_residual_mode": "no_such_mode"}).resolve()
+    NestorConfig(**{**base, "block_residual_mode": "projection"}).resolve()      # plain residual blocks are a supported mode
     with pytest.raises(ValueError):
         NestorConfig(**{**base, "num_groups": 2, "num_groups_per_token": 3}).resolve()
+
+
+def test_part_registries_dispatch_on_config_type():
+    import dataclasses as dc
+    import pytest
+    from nestor_b200.configs.model import LanguageModelingHeadConfig, NestorConfig, SequenceModelConfig, TextAdapterConfig
+    from nestor_b200.models import Backbone, Nestor, SequenceModel, TextAdapter
+    from nestor_b200.models.registry import ADAPTERS, BACKBONES, HEADS, MODELS, Registry
+    assert MODELS.registered()[SequenceModelConfig] is SequenceModel and ADAPTERS.registered()[TextAdapterConfig] is TextAdapter
+    assert NestorConfig in BACKBONES.registered() and LanguageModelingHeadConfig in HEADS.registered()
+    assert issubclass(Nestor, Backbone)
+
+    @dc.dataclass
+    class Special(TextAdapterConfig):       # a subclassed config builds its parent's part
+        pass
+
+    a = ADAPTERS.build(Special(vocab_size=50, embed_dim=8), None)
+    assert isinstance(a, TextAdapter)
+    r = Registry("widget")
+    with pytest.raises(TypeError, match="no widget registered"):
+        r.build(object())
+    r.register(int)(lambda c: c + 1)
+    assert r.build(True) == 2                # bool -> int through the MRO
+    with pytest.raises(ValueError, match="already registered"):
+        r.register(int)(lambda c: c)
