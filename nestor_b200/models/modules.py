@@ -101,6 +101,25 @@ class RouterParams(nn.Module):
         self.score_mlp = mlp()
         self.noise_mlp = mlp() if noisy else None
         self.register_buffer("choice_bias", torch.zeros(choices))
+        # NESTOR_ROUTER_NOISE_ANNEAL_STEPS=n: the exploration noise fades linearly to zero over the first n training
+        # forwards; the forward counter is a persistent buffer (it is part of a checkpoint of such a run), reference
+        # nestor/backbones/nestor.py:478-484
+        import os
+        self.noise_anneal_steps = int(os.environ.get("NESTOR_ROUTER_NOISE_ANNEAL_STEPS", "0") or 0) if noisy else 0
+        if self.noise_anneal_steps > 0:
+            self.register_buffer("_noise_steps", torch.zeros((), dtype=torch.long))
+
+    def noise_scale(self, advance: bool) -> Tensor | None:
+        """``1 - min(steps / anneal, 1)`` as a device scalar (``None`` when the noise does not anneal). ``advance``
+        counts this forward; recomputed regions and self-checks pass ``False`` so that the schedule follows the
+        optimizer's steps, not the number of times a forward is replayed."""
+
+        if self.noise_anneal_steps <= 0:
+            return None
+        scale = 1.0 - (self._noise_steps.float() / self.noise_anneal_steps).clamp(max=1.0)
+        if advance:
+            self._noise_steps += 1
+        return scale
 
     def weights(self, which: str = "score") -> tuple[Tensor | None, Tensor]:
         stack = self.score_mlp if which == "score" else self.noise_mlp

@@ -397,6 +397,7 @@ class Block(nn.Module):
         if self.training and r.noise_mlp is not None and not getattr(self, "freeze_routing_noise", False):
             eps = torch.randn_like(scores) if noise is None else noise.to(scores.dtype)
             n1, n2 = r.weights("noise")
+            # (an annealing schedule, if any, is already folded into ``noise`` by the backbone: see Nestor.forward)
             scores = scores + eps * torch.nn.functional.softplus(ops.router_scores(x, W(self, n1), W(self, n2), cd))
         if not self.training and not torch.is_grad_enabled():
             self._last_group_prob = torch.softmax(scores.float(), dim=-1).sum(0)
@@ -607,10 +608,21 @@ class Nestor(Backbone):
         # recomputation replays the random state, and the kernels are deterministic, so routing repeats exactly.
         rung = RecomputeLadder.current(self.training)
         recompute = rung.any
-        if recompute and noises is None and self.training:
-            # router noise is drawn here, outside every recomputed region, so a region is a pure function of its inputs
-            noises = [torch.randn(x0.shape[0], b.spec.G, device=x0.device) if b.spec.G > 1 and b.group_router.noise_mlp is not None
-                      else None for b in self.blocks]
+        noisy = [b.spec.G > 1 and b.group_router.noise_mlp is not None for b in self.blocks]
+        anneal = self.training and any(b.group_router.noise_anneal_steps > 0 for b, n in zip(self.blocks, noisy) if n)
+        if self.training and (recompute or anneal):
+            # Router noise is drawn here, outside every recomputed region, so a region is a pure function of its
+            # inputs; an annealing schedule scales the draw here as well and counts this forward once (a replayed region
+            # sees the very same tensor again).
+            drawn = []
+            for i, (b, n) in enumerate(zip(self.blocks, noisy)):
+                if not n:
+                    drawn.append(None)
+                    continue
+                eps = torch.randn(x0.shape[0], b.spec.G, device=x0.device) if noises is None or noises[i] is None else noises[i]
+                fade = b.group_router.noise_scale(advance=True)
+                drawn.append(eps if fade is None else eps * fade.to(eps.dtype))
+            noises = drawn
         # Key scales of the completed sources are shared by every sublayer read (NESTOR_NO_DEPTH_KEY_CACHE=1 turns the
         # sharing off). Off under recomputation, as in the reference (nestor/backbones/nestor.py:10334-10346): a replayed
         # block must not pick up tensors of the first pass. The fused kernel ignores it (the scale is free there).

@@ -149,6 +149,9 @@ class SequenceModel(nn.Module):
         self.head = HEADS.build(config.head_config, self.backbone.output_dim, mup)
         self.fused_head = False
         self.compute_dtype: torch.dtype | None = None
+        # NESTOR_FASTPATH_CHECK=1: the first three kernel-path forwards are repeated on the PyTorch statement of the
+        # ops with the same routing and the largest difference is printed (reference nestor/backbones/nestor.py:4868-4884)
+        self._fastpath_checks = 3 if os.environ.get("NESTOR_FASTPATH_CHECK") == "1" else 0
 
     def resolve_compute_dtype(self, device: torch.device) -> torch.dtype:
         if self.compute_dtype is not None:
@@ -174,7 +177,14 @@ class SequenceModel(nn.Module):
         x0 = self.adapter(ids).reshape(B * S, -1)
         if valid is not None:
             x0 = x0 * valid.reshape(B * S, 1).to(x0.dtype)
-        h, aux = self.backbone(x0, B, S, cd, pos=pos, noises=noises)
+        if ids.is_cuda and cd != torch.bfloat16 and ops.use_kernels(ids):
+            # the kernels compute in bf16; a full-precision forward on a GPU is the PyTorch statement of every op
+            with ops.oracle_ops():
+                h, aux = self.backbone(x0, B, S, cd, pos=pos, noises=noises)
+        elif self._fastpath_checks > 0 and ops.use_kernels(ids) and not torch.cuda.is_current_stream_capturing():
+            h, aux = self._checked_forward(x0, B, S, cd, pos, noises)
+        else:
+            h, aux = self.backbone(x0, B, S, cd, pos=pos, noises=noises)
         if valid is not None:
             aux["valid_token_mask"] = valid
             aux["input_ids"] = ids
@@ -189,6 +199,27 @@ class SequenceModel(nn.Module):
             aux["fused_head_module"] = self.head
             return ModelOutput(pred=h.view(B, S, -1), aux=aux)
         return ModelOutput(pred=self.head(h, cd).view(B, S, -1), aux=aux)
+
+    def _checked_forward(self, x0: Tensor, B: int, S: int, cd: torch.dtype, pos, noises):
+        """Kernel-path forward followed by the same forward on the PyTorch ops, with the first pass's routing replayed
+        and the same router noise; prints ``[FASTPATH-CHECK] max|kernels - oracle|`` of the head input."""
+
+        self._fastpath_checks -= 1
+        if noises is None and self.training:
+            noises = [torch.randn(x0.shape[0], b.spec.G, device=x0.device) if b.spec.G > 1 else None
+                      for b in self.backbone.blocks]
+        tape = ops.RoutingTape()
+        ops.set_routing_tape(tape, "record")
+        try:
+            h, aux = self.backbone(x0, B, S, cd, pos=pos, noises=noises)
+            ops.set_routing_tape(tape, "replay")
+            with torch.no_grad(), ops.oracle_ops():
+                h_ref, _ = self.backbone(x0.detach(), B, S, cd, pos=pos, noises=noises)
+        finally:
+            ops.set_routing_tape(None)
+        diff = (h.detach().float() - h_ref.float()).abs().max().item()
+        print(f"[FASTPATH-CHECK] max|kernels - oracle| = {diff:.3e} (head input, {x0.shape[0]} tokens)", flush=True)
+        return h, aux
 
     # ------------------------------------------------------------------ incremental decoding
     def init_kv_cache(self, batch_size: int, max_len: int, device=None, dtype: torch.dtype = torch.float32):

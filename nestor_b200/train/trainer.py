@@ -91,6 +91,7 @@ class Trainer:
         self.zero = bool(self.param_push is not None and getattr(self.optimizer, "shard_adamw", False))
         # Device status word of the in-kernel collectives: a bounded peer wait that gave up leaves a nonzero code
         # there and the kernel returns without reducing / pushing. It is read back once per optimizer step.
+        self.nvtx = _env_flag("NESTOR_NVTX")
         self.phase_events: list | None = None     # set to [] to time the phases of the next update_weights
         self.peer_status: Tensor | None = None
         self._status_host: Tensor | None = None
@@ -131,6 +132,19 @@ class Trainer:
             return activation_offload()
         return contextlib.nullcontext()
 
+    @contextlib.contextmanager
+    def _nvtx(self, name: str):
+        """NVTX range around a phase of the step (``NESTOR_NVTX=1``): shows up in timeline profilers."""
+
+        on = self.nvtx and self.device.type == "cuda"
+        if on:
+            torch.cuda.nvtx.range_push(name)
+        try:
+            yield
+        finally:
+            if on:
+                torch.cuda.nvtx.range_pop()
+
     def train_step(self, batch: Any) -> tuple[LossOutput, dict[str, Tensor]]:
         """Forward + backward of one micro-batch; gradients accumulate into the arena.
 
@@ -141,9 +155,10 @@ class Trainer:
         keeps eager launches; activation offload and the eager profiler also disable capture.
         """
 
-        if self._graph_enabled and self.model.training:
-            return self._graphed_step(batch)
-        return self._eager_step(batch)
+        with self._nvtx("micro_batch"):
+            if self._graph_enabled and self.model.training:
+                return self._graphed_step(batch)
+            return self._eager_step(batch)
 
     def _graphed_step(self, batch: Any) -> tuple[LossOutput, dict[str, Tensor]]:
         inputs, _ = batch
@@ -251,6 +266,13 @@ class Trainer:
     def _mark(self, name: str) -> None:
         """Phase boundary of ``update_weights`` (CUDA events, only while ``phase_events`` is a list)."""
 
+        if self.nvtx and self.device.type == "cuda":
+            if name != "start":
+                torch.cuda.nvtx.range_pop()
+            if name != "rest":
+                nxt = {"start": "grad_reduce", "grad_reduce": "clip", "clip": "optimizer", "optimizer": "param_push",
+                       "param_push": "rest"}[name]
+                torch.cuda.nvtx.range_push(f"update/{nxt}")
         if self.phase_events is not None and self.device.type == "cuda":
             ev = torch.cuda.Event(enable_timing=True)
             ev.record()
@@ -310,6 +332,14 @@ class Trainer:
         peak = float(os.environ.get("NESTOR_MFU_PEAK_TFLOPS", "2250")) * 1e12
         flops_tok = float(os.environ.get("NESTOR_MFU_FLOPS_PER_TOKEN", "0")) or train_flops_per_token(
             self.model.config, self._seq_len())
+        if _env_flag("NESTOR_MFU_CALIBRATE"):
+            # cross-check of the analytic count against FlopCounterMode on the PyTorch statement of the model
+            from nestor_b200.train.flops import calibrate_flops
+            cal = calibrate_flops(self.model, seq_len=int(os.environ.get("NESTOR_MFU_CALIB_SEQ", "128")),
+                                  batch=int(os.environ.get("NESTOR_MFU_CALIB_BATCH", "1")))
+            self.logger.info("[MFU] forward FLOPs/token at the calibration length: counted %.4e, analytic %.4e (ratio %.4f)",
+                             cal["counted"], cal["analytic"], cal["ratio"])
+            flops_tok *= cal["ratio"]
         profile = _env_flag("NESTOR_TRAIN_PROFILE")
         tprof, tp_start, tp_n = None, int(os.environ.get("NESTOR_TORCH_PROFILE_START", "12")), \
             int(os.environ.get("NESTOR_TORCH_PROFILE_STEPS", "10"))

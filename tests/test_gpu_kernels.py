@@ -522,3 +522,81 @@ def test_dispatch_refuses_cuda_tensor_without_kernel_body():
     with ops.oracle_ops():
         assert not ops.use_kernels(x)
     assert ops.use_kernels(x)
+
+
+def _poison_allocator(gib: float = 1.5):
+    """Fill the caching allocator's free blocks with inf / NaN: memory a later ``torch.empty`` hands out is dirty, so
+    any row or column a kernel leaves unwritten shows up in its output (the reference's dirty-allocator discipline,
+    ``tests/test_triton_packed_attn.py:209-270``)."""
+
+    sizes = [1 << 20, 4 << 20, 16 << 20, 64 << 20, 256 << 20]
+    blocks = []
+    budget = int(gib * (1 << 30))
+    for i, sz in enumerate(sizes * 3):
+        if budget < sz:
+            break
+        t = torch.empty(sz // 4, device="cuda")
+        t.fill_(float("inf") if i % 2 else float("nan"))
+        blocks.append(t)
+        budget -= sz
+    torch.cuda.synchronize()
+    del blocks                      # freed blocks stay in the allocator's pool, poisoned
+
+
+@pytest.mark.parametrize("shape", [(2, 96, 8, 3, 2, 40), (1, 200, 8, 8, 2, 40), (3, 64, 4, 2, 3, 30)])
+def test_dirty_allocator_column_attention_and_expert_bank(shape):
+    """Column attention and a routed expert bank on poisoned memory: outputs and gradients stay finite and equal the
+    clean-memory run bit for bit (every buffer element that is read was written first)."""
+
+    from nestor_b200.ops import cuda as K
+    B, S, G, k, heads, hd = shape
+    d, T = 64, B * S
+    torch.manual_seed(5)
+    n = torch.randn(T, d, device="cuda", requires_grad=True)
+    scores = torch.randn(T, G, device="cuda")
+    idx = scores.topk(k, dim=-1).indices.to(torch.int32)
+    gates = torch.softmax(torch.randn(T, k, device="cuda"), -1).requires_grad_()
+    inner = heads * hd
+    wqkv = (torch.randn(G, 3 * inner, d, device="cuda") * 0.1).to(BF)
+    wo = (torch.randn(G, d, inner, device="cuda") * 0.1).to(BF)
+    E, h = 6, 48
+    ids = torch.randint(0, E, (T, 2), device="cuda", dtype=torch.int32)
+    ids[:, 0] = ids[:, 0].clamp_max(E - 2)                 # expert E-1 may stay empty in slot 0
+    w = torch.rand(T, 2, device="cuda").to(BF)
+    wu, wg = ((torch.randn(E, d, h, device="cuda") * 0.1).to(BF) for _ in range(2))
+    wd = (torch.randn(E, h, d, device="cuda") * 0.1).to(BF)
+
+    def run():
+        plan = K.build_column_plan(idx.view(B, S, k), G) if G > 1 else None
+        a = K.column_attention(n, plan, gates, wqkv, wo, heads, hd, 10000.0, BF)
+        eplan = K.build_expert_plan(ids, E)
+        e = K.expert_bank(n, eplan, w, wu, wg, wd, BF, group=2)
+        ga, gg = torch.autograd.grad(a.sum() + e.sum(), (n, gates))
+        return a.detach().clone(), e.detach().clone(), ga.clone(), gg.clone()
+
+    clean = run()
+    torch.cuda.synchronize()
+    _poison_allocator()
+    dirty = run()
+    for c, x in zip(clean, dirty):
+        assert torch.isfinite(x).all() and torch.equal(c, x)
+
+
+def test_fastpath_check_prints_kernel_vs_oracle_difference(capsys, monkeypatch):
+    """NESTOR_FASTPATH_CHECK=1: the first forwards are repeated on the PyTorch ops with the same routing."""
+
+    import re
+    monkeypatch.setenv("NESTOR_FASTPATH_CHECK", "1")
+    monkeypatch.setenv("DCLM_DATA_PATH", "/tmp/unused.bin")
+    from nestor_b200.experiments.tiny import nestor_tiny
+    from nestor_b200.models import Model
+    torch.manual_seed(0)
+    m = Model.from_config(nestor_tiny().jobs[0].model).cuda().eval()
+    m.compute_dtype = BF
+    ids = torch.randint(0, 100277, (2, 128), device="cuda")
+    with torch.no_grad():
+        for _ in range(4):
+            m(ids)
+    out = capsys.readouterr().out
+    diffs = [float(x) for x in re.findall(r"\[FASTPATH-CHECK\] max\|kernels - oracle\| = ([0-9.e+-]+)", out)]
+    assert len(diffs) == 3 and max(diffs) < 0.25, out          # three checked forwards, bf16-level agreement

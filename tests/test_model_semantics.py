@@ -330,3 +330,25 @@ def test_drop_path_is_identity_in_eval_and_unbiased_in_training(tiny_scale):
     m.train()
     d = layer.drop(u, 4).view(4, 8, 3)
     assert set(d.unique().tolist()) <= {0.0, 2.0} and all(len(d[b].unique()) == 1 for b in range(4))   # whole sequences
+
+
+def test_router_noise_anneals_per_real_forward(tiny_scale, monkeypatch):
+    """NESTOR_ROUTER_NOISE_ANNEAL_STEPS: the noise fades linearly, the counter is a persistent buffer, and a recomputed
+    region's replay does not advance it."""
+
+    monkeypatch.setenv("NESTOR_ROUTER_NOISE_ANNEAL_STEPS", "4")
+    monkeypatch.setenv("NESTOR_ACTIVATION_CHECKPOINT", "1")
+    monkeypatch.setenv("NESTOR_ACTIVATION_CHECKPOINT_BLOCK", "1")
+    m = _model(tiny_scale, "nestor").train()
+    r = m.backbone.blocks[0].group_router
+    assert "backbone.blocks.0.group_router._noise_steps" in m.state_dict()
+    ids = torch.randint(0, 100263, (2, 32))
+    for step in range(1, 6):
+        out = m(ids)
+        F.cross_entropy(out.pred.reshape(-1, out.pred.shape[-1]).float(), ids.reshape(-1)).backward()   # replays the blocks
+        assert int(r._noise_steps) == step
+    assert float(r.noise_scale(advance=False)) == 0.0            # fully annealed after 4 forwards
+    m.eval()
+    with torch.no_grad():
+        a, b = m(ids).pred, m(ids).pred
+    assert torch.equal(a, b) and int(r._noise_steps) == 5         # evaluation neither draws noise nor counts

@@ -138,3 +138,18 @@ def test_part_registries_dispatch_on_config_type():
     assert r.build(True) == 2                # bool -> int through the MRO
     with pytest.raises(ValueError, match="already registered"):
         r.register(int)(lambda c: c)
+
+
+@pytest.mark.parametrize("family", ["nestor", "moe", "dense"])
+def test_analytic_flops_agree_with_flop_counter(family, tiny_scale):
+    """The analytic per-token FLOP formula against ``FlopCounterMode`` on the PyTorch statement of the model."""
+
+    import torch
+    from nestor_b200.models import Model
+    from nestor_b200.train.flops import calibrate_flops, grouped_mm_flops, register_extra_flop_formulas
+    torch.manual_seed(0)
+    m = Model.from_config(tiny_scale.build_experiment(family, "tiny").jobs[0].model)
+    cal = calibrate_flops(m, seq_len=64, batch=2)
+    assert cal["counted"] > 0 and abs(cal["ratio"] - 1.0) < 0.06, cal
+    assert grouped_mm_flops(10, 4, 6) == 480
+    register_extra_flop_formulas(); register_extra_flop_formulas()      # idempotent
