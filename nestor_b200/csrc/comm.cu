@@ -122,9 +122,12 @@ allreduce_push_kernel(Peers P, long offset, long numel, float scale, int write_m
   block_barrier(P, 1, epoch, budget, status);
 }
 
-// Store master[lo:hi) (fp32) into every peer's master and its bf16 rounding into every rank's compute buffer.
+// Store the bf16 rounding of master[lo:hi) into every rank's compute buffer and, with `push_master`, the fp32 values
+// into every peer's master as well. Without it a rank's fp32 masters outside its own range go stale, which nothing on
+// the training path reads (they are brought up to date from their owners when a checkpoint is written): the push then
+// moves 2 bytes per parameter instead of 6.
 __global__ void __launch_bounds__(512, 1)
-param_push_kernel(Peers P, long lo, long hi, uint32_t epoch, long budget, int* status) {
+param_push_kernel(Peers P, long lo, long hi, uint32_t epoch, long budget, int* status, int push_master) {
   if (!block_barrier(P, 2, epoch, budget, status)) return;
   const long lo4 = lo / 4, hi4 = hi / 4;
   const long stride = long(gridDim.x) * blockDim.x;
@@ -136,7 +139,7 @@ param_push_kernel(Peers P, long lo, long hi, uint32_t epoch, long budget, int* s
 #pragma unroll
     for (int p = 0; p < kMaxWorld; ++p) {
       if (p < P.world) {
-        if (p != P.rank) reinterpret_cast<float4*>(P.buf[p])[i] = v;
+        if (push_master && p != P.rank) reinterpret_cast<float4*>(P.buf[p])[i] = v;
         if (P.aux[p]) reinterpret_cast<uint2*>(P.aux[p])[i] = packed;
       }
     }
@@ -208,7 +211,7 @@ allreduce_nvls_kernel(Peers P, float* mc_buf, __nv_bfloat16* mc_aux, long offset
 // which rewrites its own master with the value just read).
 __global__ void __launch_bounds__(512, 1)
 param_push_nvls_kernel(Peers P, float* mc_master, __nv_bfloat16* mc_compute, long lo, long hi, uint32_t epoch, long budget,
-                       int* status) {
+                       int* status, int push_master) {
   if (!block_barrier(P, 2, epoch, budget, status)) return;
   const long lo4 = lo / 4, hi4 = hi / 4;
   const long stride = long(gridDim.x) * blockDim.x;
@@ -217,7 +220,7 @@ param_push_nvls_kernel(Peers P, float* mc_master, __nv_bfloat16* mc_compute, lon
     const float4 v = src[i];
     __nv_bfloat162 b0 = __floats2bfloat162_rn(v.x, v.y), b1 = __floats2bfloat162_rn(v.z, v.w);
     const uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&b0), *reinterpret_cast<uint32_t*>(&b1));
-    mm_st_f32x4(mc_master + 4 * i, v);
+    if (push_master) mm_st_f32x4(mc_master + 4 * i, v);
     if (mc_compute) mm_st_bf16x4(mc_compute + 4 * i, packed);
   }
   block_barrier(P, 3, epoch, budget, status);
@@ -285,9 +288,12 @@ int nb_reduce_scatter_push(const NbPeers* a, long lo, long hi, float scale, int 
   return int(cudaGetLastError());
 }
 
-int nb_param_push(const NbPeers* a, long lo, long hi, unsigned epoch, long budget, int blocks, int* status, cudaStream_t st) {
+// push_master = 0 requires a compute buffer (aux) on every rank: it is then the only thing written.
+int nb_param_push(const NbPeers* a, long lo, long hi, unsigned epoch, long budget, int blocks, int* status, int push_master,
+                  cudaStream_t st) {
   if (a->world < 1 || a->world > 8 || (lo % 4) || (hi % 4) || blocks < 1 || blocks > max_blocks()) return -1;
-  nbc::param_push_kernel<<<blocks, 512, 0, st>>>(to_peers(a), lo, hi, epoch, budget, status);
+  if (!push_master) for (int r = 0; r < a->world; ++r) if (!a->aux[r]) return -2;
+  nbc::param_push_kernel<<<blocks, 512, 0, st>>>(to_peers(a), lo, hi, epoch, budget, status, push_master);
   return int(cudaGetLastError());
 }
 
@@ -311,10 +317,12 @@ int nb_reduce_scatter_nvls(const NbPeers* a, void* mc_buf, long lo, long hi, flo
 }
 
 int nb_param_push_nvls(const NbPeers* a, void* mc_master, void* mc_compute, long lo, long hi, unsigned epoch, long budget,
-                       int blocks, int* status, cudaStream_t st) {
+                       int blocks, int* status, int push_master, cudaStream_t st) {
   if (a->world < 1 || a->world > 8 || !mc_master || (lo % 4) || (hi % 4) || blocks < 1 || blocks > max_blocks()) return -1;
+  if (!push_master && !mc_compute) return -2;
   nbc::param_push_nvls_kernel<<<blocks, 512, 0, st>>>(to_peers(a), static_cast<float*>(mc_master),
-                                                      static_cast<__nv_bfloat16*>(mc_compute), lo, hi, epoch, budget, status);
+                                                      static_cast<__nv_bfloat16*>(mc_compute), lo, hi, epoch, budget, status,
+                                                      push_master);
   return int(cudaGetLastError());
 }
 

@@ -68,6 +68,7 @@ struct GatherParams {
   int nbuf;                    // shared-memory ring depth per copying lane (chunks), >= 2
   int lanes;                   // lanes of the copy warp that copy (1..4); lanes * nbuf <= 8
   int* flags;                  // [groups] finished chunks per group, then [groups]: CTAs that left
+  unsigned wait_polls;         // polls (>= 100 ns each) a B producer spends on a group's counter before it gives up
 };
 
 struct GemmParams {
@@ -216,7 +217,7 @@ __device__ __forceinline__ void load_chunk_bf16(uint8_t* slab, int lane, uint32_
 // completion (store -> this thread) arguably order them already: taking the fences out did not raise the copy rate
 // when that was tried, so the loop keeps them and does not depend on that reading of the proxy rules.
 constexpr int kGatherLag = 4;
-constexpr uint32_t kGatherSpinLimit = 1u << 22;   // polls of >= 100 ns: a consumer gives up after about half a second
+constexpr uint32_t kGatherSpinLimit = 1u << 22;   // default wait budget: polls of >= 100 ns, about half a second
 __device__ __noinline__ void gather_role(const GatherParams& g, int groups, uint8_t* smem, uint64_t* bars, int* status,
                                          volatile int* abort_flag) {
   // per-buffer destination and size, and the group of each recent chunk, are computed once when the chunk's load
@@ -459,7 +460,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           uint32_t spins = 0;
           while (*fl < need) {
             __nanosleep(100);
-            if (++spins > kGatherSpinLimit || *abort_flag) {
+            if (++spins > p.gather.wait_polls || *abort_flag) {
               if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, int(kTimeoutPeer)); }
               break;
             }
@@ -797,6 +798,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   }
 
   // ----------------------------------------------------------------------- teardown
+  // After a wait gave up, tile loads issued before the abort may still be on their way into this CTA's shared memory
+  // (at most one per pipeline stage, each a few microseconds): let them land before the CTA gives its memory back.
+  if (*abort_flag) for (int i = 0; i < 64; ++i) __nanosleep(1000);
   tc_fence_before();
   __syncthreads();
   if (pair) cluster_sync_all();     // neither CTA leaves (or frees TMEM) while its peer may still signal or read it
@@ -886,6 +890,7 @@ struct NbGemmArgs {
   int* gather_flags;        // [groups + 1] ints, zero before the first launch
   int gather_nbuf;          // ring depth per copying lane (chunks)
   int gather_lanes;         // copying lanes of the copy warp (0 = 1)
+  unsigned gather_wait_polls;  // 0 = default (about half a second)
 };
 
 // Returns 0 on success, a negative code for bad arguments / map failures, or a CUDA error code.
@@ -997,6 +1002,7 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
     p.gather.group_bytes = a->gather_group_bytes; p.gather.group_stride_src = a->gather_group_stride_src;
     p.gather.nseg = a->gather_nseg; p.gather.groups_per_rank = a->gather_groups_per_rank;
     p.gather.flags = a->gather_flags;
+    p.gather.wait_polls = a->gather_wait_polls ? a->gather_wait_polls : kGatherSpinLimit;
     ring_bytes = size_t(p.gather.nbuf) * p.gather.lanes * a->gather_chunk;
   }
   int stages = int((200 * 1024 - ring_bytes) / stage_bytes);   // 227 KB per CTA minus epilogue slabs, barriers, offsets, alignment slack
@@ -1023,6 +1029,13 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
   if (int e = configured[gat][pair][a->epilogue].ensure(kernel, smem)) return e;
   int sms = a->sms > 0 ? a->sms : g_num_sms;
   const int threads = p.gather.on ? 384 : 352;
+  if (p.gather.on) {
+    // The B producers of a gathering launch wait for chunks that the copy warps of ALL its CTAs stage, so every CTA
+    // of the grid has to be resident at the same time: never launch more than the occupancy calculator grants.
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess || per_sm < 1) return -28;
+    if (sms > per_sm * g_num_sms) sms = per_sm * g_num_sms;
+  }
   if (!pair) {
     int grid = int(tiles < sms ? tiles : sms);
     kernel<<<grid, threads, smem, stream>>>(tmA, tmB, tmA2, tmB2, p, stages);

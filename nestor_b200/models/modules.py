@@ -179,15 +179,16 @@ class BlockAttentionResidual(nn.Module):
     (reference ``nestor/backbones/attention_residual.py:259-392``).
     """
 
-    def __init__(self, source_widths: list[int], target_width: int, std: float) -> None:
+    def __init__(self, source_widths: list[int], target_width: int, std: float | None = None) -> None:
         super().__init__()
         if not source_widths or min(source_widths) < 1 or target_width < 1:
             raise ValueError("BlockAttentionResidual needs at least one source and positive widths.")
         self.source_widths, self.target_width = tuple(int(w) for w in source_widths), int(target_width)
-        mk = lambda w: Matrix(w, target_width, muon_matrix(target_width, w), std)   # noqa: E731
+        from nestor_b200.models.scaling import ScaledLinear
+        mk = lambda w: ScaledLinear(w, target_width, role="projection", bias=False)   # noqa: E731
         self.key_projections = nn.ModuleList([mk(w) for w in self.source_widths])
         self.value_projections = nn.ModuleList([mk(w) for w in self.source_widths])
-        self.query = Matrix(target_width, 1, ParamTag("adamw", lr_mul=1.0 / target_width), 0.0)
+        self.query = ScaledLinear(target_width, 1, role="score", bias=False, zero_init=True)
 
     def forward(self, sources: list[Tensor]) -> Tensor:
         if len(sources) != len(self.source_widths):

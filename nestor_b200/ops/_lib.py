@@ -41,6 +41,7 @@ class GemmArgs(C.Structure):
         ("gather_group_bytes", C.c_long), ("gather_group_stride_src", C.c_long),
         ("gather_nseg", C.c_int), ("gather_groups_per_rank", C.c_int), ("gather_on", C.c_int), ("gather_chunk", C.c_int),
         ("gather_flags", C.c_void_p), ("gather_nbuf", C.c_int), ("gather_lanes", C.c_int),
+        ("gather_wait_polls", C.c_uint),
     ]
 
 

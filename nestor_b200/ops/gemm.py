@@ -44,7 +44,9 @@ class Gather:
     into ``stage`` by a copy warp in every CTA of the same launch, and the tensor maps of the product point at
     ``stage``. ``lanes`` lanes of that warp copy independently; ``chunk`` x ``nbuf`` x ``lanes`` bytes of shared
     memory per CTA go to the copy rings (``nbuf * lanes <= 8``).
-    ``flags`` is an ``int32`` tensor of at least ``groups + 1`` zeros shared by stream-ordered launches.
+    ``flags`` is an ``int32`` tensor of at least ``groups + 1`` zeros shared by stream-ordered launches. Every CTA of a
+    gathering launch must be resident at once (the launcher clamps the grid to what the occupancy calculator grants);
+    do not run it next to another kernel that holds SMs for its whole duration.
     """
 
     src: list[int]
@@ -55,6 +57,7 @@ class Gather:
     chunk: int = 8192
     nbuf: int = 4
     lanes: int = 1
+    wait_polls: int = 0      # polls (>= 100 ns each) a B producer waits for a group's chunks; 0 = about half a second
 
 
 def pick_bn(n: int, *, mult: int = 16, cap: int = 256) -> int:
@@ -115,6 +118,7 @@ def _stage_for_gather(a: _lib.GemmArgs, g: Gather, B: Tensor, B2: Tensor | None)
     a.gather_group_bytes, a.gather_group_stride_src = group_elems * 2, B.stride(0) * 2
     a.gather_nseg, a.gather_groups_per_rank, a.gather_on, a.gather_chunk = len(segs), g.groups_per_rank, 1, g.chunk
     a.gather_nbuf, a.gather_lanes = g.nbuf, g.lanes
+    a.gather_wait_polls = int(g.wait_polls)
     a.gather_flags = g.flags.data_ptr()
     return staged[0], (staged[1] if B2 is not None else None)
 

@@ -59,11 +59,11 @@ def _L():
         L.nb_allreduce_push.argtypes = [C.POINTER(Peers), l, l, f, i, u, l, i, vp, vp]
         L.nb_reduce_scatter_push.argtypes = [C.POINTER(Peers), l, l, f, i, u, l, i, vp, vp]
         L.nb_reduce_scatter_push.restype = C.c_int
-        L.nb_param_push.argtypes = [C.POINTER(Peers), l, l, u, l, i, vp, vp]
+        L.nb_param_push.argtypes = [C.POINTER(Peers), l, l, u, l, i, vp, i, vp]
         L.nb_wait_timeout_probe.argtypes = [vp, u, l, vp, vp]
         L.nb_allreduce_nvls.argtypes = [C.POINTER(Peers), vp, vp, l, l, f, i, u, l, i, vp, vp]
         L.nb_reduce_scatter_nvls.argtypes = [C.POINTER(Peers), vp, l, l, f, i, u, l, i, vp, vp]
-        L.nb_param_push_nvls.argtypes = [C.POINTER(Peers), vp, vp, l, l, u, l, i, vp, vp]
+        L.nb_param_push_nvls.argtypes = [C.POINTER(Peers), vp, vp, l, l, u, l, i, vp, i, vp]
         L.nb_comm_max_blocks.argtypes = []
         for fn in (L.nb_allreduce_push, L.nb_param_push, L.nb_wait_timeout_probe, L.nb_allreduce_nvls,
                    L.nb_reduce_scatter_nvls, L.nb_param_push_nvls, L.nb_comm_max_blocks):
@@ -189,10 +189,20 @@ class FusedReduceScatter:
 
 
 class ParamPush:
-    """After a sharded optimizer step: store this rank's master range into every replica (fp32 + bf16 cast)."""
+    """After a sharded optimizer step: store the bf16 cast of this rank's master range into every replica's compute
+    copy, and (``push_master``) the fp32 values into every replica's master too.
 
-    def __init__(self, master: torch.Tensor, compute: torch.Tensor | None) -> None:
+    ``push_master=None`` reads ``NESTOR_B200_PUSH_MASTER`` (default 0): only the compute copy travels, 2 bytes per
+    parameter instead of 6; fp32 masters outside a rank's own range then go stale until ``gather_masters`` brings them
+    up to date from their owners (checkpoints, comparisons). Without a separate compute copy (fp32 compute) the master
+    is what is pushed.
+    """
+
+    def __init__(self, master: torch.Tensor, compute: torch.Tensor | None, push_master: bool | None = None) -> None:
         self.group = PeerGroup(master, compute if compute is not None and compute is not master else None)
+        if push_master is None:
+            push_master = os.environ.get("NESTOR_B200_PUSH_MASTER", "0") == "1"
+        self.push_master = bool(push_master) or self.group.aux is None
         # A multicast store also lands in the sender's own copy, so on few ranks it moves more bytes than the
         # world - 1 peer stores it replaces (measured on 2 GPUs: 330 vs 609 GB/s); it pays from 4 ranks on.
         self.use_nvls = self.group.nvls and self.group.world >= int(os.environ.get("NESTOR_B200_NVLS_PUSH_MIN_WORLD", "4"))
@@ -202,13 +212,28 @@ class ParamPush:
         g = self.group
         if self.use_nvls:
             rc = _L().nb_param_push_nvls(C.byref(g.peers), g.mc_main, g.mc_aux or None, lo, hi, PeerGroup.next_epoch(),
-                                         wait_budget(), g.blocks, g.status.data_ptr(), C.c_void_p(_lib.stream_ptr()))
+                                         wait_budget(), g.blocks, g.status.data_ptr(), int(self.push_master),
+                                         C.c_void_p(_lib.stream_ptr()))
         else:
             rc = _L().nb_param_push(C.byref(g.peers), lo, hi, PeerGroup.next_epoch(), wait_budget(), g.blocks,
-                                    g.status.data_ptr(), C.c_void_p(_lib.stream_ptr()))
+                                    g.status.data_ptr(), int(self.push_master), C.c_void_p(_lib.stream_ptr()))
         if rc != 0:
             raise RuntimeError(f"fused parameter push launch failed with code {rc}")
         _lib.count_launch()
+
+
+@torch.no_grad()
+def gather_ranges(flat: torch.Tensor, cuts: list[int]) -> None:
+    """Bring ``flat`` up to date on every rank from the owners of its ranges: rank ``r`` broadcasts
+    ``flat[cuts[r]:cuts[r + 1]]`` (control-plane collective; used when a checkpoint or a comparison needs the whole
+    fp32 state that the training step keeps sharded)."""
+
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return
+    for r in range(dist.get_world_size()):
+        lo, hi = cuts[r], cuts[r + 1]
+        if hi > lo:
+            dist.broadcast(flat[lo:hi], src=r)
 
 
 def wait_timeout_probe(device: torch.device, budget: int = 20000) -> int:

@@ -126,10 +126,15 @@ def main(argv: list[str] | None = None) -> None:
         per = n // world
 
         def make_pp():
-            pp = symm.ParamPush(master, comp)
+            pp = symm.ParamPush(master, comp, push_master=True)
+            return pp, lambda: pp.run(rank * per, (rank + 1) * per)
+
+        def make_pp_bf16():
+            pp = symm.ParamPush(master, comp, push_master=False)
             return pp, lambda: pp.run(rank * per, (rank + 1) * per)
 
         res = both(make_pp)
+        res16 = both(make_pp_bf16)
         shard = master[rank * per : (rank + 1) * per].clone()
         full = torch.empty(n, dtype=torch.float32, device=dev)
         ms_nccl = timed(lambda: (dist.all_gather_into_tensor(full, shard), full.to(torch.bfloat16)), a.reps, dev)
@@ -138,6 +143,9 @@ def main(argv: list[str] | None = None) -> None:
             ours = " | ".join(f"{k} {v:8.3f} ms {bus / v * 1e3:6.0f} GB/s ({bus / v * 1e3 / PEER_COPY_GBS:5.1%} of the peer-copy rate)"
                               for k, v in res.items())
             print(f"param push {mb:5d} MB: {ours} | NCCL all-gather + cast {ms_nccl:8.3f} ms", flush=True)
+            bus16 = (world - 1) / world * n * 2 / 1e9       # the bf16 compute copy alone crosses the links
+            ours16 = " | ".join(f"{k} {v:8.3f} ms {bus16 / v * 1e3:6.0f} GB/s" for k, v in res16.items())
+            print(f"param push {mb:5d} MB, compute copy only (what the training step uses): {ours16}", flush=True)
     if a.ag_gemm:
         bench_ag_gemm(dev, rank, world, a.reps, a.gather_rings)
     # leave in step: nothing of a rank is unmapped while a peer may still touch it

@@ -89,6 +89,9 @@ class Trainer:
         # the pushed range carries every parameter in it; when its owner is the only one to update them (ZeRO-1 for
         # AdamW as well) it is also the only one that needs their reduced gradients: reduce-scatter
         self.zero = bool(self.param_push is not None and getattr(self.optimizer, "shard_adamw", False))
+        # the push distributes the bf16 compute copy only: fp32 masters (and the EMA shadow) outside this rank's range
+        # are stale between checkpoints (see gather_masters)
+        self.masters_sharded = bool(self.param_push is not None and not self.param_push.push_master)
         # Device status word of the in-kernel collectives: a bounded peer wait that gave up leaves a nonzero code
         # there and the kernel returns without reducing / pushing. It is read back once per optimizer step.
         self.nvtx = _env_flag("NESTOR_NVTX")
@@ -314,7 +317,11 @@ class Trainer:
         self._mark("param_push")
         self.arena.zero_grad()
         if self.ema is not None:
-            self.ema["flat"].lerp_(self.arena.master, 1.0 - self.ema_decay)
+            if self.masters_sharded:      # only this rank's range of the master is current; the shadow is sharded the same way
+                lo, hi = self.optimizer.owned_range()
+                self.ema["flat"][lo:hi].lerp_(self.arena.master[lo:hi], 1.0 - self.ema_decay)
+            else:
+                self.ema["flat"].lerp_(self.arena.master, 1.0 - self.ema_decay)
         if self.scheduler is not None:
             self.scheduler.step()
         apply_bias_updates(self.model.backbone, window_counts, global_counts=self.global_counts)
@@ -492,10 +499,26 @@ class Trainer:
         d = self.run_dir / self.config.checkpoint_dir
         return d / ("model_final.pt" if final else f"model_{self.global_step:08d}.pt")
 
+    @torch.no_grad()
+    def gather_masters(self) -> None:
+        """Bring the fp32 masters (and the EMA shadow) of every range up to date from their owners.
+
+        With the bf16-only parameter push each rank's fp32 state is current for its own arena range only; everything
+        that reads the whole fp32 model (checkpoints, weight comparisons across ranks) calls this first. All ranks
+        must call it together."""
+
+        if not self.masters_sharded:
+            return
+        from nestor_b200.parallel.symm import gather_ranges
+        gather_ranges(self.arena.master, self.optimizer.owner_cuts)
+        if self.ema is not None:
+            gather_ranges(self.ema["flat"], self.optimizer.owner_cuts)
+
     def save_checkpoint(self, final: bool = False) -> None:
         path = self.checkpoint_path(final)
         if path is None:
             return
+        self.gather_masters()
         ema = None
         if self.ema is not None:
             ema = {s.name: self.ema["flat"][s.offset : s.offset + s.numel].view(s.shape).cpu().clone()

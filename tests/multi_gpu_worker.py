@@ -94,12 +94,25 @@ def check_collectives(dev, rank: int, world: int, nvls: str) -> bool:
     torch.cuda.synchronize()
     dist.barrier()
     per = M // world
-    pp = symm.ParamPush(master, comp)
+    pp = symm.ParamPush(master, comp, push_master=False)      # the compute copy alone travels
     pp.run(rank * per, (rank + 1) * per)
     torch.cuda.synchronize()
     pp.group.check()
     dist.barrier()
     want = torch.arange(1, world + 1, device=dev, dtype=torch.float32).repeat_interleave(per)
+    assert torch.equal(comp.float(), want), "parameter push (compute copy) mismatch"
+    assert torch.equal(master, torch.full_like(master, float(rank + 1))), "a bf16-only push must not touch the masters"
+    symm.gather_ranges(master, [r * per for r in range(world + 1)])
+    assert torch.equal(master, want), "gather_ranges mismatch"
+    master.fill_(float(rank + 1))
+    comp.zero_()
+    torch.cuda.synchronize()
+    dist.barrier()
+    pp = symm.ParamPush(master, comp, push_master=True)
+    pp.run(rank * per, (rank + 1) * per)
+    torch.cuda.synchronize()
+    pp.group.check()
+    dist.barrier()
     assert torch.equal(master, want) and torch.equal(comp.float(), want), "parameter push mismatch"
     used = bool(far.group.nvls and frs.group.nvls and pp.group.nvls)
     torch.cuda.synchronize()
@@ -136,6 +149,13 @@ def main() -> None:
             tr.update_weights(counts)
         torch.cuda.synchronize()
         _lib.check_status(dev)
+        if zero == "1":
+            # the push moved the bf16 copy only: a rank's masters outside its own range are stale until gathered
+            assert tr.masters_sharded
+            lo, hi = tr.optimizer.owned_range()
+            assert torch.equal(tr.arena.master[lo:hi].bfloat16(), tr.arena.compute[lo:hi])
+        tr.gather_masters()
+        assert torch.equal(tr.arena.master.bfloat16(), tr.arena.compute), "compute copy is not the cast of the masters"
         chk = torch.tensor([tr.arena.master.double().sum().item(), tr.arena.compute.double().sum().item()], device=dev,
                            dtype=torch.float64)
         gathered = [torch.zeros_like(chk) for _ in range(world)]
@@ -166,6 +186,7 @@ def main() -> None:
     torch.cuda.synchronize()
     _lib.check_status(dev)
     assert cuda_ops.BANK_SHARDS.gathered_bytes > 0, "no bank product used the fused all-gather"
+    tr.gather_masters()
     rel = ((tr.arena.master - results["1"]).norm() / results["1"].norm()).item()
     assert rel < 1e-5, f"rank-sharded banks disagree with replicated banks: {rel}"
     cuda_ops.BANK_SHARDS = None

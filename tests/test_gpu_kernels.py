@@ -600,3 +600,38 @@ def test_fastpath_check_prints_kernel_vs_oracle_difference(capsys, monkeypatch):
     out = capsys.readouterr().out
     diffs = [float(x) for x in re.findall(r"\[FASTPATH-CHECK\] max\|kernels - oracle\| = ([0-9.e+-]+)", out)]
     assert len(diffs) == 3 and max(diffs) < 0.25, out          # three checked forwards, bf16-level agreement
+
+
+def test_gathering_gemm_wait_runs_out_and_context_survives():
+    """The fused all-gather GEMM's B producer waits (bounded) for the copy warps to stage a group's weights. A group
+    counter that can never reach its target makes that wait run out: the launch must come back with the peer-timeout
+    status instead of hanging, leave the counters clean, and the next launch on the same context must be correct."""
+
+    from nestor_b200.ops import _lib, gemm as G
+    E, d, h, rows = 8, 128, 64, 2048
+    torch.manual_seed(3)
+    n = E * d * h
+    arena = (torch.randn(n, device="cuda") * 0.05).to(BF)
+    W = arena.view(E, d, h)
+    X = torch.randn(rows, d, device="cuda").to(BF)
+    off = (torch.arange(E + 1, dtype=torch.int32) * (rows // E)).cuda()
+    stage = torch.empty(n, dtype=BF, device="cuda")
+    flags = torch.zeros(257, dtype=torch.int32, device="cuda")
+    spec = G.Gather(src=[arena.data_ptr()] * 8, arena_ptr=arena.data_ptr(), stage=stage, flags=flags, groups_per_rank=1,
+                    wait_polls=20000)              # ~2 ms instead of the default half second
+    want = G.gemm_rows(X, W, offsets=off, groups=E, b_mn=True)
+    got = G.gemm_rows(X, W, offsets=off, groups=E, b_mn=True, gather=spec)
+    torch.cuda.synchronize()
+    _lib.check_status(torch.device("cuda"))
+    assert torch.equal(got, want)
+    flags[3] = -(1 << 20)                           # group 3 can never be reported complete
+    G.gemm_rows(X, W, offsets=off, groups=E, b_mn=True, gather=spec)
+    torch.cuda.synchronize()
+    code = int(_lib.status_word(torch.device("cuda")).item())
+    _lib.status_word(torch.device("cuda")).zero_()
+    assert code == 5, code                          # kTimeoutPeer
+    assert int(flags.abs().sum()) == 0              # the last CTA to leave cleared the counters
+    again = G.gemm_rows(X, W, offsets=off, groups=E, b_mn=True, gather=spec)
+    torch.cuda.synchronize()
+    _lib.check_status(torch.device("cuda"))
+    assert torch.equal(again, want)
