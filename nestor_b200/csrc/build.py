@@ -38,42 +38,52 @@ def _digest(path: Path) -> str:
     return h.hexdigest()[:16]
 
 
-def build(verbose: bool = False, force: bool = False) -> Path:
+CHECKED_LIB = OUT / "libnestor_b200_checked.so"      # the same sources with -DNESTOR_BOUNDS_CHECK
+
+
+def build(verbose: bool = False, force: bool = False, checked: bool = False) -> Path:
+    """Build the library (``checked``: the index-checking variant, objects cached under their own names)."""
+
     cc = nvcc()
     if cc is None:
         raise RuntimeError("nvcc not found: cannot build the sm_100a kernel library")
     OUT.mkdir(exist_ok=True)
     objs, rebuilt = [], False
+    extra = ["-DNESTOR_BOUNDS_CHECK"] if checked else []
+    kind = "chk" if checked else ""
     for cu in sorted(SRC.glob("*.cu")):
-        obj = OUT / f"{cu.stem}.{_digest(cu)}.o"
+        obj = OUT / f"{cu.stem}{kind}.{_digest(cu)}.o"
         if force or not obj.is_file():
-            for old in OUT.glob(f"{cu.stem}.*.o"):
+            for old in OUT.glob(f"{cu.stem}{kind}.*.o"):
                 old.unlink()
-            cmd = [cc, *FLAGS, "-c", str(cu), "-o", str(obj)]
+            cmd = [cc, *FLAGS, *extra, "-c", str(cu), "-o", str(obj)]
             res = subprocess.run(cmd, capture_output=True, text=True)
             if verbose or res.returncode:
                 sys.stderr.write(res.stdout + res.stderr)
             if res.returncode:
                 raise RuntimeError(f"nvcc failed on {cu.name}")
-            (OUT / f"{cu.stem}.ptxas.txt").write_text(res.stderr)
+            if not checked:
+                (OUT / f"{cu.stem}.ptxas.txt").write_text(res.stderr)
             rebuilt = True
         objs.append(obj)
-    if rebuilt or not LIB.is_file():
-        cmd = [cc, "-shared", "-o", str(LIB), *map(str, objs), "-lcudart"]
+    lib = CHECKED_LIB if checked else LIB
+    if rebuilt or not lib.is_file():
+        cmd = [cc, "-shared", "-o", str(lib), *map(str, objs), "-lcudart"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode:
             sys.stderr.write(res.stdout + res.stderr)
             raise RuntimeError("link failed")
-    return LIB
+    return lib
 
 
-def stale_sources() -> list[str]:
+def stale_sources(checked: bool = False) -> list[str]:
     """Sources whose cached object (named by source digest) is missing: the built library predates them."""
 
-    return [cu.name for cu in sorted(SRC.glob("*.cu")) if not (OUT / f"{cu.stem}.{_digest(cu)}.o").is_file()]
+    kind = "chk" if checked else ""
+    return [cu.name for cu in sorted(SRC.glob("*.cu")) if not (OUT / f"{cu.stem}{kind}.{_digest(cu)}.o").is_file()]
 
 
-def ensure() -> Path:
+def ensure(checked: bool = False) -> Path:
     """The up-to-date library: rebuild what changed when a compiler is present, else refuse a stale binary.
 
     A library older than its sources would be called with argument structures it does not know (the Python
@@ -81,13 +91,14 @@ def ensure() -> Path:
     """
 
     if nvcc() is not None:
-        return build()
-    stale = stale_sources()
-    if stale or not LIB.is_file():
+        return build(checked=checked)
+    lib = CHECKED_LIB if checked else LIB
+    stale = stale_sources(checked)
+    if stale or not lib.is_file():
         raise RuntimeError(
-            f"{LIB} is missing or older than {', '.join(stale) or 'its sources'} and there is no nvcc to rebuild it")
-    return LIB
+            f"{lib} is missing or older than {', '.join(stale) or 'its sources'} and there is no nvcc to rebuild it")
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(verbose="-v" in sys.argv, force="-f" in sys.argv))
+    print(build(verbose="-v" in sys.argv, force="-f" in sys.argv, checked="--checked" in sys.argv))

@@ -13,14 +13,32 @@
 
 namespace nb {
 
+// Index checking for the gather-style kernels, compiled in with -DNESTOR_BOUNDS_CHECK (a separate library build, see
+// csrc/build.py): an index outside [0, limit) is recorded once in `g_bounds` (code, kernel, index, row) and the access
+// is skipped, so a bad plan shows up as a status the host can read and never as a wild read. The normal build compiles
+// none of this.
+#ifdef NESTOR_BOUNDS_CHECK
+__device__ int g_bounds[4] = {0, 0, 0, 0};
+__device__ __forceinline__ bool index_ok(long idx, long limit, int kernel_id, long row) {
+  if (limit <= 0 || (idx >= 0 && idx < limit)) return true;
+  if (atomicCAS(&g_bounds[0], 0, 7) == 0) { g_bounds[1] = kernel_id; g_bounds[2] = int(idx); g_bounds[3] = int(row); }
+  return false;
+}
+#define NB_INDEX_OK(idx, limit, kernel_id, row) index_ok(idx, limit, kernel_id, row)
+#else
+#define NB_INDEX_OK(idx, limit, kernel_id, row) true
+#endif
+
+
 __device__ __forceinline__ float bf(const __nv_bfloat16 x) { return __bfloat162float(x); }
 
 // out[r, :] = bf16(src[idx[r] / div, :])   (src fp32 or bf16, row pitch lds)
 template <typename TIn>
 __global__ void gather_rows_kernel(const TIn* __restrict__ src, long lds, const int* __restrict__ idx, int div,
-                                   __nv_bfloat16* __restrict__ out, long ldo, int rows, int d) {
+                                   __nv_bfloat16* __restrict__ out, long ldo, int rows, int d, long src_rows) {
   int r = blockIdx.x * blockDim.y + threadIdx.y;
   if (r >= rows) return;
+  if (!NB_INDEX_OK(idx[r] / div, src_rows, 1, r)) return;
   const TIn* s = src + long(idx[r] / div) * lds;
   __nv_bfloat16* o = out + long(r) * ldo;
   for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
@@ -43,7 +61,7 @@ __global__ void gather_rows_kernel(const TIn* __restrict__ src, long lds, const 
 // rounds each weighted row to bf16 before the fp32 sum (the expert-combine contract).
 __global__ void combine_rows_kernel(const __nv_bfloat16* __restrict__ y, long ldy, const int* __restrict__ idx,
                                     const float* __restrict__ w, int group, float* __restrict__ out, long ldo,
-                                    int n_out, int d, int accumulate, int round_products) {
+                                    int n_out, int d, int accumulate, int round_products, long y_rows) {
   int o = blockIdx.x * blockDim.y + threadIdx.y;
   if (o >= n_out) return;
   float* dst = out + long(o) * ldo;
@@ -54,6 +72,7 @@ __global__ void combine_rows_kernel(const __nv_bfloat16* __restrict__ y, long ld
     for (int e = 0; e < group; ++e) {
       int s = o * group + e;
       float ww = w ? w[s] : 1.f;
+      if (!NB_INDEX_OK(idx[s], y_rows, 2, s)) continue;
       uint4 q = *reinterpret_cast<const uint4*>(y + long(idx[s]) * ldy + c);
       const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&q);
 #pragma unroll
@@ -77,10 +96,11 @@ __global__ void combine_bwd_kernel(const float* __restrict__ g, long ldg, const 
                                    const int* __restrict__ slot_of_row, const float* __restrict__ w, int group,
                                    __nv_bfloat16* __restrict__ dy, long lddy, float* __restrict__ dw, int rows, int d,
                                    const float* __restrict__ g2, const float* __restrict__ g3, long ldg2, int g2_div,
-                                   float g2_scale) {
+                                   float g2_scale, long slots) {
   int r = blockIdx.x * blockDim.y + threadIdx.y;
   if (r >= rows) return;
   int s = slot_of_row[r];
+  if (!NB_INDEX_OK(s, slots, 3, r)) return;
   float ww = w ? w[s] : 1.f;
   const float* gr = g + long(s / group) * ldg;
   // optional second gradient of the same output, shared by `g2_div` consecutive slots (the mean over a token's slots
@@ -304,34 +324,60 @@ static int nb_pointwise_sms() {
 
 extern "C" {
 
+// 1 in a library built with -DNESTOR_BOUNDS_CHECK, 0 otherwise.
+int nb_bounds_check_enabled(void) {
+#ifdef NESTOR_BOUNDS_CHECK
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+// Copies {code, kernel (1 gather_rows, 2 combine_rows, 3 combine_bwd), bad index, row} of the first recorded violation
+// to `host4` and clears the record (synchronises the device). Zeros in a normal build.
+int nb_bounds_check_read(int* host4) {
+  host4[0] = host4[1] = host4[2] = host4[3] = 0;
+#ifdef NESTOR_BOUNDS_CHECK
+  cudaError_t e = cudaMemcpyFromSymbol(host4, nb::g_bounds, 4 * sizeof(int));
+  if (e != cudaSuccess) return int(e);
+  const int zero[4] = {0, 0, 0, 0};
+  e = cudaMemcpyToSymbol(nb::g_bounds, zero, sizeof(zero));
+  return int(e);
+#else
+  return 0;
+#endif
+}
+
+// `src_rows` / `y_rows` / `slots` below bound the indices (0 = unknown); they are only looked at by a checking build.
 int nb_gather_rows(const void* src, int src_is_f32, long lds, const int* idx, int div, void* out, long ldo, int rows,
-                   int d, cudaStream_t st) {
+                   int d, long src_rows, cudaStream_t st) {
   if (d % 8) return -1;
   dim3 block(32, 8), grid((rows + 7) / 8);
   if (src_is_f32)
-    nb::gather_rows_kernel<float><<<grid, block, 0, st>>>((const float*)src, lds, idx, div, (__nv_bfloat16*)out, ldo, rows, d);
+    nb::gather_rows_kernel<float><<<grid, block, 0, st>>>((const float*)src, lds, idx, div, (__nv_bfloat16*)out, ldo, rows, d,
+                                                          src_rows);
   else
     nb::gather_rows_kernel<__nv_bfloat16><<<grid, block, 0, st>>>((const __nv_bfloat16*)src, lds, idx, div,
-                                                                  (__nv_bfloat16*)out, ldo, rows, d);
+                                                                  (__nv_bfloat16*)out, ldo, rows, d, src_rows);
   return int(cudaGetLastError());
 }
 
 int nb_combine_rows(const void* y, long ldy, const int* idx, const float* w, int group, float* out, long ldo, int n_out,
-                    int d, int accumulate, int round_products, cudaStream_t st) {
+                    int d, int accumulate, int round_products, long y_rows, cudaStream_t st) {
   if (d % 8) return -1;
   dim3 block(32, 8), grid((n_out + 7) / 8);
   nb::combine_rows_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)y, ldy, idx, w, group, out, ldo, n_out, d, accumulate,
-                                                 round_products && w != nullptr);
+                                                 round_products && w != nullptr, y_rows);
   return int(cudaGetLastError());
 }
 
 int nb_combine_bwd(const float* g, long ldg, const void* y, long ldy, const int* slot_of_row, const float* w, int group,
                    void* dy, long lddy, float* dw, int rows, int d, const float* g2, const float* g3, long ldg2, int g2_div,
-                   float g2_scale, cudaStream_t st) {
+                   float g2_scale, long slots, cudaStream_t st) {
   if (d % 8 || ((g2 || g3) && g2_div < 1)) return -1;
   dim3 block(32, 8), grid((rows + 7) / 8);
   nb::combine_bwd_kernel<<<grid, block, 0, st>>>(g, ldg, (const __nv_bfloat16*)y, ldy, slot_of_row, w, group,
-                                                (__nv_bfloat16*)dy, lddy, dw, rows, d, g2, g3, ldg2, g2_div, g2_scale);
+                                                (__nv_bfloat16*)dy, lddy, dw, rows, d, g2, g3, ldg2, g2_div, g2_scale, slots);
   return int(cudaGetLastError());
 }
 

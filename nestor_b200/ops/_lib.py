@@ -50,8 +50,11 @@ def lib() -> C.CDLL:
     if _LIB is None:
         # always go through the build front end: unchanged sources cost a hash, changed ones are recompiled, and a
         # machine without a compiler refuses a binary that is older than its sources
+        # NESTOR_B200_BOUNDS_CHECK=1 loads the index-checking build of the same sources (gather-style kernels record an
+        # out-of-range index in a status record instead of reading through it; ops.cuda.bounds_check_report())
+        import os
         from nestor_b200.csrc.build import ensure
-        _LIB = C.CDLL(str(ensure()))
+        _LIB = C.CDLL(str(ensure(checked=os.environ.get("NESTOR_B200_BOUNDS_CHECK") == "1")))
         _LIB.nb_gemm.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
         _LIB.nb_gemm.restype = C.c_int
     return _LIB

@@ -33,9 +33,9 @@ def _L():
     L = _lib.lib()
     if not _protos_done:
         vp, i, l, f = C.c_void_p, C.c_int, C.c_long, C.c_float
-        L.nb_gather_rows.argtypes = [vp, i, l, vp, i, vp, l, i, i, vp]
-        L.nb_combine_rows.argtypes = [vp, l, vp, vp, i, vp, l, i, i, i, i, vp]
-        L.nb_combine_bwd.argtypes = [vp, l, vp, l, vp, vp, i, vp, l, vp, i, i, vp, vp, l, i, f, vp]
+        L.nb_gather_rows.argtypes = [vp, i, l, vp, i, vp, l, i, i, l, vp]
+        L.nb_combine_rows.argtypes = [vp, l, vp, vp, i, vp, l, i, i, i, i, l, vp]
+        L.nb_combine_bwd.argtypes = [vp, l, vp, l, vp, vp, i, vp, l, vp, i, i, vp, vp, l, i, f, l, vp]
         L.nb_rope.argtypes = [vp, l, vp, i, i, i, i, f, f, vp]
         L.nb_repack_heads.argtypes = [vp, l, vp, l, i, i, i, i, i, vp]
         L.nb_repack_heads.restype = C.c_int
@@ -73,6 +73,23 @@ def _ck(rc: int, what: str) -> None:
     _lib.count_launch()
 
 
+def bounds_check_report() -> dict | None:
+    """First index violation the gather-style kernels recorded since the last call (checking library builds only:
+    ``NESTOR_B200_BOUNDS_CHECK=1``); ``None`` when there was none. Synchronises the device."""
+
+    L = _L()
+    if not L.nb_bounds_check_enabled():
+        return None
+    rec = (C.c_int * 4)()
+    rc = L.nb_bounds_check_read(rec)
+    if rc != 0:
+        raise RuntimeError(f"nb_bounds_check_read failed with code {rc}")
+    if rec[0] == 0:
+        return None
+    return {"code": rec[0], "kernel": {1: "gather_rows", 2: "combine_rows", 3: "combine_bwd"}.get(rec[1], rec[1]),
+            "index": rec[2], "row": rec[3]}
+
+
 def _ptr(t: Tensor | None):
     return None if t is None else t.data_ptr()
 
@@ -88,7 +105,7 @@ def gather_rows(src: Tensor, idx: Tensor, div: int = 1) -> Tensor:
     rows, d = idx.numel(), src.shape[-1]
     out = torch.empty(rows, d, dtype=BF16, device=src.device)
     _ck(_L().nb_gather_rows(src.data_ptr(), int(src.dtype == torch.float32), src.stride(0), idx.data_ptr(), div,
-                            out.data_ptr(), d, rows, d, _st()), "gather_rows")
+                            out.data_ptr(), d, rows, d, src.shape[0], _st()), "gather_rows")
     return out
 
 
@@ -101,7 +118,7 @@ def combine_rows(y: Tensor, idx: Tensor, w: Tensor | None, group: int, n_out: in
     if out is None:
         out = torch.empty(n_out, d, dtype=torch.float32, device=y.device)
     _ck(_L().nb_combine_rows(y.data_ptr(), y.stride(0), idx.data_ptr(), _ptr(w), group, out.data_ptr(), out.stride(0),
-                             n_out, d, int(accumulate), int(round_products), _st()), "combine_rows")
+                             n_out, d, int(accumulate), int(round_products), y.shape[0], _st()), "combine_rows")
     return out
 
 
@@ -122,7 +139,7 @@ def combine_bwd(g: Tensor, y: Tensor, slot_of_row: Tensor, w: Tensor | None, gro
     dw = torch.empty(rows, dtype=torch.float32, device=y.device) if need_dw else None
     _ck(_L().nb_combine_bwd(g.data_ptr(), g.stride(0), y.data_ptr(), y.stride(0), slot_of_row.data_ptr(), _ptr(w), group,
                             dy.data_ptr(), d, _ptr(dw), rows, d, _ptr(sh0), _ptr(sh1), sh0.stride(0) if sh0 is not None else 0,
-                            shared_div, float(shared_scale), _st()), "combine_bwd")
+                            shared_div, float(shared_scale), g.shape[0] * group, _st()), "combine_bwd")
     return dy, dw
 
 

@@ -635,3 +635,35 @@ def test_gathering_gemm_wait_runs_out_and_context_survives():
     torch.cuda.synchronize()
     _lib.check_status(torch.device("cuda"))
     assert torch.equal(again, want)
+
+
+def test_bounds_checking_build_records_a_bad_index_instead_of_reading_it():
+    """The index-checking library build (NESTOR_B200_BOUNDS_CHECK=1): an out-of-range gather index is recorded in the
+    status record and the row is skipped; valid rows are unaffected. Runs in a child process because a process loads
+    one build of the library."""
+
+    import os
+    import subprocess
+    import sys
+    code = r"""
+import torch
+from nestor_b200.ops import cuda as K, _lib
+assert _lib.lib().nb_bounds_check_enabled() == 1
+src = torch.arange(6 * 64, dtype=torch.float32, device="cuda").view(6, 64)
+idx = torch.tensor([0, 5, 17, 3], dtype=torch.int32, device="cuda")     # 17 is past the 6 source rows
+assert K.bounds_check_report() is None
+out = K.gather_rows(src, idx)
+rep = K.bounds_check_report()
+assert rep == {"code": 7, "kernel": "gather_rows", "index": 17, "row": 2}, rep
+assert torch.equal(out[[0, 1, 3]].float(), src[[0, 5, 3]].bfloat16().float())
+assert K.bounds_check_report() is None            # reading clears the record
+y = torch.randn(8, 64, device="cuda").bfloat16()
+bad = torch.tensor([1, 9], dtype=torch.int32, device="cuda")
+o = K.combine_rows(y, bad, None, 1, 2)
+assert K.bounds_check_report()["kernel"] == "combine_rows" and torch.equal(o[0], y[1].float()) and float(o[1].abs().sum()) == 0
+print("BOUNDS_OK")
+"""
+    env = dict(os.environ, NESTOR_B200_BOUNDS_CHECK="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and "BOUNDS_OK" in res.stdout, res.stdout + res.stderr
