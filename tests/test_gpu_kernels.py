@@ -590,9 +590,10 @@ def test_fastpath_check_prints_kernel_vs_oracle_difference(capsys, monkeypatch):
     monkeypatch.setenv("DCLM_DATA_PATH", "/tmp/unused.bin")
     from nestor_b200.experiments.tiny import nestor_tiny
     from nestor_b200.models import Model
+    from nestor_b200.train.trainer import Trainer
     torch.manual_seed(0)
-    m = Model.from_config(nestor_tiny().jobs[0].model).cuda().eval()
-    m.compute_dtype = BF
+    job = nestor_tiny().jobs[0]
+    m = Trainer(job, Model.from_config(job.model), [], device=torch.device("cuda")).model.eval()   # weights in the bf16 arena
     ids = torch.randint(0, 100277, (2, 128), device="cuda")
     with torch.no_grad():
         for _ in range(4):
