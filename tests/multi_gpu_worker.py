@@ -168,8 +168,11 @@ def main() -> None:
             sd = tr.optimizer.state_dict()
             assert len(sd["state"]) == sum(len(g["params"]) for g in sd["param_groups"]), "optimizer state incomplete"
         del tr
+    # the two paths sum the clip norm in different orders (and an in-switch reduction fixes no order at all); the
+    # Newton-Schulz iteration runs in bf16, where a last-bit difference of its input flips roundings, so the
+    # parameters agree to bf16-iteration noise rather than to fp32 round-off
     rel = ((results["1"] - results["0"]).norm() / results["0"].norm()).item()
-    assert rel < 1e-5, f"sharded and replicated optimizer paths disagree: {rel}"
+    assert rel < 5e-4, f"sharded and replicated optimizer paths disagree: {rel}"
     # expert banks read from their owner ranks through the all-gather fused into the bank GEMMs
     from nestor_b200.ops import cuda as cuda_ops
     os.environ["NESTOR_ZERO1"], os.environ["NESTOR_FSDP_BANKS"] = "1", "1"
@@ -188,7 +191,7 @@ def main() -> None:
     assert cuda_ops.BANK_SHARDS.gathered_bytes > 0, "no bank product used the fused all-gather"
     tr.gather_masters()
     rel = ((tr.arena.master - results["1"]).norm() / results["1"].norm()).item()
-    assert rel < 1e-5, f"rank-sharded banks disagree with replicated banks: {rel}"
+    assert rel < 5e-4, f"rank-sharded banks disagree with replicated banks: {rel}"
     cuda_ops.BANK_SHARDS = None
     os.environ["NESTOR_FSDP_BANKS"] = "0"
     dist.barrier()
