@@ -24,6 +24,7 @@ from nestor_b200.models.nestor import Nestor, W
 from nestor_b200.models.registry import (
     ADAPTERS, BACKBONES, HEADS, MODELS, register_adapter, register_backbone, register_head, register_model,
 )
+from nestor_b200.models.scaling import _ACTIVATIONS as SCALING_ACTIVATIONS, RMSNorm, ScaledLinear
 from nestor_b200.models.tags import ADAMW_DECAY, tag
 
 
@@ -50,7 +51,11 @@ class ByteTokenizer:
 
 @register_adapter(TextAdapterConfig)
 class TextAdapter(nn.Module):
-    """Token embedding table; output ``E[ids] * embedding_multiplier`` in fp32.
+    """Token embedding table; output ``norm(E[ids]) * embedding_multiplier`` in fp32.
+
+    Without a reference-muP recipe the embeddings are normalised to unit RMS (learned gain) before the first block, as
+    in the reference's adapter (``nestor/adapters/text.py:71-75,150``); the recipe replaces that norm by the identity
+    and scales by its embedding multiplier instead (``nestor/scaling/reference_mup.py:320``).
 
     The adapter is also the tokenizer for string inputs (reference ``nestor/adapters/text.py:59-101``): a tiktoken
     encoding named by ``config.tokenizer`` (loaded lazily; pre-tokenised tensors never need it), or the built-in
@@ -68,7 +73,7 @@ class TextAdapter(nn.Module):
         std = mup.initializer_range if mup is not None else 1.0
         nn.init.normal_(self.embed.weight, 0.0, std)
         self.embedding_multiplier = mup.embedding_multiplier if mup is not None else 1.0
-
+        self.norm = RMSNorm(config.embed_dim) if mup is None else None
         self._tokenizer: Any = None
 
     def tokenizer(self) -> Any:
@@ -101,19 +106,32 @@ class TextAdapter(nn.Module):
         return ids.to(device), valid.to(device)
 
     def forward(self, ids: Tensor) -> Tensor:
-        return self.embed(ids).float() * self.embedding_multiplier
+        x = self.embed(ids).float()
+        if self.norm is not None:
+            x = self.norm(x)
+        return x * self.embedding_multiplier
 
 
 @register_head(LanguageModelingHeadConfig)
 class LanguageModelingHead(nn.Module):
-    """Single-matrix unembedding ``[V, d]``; ``logit_multiplier = 1 / width_multiplier`` under muP."""
+    """Unembedding ``[V, d]``, optionally behind hidden layers; ``logit_multiplier = 1 / width_multiplier`` under muP.
+
+    ``hidden_dims`` (usually empty) inserts in-stream layers with ``activation`` between the backbone features and the
+    vocabulary matrix (reference ``nestor/heads/language_modeling.py:70-76``). They run as ``pre``; the vocabulary
+    matrix stays a single ``[V, d_last]`` weight so that the fused head + cross-entropy kernel path applies to it
+    unchanged.
+    """
 
     def __init__(self, config: LanguageModelingHeadConfig, dim: int, mup: ReferenceMupConfig | None) -> None:
         super().__init__()
-        if config.hidden_dims:
-            raise ValueError("Only the single-matrix LM head is supported (hidden_dims must be empty).")
-        std = mup.initializer_range if mup is not None else 1.0 / dim
-        self.projection = LayerStack([Matrix(dim, config.vocab_size, ADAMW_DECAY, std)])
+        dims = [dim, *config.hidden_dims]
+        self.hidden = nn.ModuleList(ScaledLinear(a, b, role="in_stream") for a, b in zip(dims[:-1], dims[1:]))
+        if config.activation not in SCALING_ACTIVATIONS:
+            raise ValueError(f"Unknown head activation {config.activation!r}.")
+        self.activation = config.activation
+        last = dims[-1]
+        std = mup.initializer_range if mup is not None else 1.0 / last
+        self.projection = LayerStack([Matrix(last, config.vocab_size, ADAMW_DECAY, std)])
         self.logit_multiplier = 1.0 / mup.width_multiplier if mup is not None else 1.0
         self.vocab_size = config.vocab_size
 
@@ -121,8 +139,16 @@ class LanguageModelingHead(nn.Module):
     def weight(self) -> Tensor:
         return self.projection.layers[0].weight
 
+    def pre(self, h: Tensor) -> Tensor:
+        """The hidden layers in front of the vocabulary matrix (identity for the usual single-matrix head)."""
+
+        act = SCALING_ACTIVATIONS[self.activation]
+        for layer in self.hidden:
+            h = act(layer(h.to(layer.weight.dtype)))
+        return h
+
     def forward(self, h: Tensor, cd: torch.dtype) -> Tensor:
-        return (h.to(cd) @ W(self, self.weight).to(cd).t()) * self.logit_multiplier
+        return (self.pre(h).to(cd) @ W(self, self.weight).to(cd).t()) * self.logit_multiplier
 
 
 register_backbone(NestorConfig)(lambda config, mup, **kw: Nestor(config, mup, **kw))
@@ -197,7 +223,7 @@ class SequenceModel(nn.Module):
                         layer["expert_router"]["valid_token_mask"] = flat
         if self.fused_head:
             aux["fused_head_module"] = self.head
-            return ModelOutput(pred=h.view(B, S, -1), aux=aux)
+            return ModelOutput(pred=self.head.pre(h).view(B, S, -1), aux=aux)
         return ModelOutput(pred=self.head(h, cd).view(B, S, -1), aux=aux)
 
     def _checked_forward(self, x0: Tensor, B: int, S: int, cd: torch.dtype, pos, noises):

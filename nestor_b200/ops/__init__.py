@@ -39,6 +39,16 @@ def launch_count() -> int:
     return _lib.LAUNCHES
 
 
+def oracle_path_report() -> dict[str, int]:
+    """Calls that left the kernel library because a shape crossed a kernel's built-in limit (op name -> count).
+
+    Such calls warn the first time and raise under ``NESTOR_B200_STRICT=1``; an empty dict means every op of the
+    process ran on the sm_100a kernels.
+    """
+
+    return cuda_ops().oracle_path_report() if _cuda_mod is not None else {}
+
+
 _oracle_depth = 0
 
 

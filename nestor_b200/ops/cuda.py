@@ -22,6 +22,28 @@ from torch import Tensor
 
 from nestor_b200.ops import _lib, flash, gemm as G
 from nestor_b200.ops import reference as ref
+
+# Shapes beyond a kernel's built-in limits run the PyTorch statement of the op instead. That is never silent: the first
+# such call of each kind warns with the limit it crossed, every call is counted (``oracle_path_report()``), and
+# ``NESTOR_B200_STRICT=1`` turns it into an error.
+_oracle_calls: dict[str, int] = {}
+
+
+def _oracle_path(op: str, why: str) -> None:
+    import os
+    import warnings
+    if os.environ.get("NESTOR_B200_STRICT", "0") == "1":
+        raise RuntimeError(f"{op}: {why}; the kernel library has no body for this shape (NESTOR_B200_STRICT=1)")
+    if op not in _oracle_calls:
+        warnings.warn(f"{op}: {why}; running the PyTorch statement of the op instead of the sm_100a kernel", RuntimeWarning,
+                      stacklevel=3)
+    _oracle_calls[op] = _oracle_calls.get(op, 0) + 1
+
+
+def oracle_path_report() -> dict[str, int]:
+    """How many calls of each op left the kernel library because of a shape limit since import."""
+
+    return dict(_oracle_calls)
 from nestor_b200.ops.reference import ColumnPlan, ExpertPlan
 
 BF16 = torch.bfloat16
@@ -722,6 +744,7 @@ def build_column_plan(idx, G_, pos=None):
 
     B, S, k = idx.shape
     if G_ * B > 256:
+        _oracle_path("build_column_plan", f"columns x sequences = {G_ * B} exceeds the 256 sort keys of the counting-sort kernels")
         return ref.build_column_plan(idx, G_, pos)
     dev = idx.device
     T, n = B * S, B * S * k
@@ -745,6 +768,7 @@ def build_expert_plan(expert_ids, E):
     """Counting sort by expert (three small kernels; the oracle sorts)."""
 
     if E > 256:
+        _oracle_path("build_expert_plan", f"{E} experts exceed the 256 sort keys of the counting-sort kernels")
         return ref.build_expert_plan(expert_ids, E)
     T, slots = expert_ids.shape
     ids = expert_ids.reshape(-1)
@@ -839,6 +863,8 @@ def route_topk(scores: Tensor, bias: Tensor, k: int, gate_mode: str):
     """Kernel body of ``reference.route_topk`` for 2-D score matrices (others take the oracle path)."""
 
     if scores.ndim != 2 or scores.shape[-1] > 64 or k > 8 or scores.stride(-1) != 1:
+        _oracle_path("route_topk", f"scores {tuple(scores.shape)} stride {scores.stride()} k={k}: the routing kernel takes 2-D "
+                                   "row-major scores with at most 64 candidates and k <= 8")
         return ref.route_topk(scores, bias, k, gate_mode)
     tape = ref._TAPE
     idx_in = None
@@ -854,6 +880,8 @@ def route_topk(scores: Tensor, bias: Tensor, k: int, gate_mode: str):
 def route_selected(scores: Tensor, bias: Tensor, cols: Tensor, col_gates: Tensor, k: int, gate_mode: str, cd):
     T, Gn, Q = scores.shape
     if Q > 64 or k > 8 or scores.stride(-1) != 1 or scores.stride(1) != Q or cd != BF16:
+        _oracle_path("route_selected", f"scores {tuple(scores.shape)} k={k} dtype {cd}: the routing kernel takes packed bf16-path "
+                                       "scores with at most 64 experts per column and k <= 8")
         return ref.route_selected(scores, bias, cols, col_gates, k, gate_mode, cd)
     kc = cols.shape[1]
     tape = ref._TAPE

@@ -1,7 +1,7 @@
 """Micro-benchmark of the in-kernel collectives against NCCL (gradient all-reduce + cast, parameter push).
 
 ``torchrun --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 -m nestor_b200.scripts.bench_collectives``
-times, for 1 MB ... 1 GB fp32 buffers: the all-reduce kernel (fp32 sum, 1/W scale, optional bf16 mirror) and
+(or ``python -m nestor_b200.scripts.bench_collectives`` for the one-rank local leg of each kernel) times, for 1 MB ... 1 GB fp32 buffers: the all-reduce kernel (fp32 sum, 1/W scale, optional bf16 mirror) and
 ``torch.distributed.all_reduce`` (NCCL) on the same buffer, the reduce-scatter onto per-rank ranges against
 ``reduce_scatter_tensor``, and the parameter push (all-gather fused with the bf16 cast) against
 ``all_gather_into_tensor`` + cast. Each of ours is timed on plain peer loads/stores and, when the symmetric buffers
@@ -54,6 +54,11 @@ def main(argv: list[str] | None = None) -> None:
     from nestor_b200.parallel import symm
     from nestor_b200.utils.distributed import init_distributed
     dev = init_distributed(True)
+    if not dist.is_initialized():
+        # a single rank (no launcher): the kernels then run their local leg only (flag round trip with itself, own
+        # buffer read, scaled, written), which is the case a one-GPU profiler capture can take
+        os.environ.setdefault("MASTER_PORT", "29655")
+        dist.init_process_group("nccl", init_method="env://", world_size=1, rank=0, device_id=dev)
     rank, world = dist.get_rank(), dist.get_world_size()
     nmax = max(a.sizes_mb) * 1024 * 1024 // 4
     g = symm.symmetric_empty(nmax, torch.float32, dev)

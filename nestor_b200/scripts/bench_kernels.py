@@ -200,7 +200,7 @@ def main(argv: list[str] | None = None) -> None:
     torch.manual_seed(0)
     for c in a.cases:
         if c == "small":
-            case_gemm(a.reps, small=True); case_flash(a.reps, small=True); case_depth(a.reps, small=True)
+            case_gemm(a.reps, small=True); case_flash(a.reps, small=True); case_depth(a.reps, small=True); case_ns(a.reps, small=True)
         else:
             {"gemm": case_gemm, "flash": case_flash, "depth": case_depth, "gather": case_gather, "ns": case_ns}[c](a.reps)
     from nestor_b200.ops import _lib

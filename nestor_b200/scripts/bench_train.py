@@ -23,6 +23,9 @@ def main(argv: list[str] | None = None) -> None:
     ap.add_argument("--accum", type=int, default=4)
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--kernel-table", type=int, default=0, metavar="ROWS",
+                    help="after the timed steps, run one more step under torch.profiler and print the ROWS kernels "
+                         "with the most device time (use with NESTOR_B200_CUDA_GRAPH=0: a replayed graph shows as one item)")
     a = ap.parse_args(argv)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     os.environ["DCLM_BLOCK_SIZE"] = str(a.block_size)
@@ -90,6 +93,20 @@ def main(argv: list[str] | None = None) -> None:
             "peak_mem_gib": torch.cuda.max_memory_allocated(device) / 2 ** 30,
             "gpu_launches_per_step": (ops.launch_count() - n0) / a.steps,
             "flags": {k: v for k, v in os.environ.items() if k.startswith("NESTOR_")}}), flush=True)
+    if a.kernel_table > 0 and int(os.environ.get("RANK", "0")) == 0:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            step()
+            torch.cuda.synchronize(device)
+        events = [e for e in prof.key_averages() if e.device_type == torch.autograd.DeviceType.CUDA]
+        events.sort(key=lambda e: -e.device_time_total)
+        total = sum(e.device_time_total for e in events)
+        ours = sum(e.device_time_total for e in events if "nb" in e.key.split("(")[0])
+        print(f"device time of one step: {total / 1e3:.2f} ms in {sum(e.count for e in events)} launches; "
+              f"{ours / max(total, 1):.1%} in the in-tree kernels", flush=True)
+        for e in events[: a.kernel_table]:
+            print(f"{e.device_time_total / 1e3:9.3f} ms {e.device_time_total / max(total, 1):6.1%} {e.count:6d} x "
+                  f"{e.device_time_total / max(e.count, 1):8.1f} us  {e.key[:110]}", flush=True)
     if world > 1:
         dist.destroy_process_group()
 

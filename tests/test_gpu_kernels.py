@@ -524,6 +524,27 @@ def test_dispatch_refuses_cuda_tensor_without_kernel_body():
     assert ops.use_kernels(x)
 
 
+def test_shape_beyond_a_kernel_limit_warns_counts_and_raises_when_strict(monkeypatch):
+    """k = 9 is past the routing kernel's k <= 8: the call runs the PyTorch statement, says so once, is counted, and
+    is an error under NESTOR_B200_STRICT=1."""
+
+    from nestor_b200 import ops
+    from nestor_b200.ops import reference as R
+    scores = torch.randn(64, 32, device="cuda")
+    bias = torch.zeros(32, device="cuda")
+    before = ops.cuda_ops().oracle_path_report().get("route_topk", 0)
+    ops.cuda_ops()._oracle_calls.pop("route_topk", None)
+    with pytest.warns(RuntimeWarning, match="k <= 8"):
+        idx, gates = ops.cuda_ops().route_topk(scores, bias, 9, "renorm")
+    want_idx, want_gates = R.route_topk(scores, bias, 9, "renorm")
+    assert torch.equal(idx, want_idx) and torch.allclose(gates, want_gates)
+    assert ops.oracle_path_report()["route_topk"] == 1
+    ops.cuda_ops()._oracle_calls["route_topk"] += before
+    monkeypatch.setenv("NESTOR_B200_STRICT", "1")
+    with pytest.raises(RuntimeError, match="no body for this shape"):
+        ops.cuda_ops().route_topk(scores, bias, 9, "renorm")
+
+
 def _poison_allocator(gib: float = 1.5):
     """Fill the caching allocator's free blocks with inf / NaN: memory a later ``torch.empty`` hands out is dirty, so
     any row or column a kernel leaves unwritten shows up in its output (the reference's dirty-allocator discipline,

@@ -50,3 +50,31 @@ def test_mask_must_be_a_prefix_and_tokenizer_errors_are_clear(tiny_scale):
     with pytest.raises(ValueError, match="prefix"):
         m(ids, valid=torch.tensor([[True, False, True, True, False, False]]))
     assert m.adapter.tokenizer().decode(m.adapter.tokenizer().encode_ordinary("héllo")) == "héllo"
+
+
+def test_adapter_norm_without_mup_and_head_hidden_layers(tiny_scale):
+    """Without the reference-muP recipe the adapter normalises embeddings to unit RMS (reference
+    nestor/adapters/text.py:150); a head with hidden_dims runs its hidden layers in front of the vocabulary matrix,
+    and the fused head + cross-entropy path sees the same features as the plain one."""
+
+    from nestor_b200.models import Model
+    cfg = tiny_scale.build_experiment("dense", "tiny").jobs[0].model
+    cfg = dc.replace(cfg, reference_mup=None,
+                     head_config=dc.replace(cfg.head_config, hidden_dims=[48], activation="gelu"))
+    torch.manual_seed(0)
+    m = Model.from_config(cfg).eval()
+    ids = torch.randint(0, 255, (2, 12))
+    x = m.adapter(ids)
+    assert torch.allclose(x.pow(2).mean(-1), torch.ones(2, 12), atol=1e-3)
+    assert m.adapter.norm is not None and len(m.head.hidden) == 1 and m.head.weight.shape[1] == 48
+    with torch.no_grad():
+        plain = m(ids)
+        m.fused_head = True
+        fused = m(ids)
+    assert fused.pred.shape[-1] == 48 and plain.pred.shape[-1] == cfg.head_config.vocab_size
+    a = CausalLMLoss()(plain.pred, ids, plain.aux).total
+    b = CausalLMLoss()(fused.pred, ids, fused.aux).total
+    assert torch.allclose(a, b, atol=1e-5)
+    # the hidden layer is an in-stream matrix (Muon) and trains
+    names = {n for n, _ in m.named_parameters()}
+    assert "head.hidden.0.weight" in names and "adapter.norm.weight" in names

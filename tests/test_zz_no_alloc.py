@@ -33,6 +33,31 @@ def _args(q, k, v, o, do, lse, delta, dqkv, seg, H, hd, status):
     return a
 
 
+def _oracle(qkv, do, lens, H, hd):
+    """fp32 PyTorch statement of the op: causal softmax attention per segment, gradients by autograd."""
+
+    inner = H * hd
+    x = qkv.float().requires_grad_()
+    outs, b = [], 0
+    for n in lens:
+        q, k, v = (x[b:b + n, i * inner:(i + 1) * inner].view(n, H, hd).transpose(0, 1) for i in range(3))
+        s = (q @ k.transpose(1, 2)) / hd
+        s = s.masked_fill(torch.ones(n, n, dtype=torch.bool, device=x.device).triu(1), float("-inf"))
+        outs.append((s.softmax(-1) @ v).transpose(0, 1).reshape(n, inner))
+        b += n
+    torch.cat(outs).backward(do.float())
+    return x.grad
+
+
+def test_args_struct_has_the_size_the_library_expects():
+    from nestor_b200.ops import _lib
+    L = _lib.lib()
+    L.nb_flash_bwd_args_size.restype = C.c_int
+    L.nb_flash_args_size.restype = C.c_int
+    assert L.nb_flash_bwd_args_size() == C.sizeof(_lib.FlashBwdArgs)
+    assert L.nb_flash_args_size() == C.sizeof(_lib.FlashArgs)
+
+
 def test_noalloc_entry_point_matches_regular_entry_point():
     from nestor_b200.ops import _lib, flash
     L = _lib.lib()
@@ -63,8 +88,43 @@ def test_noalloc_entry_point_matches_regular_entry_point():
         assert torch.isfinite(got.float()).all()
         rel = ((got.float() - want.float()).norm() / want.float().norm()).item()
         assert rel < 2e-2, (call, rel)
+        exact = _oracle(qkv, do, lens, H, hd)
+        rel = ((got.float() - exact).norm() / exact.norm()).item()
+        assert rel < 2e-2, ("against the fp32 statement of the op", call, rel)
     # a problem beyond the built-in scratch is refused with a message, and nothing is launched
     big = _args(q, k, v, o, do, lse, None, got, seg, H, hd, status)
     big.rows = (1 << 20) // H + 1
     assert L.nb_flash_bwd_noalloc(C.byref(big), stream) == -100
     assert b"exceeds the built-in scratch" in L.nb_flash_bwd_noalloc_error()
+
+
+def test_noalloc_entry_point_on_a_second_device():
+    """The scratch symbol is resolved per device; a call on device 1 uses device 1's copy."""
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two devices")
+    from nestor_b200.ops import _lib, flash
+    L = _lib.lib()
+    L.nb_flash_bwd_noalloc.argtypes = [C.POINTER(_lib.FlashBwdArgs), C.c_void_p]
+    L.nb_flash_bwd_noalloc.restype = C.c_int
+    L.nb_flash_bwd_noalloc_error.restype = C.c_char_p
+    dev = torch.device("cuda", 1)
+    with torch.cuda.device(dev):
+        torch.manual_seed(3)
+        H, hd, lens = 2, 40, [260, 130]
+        rows, inner = sum(lens), H * hd
+        status = _lib.status_word(dev)
+        stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        qkv = torch.randn(rows, 3 * inner, device=dev).to(torch.bfloat16)
+        seg = torch.tensor([0, 260, 390], dtype=torch.int32, device=dev)
+        q, k, v = qkv[:, :inner], qkv[:, inner:2 * inner], qkv[:, 2 * inner:]
+        o, lse = flash.flash_fwd(q, k, v, seg, H, hd, 1.0 / hd)
+        do = torch.randn(rows, inner, device=dev).to(torch.bfloat16)
+        got = torch.full((rows, 3 * inner), float("nan"), device=dev, dtype=torch.bfloat16)
+        rc = L.nb_flash_bwd_noalloc(C.byref(_args(q, k, v, o, do, lse, None, got, seg, H, hd, status)), stream)
+        assert rc == 0, L.nb_flash_bwd_noalloc_error()
+        torch.cuda.synchronize(dev)
+        _lib.check_status(dev)
+        exact = _oracle(qkv, do, lens, H, hd)
+        rel = ((got.float() - exact).norm() / exact.norm()).item()
+        assert rel < 2e-2, rel
