@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(192, HDN == 64 ? 2 : 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ uint64_t q_full, kv_full[KVS], kv_empty[KVS], s_full[2], s_empty[2], p_ready, o_full[2];
+  __shared__ uint64_t q_full, kv_full[KVS], kv_empty[KVS], s_full[2], s_empty[2], p_ready[2], o_full[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
   __shared__ int s_tile[4];   // seg begin, seg end, q0, valid
@@ -92,8 +92,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       s_abort = 0;
       mbar_init(&q_full, 1);
       for (int i = 0; i < KVS; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
-      for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4); mbar_init(&o_full[i], 1); }
-      mbar_init(&p_ready, 4);
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4); mbar_init(&o_full[i], 1); mbar_init(&p_ready[i], 4);
+      }
       fence_barrier_init();
       prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
     }
@@ -140,7 +141,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int j = 0; j < ntiles && ok; ++j) {
       const int s = j % KVS;
       FD_T(u0);
-      ok = mbar_wait(&p_ready, j & 1, abort_flag, p.status, kTimeoutTmemEmpty);
+      // One barrier per P buffer. With a single barrier a softmax warp that runs one tile ahead (it may, the buffers
+      // alternate) would supply the fourth arrival of tile j with its arrival for tile j + 1 while a slower warp is
+      // still writing its rows of P_j, and the product below would read those rows before they exist. On barrier
+      // j & 1 an early arrival is impossible: a warp reaches tile j + 2 only after P_j V_j has retired.
+      ok = mbar_wait(&p_ready[j & 1], (j >> 1) & 1, abort_flag, p.status, kTimeoutTmemEmpty);
       if (!ok) break;
       // (the V tile landed before S_j was issued, which precedes these probabilities; waiting on its barrier here as
       // well makes this warp an observer of the copy in its own right)
@@ -304,7 +309,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       fence_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_ready);
+      if (lane == 0) mbar_arrive(&p_ready[j & 1]);
       FD_T(t7); FD_ADD(6, t6, t7);
     }
 #ifdef NB_FLASH_DIAG

@@ -93,6 +93,7 @@ struct GemmParams {
   int prefetch_ops;            // operands to prefetch: 1 = A, 2 = B, 3 = both
   int pair;                    // mode 0: CTA pairs (cluster of 2) run 256-row tiles with cta_group::2 MMAs
   int a_atoms, b_atoms;        // MN-major operand read through an "atom" map: one TMA instruction per k-block
+  int c_tiled;                 // the output has a tensor map (tmC): whole 32-row chunks leave as tiled stores
   int debug;                   // timing experiments only (results are garbage): 1 = issue no MMAs, 2 = issue no loads, 4 = store nothing
   GatherParams gather;         // fused all-gather of a rank-sharded B operand (gather.on == 0: off)
 };
@@ -140,13 +141,14 @@ __device__ __forceinline__ Tile decode_tile(const GemmParams& p, const int* s_of
     r.kb = (p.K + BK - 1) / BK;
     r.kb2 = (p.K2 + BK - 1) / BK;
   } else {
-    int m_tiles = (p.M + BM - 1) / BM;
+    const int bm = p.pair ? 2 * BM : BM;             // a pair's tile is 256 output rows; rank 1 owns the lower half
+    int m_tiles = (p.M + bm - 1) / bm;
     int per_g = m_tiles * n_tiles * p.splits;
     r.g = t / per_g;
     int rem = t - r.g * per_g;
     int sp = rem % p.splits; rem /= p.splits;
     int mt = rem / n_tiles, nt = rem - mt * n_tiles;
-    r.m0 = mt * BM;
+    r.m0 = mt * bm + rank * BM;
     r.n0 = nt * p.BN;
     r.row_end = s_off[r.g + 1];
     int nkb = (s_off[r.g + 1] - s_off[r.g] + BK - 1) / BK;
@@ -164,6 +166,7 @@ __device__ __forceinline__ Tile decode_tile(const GemmParams& p, const int* s_of
 // row-per-lane writes and the read-back free of bank conflicts) and stores 8 rows x 64 B per instruction.
 constexpr int kSlabPitch = 80;
 constexpr int kSlabBytes = 32 * kSlabPitch;      // per epilogue warp
+constexpr int kSlabBytesF32 = 32 * 128;          // per epilogue warp, fp32 outputs of a reduction-grouped product
 
 // w[16] = this lane's row, 32 bf16 columns (packed pairs). Rows >= rows_ok and 8-column groups >= cols_ok (a
 // multiple of 8) are not stored. `dst` points at (row 0 of the slab's 32 rows, first column of the chunk).
@@ -310,7 +313,7 @@ template <int PAIR, int EPI, int GATHER>
 __global__ void __launch_bounds__(GATHER ? 384 : 352, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
-            const __grid_constant__ GemmParams p, int stages) {
+            const __grid_constant__ CUtensorMap tmC, const __grid_constant__ GemmParams p, int stages) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ uint64_t full_bar[8], empty_bar[8], tfull_bar[2], tempty_bar[2];
   __shared__ uint64_t gather_bar[GATHER ? 8 : 1];
@@ -361,7 +364,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   int total_tiles;
   if (p.mode == 0) total_tiles = s_tstart[p.groups] * n_tiles;
-  else total_tiles = p.groups * ((p.M + BM - 1) / BM) * n_tiles * p.splits;
+  else total_tiles = p.groups * ((p.M + (pair ? 2 * BM : BM) - 1) / (pair ? 2 * BM : BM)) * n_tiles * p.splits;
 
   volatile int* abort_flag = &s_abort;
   const int cta = pair ? int(blockIdx.x >> 1) : int(blockIdx.x);       // persistent worker index
@@ -439,8 +442,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             else { ld2(sa, mA, bar, tl.m0, row, pf); ld2(sa + 8192, mA, bar, tl.m0 + 64, row, pf); }
           }
           if (doB) {
-            if (p.b_atoms) { if (!pf) ld3(sb, mB, bar, 0, row, tl.n0 / 64, 0); }
-            else for (int a = 0; a < p.BN / 64; ++a) ld2(sb + a * 8192, mB, bar, tl.n0 + a * 64, row, pf);
+            const int nb0 = tl.n0 + int(rank) * b_cols;    // first B column staged by this CTA
+            if (p.b_atoms) { if (!pf) ld3(sb, mB, bar, 0, row, nb0 / 64, 0); }
+            else for (int a = 0; a < b_cols / 64; ++a) ld2(sb + a * 8192, mB, bar, nb0 + a * 64, row, pf);
           }
         }
       };
@@ -544,13 +548,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           {
             uint8_t* sa = smem + s * stage_bytes;
             uint8_t* sb = sa + a_bytes;
-            int natoms = 2 + p.BN / 64;
+            const int natoms = 2 + b_cols / 64;
             for (int a = 0; a < natoms; ++a) {
               uint8_t* base = (a < 2) ? sa + a * 8192 : sb + (a - 2) * 8192;
               for (int r = valid; r < BK; ++r)
                 reinterpret_cast<uint32_t*>(base + r * 128)[lane] = 0u;
+              if (pair) {
+                // the peer's half of the stage (its A rows, its B columns) sits at the same offsets of its shared
+                // memory; its loads have landed too (they complete on this CTA's barrier)
+                const uint32_t peer = mapa_shared(smem_u32(base), 1);
+                for (int r = valid; r < BK; ++r) st_shared_cluster_u32(peer + uint32_t(r) * 128u + uint32_t(lane) * 4u, 0u);
+              }
             }
-            fence_async_smem();
+            if (pair) fence_async_all(); else fence_async_smem();
             __syncwarp();
           }
         }
@@ -603,7 +613,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // chunk is in flight while the current one is converted and stored.
     const int q = warp & 3;
     const int grp = (warp - 2) >> 2;             // column group 0 / 1
-    uint8_t* slab = smem + uint32_t(stages) * stage_bytes + (warp - 2) * kSlabBytes;
+    // fp32 outputs of a reduction-grouped product leave through a 32 x 32 fp32 slab and one tiled reduce / store
+    constexpr bool kF32Epi = EPI == kStoreF32 || EPI == kAccumF32;
+    const bool tiled_out = kF32Epi && p.mode == 1 && p.c_tiled != 0;
+    // bf16 outputs of a row-grouped product: a warp whose 32 rows all belong to the tile's group hands its 32 x 32
+    // chunk to one tiled store (64-byte rows in the slab, 16-byte groups XOR-swizzled as the map expects); a warp
+    // that straddles the end of a group stores row by row through the masked path
+    constexpr bool kBf16Tiled = EPI == kStoreBf16 || EPI == kStoreBf16Stats || EPI == kAxpbyBf16;
+    const bool c_tiled = kBf16Tiled && p.c_tiled != 0;
+    uint8_t* slab = smem + uint32_t(stages) * stage_bytes + (warp - 2) * (tiled_out ? kSlabBytesF32 : kSlabBytes);
     uint32_t tile_i = 0;
     int g_hint = 0;
     const bool trace_on = kDiag && p.trace != nullptr;
@@ -676,6 +694,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if (nkb == 0) return;
           if (ncols - 32 * jj > 16) tmem_ld32(taddr + 32 * jj, v); else tmem_ld16(taddr + 32 * jj, v);
         };
+        auto store_bf16 = [&](const uint32_t* w, int c0, int rem) {
+          if (kBf16Tiled) { bulk_wait_read<0>(); __syncwarp(); }       // lane 0: the slab's last tiled store has read it
+          // (a chunk cut short by the tile's width, not by N, must not spill into the neighbouring tile's columns)
+          if (c_tiled && rows_w == 32 && (rem >= 32 || tl.n0 + c0 + rem >= p.N)) {
+            uint4* mine = reinterpret_cast<uint4*>(slab + lane * 64);
+            const int sw = (lane >> 1) & 3;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) mine[j ^ sw] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) { tma_store_2d(&tmC, slab, tl.n0 + c0, row_w); bulk_commit(); }
+          } else {
+            store_chunk_bf16(slab, lane, w, reinterpret_cast<__nv_bfloat16*>(p.C) + cw_base + tl.n0 + c0, p.ldc, rows_w, rem);
+          }
+        };
         auto process = [&](float* v, int c0) {
           const int rem = ncols - c0;            // columns of this chunk that exist: 8, 16, 24 or >= 32
           if (EPI == kStoreBf16 || EPI == kStoreBf16Stats) {
@@ -686,7 +719,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             uint32_t w[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) w[j] = pack_bf16(v[2 * j] * p.alpha, v[2 * j + 1] * p.alpha);
-            store_chunk_bf16(slab, lane, w, reinterpret_cast<__nv_bfloat16*>(p.C) + cw_base + tl.n0 + c0, p.ldc, rows_w, rem);
+            store_bf16(w, c0, rem);
             if (EPI == kStoreBf16Stats) {
               float m = run_max;
 #pragma unroll
@@ -729,15 +762,38 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             // C = alpha * acc + beta * E1 in fp32, one rounding to bf16
             const long oe = long(row_w) * p.lde + tl.n0 + c0;
             uint32_t ew[16], w[16];
+            bulk_wait_read<0>(); __syncwarp();           // the slab's last tiled store has read it
             load_chunk_bf16(slab, lane, ew, reinterpret_cast<const __nv_bfloat16*>(p.E1) + oe, p.lde, rows_w, rem);
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
               const float lo = __uint_as_float(ew[e] << 16), hi = __uint_as_float(ew[e] & 0xFFFF0000u);
               w[e] = pack_bf16(p.alpha * v[2 * e] + p.beta * lo, p.alpha * v[2 * e + 1] + p.beta * hi);
             }
-            store_chunk_bf16(slab, lane, w, reinterpret_cast<__nv_bfloat16*>(p.C) + cw_base + tl.n0 + c0, p.ldc, rows_w, rem);
+            store_bf16(w, c0, rem);
+          } else if (tiled_out) {
+            // fp32 outputs [G, M, N] (weight gradients): the lane's row goes to its 128-byte row of the slab, 16-byte
+            // groups XOR-swizzled by the row as the tensor map expects, and the 32 x 32 chunk leaves as one tiled
+            // reduce-add (or store). Rows past M and columns past N are clipped by the map. Per-lane vector
+            // reductions in the accumulator's row-per-lane shape touched 32 cache lines per instruction and cost
+            // 12.7 k cycles per 128 x 216 tile.
+            if (nkb > 0 || EPI == kStoreF32) {
+              bulk_wait_read<0>();                 // lane 0: the previous chunk's operation has read the slab
+              __syncwarp();
+              float4* mine = reinterpret_cast<float4*>(slab + lane * 128);
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                mine[j ^ (lane & 7)] = make_float4(v[4 * j] * p.alpha, v[4 * j + 1] * p.alpha, v[4 * j + 2] * p.alpha,
+                                                   v[4 * j + 3] * p.alpha);
+              fence_async_smem();
+              __syncwarp();
+              if (lane == 0 && row_w < p.M) {
+                if (EPI == kStoreF32) tma_store_3d(&tmC, slab, tl.n0 + c0, row_w, tl.g);
+                else tma_reduce_add_3d(&tmC, slab, tl.n0 + c0, row_w, tl.g);
+                bulk_commit();
+              }
+            }
           } else if (row_ok) {
-            // fp32 outputs (weight gradients): one row per lane
+            // fp32 outputs, row-grouped product: one row per lane
             float* Cp = reinterpret_cast<float*>(p.C) + c_base + tl.n0 + c0;
             if (EPI == kStoreF32) {
 #pragma unroll
@@ -791,6 +847,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (trace_on) e_work += clock64() - e_t0;
       }
     }
+    if (tiled_out || c_tiled) bulk_wait<0>();           // nothing of this CTA's shared memory is still being read when it leaves
     if (trace_on && warp == 4 && lane == 0) {
       unsigned long long* tr = p.trace + blockIdx.x * 64;
       tr[44] = e_decode; tr[45] = e_wait; tr[46] = e_work; tr[47] = tile_i;
@@ -836,14 +893,14 @@ EncodeFn encode_fn() {
 
 // bf16 tensor of rank 2 to 4 (dims innermost-first), strides in elements for dims 1.. (innermost is contiguous).
 int make_map(CUtensorMap* m, const void* base, int rank, const long* dims, const long* strides_elems,
-             const int* box) {
+             const int* box, int elem_bytes = 2, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeFn fn = encode_fn();
   if (!fn) return 1;
   cuuint64_t gd[4]; cuuint64_t gs[3]; cuuint32_t bx[4]; cuuint32_t es[4] = {1, 1, 1, 1};
   for (int i = 0; i < rank; ++i) { gd[i] = cuuint64_t(dims[i]); bx[i] = cuuint32_t(box[i]); }
-  for (int i = 0; i + 1 < rank; ++i) gs[i] = cuuint64_t(strides_elems[i]) * 2;
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, cuuint32_t(rank), const_cast<void*>(base), gd, gs, bx, es,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  for (int i = 0; i + 1 < rank; ++i) gs[i] = cuuint64_t(strides_elems[i]) * cuuint64_t(elem_bytes);
+  CUresult r = fn(m, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, cuuint32_t(rank), const_cast<void*>(base), gd, gs, bx, es,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : 2;
 }
@@ -891,6 +948,7 @@ struct NbGemmArgs {
   int gather_nbuf;          // ring depth per copying lane (chunks)
   int gather_lanes;         // copying lanes of the copy warp (0 = 1)
   unsigned gather_wait_polls;  // 0 = default (about half a second)
+  int no_tiled_store;          // 1 = bf16 outputs always leave through the row-masked store path
 };
 
 // Returns 0 on success, a negative code for bad arguments / map failures, or a CUDA error code.
@@ -903,13 +961,15 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
   if (a->mode == 1 && !(a->a_mn && a->b_mn)) return -5;
   if (a->epilogue == kSwiGLU && (a->BN % 128 || !a->b_mn)) return -6;
   const int pair = a->pair ? 1 : 0;
-  if (pair && (a->mode != 0 || a->a_mn || a->BN % 16 || (a->b_mn && a->BN % 128))) return -8;
+  // a pair splits B by columns: MN-major halves must be whole 64-column atoms. Reduction-grouped products (mode 1)
+  // take pairs too: each CTA stages its own 128 of the tile's 256 A columns and half of the B columns.
+  if (pair && ((a->mode == 0 && a->a_mn) || a->BN % 16 || ((a->b_mn || a->mode == 1) && a->BN % 128))) return -8;
   if (!g_num_sms) {   // the GPUs of one machine are identical: the first device asked answers for all
     int dev; cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  CUtensorMap tmA, tmB, tmA2, tmB2;
-  memset(&tmA2, 0, sizeof(tmA2)); memset(&tmB2, 0, sizeof(tmB2));
+  CUtensorMap tmA, tmB, tmA2, tmB2, tmC;
+  memset(&tmA2, 0, sizeof(tmA2)); memset(&tmB2, 0, sizeof(tmB2)); memset(&tmC, 0, sizeof(tmC));
   // An MN-major operand [k rows, cols] whose row pitch covers whole 64-column atoms can be viewed as
   // [64, k rows, atoms]: one box then fills every atom of a stage (atom-major in shared memory, as the MMA
   // descriptors expect). Columns past `cols` inside the last atom are whatever the pitch padding holds; they only
@@ -932,7 +992,7 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
     if (a->mode == 1) {
       if (b_atoms) {
         long dims[3] = {64, o.rows, (o.cols + 63) / 64}; long st[2] = {o.ld, 64};
-        int box[3] = {64, BK, a->BN / 64};
+        int box[3] = {64, BK, (pair ? a->BN / 2 : a->BN) / 64};
         return make_map(m, o.ptr, 3, dims, st, box);
       }
       long dims[2] = {o.cols, o.rows}; long st[1] = {o.ld};
@@ -955,6 +1015,23 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
   if (map_a(&tmA, a->A)) return -10;
   if (map_b(&tmB, a->B)) return -11;
   if (a->K2 > 0) { if (map_a(&tmA2, a->A2)) return -12; }
+  const bool tiled_out = a->mode == 1 && (a->epilogue == kStoreF32 || a->epilogue == kAccumF32) && !a->no_tiled_store;
+  if (tiled_out) {
+    // the fp32 output [G, M, N] as a tensor map: 32 x 32 boxes, 128-byte rows swizzled
+    if (a->ldc % 4 || a->c_group_stride % 4 || reinterpret_cast<uintptr_t>(a->C) % 16) return -14;
+    long dims[3] = {a->N, a->M, a->groups}; long st[2] = {a->ldc, a->groups > 1 ? a->c_group_stride : long(a->M) * a->ldc};
+    int box[3] = {32, 32, 1};
+    if (make_map(&tmC, a->C, 3, dims, st, box, 4)) return -14;
+  }
+  int c_tiled = tiled_out ? 1 : 0;
+  // bf16 output [rows, N] of a row-grouped product: 32 x 32 boxes, 64-byte rows, 64-byte swizzle
+  if (a->mode == 0 && (a->epilogue == kStoreBf16 || a->epilogue == kStoreBf16Stats || a->epilogue == kAxpbyBf16) &&
+      a->ldc % 8 == 0 && reinterpret_cast<uintptr_t>(a->C) % 16 == 0 && a->A.rows > 0 && !a->no_tiled_store) {
+    long dims[2] = {a->N, a->A.rows}; long st[1] = {a->ldc};
+    int box[2] = {32, 32};
+    if (make_map(&tmC, a->C, 2, dims, st, box, 2, CU_TENSOR_MAP_SWIZZLE_64B)) return -14;
+    c_tiled = 1;
+  }
   if (a->K2 > 0 || a->epilogue == kSwiGLU) { if (map_b(&tmB2, a->B2)) return -13; }
 
   GemmParams p;
@@ -970,12 +1047,13 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
   p.pair = pair;
   p.a_atoms = a_atoms; p.b_atoms = b_atoms;
   p.debug = a->debug;
+  p.c_tiled = c_tiled;
   p.splits = (a->mode == 1 && a->epilogue == kAccumF32 && a->splits > 1) ? a->splits : 1;
 
   const int n_tiles = (a->N + a->BN - 1) / a->BN;
   // mode 0: max_m_tiles bounds the row tiles over all groups (tiles of 256 rows for pairs)
   long tiles = a->mode == 0 ? long(a->max_m_tiles) * n_tiles
-                            : long(a->groups) * ((a->M + BM - 1) / BM) * n_tiles * p.splits;
+                            : long(a->groups) * ((a->M + (pair ? 2 * BM : BM) - 1) / (pair ? 2 * BM : BM)) * n_tiles * p.splits;
   if (tiles <= 0) return 0;
   const uint32_t stage_bytes = BM * BK * 2 + (pair ? a->BN / 2 : a->BN) * BK * 2;
   size_t ring_bytes = 0;
@@ -1005,12 +1083,13 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
     p.gather.wait_polls = a->gather_wait_polls ? a->gather_wait_polls : kGatherSpinLimit;
     ring_bytes = size_t(p.gather.nbuf) * p.gather.lanes * a->gather_chunk;
   }
-  int stages = int((200 * 1024 - ring_bytes) / stage_bytes);   // 227 KB per CTA minus epilogue slabs, barriers, offsets, alignment slack
+  const size_t slab_bytes = tiled_out ? kSlabBytesF32 : kSlabBytes;
+  int stages = int((200 * 1024 - ring_bytes - 8 * (slab_bytes - kSlabBytes)) / stage_bytes);   // 227 KB per CTA minus epilogue slabs, barriers, offsets, alignment slack
   if (stages > 8) stages = 8;
   if (a->max_stages > 0 && stages > a->max_stages) stages = a->max_stages;
   if (stages < 2) return -7;
-  size_t smem = size_t(stages) * stage_bytes + 1024 + 8 * kSlabBytes + ring_bytes;
-  typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams, int);
+  size_t smem = size_t(stages) * stage_bytes + 1024 + 8 * slab_bytes + ring_bytes;
+  typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams, int);
   static const KernelFn kernels[2][7] = {
       {gemm_kernel<0, 0, 0>, gemm_kernel<0, 1, 0>, gemm_kernel<0, 2, 0>, gemm_kernel<0, 3, 0>, gemm_kernel<0, 4, 0>, gemm_kernel<0, 5, 0>,
        gemm_kernel<0, 6, 0>},
@@ -1038,7 +1117,7 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
   }
   if (!pair) {
     int grid = int(tiles < sms ? tiles : sms);
-    kernel<<<grid, threads, smem, stream>>>(tmA, tmB, tmA2, tmB2, p, stages);
+    kernel<<<grid, threads, smem, stream>>>(tmA, tmB, tmA2, tmB2, tmC, p, stages);
     return int(cudaGetLastError());
   }
   int pairs = sms / 2;
@@ -1050,7 +1129,7 @@ int nb_gemm(const NbGemmArgs* a, cudaStream_t stream) {
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr; cfg.numAttrs = 1;
-  return int(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmA2, tmB2, p, stages));
+  return int(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmA2, tmB2, tmC, p, stages));
 }
 
 }  // extern "C"

@@ -13,12 +13,13 @@ import math
 from typing import Any
 
 import torch
-import torch.nn.functional as F
 
+from nestor_b200 import ops
 from nestor_b200.configs import EvalConfig, EvalSuiteConfig, LanguageModelingEvalConfig
 from nestor_b200.data.datasets import build_dataset
 from nestor_b200.eval.metrics import routing_metrics
 from nestor_b200.models.nestor import router_counts, router_prob_sums
+from nestor_b200.train.losses import ce_chunk_rows
 from nestor_b200.utils.distributed import get_padded_rank_indices, get_rank, get_world_size, sum_tensor_across_ranks
 
 
@@ -32,7 +33,10 @@ class LanguageModelingEval:
     def run(self, model: Any) -> dict[str, Any]:
         was_training, was_fused = model.training, model.fused_head
         model.eval()
-        model.fused_head = False
+        # the head runs inside the chunked head + cross-entropy op: no [B, S, V] logits tensor ever exists (at most
+        # NESTOR_CE_CHUNK_ROWS x V at a time; the reference chunks its evaluation head too, nestor/eval/long_context.py:75)
+        model.fused_head = True
+        head = model.head
         n = len(self.dataset)
         idx = get_padded_rank_indices(n)
         real = set(range(n)[get_rank()::get_world_size()])
@@ -44,11 +48,12 @@ class LanguageModelingEval:
             ids = torch.stack([self.dataset[i][0] for i in rows]).to(self.device)
             keep = torch.tensor([i in real for i in rows], device=self.device)
             out = model(ids)
-            logits = out.pred[:, :-1].float()
-            nll = F.cross_entropy(logits.reshape(-1, logits.shape[-1]), ids[:, 1:].reshape(-1), reduction="none")
-            nll = nll.view(ids.shape[0], -1) * keep.unsqueeze(1)
-            totals[0] += nll.sum().double()
-            totals[1] += keep.sum().double() * (ids.shape[1] - 1)
+            hidden = out.pred[:, :-1].reshape(-1, out.pred.shape[-1])
+            targets = ids[:, 1:].masked_fill(~keep.unsqueeze(1), -100).reshape(-1)     # padded rows are not targets
+            nll_sum, n_targets = ops.lm_head_ce(hidden, head.weight, targets, head.logit_multiplier, hidden.dtype,
+                                                chunk_rows=ce_chunk_rows())
+            totals[0] += nll_sum.double()
+            totals[1] += n_targets.double()
             if bool(keep.all()):
                 for k, v in router_counts(model.backbone, out.aux).items():
                     counts[k] = v if k not in counts else counts[k] + v

@@ -42,6 +42,7 @@ class GemmArgs(C.Structure):
         ("gather_nseg", C.c_int), ("gather_groups_per_rank", C.c_int), ("gather_on", C.c_int), ("gather_chunk", C.c_int),
         ("gather_flags", C.c_void_p), ("gather_nbuf", C.c_int), ("gather_lanes", C.c_int),
         ("gather_wait_polls", C.c_uint),
+        ("no_tiled_store", C.c_int),
     ]
 
 

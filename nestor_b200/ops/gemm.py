@@ -26,6 +26,11 @@ STATS_PARTS = 2
 # limit, not DRAM latency), and a cap on pipeline stages (0 = all that fit).
 PREFETCH_DIST = int(os.environ.get("NESTOR_B200_GEMM_PREFETCH", "0"))
 MAX_STAGES = int(os.environ.get("NESTOR_B200_GEMM_STAGES", "0"))
+# bf16 outputs of row-grouped products leave as tiled (TMA) stores where a warp's 32 rows are whole; "0" keeps the
+# row-masked vector stores everywhere
+TILED_STORE = os.environ.get("NESTOR_B200_TILED_STORE", "1") == "1"
+# weight-gradient (reduction-grouped) products on CTA pairs: "auto", "1" or "0"
+REDUCE_PAIR = os.environ.get("NESTOR_B200_REDUCE_PAIR", "auto")
 # CTA pairs: 256-row tiles where each CTA of a 2-CTA cluster stages half of B (cta_group::2 MMAs). The L2 -> SM
 # traffic per FLOP drops by the B half, which is what bounds these shapes. "auto" uses pairs for big row counts.
 PAIR = os.environ.get("NESTOR_B200_GEMM_PAIR", "auto")
@@ -202,6 +207,7 @@ def gemm_rows(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: in
     a.status = _lib.status_word(dev).data_ptr()
     a.pair = int(pair)
     a.debug = DEBUG
+    a.no_tiled_store = 0 if TILED_STORE else 1
     a.max_m_tiles = -(-rows // (256 if pair else 128)) + groups
     a.sms = sms
     a.trace = trace.data_ptr() if trace is not None else None
@@ -214,7 +220,7 @@ def gemm_rows(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: in
 
 def gemm_reduce(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: int = 1, out: Tensor,
                 epilogue: int = ACCUM_F32, alpha: float = 1.0, bn: int | None = None, sms: int = 0,
-                trace: Tensor | None = None) -> Tensor:
+                trace: Tensor | None = None, pair: bool | None = None) -> Tensor:
     """Reduction-grouped GEMM: ``out[g] (+)= A[rows_g]^T @ B[rows_g]`` with ``A [rows, M]``, ``B [rows, N]``.
 
     ``out`` is ``[G, M, N]`` (or ``[M, N]`` for one group) with a contiguous last dim; fp32 for the
@@ -241,8 +247,15 @@ def gemm_reduce(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: 
         "weight-gradient output rows must be 16-byte aligned (pad the inner dim)"
     a.C, a.ldc, a.c_group_stride = o3.data_ptr(), o3.stride(1), o3.stride(0)
     a.alpha = alpha
+    if pair is None:
+        # a CTA pair (256 x bn tile, each CTA staging its 128 A columns and half of B) moves a third less data into
+        # each SM per FLOP; it needs B halves of whole 64-column atoms and more than one 128-row tile of work
+        pair = REDUCE_PAIR == "1" or (REDUCE_PAIR == "auto" and bn % 128 == 0 and M > 128)
+    if pair and bn % 128:
+        pair = False
+    a.pair = int(pair)
     # few output tiles and a long reduction: let several CTAs share a tile (fp32 atomic adds)
-    tiles = groups * -(-M // 128) * -(-N // bn)
+    tiles = groups * -(-M // (256 if pair else 128)) * -(-N // bn) * (2 if pair else 1)
     kblocks = max(1, rows // (64 * groups))
     a.splits = 1
     if epilogue == ACCUM_F32 and tiles < (_lib.sm_count(A.device) * 13) // 16:
@@ -253,5 +266,6 @@ def gemm_reduce(A: Tensor, B: Tensor, *, offsets: Tensor | None = None, groups: 
     a.prefetch_dist, a.max_stages, a.prefetch_ops = PREFETCH_DIST, MAX_STAGES, 3
     a.trace = trace.data_ptr() if trace is not None else None
     a.debug = DEBUG
+    a.no_tiled_store = 0 if TILED_STORE else 1
     _launch(a)
     return out

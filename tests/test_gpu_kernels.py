@@ -82,6 +82,30 @@ def test_gemm_grouped_layouts_and_epilogues():
     assert _rel(small, dG[:, :8].float().t() @ X.float()) < 1e-4
 
 
+@pytest.mark.parametrize("M,N,E", [(640, 216, 12), (200, 600, 8), (1000, 256, 3), (640, 128, 1)])
+def test_gemm_reduce_on_cta_pairs_and_single_ctas(M, N, E):
+    """Weight-gradient products: the CTA-pair kernel (256-row tiles, each CTA staging half of B) and the single-CTA
+    kernel against the fp32 statement, with ragged groups (partial last k-block of every group), an empty group,
+    M that is not a multiple of the tile and both output epilogues."""
+
+    from nestor_b200.ops import gemm as G
+    torch.manual_seed(3)
+    rows = 3000
+    off = _offsets(rows, E, empty=(1,)) if E > 2 else torch.tensor([0, rows] if E == 1 else [0, 1111, rows], dtype=torch.int32, device="cuda")
+    o = off.tolist()
+    A = G.rows_buffer(rows, M, BF, "cuda"); A.copy_(torch.randn(rows, M, device="cuda"))
+    B = G.rows_buffer(rows, N, BF, "cuda"); B.copy_(torch.randn(rows, N, device="cuda"))
+    want = torch.stack([A[o[e]:o[e + 1]].float().t() @ B[o[e]:o[e + 1]].float() for e in range(E)])
+    for pair in (True, False):
+        st = torch.full((E, M, N), float("nan"), device="cuda")
+        G.gemm_reduce(A, B, offsets=off, groups=E, out=st, epilogue=G.STORE_F32, pair=pair)
+        assert torch.isfinite(st).all() and _rel(st, want) < 1e-4, (pair, "store")
+        acc0 = torch.randn(E, M, N, device="cuda")
+        acc = acc0.clone()
+        G.gemm_reduce(A, B, offsets=off, groups=E, out=acc, alpha=0.5, pair=pair)
+        assert _rel(acc, acc0 + 0.5 * want) < 1e-4, (pair, "accumulate")
+
+
 def test_gemm_stats_epilogue_gives_logsumexp():
     from nestor_b200.ops import gemm as G
     torch.manual_seed(2)
@@ -131,6 +155,44 @@ def test_flash_forward_backward(H, hd, lens, lazy, monkeypatch):
         sl = slice(i * inner, (i + 1) * inner)
         assert _rel(dqkv[:, sl], qr.grad[:, sl]) < 2e-2
     assert torch.isfinite(dqkv.float()).all()
+
+
+def test_flash_forward_with_softmax_warps_at_different_speeds_is_exact_and_repeatable():
+    """The four softmax warps of a q tile run independently and may be a kv tile apart. Here one quarter of every q
+    tile has row maxima that grow with every kv tile (those warps rescale the accumulator each time, the others
+    never do), which pulls the warps apart; the output must still match the fp32 statement and be bit-identical
+    over repeated launches (a product issued before a slow warp has written its probabilities reads stale rows)."""
+
+    from nestor_b200.ops import flash as F
+    torch.manual_seed(11)
+    H, hd, L, nseg = 3, 40, 1536, 6
+    rows, inner = L * nseg, H * hd
+    q = torch.randn(rows, H, hd, device="cuda") * 0.5
+    k = torch.randn(rows, H, hd, device="cuda") * 0.5
+    v = torch.randn(rows, H, hd, device="cuda")
+    pos = torch.arange(rows, device="cuda") % L
+    slow = ((torch.arange(rows, device="cuda") % 128) >= 96).float()[:, None, None]     # the last warp of each q tile
+    q = q + slow * 3.0                                     # its scores follow k[..., 0] ...
+    q[..., 0] = q[..., 0] * (1 - slow[..., 0]) + slow[..., 0] * 40.0
+    k[..., 0] = (pos.float() / L)[:, None] * 12.0          # ... which grows along the sequence: a new maximum per tile
+    qkv = torch.cat([q.reshape(rows, inner), k.reshape(rows, inner), v.reshape(rows, inner)], 1).to(BF)
+    seg = torch.arange(0, rows + 1, L, dtype=torch.int32, device="cuda")
+    qq, kk, vv = qkv[:, :inner], qkv[:, inner:2 * inner], qkv[:, 2 * inner:]
+    first, _ = F.flash_fwd(qq, kk, vv, seg, H, hd, 1.0 / hd)
+    first = first.clone()
+    want = torch.empty(rows, H, hd, device="cuda")
+    for a in range(0, rows, L):
+        q3, k3, v3 = (t[a:a + L].float().reshape(L, H, hd).transpose(0, 1) for t in (qq, kk, vv))
+        sc = (q3 @ k3.transpose(1, 2)) / hd
+        sc = sc.masked_fill(~torch.ones(L, L, dtype=torch.bool, device="cuda").tril(), float("-inf"))
+        want[a:a + L] = (torch.softmax(sc, -1) @ v3).transpose(0, 1)
+    assert _rel(first, want.reshape(rows, inner)) < 1e-2
+    junk = torch.randn(4096, 4096, device="cuda")
+    for i in range(25):
+        if i % 5 == 0:
+            junk = junk @ junk.t() * 1e-4          # other kernels in between: the attention kernel starts from a cold cache
+        again, _ = F.flash_fwd(qq, kk, vv, seg, H, hd, 1.0 / hd)
+        assert torch.equal(again, first), i
 
 
 @pytest.mark.parametrize("nsrc,d", [(3, 640), (9, 640), (47, 640), (5, 256), (4, 1280)])
