@@ -308,11 +308,12 @@ class NestorConfig(BackboneConfig):
                 raise ValueError(f"block {i}: group-router score/noise MLPs need one equal hidden width.")
             pool = Q[i] > 0
             if pool:
-                if P[i] < 1:
-                    raise ValueError(f"block {i}: private-only pools are unsupported (public experts required).")
+                if P[i] < 0:
+                    raise ValueError(f"block {i}: block_expert_pool_public_experts must be >= 0.")
                 if epg[i] != 1 or shared[i] != 1:
                     raise ValueError(f"block {i}: the hybrid pool replaces the bank (bank experts must be 1).")
-                if not (1 <= kp[i] <= P[i] and 1 <= kq[i] <= Q[i]):
+                # P == 0 is the private-only pool: no public experts, no public router, no path gate
+                if not ((P[i] == 0 or 1 <= kp[i] <= P[i]) and 1 <= kq[i] <= Q[i]):
                     raise ValueError(f"block {i}: pool top-k out of range.")
             else:
                 if epg[i] != shared[i]:
@@ -325,10 +326,12 @@ class NestorConfig(BackboneConfig):
                 index=i, dim=self.input_dim, layers=layers[i], G=G[i], k=k[i], heads=heads[i],
                 head_dim=hd[i], rope_base=float(rope[i]), pool=pool,
                 bank_experts=epg[i], bank_top_k=etop[i], bank_width=hid[i][0],
-                P=P[i] if pool else 0, k_p=kp[i] if pool else 0,
-                h_pub=public_expert_hidden_dim(self.input_dim, kp[i], active_budget=self.block_expert_pool_public_budget) if pool else 0,
+                P=P[i] if pool else 0, k_p=kp[i] if pool and P[i] > 0 else 0,
+                h_pub=public_expert_hidden_dim(self.input_dim, kp[i], active_budget=self.block_expert_pool_public_budget)
+                if pool and P[i] > 0 else 0,
                 Q=Q[i] if pool else 0, k_q=kq[i] if pool else 0,
-                h_priv=private_expert_hidden_dim(self.input_dim, k[i], kq[i], with_public_pool=True,
+                # a private-only pool spends the whole 4d active width on the private experts
+                h_priv=private_expert_hidden_dim(self.input_dim, k[i], kq[i], with_public_pool=P[i] > 0,
                                                  active_budget=self.block_expert_pool_active_budget) if pool else 0,
                 private_gate=self.block_expert_pool_private_gate,
                 router_hidden=sh[i][0], loss_free=bool(lf[i]), bias_rate=float(br[i]), token_dispatch=bool(td[i]),

@@ -72,17 +72,23 @@ class InitScales:
 
 
 class ExpertPool(nn.Module):
-    """Hybrid pool: ``P`` public experts + ``Q`` private experts per column + 2-logit path gate."""
+    """Hybrid pool: ``P`` public experts + ``Q`` private experts per column + 2-logit path gate.
+
+    ``P == 0`` is the private-only pool (reference ``nestor/backbones/expert_pools.py:23-29,1102-1104``): every column
+    draws from its own private experts only; no public router, public bank or path gate exists, and the private
+    path's weight is the constant 1.
+    """
 
     def __init__(self, s: BlockSpec, init: InitScales) -> None:
         super().__init__()
         self.spec = s
         mk = lambda c, k, mode: RouterParams(  # noqa: E731
             s.dim, c, k, std=init.router, gate_mode=mode, loss_free=s.loss_free, bias_rate=s.bias_rate)
-        self.public_router = mk(s.P, s.k_p, "renorm")
+        self.has_public = s.P > 0
+        self.public_router = mk(s.P, s.k_p, "renorm") if self.has_public else None
         self.private_routers = nn.ModuleList([mk(s.Q, s.k_q, s.private_gate) for _ in range(s.G)])
-        self.path_gate = Matrix(s.dim, 2, ADAMW_DECAY, init.matrix)
-        self.stacked_public = ExpertBank(s.P, s.dim, s.h_pub, init.matrix, init.output)
+        self.path_gate = Matrix(s.dim, 2, ADAMW_DECAY, init.matrix) if self.has_public else None
+        self.stacked_public = ExpertBank(s.P, s.dim, s.h_pub, init.matrix, init.output) if self.has_public else None
         self.stacked_private = ExpertBank(s.G * s.Q, s.dim, s.h_priv, init.matrix, init.output)
 
     def private_router_weight(self) -> Tensor:
@@ -101,6 +107,8 @@ class ExpertPool(nn.Module):
         s = self.spec
         T = n.shape[0]
         # one GEMM for the public router, the G private routers and the path gate (adjacent parameters)
+        if not self.has_public:
+            return self._forward_private_only(n, idx, gates, cd)
         heads = [self.public_router.score_mlp.layers[0].weight,
                  *[r.score_mlp.layers[0].weight for r in self.private_routers], self.path_gate.weight]
         arena = self.__dict__.get("_nestor_arena")
@@ -130,6 +138,22 @@ class ExpertPool(nn.Module):
             member = torch.zeros(T, s.G, device=n.device).scatter_(1, idx.long(), 1.0)
             aux["private_prob"] = (torch.softmax(priv_scores.float(), dim=-1) * member.unsqueeze(-1)).sum(0)
         return public[:, 0], private, path, aux
+
+    def _forward_private_only(self, n: Tensor, idx: Tensor, gates: Tensor, cd: torch.dtype):
+        """No public path and no path gate: ``(zeros [T, d], private [T, k, d], None, aux)``."""
+
+        s = self.spec
+        T = n.shape[0]
+        scores = ops.router_scores(n, None, self.private_router_weight(), cd).reshape(T, s.G, s.Q)
+        priv_ids, priv_w, priv_idx = ops.route_selected(scores, self.private_bias(), idx, gates, s.k_q, s.private_gate, cd)
+        plan = ops.build_expert_plan(priv_ids, s.G * s.Q)
+        private = ops.expert_bank(n, plan, priv_w, W(self, self.stacked_private.w_up), W(self, self.stacked_private.w_gate),
+                                  W(self, self.stacked_private.w_down), cd, group=s.k_q)
+        aux = {"private_idx": priv_idx, "columns": idx, "private_offsets": plan.offsets}
+        if not self.training and not torch.is_grad_enabled():
+            member = torch.zeros(T, s.G, device=n.device).scatter_(1, idx.long(), 1.0)
+            aux["private_prob"] = (torch.softmax(scores.float(), dim=-1) * member.unsqueeze(-1)).sum(0)
+        return torch.zeros(T, s.dim, dtype=cd, device=n.device), private, None, aux
 
 
 class Layer(nn.Module):
@@ -700,11 +724,14 @@ def router_counts(backbone: Nestor, aux: dict) -> dict[str, Tensor]:
         for l, (layer, laux) in enumerate(zip(block.layers, baux["layers"])):
             base = f"blocks.{b}.layers.{l}"
             if layer.expert_pool is not None:
-                if "public_offsets" in laux and valid is None:      # the dispatch plans already hold the per-expert histograms
-                    out[f"{base}.expert_pool.public_router"] = laux["public_offsets"].diff().float()
+                has_public = layer.expert_pool.has_public
+                if "private_offsets" in laux and valid is None:     # the dispatch plans already hold the per-expert histograms
+                    if has_public:
+                        out[f"{base}.expert_pool.public_router"] = laux["public_offsets"].diff().float()
                     per = laux["private_offsets"].diff().float().view(s.G, s.Q)
                 else:
-                    out[f"{base}.expert_pool.public_router"] = _count(laux["public_idx"], s.P, valid)
+                    if has_public:
+                        out[f"{base}.expert_pool.public_router"] = _count(laux["public_idx"], s.P, valid)
                     flat = laux["columns"].long().unsqueeze(-1) * s.Q + laux["private_idx"].long()
                     per = _count(flat, s.G * s.Q, valid).view(s.G, s.Q)
                 for g in range(s.G):
@@ -725,8 +752,9 @@ def router_prob_sums(backbone: Nestor, aux: dict) -> dict[str, Tensor]:
             out[f"blocks.{b}.group_router"] = baux["group_prob"]
         for l, (layer, laux) in enumerate(zip(block.layers, baux["layers"])):
             base = f"blocks.{b}.layers.{l}"
-            if "public_prob" in laux:
-                out[f"{base}.expert_pool.public_router"] = laux["public_prob"]
+            if "private_prob" in laux:
+                if "public_prob" in laux:
+                    out[f"{base}.expert_pool.public_router"] = laux["public_prob"]
                 for g in range(s.G):
                     out[f"{base}.expert_pool.private_routers.{g}"] = laux["private_prob"][g]
             elif "expert_prob" in laux:

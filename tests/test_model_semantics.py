@@ -352,3 +352,57 @@ def test_router_noise_anneals_per_real_forward(tiny_scale, monkeypatch):
     with torch.no_grad():
         a, b = m(ids).pred, m(ids).pred
     assert torch.equal(a, b) and int(r._noise_steps) == 5         # evaluation neither draws noise nor counts
+
+
+def test_private_only_pool_matches_reference(tiny_scale, monkeypatch):
+    """``block_expert_pool_public_experts = 0``: every column draws from its own private experts only; no public router,
+    public bank or path gate exists (reference nestor/backbones/expert_pools.py:23-29). Same state-dict keys, logits and
+    gradients as the reference model configured the same way; router statistics only name the private routers."""
+
+    import dataclasses as dc
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "nestor").is_dir():
+        pytest.skip("reference package not installed under baseline/_ref")
+    monkeypatch.setenv("NESTOR_STACKED_EXPERT_BANKS", "1")
+    monkeypatch.setenv("NESTOR_DENSE_NO_ROUTER", "1")
+    monkeypatch.syspath_prepend(str(ref_root))
+    try:
+        from nestor.experiments import pretrain as RP
+        from nestor.models import Model as RefModel
+    except Exception as exc:
+        pytest.skip(f"reference import failed: {exc}")
+    P = tiny_scale
+    monkeypatch.setitem(RP.SCALES, "tiny", RP.Scale("tiny", 128, 4, 8, 512, 10, 2, 1024))
+    monkeypatch.setitem(RP.NESTOR_LAYERS, "tiny", (2, 1, 1, 1, 1, 1, 2))
+    monkeypatch.setitem(RP.NESTOR_PRIVATE_EXPERTS, "tiny", 3)
+    monkeypatch.setattr(RP, "NESTOR_MIN_PRIVATE_WIDTH", 24)
+    monkeypatch.setattr(RP, "BLOCK_SIZE", 64)
+    for fam in ("dense", "moe", "nestor"):
+        monkeypatch.setitem(RP.BATCH_SHAPE, (fam, "tiny"), (2, 1))
+    torch.manual_seed(0)
+    rcfg = RP._nestor("tiny").jobs[0].model
+    rcfg = dc.replace(rcfg, backbone_config=dc.replace(rcfg.backbone_config, block_expert_pool_public_experts=0))
+    rm = RefModel.from_config(rcfg).eval()
+    with torch.no_grad():
+        for n, p in rm.named_parameters():
+            if "query" in n:
+                p.normal_(0, 0.5)
+    cfg = P.build_experiment("nestor", "tiny").jobs[0].model
+    cfg = dc.replace(cfg, backbone_config=dc.replace(cfg.backbone_config, block_expert_pool_public_experts=0))
+    mm = Model.from_config(cfg).eval()
+    assert set(mm.state_dict()) == set(rm.state_dict())
+    assert not any("public" in k or "path_gate" in k for k in mm.state_dict())
+    mm.load_state_dict(rm.state_dict(), strict=True)
+    ids = torch.randint(0, 100263, (2, 64))
+    lr = F.cross_entropy(rm(ids).pred[:, :-1].reshape(-1, 100263), ids[:, 1:].reshape(-1))
+    out = mm(ids)
+    lm = F.cross_entropy(out.pred[:, :-1].reshape(-1, 100263), ids[:, 1:].reshape(-1))
+    assert torch.allclose(lr, lm, atol=1e-5)
+    lr.backward(); lm.backward()
+    ref_grads = dict(rm.named_parameters())
+    for n, p in mm.named_parameters():
+        g1, g2 = ref_grads[n].grad, p.grad
+        if g1 is not None and g2 is not None and g1.norm() > 1e-5:
+            assert (g1 - g2).norm() / g1.norm() < 2e-3, n
+    counts = router_counts(mm.backbone, out.aux)
+    assert not any("public" in k for k in counts) and any("private_routers" in k for k in counts)
