@@ -236,6 +236,29 @@ def run_ours(a: argparse.Namespace) -> dict:
     comm_ms = phases.get("grad_reduce", 0.0) + phases.get("param_push", 0.0)
     exposed = ms_dev / a.steps - accum * ms_micro
 
+    # Kernel census of one untimed eager micro-batch (a replayed graph shows up as one item to the profiler): how many
+    # of the launches are kernels of the in-tree library (namespaces nb / nbr / nbo / nbm) and how many come from
+    # PyTorch (copies, fills, the embedding, small reductions).
+    census = None
+    if rank == 0:
+        try:
+            from torch.profiler import ProfilerActivity, profile
+            saved, trainer._graph_enabled = trainer._graph_enabled, False
+            trainer.train_step((resident[0][0], resident[0][0]))
+            torch.cuda.synchronize(device)
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                trainer.train_step((resident[0][0], resident[0][0]))
+                torch.cuda.synchronize(device)
+            trainer._graph_enabled = saved
+            trainer.arena.zero_grad()
+            ev = [e for e in prof.key_averages() if e.device_type == torch.autograd.DeviceType.CUDA]
+            own = [e for e in ev if e.key.replace("void ", "").startswith(("nb::", "nbr::", "nbo::", "nbm::"))]
+            census = {"own_launches": sum(e.count for e in own), "other_launches": sum(e.count for e in ev) - sum(e.count for e in own),
+                      "own_device_ms": sum(e.device_time_total for e in own) / 1e3,
+                      "other_device_ms": (sum(e.device_time_total for e in ev) - sum(e.device_time_total for e in own)) / 1e3}
+        except Exception as exc:      # the census is informative only
+            census = {"error": f"{type(exc).__name__}: {exc}"[:160]}
+
     tokens = TOKENS_PER_STEP * a.steps
     value = tokens / (ms_dev / 1e3)
     h2d = accum * SEQS_PER_GPU * SEQ_LEN * 8
@@ -252,7 +275,7 @@ def run_ours(a: argparse.Namespace) -> dict:
                   "grad_transport": os.environ.get("NESTOR_B200_GRAD_TRANSPORT", "fused")},
         "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / a.steps,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "last_loss": last_loss},
-        "gpu_launches": launches, "clocks": clocks,
+        "gpu_launches": launches, "clocks": clocks, "micro_batch_kernel_census": census,
         "step_breakdown_ms": {"micro_batch": ms_micro, "outside_micro_batches": exposed, "exposed_comm_ms": comm_ms if world > 1 else 0.0,
                               **{f"update_{k}": v for k, v in phases.items()}},
     }

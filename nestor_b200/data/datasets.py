@@ -119,7 +119,10 @@ class PinnedWindowLoader:
     """Micro-batch iterator over a :class:`DclmTokenDataset` with pinned staging + prefetch thread.
 
     Yields ``(inputs, targets)`` int64 CPU tensors of shape ``[per_rank_batch, block_size]`` that
-    live in page-locked memory (valid until ``depth`` further batches have been drawn).
+    live in page-locked memory. A yielded buffer stays untouched until ``depth`` further batches have been drawn
+    (the ring holds ``2 * depth + 2`` buffers: ``depth`` queued, one being filled, one being handed over, ``depth``
+    still owned by the consumer), so a consumer that copies asynchronously has to make sure that the copy of batch
+    ``i`` has executed before it draws batch ``i + depth`` (``Trainer`` bounds its run-ahead to three batches).
     ``config.batch_size`` is the global batch; each rank takes ``batch_size // world``.
     """
 
@@ -134,7 +137,7 @@ class PinnedWindowLoader:
         self.depth = max(2, depth)
         pin = (config.pin_memory and torch.cuda.is_available()) if pin is None else pin
         self._ring = [torch.empty(self.per_rank, dataset.block_size, dtype=torch.int64,
-                                  pin_memory=pin) for _ in range(self.depth + 2)]
+                                  pin_memory=pin) for _ in range(2 * self.depth + 2)]
 
     def set_epoch(self, epoch: int) -> None:
         self.epoch = epoch

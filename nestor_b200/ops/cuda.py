@@ -79,7 +79,7 @@ def _L():
         L.nb_route_bwd.argtypes = [vp, vp, vp, vp, l, i, vp, vp]
         for fn in (L.nb_expert_plan, L.nb_route_fwd, L.nb_route_bwd):
             fn.restype = C.c_int
-        L.nb_ns_prepare.argtypes = [vp, vp, i, i, i, i, i, vp]
+        L.nb_ns_prepare.argtypes = [vp, vp, i, i, i, i, i, vp, vp]
         L.nb_ns_finish.argtypes = [vp, vp, i, i, i, i, i, vp]
         L.nb_ns_prepare.restype = L.nb_ns_finish.restype = C.c_int
         for fn in (L.nb_gather_rows, L.nb_combine_rows, L.nb_combine_bwd, L.nb_rope, L.nb_ce_grad,
@@ -903,7 +903,7 @@ _NS_MAX_BATCH = 256      # groups per grouped-GEMM launch
 def newton_schulz(g: Tensor, steps: int = 5, out_dtype: torch.dtype | None = None) -> Tensor:
     """Quintic Newton-Schulz on ``[..., m, n]`` matrices, every product on the tcgen05 grouped GEMM.
 
-    One batch (up to 256 same-shape matrices) costs ``2 + 3 * steps`` launches: normalise + cast + orient
+    One batch (up to 256 same-shape matrices) costs ``3 + 3 * steps`` launches: normalise + cast + orient
     (``nb_ns_prepare``), then per iteration ``A = X X^T`` (K-major B = X), ``B = b A + c A A`` and
     ``X <- a X + B X`` (B operand X read MN-major), the last two through the ``alpha * acc + beta * E1``
     epilogue, then ``nb_ns_finish`` when the result has to be turned back or un-padded. Matrices are the
@@ -929,7 +929,8 @@ def newton_schulz(g: Tensor, steps: int = 5, out_dtype: torch.dtype | None = Non
         X2 = out[lo : lo + nb].view(nb * mp, npad) if direct and steps % 2 == 1 else torch.empty(nb * mp, npad, dtype=BF16, device=dev)
         A = torch.empty(nb * mp, mp, dtype=BF16, device=dev)
         Bm = torch.empty(nb * mp, mp, dtype=BF16, device=dev)
-        _ck(L.nb_ns_prepare(x[lo : lo + nb].data_ptr(), X.data_ptr(), nb, m, n, mp, npad, _st()), "ns_prepare")
+        partial = torch.empty(nb * 32, dtype=torch.float32, device=dev)
+        _ck(L.nb_ns_prepare(x[lo : lo + nb].data_ptr(), X.data_ptr(), nb, m, n, mp, npad, partial.data_ptr(), _st()), "ns_prepare")
         for _ in range(steps):
             G.gemm_rows(X, X.view(nb, mp, npad), groups=nb, out=A)
             G.gemm_rows(A, A.view(nb, mp, mp), groups=nb, out=Bm, epilogue=G.AXPBY_BF16, alpha=c, beta=b, extra_in=(A,))

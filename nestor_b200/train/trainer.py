@@ -110,6 +110,7 @@ class Trainer:
             self.ema = {"flat": self.arena.master.clone()}
         self.runahead = int(os.environ.get("NESTOR_RUNAHEAD", "0"))
         self._step_events: collections.deque = collections.deque()
+        self._h2d_events: collections.deque = collections.deque()
         self.global_counts = _env_flag("NESTOR_LOSSFREE_GLOBAL_COUNTS")
         self.offload = _env_flag("NESTOR_ACTIVATION_OFFLOAD")
         self.tokens_per_micro: int | None = None
@@ -125,9 +126,27 @@ class Trainer:
     # ------------------------------------------------------------------ one micro-batch
     def _to_device(self, batch: Any) -> tuple[Tensor, Tensor]:
         inputs, targets = batch
+        staged = not inputs.is_cuda
         inputs = inputs.to(self.device, non_blocking=True)
         targets = inputs if targets is batch[0] else targets.to(self.device, non_blocking=True)
+        if staged:
+            self._note_host_copy()
         return inputs, targets
+
+    # A loader that stages batches in a ring of pinned buffers reuses a buffer a few batches later. The copies above are
+    # asynchronous and the host runs ahead of the device (a whole optimizer step of micro-batches when nothing is read
+    # back), so without a bound a buffer could be refilled before the device has read it. The host therefore never gets
+    # more than ``H2D_WINDOW`` batches ahead of the last executed copy; the ring of ``PinnedWindowLoader`` is sized for it.
+    H2D_WINDOW = 3
+
+    def _note_host_copy(self) -> None:
+        if self.device.type != "cuda":
+            return
+        ev = torch.cuda.Event()
+        ev.record()
+        self._h2d_events.append(ev)
+        while len(self._h2d_events) > self.H2D_WINDOW:
+            self._h2d_events.popleft().synchronize()
 
     def _activation_ctx(self):
         if self.offload and self.device.type == "cuda":
@@ -191,6 +210,8 @@ class Trainer:
             return loss, counts
         from nestor_b200.ops import _lib
         g["ids"].copy_(inputs, non_blocking=True)
+        if not inputs.is_cuda:
+            self._note_host_copy()
         g["graph"].replay()
         _lib.count_launch(g["kernels"])
         return g["loss"], g["counts"]

@@ -150,3 +150,28 @@ def test_source_snapshot_keeps_sources_and_prunes_the_rest(tmp_path):
     assert names == {"pkg/a.py", "pkg/csrc/k.cu", "README.md", "big.txt"}
     out = snapshot_sources(root, tmp_path / "run" / "source_snapshot", max_file_bytes=32)
     assert out.suffix == ".zip" and set(zipfile.ZipFile(out).namelist()) == names - {"big.txt"}
+
+
+def test_pinned_window_loader_keeps_a_batch_intact_for_depth_more_draws(tmp_path):
+    """A consumer that copies asynchronously may still be reading batch i while it draws later ones: the ring must not
+    refill batch i's buffer before ``depth`` further batches have been drawn."""
+
+    import time
+
+    import torch
+
+    from nestor_b200.configs import DataLoaderConfig, DclmDatasetConfig
+    from nestor_b200.data.datasets import DclmTokenDataset, PinnedWindowLoader, write_synthetic_bin
+
+    path = tmp_path / "tokens.bin"
+    write_synthetic_bin(path, 64 * 40 + 1, 1000, seed=3)
+    ds = DclmTokenDataset(DclmDatasetConfig(data_path=path, block_size=64))
+    loader = PinnedWindowLoader(ds, DataLoaderConfig(batch_size=2, num_workers=0, shuffle=False), depth=3, pin=False)
+    held = []
+    for i, (x, _) in enumerate(loader):
+        held.append((x, x.clone()))
+        time.sleep(0.01)                      # let the producer thread run as far ahead as the queue allows
+        for j in range(max(0, i - 3), i + 1):   # the last depth + 1 batches drawn are all still what they were
+            assert torch.equal(held[j][0], held[j][1]), (i, j)
+        if i >= 14:
+            break
