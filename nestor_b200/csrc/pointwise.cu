@@ -444,7 +444,7 @@ __global__ void depth_read_norm_bwd_kernel(SourceList src, GradList dsrc, int n,
                                            const float* __restrict__ stats, const float* __restrict__ rstd_in,
                                            const __nv_bfloat16* __restrict__ dn, const float* __restrict__ dh_in,
                                            float* __restrict__ partial, int has_gamma, int T, int d,
-                                           unsigned long long acc_mask) {
+                                           unsigned long long acc_mask, const float* __restrict__ h_saved, int pair_sweep) {
   // Parameter gradients leave the kernel as one partial row per block, [dquery (d) | dgamma (d) | dgains (64)],
   // summed by depth_param_reduce_kernel: thousands of warps adding atomically into the same 2d + n addresses
   // serialised in L2 and cost more than the rest of the kernel.
@@ -486,11 +486,14 @@ __global__ void depth_read_norm_bwd_kernel(SourceList src, GradList dsrc, int n,
     for (int sft = 16; sft > 0; sft >>= 1) zsum += __shfl_xor_sync(0xffffffffu, zsum, sft);
     __syncwarp();
     const float inv_z = 1.f / zsum;
-    // sweep 1: h
+    // sweep 1: h, read back when the forward kept it (one row instead of a pass over all the sources), else rebuilt
     float4 h[NV];
 #pragma unroll
-    for (int v = 0; v < NV; ++v) h[v] = make_float4(0, 0, 0, 0);
-    for (int i = 0; i < n; ++i) {
+    for (int v = 0; v < NV; ++v) {
+      const int c = lane + 32 * v;
+      h[v] = (h_saved && c < nchunk) ? reinterpret_cast<const float4*>(h_saved + long(t) * d)[c] : make_float4(0, 0, 0, 0);
+    }
+    for (int i = 0; i < n && !h_saved; ++i) {
       float a = s_w[wy][i] * inv_z * gains[i] * stats[(long(t) * n + i) * 2];
       const float4* s = reinterpret_cast<const float4*>(src.ptr[i] + long(t) * d);
 #pragma unroll
@@ -536,8 +539,29 @@ __global__ void depth_read_norm_bwd_kernel(SourceList src, GradList dsrc, int n,
         dh[v] = c < nchunk ? reinterpret_cast<const float4*>(dh_in + long(t) * d)[c] : make_float4(0, 0, 0, 0);
       }
     }
-    // sweep 2: t_i = <dh, s_i>
-    for (int i = 0; i < n; ++i) {
+    // sweep 2: t_i = <dh, s_i>, two sources at a time (their loads are in flight together, their reductions interleave)
+    int i2 = 0;
+    for (; pair_sweep && i2 + 1 < n; i2 += 2) {
+      const float4* s0 = reinterpret_cast<const float4*>(src.ptr[i2] + long(t) * d);
+      const float4* s1 = reinterpret_cast<const float4*>(src.ptr[i2 + 1] + long(t) * d);
+      float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        int c = lane + 32 * v;
+        if (c < nchunk) {
+          float4 x = s0[c], y = s1[c];
+          a0 += dh[v].x * x.x + dh[v].y * x.y + dh[v].z * x.z + dh[v].w * x.w;
+          a1 += dh[v].x * y.x + dh[v].y * y.y + dh[v].z * y.z + dh[v].w * y.w;
+        }
+      }
+#pragma unroll
+      for (int sft = 16; sft > 0; sft >>= 1) {
+        a0 += __shfl_xor_sync(0xffffffffu, a0, sft);
+        a1 += __shfl_xor_sync(0xffffffffu, a1, sft);
+      }
+      if (lane == 0) { s_t[wy][i2] = a0; s_t[wy][i2 + 1] = a1; }
+    }
+    for (int i = i2; i < n; ++i) {
       const float4* s = reinterpret_cast<const float4*>(src.ptr[i] + long(t) * d);
       float acc = 0.f;
 #pragma unroll
@@ -629,7 +653,8 @@ __global__ void depth_param_reduce_kernel(const float* __restrict__ partial, int
 extern "C" int nb_depth_read_norm_bwd(const float* const* sources, float* const* dsources, int n, const float* query,
                                       const float* gains, const float* gamma, const float* stats, const float* rstd,
                                       const void* dn, const float* dh, float* dquery, float* dgains, float* dgamma, int T,
-                                      int d, unsigned long long acc_mask, float* scratch, cudaStream_t st) {
+                                      int d, unsigned long long acc_mask, float* scratch, const float* h_saved,
+                                      int pair_sweep, cudaStream_t st) {
   // scratch: fp32 [8 * SMs * (2d + 64)] per-block partial sums of the parameter gradients
   if (n < 1 || n > nb::kMaxSources || d % 4 || d > nb::kMaxDepthDim || !scratch) return -1;
   nb::SourceList sl; nb::GradList gl;
@@ -639,7 +664,7 @@ extern "C" int nb_depth_read_norm_bwd(const float* const* sources, float* const*
   if (blocks > nb_pointwise_sms() * 8) blocks = nb_pointwise_sms() * 8;
   int nv = (d / 4 + 31) / 32;
 #define NB_DRB(NV) nb::depth_read_norm_bwd_kernel<NV><<<blocks, block, 0, st>>>(sl, gl, n, query, gains, gamma, stats, rstd, \
-      (const __nv_bfloat16*)dn, dh, scratch, dgamma != nullptr, T, d, acc_mask)
+      (const __nv_bfloat16*)dn, dh, scratch, dgamma != nullptr, T, d, acc_mask, h_saved, pair_sweep)
   if (nv <= 1) NB_DRB(1); else if (nv <= 2) NB_DRB(2); else if (nv <= 4) NB_DRB(4); else if (nv <= 5) NB_DRB(5);
   else if (nv <= 8) NB_DRB(8); else if (nv <= 10) NB_DRB(10); else return -2;
 #undef NB_DRB

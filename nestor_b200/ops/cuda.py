@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 
 import torch
 from torch import Tensor
@@ -63,7 +64,7 @@ def _L():
         L.nb_repack_heads.restype = C.c_int
         L.nb_ce_grad.argtypes = [vp, l, i, vp, i, vp, l, vp, i, vp]
         L.nb_depth_read_norm.argtypes = [vp, i, vp, vp, vp, f, f, vp, vp, vp, vp, i, i, vp]
-        L.nb_depth_read_norm_bwd.argtypes = [vp, vp, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, C.c_ulonglong, vp, vp]
+        L.nb_depth_read_norm_bwd.argtypes = [vp, vp, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, C.c_ulonglong, vp, vp, i, vp]
         L.nb_depth_read_norm_bwd.restype = C.c_int
         L.nb_mid_source.argtypes = [vp, vp, vp, i, i, i, vp]
         L.nb_layer_combine.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, vp]
@@ -570,6 +571,9 @@ def grad_sink(x: Tensor) -> Tensor:
     return out
 
 
+KEEP_DEPTH_H = os.environ.get("NESTOR_DEPTH_READ_KEEP_H", "1") == "1"
+
+
 class _DepthReadNorm(torch.autograd.Function):
     """One pass over the sources forward (online softmax over depth), three sweeps backward."""
 
@@ -582,10 +586,15 @@ class _DepthReadNorm(torch.autograd.Function):
         stats = torch.empty(T, n, 2, dtype=torch.float32, device=out.device)
         rstd = torch.empty(T, dtype=torch.float32, device=out.device)
         q32, g32, w32 = query.float().contiguous(), gains.float().contiguous(), gamma.float().contiguous()
+        # the mixture h is kept for the backward when anything needs a gradient (one [T, d] row per token instead of a
+        # third pass over all n sources there); NESTOR_DEPTH_READ_KEEP_H=0 trades that memory back for the pass
+        keep_h = KEEP_DEPTH_H and any(ctx.needs_input_grad)
+        h = torch.empty(T, d, dtype=torch.float32, device=out.device) if keep_h else None
         _ck(_L().nb_depth_read_norm(_ptr_array(srcs), n, q32.data_ptr(), g32.data_ptr(), w32.data_ptr(), eps_read,
-                                    eps_norm, out.data_ptr(), None, stats.data_ptr(), rstd.data_ptr(), T, d, _st()),
+                                    eps_norm, out.data_ptr(), _ptr(h), stats.data_ptr(), rstd.data_ptr(), T, d, _st()),
             "depth_read_norm")
-        ctx.save_for_backward(q32, g32, w32, stats, rstd, *srcs)
+        ctx.kept_h = keep_h
+        ctx.save_for_backward(q32, g32, w32, stats, rstd, *([h] if keep_h else []), *srcs)
         ctx.sinks = [getattr(s, "_nb_sink", None) if c is s else None for s, c in zip(sources, srcs)]
         ctx.dtypes = (query.dtype, gains.dtype, gamma.dtype, [s.dtype for s in sources])
         ctx.n_gains = gains.numel()
@@ -594,6 +603,7 @@ class _DepthReadNorm(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dn):
         q32, g32, w32, stats, rstd, *srcs = ctx.saved_tensors
+        h = srcs.pop(0) if ctx.kept_h else None
         n = len(srcs)
         T, d = srcs[0].shape
         # sources with a shared gradient buffer: the first reader to run backward creates it, later ones add
@@ -615,7 +625,7 @@ class _DepthReadNorm(torch.autograd.Function):
         _ck(_L().nb_depth_read_norm_bwd(_ptr_array(srcs), _ptr_array(outs), n, q32.data_ptr(),
                                         g32.data_ptr(), w32.data_ptr(), stats.data_ptr(), rstd.data_ptr(), dnb.data_ptr(),
                                         None, dq.data_ptr(), dg.data_ptr(), dw.data_ptr(), T, d, C.c_ulonglong(mask),
-                                        scratch.data_ptr(), _st()),
+                                        scratch.data_ptr(), _ptr(h), int(os.environ.get('NESTOR_DEPTH_READ_PAIR', '1')), _st()),
             "depth_read_norm_bwd")
         _lib.count_launch()
         qd, gd, wd, sd = ctx.dtypes
