@@ -444,7 +444,7 @@ __global__ void depth_read_norm_bwd_kernel(SourceList src, GradList dsrc, int n,
                                            const float* __restrict__ stats, const float* __restrict__ rstd_in,
                                            const __nv_bfloat16* __restrict__ dn, const float* __restrict__ dh_in,
                                            float* __restrict__ partial, int has_gamma, int T, int d,
-                                           unsigned long long acc_mask, const float* __restrict__ h_saved, int pair_sweep) {
+                                           unsigned long long acc_mask, const float* __restrict__ h_saved) {
   // Parameter gradients leave the kernel as one partial row per block, [dquery (d) | dgamma (d) | dgains (64)],
   // summed by depth_param_reduce_kernel: thousands of warps adding atomically into the same 2d + n addresses
   // serialised in L2 and cost more than the rest of the kernel.
@@ -541,7 +541,7 @@ __global__ void depth_read_norm_bwd_kernel(SourceList src, GradList dsrc, int n,
     }
     // sweep 2: t_i = <dh, s_i>, two sources at a time (their loads are in flight together, their reductions interleave)
     int i2 = 0;
-    for (; pair_sweep && i2 + 1 < n; i2 += 2) {
+    for (; i2 + 1 < n; i2 += 2) {
       const float4* s0 = reinterpret_cast<const float4*>(src.ptr[i2] + long(t) * d);
       const float4* s1 = reinterpret_cast<const float4*>(src.ptr[i2 + 1] + long(t) * d);
       float a0 = 0.f, a1 = 0.f;
@@ -591,16 +591,27 @@ __global__ void depth_read_norm_bwd_kernel(SourceList src, GradList dsrc, int n,
       const float a = w * g * r, cs = -dr * r * r * r / d;
       const float4* s = reinterpret_cast<const float4*>(src.ptr[i] + long(t) * d);
       float4* o = reinterpret_cast<float4*>(dsrc.ptr[i] + long(t) * d);
+      // all loads of the source row (and of the gradient row it is added to) first: a store between two loads
+      // would make the second wait, since the compiler cannot know that the rows do not overlap
+      const bool add = (acc_mask >> i) & 1ull;
+      float4 x[NV], old[NV];
 #pragma unroll
       for (int v = 0; v < NV; ++v) {
-        int c = lane + 32 * v;
+        const int c = lane + 32 * v;
+        x[v] = c < nchunk ? s[c] : make_float4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        const int c = lane + 32 * v;
+        old[v] = (add && c < nchunk) ? o[c] : make_float4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        const int c = lane + 32 * v;
         if (c < nchunk) {
-          float4 x = s[c];
-          float4 r4 = make_float4(a * dh[v].x + du * qv[v].x + cs * x.x, a * dh[v].y + du * qv[v].y + cs * x.y,
-                                  a * dh[v].z + du * qv[v].z + cs * x.z, a * dh[v].w + du * qv[v].w + cs * x.w);
-          if ((acc_mask >> i) & 1ull) { float4 old = o[c]; r4.x += old.x; r4.y += old.y; r4.z += old.z; r4.w += old.w; }
-          o[c] = r4;
-          gq[v].x += du * x.x; gq[v].y += du * x.y; gq[v].z += du * x.z; gq[v].w += du * x.w;
+          o[c] = make_float4(a * dh[v].x + du * qv[v].x + cs * x[v].x + old[v].x, a * dh[v].y + du * qv[v].y + cs * x[v].y + old[v].y,
+                             a * dh[v].z + du * qv[v].z + cs * x[v].z + old[v].z, a * dh[v].w + du * qv[v].w + cs * x[v].w + old[v].w);
+          gq[v].x += du * x[v].x; gq[v].y += du * x[v].y; gq[v].z += du * x[v].z; gq[v].w += du * x[v].w;
         }
       }
     }
@@ -654,7 +665,7 @@ extern "C" int nb_depth_read_norm_bwd(const float* const* sources, float* const*
                                       const float* gains, const float* gamma, const float* stats, const float* rstd,
                                       const void* dn, const float* dh, float* dquery, float* dgains, float* dgamma, int T,
                                       int d, unsigned long long acc_mask, float* scratch, const float* h_saved,
-                                      int pair_sweep, cudaStream_t st) {
+                                      cudaStream_t st) {
   // scratch: fp32 [8 * SMs * (2d + 64)] per-block partial sums of the parameter gradients
   if (n < 1 || n > nb::kMaxSources || d % 4 || d > nb::kMaxDepthDim || !scratch) return -1;
   nb::SourceList sl; nb::GradList gl;
@@ -664,7 +675,7 @@ extern "C" int nb_depth_read_norm_bwd(const float* const* sources, float* const*
   if (blocks > nb_pointwise_sms() * 8) blocks = nb_pointwise_sms() * 8;
   int nv = (d / 4 + 31) / 32;
 #define NB_DRB(NV) nb::depth_read_norm_bwd_kernel<NV><<<blocks, block, 0, st>>>(sl, gl, n, query, gains, gamma, stats, rstd, \
-      (const __nv_bfloat16*)dn, dh, scratch, dgamma != nullptr, T, d, acc_mask, h_saved, pair_sweep)
+      (const __nv_bfloat16*)dn, dh, scratch, dgamma != nullptr, T, d, acc_mask, h_saved)
   if (nv <= 1) NB_DRB(1); else if (nv <= 2) NB_DRB(2); else if (nv <= 4) NB_DRB(4); else if (nv <= 5) NB_DRB(5);
   else if (nv <= 8) NB_DRB(8); else if (nv <= 10) NB_DRB(10); else return -2;
 #undef NB_DRB

@@ -64,7 +64,7 @@ def _L():
         L.nb_repack_heads.restype = C.c_int
         L.nb_ce_grad.argtypes = [vp, l, i, vp, i, vp, l, vp, i, vp]
         L.nb_depth_read_norm.argtypes = [vp, i, vp, vp, vp, f, f, vp, vp, vp, vp, i, i, vp]
-        L.nb_depth_read_norm_bwd.argtypes = [vp, vp, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, C.c_ulonglong, vp, vp, i, vp]
+        L.nb_depth_read_norm_bwd.argtypes = [vp, vp, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, C.c_ulonglong, vp, vp, vp]
         L.nb_depth_read_norm_bwd.restype = C.c_int
         L.nb_mid_source.argtypes = [vp, vp, vp, i, i, i, vp]
         L.nb_layer_combine.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, vp]
@@ -625,7 +625,7 @@ class _DepthReadNorm(torch.autograd.Function):
         _ck(_L().nb_depth_read_norm_bwd(_ptr_array(srcs), _ptr_array(outs), n, q32.data_ptr(),
                                         g32.data_ptr(), w32.data_ptr(), stats.data_ptr(), rstd.data_ptr(), dnb.data_ptr(),
                                         None, dq.data_ptr(), dg.data_ptr(), dw.data_ptr(), T, d, C.c_ulonglong(mask),
-                                        scratch.data_ptr(), _ptr(h), int(os.environ.get('NESTOR_DEPTH_READ_PAIR', '1')), _st()),
+                                        scratch.data_ptr(), _ptr(h), _st()),
             "depth_read_norm_bwd")
         _lib.count_launch()
         qd, gd, wd, sd = ctx.dtypes
