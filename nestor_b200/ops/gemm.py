@@ -66,12 +66,18 @@ class Gather:
 
 
 def pick_bn(n: int, *, mult: int = 16, cap: int = 256) -> int:
-    """Tile width: least padded-N, ties to the wider tile; multiples of ``mult`` up to ``cap``."""
+    """Tile width: least padded-N plus a fixed cost per tile, ties to the wider tile; multiples of ``mult`` up to ``cap``.
 
+    The fixed cost stands for what a tile costs beyond its columns (operand A fetched again, MMA issue and hand-over
+    latency). For MN-major B (``mult`` 64) it is large: on ``[98304 x 216] x [64, 216, 640]`` three tiles of 256 columns
+    ran in 56 us against 68 us for five tiles of 128, although a sixth of the wide tiles' columns is padding.
+    """
+
+    fixed = 160.0 if mult >= 64 else 24.0
     best, best_cost = mult, None
     for bn in range(mult, cap + 1, mult):
         tiles = -(-n // bn)
-        cost = tiles * bn * (1.0 + 24.0 / bn)
+        cost = tiles * (bn + fixed)
         if best_cost is None or cost <= best_cost:
             best, best_cost = bn, cost
     return best
