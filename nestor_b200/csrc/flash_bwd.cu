@@ -42,7 +42,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
                  const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ CUtensorMap tmX2,
                  const FlashBwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ uint64_t r_full, x_full[3], x_empty[3], sc_full, ds_ready, acc_done;
+  __shared__ uint64_t r_full, x_full[3], x_empty[3], sc_full, sc_empty, ds_ready, acc_done;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
   __shared__ int s_tile[4];
@@ -71,7 +71,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
       s_abort = 0;
       mbar_init(&r_full, 1);
       for (int i = 0; i < 3; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 1); }
-      mbar_init(&sc_full, 1); mbar_init(&ds_ready, 8); mbar_init(&acc_done, 1);
+      mbar_init(&sc_full, 1); mbar_init(&sc_empty, 8); mbar_init(&ds_ready, 8); mbar_init(&acc_done, 1);
       fence_barrier_init();
       prefetch_tmap(&tmR1); prefetch_tmap(&tmR2); prefetch_tmap(&tmX1); prefetch_tmap(&tmX2);
     }
@@ -119,15 +119,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
     const uint64_t ds_desc = sdesc_kmajor(smem_u32(sDS)), pt_desc = sdesc_kmajor(smem_u32(sPT));
     const int ks = hd16 / 16;
     bool ok = mbar_wait(&r_full, 0, abort_flag, p.status, kTimeoutFull);
-    int s = 0; uint32_t ph = 0;
-    for (int it = 0; it < niter && ok; ++it) {
-      // (the score accumulators are free: the previous iteration's ds_ready was awaited below)
-      ok = mbar_wait(&x_full[s], ph, abort_flag, p.status, kTimeoutFull);
-      if (!ok) break;
-      uint8_t* x1 = sX + s * 2 * xtile_bytes;
+    // The score products of tile it + 1 are issued as soon as the softmax warps have read tile it's scores out of
+    // TMEM (sc_empty), i.e. while they are still computing on them; the accumulate products of tile it follow when its
+    // dS / P^T tiles are written (ds_ready). One iteration then costs the longer of the two chains instead of their
+    // sum. `ss` / `sph` walk the ring for the score products, `s` / `ph` for the accumulate products.
+    int s = 0, ss = 0; uint32_t sph = 0;
+    auto issue_scores = [&](int stage) {
+      uint8_t* x1 = sX + stage * 2 * xtile_bytes;
       uint8_t* x2 = x1 + xtile_bytes;
       const uint64_t x1_k = sdesc_kmajor(smem_u32(x1)), x2_k = sdesc_kmajor(smem_u32(x2));
-      const uint64_t x1_mn = sdesc_mnmajor(smem_u32(x1), 8192), x2_mn = sdesc_mnmajor(smem_u32(x2), 8192);
       if (elect_one()) {
         for (int k = 0; k < ks; ++k) {   // 64-column blocks are 16 KB apart in the resident tile, 8 KB in the streamed one
           const uint32_t roff = (k >> 2) * 1024 + (k & 3) * 2, xoff = (k >> 2) * 512 + (k & 3) * 2;
@@ -140,6 +140,26 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
         umma_commit(&sc_full);
       }
       __syncwarp();
+    };
+    if (ok && niter > 0) {
+      ok = mbar_wait(&x_full[0], 0, abort_flag, p.status, kTimeoutFull);
+      if (ok) issue_scores(0);
+      if (++ss == stages) { ss = 0; sph ^= 1; }
+    }
+    for (int it = 0; it < niter && ok; ++it) {
+      if (it + 1 < niter) {
+        // tile it's scores have left TMEM: the next tile's products may overwrite them
+        ok = mbar_wait(&sc_empty, it & 1, abort_flag, p.status, kTimeoutTmemEmpty);
+        if (!ok) break;
+        ok = mbar_wait(&x_full[ss], sph, abort_flag, p.status, kTimeoutFull);
+        if (!ok) break;
+        tc_fence_after();
+        issue_scores(ss);
+        if (++ss == stages) { ss = 0; sph ^= 1; }
+      }
+      uint8_t* x1 = sX + s * 2 * xtile_bytes;
+      uint8_t* x2 = x1 + xtile_bytes;
+      const uint64_t x1_mn = sdesc_mnmajor(smem_u32(x1), 8192), x2_mn = sdesc_mnmajor(smem_u32(x2), 8192);
       ok = mbar_wait(&ds_ready, it & 1, abort_flag, p.status, kTimeoutTmemEmpty);
       if (!ok) break;
       tc_fence_after();
@@ -158,7 +178,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
         umma_commit(&acc_done);
       }
       __syncwarp();
-      if (++s == stages) { s = 0; ph ^= 1; }
+      if (++s == stages) s = 0;
     }
   } else {
     // Eight warps: warp w reads TMEM lane quarter w % 4 (its 32 rows of the resident tile); the two warps of a quarter
@@ -199,13 +219,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
       }
       if (!mbar_wait(&sc_full, it & 1, abort_flag, p.status, kTimeoutTmemFull)) { ok = false; break; }
       tc_fence_after();
-      // the smem tiles are free once the previous iteration's accumulate products retired
-      if (it > 0 && !mbar_wait(&acc_done, (it - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) { ok = false; break; }
       // does any (row of the resident tile, column of the streamed tile) pair fall on the hidden side of the diagonal?
       const bool diag = (MODE == 0) ? (x0 < r0 + BT - 1) : (x0 + BX - 1 > r0);
       float sv[32], dv[32];
       tmem_ld32(tS + lane_off + c0, sv); tmem_ld32(tDP + lane_off + c0, dv);
       tmem_ld_wait32x2(sv, dv);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sc_empty);          // the next tile's score products may overwrite S and dP
       // phase 1: scaled, shifted scores and (dP - delta), two columns per instruction
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
@@ -233,6 +254,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
         wd[i >> 1] = pack_bf16(d0, d1);
         if (MODE == 0) wp[i >> 1] = pack_bf16(sv[i], sv[i + 1]);
       }
+      // the dS / P^T tiles are free once the previous iteration's accumulate products have retired (they have been
+      // running under the arithmetic above)
+      if (it > 0 && !mbar_wait(&acc_done, (it - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) { ok = false; break; }
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         st_tile_chunk(sDS, r, c0 + 8 * g, wd + 4 * g);
@@ -334,13 +358,15 @@ int nb_flash_bwd(const NbFlashBwdArgs* a, cudaStream_t stream) {
   p.lse = a->lse; p.delta = a->delta; p.ldo = a->ld_dqkv; p.status = a->status;
   const int nkb = (a->hd + 63) / 64;
   // Streamed-tile ring: two stages next to the two 16 KB operand tiles of the dK/dV pass, three in the dQ pass, which
-  // has no P^T tile (both sized so that two CTAs of head dims <= 64 share an SM)
+  // has no P^T tile (both sized so that two CTAs of head dims <= 64 share an SM); two stages for head dims above 64
+  // (165 KB, one CTA per SM). At least two are needed: the score products of tile it + 1 are issued while tile it's
+  // stage is still being read by its accumulate products.
   dim3 grid(a->max_tiles, a->H);
   size_t smem = 0;
 #define NB_LAUNCH(MODE, HDN, R1, R2, X1, X2)                                                                        \
   do {                                                                                                               \
     static SmemAttr attr;                                                                                            \
-    p.stages = nkb == 1 ? (MODE == 0 ? 2 : 3) : 1;                                                                   \
+    p.stages = nkb == 1 ? (MODE == 0 ? 2 : 3) : 2;                                                                   \
     smem = size_t(nkb) * (2 * 16384 + 2 * p.stages * 8192) + (MODE == 0 ? 32768 : 16384) + 1024;                     \
     if (int e = attr.ensure(flash_bwd_kernel<MODE, HDN>, smem)) return e;                                            \
     flash_bwd_kernel<MODE, HDN><<<grid, 320, smem, stream>>>(R1, R2, X1, X2, p);                                     \
