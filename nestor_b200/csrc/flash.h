@@ -21,7 +21,7 @@ struct NbFlashArgs {
   float scale;                                   // logit scale (the models use 1/hd)
   int* status;
   int max_tiles;                                 // upper bound on q tiles: ceil(rows/128) + nseg
-  int lazy_rescale;                              // unused (the accumulator always stays in tensor memory)
+  int lazy_rescale;                              // flag bits: 2 = probabilities through tensor memory (head dims <= 64); bit 0 unused
 };
 
 struct NbFlashBwdArgs {

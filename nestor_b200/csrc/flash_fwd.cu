@@ -42,6 +42,7 @@ struct FlashParams {
   __nv_bfloat16* O; long ldo;  // [rows, H*hd]
   float* lse;                  // [rows, H] log2-domain logsumexp of scaled scores
   int* status;
+  int p_tmem;                  // probabilities handed to the P V product through tensor memory instead of shared memory
   long long* diag;             // NB_FLASH_DIAG builds: [grid.x][16] cycle sums
 };
 
@@ -107,6 +108,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
   const uint32_t tS0 = tmem, tO = tmem + 2 * FK;        // S double-buffered in columns [0, 128), O from 128
+  const uint32_t tP0 = tmem + 2 * FK + 64;              // bf16 P, 32 columns per buffer, in [192, 256) (head dims <= 64)
   const int seg_b = s_tile[0], seg_e = s_tile[1], q0 = s_tile[2];
   const int ntiles = (min(q0 + FQ, seg_e) - seg_b + FK - 1) / FK;   // kv tiles up to and including the diagonal
   volatile int* abort_flag = &s_abort;
@@ -157,8 +159,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint64_t pj_desc = p_desc + uint64_t((j & 1) * (16384 >> 4));
       if (el) {
 #pragma unroll
-        for (int k = 0; k < FK / 16; ++k)
-          umma_bf16(tO, pj_desc + (k & 3) * 2, v_desc + k * 128, idesc_o, (j | k) != 0);   // O accumulates in TMEM over the kv tiles
+        for (int k = 0; k < FK / 16; ++k) {
+          // O accumulates in TMEM over the kv tiles
+          if (p.p_tmem) umma_bf16_ts(tO, tP0 + (j & 1) * (FK / 2) + k * 8, v_desc + k * 128, idesc_o, (j | k) != 0);
+          else umma_bf16(tO, pj_desc + (k & 3) * 2, v_desc + k * 128, idesc_o, (j | k) != 0);
+        }
         umma_commit(&kv_empty[s]);
         umma_commit(&o_full[j & 1]);      // P buffer j & 1 may be rewritten; with the last tile: O is final
       }
@@ -291,6 +296,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       FD_T(t5); FD_ADD(4, t4, t5);
       const float neg_m = (m == -INFINITY) ? 0.f : -m;
       const uint64_t neg2 = f2_pack(neg_m, neg_m);
+      if (p.p_tmem) {
+        // probabilities -> bf16 pairs -> this row's lane of the P buffer in tensor memory
+        uint32_t pw[FK / 2];
+#pragma unroll
+        for (int c = 0; c < FK; c += 2) {
+          float t0, t1;
+          f2_unpack(f2_fma(f2_pack(sv[c], sv[c + 1]), scale2, neg2), t0, t1);
+          const float p0 = ex2_approx(t0), p1 = ex2_approx(t1);
+          l2 = f2_add(l2, f2_pack(p0, p1));
+          pw[c >> 1] = pack_bf16(p0, p1);
+        }
+        tmem_st32(tP0 + (j & 1) * (FK / 2) + lane_off, reinterpret_cast<const float*>(pw));
+        tmem_st_wait();
+      } else
       // probabilities -> bf16 -> swizzled smem, 8 columns (one 16-byte chunk) at a time
 #pragma unroll
       for (int c = 0; c < FK; c += 8) {
@@ -412,6 +431,7 @@ int nb_flash_fwd(const NbFlashArgs* a, cudaStream_t stream) {
   p.scale_log2 = a->scale * 1.4426950408889634f;
   p.O = reinterpret_cast<__nv_bfloat16*>(a->O); p.ldo = a->ldo; p.lse = a->lse; p.status = a->status;
   p.diag = nullptr;
+  p.p_tmem = (a->lazy_rescale & 2) && a->hd <= 64 ? 1 : 0;
 #ifdef NB_FLASH_DIAG
   p.diag = nb_flash_diag_buffer;
 #endif

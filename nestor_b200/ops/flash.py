@@ -13,6 +13,9 @@ from nestor_b200.ops import _lib
 # Forward variant: keep the output accumulator in TMEM across kv tiles and rescale it only when a row maximum moves by
 # more than 2^8 (1), or fold it into registers after every tile (0).
 LAZY_RESCALE = os.environ.get("NESTOR_B200_FLASH_LAZY", "1") == "1"
+# head dims <= 64: the softmax warps hand the probabilities to the P V product through tensor memory (tcgen05.st, A
+# operand of the MMA read from TMEM) instead of a swizzled shared-memory tile; "0" keeps the shared-memory path
+P_IN_TMEM = os.environ.get("NESTOR_B200_FLASH_P_TMEM", "1") == "1"
 
 
 def flash_fwd(q: Tensor, k: Tensor, v: Tensor, seg_start: Tensor, heads: int, head_dim: int, scale: float,
@@ -41,7 +44,7 @@ def flash_fwd(q: Tensor, k: Tensor, v: Tensor, seg_start: Tensor, heads: int, he
     a.rows, a.H, a.hd, a.scale = rows, heads, head_dim, scale
     a.status = _lib.status_word(q.device).data_ptr()
     a.max_tiles = -(-rows // 128) + nseg
-    a.lazy_rescale = int(LAZY_RESCALE)
+    a.lazy_rescale = int(LAZY_RESCALE) | (2 if P_IN_TMEM else 0)
     L = _lib.lib()
     L.nb_flash_fwd.argtypes = [C.POINTER(_lib.FlashArgs), C.c_void_p]
     L.nb_flash_fwd.restype = C.c_int
