@@ -42,12 +42,28 @@ CHECKED_LIB = OUT / "libnestor_b200_checked.so"      # the same sources with -DN
 
 
 def build(verbose: bool = False, force: bool = False, checked: bool = False) -> Path:
-    """Build the library (``checked``: the index-checking variant, objects cached under their own names)."""
+    """Build the library (``checked``: the index-checking variant, objects cached under their own names).
 
+    Several processes may get here at once (every rank of a multi-GPU launch checks the library when it loads it):
+    the whole build runs under an exclusive file lock, so one of them compiles and the others find the objects of
+    the current digests when their turn comes; objects and the library are written under temporary names and renamed.
+    """
+
+    import fcntl
+
+    OUT.mkdir(exist_ok=True)
+    with open(OUT / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            return _build_locked(verbose, force, checked)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(verbose: bool, force: bool, checked: bool) -> Path:
     cc = nvcc()
     if cc is None:
         raise RuntimeError("nvcc not found: cannot build the sm_100a kernel library")
-    OUT.mkdir(exist_ok=True)
     objs, rebuilt = [], False
     extra = ["-DNESTOR_BOUNDS_CHECK"] if checked else []
     kind = "chk" if checked else ""
@@ -55,24 +71,30 @@ def build(verbose: bool = False, force: bool = False, checked: bool = False) -> 
         obj = OUT / f"{cu.stem}{kind}.{_digest(cu)}.o"
         if force or not obj.is_file():
             for old in OUT.glob(f"{cu.stem}{kind}.*.o"):
-                old.unlink()
-            cmd = [cc, *FLAGS, *extra, "-c", str(cu), "-o", str(obj)]
+                old.unlink(missing_ok=True)
+            tmp = obj.with_suffix(f".{os.getpid()}.tmp")
+            cmd = [cc, *FLAGS, *extra, "-c", str(cu), "-o", str(tmp)]
             res = subprocess.run(cmd, capture_output=True, text=True)
             if verbose or res.returncode:
                 sys.stderr.write(res.stdout + res.stderr)
             if res.returncode:
+                tmp.unlink(missing_ok=True)
                 raise RuntimeError(f"nvcc failed on {cu.name}")
+            tmp.replace(obj)
             if not checked:
                 (OUT / f"{cu.stem}.ptxas.txt").write_text(res.stderr)
             rebuilt = True
         objs.append(obj)
     lib = CHECKED_LIB if checked else LIB
     if rebuilt or not lib.is_file():
-        cmd = [cc, "-shared", "-o", str(lib), *map(str, objs), "-lcudart"]
+        tmp = lib.with_suffix(f".{os.getpid()}.tmp")
+        cmd = [cc, "-shared", "-o", str(tmp), *map(str, objs), "-lcudart"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode:
             sys.stderr.write(res.stdout + res.stderr)
+            tmp.unlink(missing_ok=True)
             raise RuntimeError("link failed")
+        tmp.replace(lib)
     return lib
 
 

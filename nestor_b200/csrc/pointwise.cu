@@ -59,9 +59,10 @@ __global__ void gather_rows_kernel(const TIn* __restrict__ src, long lds, const 
 // out[t, g, :] = sum_{e < group} round_bf16(y[idx[(t*G + g)*group + e], :] * w[(t*G + g)*group + e])   (fp32 out)
 // With w == nullptr the weight is 1. `accumulate` adds into out instead of overwriting; `round_products`
 // rounds each weighted row to bf16 before the fp32 sum (the expert-combine contract).
+// `out_bf16` stores the fp32 sums rounded to bf16 (no accumulate): the data gradient that goes back into a bf16 stream.
 __global__ void combine_rows_kernel(const __nv_bfloat16* __restrict__ y, long ldy, const int* __restrict__ idx,
                                     const float* __restrict__ w, int group, float* __restrict__ out, long ldo,
-                                    int n_out, int d, int accumulate, int round_products, long y_rows) {
+                                    int n_out, int d, int accumulate, int round_products, long y_rows, int out_bf16) {
   int o = blockIdx.x * blockDim.y + threadIdx.y;
   if (o >= n_out) return;
   float* dst = out + long(o) * ldo;
@@ -77,6 +78,14 @@ __global__ void combine_rows_kernel(const __nv_bfloat16* __restrict__ y, long ld
       const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&q);
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] += round_products ? bf(__float2bfloat16(bf(v[i]) * ww)) : bf(v[i]) * ww;
+    }
+    if (out_bf16) {
+      __nv_bfloat162 t0 = __floats2bfloat162_rn(acc[0], acc[1]), t1 = __floats2bfloat162_rn(acc[2], acc[3]);
+      __nv_bfloat162 t2 = __floats2bfloat162_rn(acc[4], acc[5]), t3 = __floats2bfloat162_rn(acc[6], acc[7]);
+      __nv_bfloat16* d16 = reinterpret_cast<__nv_bfloat16*>(out) + long(o) * ldo + c;
+      *reinterpret_cast<uint4*>(d16) = make_uint4(*reinterpret_cast<uint32_t*>(&t0), *reinterpret_cast<uint32_t*>(&t1),
+                                                  *reinterpret_cast<uint32_t*>(&t2), *reinterpret_cast<uint32_t*>(&t3));
+      continue;
     }
     float4* d4 = reinterpret_cast<float4*>(dst + c);
     if (accumulate) {
@@ -363,11 +372,11 @@ int nb_gather_rows(const void* src, int src_is_f32, long lds, const int* idx, in
 }
 
 int nb_combine_rows(const void* y, long ldy, const int* idx, const float* w, int group, float* out, long ldo, int n_out,
-                    int d, int accumulate, int round_products, long y_rows, cudaStream_t st) {
-  if (d % 8) return -1;
+                    int d, int accumulate, int round_products, long y_rows, int out_bf16, cudaStream_t st) {
+  if (d % 8 || (out_bf16 && (accumulate || ldo % 8))) return -1;
   dim3 block(32, 8), grid((n_out + 7) / 8);
   nb::combine_rows_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)y, ldy, idx, w, group, out, ldo, n_out, d, accumulate,
-                                                 round_products && w != nullptr, y_rows);
+                                                 round_products && w != nullptr, y_rows, out_bf16);
   return int(cudaGetLastError());
 }
 

@@ -57,7 +57,7 @@ def _L():
     if not _protos_done:
         vp, i, l, f = C.c_void_p, C.c_int, C.c_long, C.c_float
         L.nb_gather_rows.argtypes = [vp, i, l, vp, i, vp, l, i, i, l, vp]
-        L.nb_combine_rows.argtypes = [vp, l, vp, vp, i, vp, l, i, i, i, i, l, vp]
+        L.nb_combine_rows.argtypes = [vp, l, vp, vp, i, vp, l, i, i, i, i, l, i, vp]
         L.nb_combine_bwd.argtypes = [vp, l, vp, l, vp, vp, i, vp, l, vp, i, i, vp, vp, l, i, f, l, vp]
         L.nb_rope.argtypes = [vp, l, vp, i, i, i, i, f, f, vp]
         L.nb_repack_heads.argtypes = [vp, l, vp, l, i, i, i, i, i, vp]
@@ -133,15 +133,17 @@ def gather_rows(src: Tensor, idx: Tensor, div: int = 1) -> Tensor:
 
 
 def combine_rows(y: Tensor, idx: Tensor, w: Tensor | None, group: int, n_out: int, out: Tensor | None = None,
-                 accumulate: bool = False, round_products: bool = True) -> Tensor:
+                 accumulate: bool = False, round_products: bool = True, out_dtype: torch.dtype = torch.float32) -> Tensor:
     """``out[o] = sum_{e<group} y[idx[o*group+e]] * w[o*group+e]`` in fp32 (each product first rounded to
-    bf16 when ``round_products``)."""
+    bf16 when ``round_products``); ``out_dtype=bfloat16`` stores the fp32 sums rounded once (no separate cast pass)."""
 
     d = y.shape[-1]
     if out is None:
-        out = torch.empty(n_out, d, dtype=torch.float32, device=y.device)
+        out = torch.empty(n_out, d, dtype=out_dtype, device=y.device)
+    assert out.dtype in (torch.float32, BF16) and not (out.dtype == BF16 and accumulate)
     _ck(_L().nb_combine_rows(y.data_ptr(), y.stride(0), idx.data_ptr(), _ptr(w), group, out.data_ptr(), out.stride(0),
-                             n_out, d, int(accumulate), int(round_products), y.shape[0], _st()), "combine_rows")
+                             n_out, d, int(accumulate), int(round_products), y.shape[0], int(out.dtype == BF16), _st()),
+        "combine_rows")
     return out
 
 
@@ -292,7 +294,9 @@ class _ExpertBank(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dxs = G.gemm_rows(dgt, w_gate, A2=dut, B2=w_up, offsets=plan.offsets, groups=E,
                               gather=_bank_gather(w_gate, w_up))                                # [n, d]
-            dx = combine_rows(dxs, plan.inv, None, plan.slots, T).to(ctx.x_dtype)
+            direct = ctx.x_dtype in (torch.float32, BF16)
+            dx = combine_rows(dxs, plan.inv, None, plan.slots, T, out_dtype=ctx.x_dtype if direct else torch.float32)
+            dx = dx if direct else dx.to(ctx.x_dtype)
         dweights = None
         if dw_sorted is not None:      # the kernel indexes dw by flat slot already
             dweights = dw_sorted.view(T, plan.slots).to(ctx.w_dtype)
@@ -412,7 +416,12 @@ class _Attention(torch.autograd.Function):
         dn = None
         if ctx.needs_input_grad[0]:
             dx = G.gemm_rows(dq3, wqkv, offsets=col_start, groups=groups, b_mn=True, n=d)  # wqkv [G, K=3inner, N=d]
-            dn = (combine_rows(dx, row_of_slot.view(-1), None, k, T) if tok_of_row is not None else dx.float()).to(n_dtype)
+            if tok_of_row is not None:       # sum of the token's k packed rows, stored in the stream's dtype directly
+                direct = n_dtype in (torch.float32, BF16)
+                dn = combine_rows(dx, row_of_slot.view(-1), None, k, T, out_dtype=n_dtype if direct else torch.float32)
+                dn = dn if direct else dn.to(n_dtype)
+            else:
+                dn = dx if dx.dtype == n_dtype else dx.to(n_dtype)
         dgates = None
         if dg_sorted is not None:
             dgates = dg_sorted.view(T, k).to(g_dtype)
