@@ -258,6 +258,7 @@ def run_ours(a: argparse.Namespace) -> dict:
                       "other_device_ms": (sum(e.device_time_total for e in ev) - sum(e.device_time_total for e in own)) / 1e3}
         except Exception as exc:      # the census is informative only
             census = {"error": f"{type(exc).__name__}: {exc}"[:160]}
+    _bracket(device)      # every rank leaves together (rank 0 alone ran the census)
 
     tokens = TOKENS_PER_STEP * a.steps
     value = tokens / (ms_dev / 1e3)
