@@ -137,7 +137,7 @@ class ExpertPool(nn.Module):
             aux["public_prob"] = torch.softmax(pub_scores.float(), dim=-1).sum(0)
             member = torch.zeros(T, s.G, device=n.device).scatter_(1, idx.long(), 1.0)
             aux["private_prob"] = (torch.softmax(priv_scores.float(), dim=-1) * member.unsqueeze(-1)).sum(0)
-        return public[:, 0], private, path, aux
+        return public.view(T, s.dim), private, path, aux      # [T, 1, d] -> [T, d] as a view (a select would zero-fill in backward)
 
     def _forward_private_only(self, n: Tensor, idx: Tensor, gates: Tensor, cd: torch.dtype):
         """No public path and no path gate: ``(zeros [T, d], private [T, k, d], None, aux)``."""
