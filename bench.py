@@ -178,8 +178,7 @@ def run_ours(a: argparse.Namespace) -> dict:
         for _ in range(accum):
             loss, c = trainer.train_step(next(batches))
             total = loss.total.detach() if total is None else total + loss.total.detach()
-            for k, v in c.items():
-                counts[k] = v if k not in counts else counts[k] + v
+            counts = trainer.add_counts(counts, c)
         trainer.update_weights(counts)
         return float(total.item()) / accum       # device -> host read of the step's loss
 
@@ -189,8 +188,7 @@ def run_ours(a: argparse.Namespace) -> dict:
         counts: dict = {}
         for b in resident:
             _, c = trainer.train_step((b[0], b[0]))
-            for k, v in c.items():
-                counts[k] = v if k not in counts else counts[k] + v
+            counts = trainer.add_counts(counts, c)
         trainer.update_weights(counts)
 
     for _ in range(max(3, a.warmup)):

@@ -706,6 +706,56 @@ def _count(idx: Tensor, n: int, valid: Tensor | None = None) -> Tensor:
     return torch.zeros(n, dtype=torch.float32, device=idx.device).scatter_add_(0, flat, w)
 
 
+class RouterCounts(dict):
+    """Selection counts of every router, keyed by module path, whose values are views of one flat fp32 tensor.
+
+    A model has some two hundred routers; summing their counts over the micro-batches of a step key by key costs as
+    many tiny launches per micro-batch. ``total.add_(counts)`` is one.
+    """
+
+    flat: Tensor
+
+    @classmethod
+    def pack(cls, counts: dict[str, Tensor]) -> "RouterCounts":
+        out = cls()
+        names = sorted(counts)
+        if not names:
+            out.flat, out.layout = torch.zeros(0), []
+            return out
+        out.flat = torch.cat([counts[n].reshape(-1).float() for n in names])
+        out._wire(names, [counts[n].shape for n in names])
+        return out
+
+    def _wire(self, names, shapes) -> None:
+        off = 0
+        self.layout = list(zip(names, shapes))
+        for n, shape in self.layout:
+            size = int(torch.Size(shape).numel())
+            self[n] = self.flat[off : off + size].view(shape)
+            off += size
+
+    def clone(self) -> "RouterCounts":
+        out = RouterCounts()
+        out.flat = self.flat.clone()
+        out._wire([n for n, _ in self.layout], [s for _, s in self.layout])
+        return out
+
+    def add_(self, other: "RouterCounts") -> "RouterCounts":
+        self.flat.add_(other.flat)
+        return self
+
+
+def add_router_counts(total: dict | None, counts: dict) -> dict:
+    """``total + counts`` for the counts of successive micro-batches (``total`` may be ``None`` or empty)."""
+
+    if isinstance(counts, RouterCounts) and (not total or isinstance(total, RouterCounts)):
+        return counts.clone() if not total else total.add_(counts)
+    total = {} if total is None else total
+    for k, v in counts.items():
+        total[k] = v if k not in total else total[k] + v
+    return total
+
+
 @torch.no_grad()
 def router_counts(backbone: Nestor, aux: dict) -> dict[str, Tensor]:
     """Per-router selection counts of one forward, keyed by the router's module path.

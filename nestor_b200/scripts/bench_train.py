@@ -61,8 +61,7 @@ def main(argv: list[str] | None = None) -> None:
         for _ in range(a.accum):
             ids = torch.randint(0, vocab, (a.seqs_per_gpu, a.block_size), device=device, generator=gen)
             _, c = trainer.train_step((ids, ids))
-            for k, v in c.items():
-                counts[k] = v if k not in counts else counts[k] + v
+            counts = trainer.add_counts(counts, c)
         trainer.update_weights(counts)
 
     def bracket() -> None:

@@ -32,7 +32,7 @@ import torch
 from torch import Tensor, nn
 
 from nestor_b200.configs import TrainJobConfig
-from nestor_b200.models.nestor import apply_bias_updates, router_counts
+from nestor_b200.models.nestor import RouterCounts, add_router_counts, apply_bias_updates, router_counts
 from nestor_b200.parallel.arena import ParamArena
 from nestor_b200.parallel.grad_sync import GradReducer
 from nestor_b200.train import checkpoint as ckpt
@@ -167,6 +167,12 @@ class Trainer:
             if on:
                 torch.cuda.nvtx.range_pop()
 
+    @staticmethod
+    def add_counts(total: dict | None, counts: dict) -> dict:
+        """Sum the router counts of successive ``train_step`` calls (one launch per micro-batch when both are packed)."""
+
+        return add_router_counts(total, counts)
+
     def train_step(self, batch: Any) -> tuple[LossOutput, dict[str, Tensor]]:
         """Forward + backward of one micro-batch; gradients accumulate into the arena.
 
@@ -223,7 +229,8 @@ class Trainer:
             out = self.model(inputs)
             loss = self.loss_fn(out.pred, targets, out.aux)
         (loss.total / self.config.grad_accum_steps).backward()
-        counts = router_counts(self.model.backbone, out.aux) if self.model.training else {}
+        # (packed: the values are views of one flat tensor, so that a step's micro-batches are summed with one launch)
+        counts = RouterCounts.pack(router_counts(self.model.backbone, out.aux)) if self.model.training else {}
         # hand back values only: a live grad_fn would keep this step's autograd nodes alive
         loss = LossOutput(total=loss.total.detach(), components={k: v.detach() for k, v in loss.components.items()})
         return loss, counts
@@ -423,8 +430,7 @@ class Trainer:
                     loss_acc = d if loss_acc is None else loss_acc + d
                     for k, v in loss.components.items():
                         comp_acc[k] = v.detach() if k not in comp_acc else comp_acc[k] + v.detach()
-                for k, v in counts.items():
-                    counts_acc[k] = v if k not in counts_acc else counts_acc[k] + v
+                counts_acc = add_router_counts(counts_acc, counts)
                 micro += 1
                 if micro < cfg.grad_accum_steps:
                     t_prev = time.perf_counter()

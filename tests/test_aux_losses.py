@@ -68,3 +68,24 @@ def test_model_feeds_the_aux_losses(family, tiny_scale):
         ref.total.backward()
         g = m.backbone.blocks[0].layers[0].expert_router.score_mlp.layers[0].weight.grad
         assert g is not None and g.abs().sum() > 0
+
+
+def test_packed_router_counts_sum_like_the_dictionaries():
+    import torch
+
+    from nestor_b200.models.nestor import RouterCounts, add_router_counts
+
+    a = {"blocks.0.group_router": torch.tensor([3.0, 1.0, 4.0]), "blocks.0.layers.0.expert_router": torch.tensor([[1.0, 2.0], [3.0, 4.0]])}
+    b = {k: v * 2 + 1 for k, v in a.items()}
+    pa, pb = RouterCounts.pack(a), RouterCounts.pack(b)
+    assert set(pa) == set(a) and all(torch.equal(pa[k], a[k]) and pa[k].shape == a[k].shape for k in a)
+    total = add_router_counts(None, pa)
+    assert total is not pa and torch.equal(total.flat, pa.flat)          # the first micro-batch's counts are copied
+    total = add_router_counts(total, pb)
+    pa.flat.zero_()                                                     # a replayed graph overwrites its static output
+    for k in a:
+        assert torch.equal(total[k], a[k] + b[k])
+    plain = add_router_counts({}, a)
+    plain = add_router_counts(plain, b)
+    assert all(torch.equal(plain[k], total[k]) for k in a)
+    assert add_router_counts(None, RouterCounts.pack({})) is not None
