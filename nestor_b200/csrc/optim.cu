@@ -61,9 +61,37 @@ __global__ void __launch_bounds__(256) multi_tensor_kernel(const Entry* __restri
   }
 }
 
+// Loss-free balancing nudge for every router at once: bias += rate * sign(mean(c) - c), one warp per router.
+// `counts` is the flat tensor of all routers' summed selection counts; a router's slice starts at `offset`.
+struct BiasEntry { float* bias; long offset; int n; float rate; };
+
+__global__ void __launch_bounds__(128) bias_update_kernel(const BiasEntry* __restrict__ table, int n_routers,
+                                                          const float* __restrict__ counts) {
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= n_routers) return;
+  const BiasEntry e = table[r];
+  const float* c = counts + e.offset;
+  float sum = 0.f;
+  for (int i = lane; i < e.n; i += 32) sum += c[i];
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
+  const float mean = sum / float(e.n);
+  for (int i = lane; i < e.n; i += 32) {
+    const float d = mean - c[i];
+    e.bias[i] += e.rate * (d > 0.f ? 1.f : (d < 0.f ? -1.f : 0.f));
+  }
+}
+
 }  // namespace nbo
 
 extern "C" {
+
+// table: device array of {bias pointer, offset into counts, n, rate} (24 bytes per router)
+int nb_bias_update(const void* table, int n_routers, const float* counts, cudaStream_t st) {
+  if (n_routers <= 0) return 0;
+  nbo::bias_update_kernel<<<(n_routers + 3) / 4, 128, 0, st>>>(reinterpret_cast<const nbo::BiasEntry*>(table), n_routers, counts);
+  return int(cudaGetLastError());
+}
 
 int nb_multi_tensor_chunk() { return nbo::kChunk; }
 

@@ -71,6 +71,24 @@ class InitScales:
             self.norm_eps = 1e-6
 
 
+class _SplitColumns(torch.autograd.Function):
+    """Contiguous column blocks of a ``[T, C]`` matrix. Plain slices would each send a zero-filled ``[T, C]`` gradient
+    back (a fill, a copy and an add per slice); here the blocks' gradients are concatenated once."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, sizes: tuple[int, ...]):
+        ctx.sizes, ctx.dtype = sizes, x.dtype
+        return tuple(part.contiguous() for part in torch.split(x, list(sizes), dim=1))
+
+    @staticmethod
+    def backward(ctx, *grads):
+        T = next(g for g in grads if g is not None).shape[0]
+        dev = next(g for g in grads if g is not None).device
+        parts = [g.to(ctx.dtype) if g is not None else torch.zeros(T, n, dtype=ctx.dtype, device=dev)
+                 for g, n in zip(grads, ctx.sizes)]
+        return torch.cat(parts, dim=1), None
+
+
 class ExpertPool(nn.Module):
     """Hybrid pool: ``P`` public experts + ``Q`` private experts per column + 2-logit path gate.
 
@@ -114,9 +132,8 @@ class ExpertPool(nn.Module):
         arena = self.__dict__.get("_nestor_arena")
         wcat = arena.concat_view(heads) if arena is not None and heads[0].requires_grad else torch.cat(heads, dim=0)
         scores = ops.router_scores(n, None, wcat, cd)
-        pub_scores = scores[:, : s.P]
-        priv_scores = scores[:, s.P : s.P + s.G * s.Q].reshape(T, s.G, s.Q)
-        path_logits = scores[:, s.P + s.G * s.Q :]
+        pub_scores, priv_scores, path_logits = _SplitColumns.apply(scores, (s.P, s.G * s.Q, 2))
+        priv_scores = priv_scores.view(T, s.G, s.Q)
         pub_idx, pub_gate = ops.route_topk(pub_scores, self.public_router.choice_bias, s.k_p, "renorm")
         # every (token, selected column) pair picks k_q of that column's Q private experts
         priv_ids, priv_w, priv_idx = ops.route_selected(priv_scores, self.private_bias(), idx, gates, s.k_q,
@@ -825,8 +842,15 @@ def apply_bias_updates(backbone: Nestor, counts: dict[str, Tensor], *, global_co
     if not counts:
         return
     names = sorted(counts)
-    if global_counts and torch.distributed.is_available() and torch.distributed.is_initialized() \
-            and torch.distributed.get_world_size() > 1:
+    multi = global_counts and torch.distributed.is_available() and torch.distributed.is_initialized() \
+        and torch.distributed.get_world_size() > 1
+    if isinstance(counts, RouterCounts) and counts.flat.is_cuda and counts.flat.numel() > 0:
+        # packed counts on a GPU: one all-reduce of the flat tensor (if asked for) and one kernel for every router
+        if multi:
+            torch.distributed.all_reduce(counts.flat)
+        _fused_bias_update(backbone, counts)
+        return
+    if multi:
         flat = torch.cat([counts[n].reshape(-1) for n in names])
         torch.distributed.all_reduce(flat)
         off = 0
@@ -840,3 +864,42 @@ def apply_bias_updates(backbone: Nestor, counts: dict[str, Tensor], *, global_co
         if r.loss_free and r.bias_rate:
             c = counts[n]
             r.choice_bias.add_(r.bias_rate * torch.sign(c.mean() - c))
+
+
+def _fused_bias_update(backbone: Nestor, counts: RouterCounts) -> None:
+    """``nb_bias_update``: the table of (bias pointer, offset into the flat counts, size, rate) is built once per
+    backbone and layout (router buffers do not move), the flat counts pointer is a launch argument."""
+
+    import ctypes as C
+
+    from nestor_b200.ops import _lib
+    names = [n for n, _ in counts.layout]
+    cache = backbone.__dict__.setdefault("_bias_update_tables", {})
+    key = (tuple(names), counts.flat.device)
+    hit = cache.get(key)
+    if hit is not None and [r.choice_bias.data_ptr() for r in hit[3]] != hit[2]:
+        hit = None                                   # a buffer was re-created (model moved or rebuilt): new table
+    if hit is None:
+        modules = dict(backbone.named_modules())
+        rows, off = [], 0
+        for n, shape in counts.layout:
+            size = int(torch.Size(shape).numel())
+            r = modules[n]
+            if r.loss_free and r.bias_rate:
+                assert r.choice_bias.numel() == size and r.choice_bias.dtype == torch.float32 and r.choice_bias.is_contiguous()
+                rate = torch.tensor([r.bias_rate], dtype=torch.float32).view(torch.int32).item()
+                rows.append([r.choice_bias.data_ptr(), off, size | (rate << 32)])
+            off += size
+        table = torch.tensor(rows, dtype=torch.int64).reshape(-1, 3).to(counts.flat.device) if rows else None
+        routers = [modules[n] for n in names]
+        hit = cache[key] = (table, len(rows), [r.choice_bias.data_ptr() for r in routers], routers)
+    table, n_rows = hit[0], hit[1]
+    if n_rows == 0:
+        return
+    L = _lib.lib()
+    L.nb_bias_update.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+    L.nb_bias_update.restype = C.c_int
+    rc = L.nb_bias_update(table.data_ptr(), n_rows, counts.flat.data_ptr(), C.c_void_p(_lib.stream_ptr()))
+    if rc != 0:
+        raise RuntimeError(f"nb_bias_update failed with code {rc}")
+    _lib.count_launch()

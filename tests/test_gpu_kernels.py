@@ -751,3 +751,29 @@ print("BOUNDS_OK")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     res = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0 and "BOUNDS_OK" in res.stdout, res.stdout + res.stderr
+
+
+def test_fused_router_bias_update_matches_the_per_router_rule():
+    """One kernel for every router: bias += rate * sign(mean(c) - c) on packed counts, against the PyTorch statement."""
+
+    from nestor_b200.experiments.tiny import nestor_tiny
+    from nestor_b200.models import Model
+    from nestor_b200.models.nestor import RouterCounts, apply_bias_updates
+
+    torch.manual_seed(5)
+    m = Model.from_config(nestor_tiny().jobs[0].model).cuda()
+    routers = {n: r for n, r in m.backbone.named_modules() if hasattr(r, "choice_bias") and getattr(r, "loss_free", False)}
+    assert len(routers) >= 6
+    counts = {n: torch.randint(0, 5, r.choice_bias.shape, device="cuda").float() for n, r in routers.items()}
+    first = next(iter(counts))
+    counts[first][:] = 3.0                                   # a router in perfect balance moves nothing
+    want = {n: r.choice_bias.clone() + r.bias_rate * torch.sign(counts[n].mean() - counts[n]) for n, r in routers.items()}
+    from nestor_b200 import ops
+    before = ops.launch_count()
+    apply_bias_updates(m.backbone, RouterCounts.pack(counts))
+    assert ops.launch_count() == before + 1
+    for n, r in routers.items():
+        assert torch.allclose(r.choice_bias, want[n], atol=1e-7), n
+    apply_bias_updates(m.backbone, RouterCounts.pack(counts))     # cached table, second application
+    for n, r in routers.items():
+        assert torch.allclose(r.choice_bias, want[n] + r.bias_rate * torch.sign(counts[n].mean() - counts[n]), atol=1e-7), n
