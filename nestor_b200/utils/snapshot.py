@@ -15,16 +15,27 @@ from pathlib import Path
 
 PRUNED_DIRS = frozenset({
     ".git", ".cursor", ".claude", "__pycache__", ".venv", "venv", ".mypy_cache", ".ruff_cache", ".pytest_cache",
-    ".hypothesis", "data", "logs", "tmp", "outputs", "checkpoints", "wandb", "_C", "_ref", "build", "gpurun_out", "_work",
+    ".hypothesis", "data", "logs", "tmp", "outputs", "checkpoints", "wandb", "_C", "_ref", "build",
 })
 SKIPPED_FILES = ("*.pyc", "*.pyo", "*.pt", "*.pth", "*.ckpt", "*.zip", "*.tar", "*.tar.gz", "*.h5", "*.hdf5", "*.bin",
                  "*.o", "*.so", "*.a", "*.ncu-rep", ".env", ".DS_Store")
+
+
+def _scratch_dirs(root: Path) -> set[str]:
+    """Top-level directories that the repository's own ignore file lists: scratch output is not source."""
+
+    ignore = root / ".gitignore"
+    if not ignore.is_file():
+        return set()
+    return {line.strip().strip("/") for line in ignore.read_text().splitlines()
+            if line.strip().endswith("/") and "*" not in line and not line.startswith("#")}
 
 
 def source_files(root: Path, pruned_dirs=PRUNED_DIRS, skipped_files=SKIPPED_FILES) -> list[Path]:
     """Relative paths of the files a snapshot of ``root`` contains, sorted (the walk never enters a pruned directory)."""
 
     root = Path(root)
+    pruned_dirs = set(pruned_dirs) | _scratch_dirs(root)
     out: list[Path] = []
     stack = [root]
     while stack:
