@@ -335,10 +335,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                            : (2 * p.BN <= 256) ? 256 : 512;
   const int n_tiles = (p.N + p.BN - 1) / p.BN;
 
+  // every thread fetches one group offset (one round of loads in flight; a single thread walking up to 257 offsets
+  // paid a global-memory latency per group before the first tile could start)
+  for (int g = threadIdx.x; g <= p.groups; g += blockDim.x)
+    s_off[g] = p.offsets ? p.offsets[g] : g * p.rows_per_group;
+  __syncthreads();
   if (threadIdx.x == 0) {
     s_abort = 0;
-    for (int g = 0; g <= p.groups; ++g)
-      s_off[g] = p.offsets ? p.offsets[g] : g * p.rows_per_group;
     int acc = 0;
     for (int g = 0; g < p.groups; ++g) {
       s_tstart[g] = acc;
