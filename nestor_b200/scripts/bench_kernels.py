@@ -31,21 +31,25 @@ WARMUP = 3
 
 
 def timed(fn, reps: int, flush: bool = True) -> float:
+    """Mean device time of ``fn`` in ms. Every repetition (L2 flush, start event, ``fn``, stop event) is enqueued behind
+    a spin kernel before anything is waited for, so the host is always ahead of the device: the events bracket the
+    kernels of ``fn`` and nothing else. (With a synchronise per repetition the start event completes on an idle GPU
+    and the host time of the Python launch path, some 50 us, is counted as kernel time.)"""
+
     global _flush
     if flush and _flush is None:
         _flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device="cuda")
     for _ in range(WARMUP):
         fn()
     torch.cuda.synchronize()
-    total = 0.0
-    for _ in range(reps):
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+    torch.cuda._sleep(4_000_000)          # about 2 ms of device time for the host to get ahead
+    for e0, e1 in pairs:
         if flush:
             _flush.zero_()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(); fn(); e1.record()
-        torch.cuda.synchronize()
-        total += e0.elapsed_time(e1)
-    return total / reps
+    torch.cuda.synchronize()
+    return sum(e0.elapsed_time(e1) for e0, e1 in pairs) / reps
 
 
 def offsets(rows: int, groups: int) -> torch.Tensor:
