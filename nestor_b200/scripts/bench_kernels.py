@@ -3,7 +3,8 @@
 ``python -m nestor_b200.scripts.bench_kernels [case ...] [--reps N]`` prints one line per kernel launch
 shape: time, achieved TFLOP/s or GB/s and the fraction of the measured peaks in ``MEASURED_PEAKS.json``
 (fallback 1590 TFLOP/s, 6650 GB/s). Cases: ``gemm`` (expert / attention / head GEMMs of nestor_200m),
-``flash``, ``depth``, ``ns`` (Newton-Schulz), ``small`` (one launch of each, sized for a profiler capture). Inputs are larger
+``flash``, ``depth``, ``ns`` (Newton-Schulz), ``gather`` (all-gather fused into the bank GEMMs, one GPU), ``small`` /
+``gather-small`` (one launch of each, sized for a profiler capture). Inputs are larger
 than the 126 MB L2 or an L2 flush is written between repetitions.
 """
 
@@ -206,7 +207,8 @@ def main(argv: list[str] | None = None) -> None:
         if c == "small":
             case_gemm(a.reps, small=True); case_flash(a.reps, small=True); case_depth(a.reps, small=True); case_ns(a.reps, small=True)
         else:
-            {"gemm": case_gemm, "flash": case_flash, "depth": case_depth, "gather": case_gather, "ns": case_ns}[c](a.reps)
+            {"gemm": case_gemm, "flash": case_flash, "depth": case_depth, "gather": case_gather, "ns": case_ns,
+             "gather-small": lambda r: case_gather(r, small=True)}[c](a.reps)
     from nestor_b200.ops import _lib
     _lib.check_status(torch.device("cuda"))
 
