@@ -21,3 +21,13 @@ export NESTOR_DDP_BROADCAST_BUFFERS="${NESTOR_DDP_BROADCAST_BUFFERS:-1}" # rank 
 export NESTOR_B200_CUDA_GRAPH="${NESTOR_B200_CUDA_GRAPH:-1}"          # replay the micro-batch as one CUDA graph
 export NESTOR_B200_GRAD_TRANSPORT="${NESTOR_B200_GRAD_TRANSPORT:-fused}" # fused peer-memory all-reduce | nccl
 export NESTOR_MFU_PEAK_TFLOPS="${NESTOR_MFU_PEAK_TFLOPS:-2250}"       # B200 dense bf16
+# Recipe and bookkeeping switches that are read when set (unset = the registered recipe):
+#   NESTOR_MUP_ROUTER_BASE_LR=1 / NESTOR_MUP_ROUTER_BASE_INIT=1  routers at the base AdamW rate / drawn at initializer_range
+#                                (only differ from the default under matrix_optimizer="adamw")
+#   NESTOR_DROP_MUP=1            ignore every optimizer tag: one AdamW group at the base rate
+#   NESTOR_MFU_FLOPS_PER_STEP=x  pin the FLOPs of one rank's forward + backward micro-batch used by the MFU metric
+#   NESTOR_BF16_MASTER           accepted; bf16 compute with fp32 masters is the only bf16 mode here
+#   NESTOR_B200_NVLS=0           keep the in-kernel collectives on plain peer loads / stores (no multimem)
+#   NESTOR_B200_STRICT=1         a shape beyond a kernel's built-in limit raises instead of running the PyTorch statement
+#   NESTOR_B200_BOUNDS_CHECK=1   load the index-checking build of the kernel library
+#   NESTOR_DEPTH_READ_KEEP_H=0   do not keep the depth-read mixture for the backward (one [T, d] fp32 row per read)

@@ -25,7 +25,7 @@ from nestor_b200.models.registry import (
     ADAPTERS, BACKBONES, HEADS, MODELS, register_adapter, register_backbone, register_head, register_model,
 )
 from nestor_b200.models.scaling import _ACTIVATIONS as SCALING_ACTIVATIONS, RMSNorm, ScaledLinear
-from nestor_b200.models.tags import ADAMW_DECAY, tag
+from nestor_b200.models.tags import ADAMW_DECAY, ParamTag, tag
 
 
 @dc.dataclass
@@ -154,6 +154,68 @@ class LanguageModelingHead(nn.Module):
 register_backbone(NestorConfig)(lambda config, mup, **kw: Nestor(config, mup, **kw))
 
 
+def apply_recipe_variants(model: nn.Module, mup: ReferenceMupConfig) -> None:
+    """Optimizer-tag variants of the reference-muP recipe (``nestor/scaling/reference_mup.py:126-311``).
+
+    The models are built with the tags of the Muon pairing (in-stream matrices Muon, single-matrix routers and path
+    gates AdamW at the base rate). This pass applies what differs from it:
+
+    * ``matrix_optimizer="adamw"``: attention and expert matrices move to AdamW at ``1 / width_multiplier`` of the base
+      rate; routers follow them unless ``NESTOR_MUP_ROUTER_BASE_LR=1`` keeps them at the base rate (the reference
+      transform never marks a router); path gates take the matrix rate. The group router's hidden layers stay Muon.
+    * ``group_router_lr="base"``: the group router's score / noise read-outs train at the base AdamW rate instead of
+      ``score_lr_mul / hidden``.
+    * ``NESTOR_MUP_ROUTER_BASE_INIT=1``: single-matrix routers are re-drawn at ``initializer_range`` instead of
+      ``initializer_range / sqrt(width_multiplier)``.
+    """
+
+    if not mup.enabled("optimizer"):
+        return
+    muon_matrices = mup.matrix_optimizer == "muon"
+    matrix_lr_mul = 1.0 / mup.width_multiplier
+    router_lr_mul = 1.0 if muon_matrices or os.environ.get("NESTOR_MUP_ROUTER_BASE_LR", "0") == "1" else matrix_lr_mul
+    router_init = os.environ.get("NESTOR_MUP_ROUTER_BASE_INIT", "0") == "1" and mup.enabled("initialization")
+
+    def adamw(p: Tensor, lr_mul: float) -> None:
+        tag(p, ParamTag("adamw", lr_mul=lr_mul, weight_decay=True))
+
+    def router(r) -> None:
+        w = r.score_mlp.layers[0].weight
+        if len(r.score_mlp.layers) == 1:
+            adamw(w, router_lr_mul)
+            if router_init:
+                with torch.no_grad():
+                    w.normal_(0.0, mup.initializer_range)
+
+    for block in model.backbone.blocks:
+        for layer in block.layers:
+            if not muon_matrices:
+                for g in layer.attention_groups:
+                    for lin in (g.q_proj, g.k_proj, g.v_proj, g.out_proj):
+                        adamw(lin.weight, matrix_lr_mul)
+                banks = [b for b in (layer.stacked_moe_bank,) if b is not None]
+                if layer.expert_pool is not None:
+                    banks += [b for b in (layer.expert_pool.stacked_public, layer.expert_pool.stacked_private) if b is not None]
+                for bank in banks:
+                    for w in (bank.w_up, bank.w_gate, bank.w_down):
+                        adamw(w, matrix_lr_mul)
+                for expert in layer.shared_experts or []:
+                    for lin in (*expert.layers, expert.gate):
+                        adamw(lin.weight, matrix_lr_mul)
+            if layer.expert_router is not None:
+                router(layer.expert_router)
+            pool = layer.expert_pool
+            if pool is not None:
+                for r in ([pool.public_router] if pool.public_router is not None else []) + list(pool.private_routers):
+                    router(r)
+                if pool.path_gate is not None:
+                    adamw(pool.path_gate.weight, router_lr_mul if muon_matrices else matrix_lr_mul)
+        if mup.group_router_lr == "base" and block.spec.G > 1:
+            for mlp in (block.group_router.score_mlp, block.group_router.noise_mlp):
+                if mlp is not None:
+                    adamw(mlp.layers[-1].weight, 1.0)
+
+
 @register_model(SequenceModelConfig)
 class SequenceModel(nn.Module):
     """adapter -> backbone -> head, each built from its config through the registries.
@@ -173,6 +235,8 @@ class SequenceModel(nn.Module):
         self.adapter = ADAPTERS.build(config.adapter_config, mup)
         self.backbone = BACKBONES.build(config.backbone_config, mup, dense_no_router=dense_no_router)
         self.head = HEADS.build(config.head_config, self.backbone.output_dim, mup)
+        if mup is not None:
+            apply_recipe_variants(self, mup)
         self.fused_head = False
         self.compute_dtype: torch.dtype | None = None
         # NESTOR_FASTPATH_CHECK=1: the first three kernel-path forwards are repeated on the PyTorch statement of the

@@ -355,10 +355,13 @@ def build_param_groups(config: MuonAdamWConfig, model: nn.Module) -> list[dict[s
     muon: dict[float, list[nn.Parameter]] = defaultdict(list)
     adamw: dict[tuple[float, bool], list[nn.Parameter]] = defaultdict(list)
     untagged = []
+    # NESTOR_DROP_MUP=1 ignores every tag: one plain AdamW group at the base rate with decay (the regime the reference's
+    # first sweeps ran in, ``nestor/train/optim.py:231-238``)
+    drop_tags = os.environ.get("NESTOR_DROP_MUP") == "1"
     for name, p in model.named_parameters():
         if not p.requires_grad:
             continue
-        t = get_tag(p)
+        t = None if drop_tags else get_tag(p)
         if t is None:
             untagged.append(name)
             adamw[(1.0, True)].append(p)
@@ -368,7 +371,7 @@ def build_param_groups(config: MuonAdamWConfig, model: nn.Module) -> list[dict[s
             adamw[(round(t.lr_mul, 10), t.weight_decay)].append(p)
         else:
             raise ValueError(f"Parameter '{name}' has unknown optimizer '{t.optimizer}'.")
-    if untagged:
+    if untagged and not drop_tags:
         warnings.warn(f"MuonAdamW: {len(untagged)} untagged parameter(s) (e.g. {untagged[0]}) use default AdamW.")
     groups: list[dict[str, Any]] = []
     for scale, ps in sorted(muon.items()):

@@ -94,6 +94,10 @@ class Trainer:
         self.masters_sharded = bool(self.param_push is not None and not self.param_push.push_master)
         # Device status word of the in-kernel collectives: a bounded peer wait that gave up leaves a nonzero code
         # there and the kernel returns without reducing / pushing. It is read back once per optimizer step.
+        if os.environ.get("NESTOR_BF16_MASTER") == "0" and bf16:
+            # the reference's NESTOR_BF16_MASTER=1 (bf16 matrices with fp32 masters in the optimizer, no cast per use)
+            # is how this trainer always runs in bf16; there is no per-use-cast mode to fall back to
+            self.logger.info("NESTOR_BF16_MASTER=0 has no effect: the bf16 compute copy with fp32 masters is the only bf16 mode")
         self.nvtx = _env_flag("NESTOR_NVTX")
         self.phase_events: list | None = None     # set to [] to time the phases of the next update_weights
         self.peer_status: Tensor | None = None
@@ -367,6 +371,14 @@ class Trainer:
         peak = float(os.environ.get("NESTOR_MFU_PEAK_TFLOPS", "2250")) * 1e12
         flops_tok = float(os.environ.get("NESTOR_MFU_FLOPS_PER_TOKEN", "0")) or train_flops_per_token(
             self.model.config, self._seq_len())
+        pinned = float(os.environ.get("NESTOR_MFU_FLOPS_PER_STEP", "0") or 0)
+        if pinned > 0:
+            # FLOPs of one forward + backward micro-batch of one rank, as the reference takes it
+            # (nestor/train/trainer.py:587-603); divided by the micro-batch's tokens once they are known
+            loader_cfg = getattr(cfg, "train_dataloader", None)
+            per_rank = max(1, int(getattr(loader_cfg, "batch_size", self.world)) // self.world)
+            flops_tok = pinned / max(1, per_rank * self._seq_len())
+            self.logger.info("[MFU] flops/microbatch pinned via env: %.3e", pinned)
         if _env_flag("NESTOR_MFU_CALIBRATE"):
             # cross-check of the analytic count against FlopCounterMode on the PyTorch statement of the model
             from nestor_b200.train.flops import calibrate_flops

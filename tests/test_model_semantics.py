@@ -406,3 +406,57 @@ def test_private_only_pool_matches_reference(tiny_scale, monkeypatch):
             assert (g1 - g2).norm() / g1.norm() < 2e-3, n
     counts = router_counts(mm.backbone, out.aux)
     assert not any("public" in k for k in counts) and any("private_routers" in k for k in counts)
+
+
+@pytest.mark.parametrize("variant", ["muon", "adamw", "adamw_router_base", "muon_group_router_base"])
+def test_optimizer_recipe_variants_match_reference_groups(variant, tiny_scale, monkeypatch):
+    """Per-parameter optimizer, learning rate and weight decay of the reference-muP recipe variants
+    (``matrix_optimizer="adamw"``, ``NESTOR_MUP_ROUTER_BASE_LR``, ``group_router_lr="base"``) agree with the groups the
+    reference builds for the same configuration."""
+
+    import dataclasses as dc
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "nestor").is_dir():
+        pytest.skip("reference package not installed under baseline/_ref")
+    monkeypatch.setenv("NESTOR_STACKED_EXPERT_BANKS", "1")
+    monkeypatch.setenv("NESTOR_DENSE_NO_ROUTER", "1")
+    if variant == "adamw_router_base":
+        monkeypatch.setenv("NESTOR_MUP_ROUTER_BASE_LR", "1")
+    monkeypatch.syspath_prepend(str(ref_root))
+    try:
+        from nestor.experiments import pretrain as RP
+        from nestor.models import Model as RefModel
+        from nestor.train.optim import build_optimizer as ref_build
+    except Exception as exc:
+        pytest.skip(f"reference import failed: {exc}")
+    from nestor_b200.train.optim import build_param_groups
+    P = tiny_scale
+    monkeypatch.setitem(RP.SCALES, "tiny", RP.Scale("tiny", 128, 4, 8, 512, 10, 2, 1024))
+    monkeypatch.setitem(RP.NESTOR_LAYERS, "tiny", (2, 1, 1, 1, 1, 1, 2))
+    monkeypatch.setitem(RP.NESTOR_PRIVATE_EXPERTS, "tiny", 3)
+    monkeypatch.setattr(RP, "NESTOR_MIN_PRIVATE_WIDTH", 24)
+    monkeypatch.setattr(RP, "BLOCK_SIZE", 64)
+    for fam in ("dense", "moe", "nestor"):
+        monkeypatch.setitem(RP.BATCH_SHAPE, (fam, "tiny"), (2, 1))
+    changes = {"matrix_optimizer": "adamw" if variant.startswith("adamw") else "muon",
+               "group_router_lr": "base" if variant == "muon_group_router_base" else "native"}
+    rjob = RP._nestor("tiny").jobs[0]
+    rcfg = dc.replace(rjob.model, reference_mup=dc.replace(rjob.model.reference_mup, **changes))
+    rm = RefModel.from_config(rcfg)
+    ropt = ref_build(rjob.optimizer, rm)
+    rnames = {id(p): n for n, p in rm.named_parameters()}
+    want = {}
+    for g in ropt.param_groups:
+        for p in g["params"]:
+            want[rnames[id(p)]] = (g.get("method", "adamw"), round(float(g["lr"]), 12), round(float(g["weight_decay"]), 12))
+    job = P.build_experiment("nestor", "tiny").jobs[0]
+    cfg = dc.replace(job.model, reference_mup=dc.replace(job.model.reference_mup, **changes))
+    mm = Model.from_config(cfg)
+    names = {id(p): n for n, p in mm.named_parameters()}
+    got = {}
+    for g in build_param_groups(job.optimizer, mm):
+        for p in g["params"]:
+            got[names[id(p)]] = (g["method"], round(float(g["lr"]), 12), round(float(g["weight_decay"]), 12))
+    assert set(got) == set(want)
+    wrong = {n: (got[n], want[n]) for n in want if got[n] != want[n]}
+    assert not wrong, dict(list(wrong.items())[:6])

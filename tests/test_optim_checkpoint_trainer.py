@@ -207,3 +207,16 @@ def test_update_weights_raises_when_a_collective_reported_a_timeout(tiny_scale, 
     with pytest.raises(PeerTimeout, match="status 5"):
         trainer.update_weights({})
     assert int(trainer.peer_status.item()) == 0     # cleared, so a caller that recovers can carry on
+
+
+def test_drop_mup_puts_every_parameter_in_one_adamw_group(tiny_scale, monkeypatch):
+    from nestor_b200.models import Model
+    from nestor_b200.train.optim import build_param_groups
+
+    job = tiny_scale.build_experiment("nestor", "tiny").jobs[0]
+    m = Model.from_config(job.model)
+    assert len(build_param_groups(job.optimizer, m)) > 2
+    monkeypatch.setenv("NESTOR_DROP_MUP", "1")
+    groups = build_param_groups(job.optimizer, m)
+    assert len(groups) == 1 and groups[0]["method"] == "adamw" and groups[0]["lr"] == job.optimizer.lr_adamw
+    assert sum(p.numel() for p in groups[0]["params"]) == sum(p.numel() for p in m.parameters() if p.requires_grad)
