@@ -17,6 +17,10 @@ memory and the step's loss read back to the host. Inputs per step (4 x 4096 x 8 
 are tiny next to the 126 MB L2, but the working set of one micro-batch (several GB of
 activations and 3 GB of parameters) is far larger than L2, so no explicit flush is needed.
 
+``--experiment`` takes any registered cell (``{dense,moe,nestor}_{100m,200m,500m,1b}``); the accumulation follows the
+cell's tokens per optimizer step (``nestor_1b``: 2,097,152 tokens, accumulation 128/N; run it with
+``NESTOR_ACTIVATION_CHECKPOINT=1``, and the reference arm with ``NESTOR_DDP=0`` as well, for the FSDP2 configuration).
+
 ``--impl reference`` runs the unmodified reference package installed under
 ``baseline/_ref`` through its own ``TrainPipeline`` with its launcher's speed-stack flags.
 """
@@ -37,7 +41,15 @@ ROOT = Path(__file__).resolve().parent
 EXPERIMENT = "nestor_200m"
 SEQ_LEN = 4096
 SEQS_PER_GPU = 4
-TOKENS_PER_STEP = 524_288
+TOKENS_PER_STEP = 524_288       # the 200m rung; other rungs: see tokens_per_step()
+_RUNG_TOKENS = {"100m": 262_144, "200m": 524_288, "500m": 1_048_576, "1b": 2_097_152}
+
+
+def tokens_per_step(experiment: str) -> int:
+    """Tokens per optimizer step of an experiment's scale rung (the registries of both arms insist on it)."""
+
+    return _RUNG_TOKENS.get(experiment.rsplit("_", 1)[-1], TOKENS_PER_STEP)
+
 VOCAB = 100_263
 BASELINE_TOKENS_PER_SEC = None  # the reference publishes no throughput figure
 
@@ -100,11 +112,11 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def _data_path(world: int, rank: int, steps_total: int) -> Path:
+def _data_path(world: int, rank: int, steps_total: int, step_tokens: int = TOKENS_PER_STEP) -> Path:
     """Synthetic corpus shared by all ranks (rank 0 writes, others wait for the sidecar)."""
 
     path = Path(tempfile.gettempdir()) / f"nestor_bench_{VOCAB}_{SEQ_LEN}.bin"
-    need = max(2 * steps_total * TOKENS_PER_STEP, 16 * 1024 * 1024)
+    need = max(2 * steps_total * step_tokens, 16 * 1024 * 1024)
     meta = Path(f"{path}.meta.json")
     if rank == 0:
         ok = meta.is_file() and json.loads(meta.read_text()).get("num_tokens", 0) >= need
@@ -140,7 +152,8 @@ def run_ours(a: argparse.Namespace) -> dict:
     sys.path.insert(0, str(ROOT))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
-    accum = max(1, 32 // world)
+    step_tokens = tokens_per_step(a.experiment)
+    accum = max(1, step_tokens // (SEQS_PER_GPU * SEQ_LEN * world))
     os.environ["DCLM_GLOBAL_BATCH"] = str(SEQS_PER_GPU * world)
     os.environ["DCLM_GRAD_ACCUM"] = str(accum)
     os.environ["DCLM_MAX_STEPS"] = str(10_000)
@@ -151,7 +164,7 @@ def run_ours(a: argparse.Namespace) -> dict:
     device = init_distributed(enabled=True)
     if device.type != "cuda":
         raise SystemExit("bench.py needs a CUDA device")
-    path = _data_path(world, rank, a.steps * 2 + a.warmup + 2)
+    path = _data_path(world, rank, a.steps * 2 + a.warmup + 2, step_tokens)
     barrier()
     os.environ["DCLM_DATA_PATH"] = str(path)
 
@@ -258,17 +271,17 @@ def run_ours(a: argparse.Namespace) -> dict:
             census = {"error": f"{type(exc).__name__}: {exc}"[:160]}
     _bracket(device)      # every rank leaves together (rank 0 alone ran the census)
 
-    tokens = TOKENS_PER_STEP * a.steps
+    tokens = step_tokens * a.steps
     value = tokens / (ms_dev / 1e3)
     h2d = accum * SEQS_PER_GPU * SEQ_LEN * 8
     return {
-        "metric": "nestor_200m train tokens/sec", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "metric": f"{a.experiment} train tokens/sec", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": a.steps, "warmup": max(3, a.warmup), "ms_per_step": ms_dev / a.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None if BASELINE_TOKENS_PER_SEC is None else value / BASELINE_TOKENS_PER_SEC,
         "dtype": "bf16", "data": "synthetic uniform token ids in log-uniform-length documents; random-init weights",
         "impl": "ours",
         "config": {"model": a.experiment, "global_batch": SEQS_PER_GPU * world, "grad_accum": accum,
-                   "tokens_per_step": TOKENS_PER_STEP, "seq_len": SEQ_LEN, "parallelism": f"dp{world}",
+                   "tokens_per_step": step_tokens, "seq_len": SEQ_LEN, "parallelism": f"dp{world}",
                    "optimizer": "sharded Muon + AdamW, clip 1.0", "l2": "working set >> L2 (no flush needed)"},
         "stack": {"kernels": "in-tree sm_100a library (tcgen05 / TMA), CUDA-graph micro-batch",
                   "grad_transport": os.environ.get("NESTOR_B200_GRAD_TRANSPORT", "fused")},
@@ -343,7 +356,8 @@ def run_reference(a: argparse.Namespace) -> dict:
         return {"impl": "reference", "unavailable": "baseline/_ref is not installed (pip install --target baseline/_ref)"}
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
-    accum = max(1, 32 // world)
+    step_tokens = tokens_per_step(a.experiment)
+    accum = max(1, step_tokens // (SEQS_PER_GPU * SEQ_LEN * world))
     warm = max(3, a.warmup)
     # The launcher's speed stack (scripts/lib/speed_stack.sh of the reference), verbatim defaults.
     stack = dict(
@@ -369,7 +383,7 @@ def run_reference(a: argparse.Namespace) -> dict:
     for k, v in (("MASTER_ADDR", "127.0.0.1"), ("MASTER_PORT", "29533"), ("RANK", "0"), ("WORLD_SIZE", "1"),
                  ("LOCAL_RANK", "0")):
         os.environ.setdefault(k, v)   # a bare `python bench.py` run still gets an env:// rendezvous
-    path = _data_path(world, rank, a.steps + warm + 2)
+    path = _data_path(world, rank, a.steps + warm + 2, step_tokens)
     os.environ["DCLM_DATA_PATH"] = str(path)
     sys.path.insert(0, str(ref))
     try:
@@ -416,15 +430,15 @@ def run_reference(a: argparse.Namespace) -> dict:
         torch.cuda.synchronize()
         clocks = sampler.stop() if rank == 0 else {}
         ms = _max_over_ranks(events[warm - 1].elapsed_time(events[warm + a.steps - 1]), torch.device(device))
-        tokens = TOKENS_PER_STEP * a.steps
+        tokens = step_tokens * a.steps
         value = tokens / (ms / 1e3)
         out = {
-            "metric": "nestor_200m train tokens/sec", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "metric": f"{a.experiment} train tokens/sec", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": a.steps, "warmup": warm, "ms_per_step": ms / a.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "impl": "reference",
             "data": "synthetic uniform token ids in log-uniform-length documents; random-init weights",
             "config": {"model": a.experiment, "global_batch": SEQS_PER_GPU * world, "grad_accum": accum,
-                       "tokens_per_step": TOKENS_PER_STEP, "seq_len": SEQ_LEN, "parallelism": f"dp{world}",
+                       "tokens_per_step": step_tokens, "seq_len": SEQ_LEN, "parallelism": f"dp{world}",
                        "optimizer": "sharded Muon + AdamW, clip 1.0", "l2": "working set >> L2 (no flush needed)"},
             "stack": {"speed_stack": {k: os.environ[k] for k in stack}, "speed_stack_adjusted": adjusted},
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": accum * SEQS_PER_GPU * SEQ_LEN * 16,
