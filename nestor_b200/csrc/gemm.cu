@@ -1,5 +1,6 @@
 // Persistent grouped GEMM for sm_100a: TMA -> 128B-swizzled shared memory -> tcgen05.mma
-// with fp32 accumulators in TMEM -> register epilogue.
+// with fp32 accumulators in TMEM -> epilogue through registers and per-warp shared-memory slabs (tiled TMA stores /
+// reduce-adds where a warp's 32 rows are whole, masked vector stores at the ragged end of a group).
 //
 // One kernel covers every matrix product of the model; it is configured at run time:
 //   mode 0 ("row-grouped"): C[r, :] = A[r, :] . B[g(r)]   for rows r packed by group
@@ -8,7 +9,7 @@
 //        end; those rows are computed and discarded by the masked epilogue.
 //   mode 1 ("reduction-grouped", weight gradients): C[g] (+)= A[rows of g]^T . B[rows of g].
 //        The last 64-row block of a group is zeroed in shared memory past the group's end
-//        before the tensor core reads it.
+//        before the tensor core reads it (in both CTAs' stages when the product runs on a CTA pair).
 // Operands are bf16, K-major (rows of K) or MN-major (rows of M/N); see sm100.cuh.
 // A second (A2, B2) operand pair extends the reduction (dX = dG.Wg^T + dU.Wu^T in one pass).
 //
@@ -20,8 +21,9 @@
 //
 // What bounds it (measured with the trace / debug switches below): shared memory is filled at about 85 bytes per
 // clock per SM whatever the number of producer warps, so a 128 x 256 x 64 k-block (48 KB) takes ~560 cycles to
-// load against 512 cycles of tensor-core time; pairs cut the bytes per CTA to 32 KB. Short-K products are bound
-// by the epilogue and the per-tile hand-shakes instead.
+// load against 512 cycles of tensor-core time; pairs cut the bytes per CTA to 32 KB. Short-K products (K of a few
+// hundred, outputs as large as the inputs) are bound by DRAM once their operands are cold: with everything resident
+// in L2 the expert down projection takes 27 us on the chip, 60 us after an L2 flush.
 //
 // Replaces the reference's torch._grouped_mm call sites (nestor/backbones/grouped_mm.py:83,
 // :417-450; nestor/backbones/nestor.py:6337, :6367) and their Triton pointwise companions.
