@@ -12,6 +12,8 @@
 // scores are folded back with the softmax scale when dQ / dK are stored.
 // The same shared-memory tile serves as a K-major operand of the score products and as an
 // MN-major operand of the accumulate products, so every tile is fetched once.
+// The MMA warp issues the score products of tile it + 1 as soon as the softmax warps have read tile it's scores out
+// of TMEM, and the accumulate products of tile it when its dS / P^T tiles are written: the two chains overlap.
 #include "sm100.cuh"
 #include "flash.h"
 

@@ -6,8 +6,9 @@
 // segment up to the diagonal:
 //     S  = Q K^T            tcgen05.mma, K-major operands, fp32 in TMEM (double-buffered)
 //     P  = exp2(S*c - m)    softmax warps: one thread per q row, online max / sum
-//     O += P V              tcgen05.mma, A = P (bf16, written to swizzled smem), B = V (MN-major)
-//     O += P V             accumulated in TMEM (see the kernel's comment on the lazy rescale)
+//     O += P V              tcgen05.mma, B = V (MN-major); A = P in bf16, handed over through tensor memory
+//                           (tcgen05.st, A operand read from TMEM) for head dims <= 64, else through a swizzled
+//                           shared-memory tile; O stays in TMEM and is rescaled lazily (see the kernel)
 // Heads are `hd` wide (any multiple of 8 up to 128); tiles are zero-extended to a multiple
 // of 16 by TMA out-of-bounds fill (the tensor map's innermost extent is `hd`).
 // Tiles start at the segment's first row, so a q or kv tile may run past the segment end;
