@@ -152,6 +152,7 @@ class BlockSpec:
     loss_free: bool
     bias_rate: float
     token_dispatch: bool
+    dense_shared: int = 0        # always-on SwiGLU experts of the bank's width beside the routed bank (unit gate)
 
     @property
     def inner(self) -> int:
@@ -265,8 +266,9 @@ class NestorConfig(BackboneConfig):
             raise ValueError("mlp_auto_dense_ratio / attention_auto_head_split are unsupported.")
         if self.block_layer_num_experts is not None:
             raise ValueError("block_layer_num_experts is unsupported.")
-        if any(_per_block(self.router_num_dense_shared_experts, n, "router_num_dense_shared_experts")):
-            raise ValueError("router_num_dense_shared_experts is unsupported.")
+        dense_shared = _per_block(self.router_num_dense_shared_experts, n, "router_num_dense_shared_experts")
+        if any(int(v) < 0 for v in dense_shared):
+            raise ValueError("router_num_dense_shared_experts must be >= 0.")
         acts = _per_block(self.block_mlp_activations, n, "block_mlp_activations")
         if any(a != "swiglu" for a in acts):
             raise ValueError("Only SwiGLU expert MLPs are supported (block_mlp_activations='swiglu').")
@@ -310,8 +312,8 @@ class NestorConfig(BackboneConfig):
             if pool:
                 if P[i] < 0:
                     raise ValueError(f"block {i}: block_expert_pool_public_experts must be >= 0.")
-                if epg[i] != 1 or shared[i] != 1:
-                    raise ValueError(f"block {i}: the hybrid pool replaces the bank (bank experts must be 1).")
+                if epg[i] != 1 or shared[i] != 1 or int(dense_shared[i]) != 0:
+                    raise ValueError(f"block {i}: the hybrid pool replaces the bank (bank experts must be 1, no dense shared experts).")
                 # P == 0 is the private-only pool: no public experts, no public router, no path gate
                 if not ((P[i] == 0 or 1 <= kp[i] <= P[i]) and 1 <= kq[i] <= Q[i]):
                     raise ValueError(f"block {i}: pool top-k out of range.")
@@ -335,6 +337,7 @@ class NestorConfig(BackboneConfig):
                                                  active_budget=self.block_expert_pool_active_budget) if pool else 0,
                 private_gate=self.block_expert_pool_private_gate,
                 router_hidden=sh[i][0], loss_free=bool(lf[i]), bias_rate=float(br[i]), token_dispatch=bool(td[i]),
+                dense_shared=int(dense_shared[i]),
             ))
         return specs
 

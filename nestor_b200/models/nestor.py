@@ -205,6 +205,10 @@ class Layer(nn.Module):
                 self.shared_experts = nn.ModuleList([DenseExpert(s.dim, s.bank_width, init.matrix, init.output)])
             else:
                 self.stacked_moe_bank = ExpertBank(s.bank_experts, s.dim, s.bank_width, init.matrix, init.output)
+        # DeepSeekMoE-style always-on experts beside a routed bank: every token, unit gate, outside the router
+        # (reference nestor/backbones/nestor.py:4441-4451, 5290-5291)
+        self.dense_shared_experts = nn.ModuleList(
+            [DenseExpert(s.dim, s.bank_width, init.matrix, init.output) for _ in range(0 if s.pool else s.dense_shared)])
         self.dense_no_router = dense_no_router
 
     # -- weight views ---------------------------------------------------------------
@@ -290,7 +294,7 @@ class Layer(nn.Module):
         if self.shared_experts is not None:
             e = self.shared_experts[0]
             out = ops.dense_swiglu(n, W(self, e.layers[0].weight), W(self, e.gate.weight), W(self, e.layers[1].weight), cd)
-            return None, out, None, {}
+            return None, self._add_dense_shared(out, n, cd), None, {}
         scores = ops.router_scores(n, None, W(self, self.expert_router.score_mlp.layers[0].weight), cd)
         idx, gate = ops.route_topk(scores, self.expert_router.choice_bias, s.bank_top_k, "renorm")
         plan = ops.build_expert_plan(idx, s.bank_experts)
@@ -301,7 +305,12 @@ class Layer(nn.Module):
         aux = {"expert_idx": idx, "expert_router": {"scores": scores, "topk_indices": idx}}
         if not self.training and not torch.is_grad_enabled():
             aux["expert_prob"] = torch.softmax(scores.float(), dim=-1).sum(0)
-        return None, out, None, aux
+        return None, self._add_dense_shared(out, n, cd), None, aux
+
+    def _add_dense_shared(self, out: Tensor, n: Tensor, cd: torch.dtype) -> Tensor:
+        for e in self.dense_shared_experts:
+            out = out + ops.dense_swiglu(n, W(self, e.layers[0].weight), W(self, e.gate.weight), W(self, e.layers[1].weight), cd)
+        return out
 
 
 class LayerKVCache:

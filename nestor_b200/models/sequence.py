@@ -199,7 +199,7 @@ def apply_recipe_variants(model: nn.Module, mup: ReferenceMupConfig) -> None:
                 for bank in banks:
                     for w in (bank.w_up, bank.w_gate, bank.w_down):
                         adamw(w, matrix_lr_mul)
-                for expert in layer.shared_experts or []:
+                for expert in [*(layer.shared_experts or []), *layer.dense_shared_experts]:
                     for lin in (*expert.layers, expert.gate):
                         adamw(lin.weight, matrix_lr_mul)
             if layer.expert_router is not None:

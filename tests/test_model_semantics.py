@@ -460,3 +460,47 @@ def test_optimizer_recipe_variants_match_reference_groups(variant, tiny_scale, m
     assert set(got) == set(want)
     wrong = {n: (got[n], want[n]) for n in want if got[n] != want[n]}
     assert not wrong, dict(list(wrong.items())[:6])
+
+
+@pytest.mark.parametrize("family", ["moe", "dense"])
+def test_dense_shared_experts_match_reference(family, tiny_scale, monkeypatch):
+    """``router_num_dense_shared_experts = 1``: an always-on SwiGLU expert beside the routed bank (every token, unit gate).
+    Same state-dict keys, logits and gradients as the reference model configured the same way."""
+
+    import dataclasses as dc
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "nestor").is_dir():
+        pytest.skip("reference package not installed under baseline/_ref")
+    monkeypatch.setenv("NESTOR_STACKED_EXPERT_BANKS", "1")
+    monkeypatch.setenv("NESTOR_DENSE_NO_ROUTER", "1")
+    monkeypatch.syspath_prepend(str(ref_root))
+    try:
+        from nestor.experiments import pretrain as RP
+        from nestor.models import Model as RefModel
+    except Exception as exc:
+        pytest.skip(f"reference import failed: {exc}")
+    P = tiny_scale
+    monkeypatch.setitem(RP.SCALES, "tiny", RP.Scale("tiny", 128, 4, 8, 512, 10, 2, 1024))
+    monkeypatch.setattr(RP, "BLOCK_SIZE", 64)
+    for fam in ("dense", "moe", "nestor"):
+        monkeypatch.setitem(RP.BATCH_SHAPE, (fam, "tiny"), (2, 1))
+    torch.manual_seed(0)
+    rcfg = {"moe": RP._moe, "dense": RP._dense}[family]("tiny").jobs[0].model
+    rcfg = dc.replace(rcfg, backbone_config=dc.replace(rcfg.backbone_config, router_num_dense_shared_experts=1))
+    rm = RefModel.from_config(rcfg).eval()
+    cfg = P.build_experiment(family, "tiny").jobs[0].model
+    cfg = dc.replace(cfg, backbone_config=dc.replace(cfg.backbone_config, router_num_dense_shared_experts=1))
+    mm = Model.from_config(cfg).eval()
+    assert set(mm.state_dict()) == set(rm.state_dict())
+    assert any("dense_shared_experts.0" in k for k in mm.state_dict())
+    mm.load_state_dict(rm.state_dict(), strict=True)
+    ids = torch.randint(0, 100263, (2, 48))
+    lr = F.cross_entropy(rm(ids).pred[:, :-1].reshape(-1, 100263), ids[:, 1:].reshape(-1))
+    lm = F.cross_entropy(mm(ids).pred[:, :-1].reshape(-1, 100263), ids[:, 1:].reshape(-1))
+    assert torch.allclose(lr, lm, atol=1e-5)
+    lr.backward(); lm.backward()
+    ref_grads = dict(rm.named_parameters())
+    for n, p in mm.named_parameters():
+        g1, g2 = ref_grads[n].grad, p.grad
+        if g1 is not None and g2 is not None and g1.norm() > 1e-5:
+            assert (g1 - g2).norm() / g1.norm() < 2e-3, n
