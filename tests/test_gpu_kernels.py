@@ -285,8 +285,13 @@ def test_fused_ops_match_oracle_forward_and_backward():
         assert _rel(a.grad, b.grad) < 2e-2, a.shape
 
 
-@pytest.mark.parametrize("family", ["nestor", "moe", "dense"])
-def test_whole_model_kernels_vs_oracle_with_pinned_routing(family, tiny_scale, monkeypatch):
+@pytest.mark.parametrize("family,variant", [
+    ("nestor", {}), ("moe", {}), ("dense", {}),
+    ("moe", {"router_num_dense_shared_experts": 1}),          # an always-on expert beside the routed bank
+    ("nestor", {"block_expert_pool_public_experts": 0}),      # private-only pools: no public path, no path gate
+])
+def test_whole_model_kernels_vs_oracle_with_pinned_routing(family, variant, tiny_scale, monkeypatch):
+    import dataclasses as dc
     from nestor_b200 import ops
     from nestor_b200.models import Model
     from nestor_b200.parallel.arena import ParamArena
@@ -295,7 +300,9 @@ def test_whole_model_kernels_vs_oracle_with_pinned_routing(family, tiny_scale, m
     monkeypatch.setitem(tiny_scale.NESTOR_LAYERS, "tiny", (1,) * 7)
     monkeypatch.setenv("DCLM_BLOCK_SIZE", "512")
     torch.manual_seed(1)
-    m = Model.from_config(tiny_scale.build_experiment(family, "tiny").jobs[0].model).cuda().eval()
+    cfg = tiny_scale.build_experiment(family, "tiny").jobs[0].model
+    cfg = dc.replace(cfg, backbone_config=dc.replace(cfg.backbone_config, **variant))
+    m = Model.from_config(cfg).cuda().eval()
     with torch.no_grad():
         for name, p in m.named_parameters():
             if "query" in name:
