@@ -153,6 +153,8 @@ class BlockSpec:
     bias_rate: float
     token_dispatch: bool
     dense_shared: int = 0        # always-on SwiGLU experts of the bank's width beside the routed bank (unit gate)
+    columns: bool = True         # column mode: the block tracks per-column streams and exports their deviations
+    column_layers: int | None = None   # column mode: only this many trailing layers track streams (None = all)
 
     @property
     def inner(self) -> int:
@@ -160,9 +162,17 @@ class BlockSpec:
 
     @property
     def exports(self) -> int:
-        """Depth sources this block exports in column mode (k deviations + aggregate)."""
+        """Depth sources this block exports in column mode (k deviations + aggregate; one for a merged block)."""
 
-        return self.k + 1 if self.k > 1 else 1
+        return self.k + 1 if self.k > 1 and self.columns else 1
+
+    @property
+    def merged_prefix(self) -> int:
+        """Leading layers of a column block that run the merged recurrence (0 unless ``column_layers`` narrows it)."""
+
+        if not self.columns or self.column_layers is None or self.column_layers >= self.layers:
+            return 0
+        return self.layers - self.column_layers
 
 
 def _per_block(value: Any, n: int, name: str) -> list[Any]:
@@ -259,9 +269,25 @@ class NestorConfig(BackboneConfig):
                     "attn_res_column is built for the head-only read with aggregate and deviation "
                     "exports (block_column_head_only/include_aggregate/deviation_sources all True)."
                 )
-            if (self.block_column_mass_lambda is not None or self.block_column_head_query_per_source
-                    or self.block_column_blocks is not None or self.block_column_trailing_layers is not None):
-                raise ValueError("block_column_{mass_lambda,head_query_per_source,blocks,trailing_layers} are unsupported.")
+        else:
+            for name in ("block_column_head_query_per_source", "block_column_blocks", "block_column_trailing_layers"):
+                if getattr(self, name) not in (None, False):
+                    raise ValueError(f"{name} configures column-mode blocks: it needs block_residual_mode='attn_res_column'.")
+        if self.block_column_mass_lambda is not None:
+            # one unit of init mass per multi-column block: 1 - lambda on its aggregate, lambda / k on each column
+            if not 0.0 <= self.block_column_mass_lambda <= 1.0:
+                raise ValueError("block_column_mass_lambda must lie in [0, 1].")
+            if not self.block_column_include_aggregate:
+                raise ValueError("block_column_mass_lambda needs block_column_include_aggregate=True.")
+            if self.block_column_gain_init != 1.0:
+                raise ValueError("block_column_mass_lambda and a non-default block_column_gain_init both set the column gains; set one.")
+        if self.block_column_trailing_layers is not None and self.block_column_trailing_layers < 1:
+            raise ValueError("block_column_trailing_layers must be at least 1 (drop the block from block_column_blocks instead).")
+        if self.block_column_blocks is not None:
+            if not self.block_column_blocks:
+                raise ValueError("block_column_blocks is empty: that is plain attn_res_kimi, set that mode instead.")
+            if any(not 0 <= b < n for b in self.block_column_blocks):
+                raise ValueError(f"block_column_blocks {self.block_column_blocks} has an index outside [0, {n}).")
         if self.mlp_auto_dense_ratio is not None or self.attention_auto_head_split:
             raise ValueError("mlp_auto_dense_ratio / attention_auto_head_split are unsupported.")
         if self.block_layer_num_experts is not None:
@@ -322,8 +348,7 @@ class NestorConfig(BackboneConfig):
                     raise ValueError(f"block {i}: only shared expert banks are supported (experts_per_group == shared).")
                 if not 1 <= etop[i] <= epg[i]:
                     raise ValueError(f"block {i}: bank top-k out of range.")
-            if self.block_residual_mode == "attn_res_kimi" and G[i] != 1:
-                raise ValueError("attn_res_kimi blocks are single-column (num_groups == 1).")
+            keeps = self.column_mode and (self.block_column_blocks is None or i in self.block_column_blocks)
             specs.append(BlockSpec(
                 index=i, dim=self.input_dim, layers=layers[i], G=G[i], k=k[i], heads=heads[i],
                 head_dim=hd[i], rope_base=float(rope[i]), pool=pool,
@@ -338,6 +363,7 @@ class NestorConfig(BackboneConfig):
                 private_gate=self.block_expert_pool_private_gate,
                 router_hidden=sh[i][0], loss_free=bool(lf[i]), bias_rate=float(br[i]), token_dispatch=bool(td[i]),
                 dense_shared=int(dense_shared[i]),
+                columns=keeps, column_layers=self.block_column_trailing_layers if keeps else None,
             ))
         return specs
 

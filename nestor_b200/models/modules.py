@@ -62,12 +62,18 @@ class Norm(nn.Module):
 
 
 class DepthRead(nn.Module):
-    """Pseudo-query ``[d]`` (zero-init) and per-slot value gains ``[max_sources]`` (one-init)."""
+    """Pseudo-query ``[d]`` (zero-init) and per-slot value gains ``[max_sources]`` (one-init).
 
-    def __init__(self, dim: int, max_sources: int, eps: float = 1e-6) -> None:
+    ``per_source_queries`` gives every slot its own query row (``[max_sources, d]``, still zero-init, so the first
+    mixture stays uniform): source ``i`` is scored by ``q_i . k_i`` instead of the shared ``q . k_i``
+    (reference ``nestor/backbones/attention_residual.py:448-480``)."""
+
+    def __init__(self, dim: int, max_sources: int, eps: float = 1e-6, per_source_queries: bool = False) -> None:
         super().__init__()
         self.dim, self.max_sources, self.eps = dim, max_sources, eps
-        self.query = tag(nn.Parameter(torch.zeros(dim)), ADAMW_NO_DECAY)
+        self.per_source_queries = per_source_queries
+        self.query = tag(nn.Parameter(torch.zeros(max_sources, dim) if per_source_queries else torch.zeros(dim)),
+                         ADAMW_NO_DECAY)
         self.value_gains = tag(nn.Parameter(torch.ones(max_sources)), ADAMW_NO_DECAY)
 
 

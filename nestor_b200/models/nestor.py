@@ -474,6 +474,17 @@ class Block(nn.Module):
         streams: Tensor | None = None      # [T, k, d] fp32
         running: Tensor | None = None      # [T, d] fp32 = mean_j streams
         layer_aux = []
+        # Merged recurrence (one stream, the gate-weighted sum over a token's columns): every layer of a multi-column
+        # block that keeps no per-column streams ('attn_res_kimi', or a block left out of block_column_blocks), and
+        # the leading layers of a column block narrowed by block_column_trailing_layers.
+        merged_all = s.k > 1 and not (column_mode and s.columns)
+        n_merged = len(self.layers) if merged_all else (s.merged_prefix if column_mode else 0)
+        prefix: Tensor | None = None
+        if n_merged:
+            prefix, layer_aux = self._merged_layers(n_merged, sources, ctx, cd, cache, key_cache)
+            if merged_all:
+                return [prefix], prefix, self._block_aux(idx, layer_aux)
+            running = prefix
         rung = RecomputeLadder.current(self.training and cache is None)
         kc = {} if key_cache is None or rung.any else {"key_cache": key_cache}   # scales of the completed sources, shared by all reads
         nsrc = len(sources)
@@ -491,7 +502,12 @@ class Block(nn.Module):
             return layer.experts(n, ctx if c is None else ctx.rows(*c), cd)
 
         def one_layer(layer, li, streams, running, *srcs):
-            read = list(srcs) if running is None else [*srcs, running]
+            if prefix is None:
+                read = list(srcs) if running is None else [*srcs, running]
+            else:
+                # behind a merged prefix the attention half reads the mean of the tracked window alone, the expert half
+                # the whole running aggregate (reference nestor/backbones/nestor.py:7455-7470, 7855-7866)
+                read = list(srcs) if streams is None else [*srcs, streams.mean(dim=1)]
             attn = rung.region("half", attn_half, layer, li, *read)
             mid = ops.mid_source(running, attn)
             chunks = rung.expert_chunks(mid.shape[0]) if cache is None else None
@@ -513,15 +529,29 @@ class Block(nn.Module):
             return streams, running, aux
 
         for li, layer in enumerate(self.layers):
+            if li < n_merged:
+                continue
             streams, running, aux = rung.region("layer", one_layer, layer, li, streams, running, *sources)
             layer_aux.append(aux)
         assert len(sources) == nsrc
         if column_mode and s.k > 1:
             dev, agg = ops.block_exit(streams)
+            if prefix is not None:
+                # deviations are re-based on the window's own mean (they still sum to zero); the aggregate carries
+                # the merged prefix as well
+                agg = prefix + agg
             exports = [*dev.unbind(dim=0), agg]
         else:
             agg = streams.mean(dim=1) if s.k > 1 else streams[:, 0]
             exports = [agg]
+            if prefix is not None:
+                # a single-column block exports its tracked window; the next block's router sees prefix + window
+                # (reference nestor/backbones/nestor.py:9466-9474)
+                agg = prefix + agg
+        return exports, agg, self._block_aux(idx, layer_aux)
+
+    def _block_aux(self, idx: Tensor, layer_aux: list) -> dict:
+        s = self.spec
         baux = {"group_idx": idx, "layers": layer_aux}
         scores = self.__dict__.pop("_last_scores", None)
         if s.G > 1 and scores is not None:
@@ -529,7 +559,44 @@ class Block(nn.Module):
             baux["group_router"] = {"scores": scores, "topk_indices": idx}
         if not self.training and not torch.is_grad_enabled() and s.G > 1:
             baux["group_prob"] = self.__dict__.pop("_last_group_prob", None)
-        return exports, agg, baux
+        return baux
+
+    @staticmethod
+    def _merged_expert_update(priv: Tensor | None, shared: Tensor, path: Tensor | None, cd: torch.dtype) -> Tensor:
+        """One ``[T, d]`` fp32 update from an expert half: path-weighted public + path-weighted sum of the private slots
+        (weights absent for banks, dense layers and the private-only pool)."""
+
+        if path is not None:
+            update = (path[:, 0:1].float() * shared.float()).to(cd).float()
+            if priv is not None:
+                update = update + (path[:, 1:2].float() * priv.float().sum(dim=1)).to(cd).float()
+            return update
+        update = shared.float()
+        return update if priv is None else update + priv.float().sum(dim=1)
+
+    def _merged_layers(self, count: int, sources: list[Tensor], ctx: "BlockContext", cd: torch.dtype,
+                       cache: list | None, key_cache: Any) -> tuple[Tensor, list]:
+        """The first ``count`` layers as the merged recurrence: every sublayer reads the completed sources plus the
+        running sum ``partial`` of this block's updates, and adds its update, summed over the token's columns, to it
+        (reference ``nestor/backbones/nestor.py:7005-7034``). Returns ``(partial [T, d] fp32, per-layer aux)``."""
+
+        rung = RecomputeLadder.current(self.training and cache is None)
+        kc = {} if key_cache is None or rung.any else {"key_cache": key_cache}
+        partial: Tensor | None = None
+        layer_aux = []
+        for li, layer in enumerate(self.layers[:count]):
+            read = list(sources) if partial is None else [*sources, partial]
+            n = ops.depth_read_norm(read, layer.kimi_attn_read.query, layer.kimi_attn_read.value_gains,
+                                    layer.attn_norm.weight, layer.kimi_attn_read.eps, layer.attn_norm.eps, cd, **kc)
+            attn = layer.attention(n, ctx, cd) if cache is None else layer.attention_step(n, ctx, cd, cache[li])
+            update = layer.drop(attn.float().sum(dim=1), ctx.B)
+            partial = update if partial is None else partial + update
+            n = ops.depth_read_norm([*sources, partial], layer.kimi_mlp_read.query, layer.kimi_mlp_read.value_gains,
+                                    layer.mlp_norm.weight, layer.kimi_mlp_read.eps, layer.mlp_norm.eps, cd, **kc)
+            priv, shared, path, aux = layer.experts(n, ctx, cd)
+            partial = partial + layer.drop(self._merged_expert_update(priv, shared, path, cd), ctx.B)
+            layer_aux.append(aux)
+        return partial, layer_aux
 
 
     def _apply_residual(self, x: Tensor, update: Tensor) -> Tensor:
@@ -549,13 +616,7 @@ class Block(nn.Module):
             x = self._apply_residual(x, layer.drop(attn.float().sum(dim=1), ctx.B))
             n = ops.rmsnorm(x, layer.mlp_norm.weight, layer.mlp_norm.eps, cd)
             priv, shared, path, aux = layer.experts(n, ctx, cd)
-            if path is not None:
-                update = (path[:, 0:1].float() * shared.float()).to(cd).float()
-                if priv is not None:
-                    update = update + (path[:, 1:2].float() * priv.float().sum(dim=1)).to(cd).float()
-            else:
-                update = shared.float()
-            x = self._apply_residual(x, layer.drop(update, ctx.B))
+            x = self._apply_residual(x, layer.drop(self._merged_expert_update(priv, shared, path, cd), ctx.B))
             layer_aux.append(aux)
         baux = {"group_idx": idx, "layers": layer_aux}
         scores = self.__dict__.pop("_last_scores", None)
@@ -586,7 +647,8 @@ class Nestor(Backbone):
             [Block(s, init, self.max_depth_sources, dense_no_router, self.depth_reads, residual, rates[i])
              for i, s in enumerate(self.specs)])
         if self.depth_reads:
-            self.final_depth_read = DepthRead(config.output_dim, self.max_depth_sources)
+            self.final_depth_read = DepthRead(config.output_dim, self.max_depth_sources,
+                                              per_source_queries=config.block_column_head_query_per_source)
         # 'attn_res': plain residual blocks joined by a per-source key/value mixture of the block outputs so far
         self.block_attention_residuals: nn.ModuleList | None = None
         if config.block_residual_mode == "attn_res":
@@ -594,15 +656,21 @@ class Nestor(Backbone):
             self.block_attention_residuals = nn.ModuleList(
                 [BlockAttentionResidual([d] * (b + 1 + emb), d, std=1.0 / math.sqrt(d)) for b in range(len(self.specs))])
         self.final_norm = Norm(config.output_dim, init.norm_eps)
-        if self.depth_reads and self.column_mode and config.block_column_gain_init != 1.0:
-            # Head-read gains: deviation slots of every multi-column block start at the
-            # configured value (0 for the registered cells); embedding and aggregates stay 1.
+        lam = config.block_column_mass_lambda
+        if self.depth_reads and self.column_mode and (config.block_column_gain_init != 1.0 or lam is not None):
+            # Head-read gains: deviation slots of every multi-column block start at the configured value (0 for the
+            # registered cells); embedding, aggregates and merged blocks stay 1. With block_column_mass_lambda each
+            # multi-column block holds one unit of init mass instead: lambda / k per column, 1 - lambda on the
+            # aggregate (reference nestor/backbones/nestor.py:10106-10145).
             g = torch.ones(self.max_depth_sources)
             slot = 1
             for s in self.specs:
-                if s.k > 1:
-                    g[slot : slot + s.k] = config.block_column_gain_init
+                if s.k > 1 and s.columns:
+                    g[slot : slot + s.k] = config.block_column_gain_init if lam is None else lam / s.k
+                    if lam is not None:
+                        g[slot + s.k] = 1.0 - lam
                 slot += s.exports
+            assert slot == self.max_depth_sources
             with torch.no_grad():
                 self.final_depth_read.value_gains.copy_(g)
 
@@ -634,9 +702,8 @@ class Nestor(Backbone):
             narrow, wide, x, aux = [x0], [x0], x0, []
             for block, bcache in zip(self.blocks, cache.blocks):
                 exports, x, a = block(x, narrow, B, 1, cd, pos, self.column_mode, None, cache=bcache)
-                x = exports[-1]
                 wide.extend(exports)
-                narrow = [*narrow, x]
+                narrow = [*narrow, exports[-1]]
                 if self.block_attention_residuals is not None:
                     x = self._mix_block_outputs(len(aux), narrow)
                 aux.append(a)
@@ -688,12 +755,14 @@ class Nestor(Backbone):
                 exports, x, a = checkpoint(block, x, narrow, B, S, cd, pos, self.column_mode, noise, use_reentrant=False)
             else:
                 exports, x, a = block(x, narrow, B, S, cd, pos, self.column_mode, noise, key_cache=key_cache)
+            same = x is exports[-1]
             exports = [ops.grad_sink(e) for e in exports]
-            x = exports[-1]      # the aggregate is the block's last export
+            if same:
+                x = exports[-1]      # the aggregate is the block's last export
             wide.extend(exports)
-            narrow = [*narrow, x]
+            narrow = [*narrow, exports[-1]]
             if key_cache is not None:
-                key_cache.extend([x])
+                key_cache.extend([exports[-1]])
             if self.block_attention_residuals is not None:
                 x = self._mix_block_outputs(i, narrow)
             aux.append(a)

@@ -647,6 +647,10 @@ def depth_read_norm(sources, query, gains, gamma, eps_read, eps_norm, out_dtype,
     # (a key cache is accepted and ignored: the kernel derives every source's scale inside its one pass)
     if out_dtype != BF16:
         raise RuntimeError("the fused depth-read kernel writes bf16; run full-precision evaluation under ops.oracle_ops()")
+    if query.dim() == 2:
+        # one query row per source: the fused kernel scores every source with one shared vector
+        _oracle_path("depth_read_norm", "per-source queries")
+        return ref.depth_read_norm(sources, query, gains, gamma, eps_read, eps_norm, out_dtype)
     return _DepthReadNorm.apply(query, gains, gamma, float(eps_read), float(eps_norm), *sources)
 
 

@@ -191,7 +191,8 @@ def depth_read(sources: list[Tensor], query: Tensor, gains: Tensor, eps: float =
 
     ``r_i = rsqrt(mean(s_i^2) + eps)``, ``z_i = r_i (s_i . q) / sqrt(d)``,
     ``w = softmax_i(z) * gain_i``, ``out = sum_i (w_i r_i) s_i``. Sources are ``[..., d]``. ``key_cache`` supplies the
-    scales of the leading sources (which must be the very tensors it holds).
+    scales of the leading sources (which must be the very tensors it holds). A two-dimensional ``query [n_max, d]``
+    scores source ``i`` with its own row ``q_i``.
     """
 
     d = sources[0].shape[-1]
@@ -209,7 +210,7 @@ def depth_read(sources: list[Tensor], query: Tensor, gains: Tensor, eps: float =
         s32 = s.float()
         ri = cached[i] if i < len(cached) else torch.rsqrt(s32.pow(2).mean(dim=-1) + eps)
         r.append(ri)
-        z.append(ri * (s32 @ q))
+        z.append(ri * (s32 @ (q if q.dim() == 1 else q[i])))
     r_all = torch.stack(r, dim=-1)
     w = torch.softmax(torch.stack(z, dim=-1) / math.sqrt(d), dim=-1) * gains[:n].float()
     alpha = w * r_all

@@ -30,6 +30,34 @@ def test_stepwise_decode_matches_full_forward(family, tiny_scale):
     assert int(counts.sum()) == B * S * blk.spec.k and int(counts.max()) <= S
 
 
+def test_stepwise_decode_through_merged_blocks_and_trailing_windows(tiny_scale):
+    """Blocks left out of ``block_column_blocks`` (merged recurrence) and blocks whose leading layers are merged
+    (``block_column_trailing_layers``) decode token by token to the same logits as the full forward."""
+
+    import dataclasses as dc
+    from nestor_b200.models import Model
+    torch.manual_seed(2)
+    cfg = tiny_scale.build_experiment("nestor", "tiny").jobs[0].model
+    cfg = dc.replace(cfg, backbone_config=dc.replace(cfg.backbone_config, block_column_blocks=[0, 3],
+                                                     block_column_trailing_layers=1,
+                                                     block_column_head_query_per_source=True))
+    m = Model.from_config(cfg).eval()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if "query" in n:
+                p.normal_(0, 0.5)
+            if "value_gains" in n:
+                p.uniform_(0.5, 1.5)
+    B, S = 2, 16
+    ids = torch.randint(0, 100263, (B, S))
+    with torch.no_grad():
+        full = m(ids).pred.float()
+    cache = m.init_kv_cache(B, S)
+    for t in range(S):
+        step = m.decode_step(ids[:, t], cache)
+        assert torch.allclose(step, full[:, t], atol=2e-4, rtol=1e-4), (t, (step - full[:, t]).abs().max())
+
+
 def test_generate_is_greedy_continuation(tiny_scale):
     from nestor_b200.models import Model
     torch.manual_seed(1)

@@ -504,3 +504,84 @@ def test_dense_shared_experts_match_reference(family, tiny_scale, monkeypatch):
         g1, g2 = ref_grads[n].grad, p.grad
         if g1 is not None and g2 is not None and g1.norm() > 1e-5:
             assert (g1 - g2).norm() / g1.norm() < 2e-3, n
+
+
+_COLUMN_VARIANTS = {
+    # one unit of init mass per multi-column block, split between its aggregate and its columns
+    "mass_lambda": dict(block_column_mass_lambda=0.3, block_column_gain_init=1.0),
+    # one query row per source on the final head read
+    "head_queries": dict(block_column_head_query_per_source=True),
+    # only blocks 1, 2 and 6 keep per-column streams; the others run the merged recurrence and export one source
+    "blocks": dict(block_column_blocks=[1, 2, 6]),
+    # only the last layer of a block tracks streams: blocks 0 and 6 (two layers) get a merged first layer
+    "trailing": dict(block_column_trailing_layers=1),
+    "blocks_and_trailing": dict(block_column_blocks=[0, 3], block_column_trailing_layers=1, block_column_mass_lambda=0.5,
+                                block_column_gain_init=1.0),
+    # the merged recurrence for every block: depth reads over one export per block, multi-column routing inside
+    "kimi_multi_column": dict(block_residual_mode="attn_res_kimi", block_column_head_only=False,
+                              block_column_include_aggregate=False, block_column_deviation_sources=False,
+                              block_column_gain_init=1.0),
+}
+
+
+@pytest.mark.parametrize("variant", list(_COLUMN_VARIANTS))
+def test_column_mode_variants_match_reference(variant, tiny_scale, monkeypatch):
+    """The column-mode knobs beyond the registered cells (``block_column_mass_lambda``,
+    ``block_column_head_query_per_source``, ``block_column_blocks``, ``block_column_trailing_layers``) and multi-column
+    blocks under ``attn_res_kimi``: same state-dict keys and initial gains, same logits, same gradients as the
+    reference model configured the same way (reference nestor/backbones/nestor.py:2276-2338, 9382-9520, 10106-10164)."""
+
+    import dataclasses as dc
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "nestor").is_dir():
+        pytest.skip("reference package not installed under baseline/_ref")
+    monkeypatch.setenv("NESTOR_STACKED_EXPERT_BANKS", "1")
+    monkeypatch.setenv("NESTOR_DENSE_NO_ROUTER", "1")
+    # the reference threads a block's running aggregate through every column layer on this path
+    monkeypatch.setenv("NESTOR_COLUMN_SLOT_UPDATES", "1")
+    monkeypatch.syspath_prepend(str(ref_root))
+    try:
+        from nestor.experiments import pretrain as RP
+        from nestor.models import Model as RefModel
+    except Exception as exc:
+        pytest.skip(f"reference import failed: {exc}")
+    P = tiny_scale
+    monkeypatch.setitem(RP.SCALES, "tiny", RP.Scale("tiny", 128, 4, 8, 512, 10, 2, 1024))
+    monkeypatch.setitem(RP.NESTOR_LAYERS, "tiny", (2, 1, 1, 1, 1, 1, 2))
+    monkeypatch.setitem(RP.NESTOR_PRIVATE_EXPERTS, "tiny", 3)
+    monkeypatch.setattr(RP, "NESTOR_MIN_PRIVATE_WIDTH", 24)
+    monkeypatch.setattr(RP, "BLOCK_SIZE", 64)
+    for fam in ("dense", "moe", "nestor"):
+        monkeypatch.setitem(RP.BATCH_SHAPE, (fam, "tiny"), (2, 1))
+    changes = _COLUMN_VARIANTS[variant]
+    torch.manual_seed(0)
+    rcfg = RP._nestor("tiny").jobs[0].model
+    rcfg = dc.replace(rcfg, backbone_config=dc.replace(rcfg.backbone_config, **changes))
+    rm = RefModel.from_config(rcfg).eval()
+    cfg = P.build_experiment("nestor", "tiny").jobs[0].model
+    cfg = dc.replace(cfg, backbone_config=dc.replace(cfg.backbone_config, **changes))
+    mm = Model.from_config(cfg).eval()
+    ref_state = rm.state_dict()
+    assert set(mm.state_dict()) == set(ref_state)
+    assert all(mm.state_dict()[k].shape == v.shape for k, v in ref_state.items())
+    # the initial head-read gains follow the same slot layout
+    key = "backbone.final_depth_read.value_gains"
+    assert torch.equal(mm.state_dict()[key], ref_state[key])
+    with torch.no_grad():
+        for n, p in rm.named_parameters():
+            if "query" in n:
+                p.normal_(0, 0.5)
+    mm.load_state_dict(rm.state_dict(), strict=True)
+    ids = torch.randint(0, 100263, (2, 64))
+    lr = F.cross_entropy(rm(ids).pred[:, :-1].reshape(-1, 100263), ids[:, 1:].reshape(-1))
+    lm = F.cross_entropy(mm(ids).pred[:, :-1].reshape(-1, 100263), ids[:, 1:].reshape(-1))
+    assert torch.allclose(lr, lm, atol=1e-5), (float(lr), float(lm))
+    lr.backward(); lm.backward()
+    ref_grads = dict(rm.named_parameters())
+    checked = 0
+    for n, p in mm.named_parameters():
+        g1, g2 = ref_grads[n].grad, p.grad
+        if g1 is not None and g2 is not None and g1.norm() > 1e-5:
+            assert (g1 - g2).norm() / g1.norm() < 2e-3, n
+            checked += 1
+    assert checked > 50
