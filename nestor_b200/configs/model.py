@@ -153,8 +153,12 @@ class BlockSpec:
     bias_rate: float
     token_dispatch: bool
     dense_shared: int = 0        # always-on SwiGLU experts of the bank's width beside the routed bank (unit gate)
-    columns: bool = True         # column mode: the block tracks per-column streams and exports their deviations
+    columns: bool = True         # column mode: the block tracks per-column streams and exports them
     column_layers: int | None = None   # column mode: only this many trailing layers track streams (None = all)
+    column_aggregate: bool = True      # column mode, k > 1: the mean of the streams is a further export
+    column_deviation: bool = True      # column mode, k > 1: columns are exported / read as ``s_j - mean``
+    column_head_only: bool = True      # column mode: sublayer reads see one aggregate per block; only the head read
+                                       # sees the columns (False: every read sees every column)
 
     @property
     def inner(self) -> int:
@@ -162,9 +166,10 @@ class BlockSpec:
 
     @property
     def exports(self) -> int:
-        """Depth sources this block exports in column mode (k deviations + aggregate; one for a merged block)."""
+        """Depth sources this block exports in column mode (k columns + the aggregate if it is exported; one for a
+        merged or single-column block)."""
 
-        return self.k + 1 if self.k > 1 and self.columns else 1
+        return self.k + int(self.column_aggregate) if self.k > 1 and self.columns else 1
 
     @property
     def merged_prefix(self) -> int:
@@ -263,16 +268,23 @@ class NestorConfig(BackboneConfig):
         if self.residual_mode != "convex":
             raise ValueError("residual_mode must be 'convex' (the additive rule comes with the reference-muP config).")
         if self.block_residual_mode == "attn_res_column":
-            if not (self.block_column_head_only and self.block_column_include_aggregate
-                    and self.block_column_deviation_sources):
-                raise ValueError(
-                    "attn_res_column is built for the head-only read with aggregate and deviation "
-                    "exports (block_column_head_only/include_aggregate/deviation_sources all True)."
-                )
+            # the narrow sublayer reads are made of the aggregates, and deviations are relative to them
+            if self.block_column_head_only and not self.block_column_include_aggregate:
+                raise ValueError("block_column_head_only requires block_column_include_aggregate=True.")
+            if self.block_column_deviation_sources and not self.block_column_include_aggregate:
+                raise ValueError("block_column_deviation_sources requires block_column_include_aggregate=True.")
+            if all(v <= 1 for v in _per_block(self.num_groups_per_token, n, "num_groups_per_token")):
+                raise ValueError("attn_res_column needs a block with num_groups_per_token > 1; with one column per "
+                                 "block everywhere it is 'attn_res_kimi', set that mode instead.")
         else:
-            for name in ("block_column_head_query_per_source", "block_column_blocks", "block_column_trailing_layers"):
+            for name in ("block_column_head_query_per_source", "block_column_blocks", "block_column_trailing_layers",
+                         "block_column_head_only", "block_column_include_aggregate", "block_column_deviation_sources"):
                 if getattr(self, name) not in (None, False):
                     raise ValueError(f"{name} configures column-mode blocks: it needs block_residual_mode='attn_res_column'.")
+            if self.block_column_gain_init != 1.0:
+                raise ValueError("block_column_gain_init scales column sources: it needs block_residual_mode='attn_res_column'.")
+        if self.block_column_gain_init < 0.0:
+            raise ValueError("block_column_gain_init must be non-negative.")
         if self.block_column_mass_lambda is not None:
             # one unit of init mass per multi-column block: 1 - lambda on its aggregate, lambda / k on each column
             if not 0.0 <= self.block_column_mass_lambda <= 1.0:
@@ -288,8 +300,8 @@ class NestorConfig(BackboneConfig):
                 raise ValueError("block_column_blocks is empty: that is plain attn_res_kimi, set that mode instead.")
             if any(not 0 <= b < n for b in self.block_column_blocks):
                 raise ValueError(f"block_column_blocks {self.block_column_blocks} has an index outside [0, {n}).")
-        if self.mlp_auto_dense_ratio is not None or self.attention_auto_head_split:
-            raise ValueError("mlp_auto_dense_ratio / attention_auto_head_split are unsupported.")
+        if self.mlp_auto_dense_ratio is not None and self.mlp_auto_dense_ratio <= 0:
+            raise ValueError("mlp_auto_dense_ratio must be positive.")
         if self.block_layer_num_experts is not None:
             raise ValueError("block_layer_num_experts is unsupported.")
         dense_shared = _per_block(self.router_num_dense_shared_experts, n, "router_num_dense_shared_experts")
@@ -305,11 +317,19 @@ class NestorConfig(BackboneConfig):
         heads = _per_block(self.block_num_heads, n, "block_num_heads")
         hd = _per_block(self.block_head_dims, n, "block_head_dims")
         rope = _per_block(self.block_rope_bases, n, "block_rope_bases")
+        if self.attention_auto_head_split:
+            # a block's full head budget d / head_dim split over a token's k columns, so the active attention
+            # compute matches a dense block at any k (reference nestor/backbones/nestor.py:2609-2622)
+            heads = [max(1, round((self.feature_dims[i] // hd[i]) / k[i])) for i in range(n)]
         hid = self.block_mlp_hidden_dims
         hid = [list(h) for h in hid] if hid and isinstance(hid[0], (list, tuple)) else [list(hid)] * n
         epg = _per_block(self.router_num_experts_per_group, n, "router_num_experts_per_group")
         shared = _per_block(self.router_num_shared_experts, n, "router_num_shared_experts")
         etop = _per_block(self.router_num_experts_per_group_per_token, n, "router_num_experts_per_group_per_token")
+        if self.mlp_auto_dense_ratio is not None:
+            # fine-grained experts: width = ratio * d / top_k, so the active expert FLOPs equal a dense (ratio x)
+            # feed-forward at any top_k (reference nestor/backbones/nestor.py:2672-2690)
+            hid = [[max(1, round(self.mlp_auto_dense_ratio * self.feature_dims[i] / etop[i]))] for i in range(n)]
         sh = self.router_score_mlp_hidden_dims
         sh = [list(h) for h in sh] if sh and isinstance(sh[0], (list, tuple)) else [list(sh)] * n
         nh = self.router_noise_mlp_hidden_dims
@@ -364,6 +384,9 @@ class NestorConfig(BackboneConfig):
                 router_hidden=sh[i][0], loss_free=bool(lf[i]), bias_rate=float(br[i]), token_dispatch=bool(td[i]),
                 dense_shared=int(dense_shared[i]),
                 columns=keeps, column_layers=self.block_column_trailing_layers if keeps else None,
+                column_aggregate=self.block_column_include_aggregate and k[i] > 1,
+                column_deviation=self.block_column_deviation_sources and k[i] > 1,
+                column_head_only=self.block_column_head_only,
             ))
         return specs
 

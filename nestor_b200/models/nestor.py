@@ -471,6 +471,8 @@ class Block(nn.Module):
         ctx = BlockContext(B, S, idx, gates, plan, pos)
         if not self.depth_reads:
             return self._forward_projection(x, ctx, cd, cache, idx)
+        if column_mode and s.columns and not s.column_head_only:
+            return self._forward_wide_reads(sources, ctx, cd, cache, key_cache, idx)
         streams: Tensor | None = None      # [T, k, d] fp32
         running: Tensor | None = None      # [T, d] fp32 = mean_j streams
         layer_aux = []
@@ -540,7 +542,7 @@ class Block(nn.Module):
                 # deviations are re-based on the window's own mean (they still sum to zero); the aggregate carries
                 # the merged prefix as well
                 agg = prefix + agg
-            exports = [*dev.unbind(dim=0), agg]
+            exports = [*(dev.unbind(dim=0) if s.column_deviation else streams.unbind(dim=1)), agg]
         else:
             agg = streams.mean(dim=1) if s.k > 1 else streams[:, 0]
             exports = [agg]
@@ -548,6 +550,63 @@ class Block(nn.Module):
                 # a single-column block exports its tracked window; the next block's router sees prefix + window
                 # (reference nestor/backbones/nestor.py:9466-9474)
                 agg = prefix + agg
+        return exports, agg, self._block_aux(idx, layer_aux)
+
+    def _live_sources(self, streams: Tensor) -> list[Tensor]:
+        """This block's entries of a column-resolved read / its exports: the ``k`` streams (as deviations from their
+        mean if the model re-bases them), then the mean if it is exported; a single-column block is its one stream
+        (reference ``nestor/backbones/nestor.py:860-909``)."""
+
+        s = self.spec
+        if s.k == 1:
+            return [streams[:, 0]]
+        agg = streams.mean(dim=1)
+        cols = streams - agg.unsqueeze(1) if s.column_deviation else streams
+        return [*cols.unbind(dim=1), *([agg] if s.column_aggregate else [])]
+
+    def _forward_wide_reads(self, sources: list[Tensor], ctx: "BlockContext", cd: torch.dtype, cache: list | None,
+                            key_cache: Any, idx: Tensor) -> tuple[list[Tensor], Tensor, dict]:
+        """Column mode whose sublayer reads are column-resolved (``block_column_head_only=False``): ``sources`` holds
+        every export of the completed blocks, and each read appends this block's live streams to them
+        (reference ``nestor/backbones/nestor.py:7172-7254``, ``7301-7318``). A merged prefix
+        (``block_column_trailing_layers``) only enters the aggregate handed to the next block's router. The per-layer
+        recompute regions are not applied here; block-level recomputation wraps the whole block as usual."""
+
+        s = self.spec
+        rung = RecomputeLadder.current(self.training and cache is None)
+        kc = {} if key_cache is None or rung.any else {"key_cache": key_cache}
+        layer_aux: list = []
+        prefix: Tensor | None = None
+        n_merged = s.merged_prefix
+        if n_merged:
+            prefix, layer_aux = self._merged_layers(n_merged, sources, ctx, cd, cache, key_cache)
+        streams: Tensor | None = None
+        running: Tensor | None = None
+        for li, layer in enumerate(self.layers):
+            if li < n_merged:
+                continue
+            read = list(sources) if streams is None else [*sources, *self._live_sources(streams)]
+            n = ops.depth_read_norm(read, layer.kimi_attn_read.query, layer.kimi_attn_read.value_gains,
+                                    layer.attn_norm.weight, layer.kimi_attn_read.eps, layer.attn_norm.eps, cd, **kc)
+            attn = layer.attention(n, ctx, cd) if cache is None else layer.attention_step(n, ctx, cd, cache[li])
+            if layer.drop_path > 0.0 and self.training:
+                attn = layer.drop(attn, ctx.B)
+            mid = attn.float() if streams is None else streams + attn.float()
+            n = ops.depth_read_norm([*sources, *self._live_sources(mid)], layer.kimi_mlp_read.query,
+                                    layer.kimi_mlp_read.value_gains, layer.mlp_norm.weight, layer.kimi_mlp_read.eps,
+                                    layer.mlp_norm.eps, cd, **kc)
+            priv, shared, path, aux = layer.experts(n, ctx, cd)
+            if layer.drop_path > 0.0 and self.training:
+                shared = layer.drop(shared, ctx.B)
+                priv = None if priv is None else layer.drop(priv, ctx.B)
+            streams, running = ops.layer_combine(attn, priv, shared, path, streams, running, cd)
+            layer_aux.append(aux)
+        exports = self._live_sources(streams)
+        agg = exports[-1] if (s.k == 1 or s.column_aggregate) else streams.mean(dim=1)
+        if prefix is not None:
+            agg = prefix + agg
+            if s.k > 1 and s.column_aggregate:
+                exports[-1] = agg
         return exports, agg, self._block_aux(idx, layer_aux)
 
     def _block_aux(self, idx: Tensor, layer_aux: list) -> dict:
@@ -634,6 +693,8 @@ class Nestor(Backbone):
         self.config = config
         self.specs = config.resolve()
         self.column_mode = config.column_mode
+        # column mode with column-resolved sublayer reads: blocks read every export so far, not one aggregate per block
+        self.wide_reads = config.column_mode and not config.block_column_head_only
         self.max_depth_sources = config.max_depth_sources()
         total_layers = sum(s.layers for s in self.specs)
         init = InitScales(mup, config.input_dim, total_layers)
@@ -668,11 +729,16 @@ class Nestor(Backbone):
                 if s.k > 1 and s.columns:
                     g[slot : slot + s.k] = config.block_column_gain_init if lam is None else lam / s.k
                     if lam is not None:
-                        g[slot + s.k] = 1.0 - lam
+                        g[slot + s.k] = 1.0 - lam      # (the aggregate slot exists: resolve() requires it with lambda)
                 slot += s.exports
             assert slot == self.max_depth_sources
+            # narrow sublayer reads keep their unit init (their slot 1 is an aggregate, not a column); column-resolved
+            # sublayer reads share the head read's positional layout, each slicing its prefix
+            reads = [self.final_depth_read] if config.block_column_head_only else \
+                [m for m in self.modules() if isinstance(m, DepthRead)]
             with torch.no_grad():
-                self.final_depth_read.value_gains.copy_(g)
+                for m in reads:
+                    m.value_gains.copy_(g)
 
     @property
     def output_dim(self) -> int:
@@ -701,7 +767,8 @@ class Nestor(Backbone):
         with ops.oracle_ops():        # per-token work: the PyTorch statement of the ops on any device
             narrow, wide, x, aux = [x0], [x0], x0, []
             for block, bcache in zip(self.blocks, cache.blocks):
-                exports, x, a = block(x, narrow, B, 1, cd, pos, self.column_mode, None, cache=bcache)
+                exports, x, a = block(x, list(wide) if self.wide_reads else narrow, B, 1, cd, pos, self.column_mode, None,
+                                      cache=bcache)
                 wide.extend(exports)
                 narrow = [*narrow, exports[-1]]
                 if self.block_attention_residuals is not None:
@@ -746,15 +813,16 @@ class Nestor(Backbone):
         key_cache = None
         if (self.depth_reads and not recompute and not ops.use_kernels(x0)
                 and os.environ.get("NESTOR_NO_DEPTH_KEY_CACHE") != "1"):
-            key_cache = ops.DepthKeyCache(narrow, eps=self.final_depth_read.eps)
+            key_cache = ops.DepthKeyCache(wide if self.wide_reads else narrow, eps=self.final_depth_read.eps)
         self.last_key_cache = key_cache
         for i, block in enumerate(self.blocks):
             noise = None if noises is None else noises[i]
+            reads = list(wide) if self.wide_reads else narrow     # (a snapshot: ``wide`` grows in place below)
             if rung.outer:
                 from torch.utils.checkpoint import checkpoint
-                exports, x, a = checkpoint(block, x, narrow, B, S, cd, pos, self.column_mode, noise, use_reentrant=False)
+                exports, x, a = checkpoint(block, x, reads, B, S, cd, pos, self.column_mode, noise, use_reentrant=False)
             else:
-                exports, x, a = block(x, narrow, B, S, cd, pos, self.column_mode, noise, key_cache=key_cache)
+                exports, x, a = block(x, reads, B, S, cd, pos, self.column_mode, noise, key_cache=key_cache)
             same = x is exports[-1]
             exports = [ops.grad_sink(e) for e in exports]
             if same:
@@ -762,7 +830,7 @@ class Nestor(Backbone):
             wide.extend(exports)
             narrow = [*narrow, exports[-1]]
             if key_cache is not None:
-                key_cache.extend([exports[-1]])
+                key_cache.extend(exports if self.wide_reads else [exports[-1]])
             if self.block_attention_residuals is not None:
                 x = self._mix_block_outputs(i, narrow)
             aux.append(a)

@@ -30,9 +30,11 @@ def test_stepwise_decode_matches_full_forward(family, tiny_scale):
     assert int(counts.sum()) == B * S * blk.spec.k and int(counts.max()) <= S
 
 
-def test_stepwise_decode_through_merged_blocks_and_trailing_windows(tiny_scale):
+@pytest.mark.parametrize("head_only", [True, False])
+def test_stepwise_decode_through_merged_blocks_and_trailing_windows(head_only, tiny_scale):
     """Blocks left out of ``block_column_blocks`` (merged recurrence) and blocks whose leading layers are merged
-    (``block_column_trailing_layers``) decode token by token to the same logits as the full forward."""
+    (``block_column_trailing_layers``) decode token by token to the same logits as the full forward, with narrow
+    and with column-resolved sublayer reads."""
 
     import dataclasses as dc
     from nestor_b200.models import Model
@@ -40,6 +42,7 @@ def test_stepwise_decode_through_merged_blocks_and_trailing_windows(tiny_scale):
     cfg = tiny_scale.build_experiment("nestor", "tiny").jobs[0].model
     cfg = dc.replace(cfg, backbone_config=dc.replace(cfg.backbone_config, block_column_blocks=[0, 3],
                                                      block_column_trailing_layers=1,
+                                                     block_column_head_only=head_only,
                                                      block_column_head_query_per_source=True))
     m = Model.from_config(cfg).eval()
     with torch.no_grad():

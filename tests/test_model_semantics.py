@@ -517,6 +517,17 @@ _COLUMN_VARIANTS = {
     "trailing": dict(block_column_trailing_layers=1),
     "blocks_and_trailing": dict(block_column_blocks=[0, 3], block_column_trailing_layers=1, block_column_mass_lambda=0.5,
                                 block_column_gain_init=1.0),
+    # column-resolved sublayer reads (every read sees every column), with and without the aggregate / re-basing
+    "wide_raw": dict(block_column_head_only=False, block_column_include_aggregate=False,
+                     block_column_deviation_sources=False, block_column_gain_init=1.0),
+    "wide_aggregate": dict(block_column_head_only=False, block_column_deviation_sources=False,
+                           block_column_gain_init=0.5),
+    "wide_deviation": dict(block_column_head_only=False, block_column_gain_init=0.25),
+    "wide_deviation_subset": dict(block_column_head_only=False, block_column_blocks=[0, 2, 5],
+                                  block_column_trailing_layers=1, block_column_mass_lambda=0.4,
+                                  block_column_gain_init=1.0),
+    # narrow sublayer reads, raw columns (not deviations) on the head read
+    "head_only_raw": dict(block_column_deviation_sources=False),
     # the merged recurrence for every block: depth reads over one export per block, multi-column routing inside
     "kimi_multi_column": dict(block_residual_mode="attn_res_kimi", block_column_head_only=False,
                               block_column_include_aggregate=False, block_column_deviation_sources=False,
@@ -564,9 +575,10 @@ def test_column_mode_variants_match_reference(variant, tiny_scale, monkeypatch):
     ref_state = rm.state_dict()
     assert set(mm.state_dict()) == set(ref_state)
     assert all(mm.state_dict()[k].shape == v.shape for k, v in ref_state.items())
-    # the initial head-read gains follow the same slot layout
-    key = "backbone.final_depth_read.value_gains"
-    assert torch.equal(mm.state_dict()[key], ref_state[key])
+    # the initial gains of every read follow the same slot layout
+    for key in ref_state:
+        if key.endswith("value_gains"):
+            assert torch.equal(mm.state_dict()[key], ref_state[key]), key
     with torch.no_grad():
         for n, p in rm.named_parameters():
             if "query" in n:

@@ -8,6 +8,8 @@ against fixtures captured from the reference implementation on the meta device.
 import json
 from pathlib import Path
 
+ROOT = Path(__file__).resolve().parent.parent
+
 import pytest
 import torch
 
@@ -153,3 +155,42 @@ def test_analytic_flops_agree_with_flop_counter(family, tiny_scale):
     assert cal["counted"] > 0 and abs(cal["ratio"] - 1.0) < 0.06, cal
     assert grouped_mm_flops(10, 4, 6) == 480
     register_extra_flop_formulas(); register_extra_flop_formulas()      # idempotent
+
+
+def test_auto_head_split_and_dense_ratio_follow_the_reference(tiny_scale, monkeypatch):
+    """``attention_auto_head_split`` and ``mlp_auto_dense_ratio`` derive the same per-block head counts and expert
+    widths as the reference's config expansion (reference nestor/backbones/nestor.py:2609-2690)."""
+
+    import dataclasses as dc
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "nestor").is_dir():
+        pytest.skip("reference package not installed under baseline/_ref")
+    monkeypatch.syspath_prepend(str(ref_root))
+    try:
+        from nestor.experiments import pretrain as RP
+    except Exception as exc:
+        pytest.skip(f"reference import failed: {exc}")
+    P = tiny_scale
+    monkeypatch.setitem(RP.SCALES, "tiny", RP.Scale("tiny", 128, 4, 8, 512, 10, 2, 1024))
+    monkeypatch.setitem(RP.NESTOR_LAYERS, "tiny", (2, 1, 1, 1, 1, 1, 2))
+    monkeypatch.setitem(RP.NESTOR_PRIVATE_EXPERTS, "tiny", 3)
+    monkeypatch.setattr(RP, "NESTOR_MIN_PRIVATE_WIDTH", 24)
+    monkeypatch.setattr(RP, "BLOCK_SIZE", 64)
+    for fam in ("dense", "moe", "nestor"):
+        monkeypatch.setitem(RP.BATCH_SHAPE, (fam, "tiny"), (2, 1))
+    changes = dict(attention_auto_head_split=True, mlp_auto_dense_ratio=2.5)
+    resolved = {}
+    for fam, ref_build in (("nestor", RP._nestor), ("moe", RP._moe)):
+        rcfg = ref_build("tiny").jobs[0].model.backbone_config
+        ref_blocks = dc.replace(rcfg, **changes).to_dict()["block_configs"]
+        ours = dc.replace(P.build_experiment(fam, "tiny").jobs[0].model.backbone_config, **changes).resolve()
+        assert len(ours) == len(ref_blocks)
+        for s, r in zip(ours, ref_blocks):
+            assert s.heads == r["block_num_heads"]
+            assert [s.bank_width] == list(r["block_mlp_hidden_dims"])
+        resolved[fam] = ours
+    # the derived values replace the configured ones
+    base = P.build_experiment("nestor", "tiny").jobs[0].model.backbone_config
+    odd = dc.replace(base, block_num_heads=1, block_mlp_hidden_dims=[8], **changes).resolve()
+    assert [s.heads for s in odd] == [s.heads for s in resolved["nestor"]]
+    assert [s.bank_width for s in odd] == [s.bank_width for s in resolved["nestor"]]
