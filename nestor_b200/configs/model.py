@@ -153,6 +153,8 @@ class BlockSpec:
     bias_rate: float
     token_dispatch: bool
     dense_shared: int = 0        # always-on SwiGLU experts of the bank's width beside the routed bank (unit gate)
+    layer_experts: tuple[int, ...] | None = None   # bank size per layer (None: ``bank_experts`` everywhere)
+    activation: str = "swiglu"   # bank / dense experts: 'swiglu' (gated) or a pointwise 'relu' / 'gelu' / 'silu' / 'tanh'
     columns: bool = True         # column mode: the block tracks per-column streams and exports them
     column_layers: int | None = None   # column mode: only this many trailing layers track streams (None = all)
     column_aggregate: bool = True      # column mode, k > 1: the mean of the streams is a further export
@@ -163,6 +165,11 @@ class BlockSpec:
     @property
     def inner(self) -> int:
         return self.heads * self.head_dim
+
+    def experts_of_layer(self, layer: int) -> int:
+        """Routed experts in the bank of layer ``layer`` of this block."""
+
+        return self.bank_experts if self.layer_experts is None else self.layer_experts[layer]
 
     @property
     def exports(self) -> int:
@@ -302,14 +309,21 @@ class NestorConfig(BackboneConfig):
                 raise ValueError(f"block_column_blocks {self.block_column_blocks} has an index outside [0, {n}).")
         if self.mlp_auto_dense_ratio is not None and self.mlp_auto_dense_ratio <= 0:
             raise ValueError("mlp_auto_dense_ratio must be positive.")
-        if self.block_layer_num_experts is not None:
-            raise ValueError("block_layer_num_experts is unsupported.")
+        schedule = self.block_layer_num_experts
+        if schedule is not None:
+            # depth-varying bank sizes: one count per layer of every block, same top-k and width everywhere
+            # (reference nestor/backbones/nestor.py:2131-2141, 2785-2812)
+            if len(schedule) != n:
+                raise ValueError("block_layer_num_experts must have one entry per block.")
+            schedule = [[int(e) for e in row] for row in schedule]
+            if any(e < 1 for row in schedule for e in row):
+                raise ValueError("block_layer_num_experts entries must be >= 1.")
         dense_shared = _per_block(self.router_num_dense_shared_experts, n, "router_num_dense_shared_experts")
         if any(int(v) < 0 for v in dense_shared):
             raise ValueError("router_num_dense_shared_experts must be >= 0.")
         acts = _per_block(self.block_mlp_activations, n, "block_mlp_activations")
-        if any(a != "swiglu" for a in acts):
-            raise ValueError("Only SwiGLU expert MLPs are supported (block_mlp_activations='swiglu').")
+        if any(a not in ("swiglu", "relu", "gelu", "silu", "tanh") for a in acts):
+            raise ValueError("block_mlp_activations must be 'swiglu' or one of 'relu', 'gelu', 'silu', 'tanh'.")
 
         layers = _per_block(self.block_num_layers, n, "block_num_layers")
         G = _per_block(self.num_groups, n, "num_groups")
@@ -324,6 +338,12 @@ class NestorConfig(BackboneConfig):
         hid = self.block_mlp_hidden_dims
         hid = [list(h) for h in hid] if hid and isinstance(hid[0], (list, tuple)) else [list(hid)] * n
         epg = _per_block(self.router_num_experts_per_group, n, "router_num_experts_per_group")
+        if schedule is not None:
+            for i, row in enumerate(schedule):
+                if len(row) != layers[i]:
+                    raise ValueError(f"block_layer_num_experts[{i}] must have block_num_layers ({layers[i]}) entries, "
+                                     f"got {len(row)}.")
+            epg = [max(row) for row in schedule]
         shared = _per_block(self.router_num_shared_experts, n, "router_num_shared_experts")
         etop = _per_block(self.router_num_experts_per_group_per_token, n, "router_num_experts_per_group_per_token")
         if self.mlp_auto_dense_ratio is not None:
@@ -351,7 +371,7 @@ class NestorConfig(BackboneConfig):
             if hd[i] % 2:
                 raise ValueError(f"block {i}: RoPE needs an even head_dim.")
             if len(hid[i]) != 1:
-                raise ValueError(f"block {i}: SwiGLU experts take exactly one hidden width.")
+                raise ValueError(f"block {i}: expert MLPs take exactly one hidden width.")
             if len(sh[i]) != 1 or len(nh[i]) != 1 or sh[i] != nh[i]:
                 raise ValueError(f"block {i}: group-router score/noise MLPs need one equal hidden width.")
             pool = Q[i] > 0
@@ -364,9 +384,15 @@ class NestorConfig(BackboneConfig):
                 if not ((P[i] == 0 or 1 <= kp[i] <= P[i]) and 1 <= kq[i] <= Q[i]):
                     raise ValueError(f"block {i}: pool top-k out of range.")
             else:
-                if epg[i] != shared[i]:
-                    raise ValueError(f"block {i}: only shared expert banks are supported (experts_per_group == shared).")
-                if not 1 <= etop[i] <= epg[i]:
+                fewest = epg[i] if schedule is None else min(schedule[i])
+                if G[i] > 1 and (fewest != shared[i] or epg[i] != shared[i]):
+                    # with one column the column-specific experts of a bank are plain further experts; with several
+                    # they would be one bank per column
+                    raise ValueError(f"block {i}: with several columns only shared expert banks are supported "
+                                     "(experts_per_group == shared in every layer).")
+                if not 0 <= shared[i] <= fewest:
+                    raise ValueError(f"block {i}: router_num_shared_experts must be in [0, fewest experts of a layer].")
+                if not 1 <= etop[i] <= fewest:
                     raise ValueError(f"block {i}: bank top-k out of range.")
             keeps = self.column_mode and (self.block_column_blocks is None or i in self.block_column_blocks)
             specs.append(BlockSpec(
@@ -383,6 +409,8 @@ class NestorConfig(BackboneConfig):
                 private_gate=self.block_expert_pool_private_gate,
                 router_hidden=sh[i][0], loss_free=bool(lf[i]), bias_rate=float(br[i]), token_dispatch=bool(td[i]),
                 dense_shared=int(dense_shared[i]),
+                layer_experts=None if pool or schedule is None else tuple(schedule[i]),
+                activation="swiglu" if pool else acts[i],      # pool experts are always SwiGLU
                 columns=keeps, column_layers=self.block_column_trailing_layers if keeps else None,
                 column_aggregate=self.block_column_include_aggregate and k[i] > 1,
                 column_deviation=self.block_column_deviation_sources and k[i] > 1,

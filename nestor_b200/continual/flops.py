@@ -49,7 +49,7 @@ def backbone_body_flops(backbone: NestorConfig, *, seq_len: int, causal: bool = 
         p = 8.0 * seq_len * s.dim * s.inner * s.k
         c = s.G * (2.0 if causal else 4.0) * members ** 2 * s.inner
         active = (s.k_p * s.h_pub + s.k * s.k_q * s.h_priv) if s.pool else (s.bank_top_k + s.dense_shared) * s.bank_width
-        m = 6.0 * seq_len * s.dim * active
+        m = (6.0 if s.activation == "swiglu" else 4.0) * seq_len * s.dim * active     # three matrices gated, two pointwise
         proj += s.layers * p
         core += s.layers * c
         mlp += s.layers * m

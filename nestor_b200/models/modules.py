@@ -148,31 +148,41 @@ class ExpertBank(nn.Module):
     """Stacked SwiGLU bank: ``w_up, w_gate [E, d, h]`` and ``w_down [E, h, d]``.
 
     Each ``[d_in, d_out]`` slice is the transpose of the per-expert ``nn.Linear`` weight the
-    unstacked layout stores, so Muon treats the bank as ``E`` independent matrices.
+    unstacked layout stores, so Muon treats the bank as ``E`` independent matrices. ``gated=False`` is the bank of
+    pointwise experts ``down(act(up(x)))``: no ``w_gate`` (reference ``nestor/backbones/expert_bank_stack.py:62-130``).
     """
 
-    def __init__(self, experts: int, dim: int, hidden: int, std: float, out_std: float) -> None:
+    def __init__(self, experts: int, dim: int, hidden: int, std: float, out_std: float, gated: bool = True) -> None:
         super().__init__()
-        self.num_experts, self.dim, self.hidden = experts, dim, hidden
+        self.num_experts, self.dim, self.hidden, self.gated = experts, dim, hidden, gated
         self.w_up = tag(nn.Parameter(torch.empty(experts, dim, hidden)), muon_matrix(hidden, dim))
-        self.w_gate = tag(nn.Parameter(torch.empty(experts, dim, hidden)), muon_matrix(hidden, dim))
+        self.w_gate = tag(nn.Parameter(torch.empty(experts, dim, hidden)), muon_matrix(hidden, dim)) if gated else None
         self.w_down = tag(nn.Parameter(torch.empty(experts, hidden, dim)), muon_matrix(dim, hidden))
         with torch.no_grad():
             self.w_up.normal_(0.0, std)
-            self.w_gate.normal_(0.0, std)
+            if gated:
+                self.w_gate.normal_(0.0, std)
             self.w_down.normal_(0.0, out_std)
+
+    def matrices(self) -> list[nn.Parameter]:
+        return [w for w in (self.w_up, self.w_gate, self.w_down) if w is not None]
 
 
 class DenseExpert(nn.Module):
-    """A lone SwiGLU (never stacked): ``layers.0`` = up ``[h, d]``, ``layers.1`` = down ``[d, h]``, ``gate [h, d]``."""
+    """A lone SwiGLU (never stacked): ``layers.0`` = up ``[h, d]``, ``layers.1`` = down ``[d, h]``, ``gate [h, d]``;
+    ``gated=False`` is the pointwise MLP ``down(act(up(x)))`` without the gate matrix."""
 
-    def __init__(self, dim: int, hidden: int, std: float, out_std: float) -> None:
+    def __init__(self, dim: int, hidden: int, std: float, out_std: float, gated: bool = True) -> None:
         super().__init__()
+        self.gated = gated
         self.layers = nn.ModuleList([
             Matrix(dim, hidden, muon_matrix(hidden, dim), std),
             Matrix(hidden, dim, muon_matrix(dim, hidden), out_std),
         ])
-        self.gate = Matrix(dim, hidden, muon_matrix(hidden, dim), std)
+        self.gate = Matrix(dim, hidden, muon_matrix(hidden, dim), std) if gated else None
+
+    def matrices(self) -> list[Matrix]:
+        return [*self.layers, *([self.gate] if self.gate is not None else [])]
 
 
 class BlockAttentionResidual(nn.Module):

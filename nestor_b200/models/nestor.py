@@ -177,9 +177,11 @@ class Layer(nn.Module):
     """One transformer layer (attention half + expert half) of a block."""
 
     def __init__(self, s: BlockSpec, init: InitScales, max_sources: int, dense_no_router: bool,
-                 depth_reads: bool = True, drop_path: float = 0.0) -> None:
+                 depth_reads: bool = True, drop_path: float = 0.0, bank_experts: int | None = None) -> None:
         super().__init__()
         self.spec = s
+        self.bank_experts = E = s.bank_experts if bank_experts is None else bank_experts   # this layer's bank size
+        gated = s.activation == "swiglu"      # pointwise activations: experts without a gate matrix
         self.attn_norm = Norm(s.dim, init.norm_eps)
         self.mlp_norm = Norm(s.dim, init.norm_eps)
         self.drop_path = float(os.environ.get("NESTOR_DROP_PATH_RATE") or drop_path)
@@ -196,19 +198,19 @@ class Layer(nn.Module):
             self.expert_pool = ExpertPool(s, init)
         else:
             self.expert_router = RouterParams(
-                s.dim, s.bank_experts, s.bank_top_k, std=init.router,
+                s.dim, E, s.bank_top_k, std=init.router,
                 loss_free=s.loss_free, bias_rate=s.bias_rate)
-            if s.bank_experts == 1:
+            if E == 1:
                 # A one-choice gate is the constant 1.0: the router can never receive a
                 # gradient, so it is frozen (and, with dense_no_router, skipped entirely).
                 self.expert_router.requires_grad_(False)
-                self.shared_experts = nn.ModuleList([DenseExpert(s.dim, s.bank_width, init.matrix, init.output)])
+                self.shared_experts = nn.ModuleList([DenseExpert(s.dim, s.bank_width, init.matrix, init.output, gated)])
             else:
-                self.stacked_moe_bank = ExpertBank(s.bank_experts, s.dim, s.bank_width, init.matrix, init.output)
+                self.stacked_moe_bank = ExpertBank(E, s.dim, s.bank_width, init.matrix, init.output, gated)
         # DeepSeekMoE-style always-on experts beside a routed bank: every token, unit gate, outside the router
         # (reference nestor/backbones/nestor.py:4441-4451, 5290-5291)
         self.dense_shared_experts = nn.ModuleList(
-            [DenseExpert(s.dim, s.bank_width, init.matrix, init.output) for _ in range(0 if s.pool else s.dense_shared)])
+            [DenseExpert(s.dim, s.bank_width, init.matrix, init.output, gated) for _ in range(0 if s.pool else s.dense_shared)])
         self.dense_no_router = dense_no_router
 
     # -- weight views ---------------------------------------------------------------
@@ -292,24 +294,32 @@ class Layer(nn.Module):
             public, private, path, aux = self.expert_pool(n, ctx.idx, ctx.gates, cd)
             return private, public, path, aux
         if self.shared_experts is not None:
-            e = self.shared_experts[0]
-            out = ops.dense_swiglu(n, W(self, e.layers[0].weight), W(self, e.gate.weight), W(self, e.layers[1].weight), cd)
-            return None, self._add_dense_shared(out, n, cd), None, {}
+            return None, self._add_dense_shared(self._dense_expert(self.shared_experts[0], n, cd), n, cd), None, {}
         scores = ops.router_scores(n, None, W(self, self.expert_router.score_mlp.layers[0].weight), cd)
         idx, gate = ops.route_topk(scores, self.expert_router.choice_bias, s.bank_top_k, "renorm")
-        plan = ops.build_expert_plan(idx, s.bank_experts)
+        plan = ops.build_expert_plan(idx, self.bank_experts)
         bank = self.stacked_moe_bank
         ones = torch.ones_like(gate, dtype=cd)
-        rows = ops.expert_bank(n, plan, ones, W(self, bank.w_up), W(self, bank.w_gate), W(self, bank.w_down), cd, group=1)
+        if bank.gated:
+            rows = ops.expert_bank(n, plan, ones, W(self, bank.w_up), W(self, bank.w_gate), W(self, bank.w_down), cd, group=1)
+        else:
+            rows = ops.expert_bank(n, plan, ones, W(self, bank.w_up), None, W(self, bank.w_down), cd, group=1,
+                                   activation=s.activation)
         out = (rows * gate.to(cd).float().unsqueeze(-1)).sum(dim=1).to(cd).float()
         aux = {"expert_idx": idx, "expert_router": {"scores": scores, "topk_indices": idx}}
         if not self.training and not torch.is_grad_enabled():
             aux["expert_prob"] = torch.softmax(scores.float(), dim=-1).sum(0)
         return None, self._add_dense_shared(out, n, cd), None, aux
 
+    def _dense_expert(self, e: DenseExpert, n: Tensor, cd: torch.dtype) -> Tensor:
+        if e.gated:
+            return ops.dense_swiglu(n, W(self, e.layers[0].weight), W(self, e.gate.weight), W(self, e.layers[1].weight), cd)
+        return ops.dense_swiglu(n, W(self, e.layers[0].weight), None, W(self, e.layers[1].weight), cd,
+                                activation=self.spec.activation)
+
     def _add_dense_shared(self, out: Tensor, n: Tensor, cd: torch.dtype) -> Tensor:
         for e in self.dense_shared_experts:
-            out = out + ops.dense_swiglu(n, W(self, e.layers[0].weight), W(self, e.gate.weight), W(self, e.layers[1].weight), cd)
+            out = out + self._dense_expert(e, n, cd)
         return out
 
 
@@ -430,8 +440,8 @@ class Block(nn.Module):
         if s.G == 1:
             self.group_router.requires_grad_(False)
         rates = drop_rates or [0.0] * s.layers
-        self.layers = nn.ModuleList([Layer(s, init, max_sources, dense_no_router, depth_reads, rates[i])
-                                     for i in range(s.layers)])
+        self.layers = nn.ModuleList([Layer(s, init, max_sources, dense_no_router, depth_reads, rates[i],
+                                           bank_experts=s.experts_of_layer(i)) for i in range(s.layers)])
 
     def route(self, x: Tensor, noise: Tensor | None, cd: torch.dtype) -> tuple[Tensor, Tensor]:
         """Group router on the block input ``[T, d]`` -> ``(idx [T, k], gates [T, k] fp32)``."""
@@ -950,7 +960,7 @@ def router_counts(backbone: Nestor, aux: dict) -> dict[str, Tensor]:
                 for g in range(s.G):
                     out[f"{base}.expert_pool.private_routers.{g}"] = per[g]
             elif "expert_idx" in laux:
-                out[f"{base}.expert_router"] = _count(laux["expert_idx"], s.bank_experts, valid)
+                out[f"{base}.expert_router"] = _count(laux["expert_idx"], layer.bank_experts, valid)
     return out
 
 

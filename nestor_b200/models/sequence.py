@@ -197,10 +197,10 @@ def apply_recipe_variants(model: nn.Module, mup: ReferenceMupConfig) -> None:
                 if layer.expert_pool is not None:
                     banks += [b for b in (layer.expert_pool.stacked_public, layer.expert_pool.stacked_private) if b is not None]
                 for bank in banks:
-                    for w in (bank.w_up, bank.w_gate, bank.w_down):
+                    for w in bank.matrices():
                         adamw(w, matrix_lr_mul)
                 for expert in [*(layer.shared_experts or []), *layer.dense_shared_experts]:
-                    for lin in (*expert.layers, expert.gate):
+                    for lin in expert.matrices():
                         adamw(lin.weight, matrix_lr_mul)
             if layer.expert_router is not None:
                 router(layer.expert_router)

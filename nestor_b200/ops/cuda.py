@@ -307,13 +307,19 @@ class _ExpertBank(torch.autograd.Function):
         return dx, dweights, d_up, d_gate, d_down, None, None
 
 
-def expert_bank(x, plan, weights, w_up, w_gate, w_down, cd, group):
+def expert_bank(x, plan, weights, w_up, w_gate, w_down, cd, group, activation="swiglu"):
+    if activation != "swiglu":
+        # the grouped GEMM's fused epilogue is the SwiGLU product; a pointwise bank runs the PyTorch statement
+        _oracle_path("expert_bank", f"pointwise activation {activation!r}")
+        return ref.expert_bank(x, plan, weights, w_up, None, w_down, cd, group, activation)
     return _ExpertBank.apply(x, weights, w_up, w_gate, w_down, plan, group)
 
 
-def dense_swiglu(x, w_up, w_gate, w_down, cd):
-    g = linear(x, w_gate)
+def dense_swiglu(x, w_up, w_gate, w_down, cd, activation="swiglu"):
     u = linear(x, w_up)
+    if activation != "swiglu":
+        return linear(ref.POINTWISE_ACTIVATIONS[activation](u), w_down).float()
+    g = linear(x, w_gate)
     return linear(torch.nn.functional.silu(g) * u, w_down).float()
 
 

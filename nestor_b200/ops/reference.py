@@ -463,16 +463,20 @@ def swiglu(gate: Tensor, up: Tensor) -> Tensor:
     return F.silu(gate) * up
 
 
+POINTWISE_ACTIVATIONS = {"relu": F.relu, "gelu": F.gelu, "silu": F.silu, "tanh": torch.tanh}
+
+
 def expert_bank(
-    x: Tensor, plan: ExpertPlan, weights: Tensor, w_up: Tensor, w_gate: Tensor, w_down: Tensor,
-    cd: torch.dtype, group: int,
+    x: Tensor, plan: ExpertPlan, weights: Tensor, w_up: Tensor, w_gate: Tensor | None, w_down: Tensor,
+    cd: torch.dtype, group: int, activation: str = "swiglu",
 ) -> Tensor:
     """Routed SwiGLU bank: ``[T, d] -> [T, slots/group, d]`` (fp32).
 
     Banks are stacked ``w_up, w_gate [E, d, h]``, ``w_down [E, h, d]``. Slot ``s`` of token
     ``t`` runs expert ``ids[t, s]``; the outputs of each run of ``group`` consecutive slots
     are summed with their ``weights [T, slots]`` (each product rounded to ``cd`` before
-    the fp32 sum).
+    the fp32 sum). A pointwise ``activation`` (``relu / gelu / silu / tanh``) takes no gate bank: the hidden row is
+    ``act(x @ w_up)``.
     """
 
     T, d = x.shape
@@ -482,18 +486,23 @@ def expert_bank(
     for e in range(plan.E):
         a, b = off[e], off[e + 1]
         if b > a:
-            h = swiglu(xs[a:b] @ w_gate[e].to(cd), xs[a:b] @ w_up[e].to(cd))
+            up = xs[a:b] @ w_up[e].to(cd)
+            h = swiglu(xs[a:b] @ w_gate[e].to(cd), up) if activation == "swiglu" else POINTWISE_ACTIVATIONS[activation](up)
             y[a:b] = h @ w_down[e].to(cd)
     per_slot = y[plan.inv.long()].view(T, plan.slots, d)
     weighted = (per_slot.float() * weights.float().unsqueeze(-1)).to(cd)
     return weighted.view(T, plan.slots // group, group, d).float().sum(dim=2)
 
 
-def dense_swiglu(x: Tensor, w_up: Tensor, w_gate: Tensor, w_down: Tensor, cd: torch.dtype) -> Tensor:
-    """One SwiGLU MLP with ``nn.Linear``-layout weights (``[h, d]``, ``[h, d]``, ``[d, h]``)."""
+def dense_swiglu(x: Tensor, w_up: Tensor, w_gate: Tensor | None, w_down: Tensor, cd: torch.dtype,
+                 activation: str = "swiglu") -> Tensor:
+    """One SwiGLU MLP with ``nn.Linear``-layout weights (``[h, d]``, ``[h, d]``, ``[d, h]``); with a pointwise
+    ``activation`` the MLP is ``act(x @ w_up^T) @ w_down^T`` and takes no gate."""
 
     h = x.to(cd)
-    return (swiglu(h @ w_gate.to(cd).t(), h @ w_up.to(cd).t()) @ w_down.to(cd).t()).float()
+    up = h @ w_up.to(cd).t()
+    hidden = swiglu(h @ w_gate.to(cd).t(), up) if activation == "swiglu" else POINTWISE_ACTIVATIONS[activation](up)
+    return (hidden @ w_down.to(cd).t()).float()
 
 
 # --------------------------------------------------------------------------------- head

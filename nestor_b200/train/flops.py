@@ -86,8 +86,10 @@ def forward_flops_per_token(config: SequenceModelConfig, seq_len: int) -> float:
     for s in bb.resolve():
         if s.G > 1:
             routers += 2 * 2.0 * (s.dim * s.router_hidden + s.router_hidden * s.G)   # score + noise MLPs, once per block
-        per_layer = (2.0 * s.dim * (s.P + s.G * s.Q + 2)) if s.pool else 2.0 * s.dim * s.bank_experts
-        routers += s.layers * per_layer
+        if s.pool:
+            routers += s.layers * 2.0 * s.dim * (s.P + s.G * s.Q + 2)
+        else:
+            routers += sum(2.0 * s.dim * s.experts_of_layer(i) for i in range(s.layers))
     head = 2.0 * bb.output_dim * config.head_config.vocab_size
     return body + routers + head
 

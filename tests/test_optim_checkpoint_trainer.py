@@ -220,3 +220,49 @@ def test_drop_mup_puts_every_parameter_in_one_adamw_group(tiny_scale, monkeypatc
     groups = build_param_groups(job.optimizer, m)
     assert len(groups) == 1 and groups[0]["method"] == "adamw" and groups[0]["lr"] == job.optimizer.lr_adamw
     assert sum(p.numel() for p in groups[0]["params"]) == sum(p.numel() for p in m.parameters() if p.requires_grad)
+
+
+_TRAIN_VARIANTS = {
+    # column-resolved sublayer reads, one block merged, per-source head queries, mass-conserving gains
+    "wide_reads": dict(block_column_head_only=False, block_column_blocks=[0], block_column_gain_init=1.0,
+                       block_column_mass_lambda=0.5, block_column_head_query_per_source=True),
+    # banks of pointwise experts whose size changes with depth, single-column blocks, merged depth reads
+    "pointwise_banks": dict(
+        block_residual_mode="attn_res_kimi", block_column_include_aggregate=False, block_column_gain_init=1.0,
+        block_column_head_only=False, block_column_deviation_sources=False, num_groups=[1, 1],
+        num_groups_per_token=[1, 1], block_num_layers=[2, 1], block_layer_num_experts=[[3, 5], [4]],
+        router_num_shared_experts=[2, 4], router_num_experts_per_group_per_token=[2, 2],
+        block_mlp_activations="gelu", block_mlp_hidden_dims=[[96]] * 2, router_num_dense_shared_experts=1,
+        block_expert_pool_public_experts=[0, 0], block_expert_pool_private_experts=[0, 0]),
+}
+
+
+@pytest.mark.parametrize("variant", list(_TRAIN_VARIANTS))
+def test_configuration_variants_train_and_checkpoint(variant, tmp_path, monkeypatch):
+    """Models outside the registered cells go through the whole pipeline on CPU: parameter arena, Muon + AdamW
+    groups, three optimizer steps with finite weights, balancing-bias updates, a checkpoint that holds the final state."""
+
+    import dataclasses as dc
+    data = write_synthetic_bin(tmp_path / "train.bin", 64 * 40, 100_277, doc_len_range=(16, 64))
+    monkeypatch.setenv("DCLM_DATA_PATH", str(data))
+    monkeypatch.setenv("NESTOR_OUTPUT_ROOT", str(tmp_path / "out"))
+    monkeypatch.setenv("DCLM_BLOCK_SIZE", "64")
+    monkeypatch.setenv("DCLM_MAX_STEPS", "3")
+    monkeypatch.setenv("DCLM_CKPT_FREQ", "3")
+    from nestor_b200.experiments.tiny import nestor_tiny
+    exp = nestor_tiny(); exp.name = f"nestor_tiny_{variant}"
+    job = exp.jobs[0]
+    job = dc.replace(job, model=dc.replace(job.model, backbone_config=dc.replace(
+        job.model.backbone_config, **_TRAIN_VARIANTS[variant])))
+    exp.jobs[0] = job
+    pipe = TrainPipeline.from_config(job_config=job, experiment_config=exp)
+    trainer = pipe.setup()
+    trainer.train()
+    assert trainer.global_step == 3
+    state = {k: v.detach().float().cpu().clone() for k, v in trainer.model.state_dict().items()}
+    assert all(torch.isfinite(v).all() for v in state.values() if v.is_floating_point())
+    pipe.ctx.close()
+    (ckpt,) = list((tmp_path / "out").glob("*/*/checkpoints/model_00000003.pt"))
+    payload = torch.load(ckpt, weights_only=False)
+    assert payload["step"] == 3 and set(payload["model"]) == set(state)
+    assert all(torch.allclose(payload["model"][k].float(), state[k]) for k in state if state[k].is_floating_point())
