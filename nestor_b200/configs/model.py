@@ -272,8 +272,12 @@ class NestorConfig(BackboneConfig):
                 "block_residual_mode must be 'projection', 'attn_res', 'attn_res_kimi' or 'attn_res_column', got "
                 f"{self.block_residual_mode!r}."
             )
-        if self.residual_mode != "convex":
-            raise ValueError("residual_mode must be 'convex' (the additive rule comes with the reference-muP config).")
+        if self.residual_mode not in ("convex", "attn_res"):
+            raise ValueError("residual_mode must be 'convex' or 'attn_res' ('attn_res_xblock' pools over all tokens: "
+                             "non-causal models only).")
+        if self.residual_mode == "attn_res" and self.block_residual_mode in ("attn_res_kimi", "attn_res_column"):
+            raise ValueError(f"block_residual_mode={self.block_residual_mode!r} replaces the within-block stream by "
+                             "its own recurrence: it requires residual_mode='convex'.")
         if self.block_residual_mode == "attn_res_column":
             # the narrow sublayer reads are made of the aggregates, and deviations are relative to them
             if self.block_column_head_only and not self.block_column_include_aggregate:
@@ -425,6 +429,13 @@ class NestorConfig(BackboneConfig):
     @property
     def column_mode(self) -> bool:
         return self.block_residual_mode == "attn_res_column"
+
+    @property
+    def history_attention(self) -> bool:
+        """``residual_mode='attn_res'``: inside a block every sublayer reads a softmax mixture of the block input and
+        all earlier sublayer updates instead of a residual stream."""
+
+        return self.residual_mode == "attn_res"
 
     @property
     def depth_reads(self) -> bool:

@@ -177,9 +177,18 @@ class Layer(nn.Module):
     """One transformer layer (attention half + expert half) of a block."""
 
     def __init__(self, s: BlockSpec, init: InitScales, max_sources: int, dense_no_router: bool,
-                 depth_reads: bool = True, drop_path: float = 0.0, bank_experts: int | None = None) -> None:
+                 depth_reads: bool = True, drop_path: float = 0.0, bank_experts: int | None = None,
+                 history_attention: bool = False) -> None:
         super().__init__()
         self.spec = s
+        if history_attention:
+            # residual_mode='attn_res': a zero-initialised pseudo-query and a gain-only key norm per sublayer
+            # (reference nestor/backbones/nestor.py:4282-4295)
+            from nestor_b200.models.scaling import ScaledLinear
+            self.attn_query = ScaledLinear(s.dim, 1, role="score", bias=False, zero_init=True)
+            self.attn_key_norm = Norm(s.dim, init.norm_eps)
+            self.mlp_query = ScaledLinear(s.dim, 1, role="score", bias=False, zero_init=True)
+            self.mlp_key_norm = Norm(s.dim, init.norm_eps)
         self.bank_experts = E = s.bank_experts if bank_experts is None else bank_experts   # this layer's bank size
         gated = s.activation == "swiglu"      # pointwise activations: experts without a gate matrix
         self.attn_norm = Norm(s.dim, init.norm_eps)
@@ -429,10 +438,18 @@ def _merge_chunk_aux(parts: list[dict]) -> dict:
 class Block(nn.Module):
     def __init__(self, s: BlockSpec, init: InitScales, max_sources: int, dense_no_router: bool,
                  depth_reads: bool = True, residual: tuple[str, float] = ("add", 1.0),
-                 drop_rates: list[float] | None = None) -> None:
+                 drop_rates: list[float] | None = None, history_attention: bool = False) -> None:
         super().__init__()
         self.spec = s
         self.depth_reads = depth_reads
+        self.history_attention = history_attention
+        if history_attention:
+            # the block output: one more read over the whole history, then an RMSNorm that restores unit scale (a
+            # uniform mixture of M updates has RMS ~ 1/sqrt(M)); reference nestor/backbones/nestor.py:8409-8419
+            from nestor_b200.models.scaling import ScaledLinear
+            self.out_query = ScaledLinear(s.dim, 1, role="score", bias=False, zero_init=True)
+            self.out_key_norm = Norm(s.dim, init.norm_eps)
+            self.out_norm = Norm(s.dim, init.norm_eps)
         self.residual = residual       # projection mode: ("add", m) -> x + m*u, ("convex", 1/D) -> (1 - 1/D) x + u/D
         self.group_router = RouterParams(
             s.dim, s.G, s.k, hidden=s.router_hidden, score_lr_mul=s.layers ** -0.5,
@@ -441,7 +458,8 @@ class Block(nn.Module):
             self.group_router.requires_grad_(False)
         rates = drop_rates or [0.0] * s.layers
         self.layers = nn.ModuleList([Layer(s, init, max_sources, dense_no_router, depth_reads, rates[i],
-                                           bank_experts=s.experts_of_layer(i)) for i in range(s.layers)])
+                                           bank_experts=s.experts_of_layer(i), history_attention=history_attention)
+                                     for i in range(s.layers)])
 
     def route(self, x: Tensor, noise: Tensor | None, cd: torch.dtype) -> tuple[Tensor, Tensor]:
         """Group router on the block input ``[T, d]`` -> ``(idx [T, k], gates [T, k] fp32)``."""
@@ -678,6 +696,8 @@ class Block(nn.Module):
         expert updates to one fp32 stream with the model's residual rule, a token's update being the gate-weighted
         sum over its columns (reference ``nestor/backbones/nestor.py:4746-4763``, ``:4918-4940``)."""
 
+        if self.history_attention:
+            return self._forward_history_attention(x, ctx, cd, cache, idx)
         layer_aux = []
         for li, layer in enumerate(self.layers):
             n = ops.rmsnorm(x, layer.attn_norm.weight, layer.attn_norm.eps, cd)
@@ -692,6 +712,36 @@ class Block(nn.Module):
         if self.spec.G > 1 and scores is not None:
             baux["group_router"] = {"scores": scores, "topk_indices": idx}
         return [x], x, baux
+
+
+    def _forward_history_attention(self, x: Tensor, ctx: "BlockContext", cd: torch.dtype, cache: list | None,
+                                   idx: Tensor) -> tuple[list[Tensor], Tensor, dict]:
+        """``residual_mode='attn_res'``: no residual stream inside the block. The history starts with the block input;
+        every sublayer reads a softmax mixture of the whole history, normalises it, and appends its update (summed
+        over the token's columns); the block output is one more read over the history followed by ``out_norm``
+        (reference ``nestor/backbones/nestor.py:6913-6950``, ``9547-9572``)."""
+
+        # (the history's inverse RMS uses the op's own 1e-6 floor, not the key norms' epsilon: the reference caches it
+        # with that default, nestor/backbones/nestor.py:3900-3914)
+        history = [x]
+        layer_aux = []
+        for li, layer in enumerate(self.layers):
+            h = ops.depth_attention(history, layer.attn_query.weight, layer.attn_key_norm.weight)
+            n = ops.rmsnorm(h, layer.attn_norm.weight, layer.attn_norm.eps, cd)
+            attn = layer.attention(n, ctx, cd) if cache is None else layer.attention_step(n, ctx, cd, cache[li])
+            history.append(layer.drop(attn.float().sum(dim=1), ctx.B))
+            h = ops.depth_attention(history, layer.mlp_query.weight, layer.mlp_key_norm.weight)
+            n = ops.rmsnorm(h, layer.mlp_norm.weight, layer.mlp_norm.eps, cd)
+            priv, shared, path, aux = layer.experts(n, ctx, cd)
+            history.append(layer.drop(self._merged_expert_update(priv, shared, path, cd), ctx.B))
+            layer_aux.append(aux)
+        out = ops.depth_attention(history, self.out_query.weight, self.out_key_norm.weight)
+        out = ops.rmsnorm(out, self.out_norm.weight, self.out_norm.eps, torch.float32)
+        baux = {"group_idx": idx, "layers": layer_aux}
+        scores = self.__dict__.pop("_last_scores", None)
+        if self.spec.G > 1 and scores is not None:
+            baux["group_router"] = {"scores": scores, "topk_indices": idx}
+        return [out], out, baux
 
 
 class Nestor(Backbone):
@@ -715,7 +765,8 @@ class Nestor(Backbone):
         # configured rate for its last (reference ``nestor/backbones/nestor.py:2338-2345``)
         rates = [[config.drop_path_rate * i / max(s.layers - 1, 1) for i in range(s.layers)] for s in self.specs]
         self.blocks = nn.ModuleList(
-            [Block(s, init, self.max_depth_sources, dense_no_router, self.depth_reads, residual, rates[i])
+            [Block(s, init, self.max_depth_sources, dense_no_router, self.depth_reads, residual, rates[i],
+                   history_attention=config.history_attention)
              for i, s in enumerate(self.specs)])
         if self.depth_reads:
             self.final_depth_read = DepthRead(config.output_dim, self.max_depth_sources,

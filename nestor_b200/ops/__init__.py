@@ -98,6 +98,7 @@ def _dispatch(name: str):
 # The two halves of ``depth_read_norm`` as separate equations: test oracles only (the model calls the fused op).
 rmsnorm = _ref.rmsnorm
 depth_read = _ref.depth_read
+depth_attention = _ref.depth_attention      # within-block history attention: plain PyTorch arithmetic on any device
 depth_read_norm = _dispatch("depth_read_norm")
 grad_sink = _dispatch("grad_sink")
 mid_source = _dispatch("mid_source")

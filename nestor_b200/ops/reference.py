@@ -220,6 +220,23 @@ def depth_read(sources: list[Tensor], query: Tensor, gains: Tensor, eps: float =
     return out
 
 
+def depth_attention(values: list[Tensor], query: Tensor, key_gain: Tensor, eps: float = 1e-6) -> Tensor:
+    """Attention over a block's sublayer history (``residual_mode='attn_res'``): ``values[0]`` is the block input and
+    every later entry one sublayer update, each ``[T, d]``. The logit of entry ``i`` is the pseudo-query ``query [d]``
+    against its gain-only RMSNorm, ``z_i = ((q * g) . v_i) * rsqrt(mean(v_i^2) + eps)``; the output is the fp32
+    softmax-over-history mixture of the raw values (reference ``nestor/backbones/nestor.py:3900-4074``). Unlike
+    :func:`depth_read` the mixture uses the raw values (no unit-RMS rescale), has no per-entry gains and no
+    ``1/sqrt(d)`` temperature."""
+
+    w = (query.float().reshape(-1) * key_gain.float())
+    z = torch.stack([(v.float() @ w) * torch.rsqrt(v.float().pow(2).mean(dim=-1) + eps) for v in values], dim=-1)
+    alpha = torch.softmax(z, dim=-1)
+    out = values[0].float() * alpha[..., 0:1]
+    for i in range(1, len(values)):
+        out = out + values[i].float() * alpha[..., i : i + 1]
+    return out
+
+
 def depth_read_norm(sources: list[Tensor], query: Tensor, gains: Tensor, gamma: Tensor, eps_read: float,
                     eps_norm: float, out_dtype: torch.dtype, key_cache: DepthKeyCache | None = None) -> Tensor:
     """``rmsnorm(depth_read(sources))``: the input of every attention / expert half and of the head."""

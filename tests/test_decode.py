@@ -75,3 +75,27 @@ def test_generate_is_greedy_continuation(tiny_scale):
         cache = m.init_kv_cache(2, 2)
         for t in range(3):
             m.decode_step(prompt[:, t], cache)
+
+
+def test_stepwise_decode_with_within_block_history_attention(tiny_scale):
+    """``residual_mode='attn_res'`` mixes a token's own sublayer history, so it decodes token by token as well."""
+
+    import dataclasses as dc
+    from nestor_b200.models import Model
+    torch.manual_seed(3)
+    cfg = tiny_scale.build_experiment("moe", "tiny").jobs[0].model
+    cfg = dc.replace(cfg, backbone_config=dc.replace(cfg.backbone_config, residual_mode="attn_res",
+                                                     block_residual_mode="attn_res"))
+    m = Model.from_config(cfg).eval()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if "query" in n:
+                p.normal_(0, 0.1)
+    B, S = 2, 12
+    ids = torch.randint(0, 100263, (B, S))
+    with torch.no_grad():
+        full = m(ids).pred.float()
+    cache = m.init_kv_cache(B, S)
+    for t in range(S):
+        step = m.decode_step(ids[:, t], cache)
+        assert torch.allclose(step, full[:, t], atol=2e-4, rtol=1e-4), (t, (step - full[:, t]).abs().max())

@@ -707,3 +707,74 @@ def test_pointwise_expert_activations_match_reference(family, activation, tiny_s
     ours = backbone_body_flops(dc.replace(cfg.backbone_config, router_num_dense_shared_experts=0), seq_len=64)
     ref = RF.backbone_body_flops(dc.replace(rcfg.backbone_config, router_num_dense_shared_experts=0), seq_len=64)
     assert abs(ours.total - ref.total) / ref.total < 1e-9
+
+
+@pytest.mark.parametrize("family,block_mode", [("dense", "projection"), ("moe", "attn_res"), ("nestor", "projection")])
+def test_within_block_history_attention_matches_reference(family, block_mode, tiny_scale, monkeypatch):
+    """``residual_mode='attn_res'``: inside a block every sublayer reads a softmax mixture of the block input and all
+    earlier sublayer updates (zero-initialised pseudo-query, gain-only key norm), and the block output is one more
+    such read plus an RMSNorm. Same state-dict keys, logits, gradients and optimizer groups as the reference."""
+
+    import dataclasses as dc
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "nestor").is_dir():
+        pytest.skip("reference package not installed under baseline/_ref")
+    monkeypatch.setenv("NESTOR_STACKED_EXPERT_BANKS", "1")
+    monkeypatch.setenv("NESTOR_DENSE_NO_ROUTER", "1")
+    monkeypatch.syspath_prepend(str(ref_root))
+    try:
+        from nestor.experiments import pretrain as RP
+        from nestor.models import Model as RefModel
+        from nestor.train.optim import build_optimizer as ref_build
+    except Exception as exc:
+        pytest.skip(f"reference import failed: {exc}")
+    from nestor_b200.train.optim import build_param_groups
+    P = tiny_scale
+    monkeypatch.setitem(RP.SCALES, "tiny", RP.Scale("tiny", 128, 4, 8, 512, 10, 2, 1024))
+    monkeypatch.setitem(RP.NESTOR_LAYERS, "tiny", (2, 1, 1, 1, 1, 1, 2))
+    monkeypatch.setitem(RP.NESTOR_PRIVATE_EXPERTS, "tiny", 3)
+    monkeypatch.setattr(RP, "NESTOR_MIN_PRIVATE_WIDTH", 24)
+    monkeypatch.setattr(RP, "BLOCK_SIZE", 64)
+    for fam in ("dense", "moe", "nestor"):
+        monkeypatch.setitem(RP.BATCH_SHAPE, (fam, "tiny"), (2, 1))
+    changes = dict(residual_mode="attn_res", block_residual_mode=block_mode)
+    if family == "nestor":
+        changes.update(block_column_include_aggregate=False, block_column_gain_init=1.0, block_column_head_only=False,
+                       block_column_deviation_sources=False)
+    torch.manual_seed(0)
+    rjob = {"moe": RP._moe, "dense": RP._dense, "nestor": RP._nestor}[family]("tiny").jobs[0]
+    rcfg = dc.replace(rjob.model, backbone_config=dc.replace(rjob.model.backbone_config, **changes))
+    rm = RefModel.from_config(rcfg).eval()
+    job = P.build_experiment(family, "tiny").jobs[0]
+    cfg = dc.replace(job.model, backbone_config=dc.replace(job.model.backbone_config, **changes))
+    mm = Model.from_config(cfg).eval()
+    assert set(mm.state_dict()) == set(rm.state_dict())
+    assert all(mm.state_dict()[k].shape == v.shape for k, v in rm.state_dict().items())
+    with torch.no_grad():
+        for n, p in rm.named_parameters():
+            if "query" in n:
+                p.normal_(0, 0.1)          # (history logits are not tempered by 1/sqrt(d): keep the softmax well conditioned)
+            if "key_norm" in n:
+                p.uniform_(0.5, 1.5)
+    mm.load_state_dict(rm.state_dict(), strict=True)
+    ids = torch.randint(0, 100263, (2, 64))
+    lr = F.cross_entropy(rm(ids).pred[:, :-1].reshape(-1, 100263), ids[:, 1:].reshape(-1))
+    lm = F.cross_entropy(mm(ids).pred[:, :-1].reshape(-1, 100263), ids[:, 1:].reshape(-1))
+    assert torch.allclose(lr, lm, atol=1e-5), (float(lr), float(lm))
+    lr.backward(); lm.backward()
+    ref_grads = dict(rm.named_parameters())
+    for n, p in mm.named_parameters():
+        g1, g2 = ref_grads[n].grad, p.grad
+        if g1 is not None and g2 is not None and g1.norm() > 1e-5:
+            assert (g1 - g2).norm() / g1.norm() < 2e-3, n
+    # every parameter lands in the same optimizer, with the same rate and decay
+    ropt = ref_build(rjob.optimizer, rm)
+    rnames = {id(p): n for n, p in rm.named_parameters()}
+    want = {rnames[id(p)]: (g.get("method", "adamw"), round(float(g["lr"]), 12), round(float(g["weight_decay"]), 12))
+            for g in ropt.param_groups for p in g["params"]}
+    names = {id(p): n for n, p in mm.named_parameters()}
+    got = {names[id(p)]: (g["method"], round(float(g["lr"]), 12), round(float(g["weight_decay"]), 12))
+           for g in build_param_groups(job.optimizer, mm) for p in g["params"]}
+    assert set(got) == set(want)
+    wrong = {n: (got[n], want[n]) for n in want if got[n] != want[n]}
+    assert not wrong, dict(list(wrong.items())[:6])
