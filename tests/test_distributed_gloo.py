@@ -125,3 +125,96 @@ def test_missing_rank_is_detected_by_timeout():
     p.join(60)
     assert not p.is_alive()
     assert q.get() != "joined"
+
+
+# ------------------------------------------------------------------ the whole trainer on two ranks
+def _tiny_job(accum):
+    import dataclasses as dc
+    from nestor_b200.experiments.tiny import nestor_tiny
+    job = nestor_tiny().jobs[0]
+    return dc.replace(job, grad_accum_steps=accum)
+
+
+def _tokens(shard, step):
+    g = torch.Generator().manual_seed(1000 + 10 * step + shard)
+    return torch.randint(0, 100_277, (2, 64), generator=g)
+
+
+def _quiet(trainer):
+    trainer.model.train()
+    for blk in trainer.model.backbone.blocks:      # no exploration noise: both runs must route identically
+        blk.freeze_routing_noise = True
+
+
+def _trainer_rank(rank, world, port, q, sharded):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      DCLM_BLOCK_SIZE="64", NESTOR_LOSSFREE_GLOBAL_COUNTS="1",
+                      NESTOR_MUON_SHARD="1" if sharded else "0", WANDB_MODE="disabled")
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    from nestor_b200.models import Model
+    from nestor_b200.train.trainer import Trainer
+    torch.manual_seed(0)
+    job = _tiny_job(1)
+    tr = Trainer(job, Model.from_config(job.model), [], device=torch.device("cpu"))
+    _quiet(tr)
+    norms = []
+    for step in range(2):
+        ids = _tokens(rank, step)
+        loss, counts = tr.train_step((ids, ids))
+        norms.append(float(tr.update_weights(counts)))
+    bias = torch.cat([r.choice_bias.flatten() for _, r in tr.model.backbone.routers()])
+    q.put((rank, tr.arena.master.clone().numpy(), bias.numpy(), norms))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("sharded", [False, True])
+def test_trainer_on_two_ranks_matches_accumulation_in_one_process(sharded, monkeypatch):
+    """Two gloo ranks, one micro-batch each, against one process that accumulates the same two micro-batches: the
+    gradient mean over ranks, the clipping norm, both optimizers (replicated, and with owner-sharded state), the
+    parameter broadcast and the balancing-bias update from global counts leave every rank with the single-process
+    weights and biases."""
+
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    procs = [ctx.Process(target=_trainer_rank, args=(r, world, port, q, sharded)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted((q.get() for _ in range(world)), key=lambda t: t[0])
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+
+    monkeypatch.setenv("DCLM_BLOCK_SIZE", "64")
+    monkeypatch.setenv("NESTOR_LOSSFREE_GLOBAL_COUNTS", "1")
+    from nestor_b200.models import Model
+    from nestor_b200.models.nestor import add_router_counts
+    from nestor_b200.train.trainer import Trainer
+    torch.manual_seed(0)
+    job = _tiny_job(2)
+    tr = Trainer(job, Model.from_config(job.model), [], device=torch.device("cpu"))
+    _quiet(tr)
+    start = tr.arena.master.clone().numpy()
+    want_norms = []
+    for step in range(2):
+        total = None
+        for shard in range(world):
+            ids = _tokens(shard, step)
+            loss, counts = tr.train_step((ids, ids))
+            total = add_router_counts(total, counts)
+        want_norms.append(float(tr.update_weights(total)))
+    want = tr.arena.master.clone().numpy()
+    want_bias = torch.cat([r.choice_bias.flatten() for _, r in tr.model.backbone.routers()]).numpy()
+    assert abs(want_bias).max() > 0                      # the balancing update really moved the biases
+    import numpy as np
+    moved = np.linalg.norm(want - start)
+    for rank, master, bias, norms in results:
+        # (Newton-Schulz runs in bf16: a last-bit difference in a reduced gradient can flip a rounding inside it, which
+        # moves single matrices by a percent or two of their update; the clipping norms below are the sharp check of
+        # the reduced gradients, and the ranks must agree with each other exactly)
+        assert np.linalg.norm(master - want) < 1e-2 * moved, (rank, np.linalg.norm(master - want), moved)
+        assert abs(master - want).max() < 1e-3, (rank, abs(master - want).max())
+        assert (bias == want_bias).all(), rank
+        assert all(abs(a - b) < 1e-5 * max(1.0, abs(b)) for a, b in zip(norms, want_norms)), (norms, want_norms)
+    assert (results[0][1] == results[1][1]).all()
