@@ -778,3 +778,50 @@ def test_within_block_history_attention_matches_reference(family, block_mode, ti
     assert set(got) == set(want)
     wrong = {n: (got[n], want[n]) for n in want if got[n] != want[n]}
     assert not wrong, dict(list(wrong.items())[:6])
+
+
+def test_silent_columns_start_at_the_merged_mixture(tiny_scale):
+    """Gain-init identities of the column head read (reference nestor/backbones/nestor.py:2098-2108): with the column
+    gains at zero and the pseudo-query at its zero init, the head input is the one a read over the embedding and the
+    block aggregates alone would give (the softmax mass parked on the silent slots only rescales the mixture, and
+    the RMSNorm removes the scale down to its epsilon floor); ``block_column_mass_lambda = 0`` is the same init; a
+    non-zero lambda keeps one unit of mass per multi-column block."""
+
+    import dataclasses as dc
+    from nestor_b200 import ops
+    cfg = tiny_scale.build_experiment("nestor", "tiny").jobs[0].model
+    silent = Model.from_config(cfg).eval()
+    assert cfg.backbone_config.block_column_gain_init == 0.0
+    lam0 = Model.from_config(dc.replace(cfg, backbone_config=dc.replace(
+        cfg.backbone_config, block_column_gain_init=1.0, block_column_mass_lambda=0.0)))
+    assert torch.equal(lam0.backbone.final_depth_read.value_gains, silent.backbone.final_depth_read.value_gains)
+    lam = Model.from_config(dc.replace(cfg, backbone_config=dc.replace(
+        cfg.backbone_config, block_column_gain_init=1.0, block_column_mass_lambda=0.6)))
+    g, slot = lam.backbone.final_depth_read.value_gains.detach(), 1
+    for s in lam.backbone.specs:
+        assert abs(float(g[slot : slot + s.exports].sum()) - 1.0) < 1e-6       # lambda / k per column + (1 - lambda)
+        assert torch.allclose(g[slot : slot + s.k], torch.full((s.k,), 0.6 / s.k))
+        slot += s.exports
+
+    # the read itself: wide sources with silent columns == narrow sources, after the norm
+    torch.manual_seed(0)
+    bb = silent.backbone
+    T, d = 12, cfg.backbone_config.input_dim
+    narrow, wide = [torch.randn(T, d)], []
+    wide.append(narrow[0])
+    for s in bb.specs:
+        streams = torch.randn(T, s.k, d)
+        agg = streams.mean(dim=1)
+        wide.extend([*(streams - agg.unsqueeze(1)).unbind(dim=1), agg])
+        narrow.append(agg)
+    read, norm = bb.final_depth_read, bb.final_norm
+    assert float(read.query.abs().max()) == 0.0
+    # before the norm the two mixtures differ by the share of softmax mass on the silent slots, exactly
+    raw_full = ops.depth_read(wide, read.query, read.value_gains, read.eps)
+    raw_merged = ops.depth_read(narrow, read.query, torch.ones(len(narrow)), read.eps)
+    assert torch.allclose(raw_full * len(wide), raw_merged * len(narrow), atol=1e-5)
+    # after it they agree down to the norm's epsilon floor
+    full = ops.depth_read_norm(wide, read.query, read.value_gains, norm.weight, read.eps, norm.eps, torch.float32)
+    merged = ops.depth_read_norm(narrow, read.query, torch.ones(len(narrow)), norm.weight, read.eps, norm.eps,
+                                 torch.float32)
+    assert torch.allclose(full, merged, rtol=5e-3, atol=1e-4)

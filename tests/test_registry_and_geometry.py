@@ -194,3 +194,64 @@ def test_auto_head_split_and_dense_ratio_follow_the_reference(tiny_scale, monkey
     odd = dc.replace(base, block_num_heads=1, block_mlp_hidden_dims=[8], **changes).resolve()
     assert [s.heads for s in odd] == [s.heads for s in resolved["nestor"]]
     assert [s.bank_width for s in odd] == [s.bank_width for s in resolved["nestor"]]
+
+
+_COLUMN = dict(input_dim=64, num_blocks=2, feature_dims=[64, 64], causal=True, block_mlp_activations="swiglu",
+               block_mlp_hidden_dims=[256], block_residual_mode="attn_res_column", router_num_shared_experts=1,
+               num_groups=4, num_groups_per_token=[2, 1], block_num_layers=[2, 1],
+               block_column_include_aggregate=True, block_column_head_only=True, block_column_deviation_sources=True)
+
+
+@pytest.mark.parametrize("change,message", [
+    (dict(block_column_mass_lambda=1.5), r"\[0, 1\]"),
+    (dict(block_column_mass_lambda=0.5, block_column_gain_init=0.0), "set one"),
+    (dict(block_column_mass_lambda=0.5, block_column_include_aggregate=False, block_column_head_only=False,
+          block_column_deviation_sources=False), "include_aggregate"),
+    (dict(block_column_include_aggregate=False), "include_aggregate"),                      # head-only needs the aggregates
+    (dict(block_column_include_aggregate=False, block_column_head_only=False), "include_aggregate"),   # so do deviations
+    (dict(block_column_gain_init=-0.1), "non-negative"),
+    (dict(block_column_trailing_layers=0), "at least 1"),
+    (dict(block_column_blocks=[]), "attn_res_kimi"),
+    (dict(block_column_blocks=[2]), "outside"),
+    (dict(num_groups_per_token=[1, 1]), "attn_res_kimi"),                                    # no block has columns to keep
+    (dict(block_residual_mode="attn_res_kimi"), "attn_res_column"),                         # column flags outside column mode
+    (dict(residual_mode="attn_res"), "requires residual_mode='convex'"),
+    (dict(residual_mode="attn_res_xblock"), "non-causal"),
+    (dict(block_mlp_activations="swish"), "block_mlp_activations"),
+    (dict(block_mlp_hidden_dims=[[256, 256]] * 2), "one hidden width"),
+    (dict(block_layer_num_experts=[[1, 1]]), "one entry per block"),
+    (dict(block_layer_num_experts=[[1], [1]]), "entries"),
+    (dict(block_layer_num_experts=[[1, 0], [1]]), ">= 1"),
+    (dict(block_layer_num_experts=[[1, 3], [1]]), "shared expert banks"),                    # several columns: one bank per column
+    (dict(mlp_auto_dense_ratio=0.0), "positive"),
+])
+def test_configuration_rules_are_enforced(change, message):
+    """Every rule the configuration variants come with is checked when the config is resolved, with a message that
+    names the field (same constraints as the reference's expansion, nestor/backbones/nestor.py:2399-2600, 2785-2812)."""
+
+    NestorConfig(**_COLUMN).resolve()
+    with pytest.raises(ValueError, match=message):
+        NestorConfig(**{**_COLUMN, **change}).resolve()
+
+
+def test_block_specs_of_column_variants():
+    """What ``resolve()`` derives for the column knobs: exports per block, merged prefixes, which blocks keep columns,
+    and the widest read."""
+
+    cfg = NestorConfig(**{**_COLUMN, "num_groups_per_token": [3, 2], "block_column_blocks": [0],
+                          "block_column_trailing_layers": 1})
+    a, b = cfg.resolve()
+    assert (a.columns, a.exports, a.merged_prefix) == (True, 4, 1)        # 3 deviations + aggregate; first layer merged
+    assert (b.columns, b.exports, b.merged_prefix) == (False, 1, 0)       # left out: one merged export
+    assert cfg.max_depth_sources() == 1 + 4 + 1
+    raw = NestorConfig(**{**_COLUMN, "num_groups_per_token": [3, 1], "block_column_include_aggregate": False,
+                          "block_column_head_only": False, "block_column_deviation_sources": False}).resolve()
+    assert [s.exports for s in raw] == [3, 1] and not raw[0].column_aggregate and not raw[0].column_deviation
+    assert raw[1].column_aggregate is False                                 # a single column is its own aggregate
+    sched = NestorConfig(**{**_COLUMN, "block_residual_mode": "attn_res_kimi", "num_groups": 1,
+                            "num_groups_per_token": 1, "block_column_include_aggregate": False,
+                            "block_column_head_only": False, "block_column_deviation_sources": False,
+                            "block_layer_num_experts": [[4, 6], [5]], "router_num_shared_experts": [2, 5],
+                            "router_num_experts_per_group_per_token": 2}).resolve()
+    assert [sched[0].experts_of_layer(i) for i in range(2)] == [4, 6] and sched[0].bank_experts == 6
+    assert sched[1].experts_of_layer(0) == 5
