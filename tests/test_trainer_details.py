@@ -1,0 +1,114 @@
+"""Trainer details: fused head + cross-entropy against materialised logits, the weight average (EMA) and its
+checkpoint entry, explicit positions against the default, private routers batched against one-by-one."""
+
+import dataclasses as dc
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from nestor_b200.models import Model
+from nestor_b200.ops import reference as R
+
+
+def _tokens(seed, shape=(2, 64)):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, 100_263, shape, generator=g)
+
+
+def test_fused_head_loss_equals_the_loss_on_materialised_logits(tiny_scale):
+    """``fused_head``: the model hands the loss the normalised hidden state and the head weight, and the chunked
+    head + cross-entropy op never holds ``[B*S, V]`` logits; loss and every gradient equal the plain path's."""
+
+    from nestor_b200.train.losses import CausalLMLoss
+    cfg = tiny_scale.build_experiment("moe", "tiny").jobs[0].model
+    torch.manual_seed(0)
+    m = Model.from_config(cfg).eval()
+    ids = _tokens(1)
+    grads = {}
+    for fused in (False, True):
+        m.zero_grad(set_to_none=True)
+        m.fused_head = fused
+        out = m(ids)
+        loss = CausalLMLoss()(out.pred, ids, out.aux).total
+        loss.backward()
+        grads[fused] = (float(loss), {n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None})
+    assert abs(grads[True][0] - grads[False][0]) < 1e-5
+    assert set(grads[True][1]) == set(grads[False][1])
+    for n, g in grads[False][1].items():
+        assert torch.allclose(grads[True][1][n], g, atol=1e-6, rtol=1e-4), n
+
+
+def test_explicit_positions_equal_the_default(tiny_scale):
+    """Token tensors come with no mask and implicit positions ``0..S-1`` (the trivial-mask contract of the text
+    adapter, reference nestor/adapters/text.py:167-170); passing those positions explicitly changes nothing, shifted
+    positions do (RoPE)."""
+
+    cfg = tiny_scale.build_experiment("nestor", "tiny").jobs[0].model
+    torch.manual_seed(0)
+    m = Model.from_config(cfg).eval()
+    ids = _tokens(2, (2, 32))
+    pos = torch.arange(32).unsqueeze(0).expand(2, -1)
+    with torch.no_grad():
+        a, b, c = m(ids).pred, m(ids, pos=pos).pred, m(ids, pos=pos + 5).pred
+    assert torch.equal(a, b)
+    assert not torch.allclose(a, c)
+
+
+@pytest.mark.parametrize("gate_mode", ["renorm", "switch"])
+def test_private_routers_batched_equal_one_router_at_a_time(gate_mode):
+    """``route_selected`` routes every (token, selected column) pair through that column's private router in one
+    batched call; the result is what each column's own top-k router gives for its members (reference
+    nestor/backbones/batched_router.py:140-240)."""
+
+    torch.manual_seed(0)
+    T, G, Q, kc, k = 40, 5, 6, 3, 2
+    scores = torch.randn(T, G, Q)
+    bias = torch.randn(G, Q) * 0.3
+    cols = torch.stack([torch.randperm(G)[:kc] for _ in range(T)])
+    col_gates = torch.rand(T, kc)
+    ids, w, idx = R.route_selected(scores, bias, cols, col_gates, k, gate_mode, torch.float32)
+    assert ids.shape == (T, kc * k) and w.shape == (T, kc * k) and idx.shape == (T, kc, k)
+    for g in range(G):
+        members = (cols == g).nonzero()                       # (token, slot) pairs of column g
+        if members.numel() == 0:
+            continue
+        t, slot = members[:, 0], members[:, 1]
+        want_idx, want_gate = R.route_topk(scores[t, g], bias[g], k, gate_mode)
+        assert torch.equal(idx[t, slot], want_idx)
+        got = w.view(T, kc, k)[t, slot]
+        assert torch.allclose(got, want_gate * col_gates[t, slot].unsqueeze(-1), atol=1e-6)
+        assert torch.equal(ids.view(T, kc, k)[t, slot], g * Q + want_idx)
+
+
+def test_weight_average_follows_the_masters_and_is_checkpointed(tmp_path, monkeypatch):
+    """``ema_decay``: after every optimizer step the shadow moves ``1 - decay`` of the way to the fp32 masters; the
+    checkpoint carries it by parameter name and a resumed trainer continues from it."""
+
+    from nestor_b200.experiments.tiny import nestor_tiny
+    from nestor_b200.train.trainer import Trainer
+    monkeypatch.setenv("DCLM_BLOCK_SIZE", "64")
+    torch.manual_seed(0)
+    job = dc.replace(nestor_tiny().jobs[0], ema_decay=0.9)
+    tr = Trainer(job, Model.from_config(job.model), [], device=torch.device("cpu"), run_dir=tmp_path)
+    assert tr.ema is not None and torch.equal(tr.ema["flat"], tr.arena.master)
+    shadow = tr.arena.master.clone()
+    for step in range(2):
+        ids = _tokens(10 + step)
+        loss, counts = tr.train_step((ids, ids))
+        tr.update_weights(counts)
+        shadow = shadow + (tr.arena.master - shadow) * (1.0 - 0.9)
+        assert torch.allclose(tr.ema["flat"], shadow, atol=1e-7)
+    assert not torch.equal(tr.ema["flat"], tr.arena.master)
+    tr.global_step = 2
+    tr.save_checkpoint()
+    path = tr.checkpoint_path()
+    payload = torch.load(path, weights_only=False)
+    name, p = next(iter(tr.model.named_parameters()))
+    slot = tr.arena.slot(p)
+    assert torch.equal(payload["ema"][slot.name].reshape(-1), tr.ema["flat"][slot.offset : slot.offset + slot.numel])
+    torch.manual_seed(1)
+    other = Trainer(job, Model.from_config(job.model), [], device=torch.device("cpu"), run_dir=tmp_path)
+    other.resume(path)
+    assert other.global_step == 2 and torch.equal(other.ema["flat"], tr.ema["flat"])
+    assert torch.equal(other.arena.master, tr.arena.master)
