@@ -154,6 +154,8 @@ class BlockSpec:
     token_dispatch: bool
     dense_shared: int = 0        # always-on SwiGLU experts of the bank's width beside the routed bank (unit gate)
     layer_experts: tuple[int, ...] | None = None   # bank size per layer (None: ``bank_experts`` everywhere)
+    bank_shared: int | None = None   # how many of a bank's choices are experts shared by all columns (None: all); the
+                                     # other choices name one expert per column
     activation: str = "swiglu"   # bank / dense experts: 'swiglu' (gated) or a pointwise 'relu' / 'gelu' / 'silu' / 'tanh'
     columns: bool = True         # column mode: the block tracks per-column streams and exports them
     column_layers: int | None = None   # column mode: only this many trailing layers track streams (None = all)
@@ -389,11 +391,10 @@ class NestorConfig(BackboneConfig):
                     raise ValueError(f"block {i}: pool top-k out of range.")
             else:
                 fewest = epg[i] if schedule is None else min(schedule[i])
-                if G[i] > 1 and (fewest != shared[i] or epg[i] != shared[i]):
-                    # with one column the column-specific experts of a bank are plain further experts; with several
-                    # they would be one bank per column
-                    raise ValueError(f"block {i}: with several columns only shared expert banks are supported "
-                                     "(experts_per_group == shared in every layer).")
+                if G[i] > 1 and fewest == 1 and shared[i] == 0:
+                    # (one unstacked dense expert per column: the stacked bank layout needs at least two choices)
+                    raise ValueError(f"block {i}: column-specific experts need banks of at least two choices "
+                                     "(router_num_experts_per_group > 1 in every layer).")
                 if not 0 <= shared[i] <= fewest:
                     raise ValueError(f"block {i}: router_num_shared_experts must be in [0, fewest experts of a layer].")
                 if not 1 <= etop[i] <= fewest:
@@ -414,6 +415,7 @@ class NestorConfig(BackboneConfig):
                 router_hidden=sh[i][0], loss_free=bool(lf[i]), bias_rate=float(br[i]), token_dispatch=bool(td[i]),
                 dense_shared=int(dense_shared[i]),
                 layer_experts=None if pool or schedule is None else tuple(schedule[i]),
+                bank_shared=None if pool else int(shared[i]),
                 activation="swiglu" if pool else acts[i],      # pool experts are always SwiGLU
                 columns=keeps, column_layers=self.block_column_trailing_layers if keeps else None,
                 column_aggregate=self.block_column_include_aggregate and k[i] > 1,

@@ -189,7 +189,11 @@ class Layer(nn.Module):
             self.attn_key_norm = Norm(s.dim, init.norm_eps)
             self.mlp_query = ScaledLinear(s.dim, 1, role="score", bias=False, zero_init=True)
             self.mlp_key_norm = Norm(s.dim, init.norm_eps)
-        self.bank_experts = E = s.bank_experts if bank_experts is None else bank_experts   # this layer's bank size
+        self.bank_experts = E = s.bank_experts if bank_experts is None else bank_experts   # this layer's router choices
+        # Choices past the shared ones name one expert PER COLUMN: the stacked bank is [shared | column 0 | column 1 ...]
+        # (reference nestor/backbones/nestor.py:4419-4436, 4456-4470). With one column they are plain further experts.
+        self.bank_specific = E - s.bank_shared if (s.G > 1 and not s.pool and s.bank_shared is not None) else 0
+        bank_total = E + (s.G - 1) * self.bank_specific
         gated = s.activation == "swiglu"      # pointwise activations: experts without a gate matrix
         self.attn_norm = Norm(s.dim, init.norm_eps)
         self.mlp_norm = Norm(s.dim, init.norm_eps)
@@ -215,7 +219,7 @@ class Layer(nn.Module):
                 self.expert_router.requires_grad_(False)
                 self.shared_experts = nn.ModuleList([DenseExpert(s.dim, s.bank_width, init.matrix, init.output, gated)])
             else:
-                self.stacked_moe_bank = ExpertBank(E, s.dim, s.bank_width, init.matrix, init.output, gated)
+                self.stacked_moe_bank = ExpertBank(bank_total, s.dim, s.bank_width, init.matrix, init.output, gated)
         # DeepSeekMoE-style always-on experts beside a routed bank: every token, unit gate, outside the router
         # (reference nestor/backbones/nestor.py:4441-4451, 5290-5291)
         self.dense_shared_experts = nn.ModuleList(
@@ -306,15 +310,29 @@ class Layer(nn.Module):
             return None, self._add_dense_shared(self._dense_expert(self.shared_experts[0], n, cd), n, cd), None, {}
         scores = ops.router_scores(n, None, W(self, self.expert_router.score_mlp.layers[0].weight), cd)
         idx, gate = ops.route_topk(scores, self.expert_router.choice_bias, s.bank_top_k, "renorm")
-        plan = ops.build_expert_plan(idx, self.bank_experts)
         bank = self.stacked_moe_bank
-        ones = torch.ones_like(gate, dtype=cd)
+        ids, row_w = idx, gate
+        if self.bank_specific:
+            # a shared choice is one row; a column-specific choice is one row per selected column, in that column's
+            # slice of the bank and weighted by the column gate as well (rows of a shared choice past the first
+            # carry weight zero, which keeps every shape static); reference nestor/backbones/nestor.py:4816-4835
+            T, k = ctx.idx.shape
+            col = ctx.idx.to(idx.dtype)
+            specific = (idx >= self.bank_experts - self.bank_specific).unsqueeze(-1)               # [T, top_k, 1]
+            ids = torch.where(specific, idx.unsqueeze(-1) + col.unsqueeze(1) * self.bank_specific,
+                              idx.unsqueeze(-1).expand(-1, -1, k)).reshape(T, -1)
+            first = torch.zeros(k, dtype=gate.dtype, device=gate.device)
+            first[0] = 1.0
+            row_w = torch.where(specific, gate.unsqueeze(-1) * ctx.gates.to(gate.dtype).unsqueeze(1),
+                                gate.unsqueeze(-1) * first).reshape(T, -1)
+        plan = ops.build_expert_plan(ids, bank.num_experts)
+        ones = torch.ones_like(row_w, dtype=cd)
         if bank.gated:
             rows = ops.expert_bank(n, plan, ones, W(self, bank.w_up), W(self, bank.w_gate), W(self, bank.w_down), cd, group=1)
         else:
             rows = ops.expert_bank(n, plan, ones, W(self, bank.w_up), None, W(self, bank.w_down), cd, group=1,
                                    activation=s.activation)
-        out = (rows * gate.to(cd).float().unsqueeze(-1)).sum(dim=1).to(cd).float()
+        out = (rows * row_w.to(cd).float().unsqueeze(-1)).sum(dim=1).to(cd).float()
         aux = {"expert_idx": idx, "expert_router": {"scores": scores, "topk_indices": idx}}
         if not self.training and not torch.is_grad_enabled():
             aux["expert_prob"] = torch.softmax(scores.float(), dim=-1).sum(0)

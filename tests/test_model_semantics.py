@@ -602,7 +602,8 @@ def test_column_mode_variants_match_reference(variant, tiny_scale, monkeypatch):
 def test_per_layer_expert_counts_match_reference(tiny_scale, monkeypatch):
     """``block_layer_num_experts``: banks of different sizes at different depths (same top-k and width), with the
     shared count below the smallest bank. Single-column blocks, so a bank's column-specific experts are plain further
-    experts. Same state-dict keys, logits, gradients and router statistics keys as the reference."""
+    experts (several columns: ``test_column_specific_bank_experts_match_reference``). Same state-dict keys, logits,
+    gradients and router statistics keys as the reference."""
 
     import dataclasses as dc
     ref_root = ROOT / "baseline" / "_ref"
@@ -651,9 +652,9 @@ def test_per_layer_expert_counts_match_reference(tiny_scale, monkeypatch):
             assert (g1 - g2).norm() / g1.norm() < 2e-3, n
     counts = router_counts(mm.backbone, out.aux)
     assert [counts[f"blocks.{b}.layers.0.expert_router"].numel() for b in range(4)] == [5, 9, 4, 12]
-    # with several columns a bank with column-specific experts would be one bank per column: refused
-    with pytest.raises(ValueError, match="shared expert banks"):
-        dc.replace(cfg.backbone_config, num_groups=[2] * 4).resolve()
+    # with several columns, choices past the shared ones name one expert per column: the bank grows accordingly
+    two = dc.replace(cfg.backbone_config, num_groups=[2] * 4).resolve()
+    assert [s.bank_shared for s in two] == [3, 4, 4, 0]
 
 
 @pytest.mark.parametrize("family,activation", [("moe", "gelu"), ("dense", "relu"), ("moe", "tanh")])
@@ -825,3 +826,69 @@ def test_silent_columns_start_at_the_merged_mixture(tiny_scale):
     merged = ops.depth_read_norm(narrow, read.query, torch.ones(len(narrow)), norm.weight, read.eps, norm.eps,
                                  torch.float32)
     assert torch.allclose(full, merged, rtol=5e-3, atol=1e-4)
+
+
+@pytest.mark.parametrize("mode", ["attn_res_kimi", "projection", "attn_res_column"])
+def test_column_specific_bank_experts_match_reference(mode, tiny_scale, monkeypatch):
+    """Banks in multi-column blocks whose choices past the shared ones name one expert per column
+    (``router_num_shared_experts < router_num_experts_per_group``): a column-specific choice runs that expert of
+    every selected column, weighted by the expert gate times the column gate; shared choices carry the expert gate
+    alone (reference nestor/backbones/nestor.py:4798-4837). Stacked layout ``[shared | column 0 | column 1 | ...]``;
+    same keys, logits and gradients as the reference, with top-2 column routing."""
+
+    import dataclasses as dc
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "nestor").is_dir():
+        pytest.skip("reference package not installed under baseline/_ref")
+    monkeypatch.setenv("NESTOR_STACKED_EXPERT_BANKS", "1")
+    monkeypatch.setenv("NESTOR_DENSE_NO_ROUTER", "1")
+    monkeypatch.syspath_prepend(str(ref_root))
+    try:
+        from nestor.experiments import pretrain as RP
+        from nestor.models import Model as RefModel
+    except Exception as exc:
+        pytest.skip(f"reference import failed: {exc}")
+    P = tiny_scale
+    monkeypatch.setitem(RP.SCALES, "tiny", RP.Scale("tiny", 128, 4, 8, 512, 10, 2, 1024))
+    monkeypatch.setattr(RP, "BLOCK_SIZE", 64)
+    for fam in ("dense", "moe", "nestor"):
+        monkeypatch.setitem(RP.BATCH_SHAPE, (fam, "tiny"), (2, 1))
+    changes = dict(num_groups=[4] * 4, num_groups_per_token=[2, 2, 1, 3], block_num_heads=[2] * 4,
+                   router_num_experts_per_group=[6, 5, 6, 4], router_num_shared_experts=[2, 0, 3, 4],
+                   router_num_experts_per_group_per_token=[3, 2, 3, 2], block_residual_mode=mode,
+                   router_score_mlp_hidden_dims=[[16]] * 4, router_noise_mlp_hidden_dims=[[16]] * 4,
+                   attention_token_dispatch=True)
+    if mode == "attn_res_column":
+        changes.update(block_column_include_aggregate=True, block_column_head_only=True,
+                       block_column_deviation_sources=True, block_column_gain_init=0.5)
+    torch.manual_seed(0)
+    rcfg = RP._moe("tiny").jobs[0].model
+    rcfg = dc.replace(rcfg, backbone_config=dc.replace(rcfg.backbone_config, **changes))
+    rm = RefModel.from_config(rcfg).eval()
+    cfg = P.build_experiment("moe", "tiny").jobs[0].model
+    cfg = dc.replace(cfg, backbone_config=dc.replace(cfg.backbone_config, **changes))
+    mm = Model.from_config(cfg).eval()
+    assert set(mm.state_dict()) == set(rm.state_dict())
+    assert all(mm.state_dict()[k].shape == v.shape for k, v in rm.state_dict().items())
+    assert mm.backbone.blocks[0].layers[0].stacked_moe_bank.num_experts == 2 + 4 * 4      # [shared | 4 per column]
+    with torch.no_grad():
+        for n, p in rm.named_parameters():
+            if "query" in n:
+                p.normal_(0, 0.3)
+    mm.load_state_dict(rm.state_dict(), strict=True)
+    ids = torch.randint(0, 100263, (2, 64))
+    lr = F.cross_entropy(rm(ids).pred[:, :-1].reshape(-1, 100263), ids[:, 1:].reshape(-1))
+    out = mm(ids)
+    lm = F.cross_entropy(out.pred[:, :-1].reshape(-1, 100263), ids[:, 1:].reshape(-1))
+    assert torch.allclose(lr, lm, atol=1e-5), (float(lr), float(lm))
+    lr.backward(); lm.backward()
+    ref_grads = dict(rm.named_parameters())
+    checked = 0
+    for n, p in mm.named_parameters():
+        g1, g2 = ref_grads[n].grad, p.grad
+        if g1 is not None and g2 is not None and g1.norm() > 1e-5:
+            assert (g1 - g2).norm() / g1.norm() < 2e-3, n
+            checked += 1
+    assert checked > 30
+    counts = router_counts(mm.backbone, out.aux)
+    assert counts["blocks.0.layers.0.expert_router"].numel() == 6          # statistics are per router choice

@@ -222,7 +222,7 @@ _COLUMN = dict(input_dim=64, num_blocks=2, feature_dims=[64, 64], causal=True, b
     (dict(block_layer_num_experts=[[1, 1]]), "one entry per block"),
     (dict(block_layer_num_experts=[[1], [1]]), "entries"),
     (dict(block_layer_num_experts=[[1, 0], [1]]), ">= 1"),
-    (dict(block_layer_num_experts=[[1, 3], [1]]), "shared expert banks"),                    # several columns: one bank per column
+    (dict(block_layer_num_experts=[[1, 3], [1]], router_num_shared_experts=0), "at least two choices"),
     (dict(mlp_auto_dense_ratio=0.0), "positive"),
 ])
 def test_configuration_rules_are_enforced(change, message):
