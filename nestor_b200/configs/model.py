@@ -6,12 +6,13 @@ of them. ``NestorConfig.resolve()`` expands the per-block scalars/lists into a l
 of :class:`BlockSpec` records, the flat description the module tree, the kernels'
 plan builders and the FLOP formulas all read.
 
-Scope: the decoder family the twelve registered cells use — causal, stride-1,
-constant-width blocks joined by the Kimi depth read (``attn_res_kimi``) or the
-column depth read (``attn_res_column``). The reference's ViT-era knobs (pooling,
-global tokens, ``projection``/``attn_res`` residual modes, drop-path) are accepted
-at their default values only; ``resolve()`` raises on anything else rather than
-silently building a different model.
+Scope: stride-1, constant-width blocks in every residual topology of the reference (the Kimi depth read
+``attn_res_kimi``, the column depth read ``attn_res_column`` with its read / export / subset variants, the plain
+``projection`` stream, the between-block ``attn_res`` mixture, the within-block history attention), causal or
+bidirectional, with pools, banks (shared or column-specific experts, per-layer sizes) and gated or pointwise
+experts. The reference's vision-era knobs that change the token count or the width between blocks (pooling,
+global tokens, per-block ``feature_dims``) are accepted at their default values only; ``resolve()`` raises on
+anything else rather than silently building a different model.
 """
 
 from __future__ import annotations
@@ -156,6 +157,7 @@ class BlockSpec:
     layer_experts: tuple[int, ...] | None = None   # bank size per layer (None: ``bank_experts`` everywhere)
     bank_shared: int | None = None   # how many of a bank's choices are experts shared by all columns (None: all); the
                                      # other choices name one expert per column
+    causal: bool = True          # False: every member of a column attends to all members of its sequence
     activation: str = "swiglu"   # bank / dense experts: 'swiglu' (gated) or a pointwise 'relu' / 'gelu' / 'silu' / 'tanh'
     columns: bool = True         # column mode: the block tracks per-column streams and exports them
     column_layers: int | None = None   # column mode: only this many trailing layers track streams (None = all)
@@ -261,8 +263,6 @@ class NestorConfig(BackboneConfig):
             raise ValueError("feature_dims must have one entry per block.")
         if any(d != self.input_dim for d in self.feature_dims):
             raise ValueError("Only constant-width decoders are supported (feature_dims == input_dim).")
-        if not self.causal:
-            raise ValueError("Only causal decoders are supported (causal=True).")
         if any(s != 1 for s in _per_block(self.pooling_strides, n, "pooling_strides")):
             raise ValueError("Token pooling between blocks is not supported (pooling_strides must be 1).")
         if self.pooling_keep_ratios is not None or self.num_global_tokens:
@@ -416,6 +416,7 @@ class NestorConfig(BackboneConfig):
                 dense_shared=int(dense_shared[i]),
                 layer_experts=None if pool or schedule is None else tuple(schedule[i]),
                 bank_shared=None if pool else int(shared[i]),
+                causal=bool(self.causal),
                 activation="swiglu" if pool else acts[i],      # pool experts are always SwiGLU
                 columns=keeps, column_layers=self.block_column_trailing_layers if keeps else None,
                 column_aggregate=self.block_column_include_aggregate and k[i] > 1,

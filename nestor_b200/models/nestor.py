@@ -255,11 +255,13 @@ class Layer(nn.Module):
     def attention(self, n: Tensor, ctx: "BlockContext", cd: torch.dtype) -> Tensor:
         s = self.spec
         if s.G == 1:
+            extra = {} if s.causal else {"causal": False}
             out = ops.dense_attention(n, ctx.B, ctx.S, self.qkv_weight(), self.out_weight(),
-                                      s.heads, s.head_dim, s.rope_base, cd, pos=ctx.pos)
+                                      s.heads, s.head_dim, s.rope_base, cd, pos=ctx.pos, **extra)
             return out.unsqueeze(1)
+        extra = {} if s.causal else {"causal": False}
         return ops.column_attention(n, ctx.plan, ctx.gates, self.qkv_weight(), self.out_weight(),
-                                    s.heads, s.head_dim, s.rope_base, cd)
+                                    s.heads, s.head_dim, s.rope_base, cd, **extra)
 
     def attention_step(self, n: Tensor, ctx: "BlockContext", cd: torch.dtype, cache: "LayerKVCache") -> Tensor:
         """Attention half for ONE new token per sequence (``n [B, d]``) against this layer's key/value cache.
@@ -842,6 +844,8 @@ class Nestor(Backbone):
 
         if self.training:
             raise RuntimeError("forward_step is an evaluation path: call model.eval() first")
+        if not self.config.causal:
+            raise RuntimeError("stepwise decoding needs a causal model: a bidirectional token sees later ones")
         B = x0.shape[0]
         with ops.oracle_ops():        # per-token work: the PyTorch statement of the ops on any device
             narrow, wide, x, aux = [x0], [x0], x0, []

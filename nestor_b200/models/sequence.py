@@ -262,6 +262,9 @@ class SequenceModel(nn.Module):
             ids, valid = self.adapter.encode_texts(list(ids))
         if valid is not None and bool((valid[:, 1:] & ~valid[:, :-1]).any()):
             raise ValueError("valid_token_mask must be a prefix mask (padding only after the real tokens).")
+        if valid is not None and not getattr(self.backbone.config, "causal", True) and not bool(valid.all()):
+            raise ValueError("a bidirectional (causal=False) model attends to every position of its sequence: "
+                             "padded batches are not supported, pass sequences of equal length")
         B, S = ids.shape
         cd = self.resolve_compute_dtype(ids.device)
         x0 = self.adapter(ids).reshape(B * S, -1)

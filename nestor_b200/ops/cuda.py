@@ -434,7 +434,11 @@ class _Attention(torch.autograd.Function):
         return (dn, dgates, d_wqkv, d_wo) + (None,) * 12
 
 
-def column_attention(n, plan: ColumnPlan, gates, wqkv, wo, heads, head_dim, rope_base, cd):
+def column_attention(n, plan: ColumnPlan, gates, wqkv, wo, heads, head_dim, rope_base, cd, causal=True):
+    if not causal:
+        # the attention kernels mask above the diagonal of every segment; bidirectional attention runs the PyTorch statement
+        _oracle_path("column_attention", "bidirectional (non-causal) attention")
+        return ref.column_attention(n, plan, gates, wqkv, wo, heads, head_dim, rope_base, cd, causal=False)
     slot_flat = plan.extra.get("slot_flat")
     if slot_flat is None:   # flat (token*k + slot) index of every packed row
         slot_flat = (plan.tok_of_row * plan.k + plan.slot_of_row).contiguous()
@@ -450,7 +454,10 @@ def column_attention(n, plan: ColumnPlan, gates, wqkv, wo, heads, head_dim, rope
 _dense_plans: dict = {}
 
 
-def dense_attention(n, B, S, wqkv, wo, heads, head_dim, rope_base, cd, pos=None):
+def dense_attention(n, B, S, wqkv, wo, heads, head_dim, rope_base, cd, pos=None, causal=True):
+    if not causal:
+        _oracle_path("dense_attention", "bidirectional (non-causal) attention")
+        return ref.dense_attention(n, B, S, wqkv, wo, heads, head_dim, rope_base, cd, pos=pos, causal=False)
     T = n.shape[0]
     key = (B, S, n.device)
     if key not in _dense_plans:

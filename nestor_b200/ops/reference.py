@@ -383,21 +383,24 @@ def route_selected(scores: Tensor, bias: Tensor, cols: Tensor, col_gates: Tensor
 # ---------------------------------------------------------------------------- attention
 
 
-def causal_attention(q: Tensor, k: Tensor, v: Tensor, scale: float) -> Tensor:
-    """Causal softmax attention on ``[n, H, hd]`` (one segment), fp32 softmax, output in ``q.dtype``."""
+def causal_attention(q: Tensor, k: Tensor, v: Tensor, scale: float, causal: bool = True) -> Tensor:
+    """Softmax attention on ``[n, H, hd]`` (one segment), causal unless told otherwise; fp32 softmax, output in
+    ``q.dtype``."""
 
     n = q.shape[0]
     if n == 0:
         return q.new_zeros(q.shape)
     qh, kh, vh = (t.transpose(0, 1) for t in (q, k, v))
     s = (qh.float() @ kh.float().transpose(1, 2)) * scale
-    mask = torch.ones(n, n, dtype=torch.bool, device=q.device).tril()
-    p = torch.softmax(s.masked_fill(~mask, float("-inf")), dim=-1)
+    if causal:
+        mask = torch.ones(n, n, dtype=torch.bool, device=q.device).tril()
+        s = s.masked_fill(~mask, float("-inf"))
+    p = torch.softmax(s, dim=-1)
     return (p.to(q.dtype).float() @ vh.float()).to(q.dtype).transpose(0, 1)
 
 
-def segment_attention(q: Tensor, k: Tensor, v: Tensor, seg_start: Tensor, scale: float) -> Tensor:
-    """Causal attention independently inside each packed segment. ``q/k/v [rows, H, hd]``."""
+def segment_attention(q: Tensor, k: Tensor, v: Tensor, seg_start: Tensor, scale: float, causal: bool = True) -> Tensor:
+    """Attention independently inside each packed segment (causal by default). ``q/k/v [rows, H, hd]``."""
 
     out = torch.empty_like(q)
     bounds = seg_start.tolist()
@@ -406,18 +409,19 @@ def segment_attention(q: Tensor, k: Tensor, v: Tensor, seg_start: Tensor, scale:
             if q.is_cuda:
                 o = F.scaled_dot_product_attention(
                     q[a:b].transpose(0, 1).unsqueeze(0), k[a:b].transpose(0, 1).unsqueeze(0),
-                    v[a:b].transpose(0, 1).unsqueeze(0), is_causal=True, scale=scale)
+                    v[a:b].transpose(0, 1).unsqueeze(0), is_causal=causal, scale=scale)
                 out[a:b] = o.squeeze(0).transpose(0, 1)
             else:
-                out[a:b] = causal_attention(q[a:b], k[a:b], v[a:b], scale)
+                out[a:b] = causal_attention(q[a:b], k[a:b], v[a:b], scale, causal)
     return out
 
 
 def column_attention(
     n: Tensor, plan: ColumnPlan, gates: Tensor, wqkv: Tensor, wo: Tensor,
-    heads: int, head_dim: int, rope_base: float, cd: torch.dtype,
+    heads: int, head_dim: int, rope_base: float, cd: torch.dtype, causal: bool = True,
 ) -> Tensor:
-    """Column-routed causal attention: ``[T, d] -> [T, k, d]`` gated slot updates (fp32).
+    """Column-routed causal attention: ``[T, d] -> [T, k, d]`` gated slot updates (fp32). ``causal=False`` lets every
+    member of a column see all members of its sequence (bidirectional encoders).
 
     ``wqkv [G, 3*inner, d]`` stacks each column's ``q_proj, k_proj, v_proj`` rows; ``wo [G, d, inner]``.
     For every column ``c``: project its member rows, RoPE at the rows' original positions,
@@ -438,7 +442,7 @@ def column_attention(
     q = apply_rope(qkv[:, :inner].reshape(-1, heads, head_dim), cos, sin)
     kk = apply_rope(qkv[:, inner : 2 * inner].reshape(-1, heads, head_dim), cos, sin)
     v = qkv[:, 2 * inner :].reshape(-1, heads, head_dim)
-    o = segment_attention(q, kk, v, plan.seg_start, 1.0 / head_dim).reshape(plan.rows, inner)
+    o = segment_attention(q, kk, v, plan.seg_start, 1.0 / head_dim, causal).reshape(plan.rows, inner)
     y = x.new_empty(plan.rows, d)
     for c in range(plan.G):
         a, b = cs[c], cs[c + 1]
@@ -449,9 +453,10 @@ def column_attention(
 
 def dense_attention(
     n: Tensor, B: int, S: int, wqkv: Tensor, wo: Tensor,
-    heads: int, head_dim: int, rope_base: float, cd: torch.dtype, pos: Tensor | None = None,
+    heads: int, head_dim: int, rope_base: float, cd: torch.dtype, pos: Tensor | None = None, causal: bool = True,
 ) -> Tensor:
-    """Single-column causal MHA over whole sequences: ``[T, d] -> [T, d]`` (baseline arms).
+    """Single-column causal MHA over whole sequences: ``[T, d] -> [T, d]`` (baseline arms); ``causal=False`` is full
+    bidirectional attention.
 
     ``wqkv [1, 3*inner, d]`` (``q_proj, k_proj, v_proj`` rows), ``wo [1, d, inner]``.
     """
@@ -467,7 +472,7 @@ def dense_attention(
     k = apply_rope(qkv[:, inner : 2 * inner].reshape(T, heads, head_dim), cos, sin)
     v = qkv[:, 2 * inner :].reshape(T, heads, head_dim)
     seg = torch.arange(0, T + 1, S, device=n.device, dtype=torch.int32)
-    o = segment_attention(q, k, v, seg, 1.0 / head_dim).reshape(T, inner)
+    o = segment_attention(q, k, v, seg, 1.0 / head_dim, causal).reshape(T, inner)
     return (o @ wo.to(cd).t()).float()
 
 

@@ -81,7 +81,7 @@ def grouped_mm_flops(rows: int, k: int, n: int) -> int:
 
 def forward_flops_per_token(config: SequenceModelConfig, seq_len: int) -> float:
     bb = config.backbone_config
-    body = backbone_body_flops(bb, seq_len=seq_len).total / seq_len
+    body = backbone_body_flops(bb, seq_len=seq_len, causal=bool(getattr(bb, "causal", True))).total / seq_len
     routers = 0.0
     for s in bb.resolve():
         if s.G > 1:

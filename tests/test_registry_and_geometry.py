@@ -108,8 +108,11 @@ def test_config_validation():
     base = dict(input_dim=64, num_blocks=1, feature_dims=[64], causal=True, block_mlp_activations="swiglu",
                 block_mlp_hidden_dims=[256], block_residual_mode="attn_res_kimi", router_num_shared_experts=1)
     NestorConfig(**base).resolve()
+    assert NestorConfig(**{**base, "causal": False}).resolve()[0].causal is False     # bidirectional encoders are a mode
     with pytest.raises(ValueError):
-        NestorConfig(**{**base, "causal": False}).resolve()
+        NestorConfig(**{**base, "pooling_strides": 2}).resolve()
+    with pytest.raises(ValueError):
+        NestorConfig(**{**base, "causal": False, "num_global_tokens": 4}).resolve()
     with pytest.raises(ValueError):
         NestorConfig(**{**base, "block_residual_mode": "no_such_mode"}).resolve()
     NestorConfig(**{**base, "block_residual_mode": "projection"}).resolve()      # plain residual blocks are a supported mode
