@@ -304,6 +304,13 @@ def test_fused_ops_match_oracle_forward_and_backward():
              "block_layer_num_experts": [[5], [9], [4], [12]], "router_num_shared_experts": [3, 4, 4, 0]}),
     # within-block history attention joined by the between-block mixture
     ("moe", {"residual_mode": "attn_res", "block_residual_mode": "attn_res"}),
+    # banks with column-specific experts in multi-column blocks (merged recurrence)
+    ("moe", {"num_groups": [4] * 4, "num_groups_per_token": [2, 2, 1, 3], "block_num_heads": [2] * 4,
+             "router_num_experts_per_group": [6, 5, 6, 4], "router_num_shared_experts": [2, 0, 3, 4],
+             "router_num_experts_per_group_per_token": [3, 2, 3, 2], "router_score_mlp_hidden_dims": [[16]] * 4,
+             "router_noise_mlp_hidden_dims": [[16]] * 4, "attention_token_dispatch": True}),
+    # bidirectional attention (the two attention ops leave the kernels, everything else stays)
+    ("nestor", {"causal": False}),
 ])
 def test_whole_model_kernels_vs_oracle_with_pinned_routing(family, variant, tiny_scale, monkeypatch):
     import dataclasses as dc
