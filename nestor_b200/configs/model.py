@@ -265,8 +265,10 @@ class NestorConfig(BackboneConfig):
             raise ValueError("Only constant-width decoders are supported (feature_dims == input_dim).")
         if any(s != 1 for s in _per_block(self.pooling_strides, n, "pooling_strides")):
             raise ValueError("Token pooling between blocks is not supported (pooling_strides must be 1).")
-        if self.pooling_keep_ratios is not None or self.num_global_tokens:
-            raise ValueError("pooling_keep_ratios / num_global_tokens must stay at defaults.")
+        keep = [] if self.pooling_keep_ratios is None else _per_block(self.pooling_keep_ratios, n, "pooling_keep_ratios")
+        if any(r not in (None, 1.0) for r in keep) or self.num_global_tokens:
+            raise ValueError("pooling_keep_ratios (other than 1.0) / num_global_tokens are not supported: the token "
+                             "count is constant through the model.")
         if not 0.0 <= self.drop_path_rate < 1.0:
             raise ValueError("drop_path_rate must be in [0, 1).")
         if self.block_residual_mode not in ("attn_res_kimi", "attn_res_column", "projection", "attn_res"):

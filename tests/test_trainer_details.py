@@ -112,3 +112,70 @@ def test_weight_average_follows_the_masters_and_is_checkpointed(tmp_path, monkey
     other.resume(path)
     assert other.global_step == 2 and torch.equal(other.ema["flat"], tr.ema["flat"])
     assert torch.equal(other.arena.master, tr.arena.master)
+
+
+_NEUTRAL_FLAGS = [
+    {"NESTOR_NO_DEPTH_KEY_CACHE": "1"},                 # every read recomputes its key scales
+    {"NESTOR_CE_CHUNK_ROWS": "48"},                     # smaller head + cross-entropy chunks
+    {"NESTOR_FUSED_HEAD_CE": "0"},                      # materialised logits
+    {"NESTOR_RUNAHEAD": "0"},                           # the host waits for every step
+    {"NESTOR_LOSSFREE_GLOBAL_COUNTS": "1"},             # one rank: the global counts are the local ones
+    {"NESTOR_MUON_SHARD": "1", "NESTOR_ZERO1": "1"},    # one rank owns everything
+    {"NESTOR_ACTIVATION_OFFLOAD": "1"},                 # nothing to spill without a GPU
+    {"NESTOR_EMA_DECAY": "0.99"},                       # the shadow never feeds back
+    {"NESTOR_ACTIVATION_CHECKPOINT": "1", "NESTOR_ACTIVATION_CHECKPOINT_SPLIT": "1", "NESTOR_EXPERT_HALF_CHUNKS": "2"},
+]
+
+
+def _two_steps(monkeypatch, flags):
+    from nestor_b200.experiments.tiny import nestor_tiny
+    from nestor_b200.train.trainer import Trainer
+    for k, v in flags.items():
+        monkeypatch.setenv(k, v)
+    monkeypatch.setenv("DCLM_BLOCK_SIZE", "64")
+    torch.manual_seed(0)
+    job = nestor_tiny().jobs[0]
+    tr = Trainer(job, Model.from_config(job.model), [], device=torch.device("cpu"))
+    tr.model.train()
+    for blk in tr.model.backbone.blocks:
+        blk.freeze_routing_noise = True
+    losses = []
+    for step in range(2):
+        ids = _tokens(20 + step)
+        loss, counts = tr.train_step((ids, ids))
+        tr.update_weights(counts)
+        losses.append(float(loss.total))
+    for k in flags:
+        monkeypatch.delenv(k)
+    return losses, tr.arena.master.clone()
+
+
+@pytest.fixture(scope="module")
+def _plain_run():
+    threads = torch.get_num_threads()
+    torch.set_num_threads(1)                             # one thread: CPU reductions are then repeatable to the bit
+    mp = pytest.MonkeyPatch()
+    try:
+        yield _two_steps(mp, {})
+    finally:
+        mp.undo()
+        torch.set_num_threads(threads)
+
+
+@pytest.mark.parametrize("flags", _NEUTRAL_FLAGS, ids=lambda f: "+".join(sorted(f)))
+def test_execution_flags_leave_the_training_trajectory_unchanged(flags, _plain_run, monkeypatch):
+    """Flag twins: the knobs that choose HOW a step is executed (caching, chunking, recomputation, sharding of state,
+    host synchronisation, offload, weight averaging) give the same losses and the same weights after two optimizer
+    steps as the plain run. Bit for bit, except where the flag changes a summation order (chunked cross-entropy,
+    materialised logits, recomputed halves, per-read key scales), where the weights agree to rounding."""
+
+    want_losses, want = _plain_run
+    losses, got = _two_steps(monkeypatch, flags)
+    assert all(abs(a - b) < 2e-6 for a, b in zip(losses, want_losses)), (losses, want_losses)
+    reordered = {"NESTOR_CE_CHUNK_ROWS", "NESTOR_FUSED_HEAD_CE", "NESTOR_ACTIVATION_CHECKPOINT",
+                 "NESTOR_NO_DEPTH_KEY_CACHE"} & set(flags)          # (shared vs per-read scale nodes: another backward order)
+    if reordered:
+        moved = float((want - got).norm() / want.norm())
+        assert moved < 1e-4, moved
+    else:
+        assert torch.equal(got, want), float((got - want).abs().max())
