@@ -70,12 +70,30 @@ _MIN_TOKENS = 0
 _MAX_TOKENS: int | None = None
 
 
+class _ByteEncoding:
+    """``--tokenizer bytes``: UTF-8 bytes as ids 0..255 and 256 as end-of-text. Needs no vocabulary file, so the
+    preprocessing tools also run on machines without network access (tests, smoke corpora)."""
+
+    eot_token = 256
+
+    def encode_ordinary_batch(self, texts: list[str]) -> list[list[int]]:
+        return [list(t.encode("utf-8")) for t in texts]
+
+
+def load_encoding(tokenizer_name: str) -> Any:
+    """The tiktoken encoding of that name, or the byte-level stand-in for ``"bytes"``."""
+
+    if tokenizer_name == "bytes":
+        return _ByteEncoding()
+    import tiktoken
+    return tiktoken.get_encoding(tokenizer_name)
+
+
 def init_tokenizer_worker(tokenizer_name: str, min_doc_tokens: int = 0, max_doc_tokens: int | None = None) -> None:
     """Pool initialiser: load the encoding once per worker process and set the length filter."""
 
     global _ENCODING, _MIN_TOKENS, _MAX_TOKENS
-    import tiktoken
-    _ENCODING = tiktoken.get_encoding(tokenizer_name)
+    _ENCODING = load_encoding(tokenizer_name)
     _MIN_TOKENS, _MAX_TOKENS = int(min_doc_tokens), max_doc_tokens
 
 
@@ -100,8 +118,7 @@ def encode_documents(texts: list[str]) -> tuple[np.ndarray, int]:
 def write_bin_meta(bin_path: Path, *, num_tokens: int, num_docs: int, tokenizer_name: str,
                    extra: dict[str, Any] | None = None, eot_token: int | None = None) -> None:
     if eot_token is None:
-        import tiktoken
-        eot_token = tiktoken.get_encoding(tokenizer_name).eot_token
+        eot_token = load_encoding(tokenizer_name).eot_token
     meta: dict[str, Any] = {"token_dtype": "uint32", "num_tokens": int(num_tokens), "num_docs": int(num_docs),
                             "tokenizer": tokenizer_name, "eot_token": int(eot_token)}
     meta.update(extra or {})

@@ -42,6 +42,7 @@ def nestor_tiny() -> ExperimentConfig:
     block = int(os.environ.get("DCLM_BLOCK_SIZE", "256"))
     steps = int(os.environ.get("DCLM_MAX_STEPS", "4"))
     backbone = tiny_backbone()
+    init_ckpt = os.environ.get("DCLM_INIT_CHECKPOINT", "").strip()     # weights-only start, as for the pretraining cells
     job = TrainJobConfig(
         name="nestor_tiny_train",
         model=SequenceModelConfig(
@@ -60,6 +61,7 @@ def nestor_tiny() -> ExperimentConfig:
         use_amp=True, loss=CausalLMLossConfig(), checkpoint_frequency=int(os.environ.get("DCLM_CKPT_FREQ", "2")),
         log_frequency=int(os.environ.get("DCLM_LOG_FREQ", "1")), distributed=DistributedConfig(enabled=True),
         wandb_project=None, seed=int(os.environ.get("DCLM_SEED", "42")),
+        resume_model_checkpoint=Path(init_ckpt) if init_ckpt else None, resume_strict=not init_ckpt,
     )
     return ExperimentConfig(name="nestor_tiny", jobs=[job],
                             output_root=Path(os.environ.get("NESTOR_OUTPUT_ROOT", "./outputs")))

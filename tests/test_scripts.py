@@ -1,0 +1,106 @@
+"""The command-line tools end to end on small files: text -> token file, corpus builders, held-out and long-context
+evaluation of a checkpoint, and the frozen-router verifier across a router-frozen continuation."""
+
+import gzip
+import json
+import time
+
+import numpy as np
+import pytest
+import torch
+
+from nestor_b200.data.datasets import write_synthetic_bin
+from nestor_b200.data.documents import document_spans, open_token_bin, read_bin_meta
+
+
+def test_text_to_token_file_offline(tmp_path, capsys):
+    """``preprocess_text_bin --tokenizer bytes``: jsonl, gzipped jsonl and plain text in one call; every kept document
+    is followed by the end-of-text id, short documents are dropped, long ones cut, and the sidecar describes the file."""
+
+    from nestor_b200.scripts import preprocess_text_bin
+    docs = ["alpha beta gamma", "x", "delta " * 20, "épsilon ζ"]
+    (tmp_path / "in").mkdir()
+    (tmp_path / "in" / "a.jsonl").write_text("\n".join(json.dumps({"text": d}) for d in docs[:2]) + "\n")
+    with gzip.open(tmp_path / "in" / "b.jsonl.gz", "wt", encoding="utf-8") as f:
+        f.write(json.dumps({"text": docs[2]}) + "\n")
+    (tmp_path / "in" / "c.txt").write_text(docs[3], encoding="utf-8")
+    out = tmp_path / "tokens.bin"
+    preprocess_text_bin.main([str(tmp_path / "in"), "--output", str(out), "--tokenizer", "bytes", "--workers", "2",
+                              "--min-doc-tokens", "2", "--max-doc-tokens", "40", "--batch-docs", "2"])
+    assert "3 documents" in capsys.readouterr().out
+    tokens, eot = open_token_bin(out)
+    meta = read_bin_meta(out)
+    assert eot == 256 and meta["tokenizer"] == "bytes" and meta["num_docs"] == 3
+    assert meta["num_tokens"] == len(tokens)
+    spans = document_spans(tokens, eot)
+    texts = [bytes(int(t) for t in tokens[a:b]).decode("utf-8") for a, b in spans]
+    assert texts == [docs[0], (docs[2])[:40], docs[3]]                   # the one-byte document is gone, the long one is cut
+    assert all(int(tokens[b]) == 256 for _, b in spans)
+
+
+def test_corpus_builders_from_the_command_line(tmp_path, capsys):
+    from nestor_b200.scripts import build_corpora
+    src = write_synthetic_bin(tmp_path / "src.bin", 64 * 200, 50_000, doc_len_range=(16, 64))
+    build_corpora.main(["seen-subset", "--source", str(src), "--output", str(tmp_path / "seen.bin"), "--block-size", "64",
+                        "--cpt-tokens", str(64 * 40), "--tokens-per-step", str(64 * 4)])
+    meta = json.loads(capsys.readouterr().out)
+    seen, _ = open_token_bin(tmp_path / "seen.bin")
+    assert len(seen) == meta["num_tokens"] == 64 * 40 and len(seen) % 64 == 0
+    target = write_synthetic_bin(tmp_path / "target.bin", 64 * 100, 50_000, seed=3, doc_len_range=(16, 64))
+    build_corpora.main(["replay-mix", "--target", str(target), "--replay", str(tmp_path / "seen.bin"), "--output",
+                        str(tmp_path / "mix.bin"), "--block-size", "64", "--target-share-pct", "75",
+                        "--mix-tokens", str(64 * 32), "--tokens-per-step", str(64 * 4)])
+    mix_meta = json.loads(capsys.readouterr().out)
+    mix, _ = open_token_bin(tmp_path / "mix.bin")
+    assert len(mix) == mix_meta["num_tokens"] == 64 * 32
+
+
+def _train(tmp_path, monkeypatch, root, steps):
+    from nestor_b200.cli import main
+    monkeypatch.setenv("NESTOR_OUTPUT_ROOT", str(tmp_path / root))
+    monkeypatch.setenv("DCLM_MAX_STEPS", str(steps))
+    assert main(["--experiment", "nestor_tiny"]) == 0
+    return sorted((tmp_path / root / "nestor_tiny").glob("*/checkpoints/model_final.pt"))[-1]
+
+
+def test_evaluation_tools_and_the_frozen_router_check(tmp_path, monkeypatch, capsys):
+    """Train two steps; score the checkpoint with the held-out and the long-context tools; continue from it with the
+    routers frozen (``NESTOR_FREEZE_ROUTERS=1``) and without, and let the verifier tell the two apart."""
+
+    from nestor_b200.scripts import check_frozen_routers, eval_heldout, eval_long_context
+    data = write_synthetic_bin(tmp_path / "train.bin", 64 * 60, 100_277, doc_len_range=(16, 64))
+    held = write_synthetic_bin(tmp_path / "held.bin", 64 * 16, 100_277, seed=9, doc_len_range=(48, 64))
+    monkeypatch.setenv("DCLM_DATA_PATH", str(data))
+    monkeypatch.setenv("DCLM_BLOCK_SIZE", "64")
+    monkeypatch.setenv("DCLM_CKPT_FREQ", "100")
+    base = _train(tmp_path, monkeypatch, "base", 2)
+    capsys.readouterr()
+
+    eval_heldout.main(["--experiment", "nestor_tiny", "--checkpoint", str(base), "--data", str(held), "--block-size", "64",
+                       "--batch", "2", "--max-windows", "6", "--output", str(tmp_path / "heldout.json")])
+    res = json.loads((tmp_path / "heldout.json").read_text())
+    assert res["windows"] == 6 and res["tokens"] == 6 * 63 and 5.0 < res["cross_entropy"] < 13.0
+    assert json.loads(capsys.readouterr().out)["cross_entropy"] == res["cross_entropy"]
+
+    eval_long_context.main(["--experiment", "nestor_tiny", "--checkpoint", str(base), "--data", str(held), "--seq-len", "48",
+                            "--documents", "4", "--head-chunk", "16", "--output", str(tmp_path / "long.json")])
+    long = json.loads((tmp_path / "long.json").read_text())
+    assert long and 5.0 < float(long.get("cross_entropy", long.get("mean_nll", 0.0)) or 0.0) < 13.0
+
+    # continue from the checkpoint, once with frozen routers and once without
+    monkeypatch.setenv("DCLM_INIT_CHECKPOINT", str(base))
+    monkeypatch.setenv("NESTOR_FREEZE_ROUTERS", "1")
+    time.sleep(1.1)
+    frozen = _train(tmp_path, monkeypatch, "frozen", 2)
+    monkeypatch.delenv("NESTOR_FREEZE_ROUTERS")
+    time.sleep(1.1)
+    free = _train(tmp_path, monkeypatch, "free", 2)
+    capsys.readouterr()
+    assert check_frozen_routers.main([str(base), str(frozen)]) == 0
+    assert ", 0 changed" in capsys.readouterr().out
+    assert check_frozen_routers.main([str(base), str(free)]) == 1
+    assert "changed:" in capsys.readouterr().out
+    # the frozen continuation did train everything else
+    a = torch.load(base, weights_only=False)["model"]
+    b = torch.load(frozen, weights_only=False)["model"]
+    assert any(not torch.equal(a[k], b[k]) for k in a if "attention_groups" in k)
