@@ -14,6 +14,13 @@ Forward semantics follow the reference's registered-experiment path
   reads see only the aggregates, the final head read sees every export.
 * Baseline (Kimi) blocks are the single-column special case with a plain running sum.
 
+Beside that path the block also runs the reference's other topologies: the merged recurrence for multi-column
+blocks that keep no streams (``Block._merged_layers``: ``attn_res_kimi``, blocks left out of
+``block_column_blocks``, the leading layers under ``block_column_trailing_layers``), column-resolved sublayer reads
+(``Block._forward_wide_reads``), the plain residual stream (``Block._forward_projection``) and the within-block
+history attention (``Block._forward_history_attention``); causal or bidirectional attention; pools or banks (shared
+and column-specific experts, gated or pointwise).
+
 All tensors are flattened to ``[T, ...]`` with ``T = B * S``; residual streams are fp32
 and matrix products run in the compute dtype ``cd``.
 """
