@@ -144,8 +144,14 @@ def iter_document_texts(path: Path, text_key: str = "text") -> Iterator[str]:
     if name.endswith(".gz"):
         handle: Any = gzip.open(path, "rt", encoding="utf-8")
     elif name.endswith(".zst"):
-        import zstandard as zstd
-        handle = io.TextIOWrapper(zstd.ZstdDecompressor().stream_reader(open(path, "rb")), encoding="utf-8")
+        try:
+            import zstandard as zstd
+            raw: Any = zstd.ZstdDecompressor().stream_reader(open(path, "rb"))
+        except ImportError:
+            # no zstandard package: Arrow ships the same codec and reads the stream as well
+            import pyarrow as pa
+            raw = pa.CompressedInputStream(pa.OSFile(str(path), "rb"), "zstd")
+        handle = io.TextIOWrapper(raw, encoding="utf-8")
     else:
         handle = open(path, encoding="utf-8")
     with handle:

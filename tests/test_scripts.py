@@ -104,3 +104,36 @@ def test_evaluation_tools_and_the_frozen_router_check(tmp_path, monkeypatch, cap
     a = torch.load(base, weights_only=False)["model"]
     b = torch.load(frozen, weights_only=False)["model"]
     assert any(not torch.equal(a[k], b[k]) for k in a if "attention_groups" in k)
+
+
+def test_dclm_shard_tree_to_token_file(tmp_path, capsys):
+    """``preprocess_dclm`` walks ``global-shard_*/local-shard_*/shard_*.jsonl.zst`` in sorted order, reads only the
+    chosen global shards and stops at the token target; zstd streams are read with the ``zstandard`` package or, when
+    that is missing, through Arrow's codec."""
+
+    pa = pytest.importorskip("pyarrow")
+    from nestor_b200.scripts import preprocess_dclm
+    root = tmp_path / "dclm"
+    texts = {}
+    for g in (1, 2):
+        for l in (0, 1):
+            d = root / f"global-shard_{g:02d}_of_10" / f"local-shard_{l}_of_10"
+            d.mkdir(parents=True)
+            body = "".join(json.dumps({"text": f"g{g} l{l} doc{i} " + "w" * 10}) + "\n" for i in range(3))
+            texts[(g, l)] = body
+            with pa.CompressedOutputStream(pa.OSFile(str(d / "shard_00000000_processed.jsonl.zst"), "wb"), "zstd") as f:
+                f.write(body.encode("utf-8"))
+    out = tmp_path / "dclm.bin"
+    preprocess_dclm.main(["--dclm-root", str(root), "--out", str(out), "--global-shards", "2", "--tokenizer", "bytes",
+                          "--workers", "1"])
+    tokens, eot = open_token_bin(out)
+    spans = document_spans(tokens, eot)
+    docs = [bytes(int(t) for t in tokens[a:b]).decode() for a, b in spans]
+    assert len(docs) == 6 and all(d.startswith("g2 ") for d in docs)          # only global shard 2, both local shards
+    assert docs[0].startswith("g2 l0 doc0") and docs[3].startswith("g2 l1 doc0")
+    capsys.readouterr()
+    preprocess_dclm.main(["--dclm-root", str(root), "--out", str(out), "--tokenizer", "bytes", "--workers", "1",
+                          "--target-tokens", "30"])
+    assert read_bin_meta(out)["num_tokens"] >= 30                              # (checked once per batch of documents)
+    with pytest.raises(SystemExit):
+        preprocess_dclm.main(["--dclm-root", str(tmp_path / "nothing"), "--out", str(out)])
