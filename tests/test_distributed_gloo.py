@@ -17,6 +17,24 @@ from nestor_b200.configs import MuonAdamWConfig
 from nestor_b200.models.tags import ADAMW_DECAY, muon_matrix, tag
 
 
+def _collect(procs, q, n, timeout=240.0):
+    """``n`` results from the workers' queue, without waiting forever on a worker that died or hangs."""
+
+    import time
+    results, deadline = [], time.monotonic() + timeout
+    while len(results) < n:
+        if not q.empty():
+            results.append(q.get())
+        elif any(p.exitcode not in (None, 0) for p in procs) or time.monotonic() > deadline:
+            for p in procs:
+                if p.is_alive():
+                    p.terminate()
+            raise AssertionError(f"workers failed or timed out (exit codes {[p.exitcode for p in procs]})")
+        else:
+            time.sleep(0.05)
+    return results
+
+
 def _free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -95,7 +113,7 @@ def test_two_ranks_match_the_single_process_run(mode):
     procs = [ctx.Process(target=_worker, args=(r, world, port, q, mode)) for r in range(world)]
     for p in procs:
         p.start()
-    results = sorted((q.get() for _ in range(world)), key=lambda t: t[0])
+    results = sorted(_collect(procs, q, world), key=lambda t: t[0])
     for p in procs:
         p.join(60)
         assert p.exitcode == 0
@@ -122,9 +140,10 @@ def test_missing_rank_is_detected_by_timeout():
     q = ctx.SimpleQueue()
     p = ctx.Process(target=_lonely_rank, args=(_free_port(), q))
     p.start()
-    p.join(60)
+    (outcome,) = _collect([p], q, 1, timeout=60.0)
+    p.join(30)
     assert not p.is_alive()
-    assert q.get() != "joined"
+    assert outcome != "joined"
 
 
 # ------------------------------------------------------------------ the whole trainer on two ranks
@@ -181,7 +200,7 @@ def test_trainer_on_two_ranks_matches_accumulation_in_one_process(sharded, monke
     procs = [ctx.Process(target=_trainer_rank, args=(r, world, port, q, sharded)) for r in range(world)]
     for p in procs:
         p.start()
-    results = sorted((q.get() for _ in range(world)), key=lambda t: t[0])
+    results = sorted(_collect(procs, q, world), key=lambda t: t[0])
     for p in procs:
         p.join(120)
         assert p.exitcode == 0
