@@ -30,4 +30,5 @@ export NESTOR_MFU_PEAK_TFLOPS="${NESTOR_MFU_PEAK_TFLOPS:-2250}"       # B200 den
 #   NESTOR_B200_NVLS=0           keep the in-kernel collectives on plain peer loads / stores (no multimem)
 #   NESTOR_B200_STRICT=1         a shape beyond a kernel's built-in limit raises instead of running the PyTorch statement
 #   NESTOR_B200_BOUNDS_CHECK=1   load the index-checking build of the kernel library
+#   NESTOR_B200_POINTWISE_BANK=0 banks of pointwise (non-SwiGLU) experts run the PyTorch statement instead of the grouped kernels
 #   NESTOR_DEPTH_READ_KEEP_H=0   do not keep the depth-read mixture for the backward (one [T, d] fp32 row per read)

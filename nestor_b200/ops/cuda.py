@@ -307,9 +307,65 @@ class _ExpertBank(torch.autograd.Function):
         return dx, dweights, d_up, d_gate, d_down, None, None
 
 
+class _PointwiseBank(torch.autograd.Function):
+    """Routed bank of pointwise experts ``down(act(up(x)))``: the same dispatch gather, grouped products and weighted
+    combine as the SwiGLU bank, with the activation (and its derivative) as one elementwise pass between the two
+    products instead of a fused epilogue."""
+
+    @staticmethod
+    def forward(ctx, x, weights, w_up, w_down, plan: ExpertPlan, group: int, activation: str):
+        T, d = x.shape
+        E, _, h = w_up.shape
+        act = ref.POINTWISE_ACTIVATIONS[activation]
+        xs = gather_rows(x, plan.order, div=plan.slots)                       # dispatch gather [n, d]
+        # the up product reads its bank K-major ([E, h, d]); the transposed copy is per call and bank-sized
+        u = G.gemm_rows(xs, w_up.transpose(1, 2).contiguous(), offsets=plan.offsets, groups=E)      # [n, h]
+        a = G.rows_buffer(plan.n, h, BF16, x.device)
+        a.copy_(act(u))
+        y = G.gemm_rows(a, w_down, offsets=plan.offsets, groups=E, b_mn=True)                        # [n, d]
+        wf = weights.float().contiguous().view(-1)
+        out = combine_rows(y, plan.inv, wf, group, T * (plan.slots // group))
+        ctx.save_for_backward(xs, u, a, y, wf, w_up, w_down)
+        ctx.plan, ctx.group, ctx.T, ctx.x_dtype, ctx.w_dtype, ctx.act = plan, group, T, x.dtype, weights.dtype, act
+        ctx.w_refs = (w_up, w_down)
+        return out.view(T, plan.slots // group, d)
+
+    @staticmethod
+    def backward(ctx, dout):
+        xs, u, a, y, wf, w_up, w_down = ctx.saved_tensors
+        plan, group, T = ctx.plan, ctx.group, ctx.T
+        E, d, h = w_up.shape
+        g2 = dout.contiguous().view(-1, d).float()
+        dy, dw_sorted = combine_bwd(g2, y, plan.order, wf, group, need_dw=ctx.needs_input_grad[1])
+        da = G.gemm_rows(dy, w_down, offsets=plan.offsets, groups=E)            # dA = dY . Wd^T, Wd [E, h, d] K-major
+        with torch.enable_grad():
+            u32 = u.float().requires_grad_(True)
+            slope = torch.autograd.grad(ctx.act(u32), u32, da.float())[0]
+        du = G.rows_buffer(plan.n, h, BF16, dy.device)
+        du.copy_(slope)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dxs = G.gemm_rows(du, w_up, offsets=plan.offsets, groups=E)                             # [n, d]
+            direct = ctx.x_dtype in (torch.float32, BF16)
+            dx = combine_rows(dxs, plan.inv, None, plan.slots, T, out_dtype=ctx.x_dtype if direct else torch.float32)
+            dx = dx if direct else dx.to(ctx.x_dtype)
+        dweights = None
+        if dw_sorted is not None:
+            dweights = dw_sorted.view(T, plan.slots).to(ctx.w_dtype)
+        wu, wd = ctx.w_refs
+        d_down = _wgrad(a, dy, wd, offsets=plan.offsets, groups=E) if ctx.needs_input_grad[3] else None
+        d_up = _wgrad(xs, du, wu, offsets=plan.offsets, groups=E) if ctx.needs_input_grad[2] else None
+        return dx, dweights, d_up, d_down, None, None, None
+
+
+POINTWISE_BANK_KERNELS = os.environ.get("NESTOR_B200_POINTWISE_BANK", "1") == "1"
+
+
 def expert_bank(x, plan, weights, w_up, w_gate, w_down, cd, group, activation="swiglu"):
     if activation != "swiglu":
-        # the grouped GEMM's fused epilogue is the SwiGLU product; a pointwise bank runs the PyTorch statement
+        if POINTWISE_BANK_KERNELS and BANK_SHARDS is None:
+            return _PointwiseBank.apply(x, weights, w_up, w_down, plan, group, activation)
+        # (rank-sharded banks stage their weights inside the SwiGLU launches only)
         _oracle_path("expert_bank", f"pointwise activation {activation!r}")
         return ref.expert_bank(x, plan, weights, w_up, None, w_down, cd, group, activation)
     return _ExpertBank.apply(x, weights, w_up, w_gate, w_down, plan, group)
