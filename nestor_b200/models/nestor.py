@@ -727,10 +727,10 @@ class Block(nn.Module):
             return self._forward_history_attention(x, ctx, cd, cache, idx)
         layer_aux = []
         for li, layer in enumerate(self.layers):
-            n = ops.rmsnorm(x, layer.attn_norm.weight, layer.attn_norm.eps, cd)
+            n = ops.stream_rmsnorm(x, layer.attn_norm.weight, layer.attn_norm.eps, cd)
             attn = layer.attention(n, ctx, cd) if cache is None else layer.attention_step(n, ctx, cd, cache[li])
             x = self._apply_residual(x, layer.drop(attn.float().sum(dim=1), ctx.B))
-            n = ops.rmsnorm(x, layer.mlp_norm.weight, layer.mlp_norm.eps, cd)
+            n = ops.stream_rmsnorm(x, layer.mlp_norm.weight, layer.mlp_norm.eps, cd)
             priv, shared, path, aux = layer.experts(n, ctx, cd)
             x = self._apply_residual(x, layer.drop(self._merged_expert_update(priv, shared, path, cd), ctx.B))
             layer_aux.append(aux)
@@ -754,16 +754,16 @@ class Block(nn.Module):
         layer_aux = []
         for li, layer in enumerate(self.layers):
             h = ops.depth_attention(history, layer.attn_query.weight, layer.attn_key_norm.weight)
-            n = ops.rmsnorm(h, layer.attn_norm.weight, layer.attn_norm.eps, cd)
+            n = ops.stream_rmsnorm(h, layer.attn_norm.weight, layer.attn_norm.eps, cd)
             attn = layer.attention(n, ctx, cd) if cache is None else layer.attention_step(n, ctx, cd, cache[li])
             history.append(layer.drop(attn.float().sum(dim=1), ctx.B))
             h = ops.depth_attention(history, layer.mlp_query.weight, layer.mlp_key_norm.weight)
-            n = ops.rmsnorm(h, layer.mlp_norm.weight, layer.mlp_norm.eps, cd)
+            n = ops.stream_rmsnorm(h, layer.mlp_norm.weight, layer.mlp_norm.eps, cd)
             priv, shared, path, aux = layer.experts(n, ctx, cd)
             history.append(layer.drop(self._merged_expert_update(priv, shared, path, cd), ctx.B))
             layer_aux.append(aux)
         out = ops.depth_attention(history, self.out_query.weight, self.out_key_norm.weight)
-        out = ops.rmsnorm(out, self.out_norm.weight, self.out_norm.eps, torch.float32)
+        out = ops.stream_rmsnorm(out, self.out_norm.weight, self.out_norm.eps, torch.float32)
         baux = {"group_idx": idx, "layers": layer_aux}
         scores = self.__dict__.pop("_last_scores", None)
         if self.spec.G > 1 and scores is not None:
@@ -936,7 +936,7 @@ class Nestor(Backbone):
         """The normalised head input: the final depth read over every export, or (projection mode) the stream itself."""
 
         if not self.depth_reads:
-            return ops.rmsnorm(x, self.final_norm.weight, self.final_norm.eps, cd)
+            return ops.stream_rmsnorm(x, self.final_norm.weight, self.final_norm.eps, cd)
         read_sources = wide if self.column_mode else narrow
         return ops.depth_read_norm(read_sources, self.final_depth_read.query, self.final_depth_read.value_gains,
                                    self.final_norm.weight, self.final_depth_read.eps, self.final_norm.eps, cd)

@@ -40,10 +40,10 @@ def launch_count() -> int:
 
 
 def oracle_path_report() -> dict[str, int]:
-    """Calls that left the kernel library because a shape crossed a kernel's built-in limit (op name -> count).
-
-    Such calls warn the first time and raise under ``NESTOR_B200_STRICT=1``; an empty dict means every op of the
-    process ran on the sm_100a kernels.
+    """Calls that ran as PyTorch statements on CUDA tensors (op name -> count): a shape or option beyond a kernel's
+    built-in limits (these warn the first time and raise under ``NESTOR_B200_STRICT=1``), or an op that has no fused
+    kernel (the plain-residual and history-attention topologies). An empty dict means every op of the process ran
+    on the sm_100a kernels.
     """
 
     return cuda_ops().oracle_path_report() if _cuda_mod is not None else {}
@@ -95,10 +95,31 @@ def _dispatch(name: str):
     return op
 
 
-# The two halves of ``depth_read_norm`` as separate equations: test oracles only (the model calls the fused op).
+def _eager(name: str, report_as: str):
+    """An op without a fused kernel: the PyTorch statement on any device, counted in ``oracle_path_report()`` when
+    it runs on CUDA tensors beside the kernels (the options that use it are outside the registered cells)."""
+
+    ref_fn = getattr(_ref, name)
+
+    def op(*args, **kwargs):
+        first = next(a for a in list(args) + list(kwargs.values()) if isinstance(a, torch.Tensor)
+                     or (isinstance(a, (list, tuple)) and len(a) > 0 and isinstance(a[0], torch.Tensor)))
+        probe = first[0] if isinstance(first, (list, tuple)) else first
+        if use_kernels(probe):
+            cuda_ops().note_eager(report_as)
+        return ref_fn(*args, **kwargs)
+
+    op.__name__ = name
+    op.__doc__ = ref_fn.__doc__
+    return op
+
+
+# The two halves of ``depth_read_norm`` as separate equations: test oracles (the registered cells call the fused op).
 rmsnorm = _ref.rmsnorm
 depth_read = _ref.depth_read
-depth_attention = _ref.depth_attention      # within-block history attention: plain PyTorch arithmetic on any device
+# what the plain-residual and history-attention topologies call: no fused kernel, counted when run on a GPU
+stream_rmsnorm = _eager("rmsnorm", "rmsnorm")
+depth_attention = _eager("depth_attention", "depth_attention")
 depth_read_norm = _dispatch("depth_read_norm")
 grad_sink = _dispatch("grad_sink")
 mid_source = _dispatch("mid_source")

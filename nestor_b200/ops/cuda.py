@@ -41,8 +41,16 @@ def _oracle_path(op: str, why: str) -> None:
     _oracle_calls[op] = _oracle_calls.get(op, 0) + 1
 
 
+def note_eager(op: str) -> None:
+    """Count a call of an op that has no fused kernel (a model option outside the registered cells runs it as plain
+    PyTorch arithmetic on the GPU by design: no warning, but it shows in the report)."""
+
+    _oracle_calls[op] = _oracle_calls.get(op, 0) + 1
+
+
 def oracle_path_report() -> dict[str, int]:
-    """How many calls of each op left the kernel library because of a shape limit since import."""
+    """How many calls of each op ran as PyTorch statements on CUDA tensors since import: shapes or options beyond a
+    kernel's limits, and ops without a fused kernel."""
 
     return dict(_oracle_calls)
 from nestor_b200.ops.reference import ColumnPlan, ExpertPlan
