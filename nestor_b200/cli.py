@@ -57,6 +57,9 @@ def main(argv: list[str] | None = None) -> int:
         print(f"Error: {exc}")
         return 1
     print(f"Running experiment: {args.experiment}")
+    from nestor_b200.utils.flags import report_reference_flags
+    from nestor_b200.utils.logging import get_logger
+    report_reference_flags(get_logger("nestor_b200"))
     experiment = fn()
     experiment.name = args.experiment
     from nestor_b200.pipelines import EvalPipeline, TrainPipeline

@@ -74,3 +74,34 @@ def test_train_job_then_eval_job(tmp_path, monkeypatch):
     metrics = json.loads(results[0].read_text())["held_out"]
     assert 5.0 < metrics["cross_entropy"] < 13.0 and metrics["tokens"] > 0
     assert (results[0].parent / "eval_results.md").read_text().startswith("| eval | metric | value |")
+
+
+def test_reference_flags_are_reported_at_start_up(caplog):
+    """A launcher written for the reference exports its fast-path switches; here they select nothing, and the start-up
+    report says so (and warns about values that ask for a mode with a different equivalent)."""
+
+    import logging
+    from nestor_b200.utils.flags import NO_EFFECT, classify, report_reference_flags
+    env = {"NESTOR_TRITON_PACKED_ATTN": "1", "NESTOR_COMPILE": "0", "NESTOR_MOE_GROUPED_MM": "1", "NESTOR_DDP": "0",
+           "NESTOR_MUON_SHARD": "1", "NESTOR_STACKED_EXPERT_BANKS": "1", "NESTOR_COLUMN_SLOT_UPDATES": ""}
+    found = classify(env)
+    assert set(found["no_effect"]) == {"NESTOR_TRITON_PACKED_ATTN", "NESTOR_COMPILE", "NESTOR_MOE_GROUPED_MM"}
+    assert set(found["different"]) == {"NESTOR_DDP=0"}
+    logger = logging.getLogger("nestor_b200.test_flags")
+    logger.propagate = True
+    with caplog.at_level(logging.INFO, logger="nestor_b200.test_flags"):
+        report_reference_flags(logger, env)
+    text = caplog.text
+    assert "NESTOR_TRITON_PACKED_ATTN" in text and "no effect here" in text and "ZeRO-1" in text
+    assert classify({}) == {"no_effect": {}, "different": {}}
+    # nothing this package reads is listed as having no effect
+    import re
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent / "nestor_b200"
+    read = set()
+    for f in root.rglob("*.py"):
+        if f.name != "flags.py":
+            read |= set(re.findall(r'"(NESTOR_[A-Z0-9_]+)"', f.read_text()))
+    # (two are named elsewhere without being acted on: the trainer's note about the bf16 mode, and the variable the
+    # long-context protocol exports for launchers of the reference)
+    assert not (read & set(NO_EFFECT)) - {"NESTOR_BF16_MASTER", "NESTOR_GATHERED_CAP_BUCKET"}
