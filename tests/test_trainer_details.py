@@ -179,3 +179,55 @@ def test_execution_flags_leave_the_training_trajectory_unchanged(flags, _plain_r
         assert moved < 1e-4, moved
     else:
         assert torch.equal(got, want), float((got - want).abs().max())
+
+
+def test_evaluation_during_training_and_eval_job_submission(tmp_path, monkeypatch):
+    """A train job with an eval suite scores it every ``NESTOR_EVAL_FREQ`` steps (JSON per evaluation under
+    ``evals/``, training mode restored afterwards); ``eval_submit_scripts`` hands each new checkpoint to the
+    scheduler, and a missing ``sbatch`` only logs a warning."""
+
+    import json
+    import subprocess
+    from nestor_b200.configs import DataLoaderConfig, DclmDatasetConfig, EvalSuiteConfig, LanguageModelingEvalConfig
+    from nestor_b200.data.datasets import write_synthetic_bin
+    from nestor_b200.experiments.tiny import nestor_tiny
+    from nestor_b200.pipelines import TrainPipeline
+    data = write_synthetic_bin(tmp_path / "train.bin", 64 * 40, 100_277, doc_len_range=(16, 64))
+    held = write_synthetic_bin(tmp_path / "held.bin", 64 * 8, 100_277, seed=4, doc_len_range=(16, 64))
+    monkeypatch.setenv("DCLM_DATA_PATH", str(data))
+    monkeypatch.setenv("DCLM_BLOCK_SIZE", "64")
+    monkeypatch.setenv("DCLM_MAX_STEPS", "2")
+    monkeypatch.setenv("DCLM_CKPT_FREQ", "1")
+    monkeypatch.setenv("NESTOR_EVAL_FREQ", "1")
+    monkeypatch.setenv("NESTOR_OUTPUT_ROOT", str(tmp_path / "out"))
+    exp = nestor_tiny(); exp.name = "nestor_tiny"
+    suite = EvalSuiteConfig(evals=[LanguageModelingEvalConfig(
+        name="held_out", dataset_config=DclmDatasetConfig(data_path=held, block_size=64),
+        dataloader_config=DataLoaderConfig(batch_size=2, num_workers=0))])
+    script = tmp_path / "eval_job.sh"
+    script.write_text("#!/bin/bash\n")
+    exp.jobs[0] = dc.replace(exp.jobs[0], eval_suite=suite, eval_submit_scripts=[(script, 1)])
+    submitted = []
+
+    real_run = subprocess.run
+
+    def fake_run(cmd, **kw):
+        if cmd[0] != "sbatch":
+            return real_run(cmd, **kw)
+        submitted.append(cmd)
+        if len(submitted) == 2:
+            raise FileNotFoundError("sbatch")                 # no scheduler on this machine: a warning, not an error
+        return subprocess.CompletedProcess(cmd, 0, b"", b"")
+
+    monkeypatch.setattr(subprocess, "run", fake_run)
+    pipe = TrainPipeline.from_config(job_config=exp.jobs[0], experiment_config=exp)
+    trainer = pipe.setup()
+    trainer.train()
+    assert trainer.model.training and trainer.global_step == 2
+    files = sorted((pipe.ctx.run_dir / "evals").glob("eval_step_*.json"))
+    assert [f.name for f in files] == ["eval_step_00000001.json", "eval_step_00000002.json"]
+    metrics = json.loads(files[-1].read_text())["held_out"]
+    assert 5.0 < metrics["cross_entropy"] < 13.0 and metrics["tokens"] > 0
+    assert len(submitted) == 2 and submitted[0][0] == "sbatch" and submitted[0][1] == str(script)
+    assert submitted[0][2].endswith("model_00000001.pt") and submitted[1][2].endswith("model_00000002.pt")
+    pipe.ctx.close()
