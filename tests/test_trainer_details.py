@@ -231,3 +231,35 @@ def test_evaluation_during_training_and_eval_job_submission(tmp_path, monkeypatc
     assert len(submitted) == 2 and submitted[0][0] == "sbatch" and submitted[0][1] == str(script)
     assert submitted[0][2].endswith("model_00000001.pt") and submitted[1][2].endswith("model_00000002.pt")
     pipe.ctx.close()
+
+
+def test_throughput_and_utilisation_metrics(monkeypatch):
+    """The step metrics follow from tokens per step, FLOPs per token, the step time and the peak: tokens/s is the
+    whole job's, TFLOP/s and the utilisation are per GPU, the running average excludes the first (warm-up) step when a
+    steady-state clock exists; ``NESTOR_MFU_FLOPS_PER_STEP`` pins the FLOPs of one rank's micro-batch."""
+
+    from nestor_b200.experiments.tiny import nestor_tiny
+    from nestor_b200.train.trainer import Trainer
+    from nestor_b200.train import trainer as T
+    monkeypatch.setenv("DCLM_BLOCK_SIZE", "64")
+    job = dc.replace(nestor_tiny().jobs[0], grad_accum_steps=4)
+    tr = Trainer(job, Model.from_config(job.model), [], device=torch.device("cpu"))
+    tr.tokens_per_micro = 2 * 64
+    tr.world = 8                                                 # as if eight ranks ran this step
+    m: dict = {}
+    flops_tok, peak, dt = 3.0e6, 2.0e12, 0.5
+    t0 = T.PROCESS_START                                         # the process clock the run average is measured on
+    tr._add_mfu(m, flops_tok, peak, dt, now=t0 + 110.0, steps=5, t_steady=t0 + 100.0)
+    tokens_step = 128 * 4 * 8
+    assert m["tokens_per_sec"] == tokens_step / dt and m["samples_per_sec"] == m["tokens_per_sec"] / 2
+    per_gpu = flops_tok * tokens_step / 8
+    assert m["tflops_per_gpu"] == pytest.approx(per_gpu / dt / 1e12) and m["mfu_instant"] == pytest.approx(per_gpu / dt / peak)
+    assert m["mfu_runavg_excl_init"] == pytest.approx(per_gpu * 4 / 10.0 / peak)          # four steps in ten seconds
+    assert m["mfu_runavg_incl_init"] == pytest.approx(per_gpu * 5 / 110.0 / peak) and "mem_peak_alloc_gib" not in m
+    first: dict = {}
+    tr._add_mfu(first, flops_tok, peak, dt, now=t0 + 100.0, steps=1, t_steady=t0 + 100.0)
+    assert "mfu_runavg_excl_init" not in first                   # nothing but the warm-up step so far
+    tr.tokens_per_micro = 0
+    empty: dict = {}
+    tr._add_mfu(empty, flops_tok, peak, dt, now=1.0, steps=1, t_steady=None)
+    assert empty == {}
