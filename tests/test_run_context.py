@@ -41,7 +41,12 @@ def test_run_directory_sidecars(tmp_path, monkeypatch):
     with zipfile.ZipFile(ctx.run_dir / "source_snapshot.zip") as z:
         names = z.namelist()
     assert any(n.endswith("nestor_b200/models/nestor.py") for n in names)
-    assert not any("_work/" in n or "gpurun_out/" in n or n.endswith(".so") for n in names)
+    # nothing from the scratch folders the repository ignores, and no built artefacts
+    from pathlib import Path
+    ignore = (Path(__file__).resolve().parent.parent / ".gitignore").read_text().splitlines()
+    scratch = [line.strip().strip("/") for line in ignore if line.strip().endswith("/") and not line.startswith("#")]
+    assert scratch and not any(f"{d}/" in n for d in scratch for n in names if d not in ("build",))
+    assert not any(n.endswith(".so") for n in names)
     ctx.close()
 
 
