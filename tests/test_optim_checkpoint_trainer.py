@@ -266,3 +266,47 @@ def test_configuration_variants_train_and_checkpoint(variant, tmp_path, monkeypa
     payload = torch.load(ckpt, weights_only=False)
     assert payload["step"] == 3 and set(payload["model"]) == set(state)
     assert all(torch.allclose(payload["model"][k].float(), state[k]) for k in state if state[k].is_floating_point())
+
+
+@pytest.mark.parametrize("family", ["nestor", "moe"])
+def test_bf16_compute_copy_routes_gradients_into_the_fp32_arena(family, tiny_scale):
+    """The bf16 compute copy on CPU: strided stack / fused / concatenated views of the copy feed the ops, and their
+    gradients come back through the views into the fp32 gradient arena. With masters that are exactly representable
+    in bf16 this is the same computation as an fp32 arena whose ops round the weights per use, so loss and gradients
+    agree to the last bits; the copy follows the masters on ``refresh_compute``."""
+
+    from nestor_b200.models import Model
+    from nestor_b200.train.losses import CausalLMLoss
+    cfg = tiny_scale.build_experiment(family, "tiny").jobs[0].model
+    ids = torch.randint(0, 100263, (2, 48))
+    results = {}
+    for mode in ("copy", "per_use"):
+        torch.manual_seed(0)
+        m = Model.from_config(cfg).eval()
+        with torch.no_grad():
+            for n, p in m.named_parameters():
+                if "query" in n:
+                    p.normal_(0, 0.3)
+                p.copy_(p.to(torch.bfloat16).float())                 # masters on the bf16 grid
+        m.compute_dtype, m.fused_head = torch.bfloat16, False
+        arena = ParamArena(m, compute_dtype=torch.bfloat16 if mode == "copy" else torch.float32)
+        if mode == "copy":
+            assert arena.compute is not arena.master and arena.compute.dtype == torch.bfloat16
+            assert torch.equal(arena.compute.float(), arena.master)
+            layer = m.backbone.blocks[0].layers[0]
+            w = layer.qkv_weight()                                    # a strided view of the copy, not a new tensor
+            first = arena.slot(layer.attention_groups[0].q_proj.weight)
+            assert w.dtype == torch.bfloat16 and w._nb_grad.dtype == torch.float32
+            assert w.untyped_storage().data_ptr() == arena.compute.untyped_storage().data_ptr()
+            assert w.storage_offset() == first.offset
+        out = m(ids)
+        loss = CausalLMLoss()(out.pred, ids, out.aux).total
+        loss.backward()
+        results[mode] = (float(loss), arena.grad.clone(), arena)
+    (la, ga, arena), (lb, gb, _) = results["copy"], results["per_use"]
+    assert abs(la - lb) < 1e-6
+    assert float(ga.norm()) > 0 and float((ga - gb).norm() / gb.norm()) < 1e-5
+    arena.master.mul_(0.5)
+    arena.refresh_compute()
+    assert torch.equal(arena.compute.float(), arena.master.to(torch.bfloat16).float())
+    assert sum(n for _, n in arena.buckets(1000)) == arena.numel and max(n for _, n in arena.buckets(1000)) <= 1000
