@@ -624,8 +624,8 @@ class Block(nn.Module):
         """Column mode whose sublayer reads are column-resolved (``block_column_head_only=False``): ``sources`` holds
         every export of the completed blocks, and each read appends this block's live streams to them
         (reference ``nestor/backbones/nestor.py:7172-7254``, ``7301-7318``). A merged prefix
-        (``block_column_trailing_layers``) only enters the aggregate handed to the next block's router. The per-layer
-        recompute regions are not applied here; block-level recomputation wraps the whole block as usual."""
+        (``block_column_trailing_layers``) only enters the aggregate handed to the next block's router. Under the
+        recompute ladder every layer is one region (the rungs that split a layer fall back to that)."""
 
         s = self.spec
         rung = RecomputeLadder.current(self.training and cache is None)
@@ -635,19 +635,16 @@ class Block(nn.Module):
         n_merged = s.merged_prefix
         if n_merged:
             prefix, layer_aux = self._merged_layers(n_merged, sources, ctx, cd, cache, key_cache)
-        streams: Tensor | None = None
-        running: Tensor | None = None
-        for li, layer in enumerate(self.layers):
-            if li < n_merged:
-                continue
-            read = list(sources) if streams is None else [*sources, *self._live_sources(streams)]
+
+        def one_layer(layer, li, streams, running, *srcs):
+            read = list(srcs) if streams is None else [*srcs, *self._live_sources(streams)]
             n = ops.depth_read_norm(read, layer.kimi_attn_read.query, layer.kimi_attn_read.value_gains,
                                     layer.attn_norm.weight, layer.kimi_attn_read.eps, layer.attn_norm.eps, cd, **kc)
             attn = layer.attention(n, ctx, cd) if cache is None else layer.attention_step(n, ctx, cd, cache[li])
             if layer.drop_path > 0.0 and self.training:
                 attn = layer.drop(attn, ctx.B)
             mid = attn.float() if streams is None else streams + attn.float()
-            n = ops.depth_read_norm([*sources, *self._live_sources(mid)], layer.kimi_mlp_read.query,
+            n = ops.depth_read_norm([*srcs, *self._live_sources(mid)], layer.kimi_mlp_read.query,
                                     layer.kimi_mlp_read.value_gains, layer.mlp_norm.weight, layer.kimi_mlp_read.eps,
                                     layer.mlp_norm.eps, cd, **kc)
             priv, shared, path, aux = layer.experts(n, ctx, cd)
@@ -655,6 +652,19 @@ class Block(nn.Module):
                 shared = layer.drop(shared, ctx.B)
                 priv = None if priv is None else layer.drop(priv, ctx.B)
             streams, running = ops.layer_combine(attn, priv, shared, path, streams, running, cd)
+            return streams, running, aux
+
+        streams: Tensor | None = None
+        running: Tensor | None = None
+        for li, layer in enumerate(self.layers):
+            if li < n_merged:
+                continue
+            # every rung but the block-level one makes the layer a recomputed region here (no split halves)
+            if rung.on and not rung.block:
+                from torch.utils.checkpoint import checkpoint
+                streams, running, aux = checkpoint(one_layer, layer, li, streams, running, *sources, use_reentrant=False)
+            else:
+                streams, running, aux = one_layer(layer, li, streams, running, *sources)
             layer_aux.append(aux)
         exports = self._live_sources(streams)
         agg = exports[-1] if (s.k == 1 or s.column_aggregate) else streams.mean(dim=1)
@@ -696,19 +706,33 @@ class Block(nn.Module):
 
         rung = RecomputeLadder.current(self.training and cache is None)
         kc = {} if key_cache is None or rung.any else {"key_cache": key_cache}
+
+        def attn_part(layer, li, *tensors):
+            # tensors = completed sources (+ the partial sum from the second sublayer on)
+            n = ops.depth_read_norm(list(tensors), layer.kimi_attn_read.query, layer.kimi_attn_read.value_gains,
+                                    layer.attn_norm.weight, layer.kimi_attn_read.eps, layer.attn_norm.eps, cd, **kc)
+            attn = layer.attention(n, ctx, cd) if cache is None else layer.attention_step(n, ctx, cd, cache[li])
+            return layer.drop(attn.float().sum(dim=1), ctx.B)
+
+        def expert_part(layer, *tensors):
+            # tensors = completed sources + the partial sum
+            n = ops.depth_read_norm(list(tensors), layer.kimi_mlp_read.query, layer.kimi_mlp_read.value_gains,
+                                    layer.mlp_norm.weight, layer.kimi_mlp_read.eps, layer.mlp_norm.eps, cd, **kc)
+            priv, shared, path, aux = layer.experts(n, ctx, cd)
+            return layer.drop(self._merged_expert_update(priv, shared, path, cd), ctx.B), aux
+
+        def one_layer(layer, li, partial, *srcs):
+            read = srcs if partial is None else (*srcs, partial)
+            update = rung.region("half", attn_part, layer, li, *read)
+            partial = update if partial is None else partial + update
+            update, aux = rung.region("half", expert_part, layer, *srcs, partial)
+            return partial + update, aux
+
         partial: Tensor | None = None
         layer_aux = []
         for li, layer in enumerate(self.layers[:count]):
-            read = list(sources) if partial is None else [*sources, partial]
-            n = ops.depth_read_norm(read, layer.kimi_attn_read.query, layer.kimi_attn_read.value_gains,
-                                    layer.attn_norm.weight, layer.kimi_attn_read.eps, layer.attn_norm.eps, cd, **kc)
-            attn = layer.attention(n, ctx, cd) if cache is None else layer.attention_step(n, ctx, cd, cache[li])
-            update = layer.drop(attn.float().sum(dim=1), ctx.B)
-            partial = update if partial is None else partial + update
-            n = ops.depth_read_norm([*sources, partial], layer.kimi_mlp_read.query, layer.kimi_mlp_read.value_gains,
-                                    layer.mlp_norm.weight, layer.kimi_mlp_read.eps, layer.mlp_norm.eps, cd, **kc)
-            priv, shared, path, aux = layer.experts(n, ctx, cd)
-            partial = partial + layer.drop(self._merged_expert_update(priv, shared, path, cd), ctx.B)
+            # the same rungs as the column layers: a layer, or each of its halves, is a recomputed region
+            partial, aux = rung.region("layer", one_layer, layer, li, partial, *sources)
             layer_aux.append(aux)
         return partial, layer_aux
 

@@ -222,6 +222,55 @@ def test_every_recompute_rung_changes_nothing(family, rung, tiny_scale, monkeypa
     assert c0.keys() == c1.keys() and all(torch.equal(c0[k], c1[k]) for k in c0)
 
 
+_RUNG_VARIANTS = {
+    "merged_and_trailing": dict(block_column_blocks=[1, 2, 6], block_column_trailing_layers=1),
+    "kimi_multi_column": dict(block_residual_mode="attn_res_kimi", block_column_head_only=False,
+                              block_column_include_aggregate=False, block_column_deviation_sources=False,
+                              block_column_gain_init=1.0),
+    "wide_reads": dict(block_column_head_only=False, block_column_trailing_layers=1),
+}
+
+
+@pytest.mark.parametrize("rung", list(LADDER))
+@pytest.mark.parametrize("variant", list(_RUNG_VARIANTS))
+def test_recompute_rungs_change_nothing_in_the_other_topologies(variant, rung, tiny_scale, monkeypatch):
+    """The recompute ladder inside merged layers (a layer or each of its halves is a region) and inside
+    column-resolved reads (a layer is a region): same loss, gradients and routing statistics as the plain step, in
+    training mode with routing noise."""
+
+    import dataclasses as dc
+    ids = torch.randint(0, 100263, (2, 48))
+    flags = sorted({k for v in LADDER.values() for k in v})
+    cfg = tiny_scale.build_experiment("nestor", "tiny").jobs[0].model
+    cfg = dc.replace(cfg, backbone_config=dc.replace(cfg.backbone_config, **_RUNG_VARIANTS[variant]))
+
+    def run(env):
+        for k in flags:
+            monkeypatch.delenv(k, raising=False)
+        for k, v in env.items():
+            monkeypatch.setenv(k, v)
+        torch.manual_seed(0)
+        m = Model.from_config(cfg).train()
+        with torch.no_grad():
+            for n, p in m.named_parameters():
+                if "query" in n:
+                    p.normal_(0, 0.3)
+        torch.manual_seed(3)                      # router noise
+        noises = [torch.randn(ids.numel(), b.spec.G) if b.spec.G > 1 else None for b in m.backbone.blocks]
+        out = m(ids, noises=noises)
+        loss = F.cross_entropy(out.pred.reshape(-1, out.pred.shape[-1]).float(), ids.reshape(-1))
+        loss.backward()
+        return loss.detach(), {n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None}, \
+            router_counts(m.backbone, out.aux)
+
+    l0, g0, c0 = run({})
+    l1, g1, c1 = run(LADDER[rung])
+    assert torch.allclose(l0, l1, atol=1e-6) and g0.keys() == g1.keys()
+    for n in g0:
+        assert torch.allclose(g0[n], g1[n], atol=2e-6, rtol=1e-5), n
+    assert c0.keys() == c1.keys() and all(torch.equal(c0[k], c1[k]) for k in c0)
+
+
 def test_recompute_predraws_router_noise(tiny_scale, monkeypatch):
     """Without caller-supplied noise a recomputed step still repeats its routing exactly in the backward pass."""
 
