@@ -45,7 +45,9 @@ def main(argv: list[str] | None = None) -> None:
     a.output.parent.mkdir(parents=True, exist_ok=True)
     tokens = docs = 0
     init = (a.tokenizer, a.min_doc_tokens, a.max_doc_tokens)
-    with open(a.output, "wb") as out, mp.Pool(a.workers, initializer=init_tokenizer_worker, initargs=init) as pool:
+    # fresh interpreters for the workers: forking a process that already runs library threads can deadlock the child
+    ctx = mp.get_context("spawn")
+    with open(a.output, "wb") as out, ctx.Pool(a.workers, initializer=init_tokenizer_worker, initargs=init) as pool:
         for ids, kept in pool.imap(encode_documents, batches(files, a.text_key, a.batch_docs)):
             ids.tofile(out)
             tokens += int(ids.size)
