@@ -1,0 +1,82 @@
+"""Property tests (random shapes) of the dispatch plans and the routing op: the invariants the kernels rely on hold for
+every batch size, sequence length, column count and top-k, including positions handed in explicitly."""
+
+import pytest
+import torch
+from hypothesis import given, settings, strategies as st
+
+from nestor_b200.ops import reference as R
+
+_shapes = st.tuples(st.integers(1, 4), st.integers(1, 33), st.integers(1, 9)).flatmap(
+    lambda t: st.tuples(st.just(t[0]), st.just(t[1]), st.just(t[2]), st.integers(1, t[2]), st.integers(0, 2**31 - 1)))
+
+
+@settings(max_examples=40, deadline=None)
+@given(_shapes)
+def test_column_plan_invariants(shape):
+    B, S, G, k, seed = shape
+    g = torch.Generator().manual_seed(seed)
+    idx = torch.rand(B, S, G, generator=g).topk(k, dim=-1).indices
+    plan = R.build_column_plan(idx, G)
+    rows = B * S * k
+    tok, slot = plan.tok_of_row.long(), plan.slot_of_row.long()
+    assert plan.rows == rows and plan.k == k and plan.G == G
+    assert torch.equal(plan.row_of_slot.long()[tok, slot], torch.arange(rows))          # inverse maps agree
+    assert sorted(plan.row_of_slot.reshape(-1).tolist()) == list(range(rows))            # bijection
+    seg = plan.seg_start.long()
+    assert seg[0] == 0 and seg[-1] == rows and len(seg) == G * B + 1 and (seg[1:] >= seg[:-1]).all()
+    # every row sits in the segment of (its column, its sequence), in token order inside the segment
+    col = idx.reshape(B * S, k)[tok, slot]
+    want_segment = col * B + tok // S
+    got_segment = torch.searchsorted(seg, torch.arange(rows), right=True) - 1
+    assert torch.equal(got_segment, want_segment)
+    same = got_segment[1:] == got_segment[:-1]
+    assert (tok[1:][same] > tok[:-1][same]).all()
+    assert torch.equal(plan.pos_of_row.long(), tok % S)
+    assert torch.equal(plan.col_start.long(), seg[::B])
+
+
+@settings(max_examples=25, deadline=None)
+@given(_shapes)
+def test_column_plan_carries_explicit_positions(shape):
+    B, S, G, k, seed = shape
+    g = torch.Generator().manual_seed(seed)
+    idx = torch.rand(B, S, G, generator=g).topk(k, dim=-1).indices
+    pos = torch.randint(0, 5000, (B, S), generator=g)
+    plan = R.build_column_plan(idx, G, pos)
+    assert torch.equal(plan.pos_of_row.long(), pos.reshape(-1)[plan.tok_of_row.long()])
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.integers(1, 60), st.integers(1, 4), st.integers(1, 12), st.integers(0, 2**31 - 1))
+def test_expert_plan_invariants(T, slots, E, seed):
+    g = torch.Generator().manual_seed(seed)
+    ids = torch.randint(0, E, (T, slots), generator=g)
+    plan = R.build_expert_plan(ids, E)
+    flat = ids.reshape(-1)
+    order, inv, off = plan.order.long(), plan.inv.long(), plan.offsets.long()
+    assert plan.n == T * slots and plan.slots == slots and plan.E == E
+    assert torch.equal(inv[order], torch.arange(flat.numel())) and torch.equal(order[inv], torch.arange(flat.numel()))
+    assert off[0] == 0 and off[-1] == flat.numel() and torch.equal(off.diff(), torch.bincount(flat, minlength=E))
+    sorted_ids = flat[order]
+    assert (sorted_ids[1:] >= sorted_ids[:-1]).all()
+    same = sorted_ids[1:] == sorted_ids[:-1]
+    assert (order[1:][same] > order[:-1][same]).all()                                   # stable inside an expert
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.integers(1, 40), st.integers(1, 10), st.integers(0, 2**31 - 1), st.sampled_from(["renorm", "switch"]))
+def test_routing_invariants(T, C, seed, mode):
+    g = torch.Generator().manual_seed(seed)
+    k = int(torch.randint(1, C + 1, (1,), generator=g))
+    scores, bias = torch.randn(T, C, generator=g), torch.randn(C, generator=g)
+    idx, gates = R.route_topk(scores, bias, k, mode)
+    assert idx.shape == gates.shape == (T, k)
+    assert all(len(set(row)) == k for row in idx.tolist())                               # k distinct choices
+    assert torch.equal(idx.sort(-1).values, (scores + bias).topk(k).indices.sort(-1).values)   # the bias only selects
+    if mode == "renorm":
+        assert torch.allclose(gates.sum(-1), torch.ones(T), atol=1e-5)
+        assert torch.allclose(gates, torch.softmax(scores.gather(-1, idx), -1), atol=1e-6)
+    else:
+        assert torch.allclose(gates, torch.softmax(scores, -1).gather(-1, idx), atol=1e-6)
+        assert (gates.sum(-1) <= 1 + 1e-5).all()
