@@ -80,3 +80,69 @@ def test_routing_invariants(T, C, seed, mode):
     else:
         assert torch.allclose(gates, torch.softmax(scores, -1).gather(-1, idx), atol=1e-6)
         assert (gates.sum(-1) <= 1 + 1e-5).all()
+
+
+@settings(max_examples=12, deadline=None)
+@given(st.integers(1, 3), st.integers(1, 17), st.integers(1, 5), st.integers(0, 2**31 - 1), st.booleans())
+def test_column_attention_against_the_masked_definition(B, S, G, seed, causal):
+    """Column attention over the packed plan equals the definition written with dense masks: token ``t`` attends, in
+    column ``c``, to the members of ``c`` in its own sequence (only earlier ones and itself when causal)."""
+
+    g = torch.Generator().manual_seed(seed)
+    k = int(torch.randint(1, G + 1, (1,), generator=g))
+    H, hd, d = 2, 4, 12
+    n = torch.randn(B * S, d, generator=g)
+    idx = torch.rand(B, S, G, generator=g).topk(k, -1).indices
+    gates = torch.rand(B * S, k, generator=g)
+    wqkv = torch.randn(G, 3 * H * hd, d, generator=g) * 0.3
+    wo = torch.randn(G, d, H * hd, generator=g) * 0.3
+    plan = R.build_column_plan(idx, G)
+    got = R.column_attention(n, plan, gates, wqkv, wo, H, hd, 10000.0, torch.float32, causal=causal)
+    cos, sin = R.rope_tables(torch.arange(S).repeat(B), hd, 10000.0)
+    flat = idx.reshape(B * S, k)
+    want = torch.zeros(B * S, k, d)
+    inner = H * hd
+    for c in range(G):
+        qkv = n @ wqkv[c].t()
+        q = R.apply_rope(qkv[:, :inner].reshape(-1, H, hd), cos, sin)
+        kk = R.apply_rope(qkv[:, inner:2 * inner].reshape(-1, H, hd), cos, sin)
+        v = qkv[:, 2 * inner:].reshape(-1, H, hd)
+        member = (flat == c).any(-1)                                                      # [T]
+        for b in range(B):
+            rows = torch.arange(b * S, (b + 1) * S)
+            m = member[rows]
+            if not m.any():
+                continue
+            sc = torch.einsum("thd,shd->hts", q[rows], kk[rows]) / hd
+            mask = m.unsqueeze(0) & m.unsqueeze(1)                                        # members see members
+            if causal:
+                mask = mask & torch.ones(S, S, dtype=torch.bool).tril()
+            p = torch.softmax(sc.masked_fill(~mask, float("-inf")), dim=-1).nan_to_num(0.0)
+            o = torch.einsum("hts,shd->thd", p, v[rows]).reshape(S, inner) @ wo[c].t()
+            for j in range(k):
+                sel = flat[rows, j] == c
+                want[rows[sel], j] = o[sel] * gates[rows[sel], j].unsqueeze(-1)
+    assert torch.allclose(got, want, atol=2e-4), float((got - want).abs().max())
+
+
+@settings(max_examples=20, deadline=None)
+@given(st.integers(1, 20), st.integers(1, 6), st.sampled_from([1, 2, 3]), st.integers(0, 2**31 - 1),
+       st.sampled_from(["swiglu", "gelu", "relu", "tanh"]))
+def test_expert_bank_against_a_per_token_loop(T, E, group, seed, activation):
+    g = torch.Generator().manual_seed(seed)
+    d, h = 6, 5
+    slots = group * int(torch.randint(1, 3, (1,), generator=g))
+    x = torch.randn(T, d, generator=g)
+    ids = torch.randint(0, E, (T, slots), generator=g)
+    w = torch.rand(T, slots, generator=g)
+    wu, wg, wd = (torch.randn(*s, generator=g) * 0.4 for s in ((E, d, h), (E, d, h), (E, h, d)))
+    gated = activation == "swiglu"
+    got = R.expert_bank(x, R.build_expert_plan(ids, E), w, wu, wg if gated else None, wd, torch.float32, group, activation)
+    want = torch.zeros(T, slots // group, d)
+    for t in range(T):
+        for s in range(slots):
+            e = ids[t, s]
+            up = x[t] @ wu[e]
+            hid = torch.nn.functional.silu(x[t] @ wg[e]) * up if gated else R.POINTWISE_ACTIVATIONS[activation](up)
+            want[t, s // group] += w[t, s] * (hid @ wd[e])
+    assert torch.allclose(got, want, atol=1e-5)
