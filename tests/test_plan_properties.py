@@ -146,3 +146,41 @@ def test_expert_bank_against_a_per_token_loop(T, E, group, seed, activation):
             hid = torch.nn.functional.silu(x[t] @ wg[e]) * up if gated else R.POINTWISE_ACTIVATIONS[activation](up)
             want[t, s // group] += w[t, s] * (hid @ wd[e])
     assert torch.allclose(got, want, atol=1e-5)
+
+
+@settings(max_examples=25, deadline=None)
+@given(st.integers(1, 12), st.integers(1, 6), st.integers(1, 9), st.integers(0, 2**31 - 1), st.booleans())
+def test_depth_read_and_stream_identities(T, k, n_src, seed, per_source):
+    g = torch.Generator().manual_seed(seed)
+    d = 8
+    srcs = [torch.randn(T, d, generator=g) * float(torch.rand((), generator=g) * 3 + 0.1) for _ in range(n_src)]
+    q = torch.randn(n_src, d, generator=g) if per_source else torch.randn(d, generator=g)
+    gains = torch.rand(n_src + 2, generator=g) + 0.5
+    out = R.depth_read(srcs, q, gains)
+    r = [torch.rsqrt(s.pow(2).mean(-1) + 1e-6) for s in srcs]
+    z = torch.stack([ri * (s @ (q[i] if per_source else q)) for i, (s, ri) in enumerate(zip(srcs, r))], -1) / d ** 0.5
+    w = torch.softmax(z, -1) * gains[:n_src]
+    want = sum((w[:, i] * r[i]).unsqueeze(-1) * srcs[i] for i in range(n_src))
+    assert torch.allclose(out, want, atol=1e-5)
+    # rescaling a source changes nothing (unit-RMS keys and values), up to the epsilon floor
+    scaled = [s * 7.0 for s in srcs]
+    assert torch.allclose(R.depth_read(scaled, q, gains), out, atol=1e-3, rtol=1e-3)
+    # a zero query is the gain-weighted mean of the unit-RMS sources
+    zero = R.depth_read(srcs, torch.zeros_like(q), gains)
+    assert torch.allclose(zero, sum((gains[i] / n_src * r[i]).unsqueeze(-1) * srcs[i] for i in range(n_src)), atol=1e-5)
+    # the cache only removes repeated work
+    cache = R.DepthKeyCache(srcs[: max(1, n_src - 1)])
+    assert torch.equal(R.depth_read(srcs, q, gains, key_cache=cache), out)
+
+    # block exit: deviations sum to zero, the aggregate is the mean; layer_combine adds one update to both states
+    streams = torch.randn(T, k, d, generator=g)
+    dev, agg = R.block_exit(streams)
+    assert dev.shape == (k, T, d) and torch.allclose(dev.sum(0), torch.zeros(T, d), atol=1e-5)
+    assert torch.allclose(agg, streams.mean(1), atol=1e-6)
+    attn, pub = torch.randn(T, k, d, generator=g), torch.randn(T, d, generator=g)
+    priv, path = torch.randn(T, k, d, generator=g), torch.softmax(torch.randn(T, 2, generator=g), -1)
+    new_streams, running = R.layer_combine(attn, priv, pub, path, streams, streams.mean(1), torch.float32)
+    update = attn + path[:, 1:2].unsqueeze(-1) * priv + (path[:, 0:1] * pub).unsqueeze(1)
+    assert torch.allclose(new_streams, streams + update, atol=1e-5)
+    assert torch.allclose(running, new_streams.mean(1), atol=1e-5)                       # the running mean stays the mean
+    assert torch.allclose(R.mid_source(streams.mean(1), attn), (streams + attn).mean(1), atol=1e-5)
