@@ -172,6 +172,7 @@ def _trainer_rank(rank, world, port, q, sharded):
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
     from nestor_b200.models import Model
     from nestor_b200.train.trainer import Trainer
+    torch.set_num_threads(1)                          # repeatable reductions: the comparison does not depend on scheduling
     torch.manual_seed(0)
     job = _tiny_job(1)
     tr = Trainer(job, Model.from_config(job.model), [], device=torch.device("cpu"))
@@ -210,19 +211,24 @@ def test_trainer_on_two_ranks_matches_accumulation_in_one_process(sharded, monke
     from nestor_b200.models import Model
     from nestor_b200.models.nestor import add_router_counts
     from nestor_b200.train.trainer import Trainer
-    torch.manual_seed(0)
-    job = _tiny_job(2)
-    tr = Trainer(job, Model.from_config(job.model), [], device=torch.device("cpu"))
-    _quiet(tr)
-    start = tr.arena.master.clone().numpy()
-    want_norms = []
-    for step in range(2):
-        total = None
-        for shard in range(world):
-            ids = _tokens(shard, step)
-            loss, counts = tr.train_step((ids, ids))
-            total = add_router_counts(total, counts)
-        want_norms.append(float(tr.update_weights(total)))
+    threads = torch.get_num_threads()
+    torch.set_num_threads(1)
+    try:
+        torch.manual_seed(0)
+        job = _tiny_job(2)
+        tr = Trainer(job, Model.from_config(job.model), [], device=torch.device("cpu"))
+        _quiet(tr)
+        start = tr.arena.master.clone().numpy()
+        want_norms = []
+        for step in range(2):
+            total = None
+            for shard in range(world):
+                ids = _tokens(shard, step)
+                loss, counts = tr.train_step((ids, ids))
+                total = add_router_counts(total, counts)
+            want_norms.append(float(tr.update_weights(total)))
+    finally:
+        torch.set_num_threads(threads)
     want = tr.arena.master.clone().numpy()
     want_bias = torch.cat([r.choice_bias.flatten() for _, r in tr.model.backbone.routers()]).numpy()
     assert abs(want_bias).max() > 0                      # the balancing update really moved the biases
