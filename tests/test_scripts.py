@@ -137,3 +137,26 @@ def test_dclm_shard_tree_to_token_file(tmp_path, capsys):
     assert read_bin_meta(out)["num_tokens"] >= 30                              # (checked once per batch of documents)
     with pytest.raises(SystemExit):
         preprocess_dclm.main(["--dclm-root", str(tmp_path / "nothing"), "--out", str(out)])
+
+
+def test_describe_an_experiment_without_running_it(capsys, monkeypatch):
+    """``scripts.describe`` builds the model on the meta device and reports geometry, parameter counts by optimizer,
+    tokens per step, FLOPs per token and the per-GPU footprint; the numbers are those of the registry tests."""
+
+    from nestor_b200.scripts import describe
+    monkeypatch.delenv("DCLM_BLOCK_SIZE", raising=False)
+    info = describe.describe("nestor_200m", world=8)
+    assert info["parameters"]["total"] == 761_788_781 and info["tokens_per_step"] == 524_288
+    assert sum(info["parameters"]["by_optimizer"].values()) == info["parameters"]["trainable"]
+    assert [b["columns_per_token"] for b in info["blocks"]] == [3, 4, 5, 6, 6, 7, 8]
+    assert [b["exports"] for b in info["blocks"]] == [4, 5, 6, 7, 7, 8, 9]
+    assert info["flops_per_token"]["training"] == 3 * info["flops_per_token"]["forward"]
+    assert abs(info["per_gpu_gib"]["parameter_arenas"] - 761_788_781 * 10 / 2**30) < 0.01
+    one = describe.describe("nestor_200m", world=1)["per_gpu_gib"]["optimizer_state"]
+    assert abs(one / 8 - info["per_gpu_gib"]["optimizer_state"]) < 0.01
+    assert describe.main(["--experiment", "dense_100m"]) == 0
+    text = capsys.readouterr().out
+    assert "dense MLP" in text and "attn_res_kimi" in text and "141,011,709" in text
+    assert describe.main(["--experiment", "moe_100m", "--json"]) == 0
+    out = capsys.readouterr().out
+    assert json.loads(out[out.index("{"):])["blocks"][0]["experts"].startswith("bank: ")
