@@ -160,3 +160,35 @@ def test_describe_an_experiment_without_running_it(capsys, monkeypatch):
     assert describe.main(["--experiment", "moe_100m", "--json"]) == 0
     out = capsys.readouterr().out
     assert json.loads(out[out.index("{"):])["blocks"][0]["experts"].startswith("bank: ")
+
+
+def test_checkpoint_layout_conversion_round_trip(tmp_path, monkeypatch, capsys):
+    """Stacked banks -> one weight set per expert -> stacked again is the identity; the per-expert file has the key
+    names of the reference's unstacked layout and loads into a fresh model; optimizer state is dropped."""
+
+    from nestor_b200.eval.loading import load_experiment_checkpoint
+    from nestor_b200.scripts import convert_checkpoint
+    data = write_synthetic_bin(tmp_path / "train.bin", 64 * 40, 100_277, doc_len_range=(16, 64))
+    monkeypatch.setenv("DCLM_DATA_PATH", str(data))
+    monkeypatch.setenv("DCLM_BLOCK_SIZE", "64")
+    base = _train(tmp_path, monkeypatch, "base", 1)
+    capsys.readouterr()
+    per, back = tmp_path / "per_expert.pt", tmp_path / "stacked.pt"
+    assert convert_checkpoint.main(["--experiment", "nestor_tiny", "--checkpoint", str(base), "--output", str(per),
+                                    "--to", "per-expert"]) == 0
+    assert convert_checkpoint.main(["--experiment", "nestor_tiny", "--checkpoint", str(per), "--output", str(back),
+                                    "--to", "stacked"]) == 0
+    a = torch.load(base, weights_only=False)
+    b = torch.load(per, weights_only=False)
+    c = torch.load(back, weights_only=False)
+    assert "optimizer" in a and "optimizer" not in b and b["step"] == a["step"]
+    assert not any(".stacked_" in k for k in b["model"])
+    assert "backbone.blocks.0.layers.0.expert_pool.private_experts.3.1.gate.weight" in b["model"]
+    assert "backbone.blocks.0.layers.0.expert_pool.public_experts.2.layers.1.weight" in b["model"]
+    assert set(c["model"]) == set(a["model"]) and all(torch.equal(c["model"][k], a["model"][k]) for k in a["model"])
+    model, info = load_experiment_checkpoint("nestor_tiny", per)          # either layout loads
+    assert info["stacked"] is False and not info["skipped"]
+    want = a["model"]["backbone.blocks.0.layers.0.expert_pool.stacked_private.w_up"]
+    assert torch.equal(model.state_dict()["backbone.blocks.0.layers.0.expert_pool.stacked_private.w_up"], want)
+    with pytest.raises(ValueError, match="already"):
+        convert_checkpoint.convert(a, "nestor_tiny", "stacked")
