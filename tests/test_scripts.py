@@ -192,3 +192,27 @@ def test_checkpoint_layout_conversion_round_trip(tmp_path, monkeypatch, capsys):
     assert torch.equal(model.state_dict()["backbone.blocks.0.layers.0.expert_pool.stacked_private.w_up"], want)
     with pytest.raises(ValueError, match="already"):
         convert_checkpoint.convert(a, "nestor_tiny", "stacked")
+
+
+def test_heldout_evaluation_of_the_weight_average(tmp_path, monkeypatch, capsys):
+    """A run with ``NESTOR_EMA_DECAY`` stores the averaged weights beside the live ones; ``eval_heldout --ema`` scores
+    the average (a different number), in either bank layout."""
+
+    from nestor_b200.scripts import eval_heldout
+    data = write_synthetic_bin(tmp_path / "train.bin", 64 * 40, 100_277, doc_len_range=(16, 64))
+    held = write_synthetic_bin(tmp_path / "held.bin", 64 * 8, 100_277, seed=2, doc_len_range=(32, 64))
+    monkeypatch.setenv("DCLM_DATA_PATH", str(data))
+    monkeypatch.setenv("DCLM_BLOCK_SIZE", "64")
+    monkeypatch.setenv("NESTOR_EMA_DECAY", "0.5")
+    ckpt = _train(tmp_path, monkeypatch, "ema", 3)
+    capsys.readouterr()
+    payload = torch.load(ckpt, weights_only=False)
+    assert set(payload["ema"]) == {k for k, v in payload["model"].items() if k in payload["ema"]}
+    assert any(not torch.equal(payload["ema"][k], payload["model"][k]) for k in payload["ema"])
+    scores = {}
+    for flag in ((), ("--ema",)):
+        eval_heldout.main(["--experiment", "nestor_tiny", "--checkpoint", str(ckpt), "--data", str(held),
+                           "--block-size", "64", "--max-windows", "4", *flag])
+        out = capsys.readouterr().out
+        scores[flag] = json.loads(out[out.index("{"):])["cross_entropy"]
+    assert scores[()] != scores[("--ema",)] and all(5.0 < v < 13.0 for v in scores.values())
