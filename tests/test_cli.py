@@ -1,13 +1,10 @@
 """The command line: registry listing, error paths, the .env file, and an experiment of a train job followed by an
 eval job that reads the checkpoint the train job wrote."""
 
-import dataclasses as dc
 import json
 import os
 from pathlib import Path
 
-import pytest
-import torch
 
 from nestor_b200.data.datasets import write_synthetic_bin
 

@@ -1,7 +1,6 @@
 """Property tests (random shapes) of the dispatch plans and the routing op: the invariants the kernels rely on hold for
 every batch size, sequence length, column count and top-k, including positions handed in explicitly."""
 
-import pytest
 import torch
 from hypothesis import given, settings, strategies as st
 

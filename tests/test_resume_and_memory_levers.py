@@ -4,7 +4,6 @@ cache behind activation offload, and the once-only out-of-memory snapshot."""
 import pickle
 import time
 
-import pytest
 import torch
 
 from nestor_b200.data.datasets import write_synthetic_bin

@@ -7,7 +7,6 @@ import sys
 import types
 import zipfile
 
-import pytest
 
 from nestor_b200.pipelines import RunContext
 

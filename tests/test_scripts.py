@@ -5,7 +5,6 @@ import gzip
 import json
 import time
 
-import numpy as np
 import pytest
 import torch
 

@@ -5,7 +5,6 @@ import dataclasses as dc
 
 import pytest
 import torch
-import torch.nn.functional as F
 
 from nestor_b200.models import Model
 from nestor_b200.ops import reference as R
