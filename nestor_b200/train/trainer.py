@@ -40,6 +40,7 @@ from nestor_b200.train.flops import train_flops_per_token
 from nestor_b200.train.losses import LossOutput, build_loss
 from nestor_b200.train.optim import build_optimizer, build_scheduler
 from nestor_b200.utils.distributed import barrier, get_rank, get_world_size, is_main_process
+from nestor_b200.utils.batches import split_supervised_batch
 from nestor_b200.utils.logging import get_logger, log_metrics
 from nestor_b200.utils.timing import PROCESS_START
 
@@ -187,6 +188,7 @@ class Trainer:
         keeps eager launches; activation offload and the eager profiler also disable capture.
         """
 
+        batch = split_supervised_batch(batch)      # (inputs, targets) pairs or inputs/targets, inputs/labels, x/y mappings
         with self._nvtx("micro_batch"):
             if self._graph_enabled and self.model.training:
                 return self._graphed_step(batch)

@@ -75,3 +75,33 @@ def test_seed_covers_every_generator(monkeypatch):
     torch.backends.cudnn.deterministic = False
     set_seed(1)
     assert torch.backends.cudnn.benchmark
+
+
+def test_supervised_batches_in_every_accepted_form():
+    from nestor_b200.utils.batches import split_supervised_batch
+    x, y = torch.arange(6).view(2, 3), torch.arange(6).view(2, 3) + 1
+    for batch in ((x, y), [x, y], {"inputs": x, "targets": y}, {"inputs": x, "labels": y}, {"x": x, "y": y, "meta": 1}):
+        a, b = split_supervised_batch(batch)
+        assert a is x and b is y
+    assert split_supervised_batch((["text a", "text b"], y))[0] == ["text a", "text b"]   # inputs may be anything
+    for bad in ((x, y, x), {"inputs": x}, {"a": x, "b": y}, x, (x, [1, 2])):
+        with pytest.raises(TypeError):
+            split_supervised_batch(bad)
+
+
+def test_trainer_accepts_mapping_batches(monkeypatch):
+    from nestor_b200.experiments.tiny import nestor_tiny
+    from nestor_b200.models import Model
+    from nestor_b200.train.trainer import Trainer
+    monkeypatch.setenv("DCLM_BLOCK_SIZE", "64")
+    torch.manual_seed(0)
+    job = nestor_tiny().jobs[0]
+    tr = Trainer(job, Model.from_config(job.model), [], device=torch.device("cpu"))
+    tr.model.eval(); tr.model.training = True
+    for blk in tr.model.backbone.blocks:
+        blk.freeze_routing_noise = True
+    ids = torch.randint(0, 100_277, (2, 64))
+    a, _ = tr.train_step((ids, ids))
+    tr.arena.zero_grad()
+    b, _ = tr.train_step({"inputs": ids, "labels": ids})
+    assert float(a.total) == float(b.total)
