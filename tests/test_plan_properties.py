@@ -183,3 +183,38 @@ def test_depth_read_and_stream_identities(T, k, n_src, seed, per_source):
     assert torch.allclose(new_streams, streams + update, atol=1e-5)
     assert torch.allclose(running, new_streams.mean(1), atol=1e-5)                       # the running mean stays the mean
     assert torch.allclose(R.mid_source(streams.mean(1), attn), (streams + attn).mean(1), atol=1e-5)
+
+
+@settings(max_examples=20, deadline=None)
+@given(st.integers(1, 40), st.integers(2, 30), st.integers(1, 16), st.integers(0, 2**31 - 1))
+def test_chunked_head_loss_is_the_full_cross_entropy(T, V, chunk, seed):
+    g = torch.Generator().manual_seed(seed)
+    d = 6
+    h = torch.randn(T, d, generator=g, requires_grad=True)
+    w = torch.randn(V, d, generator=g, requires_grad=True)
+    tg = torch.randint(0, V, (T,), generator=g)
+    tg[torch.rand(T, generator=g) < 0.3] = -100                      # ignored positions (padding, the last token)
+    ls, cnt = R.lm_head_ce(h, w, tg, 0.25, torch.float32, chunk_rows=chunk)
+    want = torch.nn.functional.cross_entropy((h @ w.t()) * 0.25, tg, ignore_index=-100, reduction="sum")
+    assert int(cnt) == int((tg != -100).sum())
+    assert torch.allclose(ls, want, atol=1e-4)
+    if int(cnt):
+        g1 = torch.autograd.grad(ls, [h, w])
+        g2 = torch.autograd.grad(want, [h, w])
+        assert all(torch.allclose(a, b, atol=1e-5) for a, b in zip(g1, g2))
+
+
+@settings(max_examples=15, deadline=None)
+@given(st.integers(2, 24), st.integers(2, 24), st.integers(1, 3), st.integers(0, 2**31 - 1))
+def test_newton_schulz_contracts_the_spread_of_singular_values(rows, cols, batch, seed):
+    """Five quintic steps move every singular value of a (batch of) matrices into a band around one, for wide, tall
+    and square shapes alike (the update direction Muon applies)."""
+
+    g = torch.Generator().manual_seed(seed)
+    m = torch.randn(batch, rows, cols, generator=g)
+    out = R.newton_schulz(m, steps=5).float()
+    assert out.shape == m.shape and torch.isfinite(out).all()
+    sv = torch.linalg.svdvals(out)
+    k = min(rows, cols)
+    assert sv.shape[-1] == k and float(sv.max()) < 1.35
+    assert float(sv.median()) > 0.3                                   # the bulk has been lifted towards one
