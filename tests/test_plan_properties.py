@@ -10,7 +10,7 @@ _shapes = st.tuples(st.integers(1, 4), st.integers(1, 33), st.integers(1, 9)).fl
     lambda t: st.tuples(st.just(t[0]), st.just(t[1]), st.just(t[2]), st.integers(1, t[2]), st.integers(0, 2**31 - 1)))
 
 
-@settings(max_examples=40, deadline=None)
+@settings(max_examples=40, deadline=None, derandomize=True)
 @given(_shapes)
 def test_column_plan_invariants(shape):
     B, S, G, k, seed = shape
@@ -35,7 +35,7 @@ def test_column_plan_invariants(shape):
     assert torch.equal(plan.col_start.long(), seg[::B])
 
 
-@settings(max_examples=25, deadline=None)
+@settings(max_examples=25, deadline=None, derandomize=True)
 @given(_shapes)
 def test_column_plan_carries_explicit_positions(shape):
     B, S, G, k, seed = shape
@@ -46,7 +46,7 @@ def test_column_plan_carries_explicit_positions(shape):
     assert torch.equal(plan.pos_of_row.long(), pos.reshape(-1)[plan.tok_of_row.long()])
 
 
-@settings(max_examples=40, deadline=None)
+@settings(max_examples=40, deadline=None, derandomize=True)
 @given(st.integers(1, 60), st.integers(1, 4), st.integers(1, 12), st.integers(0, 2**31 - 1))
 def test_expert_plan_invariants(T, slots, E, seed):
     g = torch.Generator().manual_seed(seed)
@@ -63,7 +63,7 @@ def test_expert_plan_invariants(T, slots, E, seed):
     assert (order[1:][same] > order[:-1][same]).all()                                   # stable inside an expert
 
 
-@settings(max_examples=40, deadline=None)
+@settings(max_examples=40, deadline=None, derandomize=True)
 @given(st.integers(1, 40), st.integers(1, 10), st.integers(0, 2**31 - 1), st.sampled_from(["renorm", "switch"]))
 def test_routing_invariants(T, C, seed, mode):
     g = torch.Generator().manual_seed(seed)
@@ -81,7 +81,7 @@ def test_routing_invariants(T, C, seed, mode):
         assert (gates.sum(-1) <= 1 + 1e-5).all()
 
 
-@settings(max_examples=12, deadline=None)
+@settings(max_examples=12, deadline=None, derandomize=True)
 @given(st.integers(1, 3), st.integers(1, 17), st.integers(1, 5), st.integers(0, 2**31 - 1), st.booleans())
 def test_column_attention_against_the_masked_definition(B, S, G, seed, causal):
     """Column attention over the packed plan equals the definition written with dense masks: token ``t`` attends, in
@@ -124,7 +124,7 @@ def test_column_attention_against_the_masked_definition(B, S, G, seed, causal):
     assert torch.allclose(got, want, atol=2e-4), float((got - want).abs().max())
 
 
-@settings(max_examples=20, deadline=None)
+@settings(max_examples=20, deadline=None, derandomize=True)
 @given(st.integers(1, 20), st.integers(1, 6), st.sampled_from([1, 2, 3]), st.integers(0, 2**31 - 1),
        st.sampled_from(["swiglu", "gelu", "relu", "tanh"]))
 def test_expert_bank_against_a_per_token_loop(T, E, group, seed, activation):
@@ -147,7 +147,7 @@ def test_expert_bank_against_a_per_token_loop(T, E, group, seed, activation):
     assert torch.allclose(got, want, atol=1e-5)
 
 
-@settings(max_examples=25, deadline=None)
+@settings(max_examples=25, deadline=None, derandomize=True)
 @given(st.integers(1, 12), st.integers(1, 6), st.integers(1, 9), st.integers(0, 2**31 - 1), st.booleans())
 def test_depth_read_and_stream_identities(T, k, n_src, seed, per_source):
     g = torch.Generator().manual_seed(seed)
@@ -185,7 +185,7 @@ def test_depth_read_and_stream_identities(T, k, n_src, seed, per_source):
     assert torch.allclose(R.mid_source(streams.mean(1), attn), (streams + attn).mean(1), atol=1e-5)
 
 
-@settings(max_examples=20, deadline=None)
+@settings(max_examples=20, deadline=None, derandomize=True)
 @given(st.integers(1, 40), st.integers(2, 30), st.integers(1, 16), st.integers(0, 2**31 - 1))
 def test_chunked_head_loss_is_the_full_cross_entropy(T, V, chunk, seed):
     g = torch.Generator().manual_seed(seed)
@@ -204,7 +204,7 @@ def test_chunked_head_loss_is_the_full_cross_entropy(T, V, chunk, seed):
         assert all(torch.allclose(a, b, atol=1e-5) for a, b in zip(g1, g2))
 
 
-@settings(max_examples=15, deadline=None)
+@settings(max_examples=15, deadline=None, derandomize=True)
 @given(st.integers(2, 24), st.integers(2, 24), st.integers(1, 3), st.integers(0, 2**31 - 1))
 def test_newton_schulz_contracts_the_spread_of_singular_values(rows, cols, batch, seed):
     """Five quintic steps move every singular value of a (batch of) matrices into a band around one, for wide, tall
