@@ -1007,3 +1007,109 @@ def test_bidirectional_models_match_reference(family, tiny_scale, monkeypatch):
     valid[1, 40:] = False
     with pytest.raises(ValueError, match="padded"):
         mm(ids, valid=valid)
+
+
+def _sample_configuration(rng):
+    fam = rng.choice(["nestor", "moe"])
+    ch = {}
+    mode = rng.choice(["column", "kimi", "projection", "attn_res"])
+    if mode == "column":
+        combo = rng.choice([(False, False, False), (True, False, False), (True, True, False), (True, False, True), (True, True, True)])
+        ch.update(block_residual_mode="attn_res_column", block_column_include_aggregate=combo[0], block_column_deviation_sources=combo[1], block_column_head_only=combo[2])
+        if combo[0] and rng.random() < 0.4:
+            ch.update(block_column_mass_lambda=rng.choice([0.0, 0.3, 1.0]), block_column_gain_init=1.0)
+        else:
+            ch.update(block_column_gain_init=rng.choice([0.0, 0.5, 1.0]))
+        if rng.random() < 0.4: ch.update(block_column_head_query_per_source=True)
+        if rng.random() < 0.4: ch.update(block_column_trailing_layers=1)
+    else:
+        ch.update(block_residual_mode={"kimi": "attn_res_kimi", "projection": "projection", "attn_res": "attn_res"}[mode],
+                  block_column_include_aggregate=False, block_column_deviation_sources=False, block_column_head_only=False, block_column_gain_init=1.0)
+        if mode in ("projection", "attn_res") and rng.random() < 0.5: ch.update(residual_mode="attn_res")
+    if fam == "moe":
+        n = 4
+        G = rng.choice([1, 3, 4])
+        k = [rng.randint(1, G) for _ in range(n)]
+        if mode == "column" and all(v == 1 for v in k):
+            k[0] = G if G > 1 else 1
+            if G == 1: return None
+        epg = [rng.randint(2, 6) for _ in range(n)]
+        shared = [rng.randint(0, e) for e in epg]
+        top = [rng.randint(1, e) for e in epg]
+        ch.update(num_groups=[G] * n, num_groups_per_token=k, block_num_heads=[2] * n, router_num_experts_per_group=epg,
+                  router_num_shared_experts=shared, router_num_experts_per_group_per_token=top,
+                  router_score_mlp_hidden_dims=[[16]] * n, router_noise_mlp_hidden_dims=[[16]] * n, attention_token_dispatch=True,
+                  block_mlp_activations=rng.choice(["swiglu", "gelu", "relu"]), router_num_dense_shared_experts=rng.choice([0, 1]))
+        if mode == "column" and rng.random() < 0.4: ch.update(block_column_blocks=sorted(rng.sample(range(n), rng.randint(1, n))))
+    else:
+        if mode == "column" and rng.random() < 0.4: ch.update(block_column_blocks=sorted(rng.sample(range(7), rng.randint(1, 7))))
+        if rng.random() < 0.3: ch.update(block_expert_pool_public_experts=0)
+    if rng.random() < 0.25: ch.update(causal=False)
+    if rng.random() < 0.3: ch.update(drop_path_rate=0.0)
+    return fam, ch
+
+
+def test_random_configuration_combinations_match_reference(tiny_scale, monkeypatch):
+    """Eight seeded random combinations of the configuration knobs (residual topology, column read / export variants,
+    subsets and trailing windows, gain inits, pools or banks with shared and column-specific experts, gated or pointwise
+    experts, always-on experts, causal or bidirectional): same keys, loss and gradients as the reference for each."""
+
+    import dataclasses as dc
+    import random
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "nestor").is_dir():
+        pytest.skip("reference package not installed under baseline/_ref")
+    monkeypatch.setenv("NESTOR_STACKED_EXPERT_BANKS", "1")
+    monkeypatch.setenv("NESTOR_DENSE_NO_ROUTER", "1")
+    monkeypatch.setenv("NESTOR_COLUMN_SLOT_UPDATES", "1")
+    monkeypatch.syspath_prepend(str(ref_root))
+    try:
+        from nestor.experiments import pretrain as RP
+        from nestor.models import Model as RefModel
+    except Exception as exc:
+        pytest.skip(f"reference import failed: {exc}")
+    P = tiny_scale
+    monkeypatch.setitem(RP.SCALES, "tiny", RP.Scale("tiny", 128, 4, 8, 512, 10, 2, 1024))
+    monkeypatch.setitem(RP.NESTOR_LAYERS, "tiny", (2, 1, 1, 1, 1, 1, 2))
+    monkeypatch.setitem(RP.NESTOR_PRIVATE_EXPERTS, "tiny", 3)
+    monkeypatch.setattr(RP, "NESTOR_MIN_PRIVATE_WIDTH", 24)
+    monkeypatch.setattr(RP, "BLOCK_SIZE", 64)
+    for fam in ("dense", "moe", "nestor"):
+        monkeypatch.setitem(RP.BATCH_SHAPE, (fam, "tiny"), (2, 1))
+    rng = random.Random(1)
+    compared = 0
+    for trial in range(8):
+        drawn = _sample_configuration(rng)
+        if drawn is None:
+            continue
+        fam, ch = drawn
+        torch.manual_seed(trial)
+        rcfg = {"moe": RP._moe, "nestor": RP._nestor}[fam]("tiny").jobs[0].model
+        rcfg = dc.replace(rcfg, backbone_config=dc.replace(rcfg.backbone_config, **ch))
+        rm = RefModel.from_config(rcfg).eval()
+        cfg = P.build_experiment(fam, "tiny").jobs[0].model
+        cfg = dc.replace(cfg, backbone_config=dc.replace(cfg.backbone_config, **ch))
+        mm = Model.from_config(cfg).eval()
+        assert set(mm.state_dict()) == set(rm.state_dict()), ch
+        with torch.no_grad():
+            for n, p in rm.named_parameters():
+                if "query" in n:
+                    p.normal_(0, 0.1)
+        mm.load_state_dict(rm.state_dict(), strict=True)
+        ids = torch.randint(0, 100263, (2, 64))
+        if ch.get("causal") is False:
+            x, pos, _ = rm.adapter(ids)
+            ref_pred = rm.head(rm.backbone(x, pos, torch.ones(2, 64, 64, dtype=torch.bool)))
+        else:
+            ref_pred = rm(ids).pred
+        lr = F.cross_entropy(ref_pred[:, :-1].reshape(-1, 100263), ids[:, 1:].reshape(-1))
+        lm = F.cross_entropy(mm(ids).pred[:, :-1].reshape(-1, 100263), ids[:, 1:].reshape(-1))
+        assert torch.allclose(lr, lm, atol=1e-5), (ch, float(lr), float(lm))
+        lr.backward(); lm.backward()
+        ref_grads = dict(rm.named_parameters())
+        for n, p in mm.named_parameters():
+            g1, g2 = ref_grads[n].grad, p.grad
+            if g1 is not None and g2 is not None and g1.norm() > 1e-4:
+                assert (g1 - g2).norm() / g1.norm() < 2e-3, (n, ch)
+        compared += 1
+    assert compared >= 6
