@@ -512,12 +512,13 @@ class Block(nn.Module):
     def forward(self, x: Tensor, sources: list[Tensor], B: int, S: int, cd: torch.dtype,
                 pos: Tensor | None, column_mode: bool, noise: Tensor | None = None,
                 cache: list | None = None, key_cache: Any = None) -> tuple[list[Tensor], Tensor, dict]:
-        """Run the block. ``x [T, d]`` feeds the router; ``sources`` are the completed aggregates. With ``cache`` (one
-        ``LayerKVCache`` per layer) the rows are one new token per sequence and attention runs against the cache.
+        """Run the block. ``x [T, d]`` feeds the router; ``sources`` are the completed depth sources its sublayers read
+        (one aggregate per earlier block, or every earlier export when the reads are column-resolved). With ``cache``
+        (one ``LayerKVCache`` per layer) the rows are one new token per sequence and attention runs against the cache.
 
-        Returns ``(exports, aggregate, aux)``: the depth sources this block contributes (``k``
-        deviations then the aggregate in column mode with ``k > 1``; the aggregate alone
-        otherwise), the aggregate (next block's router input), and routing indices.
+        Returns ``(exports, aggregate, aux)``: the depth sources this block contributes (in column mode with
+        ``k > 1``: the ``k`` columns, as deviations from their mean if the model re-bases them, then the mean if it is
+        exported; a single tensor otherwise), the aggregate (next block's router input), and routing indices.
         """
 
         s = self.spec
