@@ -41,3 +41,22 @@ def test_memory_recipe_rungs(experiment, length, want):
     out = subprocess.run(["bash", "-c", probe, "probe", experiment, str(length)], cwd=ROOT, env=env,
                          capture_output=True, text=True)
     assert out.stdout.split()[0] == "0"
+
+
+def test_every_flag_the_launchers_export_is_known_to_the_package():
+    """A flag exported by ``launch/*.sh`` is either read somewhere in the package or listed in the catalogue of
+    reference flags that have no effect here: no launcher line can silently go stale."""
+
+    import re
+    from nestor_b200.utils.flags import DIFFERENT, NO_EFFECT
+    read = set()
+    for f in (ROOT / "nestor_b200").rglob("*.py"):
+        read |= set(re.findall(r'"((?:NESTOR|DCLM|WANDB|CONTINUAL)_[A-Z0-9_]+)"', f.read_text()))
+    read |= set(re.findall(r'"((?:NESTOR|DCLM)_[A-Z0-9_]+)"', (ROOT / "bench.py").read_text()))
+    known = read | set(NO_EFFECT) | {name for name, _, _ in DIFFERENT}
+    exported = set()
+    for script in SCRIPTS:
+        exported |= set(re.findall(r"^\s*export\s+((?:NESTOR|DCLM)_[A-Z0-9_]+)=", script.read_text(), flags=re.M))
+    assert exported, "the launchers export their flags with `export NAME=...`"
+    unknown = sorted(exported - known)
+    assert not unknown, unknown
